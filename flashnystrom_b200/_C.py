@@ -1,0 +1,198 @@
+"""Host-side mirror of the reference's `flash_nystrom._C` extension module
+(pybind signatures: csrc/flash_nystrom.cu:629-690), backed by the C-ABI library.
+
+    forward(q, k, v, num_landmarks=64, newton_iter=6, kappa_star=0.0, use_tc_pinv=False,
+            need_scaled_qk=True) -> [output, q_s, k_s, q_tilde, k_tilde, k2inv, step2, lse1, lse2,
+                                     lse3, ns_iterates, k2_softmax, b_saved]
+    backward(dO, q_s, k_s, q_tilde, k_tilde, kernel2_inv, step2, lse1, lse2, lse3, ns_iterates,
+             k2_softmax, b_saved, v, output, num_landmarks, newton_iter, fast_dk2inv=True,
+             kappa_star=0.0) -> [dQ, dK, dV]
+
+Differences from the reference, all deliberate:
+  * no scaled copies of Q and K are made: the q_s / k_s slots hold the caller's own q and k
+    (the kernels fold the D^-1/4 scale in), so `need_scaled_qk` costs nothing either way;
+  * the landmark-sized saved tensors (q_tilde, k_tilde, step2, b_saved) are FP32 whatever the
+    input dtype;
+  * num_landmarks up to 128 and head_dim 16/32/64/128 are native;
+  * `use_tc_pinv` and `fast_dk2inv` are accepted and select nothing (FP32 always);
+  * there is no CPU path: tensors must live on a CUDA device of compute capability 10.x.
+All work is enqueued on torch's current stream of the inputs' device; nothing synchronises.
+"""
+import ctypes as C
+import math
+
+import torch
+
+from . import _lib
+
+_DTYPES = {torch.float32: _lib.FNB_F32, torch.float16: _lib.FNB_F16, torch.bfloat16: _lib.FNB_BF16}
+_flags = 0
+
+
+def set_force_generic(on: bool):
+    """Route 16-bit inputs through the CUDA-core FP32 kernels too (verification aid)."""
+    global _flags
+    _flags = _lib.FNB_FLAG_FORCE_GENERIC if on else 0
+
+
+def _shape_struct(B, H, N, D, m, J, dtype, kappa_star):
+    if dtype not in _DTYPES:
+        raise RuntimeError("Supported dtypes: float32, float16, bfloat16")
+    if not (isinstance(kappa_star, (int, float)) and math.isfinite(kappa_star) and kappa_star >= 0):
+        raise RuntimeError(f"kappa_star must be finite and >= 0 (got {kappa_star}); "
+                           "0 disables the Tikhonov ridge")
+    return _lib.Shape(int(B), int(H), int(N), int(D), int(m), int(J), _DTYPES[dtype],
+                      float(kappa_star), _flags)
+
+
+def _check_big(t, name, shape=None, dtype=None):
+    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor (flashnystrom_b200 has no CPU path)")
+    if not t.is_contiguous():
+        raise RuntimeError(f"{name} must be contiguous")
+    if shape is not None and tuple(t.shape) != tuple(shape):
+        raise RuntimeError(f"{name} shape mismatch: expected {tuple(shape)}, got {tuple(t.shape)}")
+    if dtype is not None and t.dtype != dtype:
+        raise RuntimeError(f"{name} must be {dtype}, got {t.dtype}")
+
+
+def _ptr(t):
+    return C.c_void_p(t.data_ptr())
+
+
+def _workspace(nbytes, device):
+    return torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=device)
+
+
+def forward(q, k, v, num_landmarks=64, newton_iter=6, kappa_star=0.0, use_tc_pinv=False,
+            need_scaled_qk=True):
+    lib = _lib.load()
+    for t, name in ((q, "q"), (k, "k"), (v, "v")):
+        _check_big(t, name)
+    if q.dim() != 4 or k.dim() != 4 or v.dim() != 4:
+        raise RuntimeError("q, k, v must be 4D (B, H, N, D)")
+    if not (q.dtype == k.dtype == v.dtype):
+        raise RuntimeError("q, k, v dtypes must match")
+    B, H, N, D = q.shape
+    _check_big(k, "k", (B, H, N, D))
+    _check_big(v, "v", (B, H, N, D))
+    m, J = int(num_landmarks), int(newton_iter)
+    shp = _shape_struct(B, H, N, D, m, J, q.dtype, kappa_star)
+    _lib.check(lib.fnb_check_shape(C.byref(shp)))
+    dev = q.device
+    f32 = dict(dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        out = torch.empty_like(q)
+        lse1 = torch.empty(B, H, N, **f32)
+        qt = torch.empty(B, H, m, D, **f32)
+        kt = torch.empty(B, H, m, D, **f32)
+        k2 = torch.empty(B, H, m, m, **f32)
+        lse2 = torch.empty(B, H, m, **f32)
+        iters = torch.empty(B, H, J + 1, m, m, **f32)
+        k2inv = torch.empty(B, H, m, m, **f32)
+        bmat = torch.empty(B, H, m, D, **f32)
+        lse3 = torch.empty(B, H, m, **f32)
+        step2 = torch.empty(B, H, m, D, **f32)
+        ws = _workspace(lib.fnb_fwd_workspace_bytes(C.byref(shp)), dev)
+        args = _lib.FwdArgs(shp, _ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(lse1), _ptr(qt),
+                            _ptr(kt), _ptr(k2), _ptr(lse2), _ptr(iters), _ptr(k2inv), _ptr(bmat),
+                            _ptr(lse3), _ptr(step2), _ptr(ws), ws.numel(), dev.index,
+                            C.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
+        _lib.check(lib.fnb_forward(C.byref(args)))
+    return [out, q, k, qt, kt, k2inv, step2, lse1, lse2, lse3, iters, k2, bmat]
+
+
+def backward(dO, q_s, k_s, q_tilde, k_tilde, kernel2_inv, step2, lse1, lse2, lse3, ns_iterates,
+             k2_softmax, b_saved, v, output, num_landmarks, newton_iter, fast_dk2inv=True,
+             kappa_star=0.0):
+    lib = _lib.load()
+    _check_big(dO, "dO")
+    if dO.dim() != 4:
+        raise RuntimeError(f"dO must be 4D (B, H, N, D), got {dO.dim()}D")
+    B, H, N, D = dO.shape
+    m, J = int(num_landmarks), int(newton_iter)
+    dt = dO.dtype
+    shp = _shape_struct(B, H, N, D, m, J, dt, kappa_star)
+    _lib.check(lib.fnb_check_shape(C.byref(shp)))
+    f32 = torch.float32
+    _check_big(q_s, "q_s", (B, H, N, D), dt)
+    _check_big(k_s, "k_s", (B, H, N, D), dt)
+    _check_big(v, "v", (B, H, N, D), dt)
+    _check_big(q_tilde, "q_tilde", (B, H, m, D), f32)
+    _check_big(k_tilde, "k_tilde", (B, H, m, D), f32)
+    _check_big(step2, "step2", (B, H, m, D), f32)
+    _check_big(b_saved, "b_saved", (B, H, m, D), f32)
+    _check_big(kernel2_inv, "kernel2_inv", (B, H, m, m), f32)
+    _check_big(k2_softmax, "k2_softmax", (B, H, m, m), f32)
+    _check_big(lse1, "softmax1_lse", (B, H, N), f32)
+    _check_big(lse3, "softmax3_lse", (B, H, m), f32)
+    _check_big(ns_iterates, "ns_iterates", (B, H, J + 1, m, m), f32)
+    dev = dO.device
+    with torch.cuda.device(dev):
+        dq, dk, dv = torch.empty_like(dO), torch.empty_like(dO), torch.empty_like(dO)
+        ws = _workspace(lib.fnb_bwd_workspace_bytes(C.byref(shp)), dev)
+        args = _lib.BwdArgs(shp, _ptr(q_s), _ptr(k_s), _ptr(v), _ptr(dO), _ptr(lse1),
+                            _ptr(q_tilde), _ptr(k_tilde), _ptr(k2_softmax), _ptr(ns_iterates),
+                            _ptr(kernel2_inv), _ptr(b_saved), _ptr(lse3), _ptr(step2), _ptr(dq),
+                            _ptr(dk), _ptr(dv), _ptr(ws), ws.numel(), dev.index,
+                            C.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
+        _lib.check(lib.fnb_backward(C.byref(args)))
+    return [dq, dk, dv]
+
+
+def reset_caches():
+    """The reference drops its thread-local CUDA-graph and scratch caches here
+    (csrc/flash_nystrom.cu:641-650).  This library keeps no caches; nothing to do."""
+    return None
+
+
+def debug_pinv_forward(k2, newton_iter, kappa_star=0.0):
+    """(BH, m, m) softmax matrix -> (ns_iterates (BH, J+1, m, m), k2_inv (BH, m, m))."""
+    lib = _lib.load()
+    _check_big(k2, "k2", dtype=torch.float32)
+    BH, m, _ = k2.shape
+    J = int(newton_iter)
+    dev = k2.device
+    with torch.cuda.device(dev):
+        iters = torch.empty(BH, J + 1, m, m, dtype=torch.float32, device=dev)
+        k2inv = torch.empty_like(k2)
+        ws = _workspace(lib.fnb_debug_pinv_workspace_bytes(BH, m), dev)
+        _lib.check(lib.fnb_debug_pinv_forward(BH, m, J, float(kappa_star), _ptr(k2), _ptr(iters),
+                                              _ptr(k2inv), _ptr(ws), ws.numel(), dev.index,
+                                              C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)))
+    return iters, k2inv
+
+
+def debug_pinv_backward(k2, ns_iterates, d_k2_inv, kappa_star=0.0):
+    """Gradient of the pseudoinverse w.r.t. the softmax matrix k2 (lambda detached)."""
+    lib = _lib.load()
+    _check_big(k2, "k2", dtype=torch.float32)
+    BH, m, _ = k2.shape
+    J = ns_iterates.shape[1] - 1
+    _check_big(ns_iterates, "ns_iterates", (BH, J + 1, m, m), torch.float32)
+    _check_big(d_k2_inv, "d_k2_inv", (BH, m, m), torch.float32)
+    dev = k2.device
+    with torch.cuda.device(dev):
+        dk2 = torch.empty_like(k2)
+        ws = _workspace(lib.fnb_debug_pinv_workspace_bytes(BH, m), dev)
+        _lib.check(lib.fnb_debug_pinv_backward(BH, m, J, float(kappa_star), _ptr(k2),
+                                               _ptr(ns_iterates), _ptr(d_k2_inv), _ptr(dk2),
+                                               _ptr(ws), ws.numel(), dev.index,
+                                               C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)))
+    return dk2
+
+
+def query_sm_limits(device=0):
+    """Device facts, like the reference's query_sm_limits (csrc/flash_nystrom.cu:693-726)."""
+    lib = _lib.load()
+    caps = _lib.Caps()
+    _lib.check(lib.fnb_capabilities(int(device), C.byref(caps)))
+    return {f: getattr(caps, f) for f, _ in _lib.Caps._fields_}
+
+
+def last_profile():
+    """Per-kernel milliseconds of the last call on this thread (needs FNB_PROFILE=1)."""
+    lib = _lib.load()
+    buf = (_lib.KernelTime * 32)()
+    n = lib.fnb_last_profile(buf, 32)
+    return [(buf[i].name.decode(), buf[i].ms) for i in range(n)]

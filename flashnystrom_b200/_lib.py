@@ -1,0 +1,106 @@
+"""ctypes binding of the C ABI declared in include/flashnystrom_b200.h.
+
+The shared library is built in-tree (flashnystrom_b200/lib/).  Loading never falls back to
+another implementation: if the library is missing and cannot be built, import of the
+compute entry points raises."""
+import ctypes as C
+import os
+import threading
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "lib", "libflashnystrom_b200.so")
+
+FNB_F32, FNB_F16, FNB_BF16 = 0, 1, 2
+FNB_FLAG_FORCE_GENERIC = 1
+
+
+class Shape(C.Structure):
+    _fields_ = [("batch", C.c_int64), ("heads", C.c_int64), ("seq_len", C.c_int64),
+                ("head_dim", C.c_int32), ("num_landmarks", C.c_int32),
+                ("newton_iter", C.c_int32), ("dtype", C.c_int32),
+                ("kappa_star", C.c_float), ("flags", C.c_uint32)]
+
+
+class FwdArgs(C.Structure):
+    _fields_ = [("shape", Shape),
+                ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("out", C.c_void_p),
+                ("lse1", C.c_void_p), ("q_landmarks", C.c_void_p), ("k_landmarks", C.c_void_p),
+                ("k2", C.c_void_p), ("lse2", C.c_void_p), ("ns_iterates", C.c_void_p),
+                ("k2_inv", C.c_void_p), ("bmat", C.c_void_p), ("lse3", C.c_void_p),
+                ("step2", C.c_void_p),
+                ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+                ("device", C.c_int32), ("stream", C.c_void_p)]
+
+
+class BwdArgs(C.Structure):
+    _fields_ = [("shape", Shape),
+                ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("d_out", C.c_void_p),
+                ("lse1", C.c_void_p), ("q_landmarks", C.c_void_p), ("k_landmarks", C.c_void_p),
+                ("k2", C.c_void_p), ("ns_iterates", C.c_void_p), ("k2_inv", C.c_void_p),
+                ("bmat", C.c_void_p), ("lse3", C.c_void_p), ("step2", C.c_void_p),
+                ("dq", C.c_void_p), ("dk", C.c_void_p), ("dv", C.c_void_p),
+                ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+                ("device", C.c_int32), ("stream", C.c_void_p)]
+
+
+class Caps(C.Structure):
+    _fields_ = [("abi_version", C.c_int32), ("cc_major", C.c_int32), ("cc_minor", C.c_int32),
+                ("sm_count", C.c_int32), ("max_smem_per_block", C.c_int32),
+                ("l2_bytes", C.c_int64), ("total_mem_bytes", C.c_int64)]
+
+
+class KernelTime(C.Structure):
+    _fields_ = [("name", C.c_char * 48), ("ms", C.c_float)]
+
+
+# every symbol include/flashnystrom_b200.h declares, with its ctypes signature
+SIGNATURES = {
+    "fnb_last_error": (C.c_char_p, []),
+    "fnb_version": (C.c_int, []),
+    "fnb_capabilities": (C.c_int, [C.c_int, C.POINTER(Caps)]),
+    "fnb_fwd_workspace_bytes": (C.c_size_t, [C.POINTER(Shape)]),
+    "fnb_bwd_workspace_bytes": (C.c_size_t, [C.POINTER(Shape)]),
+    "fnb_check_shape": (C.c_int, [C.POINTER(Shape)]),
+    "fnb_forward": (C.c_int, [C.POINTER(FwdArgs)]),
+    "fnb_backward": (C.c_int, [C.POINTER(BwdArgs)]),
+    "fnb_debug_pinv_forward": (C.c_int, [C.c_int64, C.c_int32, C.c_int32, C.c_float, C.c_void_p,
+                                         C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t,
+                                         C.c_int32, C.c_void_p]),
+    "fnb_debug_pinv_backward": (C.c_int, [C.c_int64, C.c_int32, C.c_int32, C.c_float, C.c_void_p,
+                                          C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                          C.c_size_t, C.c_int32, C.c_void_p]),
+    "fnb_debug_pinv_workspace_bytes": (C.c_size_t, [C.c_int64, C.c_int32]),
+    "fnb_last_profile": (C.c_int, [C.POINTER(KernelTime), C.c_int]),
+}
+
+_lock = threading.Lock()
+_lib = None
+
+
+def load(build_if_missing=True):
+    """Return the loaded library, building it with nvcc first if it is absent."""
+    global _lib
+    with _lock:
+        if _lib is not None:
+            return _lib
+        if not os.path.exists(LIB_PATH):
+            if not build_if_missing:
+                raise ImportError(f"{LIB_PATH} not found; run python -m flashnystrom_b200.build")
+            from . import build as _build
+            _build.build()
+        lib = C.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = lib
+        return lib
+
+
+def last_error():
+    return load().fnb_last_error().decode("utf-8", "replace")
+
+
+def check(rc):
+    if rc != 0:
+        raise RuntimeError(f"flashnystrom_b200: {last_error()} (status {rc})")

@@ -1,0 +1,452 @@
+// C ABI of flashnystrom_b200: argument validation, workspace carving and the ordered kernel
+// launches of the forward and backward passes.  See include/flashnystrom_b200.h for the
+// contract of every entry point.
+#include "../../include/flashnystrom_b200.h"
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <cmath>
+#include <vector>
+#include <string>
+
+#include "common.cuh"
+#include "mid_kernels.cuh"
+#include "generic_kernels.cuh"
+
+namespace fnb {
+
+static thread_local char g_err[512] = "";
+static int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+#define FNB_CUDA(expr)                                                                     \
+  do {                                                                                     \
+    cudaError_t e_ = (expr);                                                               \
+    if (e_ != cudaSuccess)                                                                 \
+      return fail(FNB_ERR_CUDA, "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(e_),    \
+                  __FILE__, __LINE__);                                                     \
+  } while (0)
+
+// ---- optional per-kernel profiler (FNB_PROFILE=1 read once at load) -------------------------
+static const bool g_profile = [] {
+  const char* e = getenv("FNB_PROFILE");
+  return e && e[0] == '1';
+}();
+struct ProfEntry { std::string name; float ms; };
+static thread_local std::vector<ProfEntry> g_prof;
+
+struct Launcher {
+  cudaStream_t stream;
+  cudaEvent_t e0 = nullptr, e1 = nullptr;
+  int status = 0;
+  explicit Launcher(cudaStream_t s) : stream(s) {
+    if (g_profile) {
+      g_prof.clear();
+      cudaEventCreate(&e0);
+      cudaEventCreate(&e1);
+    }
+  }
+  ~Launcher() {
+    if (e0) cudaEventDestroy(e0);
+    if (e1) cudaEventDestroy(e1);
+  }
+  void begin() {
+    if (g_profile) cudaEventRecord(e0, stream);
+  }
+  int end(const char* name) {
+    cudaError_t e = cudaPeekAtLastError();
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      return status = fail(FNB_ERR_CUDA, "launch of %s failed: %s", name, cudaGetErrorString(e));
+    }
+    if (g_profile) {
+      cudaEventRecord(e1, stream);
+      cudaEventSynchronize(e1);
+      float ms = 0.f;
+      cudaEventElapsedTime(&ms, e0, e1);
+      g_prof.push_back({name, ms});
+    }
+    return 0;
+  }
+};
+
+template <class K>
+static int set_smem(K kernel, size_t bytes, int max_optin, const char* name) {
+  if ((long long)bytes > (long long)max_optin)
+    return fail(FNB_ERR_SMEM, "insufficient smem for %s: needs %zu bytes, device allows %d", name,
+                bytes, max_optin);
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+  if (e != cudaSuccess)
+    return fail(FNB_ERR_CUDA, "cudaFuncSetAttribute(%s, %zu) failed: %s", name, bytes,
+                cudaGetErrorString(e));
+  return 0;
+}
+
+struct DeviceGuard {
+  int prev = -1;
+  bool ok = true;
+  explicit DeviceGuard(int dev) {
+    if (cudaGetDevice(&prev) != cudaSuccess) { ok = false; return; }
+    if (prev != dev && cudaSetDevice(dev) != cudaSuccess) ok = false;
+  }
+  ~DeviceGuard() {
+    int cur = -1;
+    if (prev >= 0 && cudaGetDevice(&cur) == cudaSuccess && cur != prev) cudaSetDevice(prev);
+  }
+};
+
+static int device_limits(int device, int* max_smem, int* cc_major) {
+  // attribute queries are cheap and keep the call free of cached, thread-affine state
+  FNB_CUDA(cudaDeviceGetAttribute(max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, device));
+  FNB_CUDA(cudaDeviceGetAttribute(cc_major, cudaDevAttrComputeCapabilityMajor, device));
+  if (*cc_major != 10)
+    return fail(FNB_ERR_UNSUPPORTED_DEVICE,
+                "device %d has compute capability %d.x; this library is built for sm_100a only",
+                device, *cc_major);
+  return 0;
+}
+
+static int check_shape(const fnb_shape* s) {
+  if (!s) return fail(FNB_ERR_INVALID_ARGUMENT, "shape is NULL");
+  if (s->batch <= 0 || s->heads <= 0)
+    return fail(FNB_ERR_INVALID_ARGUMENT, "batch_size and num_heads must be positive (got B=%lld, H=%lld)",
+                (long long)s->batch, (long long)s->heads);
+  if (s->dtype != FNB_F32 && s->dtype != FNB_F16 && s->dtype != FNB_BF16)
+    return fail(FNB_ERR_INVALID_ARGUMENT, "Supported dtypes: float32, float16, bfloat16 (got code %d)", s->dtype);
+  if (s->num_landmarks < 1 || s->num_landmarks > kMaxM)
+    return fail(FNB_ERR_INVALID_ARGUMENT, "num_landmarks must be in [1, %d], got %d", kMaxM, s->num_landmarks);
+  if (s->seq_len < s->num_landmarks)
+    return fail(FNB_ERR_INVALID_ARGUMENT, "seq_len (%lld) must be >= num_landmarks (%d)",
+                (long long)s->seq_len, s->num_landmarks);
+  if (!(s->head_dim == 16 || s->head_dim == 32 || s->head_dim == 64 || s->head_dim == 128))
+    return fail(FNB_ERR_INVALID_ARGUMENT, "head_dim must be 16, 32, 64 or 128, got %d", s->head_dim);
+  if (s->newton_iter < 1 || s->newton_iter > 20)
+    return fail(FNB_ERR_INVALID_ARGUMENT, "newton_iter must be in [1, 20], got %d", s->newton_iter);
+  if (!std::isfinite(s->kappa_star) || s->kappa_star < 0.f)
+    return fail(FNB_ERR_INVALID_ARGUMENT,
+                "kappa_star must be finite and >= 0 (got %g); 0 disables the Tikhonov ridge",
+                (double)s->kappa_star);
+  if (s->batch * s->heads > (int64_t)1 << 24)
+    return fail(FNB_ERR_INVALID_ARGUMENT, "batch * heads (%lld) exceeds 2^24", (long long)(s->batch * s->heads));
+  return 0;
+}
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+struct FwdWs {
+  float *land_partial, *part_acc, *part_max, *part_sum, *pinv;
+  size_t bytes;
+};
+static FwdWs carve_fwd(const Plan& p, void* base) {
+  char* b = (char*)base;
+  size_t off = 0;
+  auto take = [&](size_t nfloat) { float* r = (float*)(b + off); off += align256(nfloat * sizeof(float)); return r; };
+  FwdWs w;
+  w.land_partial = take((size_t)2 * p.BH * p.m * p.lm_chunks * p.D);
+  w.part_acc = take((size_t)p.BH * p.nchunk * p.m * p.D);
+  w.part_max = take((size_t)p.BH * p.nchunk * p.m);
+  w.part_sum = take((size_t)p.BH * p.nchunk * p.m);
+  w.pinv = take((size_t)p.BH * kPinvFwdBufs * p.m * p.m);
+  w.bytes = off;
+  return w;
+}
+
+struct BwdWs {
+  float *partA, *partB, *dstep2, *dkt_a, *dO3, *dqt_ns, *dkt_tot, *dqt_tot, *D3, *G, *dK2, *pinv;
+  size_t bytes;
+};
+static BwdWs carve_bwd(const Plan& p, void* base) {
+  char* b = (char*)base;
+  size_t off = 0;
+  auto take = [&](size_t nfloat) { float* r = (float*)(b + off); off += align256(nfloat * sizeof(float)); return r; };
+  BwdWs w;
+  const size_t md = (size_t)p.BH * p.m * p.D, mm = (size_t)p.BH * p.m * p.m;
+  w.partA = take((size_t)p.nchunk * 2 * md);
+  w.partB = take((size_t)p.nchunk * md);
+  w.dstep2 = take(md); w.dkt_a = take(md); w.dO3 = take(md);
+  w.dqt_ns = take(md); w.dkt_tot = take(md); w.dqt_tot = take(md);
+  w.D3 = take((size_t)p.BH * p.m);
+  w.G = take(mm); w.dK2 = take(mm);
+  w.pinv = take((size_t)kPinvBwdBufs * mm);
+  w.bytes = off;
+  return w;
+}
+
+static Plan plan_of(const fnb_shape& s) {
+  return make_plan(s.batch * s.heads, s.seq_len, s.head_dim, s.num_landmarks, s.newton_iter);
+}
+
+// ------------------------------------------------------------------------------------------
+template <class T>
+static int forward_impl(const fnb_fwd_args& a, const Plan& p, const FwdWs& w, int max_smem,
+                        cudaStream_t st) {
+  Launcher L(st);
+  const float scale = powf((float)p.D, -0.25f);
+
+  L.begin();
+  {
+    int64_t grid = 2 * p.BH * p.m * p.lm_chunks;
+    landmark_partial_kernel<T><<<(unsigned)grid, kThreads, 0, st>>>(
+        (const T*)a.q, (const T*)a.k, w.land_partial, p.BH, p.N, p.D, p.m, p.lm_chunks);
+  }
+  if (L.end("landmark_partial")) return L.status;
+
+  L.begin();
+  {
+    MidFwdParams mp;
+    mp.land_partial = w.land_partial; mp.C = p.lm_chunks;
+    mp.qt = a.q_landmarks; mp.kt = a.k_landmarks; mp.k2 = a.k2; mp.lse2 = a.lse2;
+    mp.iterates = a.ns_iterates; mp.k2inv = a.k2_inv; mp.scratch = w.pinv;
+    mp.BH = p.BH; mp.N = p.N; mp.m = p.m; mp.D = p.D; mp.J = p.J;
+    mp.kappa = a.shape.kappa_star; mp.scale = scale;
+    mid_fwd_kernel<<<(unsigned)p.BH, kThreads, 0, st>>>(mp);
+  }
+  if (L.end("mid_fwd")) return L.status;
+
+  StreamParams sp;
+  memset(&sp, 0, sizeof(sp));
+  sp.q = a.q; sp.k = a.k; sp.v = a.v; sp.out = a.out; sp.lse1 = a.lse1;
+  sp.qt = a.q_landmarks; sp.kt = a.k_landmarks; sp.step2 = a.step2;
+  sp.part_acc = w.part_acc; sp.part_max = w.part_max; sp.part_sum = w.part_sum;
+  sp.N = p.N; sp.rows_per_chunk = p.rows_per_chunk; sp.D = p.D; sp.m = p.m; sp.mpad = p.mpad;
+  sp.nchunk = p.nchunk; sp.scale = scale;
+  const unsigned sgrid = (unsigned)(p.BH * p.nchunk);
+
+  L.begin();
+  {
+    size_t smem = fwd_b_smem(p.mpad, p.D);
+    if (int rc = set_smem(gen_fwd_b_kernel<T>, smem, max_smem, "gen_fwd_b")) return rc;
+    gen_fwd_b_kernel<T><<<sgrid, kThreads, smem, st>>>(sp);
+  }
+  if (L.end("gen_fwd_b")) return L.status;
+
+  L.begin();
+  {
+    CombineParams cp;
+    cp.part_acc = w.part_acc; cp.part_max = w.part_max; cp.part_sum = w.part_sum;
+    cp.nchunk = p.nchunk; cp.k2inv = a.k2_inv; cp.bmat = a.bmat; cp.lse3 = a.lse3;
+    cp.step2 = a.step2; cp.m = p.m; cp.D = p.D;
+    combine_kernel<<<(unsigned)p.BH, kThreads, 0, st>>>(cp);
+  }
+  if (L.end("combine")) return L.status;
+
+  L.begin();
+  {
+    size_t smem = fwd_c_smem(p.mpad, p.D);
+    if (int rc = set_smem(gen_fwd_c_kernel<T>, smem, max_smem, "gen_fwd_c")) return rc;
+    gen_fwd_c_kernel<T><<<sgrid, kThreads, smem, st>>>(sp);
+  }
+  if (L.end("gen_fwd_c")) return L.status;
+  return 0;
+}
+
+template <class T>
+static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, int max_smem,
+                         cudaStream_t st) {
+  Launcher L(st);
+  const float scale = powf((float)p.D, -0.25f);
+  StreamParams sp;
+  memset(&sp, 0, sizeof(sp));
+  sp.q = a.q; sp.k = a.k; sp.v = a.v; sp.dO = a.d_out;
+  sp.dq = a.dq; sp.dk = a.dk; sp.dv = a.dv;
+  sp.lse1 = const_cast<float*>(a.lse1);
+  sp.qt = a.q_landmarks; sp.kt = a.k_landmarks; sp.step2 = a.step2;
+  sp.lse3 = a.lse3; sp.dO3 = w.dO3; sp.D3 = w.D3;
+  sp.dqt_tot = w.dqt_tot; sp.dkt_tot = w.dkt_tot;
+  sp.partA = w.partA; sp.partB = w.partB;
+  sp.N = p.N; sp.rows_per_chunk = p.rows_per_chunk; sp.D = p.D; sp.m = p.m; sp.mpad = p.mpad;
+  sp.nchunk = p.nchunk; sp.scale = scale;
+  const unsigned sgrid = (unsigned)(p.BH * p.nchunk);
+  const size_t smem = bwd_ac_smem(p.mpad, p.D);
+
+  L.begin();
+  if (int rc = set_smem(gen_bwd_a_kernel<T>, smem, max_smem, "gen_bwd_a")) return rc;
+  gen_bwd_a_kernel<T><<<sgrid, kThreads, smem, st>>>(sp);
+  if (L.end("gen_bwd_a")) return L.status;
+
+  L.begin();
+  {
+    MidBwdParams mp;
+    mp.partA = w.partA; mp.nchunk = p.nchunk;
+    mp.qt = a.q_landmarks; mp.kt = a.k_landmarks; mp.k2 = a.k2; mp.iterates = a.ns_iterates;
+    mp.k2inv = a.k2_inv; mp.bmat = a.bmat;
+    mp.dstep2 = w.dstep2; mp.dkt_a = w.dkt_a; mp.dO3 = w.dO3; mp.D3 = w.D3;
+    mp.dqt_ns = w.dqt_ns; mp.dkt_tot = w.dkt_tot; mp.G = w.G; mp.dK2 = w.dK2; mp.scratch = w.pinv;
+    mp.m = p.m; mp.D = p.D; mp.J = p.J; mp.kappa = a.shape.kappa_star;
+    mid_bwd_kernel<<<(unsigned)p.BH, kThreads, 0, st>>>(mp);
+  }
+  if (L.end("mid_bwd")) return L.status;
+
+  L.begin();
+  if (int rc = set_smem(gen_bwd_b_kernel<T>, smem, max_smem, "gen_bwd_b")) return rc;
+  gen_bwd_b_kernel<T><<<sgrid, kThreads, smem, st>>>(sp);
+  if (L.end("gen_bwd_b")) return L.status;
+
+  L.begin();
+  dqt_reduce_kernel<<<(unsigned)p.BH, kThreads, 0, st>>>(w.partB, p.nchunk, w.dqt_ns, w.dqt_tot,
+                                                         p.m * p.D);
+  if (L.end("dqt_reduce")) return L.status;
+
+  L.begin();
+  if (int rc = set_smem(gen_bwd_c_kernel<T>, smem, max_smem, "gen_bwd_c")) return rc;
+  gen_bwd_c_kernel<T><<<sgrid, kThreads, smem, st>>>(sp);
+  if (L.end("gen_bwd_c")) return L.status;
+  return 0;
+}
+
+}  // namespace fnb
+
+using namespace fnb;
+
+extern "C" {
+
+const char* fnb_last_error(void) { return g_err; }
+int fnb_version(void) { return FNB_ABI_VERSION; }
+
+int fnb_capabilities(int device, fnb_caps* caps) {
+  if (!caps) return fail(FNB_ERR_INVALID_ARGUMENT, "caps is NULL");
+  memset(caps, 0, sizeof(*caps));
+  caps->abi_version = FNB_ABI_VERSION;
+  cudaDeviceProp prop;
+  FNB_CUDA(cudaGetDeviceProperties(&prop, device));
+  caps->cc_major = prop.major; caps->cc_minor = prop.minor;
+  caps->sm_count = prop.multiProcessorCount;
+  caps->max_smem_per_block = (int)prop.sharedMemPerBlockOptin;
+  caps->l2_bytes = prop.l2CacheSize;
+  caps->total_mem_bytes = (int64_t)prop.totalGlobalMem;
+  if (prop.major != 10)
+    return fail(FNB_ERR_UNSUPPORTED_DEVICE,
+                "device %d (%s) has compute capability %d.%d; this library is built for sm_100a only",
+                device, prop.name, prop.major, prop.minor);
+  return 0;
+}
+
+int fnb_check_shape(const fnb_shape* shape) { return check_shape(shape); }
+
+size_t fnb_fwd_workspace_bytes(const fnb_shape* shape) {
+  if (check_shape(shape)) return 0;
+  return carve_fwd(plan_of(*shape), nullptr).bytes;
+}
+size_t fnb_bwd_workspace_bytes(const fnb_shape* shape) {
+  if (check_shape(shape)) return 0;
+  return carve_bwd(plan_of(*shape), nullptr).bytes;
+}
+
+int fnb_forward(const fnb_fwd_args* a) {
+  if (!a) return fail(FNB_ERR_INVALID_ARGUMENT, "args is NULL");
+  if (int rc = check_shape(&a->shape)) return rc;
+  const void* big[] = {a->q, a->k, a->v, a->out};
+  for (const void* ptr : big)
+    if (!ptr || !aligned16(ptr))
+      return fail(FNB_ERR_INVALID_ARGUMENT, "q, k, v, out must be non-NULL and 16-byte aligned");
+  const void* small[] = {a->lse1, a->q_landmarks, a->k_landmarks, a->k2, a->lse2, a->ns_iterates,
+                         a->k2_inv, a->bmat, a->lse3, a->step2};
+  for (const void* ptr : small)
+    if (!ptr) return fail(FNB_ERR_INVALID_ARGUMENT, "a saved-tensor output pointer is NULL");
+  Plan p = plan_of(a->shape);
+  FwdWs w = carve_fwd(p, a->workspace);
+  if (!a->workspace || a->workspace_bytes < w.bytes || (reinterpret_cast<uintptr_t>(a->workspace) & 255u))
+    return fail(FNB_ERR_WORKSPACE, "forward workspace must be 256-byte aligned and >= %zu bytes (got %zu)",
+                w.bytes, a->workspace_bytes);
+  DeviceGuard g(a->device);
+  if (!g.ok) return fail(FNB_ERR_CUDA, "cannot select CUDA device %d", a->device);
+  int max_smem = 0, cc = 0;
+  if (int rc = device_limits(a->device, &max_smem, &cc)) return rc;
+  cudaStream_t st = (cudaStream_t)a->stream;
+  switch (a->shape.dtype) {
+    case FNB_F32: return forward_impl<float>(*a, p, w, max_smem, st);
+    case FNB_F16: return forward_impl<__half>(*a, p, w, max_smem, st);
+    default: return forward_impl<__nv_bfloat16>(*a, p, w, max_smem, st);
+  }
+}
+
+int fnb_backward(const fnb_bwd_args* a) {
+  if (!a) return fail(FNB_ERR_INVALID_ARGUMENT, "args is NULL");
+  if (int rc = check_shape(&a->shape)) return rc;
+  const void* big[] = {a->q, a->k, a->v, a->d_out, a->dq, a->dk, a->dv};
+  for (const void* ptr : big)
+    if (!ptr || !aligned16(ptr))
+      return fail(FNB_ERR_INVALID_ARGUMENT, "q, k, v, d_out, dq, dk, dv must be non-NULL and 16-byte aligned");
+  const void* small[] = {a->lse1, a->q_landmarks, a->k_landmarks, a->k2, a->ns_iterates, a->k2_inv,
+                         a->bmat, a->lse3, a->step2};
+  for (const void* ptr : small)
+    if (!ptr) return fail(FNB_ERR_INVALID_ARGUMENT, "a saved-tensor input pointer is NULL");
+  Plan p = plan_of(a->shape);
+  BwdWs w = carve_bwd(p, a->workspace);
+  if (!a->workspace || a->workspace_bytes < w.bytes || (reinterpret_cast<uintptr_t>(a->workspace) & 255u))
+    return fail(FNB_ERR_WORKSPACE, "backward workspace must be 256-byte aligned and >= %zu bytes (got %zu)",
+                w.bytes, a->workspace_bytes);
+  DeviceGuard g(a->device);
+  if (!g.ok) return fail(FNB_ERR_CUDA, "cannot select CUDA device %d", a->device);
+  int max_smem = 0, cc = 0;
+  if (int rc = device_limits(a->device, &max_smem, &cc)) return rc;
+  cudaStream_t st = (cudaStream_t)a->stream;
+  switch (a->shape.dtype) {
+    case FNB_F32: return backward_impl<float>(*a, p, w, max_smem, st);
+    case FNB_F16: return backward_impl<__half>(*a, p, w, max_smem, st);
+    default: return backward_impl<__nv_bfloat16>(*a, p, w, max_smem, st);
+  }
+}
+
+size_t fnb_debug_pinv_workspace_bytes(int64_t bh, int32_t m) {
+  if (bh <= 0 || m < 1 || m > kMaxM) return 0;
+  return align256((size_t)bh * kPinvBwdBufs * m * m * sizeof(float));
+}
+
+static int check_pinv_args(int64_t bh, int32_t m, int32_t J, float kappa, const void* ws,
+                           size_t ws_bytes) {
+  if (bh <= 0 || bh > ((int64_t)1 << 24)) return fail(FNB_ERR_INVALID_ARGUMENT, "bh out of range");
+  if (m < 1 || m > kMaxM) return fail(FNB_ERR_INVALID_ARGUMENT, "num_landmarks must be in [1, %d], got %d", kMaxM, m);
+  if (J < 1 || J > 20) return fail(FNB_ERR_INVALID_ARGUMENT, "newton_iter must be in [1, 20], got %d", J);
+  if (!std::isfinite(kappa) || kappa < 0.f) return fail(FNB_ERR_INVALID_ARGUMENT, "kappa_star must be finite and >= 0");
+  if (!ws || ws_bytes < fnb_debug_pinv_workspace_bytes(bh, m))
+    return fail(FNB_ERR_WORKSPACE, "pinv workspace too small: need %zu bytes", fnb_debug_pinv_workspace_bytes(bh, m));
+  return 0;
+}
+
+int fnb_debug_pinv_forward(int64_t bh, int32_t m, int32_t J, float kappa, const float* k2,
+                           float* ns_iterates, float* k2_inv, void* workspace, size_t workspace_bytes,
+                           int32_t device, void* stream) {
+  if (int rc = check_pinv_args(bh, m, J, kappa, workspace, workspace_bytes)) return rc;
+  if (!k2 || !ns_iterates || !k2_inv) return fail(FNB_ERR_INVALID_ARGUMENT, "NULL tensor pointer");
+  DeviceGuard g(device);
+  if (!g.ok) return fail(FNB_ERR_CUDA, "cannot select CUDA device %d", device);
+  pinv_fwd_debug_kernel<<<(unsigned)bh, kThreads, 0, (cudaStream_t)stream>>>(
+      k2, ns_iterates, k2_inv, (float*)workspace, m, J, kappa);
+  FNB_CUDA(cudaPeekAtLastError());
+  return 0;
+}
+
+int fnb_debug_pinv_backward(int64_t bh, int32_t m, int32_t J, float kappa, const float* k2,
+                            const float* ns_iterates, const float* d_k2_inv, float* d_k2,
+                            void* workspace, size_t workspace_bytes, int32_t device, void* stream) {
+  if (int rc = check_pinv_args(bh, m, J, kappa, workspace, workspace_bytes)) return rc;
+  if (!k2 || !ns_iterates || !d_k2_inv || !d_k2) return fail(FNB_ERR_INVALID_ARGUMENT, "NULL tensor pointer");
+  DeviceGuard g(device);
+  if (!g.ok) return fail(FNB_ERR_CUDA, "cannot select CUDA device %d", device);
+  pinv_bwd_debug_kernel<<<(unsigned)bh, kThreads, 0, (cudaStream_t)stream>>>(
+      k2, ns_iterates, d_k2_inv, d_k2, (float*)workspace, m, J, kappa);
+  FNB_CUDA(cudaPeekAtLastError());
+  return 0;
+}
+
+int fnb_last_profile(fnb_kernel_time* out, int cap) {
+  int n = 0;
+  for (const auto& e : g_prof) {
+    if (n >= cap) break;
+    strncpy(out[n].name, e.name.c_str(), sizeof(out[n].name) - 1);
+    out[n].name[sizeof(out[n].name) - 1] = 0;
+    out[n].ms = e.ms;
+    ++n;
+  }
+  return n;
+}
+
+}  // extern "C"

@@ -1,0 +1,173 @@
+/*
+ * flashnystrom_b200 -- C ABI of the sm_100a Nystrom-attention library.
+ *
+ * Every entry point takes plain pointers and sizes; the caller (PyTorch host code through
+ * ctypes, or any FFI) owns all memory.  Unless a comment says otherwise a call
+ *   - allocates nothing and frees nothing,
+ *   - does not synchronise the host with the device,
+ *   - enqueues all work on the cudaStream_t it is given (passed as void*),
+ *   - keeps no thread-affine state,
+ * and returns 0 on success or a negative fnb_status; fnb_last_error() then holds the text.
+ *
+ * Each declaration names the interface of the reference project (athrva98/FlashNystrom) it
+ * stands in for, as file:line inside that project.
+ */
+#ifndef FLASHNYSTROM_B200_H_
+#define FLASHNYSTROM_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FNB_ABI_VERSION 1
+
+#if defined(__GNUC__)
+#define FNB_API __attribute__((visibility("default")))
+#else
+#define FNB_API
+#endif
+
+enum fnb_status {
+  FNB_OK = 0,
+  FNB_ERR_INVALID_ARGUMENT = -1, /* a shape / dtype / pointer check failed               */
+  FNB_ERR_WORKSPACE = -2,        /* workspace pointer null or smaller than required       */
+  FNB_ERR_CUDA = -3,             /* a CUDA runtime call or launch failed                  */
+  FNB_ERR_UNSUPPORTED_DEVICE = -4, /* the device is not compute capability 10.x           */
+  FNB_ERR_SMEM = -5,             /* "insufficient smem": kernel needs more shared memory  */
+  FNB_ERR_DEVICE_STATUS = -6     /* a bounded device-side wait expired (status word set)  */
+};
+
+enum fnb_dtype { FNB_F32 = 0, FNB_F16 = 1, FNB_BF16 = 2 };
+
+/* flags */
+#define FNB_FLAG_FORCE_GENERIC 1u /* use the CUDA-core FP32 kernels even where a tensor-core
+                                     kernel exists (verification, like the reference's
+                                     FP32 scalar twins csrc/kernels/kernel1_scalar.cuh:18-92) */
+
+/* Problem description shared by all entry points.
+ * Mirrors the scalar fields of NystromParams (csrc/flash_nystrom.h:21-88). */
+typedef struct fnb_shape {
+  int64_t batch;          /* B                                                    */
+  int64_t heads;          /* H                                                    */
+  int64_t seq_len;        /* N  (N >= num_landmarks)                              */
+  int32_t head_dim;       /* D  (16, 32, 64 or 128)                               */
+  int32_t num_landmarks;  /* m  (1..128)                                          */
+  int32_t newton_iter;    /* J  (1..20)                                           */
+  int32_t dtype;          /* fnb_dtype of q, k, v, out, dO, dQ, dK, dV            */
+  float kappa_star;       /* Tikhonov ridge target condition number, 0 = no ridge */
+  uint32_t flags;
+} fnb_shape;
+
+/* Forward.  Replaces nystrom_fwd + run_nystrom_fwd (csrc/flash_nystrom.cu:30-172,
+ * csrc/flash_nystrom_kernels.cu:188-251) and the kernels they launch.
+ * All tensors are contiguous row-major device memory.  Small saved tensors are FP32. */
+typedef struct fnb_fwd_args {
+  fnb_shape shape;
+  const void* q;        /* (B,H,N,D) dtype, read-only */
+  const void* k;        /* (B,H,N,D) dtype, read-only */
+  const void* v;        /* (B,H,N,D) dtype, read-only */
+  void* out;            /* (B,H,N,D) dtype                                            */
+  float* lse1;          /* (B,H,N)   log-sum-exp of softmax(Q Kt^T) rows              */
+  float* q_landmarks;   /* (B,H,m,D) D^-1/4-scaled segment means of Q                 */
+  float* k_landmarks;   /* (B,H,m,D) same for K                                       */
+  float* k2;            /* (B,H,m,m) softmax(Qt Kt^T), without ridge                  */
+  float* lse2;          /* (B,H,m)                                                    */
+  float* ns_iterates;   /* (B,H,J+1,m,m) Newton-Schulz iterates Z_0..Z_J              */
+  float* k2_inv;        /* (B,H,m,m) pseudoinverse used by the output                 */
+  float* bmat;          /* (B,H,m,D) softmax(Qt K^T) V                                */
+  float* lse3;          /* (B,H,m)                                                    */
+  float* step2;         /* (B,H,m,D) k2_inv * bmat                                    */
+  void* workspace;      /* >= fnb_fwd_workspace_bytes(), 256-byte aligned             */
+  size_t workspace_bytes;
+  int32_t device;       /* CUDA device ordinal all pointers live on                   */
+  void* stream;         /* cudaStream_t                                               */
+} fnb_fwd_args;
+
+/* Backward.  Replaces nystrom_bwd + run_nystrom_bwd_impl (csrc/flash_nystrom.cu:177-415,
+ * csrc/flash_nystrom_kernels.cu:313-391), including the cuBLAS + CUDA-graph
+ * Newton-Schulz backward (csrc/kernels/backward/kernel2_inv_bwd.cu:794-1058).
+ * dq, dk, dv are written exactly once each; they need not be zeroed. */
+typedef struct fnb_bwd_args {
+  fnb_shape shape;
+  const void* q;
+  const void* k;
+  const void* v;
+  const void* d_out;    /* (B,H,N,D) dtype */
+  const float* lse1;
+  const float* q_landmarks;
+  const float* k_landmarks;
+  const float* k2;
+  const float* ns_iterates;
+  const float* k2_inv;
+  const float* bmat;
+  const float* lse3;
+  const float* step2;
+  void* dq;             /* (B,H,N,D) dtype */
+  void* dk;
+  void* dv;
+  void* workspace;      /* >= fnb_bwd_workspace_bytes(), 256-byte aligned */
+  size_t workspace_bytes;
+  int32_t device;
+  void* stream;
+} fnb_bwd_args;
+
+typedef struct fnb_caps {
+  int32_t abi_version;
+  int32_t cc_major, cc_minor;
+  int32_t sm_count;
+  int32_t max_smem_per_block;  /* opt-in bytes */
+  int64_t l2_bytes;
+  int64_t total_mem_bytes;
+} fnb_caps;
+
+/* Text of the last failure on the calling thread (thread-local, never NULL).
+ * Stands in for the std::runtime_error text of csrc/utils.h:23-61. */
+FNB_API const char* fnb_last_error(void);
+
+/* Library ABI version (FNB_ABI_VERSION).  No counterpart in the reference. */
+FNB_API int fnb_version(void);
+
+/* Device properties; FNB_ERR_UNSUPPORTED_DEVICE unless the device is sm_100.
+ * Stands in for query_sm_limits (csrc/flash_nystrom.cu:693-726). */
+FNB_API int fnb_capabilities(int device, fnb_caps* caps);
+
+/* Scratch sizes in bytes for one call of the given shape.  The reference allocates its
+ * scratch itself (csrc/flash_nystrom.cu:292-333, kernel3_output_fused.cuh:1033-1047). */
+FNB_API size_t fnb_fwd_workspace_bytes(const fnb_shape* shape);
+FNB_API size_t fnb_bwd_workspace_bytes(const fnb_shape* shape);
+
+/* Validate a shape exactly as fnb_forward would (csrc/flash_nystrom.cu:45-79). */
+FNB_API int fnb_check_shape(const fnb_shape* shape);
+
+FNB_API int fnb_forward(const fnb_fwd_args* args);
+FNB_API int fnb_backward(const fnb_bwd_args* args);
+
+/* Isolation hooks for the Newton-Schulz kernels; (BH,m,m) FP32 device tensors.
+ * Stand in for debug_kernel2_inv_bwd_full / debug_ns_bwd_* (csrc/flash_nystrom.cu:629-690).
+ *
+ * fnb_debug_pinv_forward: k2 (already a softmax matrix) -> ns_iterates, k2_inv.
+ * fnb_debug_pinv_backward: (k2, ns_iterates, d_k2_inv) -> d_k2  (gradient w.r.t. the
+ *   softmax matrix, before the softmax Jacobian). */
+FNB_API int fnb_debug_pinv_forward(int64_t bh, int32_t m, int32_t newton_iter, float kappa_star,
+                           const float* k2, float* ns_iterates, float* k2_inv,
+                           void* workspace, size_t workspace_bytes, int32_t device,
+                           void* stream);
+FNB_API int fnb_debug_pinv_backward(int64_t bh, int32_t m, int32_t newton_iter, float kappa_star,
+                            const float* k2, const float* ns_iterates, const float* d_k2_inv,
+                            float* d_k2, void* workspace, size_t workspace_bytes,
+                            int32_t device, void* stream);
+FNB_API size_t fnb_debug_pinv_workspace_bytes(int64_t bh, int32_t m);
+
+/* Per-kernel timing of the most recent fnb_forward / fnb_backward on this thread when the
+ * environment variable FNB_PROFILE=1 was set at library load (forces a sync per kernel;
+ * stands in for KernelProfiler, csrc/profile.h:44-106).  Writes up to `cap` entries. */
+typedef struct fnb_kernel_time { char name[48]; float ms; } fnb_kernel_time;
+FNB_API int fnb_last_profile(fnb_kernel_time* out, int cap);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FLASHNYSTROM_B200_H_ */
