@@ -190,8 +190,13 @@ def query_sm_limits(device=0):
     return {f: getattr(caps, f) for f, _ in _lib.Caps._fields_}
 
 
+def set_profiling(on: bool):
+    """Switch per-kernel CUDA-event timing on or off; returns the previous setting."""
+    return bool(_lib.load().fnb_set_profiling(1 if on else 0))
+
+
 def last_profile():
-    """Per-kernel milliseconds of the last call on this thread (needs FNB_PROFILE=1)."""
+    """[(kernel name, milliseconds)] of the last forward or backward call on this thread."""
     lib = _lib.load()
     buf = (_lib.KernelTime * 32)()
     n = lib.fnb_last_profile(buf, 32)

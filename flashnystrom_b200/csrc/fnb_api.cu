@@ -34,31 +34,49 @@ static int fail(int code, const char* fmt, ...) {
                   __FILE__, __LINE__);                                                     \
   } while (0)
 
-// ---- optional per-kernel profiler (FNB_PROFILE=1 read once at load) -------------------------
-static const bool g_profile = [] {
+// ---- optional per-kernel profiler -----------------------------------------------------------
+// Off by default.  FNB_PROFILE=1 in the environment at load, or fnb_set_profiling(1), brackets
+// every kernel with a pair of CUDA events on the caller's stream (no host synchronisation in the
+// call itself); fnb_last_profile() waits for the last event and reads the times back.
+static int g_profile = [] {
   const char* e = getenv("FNB_PROFILE");
-  return e && e[0] == '1';
+  return (e && e[0] == '1') ? 1 : 0;
 }();
-struct ProfEntry { std::string name; float ms; };
-static thread_local std::vector<ProfEntry> g_prof;
+struct ProfState {
+  int device = -1;
+  std::vector<cudaEvent_t> pool;      // reused across calls on this thread
+  std::vector<std::string> names;     // kernels of the most recent call
+  size_t used = 0;
+  cudaEvent_t get(int dev) {
+    if (dev != device) {
+      for (cudaEvent_t e : pool) cudaEventDestroy(e);
+      pool.clear();
+      device = dev;
+      used = 0;
+    }
+    if (used == pool.size()) {
+      cudaEvent_t e = nullptr;
+      cudaEventCreate(&e);
+      pool.push_back(e);
+    }
+    return pool[used++];
+  }
+};
+static thread_local ProfState g_prof;
 
 struct Launcher {
   cudaStream_t stream;
-  cudaEvent_t e0 = nullptr, e1 = nullptr;
+  int device;
+  bool prof;
   int status = 0;
-  explicit Launcher(cudaStream_t s) : stream(s) {
-    if (g_profile) {
-      g_prof.clear();
-      cudaEventCreate(&e0);
-      cudaEventCreate(&e1);
+  Launcher(cudaStream_t s, int dev) : stream(s), device(dev), prof(g_profile != 0) {
+    if (prof) {
+      g_prof.names.clear();
+      g_prof.used = 0;
     }
   }
-  ~Launcher() {
-    if (e0) cudaEventDestroy(e0);
-    if (e1) cudaEventDestroy(e1);
-  }
   void begin() {
-    if (g_profile) cudaEventRecord(e0, stream);
+    if (prof) cudaEventRecord(g_prof.get(device), stream);
   }
   int end(const char* name) {
     cudaError_t e = cudaPeekAtLastError();
@@ -66,12 +84,9 @@ struct Launcher {
       cudaGetLastError();
       return status = fail(FNB_ERR_CUDA, "launch of %s failed: %s", name, cudaGetErrorString(e));
     }
-    if (g_profile) {
-      cudaEventRecord(e1, stream);
-      cudaEventSynchronize(e1);
-      float ms = 0.f;
-      cudaEventElapsedTime(&ms, e0, e1);
-      g_prof.push_back({name, ms});
+    if (prof) {
+      cudaEventRecord(g_prof.get(device), stream);
+      g_prof.names.push_back(name);
     }
     return 0;
   }
@@ -187,7 +202,7 @@ static Plan plan_of(const fnb_shape& s) {
 template <class T>
 static int forward_impl(const fnb_fwd_args& a, const Plan& p, const FwdWs& w, int max_smem,
                         cudaStream_t st) {
-  Launcher L(st);
+  Launcher L(st, a.device);
   const float scale = powf((float)p.D, -0.25f);
 
   L.begin();
@@ -250,7 +265,7 @@ static int forward_impl(const fnb_fwd_args& a, const Plan& p, const FwdWs& w, in
 template <class T>
 static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, int max_smem,
                          cudaStream_t st) {
-  Launcher L(st);
+  Launcher L(st, a.device);
   const float scale = powf((float)p.D, -0.25f);
   StreamParams sp;
   memset(&sp, 0, sizeof(sp));
@@ -437,13 +452,26 @@ int fnb_debug_pinv_backward(int64_t bh, int32_t m, int32_t J, float kappa, const
   return 0;
 }
 
+int fnb_set_profiling(int mode) {
+  int prev = g_profile;
+  g_profile = mode ? 1 : 0;
+  return prev;
+}
+
 int fnb_last_profile(fnb_kernel_time* out, int cap) {
   int n = 0;
-  for (const auto& e : g_prof) {
+  if (!out || cap <= 0) return 0;
+  for (size_t i = 0; i < g_prof.names.size() && 2 * i + 1 < g_prof.used; ++i) {
     if (n >= cap) break;
-    strncpy(out[n].name, e.name.c_str(), sizeof(out[n].name) - 1);
+    cudaEvent_t e0 = g_prof.pool[2 * i], e1 = g_prof.pool[2 * i + 1];
+    float ms = 0.f;
+    if (cudaEventSynchronize(e1) != cudaSuccess || cudaEventElapsedTime(&ms, e0, e1) != cudaSuccess) {
+      cudaGetLastError();
+      ms = -1.f;
+    }
+    strncpy(out[n].name, g_prof.names[i].c_str(), sizeof(out[n].name) - 1);
     out[n].name[sizeof(out[n].name) - 1] = 0;
-    out[n].ms = e.ms;
+    out[n].ms = ms;
     ++n;
   }
   return n;

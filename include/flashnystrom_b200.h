@@ -161,10 +161,14 @@ FNB_API int fnb_debug_pinv_backward(int64_t bh, int32_t m, int32_t newton_iter, 
                             int32_t device, void* stream);
 FNB_API size_t fnb_debug_pinv_workspace_bytes(int64_t bh, int32_t m);
 
-/* Per-kernel timing of the most recent fnb_forward / fnb_backward on this thread when the
- * environment variable FNB_PROFILE=1 was set at library load (forces a sync per kernel;
- * stands in for KernelProfiler, csrc/profile.h:44-106).  Writes up to `cap` entries. */
+/* Per-kernel timing.  Off unless the environment variable FNB_PROFILE=1 was set when the
+ * library was loaded or fnb_set_profiling(1) was called (process-wide switch; returns the
+ * previous mode).  While on, fnb_forward / fnb_backward bracket every kernel with CUDA events on
+ * the caller's stream; the call itself still does not synchronise.  fnb_last_profile() waits for
+ * the events of the most recent call made on this thread and writes up to `cap` entries.
+ * Stands in for KernelProfiler (csrc/profile.h:44-106). */
 typedef struct fnb_kernel_time { char name[48]; float ms; } fnb_kernel_time;
+FNB_API int fnb_set_profiling(int mode);
 FNB_API int fnb_last_profile(fnb_kernel_time* out, int cap);
 
 #ifdef __cplusplus
