@@ -60,6 +60,30 @@ def _ptr(t):
     return C.c_void_p(t.data_ptr())
 
 
+_status_words = {}
+
+
+def _status(device):
+    """Per-device int32 word the kernels write to when a bounded device-side wait expires."""
+    t = _status_words.get(device.index)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=device)
+        _status_words[device.index] = t
+    return t
+
+
+def check_device_status(device=None):
+    """Synchronise and raise if any kernel since the last check abandoned a bounded wait."""
+    for idx, t in list(_status_words.items()):
+        if device is not None and torch.device(device).index != idx:
+            continue
+        val = int(t.item())
+        if val != 0:
+            t.zero_()
+            raise RuntimeError(f"flashnystrom_b200: a device-side wait timed out on cuda:{idx} "
+                               f"(status 0x{val & 0xffffffff:08x}); results of that call are invalid")
+
+
 def _workspace(nbytes, device):
     return torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=device)
 
@@ -97,7 +121,7 @@ def forward(q, k, v, num_landmarks=64, newton_iter=6, kappa_star=0.0, use_tc_pin
         args = _lib.FwdArgs(shp, _ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(lse1), _ptr(qt),
                             _ptr(kt), _ptr(k2), _ptr(lse2), _ptr(iters), _ptr(k2inv), _ptr(bmat),
                             _ptr(lse3), _ptr(step2), _ptr(ws), ws.numel(), dev.index,
-                            C.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
+                            C.c_void_p(torch.cuda.current_stream(dev).cuda_stream), _ptr(_status(dev)))
         _lib.check(lib.fnb_forward(C.byref(args)))
     return [out, q, k, qt, kt, k2inv, step2, lse1, lse2, lse3, iters, k2, bmat]
 
@@ -135,7 +159,7 @@ def backward(dO, q_s, k_s, q_tilde, k_tilde, kernel2_inv, step2, lse1, lse2, lse
                             _ptr(q_tilde), _ptr(k_tilde), _ptr(k2_softmax), _ptr(ns_iterates),
                             _ptr(kernel2_inv), _ptr(b_saved), _ptr(lse3), _ptr(step2), _ptr(dq),
                             _ptr(dk), _ptr(dv), _ptr(ws), ws.numel(), dev.index,
-                            C.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
+                            C.c_void_p(torch.cuda.current_stream(dev).cuda_stream), _ptr(_status(dev)))
         _lib.check(lib.fnb_backward(C.byref(args)))
     return [dq, dk, dv]
 

@@ -29,7 +29,7 @@ class FwdArgs(C.Structure):
                 ("k2_inv", C.c_void_p), ("bmat", C.c_void_p), ("lse3", C.c_void_p),
                 ("step2", C.c_void_p),
                 ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
-                ("device", C.c_int32), ("stream", C.c_void_p)]
+                ("device", C.c_int32), ("stream", C.c_void_p), ("device_status", C.c_void_p)]
 
 
 class BwdArgs(C.Structure):
@@ -40,7 +40,7 @@ class BwdArgs(C.Structure):
                 ("bmat", C.c_void_p), ("lse3", C.c_void_p), ("step2", C.c_void_p),
                 ("dq", C.c_void_p), ("dk", C.c_void_p), ("dv", C.c_void_p),
                 ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
-                ("device", C.c_int32), ("stream", C.c_void_p)]
+                ("device", C.c_int32), ("stream", C.c_void_p), ("device_status", C.c_void_p)]
 
 
 class Caps(C.Structure):

@@ -14,6 +14,8 @@
 #include "common.cuh"
 #include "mid_kernels.cuh"
 #include "generic_kernels.cuh"
+#include "tc_host.cuh"
+#include <type_traits>
 
 namespace fnb {
 
@@ -157,6 +159,7 @@ static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 
 struct FwdWs {
   float *land_partial, *part_acc, *part_max, *part_sum, *pinv;
+  void *qt16, *kt16, *st16;   // 16-bit operand copies for the tensor-core kernels
   size_t bytes;
 };
 static FwdWs carve_fwd(const Plan& p, void* base) {
@@ -169,6 +172,9 @@ static FwdWs carve_fwd(const Plan& p, void* base) {
   w.part_max = take((size_t)p.BH * p.nchunk * p.m);
   w.part_sum = take((size_t)p.BH * p.nchunk * p.m);
   w.pinv = take((size_t)p.BH * kPinvFwdBufs * p.m * p.m);
+  const int MP = p.m <= 64 ? 64 : 128;
+  const size_t op16 = ((size_t)p.BH * MP * p.D + 1) / 2;   // 16-bit elements, counted in floats
+  w.qt16 = take(op16); w.kt16 = take(op16); w.st16 = take(op16);
   w.bytes = off;
   return w;
 }
@@ -252,6 +258,33 @@ static int forward_impl(const fnb_fwd_args& a, const Plan& p, const FwdWs& w, in
   }
   if (L.end("combine")) return L.status;
 
+  if constexpr (!std::is_same<T, float>::value) {
+    if (tc::tc_supported(a.shape.dtype, p.D, p.m, a.shape.flags)) {
+      constexpr int D = 64, MP = 64;
+      L.begin();
+      tc::pack_kernel<T><<<(unsigned)p.BH, kThreads, 0, st>>>(a.k_landmarks, (T*)w.kt16, p.m, p.D, MP, D, 0,
+                                                             scale * tc::kLog2e);
+      tc::pack_kernel<T><<<(unsigned)p.BH, kThreads, 0, st>>>(a.step2, (T*)w.st16, p.m, p.D, D, MP, 1, 1.f);
+      if (L.end("pack_fwd_c")) return L.status;
+      CUtensorMap tm_q, tm_o, tm_kt, tm_st;
+      if (!tc::make_map_3d(&tm_q, a.q, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
+          !tc::make_map_3d(&tm_o, a.out, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
+          !tc::make_map_2d(&tm_kt, w.kt16, a.shape.dtype, p.BH * MP, D, MP) ||
+          !tc::make_map_2d(&tm_st, w.st16, a.shape.dtype, p.BH * D, MP, D))
+        return fail(FNB_ERR_CUDA, "cuTensorMapEncodeTiled failed for the forward output pass");
+      tc::TcSched sch = tc::make_sched(p.BH, p.N, 296);
+      L.begin();
+      {
+        auto kern = tc::tc_fwd_c_kernel<T, D, MP>;
+        size_t smem = tc::FwdCSmem<D, MP>::kBytes;
+        if (int rc = set_smem(kern, smem, max_smem, "tc_fwd_c")) return rc;
+        kern<<<(unsigned)(p.BH * sch.nchunk), tc::kTcThreads, smem, st>>>(tm_q, tm_o, tm_kt, tm_st, a.lse1, sch,
+                                                                        p.m, a.device_status);
+      }
+      if (L.end("tc_fwd_c")) return L.status;
+      return 0;
+    }
+  }
   L.begin();
   {
     size_t smem = fwd_c_smem(p.mpad, p.D);

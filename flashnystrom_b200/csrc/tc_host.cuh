@@ -1,0 +1,82 @@
+// Host side of the tensor-core path: TMA tensor maps, tile schedule, launches.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <mutex>
+#include "tc_kernels.cuh"
+
+namespace fnb {
+namespace tc {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+// The driver entry point is resolved through the runtime, so the library does not link libcuda.
+inline EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+inline CUtensorMapDataType map_dtype(int dtype) {
+  return dtype == FNB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+}
+
+// (BH, N, D) 16-bit tensor, box = 64 columns x box_rows rows of one slice, 128-byte swizzle.
+// Rows past N read as zero and are clipped on store.
+inline bool make_map_3d(CUtensorMap* map, const void* ptr, int dtype, int64_t BH, int64_t N, int D,
+                        int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)N, (cuuint64_t)BH};
+  cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)N * D * 2};
+  cuuint32_t box[3] = {64, (cuuint32_t)box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  return fn(map, map_dtype(dtype), 3, const_cast<void*>(ptr), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// (rows, cols) 16-bit matrix, box = 64 columns x box_rows rows, 128-byte swizzle.
+inline bool make_map_2d(CUtensorMap* map, const void* ptr, int dtype, int64_t rows, int cols, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+  cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  return fn(map, map_dtype(dtype), 2, const_cast<void*>(ptr), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+inline TcSched make_sched(int64_t BH, int64_t N, int ctas_target) {
+  TcSched s;
+  s.N = N;
+  int64_t tiles = (N + kTile - 1) / kTile;
+  int64_t want = (ctas_target + BH - 1) / BH;
+  if (want > tiles) want = tiles;
+  if (want < 1) want = 1;
+  int64_t tpc = (tiles + want - 1) / want;
+  s.tiles_per_chunk = (int)tpc;
+  s.nchunk = (int)((tiles + tpc - 1) / tpc);
+  return s;
+}
+
+inline bool tc_supported(int dtype, int D, int m, uint32_t flags) {
+  if (flags & FNB_FLAG_FORCE_GENERIC) return false;
+  if (dtype != FNB_F16 && dtype != FNB_BF16) return false;
+  return D == 64 && m <= 64;
+}
+
+}  // namespace tc
+}  // namespace fnb

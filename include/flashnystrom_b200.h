@@ -84,6 +84,8 @@ typedef struct fnb_fwd_args {
   size_t workspace_bytes;
   int32_t device;       /* CUDA device ordinal all pointers live on                   */
   void* stream;         /* cudaStream_t                                               */
+  int32_t* device_status; /* optional device word, zeroed by the caller: a kernel whose
+                             bounded wait expired stores (1<<24 | location) here        */
 } fnb_fwd_args;
 
 /* Backward.  Replaces nystrom_bwd + run_nystrom_bwd_impl (csrc/flash_nystrom.cu:177-415,
@@ -112,6 +114,7 @@ typedef struct fnb_bwd_args {
   size_t workspace_bytes;
   int32_t device;
   void* stream;
+  int32_t* device_status; /* as in fnb_fwd_args */
 } fnb_bwd_args;
 
 typedef struct fnb_caps {
