@@ -160,6 +160,7 @@ static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 struct FwdWs {
   float *land_partial, *part_acc, *part_max, *part_sum, *pinv;
   void *qt16, *kt16, *st16;   // 16-bit operand copies for the tensor-core kernels
+  float* st_scale;            // [BH] power-of-two normalisation of the step2 copy
   size_t bytes;
 };
 static FwdWs carve_fwd(const Plan& p, void* base) {
@@ -175,12 +176,15 @@ static FwdWs carve_fwd(const Plan& p, void* base) {
   const int MP = p.m <= 64 ? 64 : 128;
   const size_t op16 = ((size_t)p.BH * MP * p.D + 1) / 2;   // 16-bit elements, counted in floats
   w.qt16 = take(op16); w.kt16 = take(op16); w.st16 = take(op16);
+  w.st_scale = take((size_t)p.BH);
   w.bytes = off;
   return w;
 }
 
 struct BwdWs {
   float *partA, *partB, *dstep2, *dkt_a, *dO3, *dqt_ns, *dkt_tot, *dqt_tot, *D3, *G, *dK2, *pinv;
+  void* op16[8];              // 16-bit operand copies for the tensor-core kernels
+  float *st_scale, *do3_scale;
   size_t bytes;
 };
 static BwdWs carve_bwd(const Plan& p, void* base) {
@@ -196,6 +200,10 @@ static BwdWs carve_bwd(const Plan& p, void* base) {
   w.D3 = take((size_t)p.BH * p.m);
   w.G = take(mm); w.dK2 = take(mm);
   w.pinv = take((size_t)kPinvBwdBufs * mm);
+  const int MP = p.m <= 64 ? 64 : 128;
+  const size_t op16 = ((size_t)p.BH * MP * p.D + 1) / 2;
+  for (int i = 0; i < 8; ++i) w.op16[i] = take(op16);
+  w.st_scale = take((size_t)p.BH); w.do3_scale = take((size_t)p.BH);
   w.bytes = off;
   return w;
 }
@@ -240,31 +248,60 @@ static int forward_impl(const fnb_fwd_args& a, const Plan& p, const FwdWs& w, in
   sp.nchunk = p.nchunk; sp.scale = scale;
   const unsigned sgrid = (unsigned)(p.BH * p.nchunk);
 
-  L.begin();
-  {
+  bool use_tc = false;
+  tc::TcSched sch = tc::make_sched(p.BH, p.N, 296);
+  int nchunk_b = p.nchunk;
+  if constexpr (!std::is_same<T, float>::value) {
+    use_tc = tc::tc_supported(a.shape.dtype, p.D, p.m, a.shape.flags) && sch.nchunk <= p.nchunk;
+    if (use_tc) {
+      constexpr int D = 64, MP = 64;
+      L.begin();
+      tc::pack_kernel<T><<<(unsigned)p.BH, kThreads, 0, st>>>(a.q_landmarks, (T*)w.qt16, (T*)nullptr, p.m, D, MP,
+                                                             scale * tc::kLog2e, 0, nullptr);
+      if (L.end("pack_fwd_b")) return L.status;
+      CUtensorMap tm_k, tm_v, tm_qt;
+      if (!tc::make_map_3d(&tm_k, a.k, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
+          !tc::make_map_3d(&tm_v, a.v, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
+          !tc::make_map_2d(&tm_qt, w.qt16, a.shape.dtype, p.BH * MP, D, MP))
+        return fail(FNB_ERR_CUDA, "cuTensorMapEncodeTiled failed for the forward column pass");
+      L.begin();
+      {
+        auto kern = tc::tc_fwd_b_kernel<T, D, MP>;
+        size_t smem = tc::FwdBSmem<D, MP>::kBytes;
+        if (int rc = set_smem(kern, smem, max_smem, "tc_fwd_b")) return rc;
+        kern<<<(unsigned)(p.BH * sch.nchunk), tc::kTcThreads, smem, st>>>(tm_k, tm_v, tm_qt, w.part_acc, w.part_max,
+                                                                        w.part_sum, sch, p.m, a.device_status);
+      }
+      if (L.end("tc_fwd_b")) return L.status;
+      nchunk_b = sch.nchunk;
+    }
+  }
+  if (!use_tc) {
+    L.begin();
     size_t smem = fwd_b_smem(p.mpad, p.D);
     if (int rc = set_smem(gen_fwd_b_kernel<T>, smem, max_smem, "gen_fwd_b")) return rc;
     gen_fwd_b_kernel<T><<<sgrid, kThreads, smem, st>>>(sp);
+    if (L.end("gen_fwd_b")) return L.status;
   }
-  if (L.end("gen_fwd_b")) return L.status;
 
   L.begin();
   {
     CombineParams cp;
     cp.part_acc = w.part_acc; cp.part_max = w.part_max; cp.part_sum = w.part_sum;
-    cp.nchunk = p.nchunk; cp.k2inv = a.k2_inv; cp.bmat = a.bmat; cp.lse3 = a.lse3;
+    cp.nchunk = nchunk_b; cp.k2inv = a.k2_inv; cp.bmat = a.bmat; cp.lse3 = a.lse3;
     cp.step2 = a.step2; cp.m = p.m; cp.D = p.D;
     combine_kernel<<<(unsigned)p.BH, kThreads, 0, st>>>(cp);
   }
   if (L.end("combine")) return L.status;
 
   if constexpr (!std::is_same<T, float>::value) {
-    if (tc::tc_supported(a.shape.dtype, p.D, p.m, a.shape.flags)) {
+    if (use_tc) {
       constexpr int D = 64, MP = 64;
       L.begin();
-      tc::pack_kernel<T><<<(unsigned)p.BH, kThreads, 0, st>>>(a.k_landmarks, (T*)w.kt16, p.m, p.D, MP, D, 0,
-                                                             scale * tc::kLog2e);
-      tc::pack_kernel<T><<<(unsigned)p.BH, kThreads, 0, st>>>(a.step2, (T*)w.st16, p.m, p.D, D, MP, 1, 1.f);
+      tc::pack_kernel<T><<<(unsigned)p.BH, kThreads, 0, st>>>(a.k_landmarks, (T*)w.kt16, (T*)nullptr, p.m, D, MP,
+                                                             scale * tc::kLog2e, 0, nullptr);
+      tc::pack_kernel<T><<<(unsigned)p.BH, kThreads, 0, st>>>(a.step2, (T*)nullptr, (T*)w.st16, p.m, D, MP, 1.f, 1,
+                                                             w.st_scale);
       if (L.end("pack_fwd_c")) return L.status;
       CUtensorMap tm_q, tm_o, tm_kt, tm_st;
       if (!tc::make_map_3d(&tm_q, a.q, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
@@ -272,14 +309,13 @@ static int forward_impl(const fnb_fwd_args& a, const Plan& p, const FwdWs& w, in
           !tc::make_map_2d(&tm_kt, w.kt16, a.shape.dtype, p.BH * MP, D, MP) ||
           !tc::make_map_2d(&tm_st, w.st16, a.shape.dtype, p.BH * D, MP, D))
         return fail(FNB_ERR_CUDA, "cuTensorMapEncodeTiled failed for the forward output pass");
-      tc::TcSched sch = tc::make_sched(p.BH, p.N, 296);
       L.begin();
       {
         auto kern = tc::tc_fwd_c_kernel<T, D, MP>;
         size_t smem = tc::FwdCSmem<D, MP>::kBytes;
         if (int rc = set_smem(kern, smem, max_smem, "tc_fwd_c")) return rc;
-        kern<<<(unsigned)(p.BH * sch.nchunk), tc::kTcThreads, smem, st>>>(tm_q, tm_o, tm_kt, tm_st, a.lse1, sch,
-                                                                        p.m, a.device_status);
+        kern<<<(unsigned)(p.BH * sch.nchunk), tc::kTcThreads, smem, st>>>(tm_q, tm_o, tm_kt, tm_st, a.lse1,
+                                                                        w.st_scale, sch, p.m, a.device_status);
       }
       if (L.end("tc_fwd_c")) return L.status;
       return 0;
@@ -314,15 +350,58 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
   const unsigned sgrid = (unsigned)(p.BH * p.nchunk);
   const size_t smem = bwd_ac_smem(p.mpad, p.D);
 
-  L.begin();
-  if (int rc = set_smem(gen_bwd_a_kernel<T>, smem, max_smem, "gen_bwd_a")) return rc;
-  gen_bwd_a_kernel<T><<<sgrid, kThreads, smem, st>>>(sp);
-  if (L.end("gen_bwd_a")) return L.status;
+  bool use_tc = false;
+  tc::TcSched sch = tc::make_sched(p.BH, p.N, 296);
+  int nchunk_a = p.nchunk;
+  if constexpr (!std::is_same<T, float>::value) {
+    use_tc = tc::tc_supported(a.shape.dtype, p.D, p.m, a.shape.flags) && sch.nchunk <= p.nchunk;
+  }
+  CUtensorMap tm_q, tm_g, tm_kt, tm_st, tm_ktT, tm_dq;
+  if constexpr (!std::is_same<T, float>::value) {
+    if (use_tc) {
+      constexpr int D = 64, MP = 64;
+      T* kt16 = (T*)w.op16[0];
+      T* st16 = (T*)w.op16[1];
+      T* ktT16 = (T*)w.op16[2];
+      L.begin();
+      tc::pack_kernel<T><<<(unsigned)p.BH, kThreads, 0, st>>>(a.k_landmarks, kt16, (T*)nullptr, p.m, D, MP,
+                                                             scale * tc::kLog2e, 0, nullptr);
+      tc::pack_kernel<T><<<(unsigned)p.BH, kThreads, 0, st>>>(a.k_landmarks, (T*)nullptr, ktT16, p.m, D, MP, scale,
+                                                             0, nullptr);
+      tc::pack_kernel<T><<<(unsigned)p.BH, kThreads, 0, st>>>(a.step2, st16, (T*)nullptr, p.m, D, MP, 1.f, 1,
+                                                             w.st_scale);
+      if (L.end("pack_bwd_ac")) return L.status;
+      if (!tc::make_map_3d(&tm_q, a.q, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
+          !tc::make_map_3d(&tm_g, a.d_out, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
+          !tc::make_map_3d(&tm_dq, a.dq, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
+          !tc::make_map_2d(&tm_kt, kt16, a.shape.dtype, p.BH * MP, D, MP) ||
+          !tc::make_map_2d(&tm_st, st16, a.shape.dtype, p.BH * MP, D, MP) ||
+          !tc::make_map_2d(&tm_ktT, ktT16, a.shape.dtype, p.BH * D, MP, D))
+        return fail(FNB_ERR_CUDA, "cuTensorMapEncodeTiled failed for the backward row passes");
+      L.begin();
+      {
+        auto kern = tc::tc_bwd_ac_kernel<T, D, MP, tc::kModeA>;
+        size_t sm = tc::BwdAcSmem<D, MP, tc::kModeA>::kBytes;
+        if (int rc = set_smem(kern, sm, max_smem, "tc_bwd_a")) return rc;
+        kern<<<(unsigned)(p.BH * sch.nchunk), tc::kTcThreads, sm, st>>>(
+            tm_q, tm_g, tm_kt, tm_st, tm_ktT, tm_dq, a.lse1, w.st_scale, nullptr, w.partA, sch, p.m, scale,
+            a.device_status);
+      }
+      if (L.end("tc_bwd_a")) return L.status;
+      nchunk_a = sch.nchunk;
+    }
+  }
+  if (!use_tc) {
+    L.begin();
+    if (int rc = set_smem(gen_bwd_a_kernel<T>, smem, max_smem, "gen_bwd_a")) return rc;
+    gen_bwd_a_kernel<T><<<sgrid, kThreads, smem, st>>>(sp);
+    if (L.end("gen_bwd_a")) return L.status;
+  }
 
   L.begin();
   {
     MidBwdParams mp;
-    mp.partA = w.partA; mp.nchunk = p.nchunk;
+    mp.partA = w.partA; mp.nchunk = nchunk_a;
     mp.qt = a.q_landmarks; mp.kt = a.k_landmarks; mp.k2 = a.k2; mp.iterates = a.ns_iterates;
     mp.k2inv = a.k2_inv; mp.bmat = a.bmat;
     mp.dstep2 = w.dstep2; mp.dkt_a = w.dkt_a; mp.dO3 = w.dO3; mp.D3 = w.D3;
@@ -332,16 +411,72 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
   }
   if (L.end("mid_bwd")) return L.status;
 
-  L.begin();
-  if (int rc = set_smem(gen_bwd_b_kernel<T>, smem, max_smem, "gen_bwd_b")) return rc;
-  gen_bwd_b_kernel<T><<<sgrid, kThreads, smem, st>>>(sp);
-  if (L.end("gen_bwd_b")) return L.status;
+  int nchunk_b = p.nchunk;
+  if constexpr (!std::is_same<T, float>::value) {
+    if (use_tc) {
+      constexpr int D = 64, MP = 64;
+      T* qt16 = (T*)w.op16[3];
+      T* qtT16 = (T*)w.op16[4];
+      T* do3n = (T*)w.op16[5];
+      T* do3T = (T*)w.op16[6];
+      L.begin();
+      tc::pack_kernel<T><<<(unsigned)p.BH, kThreads, 0, st>>>(a.q_landmarks, qt16, (T*)nullptr, p.m, D, MP,
+                                                             scale * tc::kLog2e, 0, nullptr);
+      tc::pack_kernel<T><<<(unsigned)p.BH, kThreads, 0, st>>>(a.q_landmarks, (T*)nullptr, qtT16, p.m, D, MP, scale,
+                                                             0, nullptr);
+      tc::pack_kernel<T><<<(unsigned)p.BH, kThreads, 0, st>>>(w.dO3, do3n, do3T, p.m, D, MP, 1.f, 1, w.do3_scale);
+      if (L.end("pack_bwd_b")) return L.status;
+      CUtensorMap tm_k, tm_v, tm_qt, tm_do3, tm_do3T, tm_qtT, tm_dk, tm_dv;
+      if (!tc::make_map_3d(&tm_k, a.k, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
+          !tc::make_map_3d(&tm_v, a.v, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
+          !tc::make_map_3d(&tm_dk, a.dk, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
+          !tc::make_map_3d(&tm_dv, a.dv, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
+          !tc::make_map_2d(&tm_qt, qt16, a.shape.dtype, p.BH * MP, D, MP) ||
+          !tc::make_map_2d(&tm_do3, do3n, a.shape.dtype, p.BH * MP, D, MP) ||
+          !tc::make_map_2d(&tm_do3T, do3T, a.shape.dtype, p.BH * D, MP, D) ||
+          !tc::make_map_2d(&tm_qtT, qtT16, a.shape.dtype, p.BH * D, MP, D))
+        return fail(FNB_ERR_CUDA, "cuTensorMapEncodeTiled failed for the backward column pass");
+      int kshift = 0;
+      while ((int64_t(2) << kshift) <= p.N && kshift < 14) ++kshift;   // floor(log2 N), at most 14
+      L.begin();
+      {
+        auto kern = tc::tc_bwd_b_kernel<T, D, MP>;
+        size_t sm = tc::BwdBSmem<D, MP>::kBytes;
+        if (int rc = set_smem(kern, sm, max_smem, "tc_bwd_b")) return rc;
+        kern<<<(unsigned)(p.BH * sch.nchunk), tc::kTcThreads, sm, st>>>(
+            tm_k, tm_v, tm_qt, tm_do3, tm_do3T, tm_qtT, tm_dk, tm_dv, a.lse3, w.D3, w.do3_scale, w.dkt_tot,
+            w.partB, sch, p.m, scale, kshift, a.device_status);
+      }
+      if (L.end("tc_bwd_b")) return L.status;
+      nchunk_b = sch.nchunk;
+    }
+  }
+  if (!use_tc) {
+    L.begin();
+    if (int rc = set_smem(gen_bwd_b_kernel<T>, smem, max_smem, "gen_bwd_b")) return rc;
+    gen_bwd_b_kernel<T><<<sgrid, kThreads, smem, st>>>(sp);
+    if (L.end("gen_bwd_b")) return L.status;
+  }
 
   L.begin();
-  dqt_reduce_kernel<<<(unsigned)p.BH, kThreads, 0, st>>>(w.partB, p.nchunk, w.dqt_ns, w.dqt_tot,
+  dqt_reduce_kernel<<<(unsigned)p.BH, kThreads, 0, st>>>(w.partB, nchunk_b, w.dqt_ns, w.dqt_tot,
                                                          p.m * p.D);
   if (L.end("dqt_reduce")) return L.status;
 
+  if constexpr (!std::is_same<T, float>::value) {
+    if (use_tc) {
+      constexpr int D = 64, MP = 64;
+      L.begin();
+      auto kern = tc::tc_bwd_ac_kernel<T, D, MP, tc::kModeC>;
+      size_t sm = tc::BwdAcSmem<D, MP, tc::kModeC>::kBytes;
+      if (int rc = set_smem(kern, sm, max_smem, "tc_bwd_c")) return rc;
+      kern<<<(unsigned)(p.BH * sch.nchunk), tc::kTcThreads, sm, st>>>(
+          tm_q, tm_g, tm_kt, tm_st, tm_ktT, tm_dq, a.lse1, w.st_scale, w.dqt_tot, nullptr, sch, p.m, scale,
+          a.device_status);
+      if (L.end("tc_bwd_c")) return L.status;
+      return 0;
+    }
+  }
   L.begin();
   if (int rc = set_smem(gen_bwd_c_kernel<T>, smem, max_smem, "gen_bwd_c")) return rc;
   gen_bwd_c_kernel<T><<<sgrid, kThreads, smem, st>>>(sp);
