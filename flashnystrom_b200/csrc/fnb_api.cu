@@ -15,6 +15,7 @@
 #include "mid_kernels.cuh"
 #include "generic_kernels.cuh"
 #include "tc_host.cuh"
+#include "ns_kernels.cuh"
 #include <type_traits>
 
 namespace fnb {
@@ -235,9 +236,20 @@ static int forward_impl(const fnb_fwd_args& a, const Plan& p, const FwdWs& w, in
     mp.iterates = a.ns_iterates; mp.k2inv = a.k2_inv; mp.scratch = w.pinv;
     mp.BH = p.BH; mp.N = p.N; mp.m = p.m; mp.D = p.D; mp.J = p.J;
     mp.kappa = a.shape.kappa_star; mp.scale = scale;
+    mp.landmarks_only = p.m <= ns::kN ? 1 : 0;
     mid_fwd_kernel<<<(unsigned)p.BH, kThreads, 0, st>>>(mp);
   }
   if (L.end("mid_fwd")) return L.status;
+  if (p.m <= ns::kN) {
+    L.begin();
+    ns::NsFwdParams np;
+    np.qt = a.q_landmarks; np.kt = a.k_landmarks; np.k2 = a.k2; np.lse2 = a.lse2;
+    np.iterates = a.ns_iterates; np.k2inv = a.k2_inv; np.m = p.m; np.D = p.D; np.J = p.J;
+    np.kappa = a.shape.kappa_star;
+    if (int rc = set_smem(ns::ns_fwd_kernel, ns::kFwdSmem, max_smem, "ns_fwd")) return rc;
+    ns::ns_fwd_kernel<<<(unsigned)p.BH, kThreads, ns::kFwdSmem, st>>>(np);
+    if (L.end("ns_fwd")) return L.status;
+  }
 
   StreamParams sp;
   memset(&sp, 0, sizeof(sp));
@@ -407,9 +419,20 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
     mp.dstep2 = w.dstep2; mp.dkt_a = w.dkt_a; mp.dO3 = w.dO3; mp.D3 = w.D3;
     mp.dqt_ns = w.dqt_ns; mp.dkt_tot = w.dkt_tot; mp.G = w.G; mp.dK2 = w.dK2; mp.scratch = w.pinv;
     mp.m = p.m; mp.D = p.D; mp.J = p.J; mp.kappa = a.shape.kappa_star;
+    mp.first_half_only = p.m <= ns::kN ? 1 : 0;
     mid_bwd_kernel<<<(unsigned)p.BH, kThreads, 0, st>>>(mp);
   }
   if (L.end("mid_bwd")) return L.status;
+  if (p.m <= ns::kN) {
+    L.begin();
+    ns::NsBwdParams np;
+    np.k2 = a.k2; np.iterates = a.ns_iterates; np.G = w.G; np.qt = a.q_landmarks; np.kt = a.k_landmarks;
+    np.dkt_a = w.dkt_a; np.dqt_ns = w.dqt_ns; np.dkt_tot = w.dkt_tot; np.spill = w.dK2;
+    np.m = p.m; np.D = p.D; np.J = p.J; np.kappa = a.shape.kappa_star;
+    if (int rc = set_smem(ns::ns_bwd_kernel, ns::kBwdSmem, max_smem, "ns_bwd")) return rc;
+    ns::ns_bwd_kernel<<<(unsigned)p.BH, kThreads, ns::kBwdSmem, st>>>(np);
+    if (L.end("ns_bwd")) return L.status;
+  }
 
   int nchunk_b = p.nchunk;
   if constexpr (!std::is_same<T, float>::value) {
@@ -601,8 +624,15 @@ int fnb_debug_pinv_forward(int64_t bh, int32_t m, int32_t J, float kappa, const 
   if (!k2 || !ns_iterates || !k2_inv) return fail(FNB_ERR_INVALID_ARGUMENT, "NULL tensor pointer");
   DeviceGuard g(device);
   if (!g.ok) return fail(FNB_ERR_CUDA, "cannot select CUDA device %d", device);
-  pinv_fwd_debug_kernel<<<(unsigned)bh, kThreads, 0, (cudaStream_t)stream>>>(
-      k2, ns_iterates, k2_inv, (float*)workspace, m, J, kappa);
+  if (m <= ns::kN) {
+    FNB_CUDA(cudaFuncSetAttribute(ns::ns_pinv_fwd_debug_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  (int)ns::kFwdSmem));
+    ns::ns_pinv_fwd_debug_kernel<<<(unsigned)bh, kThreads, ns::kFwdSmem, (cudaStream_t)stream>>>(
+        k2, ns_iterates, k2_inv, m, J, kappa);
+  } else {
+    pinv_fwd_debug_kernel<<<(unsigned)bh, kThreads, 0, (cudaStream_t)stream>>>(
+        k2, ns_iterates, k2_inv, (float*)workspace, m, J, kappa);
+  }
   FNB_CUDA(cudaPeekAtLastError());
   return 0;
 }
@@ -614,8 +644,15 @@ int fnb_debug_pinv_backward(int64_t bh, int32_t m, int32_t J, float kappa, const
   if (!k2 || !ns_iterates || !d_k2_inv || !d_k2) return fail(FNB_ERR_INVALID_ARGUMENT, "NULL tensor pointer");
   DeviceGuard g(device);
   if (!g.ok) return fail(FNB_ERR_CUDA, "cannot select CUDA device %d", device);
-  pinv_bwd_debug_kernel<<<(unsigned)bh, kThreads, 0, (cudaStream_t)stream>>>(
-      k2, ns_iterates, d_k2_inv, d_k2, (float*)workspace, m, J, kappa);
+  if (m <= ns::kN) {
+    FNB_CUDA(cudaFuncSetAttribute(ns::ns_pinv_bwd_debug_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  (int)ns::kBwdSmem));
+    ns::ns_pinv_bwd_debug_kernel<<<(unsigned)bh, kThreads, ns::kBwdSmem, (cudaStream_t)stream>>>(
+        k2, ns_iterates, d_k2_inv, d_k2, (float*)workspace, m, J, kappa);
+  } else {
+    pinv_bwd_debug_kernel<<<(unsigned)bh, kThreads, 0, (cudaStream_t)stream>>>(
+        k2, ns_iterates, d_k2_inv, d_k2, (float*)workspace, m, J, kappa);
+  }
   FNB_CUDA(cudaPeekAtLastError());
   return 0;
 }

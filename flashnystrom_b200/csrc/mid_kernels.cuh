@@ -285,6 +285,7 @@ struct MidFwdParams {
   int64_t BH, N;
   int m, D, J;
   float kappa, scale;
+  int landmarks_only;         // 1: stop after writing qt / kt (the shared-memory NS kernel follows)
 };
 
 __global__ void __launch_bounds__(kThreads) mid_fwd_kernel(MidFwdParams p) {
@@ -303,6 +304,7 @@ __global__ void __launch_bounds__(kThreads) mid_fwd_kernel(MidFwdParams p) {
     float val = s * (p.scale / (float)sg.len(l));
     (which ? kt : qt)[rem] = val;
   }
+  if (p.landmarks_only) return;
   __syncthreads();
   float* k2 = p.k2 + bh * m * m;
   cta_gemm<false, true>(k2, m, qt, D, kt, D, m, m, D, 1.f, 0.f, 0.f, sm);
@@ -424,6 +426,7 @@ struct MidBwdParams {
   float* scratch;            // [BH][kPinvBwdBufs][m][m]
   int m, D, J;
   float kappa;
+  int first_half_only;       // 1: stop after dO3 / dK2inv / D3 (the shared-memory NS kernel follows)
 };
 
 __global__ void __launch_bounds__(kThreads) mid_bwd_kernel(MidBwdParams p) {
@@ -458,6 +461,7 @@ __global__ void __launch_bounds__(kThreads) mid_bwd_kernel(MidBwdParams p) {
       if (lane == 0) p.D3[bh * m + l] = s;
     }
   }
+  if (p.first_half_only) return;
   pinv_backward(k2, p.iterates + bh * (size_t)(p.J + 1) * mm, G, dK2,
                 p.scratch + bh * (size_t)kPinvBwdBufs * mm, m, p.J, p.kappa, sm);
   // softmax-2 Jacobian, in place: dS2 = K2 o (dK2 - rowsum(dK2 o K2))

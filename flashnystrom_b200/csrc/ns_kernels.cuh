@@ -1,0 +1,448 @@
+// Newton-Schulz pseudoinverse, forward and exact backward, entirely in shared memory (FP32, CUDA
+// cores, no cuBLAS) for num_landmarks <= 64.  One CTA of 256 threads per (b,h) slice; every
+// (m x m) matrix lives in a zero-padded 64 x 64 shared buffer with row stride 68, so all loops
+// have compile-time bounds and every operand access is a conflict-free 16-byte load.
+// Larger landmark counts use the global-memory version in mid_kernels.cuh.
+#pragma once
+#include "common.cuh"
+#include "mid_kernels.cuh"
+
+namespace fnb {
+namespace ns {
+
+constexpr int kN = 64;          // padded matrix size
+constexpr int kLd = 68;         // row stride (floats): 16-byte aligned rows, rows 8 apart hit distinct banks
+constexpr int kBuf = kN * kLd;  // floats per buffer
+
+enum { NN = 0, NT = 1, TN = 2 };
+
+// C-tile of this thread for op(A) * op(B), all operands 64 x 64 in shared memory.
+//   NN: C = A B      rows ty+16i, cols 4tx+j
+//   NT: C = A B^T    rows ty+16i, cols tx+16j
+//   TN: C = A^T B    rows 4ty+i,  cols 4tx+j
+// epi(r, c, acc) is called once per owned element after a barrier, so outputs may alias inputs;
+// a second barrier follows the stores.
+template <int MODE, class Epi>
+__device__ __forceinline__ void mm(const float* __restrict__ A, const float* __restrict__ B, Epi epi) {
+  const int t = threadIdx.x, tx = t & 15, ty = t >> 4;
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+  if (MODE == NN) {
+#pragma unroll 4
+    for (int k = 0; k < kN; k += 4) {
+      float4 a[4], b[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[i] = *reinterpret_cast<const float4*>(A + (ty + 16 * i) * kLd + k);
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk) b[kk] = *reinterpret_cast<const float4*>(B + (k + kk) * kLd + 4 * tx);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float av[4] = {a[i].x, a[i].y, a[i].z, a[i].w};
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+          acc[i][0] = fmaf(av[kk], b[kk].x, acc[i][0]);
+          acc[i][1] = fmaf(av[kk], b[kk].y, acc[i][1]);
+          acc[i][2] = fmaf(av[kk], b[kk].z, acc[i][2]);
+          acc[i][3] = fmaf(av[kk], b[kk].w, acc[i][3]);
+        }
+      }
+    }
+  } else if (MODE == NT) {
+#pragma unroll 4
+    for (int k = 0; k < kN; k += 4) {
+      float4 a[4], b[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[i] = *reinterpret_cast<const float4*>(A + (ty + 16 * i) * kLd + k);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) b[j] = *reinterpret_cast<const float4*>(B + (tx + 16 * j) * kLd + k);
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          acc[i][j] = fmaf(a[i].x, b[j].x, acc[i][j]);
+          acc[i][j] = fmaf(a[i].y, b[j].y, acc[i][j]);
+          acc[i][j] = fmaf(a[i].z, b[j].z, acc[i][j]);
+          acc[i][j] = fmaf(a[i].w, b[j].w, acc[i][j]);
+        }
+    }
+  } else {
+#pragma unroll 8
+    for (int k = 0; k < kN; ++k) {
+      const float4 a = *reinterpret_cast<const float4*>(A + k * kLd + 4 * ty);
+      const float4 b = *reinterpret_cast<const float4*>(B + k * kLd + 4 * tx);
+      const float av[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        acc[i][0] = fmaf(av[i], b.x, acc[i][0]);
+        acc[i][1] = fmaf(av[i], b.y, acc[i][1]);
+        acc[i][2] = fmaf(av[i], b.z, acc[i][2]);
+        acc[i][3] = fmaf(av[i], b.w, acc[i][3]);
+      }
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int r = (MODE == TN) ? 4 * ty + i : ty + 16 * i;
+      const int c = (MODE == NT) ? tx + 16 * j : 4 * tx + j;
+      epi(r, c, acc[i][j]);
+    }
+  __syncthreads();
+}
+
+__device__ __forceinline__ void zero_buf(float* X) {
+  for (int idx = threadIdx.x; idx < kBuf; idx += kThreads) X[idx] = 0.f;
+}
+// global (m x m, dense) -> padded shared buffer
+__device__ __forceinline__ void load_mat(float* X, const float* g, int m) {
+  for (int idx = threadIdx.x; idx < kN * kN; idx += kThreads) {
+    int r = idx >> 6, c = idx & 63;
+    X[r * kLd + c] = (r < m && c < m) ? g[r * m + c] : 0.f;
+  }
+}
+__device__ __forceinline__ void store_mat(float* g, const float* X, int m) {
+  for (int idx = threadIdx.x; idx < m * m; idx += kThreads) {
+    int r = idx / m, c = idx - r * m;
+    g[idx] = X[r * kLd + c];
+  }
+}
+
+struct Norms { float n1, ninf; int jc, ir; };
+// max column / row abs-sum with first-occurrence argmax; red: 128 floats of shared scratch
+__device__ inline Norms norms(const float* X, int m, float* red) {
+  const int t = threadIdx.x;
+  if (t < kN) {
+    float cs = 0.f;
+    for (int i = 0; i < m; ++i) cs += fabsf(X[i * kLd + t]);
+    red[t] = cs;
+  } else if (t < 2 * kN) {
+    const int i = t - kN;
+    float rs = 0.f;
+    for (int j = 0; j < m; ++j) rs += fabsf(X[i * kLd + j]);
+    red[t] = rs;
+  }
+  __syncthreads();
+  Norms out;
+  {
+    float best = red[0]; int bi = 0;
+    for (int j = 1; j < m; ++j) if (red[j] > best) { best = red[j]; bi = j; }
+    out.n1 = best; out.jc = bi;
+    best = red[kN]; bi = 0;
+    for (int i = 1; i < m; ++i) if (red[kN + i] > best) { best = red[kN + i]; bi = i; }
+    out.ninf = best; out.ir = bi;
+  }
+  __syncthreads();
+  return out;
+}
+
+constexpr int kFwdBufs = 7;
+constexpr size_t kFwdSmem = (size_t)kFwdBufs * kBuf * sizeof(float) + 1024;
+
+// K2 (in shared buffer bK2, already softmaxed, padded) -> iterates / k2inv in global memory.
+__device__ inline void pinv_forward_smem(float* sm, float* red, float* iterates, float* k2inv, int m, int J,
+                                         float kappa) {
+  float* bK2 = sm;
+  float* bA = sm + 1 * kBuf;
+  float* bZ = sm + 2 * kBuf;
+  float* bM = sm + 3 * kBuf;
+  float* bU = sm + 4 * kBuf;
+  float* bV = sm + 5 * kBuf;
+  float* bT = sm + 6 * kBuf;
+  const int mm_ = m * m;
+  const float* A = bK2;
+  if (kappa > 0.f) {
+    Norms nk = norms(bK2, m, red);
+    const float lam = nk.n1 * nk.ninf / kappa;
+    mm<TN>(bK2, bK2, [&](int r, int c, float acc) { bA[r * kLd + c] = acc + ((r == c && r < m) ? lam : 0.f); });
+    A = bA;
+  }
+  Norms na = norms(A, m, red);
+  const float cden = fmaxf(na.n1 * na.ninf, 1e-12f);
+  for (int idx = threadIdx.x; idx < kN * kN; idx += kThreads) {
+    int r = idx >> 6, c = idx & 63;
+    float z = A[c * kLd + r] / cden;
+    bZ[r * kLd + c] = z;
+    if (r < m && c < m) iterates[r * m + c] = z;
+  }
+  __syncthreads();
+  for (int j = 0; j < J; ++j) {
+    float* Zn = iterates + (size_t)(j + 1) * mm_;
+    mm<NN>(A, bZ, [&](int r, int c, float acc) {
+      bM[r * kLd + c] = acc;
+      bU[r * kLd + c] = ((r == c && r < m) ? 7.f : 0.f) - acc;
+    });
+    mm<NN>(bM, bU, [&](int r, int c, float acc) { bV[r * kLd + c] = ((r == c && r < m) ? 15.f : 0.f) - acc; });
+    mm<NN>(bM, bV, [&](int r, int c, float acc) { bT[r * kLd + c] = ((r == c && r < m) ? 13.f : 0.f) - acc; });
+    mm<NN>(bZ, bT, [&](int r, int c, float acc) {
+      const float z = 0.25f * acc;
+      bZ[r * kLd + c] = z;
+      if (r < m && c < m) Zn[r * m + c] = z;
+    });
+  }
+  if (kappa > 0.f) {
+    mm<NT>(bZ, bK2, [&](int r, int c, float acc) { if (r < m && c < m) k2inv[r * m + c] = acc; });
+  } else {
+    store_mat(k2inv, bZ, m);
+    __syncthreads();
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// Forward: S2 = Qt Kt^T, softmax (K2, lse2), pseudoinverse.
+struct NsFwdParams {
+  const float* qt; const float* kt;         // [BH][m][D] (scaled landmarks)
+  float* k2; float* lse2; float* iterates; float* k2inv;
+  int m, D, J;
+  float kappa;
+};
+
+__global__ void __launch_bounds__(kThreads, 1) ns_fwd_kernel(NsFwdParams p) {
+  extern __shared__ float sm[];
+  __shared__ float red[2 * kN];
+  const int64_t bh = blockIdx.x;
+  const int m = p.m, D = p.D, t = threadIdx.x, tx = t & 15, ty = t >> 4;
+  float* bK2 = sm;
+  const float* qt = p.qt + bh * m * D;
+  const float* kt = p.kt + bh * m * D;
+  // S2 tile straight from global (L2): rows ty+16i, cols tx+16j
+  {
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+    for (int d = 0; d < D; d += 4) {
+      float4 a[4], b[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int r = ty + 16 * i;
+        a[i] = (r < m) ? *reinterpret_cast<const float4*>(qt + r * D + d) : make_float4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int c = tx + 16 * j;
+        b[j] = (c < m) ? *reinterpret_cast<const float4*>(kt + c * D + d) : make_float4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          acc[i][j] += a[i].x * b[j].x + a[i].y * b[j].y + a[i].z * b[j].z + a[i].w * b[j].w;
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) bK2[(ty + 16 * i) * kLd + tx + 16 * j] = acc[i][j];
+  }
+  __syncthreads();
+  // row softmax, one warp per row; padded rows / columns become zero
+  const int w = t >> 5, lane = t & 31;
+  float* k2g = p.k2 + bh * m * m;
+  for (int r = w; r < kN; r += kThreads / 32) {
+    float v0 = (r < m && lane < m) ? bK2[r * kLd + lane] : -INFINITY;
+    float v1 = (r < m && lane + 32 < m) ? bK2[r * kLd + lane + 32] : -INFINITY;
+    float mx = fmaxf(v0, v1);
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    float e0 = (r < m && lane < m) ? expf(v0 - mx) : 0.f;
+    float e1 = (r < m && lane + 32 < m) ? expf(v1 - mx) : 0.f;
+    float sum = e0 + e1;
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    const float p0 = (r < m) ? e0 / sum : 0.f, p1 = (r < m) ? e1 / sum : 0.f;
+    bK2[r * kLd + lane] = p0;
+    bK2[r * kLd + lane + 32] = p1;
+    if (r < m) {
+      if (lane < m) k2g[r * m + lane] = p0;
+      if (lane + 32 < m) k2g[r * m + lane + 32] = p1;
+      if (lane == 0) p.lse2[bh * m + r] = mx + logf(sum);
+    }
+  }
+  __syncthreads();
+  pinv_forward_smem(sm, red, p.iterates + bh * (size_t)(p.J + 1) * m * m, p.k2inv + bh * m * m, m, p.J,
+                    p.kappa);
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+ns_pinv_fwd_debug_kernel(const float* k2, float* iterates, float* k2inv, int m, int J, float kappa) {
+  extern __shared__ float sm[];
+  __shared__ float red[2 * kN];
+  const int64_t bh = blockIdx.x;
+  load_mat(sm, k2 + bh * m * m, m);
+  __syncthreads();
+  pinv_forward_smem(sm, red, iterates + bh * (size_t)(J + 1) * m * m, k2inv + bh * m * m, m, J, kappa);
+}
+
+// ------------------------------------------------------------------------------------------
+constexpr int kBwdBufs = 12;
+constexpr size_t kBwdSmem = (size_t)kBwdBufs * kBuf * sizeof(float) + 1024;
+
+// G = dL/d k2inv (global) -> dK2 = dL/d K2 left in shared buffer bdA (returned pointer).
+// spill: (m x m) floats of global scratch, used only with the ridge.
+__device__ inline float* pinv_backward_smem(float* sm, float* red, const float* k2g, const float* iterates,
+                                            const float* G, float* spill, int m, int J, float kappa) {
+  float* bK2 = sm;
+  float* bA = sm + 1 * kBuf;
+  float* bZ = sm + 2 * kBuf;
+  float* bM = sm + 3 * kBuf;
+  float* bU = sm + 4 * kBuf;
+  float* bV = sm + 5 * kBuf;
+  float* bT = sm + 6 * kBuf;     // T, then dZ_outer
+  float* bdZ = sm + 7 * kBuf;
+  float* bdT = sm + 8 * kBuf;
+  float* bdV = sm + 9 * kBuf;
+  float* bdM = sm + 10 * kBuf;
+  float* bdA = sm + 11 * kBuf;
+  const int mm_ = m * m;
+  load_mat(bK2, k2g, m);
+  load_mat(bdZ, G, m);          // holds G until dZ_J is formed
+  zero_buf(bdA);
+  __syncthreads();
+  const float* A = bK2;
+  if (kappa > 0.f) {
+    Norms nk = norms(bK2, m, red);
+    const float lam = nk.n1 * nk.ninf / kappa;
+    mm<TN>(bK2, bK2, [&](int r, int c, float acc) { bA[r * kLd + c] = acc + ((r == c && r < m) ? lam : 0.f); });
+    A = bA;
+    load_mat(bZ, iterates + (size_t)J * mm_, m);
+    __syncthreads();
+    // dK2_a = G^T Z_J -> global spill; dZ_J = G K2
+    mm<TN>(bdZ, bZ, [&](int r, int c, float acc) { if (r < m && c < m) spill[r * m + c] = acc; });
+    mm<NN>(bdZ, bK2, [&](int r, int c, float acc) { bdZ[r * kLd + c] = acc; });
+  }
+  for (int j = J - 1; j >= 0; --j) {
+    load_mat(bZ, iterates + (size_t)j * mm_, m);
+    __syncthreads();
+    mm<NN>(A, bZ, [&](int r, int c, float acc) {
+      bM[r * kLd + c] = acc;
+      bU[r * kLd + c] = ((r == c && r < m) ? 7.f : 0.f) - acc;
+    });
+    mm<NN>(bM, bU, [&](int r, int c, float acc) { bV[r * kLd + c] = ((r == c && r < m) ? 15.f : 0.f) - acc; });
+    mm<NN>(bM, bV, [&](int r, int c, float acc) { bT[r * kLd + c] = ((r == c && r < m) ? 13.f : 0.f) - acc; });
+    mm<TN>(bZ, bdZ, [&](int r, int c, float acc) { bdT[r * kLd + c] = 0.25f * acc; });           // dT = Z^T dZ / 4
+    mm<NT>(bdZ, bT, [&](int r, int c, float acc) { bT[r * kLd + c] = 0.25f * acc; });            // dZ_outer
+    mm<NT>(bdT, bV, [&](int r, int c, float acc) { bdM[r * kLd + c] = -acc; });                  // -dT V^T
+    mm<TN>(bM, bdT, [&](int r, int c, float acc) { bdV[r * kLd + c] = -acc; });                  // dV = -M^T dT
+    mm<NT>(bdV, bU, [&](int r, int c, float acc) { bdM[r * kLd + c] -= acc; });                  // -= dV U^T
+    mm<TN>(bM, bdV, [&](int r, int c, float acc) { bdM[r * kLd + c] += acc; });                  // += M^T dV
+    mm<NT>(bdM, bZ, [&](int r, int c, float acc) { bdA[r * kLd + c] += acc; });                  // dA += dM Z^T
+    mm<TN>(A, bdM, [&](int r, int c, float acc) { bdZ[r * kLd + c] = bT[r * kLd + c] + acc; });  // dZ_outer + A^T dM
+  }
+  // Z0 = A^T / c,  c = ||A||_1 ||A||_inf
+  Norms na = norms(A, m, red);
+  const float craw = na.n1 * na.ninf;
+  const float cden = fmaxf(craw, 1e-12f);
+  float part = 0.f;
+  for (int idx = threadIdx.x; idx < kN * kN; idx += kThreads) {
+    int a = idx >> 6, b = idx & 63;
+    part += bdZ[a * kLd + b] * A[b * kLd + a];
+  }
+  for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = part;
+  __syncthreads();
+  float S = 0.f;
+  for (int w = 0; w < kThreads / 32; ++w) S += red[w];
+  __syncthreads();
+  const bool clamped = !(craw > 1e-12f);
+  const float col_term = clamped ? 0.f : -S * na.ninf / (cden * cden);
+  const float row_term = clamped ? 0.f : -S * na.n1 / (cden * cden);
+  for (int idx = threadIdx.x; idx < kN * kN; idx += kThreads) {
+    int r = idx >> 6, c = idx & 63;
+    if (r < m && c < m) {
+      const float a = A[r * kLd + c];
+      const float sg = a > 0.f ? 1.f : (a < 0.f ? -1.f : 0.f);
+      float g = bdA[r * kLd + c] + bdZ[c * kLd + r] / cden;
+      if (c == na.jc) g += sg * col_term;
+      if (r == na.ir) g += sg * row_term;
+      bdM[r * kLd + c] = g;              // dA complete (staged in bdM to avoid the transpose hazard)
+    } else {
+      bdM[r * kLd + c] = 0.f;
+    }
+  }
+  __syncthreads();
+  if (kappa > 0.f) {
+    // dK2 = dK2_a + K2 (dA + dA^T)
+    for (int idx = threadIdx.x; idx < kN * kN; idx += kThreads) {
+      int r = idx >> 6, c = idx & 63;
+      bdT[r * kLd + c] = bdM[r * kLd + c] + bdM[c * kLd + r];
+    }
+    __syncthreads();
+    mm<NN>(bK2, bdT, [&](int r, int c, float acc) {
+      bdA[r * kLd + c] = (r < m && c < m) ? acc + spill[r * m + c] : 0.f;
+    });
+  } else {
+    for (int idx = threadIdx.x; idx < kBuf; idx += kThreads) bdA[idx] = bdM[idx];
+    __syncthreads();
+  }
+  return bdA;
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+ns_pinv_bwd_debug_kernel(const float* k2, const float* iterates, const float* G, float* dK2, float* spill,
+                         int m, int J, float kappa) {
+  extern __shared__ float sm[];
+  __shared__ float red[2 * kN];
+  const int64_t bh = blockIdx.x;
+  float* out = pinv_backward_smem(sm, red, k2 + bh * m * m, iterates + bh * (size_t)(J + 1) * m * m,
+                                  G + bh * m * m, spill + bh * m * m, m, J, kappa);
+  store_mat(dK2 + bh * m * m, out, m);
+}
+
+// Backward middle stage 2: pseudoinverse backward, softmax-2 Jacobian, landmark gradients.
+struct NsBwdParams {
+  const float* k2; const float* iterates; const float* G;   // G = dK2inv [BH][m][m]
+  const float* qt; const float* kt; const float* dkt_a;     // [BH][m][D]
+  float* dqt_ns; float* dkt_tot;                            // [BH][m][D]
+  float* spill;                                             // [BH][m][m]
+  int m, D, J;
+  float kappa;
+};
+
+__global__ void __launch_bounds__(kThreads, 1) ns_bwd_kernel(NsBwdParams p) {
+  extern __shared__ float sm[];
+  __shared__ float red[2 * kN];
+  const int64_t bh = blockIdx.x;
+  const int m = p.m, D = p.D, t = threadIdx.x, mm_ = m * m, md = m * D;
+  float* dK2 = pinv_backward_smem(sm, red, p.k2 + bh * mm_, p.iterates + bh * (size_t)(p.J + 1) * mm_,
+                                  p.G + bh * mm_, p.spill + bh * mm_, m, p.J, p.kappa);
+  const float* bK2 = sm;
+  // softmax-2 Jacobian in place: dS2 = K2 o (dK2 - rowsum(dK2 o K2))
+  const int w = t >> 5, lane = t & 31;
+  for (int r = w; r < kN; r += kThreads / 32) {
+    float a0 = dK2[r * kLd + lane], a1 = dK2[r * kLd + lane + 32];
+    float k0 = bK2[r * kLd + lane], k1 = bK2[r * kLd + lane + 32];
+    float s = a0 * k0 + a1 * k1;
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    dK2[r * kLd + lane] = k0 * (a0 - s);
+    dK2[r * kLd + lane + 32] = k1 * (a1 - s);
+  }
+  __syncthreads();
+  // dqt_ns = dS2 Kt ; dkt_tot = dkt_a + dS2^T Qt.  Thread owns 4 consecutive d of one landmark row.
+  const float* kt = p.kt + bh * md;
+  const float* qt = p.qt + bh * md;
+  const float* dkt_a = p.dkt_a + bh * md;
+  float* dqt_ns = p.dqt_ns + bh * md;
+  float* dkt_tot = p.dkt_tot + bh * md;
+  const int vec_per_row = D >> 2;
+  for (int v = t; v < m * vec_per_row; v += kThreads) {
+    const int l = v / vec_per_row, d = (v - l * vec_per_row) << 2;
+    float4 a = make_float4(0, 0, 0, 0);
+    float4 b = *reinterpret_cast<const float4*>(dkt_a + l * D + d);
+    for (int k = 0; k < m; ++k) {
+      const float s1 = dK2[l * kLd + k];     // dS2[l][k]
+      const float s2 = dK2[k * kLd + l];     // dS2[k][l]
+      const float4 kv = *reinterpret_cast<const float4*>(kt + k * D + d);
+      const float4 qv = *reinterpret_cast<const float4*>(qt + k * D + d);
+      a.x = fmaf(s1, kv.x, a.x); a.y = fmaf(s1, kv.y, a.y); a.z = fmaf(s1, kv.z, a.z); a.w = fmaf(s1, kv.w, a.w);
+      b.x = fmaf(s2, qv.x, b.x); b.y = fmaf(s2, qv.y, b.y); b.z = fmaf(s2, qv.z, b.z); b.w = fmaf(s2, qv.w, b.w);
+    }
+    *reinterpret_cast<float4*>(dqt_ns + l * D + d) = a;
+    *reinterpret_cast<float4*>(dkt_tot + l * D + d) = b;
+  }
+}
+
+}  // namespace ns
+}  // namespace fnb

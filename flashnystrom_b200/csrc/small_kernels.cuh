@@ -1,0 +1,334 @@
+// Landmark-sized glue between the streaming passes, one CTA of 256 threads per (b,h) slice,
+// row-parallel: 4 threads share one landmark row and each owns D/4 consecutive columns, so the
+// reductions over per-CTA partials are coalesced float4 streams and need no index division.
+//
+//   combine2_kernel  : merge softmax-3 partials -> Bmat, lse3; step2 = K2inv Bmat; 16-bit operand
+//                      copies for the forward output pass
+//   bwd_mid1_kernel  : reduce softmax-1 side partials -> dstep2, dKt_a; dO3 = K2inv^T dstep2;
+//                      dK2inv = dstep2 Bmat^T; D3; 16-bit operand copies for the column pass
+//   pack_bwd_ac_kernel : 16-bit operand copies for the backward row passes
+#pragma once
+#include "common.cuh"
+
+namespace fnb {
+
+__device__ __forceinline__ void store16(void* p, int dtype, size_t idx, float v) {
+  if (dtype == 1) reinterpret_cast<__half*>(p)[idx] = __float2half_rn(v);
+  else reinterpret_cast<__nv_bfloat16*>(p)[idx] = __float2bfloat16_rn(v);
+}
+
+// max over the CTA; red: 8 floats of shared scratch.  Ends with a barrier.
+__device__ __forceinline__ float cta_max(float v, float* red) {
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float r = red[0];
+  for (int w = 1; w < kThreads / 32; ++w) r = fmaxf(r, red[w]);
+  return r;
+}
+// power of two >= amax (exact scale), 1 for a zero / non-finite matrix
+__device__ __forceinline__ float pow2_scale(float amax) {
+  int e = 0;
+  if (amax > 0.f && isfinite(amax)) frexpf(amax, &e);
+  e = max(-100, min(100, e));
+  return ldexpf(1.f, e);
+}
+
+// 16-bit copies of an FP32 (m x D) global matrix: out_n[MP][D] and / or out_t[D][MP], times mul.
+__device__ __forceinline__ void pack_pair(const float* src, void* out_n, void* out_t, int dtype, int m, int D,
+                                          int MP, float mul) {
+  if (out_n)
+    for (int idx = threadIdx.x; idx < MP * D; idx += kThreads)
+      store16(out_n, dtype, idx, (idx / D) < m ? src[idx] * mul : 0.f);
+  if (out_t)
+    for (int idx = threadIdx.x; idx < D * MP; idx += kThreads) {
+      int d = idx / MP, l = idx - d * MP;
+      store16(out_t, dtype, idx, l < m ? src[l * D + d] * mul : 0.f);
+    }
+}
+
+struct Combine2Params {
+  const float* part_acc; const float* part_max; const float* part_sum;  // [BH][nchunk][m][D], [..][m]
+  int nchunk;
+  const float* k2inv;         // [BH][m][m]
+  const float* k_landmarks;   // [BH][m][D]
+  float* bmat; float* lse3; float* step2;
+  int m, D;
+  // operand copies (skipped when dtype == 0)
+  int dtype, MP;
+  void* kt16;                 // [BH][MP][D]  = kt_mul * Kt
+  void* st16T;                // [BH][D][MP]  = step2^T / st_scale
+  float* st_scale;            // [BH]
+  float kt_mul;
+};
+
+__global__ void __launch_bounds__(kThreads) combine2_kernel(Combine2Params p) {
+  extern __shared__ float sm[];            // bmat then step2: [m][D]
+  __shared__ float red[8];
+  const int64_t bh = blockIdx.x;
+  const int m = p.m, D = p.D, t = threadIdx.x, nc = p.nchunk;
+  const int q = t & 3, dpt = D >> 2, nv = dpt >> 2, d0 = q * dpt;
+  const float* pmax = p.part_max + bh * (int64_t)nc * m;
+  const float* psum = p.part_sum + bh * (int64_t)nc * m;
+  const float* pacc = p.part_acc + bh * (int64_t)nc * m * D;
+  for (int l = t >> 2; l < m; l += kThreads / 4) {
+    float M = -INFINITY;
+    for (int c = 0; c < nc; ++c) M = fmaxf(M, pmax[c * m + l]);
+    float Lsum = 0.f;
+    float4 acc[8];
+#pragma unroll
+    for (int v = 0; v < 8; ++v) acc[v] = make_float4(0, 0, 0, 0);
+    for (int c = 0; c < nc; ++c) {
+      const float w = expf(pmax[c * m + l] - M);
+      Lsum = fmaf(w, psum[c * m + l], Lsum);
+      const float4* src = reinterpret_cast<const float4*>(pacc + ((size_t)c * m + l) * D + d0);
+#pragma unroll
+      for (int v = 0; v < 8; ++v)
+        if (v < nv) {
+          const float4 x = src[v];
+          acc[v].x = fmaf(w, x.x, acc[v].x); acc[v].y = fmaf(w, x.y, acc[v].y);
+          acc[v].z = fmaf(w, x.z, acc[v].z); acc[v].w = fmaf(w, x.w, acc[v].w);
+        }
+    }
+    const float inv = 1.f / Lsum;
+    float4* dst_s = reinterpret_cast<float4*>(sm + l * D + d0);
+    float4* dst_g = reinterpret_cast<float4*>(p.bmat + (bh * m + l) * D + d0);
+#pragma unroll
+    for (int v = 0; v < 8; ++v)
+      if (v < nv) {
+        const float4 x = make_float4(acc[v].x * inv, acc[v].y * inv, acc[v].z * inv, acc[v].w * inv);
+        dst_s[v] = x;
+        dst_g[v] = x;
+      }
+    if (q == 0) p.lse3[bh * m + l] = M + logf(Lsum);
+  }
+  __syncthreads();
+  // step2 = K2inv Bmat
+  const float* k2inv = p.k2inv + bh * m * m;
+  float amax = 0.f;
+  float4 keep[2][8];   // step2 values of this thread's (up to two) rows, for the packed copy
+#pragma unroll
+  for (int pass = 0; pass < 2; ++pass) {
+    const int l = (t >> 2) + pass * (kThreads / 4);
+    float4 acc[8];
+#pragma unroll
+    for (int v = 0; v < 8; ++v) acc[v] = make_float4(0, 0, 0, 0);
+    if (l < m) {
+      for (int k = 0; k < m; ++k) {
+        const float a = k2inv[l * m + k];
+        const float4* b = reinterpret_cast<const float4*>(sm + k * D + d0);
+#pragma unroll
+        for (int v = 0; v < 8; ++v)
+          if (v < nv) {
+            const float4 x = b[v];
+            acc[v].x = fmaf(a, x.x, acc[v].x); acc[v].y = fmaf(a, x.y, acc[v].y);
+            acc[v].z = fmaf(a, x.z, acc[v].z); acc[v].w = fmaf(a, x.w, acc[v].w);
+          }
+      }
+      float4* dst_g = reinterpret_cast<float4*>(p.step2 + (bh * m + l) * D + d0);
+#pragma unroll
+      for (int v = 0; v < 8; ++v)
+        if (v < nv) {
+          dst_g[v] = acc[v];
+          amax = fmaxf(amax, fmaxf(fmaxf(fabsf(acc[v].x), fabsf(acc[v].y)), fmaxf(fabsf(acc[v].z), fabsf(acc[v].w))));
+        }
+    }
+#pragma unroll
+    for (int v = 0; v < 8; ++v) keep[pass][v] = acc[v];
+  }
+  if (p.dtype == 0) return;
+  const float sc = pow2_scale(cta_max(amax, red));
+  if (t == 0) p.st_scale[bh] = sc;
+  const float inv_sc = 1.f / sc;
+  const int MP = p.MP;
+  void* st16T = reinterpret_cast<char*>(p.st16T) + (size_t)bh * D * MP * 2;
+  void* kt16 = reinterpret_cast<char*>(p.kt16) + (size_t)bh * MP * D * 2;
+#pragma unroll
+  for (int pass = 0; pass < 2; ++pass) {
+    const int l = (t >> 2) + pass * (kThreads / 4);
+    if (l < m) {
+#pragma unroll
+      for (int v = 0; v < 8; ++v)
+        if (v < nv) {
+          const int d = d0 + 4 * v;
+          store16(st16T, p.dtype, (size_t)(d + 0) * MP + l, keep[pass][v].x * inv_sc);
+          store16(st16T, p.dtype, (size_t)(d + 1) * MP + l, keep[pass][v].y * inv_sc);
+          store16(st16T, p.dtype, (size_t)(d + 2) * MP + l, keep[pass][v].z * inv_sc);
+          store16(st16T, p.dtype, (size_t)(d + 3) * MP + l, keep[pass][v].w * inv_sc);
+        }
+    }
+  }
+  for (int idx = t; idx < D * (MP - m); idx += kThreads) {
+    const int d = idx / (MP - m), l = m + idx - d * (MP - m);
+    store16(st16T, p.dtype, (size_t)d * MP + l, 0.f);
+  }
+  pack_pair(p.k_landmarks + bh * (int64_t)m * D, kt16, nullptr, p.dtype, m, D, MP, p.kt_mul);
+}
+
+// ------------------------------------------------------------------------------------------
+struct BwdMid1Params {
+  const float* partA;         // [BH][nchunk][2][m][D]
+  int nchunk;
+  const float* k2inv; const float* bmat; const float* q_landmarks;
+  float* dkt_a;               // [BH][m][D]
+  float* dO3;                 // [BH][m][D]
+  float* D3;                  // [BH][m]
+  float* G;                   // [BH][m][m]  dK2inv
+  int m, D;
+  int dtype, MP;
+  void* qt16;                 // [BH][MP][D] = qt_mul * Qt
+  void* qtT16;                // [BH][D][MP] = qtT_mul * Qt^T
+  void* do3n;                 // [BH][MP][D] = dO3 / do3_scale
+  void* do3T;                 // [BH][D][MP]
+  float* do3_scale;           // [BH]
+  float qt_mul, qtT_mul;
+};
+
+__host__ __device__ inline size_t bwd_mid1_smem(int m, int D) {
+  return sizeof(float) * ((size_t)m * D + (size_t)m * (D + 4) + (size_t)m * D);
+}
+
+__global__ void __launch_bounds__(kThreads) bwd_mid1_kernel(BwdMid1Params p) {
+  extern __shared__ float sm[];
+  __shared__ float red[8];
+  const int64_t bh = blockIdx.x;
+  const int m = p.m, D = p.D, t = threadIdx.x, nc = p.nchunk, md = m * D, ldb = D + 4;
+  const int q = t & 3, dpt = D >> 2, nv = dpt >> 2, d0 = q * dpt;
+  float* ds = sm;                    // dstep2 [m][D]
+  float* bm = ds + md;               // Bmat   [m][D+4]
+  float* do3 = bm + m * ldb;         // dO3    [m][D]
+  const float* partA = p.partA + bh * (int64_t)nc * 2 * md;
+  const float* bmat = p.bmat + bh * (int64_t)md;
+  for (int l = t >> 2; l < m; l += kThreads / 4) {
+    float4 a0[8], a1[8];
+#pragma unroll
+    for (int v = 0; v < 8; ++v) { a0[v] = make_float4(0, 0, 0, 0); a1[v] = make_float4(0, 0, 0, 0); }
+    for (int c = 0; c < nc; ++c) {
+      const float4* s0 = reinterpret_cast<const float4*>(partA + (size_t)c * 2 * md + l * D + d0);
+      const float4* s1 = reinterpret_cast<const float4*>(partA + (size_t)c * 2 * md + md + l * D + d0);
+#pragma unroll
+      for (int v = 0; v < 8; ++v)
+        if (v < nv) {
+          const float4 x = s0[v], y = s1[v];
+          a0[v].x += x.x; a0[v].y += x.y; a0[v].z += x.z; a0[v].w += x.w;
+          a1[v].x += y.x; a1[v].y += y.y; a1[v].z += y.z; a1[v].w += y.w;
+        }
+    }
+    float4* dd = reinterpret_cast<float4*>(ds + l * D + d0);
+    float4* dk = reinterpret_cast<float4*>(p.dkt_a + bh * md + l * D + d0);
+    float4* db = reinterpret_cast<float4*>(bm + l * ldb + d0);
+    const float4* sb = reinterpret_cast<const float4*>(bmat + l * D + d0);
+#pragma unroll
+    for (int v = 0; v < 8; ++v)
+      if (v < nv) { dd[v] = a0[v]; dk[v] = a1[v]; db[v] = sb[v]; }
+  }
+  __syncthreads();
+  const float* k2inv = p.k2inv + bh * m * m;
+  float amax = 0.f;
+  for (int l = t >> 2; l < m; l += kThreads / 4) {
+    // dO3[l][:] = sum_k K2inv[k][l] dstep2[k][:]
+    float4 acc[8];
+#pragma unroll
+    for (int v = 0; v < 8; ++v) acc[v] = make_float4(0, 0, 0, 0);
+    for (int k = 0; k < m; ++k) {
+      const float a = k2inv[k * m + l];
+      const float4* b = reinterpret_cast<const float4*>(ds + k * D + d0);
+#pragma unroll
+      for (int v = 0; v < 8; ++v)
+        if (v < nv) {
+          const float4 x = b[v];
+          acc[v].x = fmaf(a, x.x, acc[v].x); acc[v].y = fmaf(a, x.y, acc[v].y);
+          acc[v].z = fmaf(a, x.z, acc[v].z); acc[v].w = fmaf(a, x.w, acc[v].w);
+        }
+    }
+    float d3 = 0.f;
+    float4* dg = reinterpret_cast<float4*>(p.dO3 + bh * md + l * D + d0);
+    float4* dsm = reinterpret_cast<float4*>(do3 + l * D + d0);
+    const float4* bb = reinterpret_cast<const float4*>(bm + l * ldb + d0);
+#pragma unroll
+    for (int v = 0; v < 8; ++v)
+      if (v < nv) {
+        dg[v] = acc[v];
+        dsm[v] = acc[v];
+        const float4 x = bb[v];
+        d3 += acc[v].x * x.x + acc[v].y * x.y + acc[v].z * x.z + acc[v].w * x.w;
+        amax = fmaxf(amax, fmaxf(fmaxf(fabsf(acc[v].x), fabsf(acc[v].y)), fmaxf(fabsf(acc[v].z), fabsf(acc[v].w))));
+      }
+    d3 += __shfl_xor_sync(0xffffffffu, d3, 1);
+    d3 += __shfl_xor_sync(0xffffffffu, d3, 2);
+    if (q == 0) p.D3[bh * m + l] = d3;
+    // G[l][j] = sum_d dstep2[l][d] Bmat[j][d],  j = q, q+4, ...
+    float* Gr = p.G + bh * m * m + l * m;
+    for (int j = q; j < m; j += 4) {
+      const float4* a = reinterpret_cast<const float4*>(ds + l * D);
+      const float4* b = reinterpret_cast<const float4*>(bm + j * ldb);
+      float s = 0.f;
+      for (int v = 0; v < (D >> 2); ++v) {
+        const float4 x = a[v], y = b[v];
+        s += x.x * y.x + x.y * y.y + x.z * y.z + x.w * y.w;
+      }
+      Gr[j] = s;
+    }
+  }
+  if (p.dtype == 0) return;
+  const float sc = pow2_scale(cta_max(amax, red));   // barrier inside: do3 is complete
+  if (t == 0) p.do3_scale[bh] = sc;
+  const float inv_sc = 1.f / sc;
+  const int MP = p.MP;
+  const size_t ob = (size_t)bh * MP * D * 2;
+  for (int idx = t; idx < MP * D; idx += kThreads)
+    store16(reinterpret_cast<char*>(p.do3n) + ob, p.dtype, idx, (idx / D) < m ? do3[idx] * inv_sc : 0.f);
+  for (int idx = t; idx < D * MP; idx += kThreads) {
+    int d = idx / MP, l = idx - d * MP;
+    store16(reinterpret_cast<char*>(p.do3T) + ob, p.dtype, idx, l < m ? do3[l * D + d] * inv_sc : 0.f);
+  }
+  const float* qt = p.q_landmarks + bh * (int64_t)md;
+  pack_pair(qt, reinterpret_cast<char*>(p.qt16) + ob, nullptr, p.dtype, m, D, MP, p.qt_mul);
+  pack_pair(qt, nullptr, reinterpret_cast<char*>(p.qtT16) + ob, p.dtype, m, D, MP, p.qtT_mul);
+}
+
+// ------------------------------------------------------------------------------------------
+struct PackBwdAcParams {
+  const float* k_landmarks; const float* step2;
+  void* kt16;      // [BH][MP][D] = kt_mul * Kt
+  void* ktT16;     // [BH][D][MP] = ktT_mul * Kt^T
+  void* st16;      // [BH][MP][D] = step2 / st_scale
+  float* st_scale;
+  int m, D, MP, dtype;
+  float kt_mul, ktT_mul;
+};
+
+__global__ void __launch_bounds__(kThreads) pack_bwd_ac_kernel(PackBwdAcParams p) {
+  __shared__ float red[8];
+  const int64_t bh = blockIdx.x;
+  const int md = p.m * p.D;
+  const size_t ob = (size_t)bh * p.MP * p.D * 2;
+  const float* kt = p.k_landmarks + bh * (int64_t)md;
+  const float* st = p.step2 + bh * (int64_t)md;
+  float amax = 0.f;
+  for (int idx = threadIdx.x; idx < md; idx += kThreads) amax = fmaxf(amax, fabsf(st[idx]));
+  const float sc = pow2_scale(cta_max(amax, red));
+  if (threadIdx.x == 0) p.st_scale[bh] = sc;
+  pack_pair(st, reinterpret_cast<char*>(p.st16) + ob, nullptr, p.dtype, p.m, p.D, p.MP, 1.f / sc);
+  pack_pair(kt, reinterpret_cast<char*>(p.kt16) + ob, nullptr, p.dtype, p.m, p.D, p.MP, p.kt_mul);
+  pack_pair(kt, nullptr, reinterpret_cast<char*>(p.ktT16) + ob, p.dtype, p.m, p.D, p.MP, p.ktT_mul);
+}
+
+// dqt_tot = dqt_ns + sum over chunks of the column-pass partials (CUDA-core path only; the
+// tensor-core dQ pass folds this reduction into its prologue)
+__global__ void __launch_bounds__(kThreads)
+dqt_reduce2_kernel(const float* partB, int nchunk, const float* dqt_ns, float* dqt_tot, int md) {
+  const int64_t bh = blockIdx.y;
+  const int idx4 = (blockIdx.x * kThreads + threadIdx.x) * 4;
+  if (idx4 >= md) return;
+  float4 s = *reinterpret_cast<const float4*>(dqt_ns + bh * md + idx4);
+  const float* src = partB + bh * (size_t)nchunk * md + idx4;
+  for (int c = 0; c < nchunk; ++c) {
+    const float4 x = *reinterpret_cast<const float4*>(src + (size_t)c * md);
+    s.x += x.x; s.y += x.y; s.z += x.z; s.w += x.w;
+  }
+  *reinterpret_cast<float4*>(dqt_tot + bh * md + idx4) = s;
+}
+
+}  // namespace fnb
