@@ -214,11 +214,18 @@ static Plan plan_of(const fnb_shape& s) {
 }
 
 // ------------------------------------------------------------------------------------------
+// Forward: pooling pass -> landmarks -> [pseudoinverse | softmax-3 column pass] -> combine ->
+// output row pass.
 template <class T>
 static int forward_impl(const fnb_fwd_args& a, const Plan& p, const FwdWs& w, int max_smem,
                         cudaStream_t st) {
   Launcher L(st, a.device);
   const float scale = powf((float)p.D, -0.25f);
+  constexpr bool k16 = !std::is_same<T, float>::value;
+  const tc::TcSched sch = tc::make_sched(p.BH, p.N, 296);
+  const bool use_tc = k16 && tc::tc_supported(a.shape.dtype, p.D, p.m, a.shape.flags) && sch.nchunk <= p.nchunk;
+  const int MP = p.m <= 64 ? 64 : 128;
+  const bool smem_ns = p.m <= ns::kN;
 
   L.begin();
   {
@@ -236,11 +243,14 @@ static int forward_impl(const fnb_fwd_args& a, const Plan& p, const FwdWs& w, in
     mp.iterates = a.ns_iterates; mp.k2inv = a.k2_inv; mp.scratch = w.pinv;
     mp.BH = p.BH; mp.N = p.N; mp.m = p.m; mp.D = p.D; mp.J = p.J;
     mp.kappa = a.shape.kappa_star; mp.scale = scale;
-    mp.landmarks_only = p.m <= ns::kN ? 1 : 0;
+    mp.landmarks_only = smem_ns ? 1 : 0;
+    mp.qt16 = use_tc ? w.qt16 : nullptr; mp.dtype = a.shape.dtype; mp.MP = MP;
+    mp.qt16_mul = scale * tc::kLog2e;
     mid_fwd_kernel<<<(unsigned)p.BH, kThreads, 0, st>>>(mp);
   }
   if (L.end("mid_fwd")) return L.status;
-  if (p.m <= ns::kN) {
+
+  if (smem_ns) {
     L.begin();
     ns::NsFwdParams np;
     np.qt = a.q_landmarks; np.kt = a.k_landmarks; np.k2 = a.k2; np.lse2 = a.lse2;
@@ -259,31 +269,22 @@ static int forward_impl(const fnb_fwd_args& a, const Plan& p, const FwdWs& w, in
   sp.N = p.N; sp.rows_per_chunk = p.rows_per_chunk; sp.D = p.D; sp.m = p.m; sp.mpad = p.mpad;
   sp.nchunk = p.nchunk; sp.scale = scale;
   const unsigned sgrid = (unsigned)(p.BH * p.nchunk);
-
-  bool use_tc = false;
-  tc::TcSched sch = tc::make_sched(p.BH, p.N, 296);
   int nchunk_b = p.nchunk;
-  if constexpr (!std::is_same<T, float>::value) {
-    use_tc = tc::tc_supported(a.shape.dtype, p.D, p.m, a.shape.flags) && sch.nchunk <= p.nchunk;
+
+  if constexpr (k16) {
     if (use_tc) {
-      constexpr int D = 64, MP = 64;
-      L.begin();
-      tc::pack_kernel<T><<<(unsigned)p.BH, kThreads, 0, st>>>(a.q_landmarks, (T*)w.qt16, (T*)nullptr, p.m, D, MP,
-                                                             scale * tc::kLog2e, 0, nullptr);
-      if (L.end("pack_fwd_b")) return L.status;
+      constexpr int D = 64, MPc = 64;
       CUtensorMap tm_k, tm_v, tm_qt;
       if (!tc::make_map_3d(&tm_k, a.k, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
           !tc::make_map_3d(&tm_v, a.v, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
-          !tc::make_map_2d(&tm_qt, w.qt16, a.shape.dtype, p.BH * MP, D, MP))
+          !tc::make_map_2d(&tm_qt, w.qt16, a.shape.dtype, p.BH * MPc, D, MPc))
         return fail(FNB_ERR_CUDA, "cuTensorMapEncodeTiled failed for the forward column pass");
       L.begin();
-      {
-        auto kern = tc::tc_fwd_b_kernel<T, D, MP>;
-        size_t smem = tc::FwdBSmem<D, MP>::kBytes;
-        if (int rc = set_smem(kern, smem, max_smem, "tc_fwd_b")) return rc;
-        kern<<<(unsigned)(p.BH * sch.nchunk), tc::kTcThreads, smem, st>>>(tm_k, tm_v, tm_qt, w.part_acc, w.part_max,
-                                                                        w.part_sum, sch, p.m, a.device_status);
-      }
+      auto kern = tc::tc_fwd_b_kernel<T, D, MPc>;
+      size_t smem = tc::FwdBSmem<D, MPc>::kBytes;
+      if (int rc = set_smem(kern, smem, max_smem, "tc_fwd_b")) return rc;
+      kern<<<(unsigned)(p.BH * sch.nchunk), tc::kTcThreads, smem, st>>>(tm_k, tm_v, tm_qt, w.part_acc, w.part_max,
+                                                                      w.part_sum, sch, p.m, a.device_status);
       if (L.end("tc_fwd_b")) return L.status;
       nchunk_b = sch.nchunk;
     }
@@ -298,37 +299,33 @@ static int forward_impl(const fnb_fwd_args& a, const Plan& p, const FwdWs& w, in
 
   L.begin();
   {
-    CombineParams cp;
-    cp.part_acc = w.part_acc; cp.part_max = w.part_max; cp.part_sum = w.part_sum;
-    cp.nchunk = nchunk_b; cp.k2inv = a.k2_inv; cp.bmat = a.bmat; cp.lse3 = a.lse3;
+    Combine2Params cp;
+    cp.part_acc = w.part_acc; cp.part_max = w.part_max; cp.part_sum = w.part_sum; cp.nchunk = nchunk_b;
+    cp.k2inv = a.k2_inv; cp.k_landmarks = a.k_landmarks; cp.bmat = a.bmat; cp.lse3 = a.lse3;
     cp.step2 = a.step2; cp.m = p.m; cp.D = p.D;
-    combine_kernel<<<(unsigned)p.BH, kThreads, 0, st>>>(cp);
+    cp.dtype = use_tc ? a.shape.dtype : 0; cp.MP = MP; cp.kt16 = w.kt16; cp.st16T = w.st16;
+    cp.st_scale = w.st_scale; cp.kt_mul = scale * tc::kLog2e;
+    size_t smem = sizeof(float) * (size_t)p.m * p.D;
+    if (int rc = set_smem(combine2_kernel, smem, max_smem, "combine")) return rc;
+    combine2_kernel<<<(unsigned)p.BH, kThreads, smem, st>>>(cp);
   }
   if (L.end("combine")) return L.status;
 
-  if constexpr (!std::is_same<T, float>::value) {
+  if constexpr (k16) {
     if (use_tc) {
-      constexpr int D = 64, MP = 64;
-      L.begin();
-      tc::pack_kernel<T><<<(unsigned)p.BH, kThreads, 0, st>>>(a.k_landmarks, (T*)w.kt16, (T*)nullptr, p.m, D, MP,
-                                                             scale * tc::kLog2e, 0, nullptr);
-      tc::pack_kernel<T><<<(unsigned)p.BH, kThreads, 0, st>>>(a.step2, (T*)nullptr, (T*)w.st16, p.m, D, MP, 1.f, 1,
-                                                             w.st_scale);
-      if (L.end("pack_fwd_c")) return L.status;
+      constexpr int D = 64, MPc = 64;
       CUtensorMap tm_q, tm_o, tm_kt, tm_st;
       if (!tc::make_map_3d(&tm_q, a.q, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
           !tc::make_map_3d(&tm_o, a.out, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
-          !tc::make_map_2d(&tm_kt, w.kt16, a.shape.dtype, p.BH * MP, D, MP) ||
-          !tc::make_map_2d(&tm_st, w.st16, a.shape.dtype, p.BH * D, MP, D))
+          !tc::make_map_2d(&tm_kt, w.kt16, a.shape.dtype, p.BH * MPc, D, MPc) ||
+          !tc::make_map_2d(&tm_st, w.st16, a.shape.dtype, p.BH * D, MPc, D))
         return fail(FNB_ERR_CUDA, "cuTensorMapEncodeTiled failed for the forward output pass");
       L.begin();
-      {
-        auto kern = tc::tc_fwd_c_kernel<T, D, MP>;
-        size_t smem = tc::FwdCSmem<D, MP>::kBytes;
-        if (int rc = set_smem(kern, smem, max_smem, "tc_fwd_c")) return rc;
-        kern<<<(unsigned)(p.BH * sch.nchunk), tc::kTcThreads, smem, st>>>(tm_q, tm_o, tm_kt, tm_st, a.lse1,
-                                                                        w.st_scale, sch, p.m, a.device_status);
-      }
+      auto kern = tc::tc_fwd_c_kernel<T, D, MPc>;
+      size_t smem = tc::FwdCSmem<D, MPc>::kBytes;
+      if (int rc = set_smem(kern, smem, max_smem, "tc_fwd_c")) return rc;
+      kern<<<(unsigned)(p.BH * sch.nchunk), tc::kTcThreads, smem, st>>>(tm_q, tm_o, tm_kt, tm_st, a.lse1,
+                                                                      w.st_scale, sch, p.m, a.device_status);
       if (L.end("tc_fwd_c")) return L.status;
       return 0;
     }
@@ -343,11 +340,20 @@ static int forward_impl(const fnb_fwd_args& a, const Plan& p, const FwdWs& w, in
   return 0;
 }
 
+// ------------------------------------------------------------------------------------------
+// Backward: softmax-1 row pass (partials) -> landmark-sized middle (dO3, dK2inv, pseudoinverse
+// backward) -> softmax-3 column pass (dK, dV, dQt partials) -> dQ row pass.
 template <class T>
 static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, int max_smem,
                          cudaStream_t st) {
   Launcher L(st, a.device);
   const float scale = powf((float)p.D, -0.25f);
+  constexpr bool k16 = !std::is_same<T, float>::value;
+  const tc::TcSched sch = tc::make_sched(p.BH, p.N, 296);
+  const bool use_tc = k16 && tc::tc_supported(a.shape.dtype, p.D, p.m, a.shape.flags) && sch.nchunk <= p.nchunk;
+  const int MP = p.m <= 64 ? 64 : 128;
+  const bool smem_ns = p.m <= ns::kN;
+
   StreamParams sp;
   memset(&sp, 0, sizeof(sp));
   sp.q = a.q; sp.k = a.k; sp.v = a.v; sp.dO = a.d_out;
@@ -360,149 +366,147 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
   sp.N = p.N; sp.rows_per_chunk = p.rows_per_chunk; sp.D = p.D; sp.m = p.m; sp.mpad = p.mpad;
   sp.nchunk = p.nchunk; sp.scale = scale;
   const unsigned sgrid = (unsigned)(p.BH * p.nchunk);
-  const size_t smem = bwd_ac_smem(p.mpad, p.D);
+  const unsigned tgrid = (unsigned)(p.BH * sch.nchunk);
+  const size_t gsmem = bwd_ac_smem(p.mpad, p.D);
+  const int nchunk_used = use_tc ? sch.nchunk : p.nchunk;
 
-  bool use_tc = false;
-  tc::TcSched sch = tc::make_sched(p.BH, p.N, 296);
-  int nchunk_a = p.nchunk;
-  if constexpr (!std::is_same<T, float>::value) {
-    use_tc = tc::tc_supported(a.shape.dtype, p.D, p.m, a.shape.flags) && sch.nchunk <= p.nchunk;
-  }
+  void* kt16 = w.op16[0]; void* st16 = w.op16[1]; void* ktT16 = w.op16[2]; void* qt16 = w.op16[3];
+  void* qtT16 = w.op16[4]; void* do3n = w.op16[5]; void* do3T = w.op16[6];
   CUtensorMap tm_q, tm_g, tm_kt, tm_st, tm_ktT, tm_dq;
-  if constexpr (!std::is_same<T, float>::value) {
+
+  // ---- pass A ---------------------------------------------------------------------------------
+  if constexpr (k16) {
     if (use_tc) {
-      constexpr int D = 64, MP = 64;
-      T* kt16 = (T*)w.op16[0];
-      T* st16 = (T*)w.op16[1];
-      T* ktT16 = (T*)w.op16[2];
+      constexpr int D = 64, MPc = 64;
       L.begin();
-      tc::pack_kernel<T><<<(unsigned)p.BH, kThreads, 0, st>>>(a.k_landmarks, kt16, (T*)nullptr, p.m, D, MP,
-                                                             scale * tc::kLog2e, 0, nullptr);
-      tc::pack_kernel<T><<<(unsigned)p.BH, kThreads, 0, st>>>(a.k_landmarks, (T*)nullptr, ktT16, p.m, D, MP, scale,
-                                                             0, nullptr);
-      tc::pack_kernel<T><<<(unsigned)p.BH, kThreads, 0, st>>>(a.step2, st16, (T*)nullptr, p.m, D, MP, 1.f, 1,
-                                                             w.st_scale);
+      {
+        PackBwdAcParams pp;
+        pp.k_landmarks = a.k_landmarks; pp.step2 = a.step2; pp.kt16 = kt16; pp.ktT16 = ktT16; pp.st16 = st16;
+        pp.st_scale = w.st_scale; pp.m = p.m; pp.D = p.D; pp.MP = MP; pp.dtype = a.shape.dtype;
+        pp.kt_mul = scale * tc::kLog2e; pp.ktT_mul = scale;
+        pack_bwd_ac_kernel<<<(unsigned)p.BH, kThreads, 0, st>>>(pp);
+      }
       if (L.end("pack_bwd_ac")) return L.status;
       if (!tc::make_map_3d(&tm_q, a.q, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
           !tc::make_map_3d(&tm_g, a.d_out, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
           !tc::make_map_3d(&tm_dq, a.dq, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
-          !tc::make_map_2d(&tm_kt, kt16, a.shape.dtype, p.BH * MP, D, MP) ||
-          !tc::make_map_2d(&tm_st, st16, a.shape.dtype, p.BH * MP, D, MP) ||
-          !tc::make_map_2d(&tm_ktT, ktT16, a.shape.dtype, p.BH * D, MP, D))
+          !tc::make_map_2d(&tm_kt, kt16, a.shape.dtype, p.BH * MPc, D, MPc) ||
+          !tc::make_map_2d(&tm_st, st16, a.shape.dtype, p.BH * MPc, D, MPc) ||
+          !tc::make_map_2d(&tm_ktT, ktT16, a.shape.dtype, p.BH * D, MPc, D))
         return fail(FNB_ERR_CUDA, "cuTensorMapEncodeTiled failed for the backward row passes");
       L.begin();
-      {
-        auto kern = tc::tc_bwd_ac_kernel<T, D, MP, tc::kModeA>;
-        size_t sm = tc::BwdAcSmem<D, MP, tc::kModeA>::kBytes;
-        if (int rc = set_smem(kern, sm, max_smem, "tc_bwd_a")) return rc;
-        kern<<<(unsigned)(p.BH * sch.nchunk), tc::kTcThreads, sm, st>>>(
-            tm_q, tm_g, tm_kt, tm_st, tm_ktT, tm_dq, a.lse1, w.st_scale, nullptr, w.partA, sch, p.m, scale,
-            a.device_status);
-      }
+      auto kern = tc::tc_bwd_ac_kernel<T, D, MPc, tc::kModeA>;
+      size_t sm = tc::BwdAcSmem<D, MPc, tc::kModeA>::kBytes;
+      if (int rc = set_smem(kern, sm, max_smem, "tc_bwd_a")) return rc;
+      kern<<<tgrid, tc::kTcThreads, sm, st>>>(tm_q, tm_g, tm_kt, tm_st, tm_ktT, tm_dq, a.lse1, w.st_scale, nullptr,
+                                             nullptr, 0, w.partA, sch, p.m, scale, a.device_status);
       if (L.end("tc_bwd_a")) return L.status;
-      nchunk_a = sch.nchunk;
     }
   }
   if (!use_tc) {
     L.begin();
-    if (int rc = set_smem(gen_bwd_a_kernel<T>, smem, max_smem, "gen_bwd_a")) return rc;
-    gen_bwd_a_kernel<T><<<sgrid, kThreads, smem, st>>>(sp);
+    if (int rc = set_smem(gen_bwd_a_kernel<T>, gsmem, max_smem, "gen_bwd_a")) return rc;
+    gen_bwd_a_kernel<T><<<sgrid, kThreads, gsmem, st>>>(sp);
     if (L.end("gen_bwd_a")) return L.status;
   }
 
-  L.begin();
-  {
-    MidBwdParams mp;
-    mp.partA = w.partA; mp.nchunk = nchunk_a;
-    mp.qt = a.q_landmarks; mp.kt = a.k_landmarks; mp.k2 = a.k2; mp.iterates = a.ns_iterates;
-    mp.k2inv = a.k2_inv; mp.bmat = a.bmat;
-    mp.dstep2 = w.dstep2; mp.dkt_a = w.dkt_a; mp.dO3 = w.dO3; mp.D3 = w.D3;
-    mp.dqt_ns = w.dqt_ns; mp.dkt_tot = w.dkt_tot; mp.G = w.G; mp.dK2 = w.dK2; mp.scratch = w.pinv;
-    mp.m = p.m; mp.D = p.D; mp.J = p.J; mp.kappa = a.shape.kappa_star;
-    mp.first_half_only = p.m <= ns::kN ? 1 : 0;
-    mid_bwd_kernel<<<(unsigned)p.BH, kThreads, 0, st>>>(mp);
-  }
-  if (L.end("mid_bwd")) return L.status;
-  if (p.m <= ns::kN) {
+  // ---- landmark-sized middle ------------------------------------------------------------------
+  if (smem_ns) {
     L.begin();
-    ns::NsBwdParams np;
-    np.k2 = a.k2; np.iterates = a.ns_iterates; np.G = w.G; np.qt = a.q_landmarks; np.kt = a.k_landmarks;
-    np.dkt_a = w.dkt_a; np.dqt_ns = w.dqt_ns; np.dkt_tot = w.dkt_tot; np.spill = w.dK2;
-    np.m = p.m; np.D = p.D; np.J = p.J; np.kappa = a.shape.kappa_star;
-    if (int rc = set_smem(ns::ns_bwd_kernel, ns::kBwdSmem, max_smem, "ns_bwd")) return rc;
-    ns::ns_bwd_kernel<<<(unsigned)p.BH, kThreads, ns::kBwdSmem, st>>>(np);
+    {
+      BwdMid1Params mp;
+      mp.partA = w.partA; mp.nchunk = nchunk_used; mp.k2inv = a.k2_inv; mp.bmat = a.bmat;
+      mp.q_landmarks = a.q_landmarks; mp.dkt_a = w.dkt_a; mp.dO3 = w.dO3; mp.D3 = w.D3; mp.G = w.G;
+      mp.m = p.m; mp.D = p.D; mp.dtype = use_tc ? a.shape.dtype : 0; mp.MP = MP;
+      mp.qt16 = qt16; mp.qtT16 = qtT16; mp.do3n = do3n; mp.do3T = do3T; mp.do3_scale = w.do3_scale;
+      mp.qt_mul = scale * tc::kLog2e; mp.qtT_mul = scale;
+      size_t sm = bwd_mid1_smem(p.m, p.D);
+      if (int rc = set_smem(bwd_mid1_kernel, sm, max_smem, "bwd_mid1")) return rc;
+      bwd_mid1_kernel<<<(unsigned)p.BH, kThreads, sm, st>>>(mp);
+    }
+    if (L.end("bwd_mid1")) return L.status;
+    L.begin();
+    {
+      ns::NsBwdParams np;
+      np.k2 = a.k2; np.iterates = a.ns_iterates; np.G = w.G; np.qt = a.q_landmarks; np.kt = a.k_landmarks;
+      np.dkt_a = w.dkt_a; np.dqt_ns = w.dqt_ns; np.dkt_tot = w.dkt_tot; np.spill = w.dK2;
+      np.m = p.m; np.D = p.D; np.J = p.J; np.kappa = a.shape.kappa_star;
+      if (int rc = set_smem(ns::ns_bwd_kernel, ns::kBwdSmem, max_smem, "ns_bwd")) return rc;
+      ns::ns_bwd_kernel<<<(unsigned)p.BH, kThreads, ns::kBwdSmem, st>>>(np);
+    }
     if (L.end("ns_bwd")) return L.status;
+  } else {
+    L.begin();
+    {
+      MidBwdParams mp;
+      mp.partA = w.partA; mp.nchunk = nchunk_used;
+      mp.qt = a.q_landmarks; mp.kt = a.k_landmarks; mp.k2 = a.k2; mp.iterates = a.ns_iterates;
+      mp.k2inv = a.k2_inv; mp.bmat = a.bmat;
+      mp.dstep2 = w.dstep2; mp.dkt_a = w.dkt_a; mp.dO3 = w.dO3; mp.D3 = w.D3;
+      mp.dqt_ns = w.dqt_ns; mp.dkt_tot = w.dkt_tot; mp.G = w.G; mp.dK2 = w.dK2; mp.scratch = w.pinv;
+      mp.m = p.m; mp.D = p.D; mp.J = p.J; mp.kappa = a.shape.kappa_star; mp.first_half_only = 0;
+      mid_bwd_kernel<<<(unsigned)p.BH, kThreads, 0, st>>>(mp);
+    }
+    if (L.end("mid_bwd")) return L.status;
   }
 
-  int nchunk_b = p.nchunk;
-  if constexpr (!std::is_same<T, float>::value) {
+  // ---- pass B ---------------------------------------------------------------------------------
+  if constexpr (k16) {
     if (use_tc) {
-      constexpr int D = 64, MP = 64;
-      T* qt16 = (T*)w.op16[3];
-      T* qtT16 = (T*)w.op16[4];
-      T* do3n = (T*)w.op16[5];
-      T* do3T = (T*)w.op16[6];
-      L.begin();
-      tc::pack_kernel<T><<<(unsigned)p.BH, kThreads, 0, st>>>(a.q_landmarks, qt16, (T*)nullptr, p.m, D, MP,
-                                                             scale * tc::kLog2e, 0, nullptr);
-      tc::pack_kernel<T><<<(unsigned)p.BH, kThreads, 0, st>>>(a.q_landmarks, (T*)nullptr, qtT16, p.m, D, MP, scale,
-                                                             0, nullptr);
-      tc::pack_kernel<T><<<(unsigned)p.BH, kThreads, 0, st>>>(w.dO3, do3n, do3T, p.m, D, MP, 1.f, 1, w.do3_scale);
-      if (L.end("pack_bwd_b")) return L.status;
+      constexpr int D = 64, MPc = 64;
       CUtensorMap tm_k, tm_v, tm_qt, tm_do3, tm_do3T, tm_qtT, tm_dk, tm_dv;
       if (!tc::make_map_3d(&tm_k, a.k, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
           !tc::make_map_3d(&tm_v, a.v, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
           !tc::make_map_3d(&tm_dk, a.dk, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
           !tc::make_map_3d(&tm_dv, a.dv, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
-          !tc::make_map_2d(&tm_qt, qt16, a.shape.dtype, p.BH * MP, D, MP) ||
-          !tc::make_map_2d(&tm_do3, do3n, a.shape.dtype, p.BH * MP, D, MP) ||
-          !tc::make_map_2d(&tm_do3T, do3T, a.shape.dtype, p.BH * D, MP, D) ||
-          !tc::make_map_2d(&tm_qtT, qtT16, a.shape.dtype, p.BH * D, MP, D))
+          !tc::make_map_2d(&tm_qt, qt16, a.shape.dtype, p.BH * MPc, D, MPc) ||
+          !tc::make_map_2d(&tm_do3, do3n, a.shape.dtype, p.BH * MPc, D, MPc) ||
+          !tc::make_map_2d(&tm_do3T, do3T, a.shape.dtype, p.BH * D, MPc, D) ||
+          !tc::make_map_2d(&tm_qtT, qtT16, a.shape.dtype, p.BH * D, MPc, D))
         return fail(FNB_ERR_CUDA, "cuTensorMapEncodeTiled failed for the backward column pass");
       int kshift = 0;
       while ((int64_t(2) << kshift) <= p.N && kshift < 14) ++kshift;   // floor(log2 N), at most 14
       L.begin();
-      {
-        auto kern = tc::tc_bwd_b_kernel<T, D, MP>;
-        size_t sm = tc::BwdBSmem<D, MP>::kBytes;
-        if (int rc = set_smem(kern, sm, max_smem, "tc_bwd_b")) return rc;
-        kern<<<(unsigned)(p.BH * sch.nchunk), tc::kTcThreads, sm, st>>>(
-            tm_k, tm_v, tm_qt, tm_do3, tm_do3T, tm_qtT, tm_dk, tm_dv, a.lse3, w.D3, w.do3_scale, w.dkt_tot,
-            w.partB, sch, p.m, scale, kshift, a.device_status);
-      }
+      auto kern = tc::tc_bwd_b_kernel<T, D, MPc>;
+      size_t sm = tc::BwdBSmem<D, MPc>::kBytes;
+      if (int rc = set_smem(kern, sm, max_smem, "tc_bwd_b")) return rc;
+      kern<<<tgrid, tc::kTcThreads, sm, st>>>(tm_k, tm_v, tm_qt, tm_do3, tm_do3T, tm_qtT, tm_dk, tm_dv, a.lse3, w.D3,
+                                             w.do3_scale, w.dkt_tot, w.partB, sch, p.m, scale, kshift,
+                                             a.device_status);
       if (L.end("tc_bwd_b")) return L.status;
-      nchunk_b = sch.nchunk;
     }
   }
   if (!use_tc) {
     L.begin();
-    if (int rc = set_smem(gen_bwd_b_kernel<T>, smem, max_smem, "gen_bwd_b")) return rc;
-    gen_bwd_b_kernel<T><<<sgrid, kThreads, smem, st>>>(sp);
+    if (int rc = set_smem(gen_bwd_b_kernel<T>, gsmem, max_smem, "gen_bwd_b")) return rc;
+    gen_bwd_b_kernel<T><<<sgrid, kThreads, gsmem, st>>>(sp);
     if (L.end("gen_bwd_b")) return L.status;
   }
 
-  L.begin();
-  dqt_reduce_kernel<<<(unsigned)p.BH, kThreads, 0, st>>>(w.partB, nchunk_b, w.dqt_ns, w.dqt_tot,
-                                                         p.m * p.D);
-  if (L.end("dqt_reduce")) return L.status;
-
-  if constexpr (!std::is_same<T, float>::value) {
+  // ---- pass C ---------------------------------------------------------------------------------
+  if constexpr (k16) {
     if (use_tc) {
-      constexpr int D = 64, MP = 64;
+      constexpr int D = 64, MPc = 64;
       L.begin();
-      auto kern = tc::tc_bwd_ac_kernel<T, D, MP, tc::kModeC>;
-      size_t sm = tc::BwdAcSmem<D, MP, tc::kModeC>::kBytes;
+      auto kern = tc::tc_bwd_ac_kernel<T, D, MPc, tc::kModeC>;
+      size_t sm = tc::BwdAcSmem<D, MPc, tc::kModeC>::kBytes;
       if (int rc = set_smem(kern, sm, max_smem, "tc_bwd_c")) return rc;
-      kern<<<(unsigned)(p.BH * sch.nchunk), tc::kTcThreads, sm, st>>>(
-          tm_q, tm_g, tm_kt, tm_st, tm_ktT, tm_dq, a.lse1, w.st_scale, w.dqt_tot, nullptr, sch, p.m, scale,
-          a.device_status);
+      kern<<<tgrid, tc::kTcThreads, sm, st>>>(tm_q, tm_g, tm_kt, tm_st, tm_ktT, tm_dq, a.lse1, w.st_scale, w.dqt_ns,
+                                             w.partB, sch.nchunk, nullptr, sch, p.m, scale, a.device_status);
       if (L.end("tc_bwd_c")) return L.status;
       return 0;
     }
   }
   L.begin();
-  if (int rc = set_smem(gen_bwd_c_kernel<T>, smem, max_smem, "gen_bwd_c")) return rc;
-  gen_bwd_c_kernel<T><<<sgrid, kThreads, smem, st>>>(sp);
+  {
+    const int md = p.m * p.D;
+    dim3 grid((unsigned)((md / 4 + kThreads - 1) / kThreads), (unsigned)p.BH);
+    dqt_reduce2_kernel<<<grid, kThreads, 0, st>>>(w.partB, p.nchunk, w.dqt_ns, w.dqt_tot, md);
+  }
+  if (L.end("dqt_reduce")) return L.status;
+  L.begin();
+  if (int rc = set_smem(gen_bwd_c_kernel<T>, gsmem, max_smem, "gen_bwd_c")) return rc;
+  gen_bwd_c_kernel<T><<<sgrid, kThreads, gsmem, st>>>(sp);
   if (L.end("gen_bwd_c")) return L.status;
   return 0;
 }

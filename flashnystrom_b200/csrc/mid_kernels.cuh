@@ -12,6 +12,7 @@
 //   dqt_reduce_kernel  : final landmark gradient of Q
 #pragma once
 #include "common.cuh"
+#include "small_kernels.cuh"
 
 namespace fnb {
 
@@ -286,6 +287,9 @@ struct MidFwdParams {
   int m, D, J;
   float kappa, scale;
   int landmarks_only;         // 1: stop after writing qt / kt (the shared-memory NS kernel follows)
+  void* qt16;                 // optional [BH][MP][D] 16-bit copy of qt16_mul * qt (tensor-core path)
+  int dtype, MP;
+  float qt16_mul;
 };
 
 __global__ void __launch_bounds__(kThreads) mid_fwd_kernel(MidFwdParams p) {
@@ -304,8 +308,11 @@ __global__ void __launch_bounds__(kThreads) mid_fwd_kernel(MidFwdParams p) {
     float val = s * (p.scale / (float)sg.len(l));
     (which ? kt : qt)[rem] = val;
   }
-  if (p.landmarks_only) return;
   __syncthreads();
+  if (p.qt16)
+    pack_pair(qt, reinterpret_cast<char*>(p.qt16) + (size_t)bh * p.MP * D * 2, nullptr, p.dtype, m, D, p.MP,
+              p.qt16_mul);
+  if (p.landmarks_only) return;
   float* k2 = p.k2 + bh * m * m;
   cta_gemm<false, true>(k2, m, qt, D, kt, D, m, m, D, 1.f, 0.f, 0.f, sm);
   // row softmax, one warp per row

@@ -226,7 +226,11 @@ __global__ void __launch_bounds__(kThreads) bwd_mid1_kernel(BwdMid1Params p) {
   __syncthreads();
   const float* k2inv = p.k2inv + bh * m * m;
   float amax = 0.f;
-  for (int l = t >> 2; l < m; l += kThreads / 4) {
+  for (int l0 = 0; l0 < m; l0 += kThreads / 4) {
+    // The trip count is uniform across the warp (the row loop contains warp shuffles); lanes
+    // past the last row recompute row m-1 and skip the stores.
+    const bool act = l0 + (t >> 2) < m;
+    const int l = act ? l0 + (t >> 2) : m - 1;
     // dO3[l][:] = sum_k K2inv[k][l] dstep2[k][:]
     float4 acc[8];
 #pragma unroll
@@ -249,15 +253,14 @@ __global__ void __launch_bounds__(kThreads) bwd_mid1_kernel(BwdMid1Params p) {
 #pragma unroll
     for (int v = 0; v < 8; ++v)
       if (v < nv) {
-        dg[v] = acc[v];
-        dsm[v] = acc[v];
+        if (act) { dg[v] = acc[v]; dsm[v] = acc[v]; }
         const float4 x = bb[v];
         d3 += acc[v].x * x.x + acc[v].y * x.y + acc[v].z * x.z + acc[v].w * x.w;
         amax = fmaxf(amax, fmaxf(fmaxf(fabsf(acc[v].x), fabsf(acc[v].y)), fmaxf(fabsf(acc[v].z), fabsf(acc[v].w))));
       }
     d3 += __shfl_xor_sync(0xffffffffu, d3, 1);
     d3 += __shfl_xor_sync(0xffffffffu, d3, 2);
-    if (q == 0) p.D3[bh * m + l] = d3;
+    if (q == 0 && act) p.D3[bh * m + l] = d3;
     // G[l][j] = sum_d dstep2[l][d] Bmat[j][d],  j = q, q+4, ...
     float* Gr = p.G + bh * m * m + l * m;
     for (int j = q; j < m; j += 4) {
@@ -268,7 +271,7 @@ __global__ void __launch_bounds__(kThreads) bwd_mid1_kernel(BwdMid1Params p) {
         const float4 x = a[v], y = b[v];
         s += x.x * y.x + x.y * y.y + x.z * y.z + x.w * y.w;
       }
-      Gr[j] = s;
+      if (act) Gr[j] = s;
     }
   }
   if (p.dtype == 0) return;

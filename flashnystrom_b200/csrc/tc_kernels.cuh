@@ -294,8 +294,8 @@ tc_bwd_ac_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                  const __grid_constant__ CUtensorMap tm_kt, const __grid_constant__ CUtensorMap tm_st,
                  const __grid_constant__ CUtensorMap tm_ktT, const __grid_constant__ CUtensorMap tm_dq,
                  const float* __restrict__ lse1, const float* __restrict__ st_scale,
-                 const float* __restrict__ dqt_tot, float* __restrict__ partA, TcSched sch, int m,
-                 float scale, int* status) {
+                 const float* __restrict__ dqt_ns, const float* __restrict__ partB, int nchunk_b,
+                 float* __restrict__ partA, TcSched sch, int m, float scale, int* status) {
   using L = BwdAcSmem<D, MP, MODE>;
   constexpr int KBD = D / 64, KBM = MP / 64;
   constexpr uint32_t kCols = (MODE == kModeA) ? 2 * MP + 2 * D : (2 * MP > D ? 2 * MP : D);
@@ -430,9 +430,21 @@ tc_bwd_ac_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const float sc = st_scale[bh];
     Segments sg(sch.N, m);
     if (MODE == kModeC) {
-      // landmark rows of s * dQt_tot / len, FP32, resident for the whole CTA
-      const float* src = dqt_tot + bh * (int64_t)m * D;
-      for (int idx = r; idx < m * D; idx += kTile) s_rows[idx] = src[idx] * (scale / (float)sg.len(idx / D));
+      // Landmark rows of s * dQt_tot / len (FP32), resident for the whole CTA, for the landmarks
+      // this CTA's rows belong to.  dQt_tot = Newton-Schulz part + the column pass's per-CTA
+      // partials, summed here in a fixed order.
+      const int64_t row_lo = (int64_t)tile0 * kTile;
+      int64_t row_hi = (int64_t)(tile0 + count) * kTile - 1;
+      if (row_hi > sch.N - 1) row_hi = sch.N - 1;
+      const int l_lo = sg.landmark_of(row_lo), l_hi = sg.landmark_of(row_hi);
+      const int md = m * D;
+      const float* ns_part = dqt_ns + bh * (int64_t)md;
+      const float* pb = partB + bh * (int64_t)nchunk_b * md;
+      for (int idx = l_lo * D + r; idx < (l_hi + 1) * D; idx += kTile) {
+        float acc = ns_part[idx];
+        for (int c = 0; c < nchunk_b; ++c) acc += pb[(size_t)c * md + idx];
+        s_rows[idx] = acc * (scale / (float)sg.len(idx / D));
+      }
       named_barrier(1, kTile);
     }
     bool alive = true;
