@@ -101,6 +101,10 @@ static int set_smem(K kernel, size_t bytes, int max_optin, const char* name) {
     return fail(FNB_ERR_SMEM, "insufficient smem for %s: needs %zu bytes, device allows %d", name,
                 bytes, max_optin);
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+  // ask for the largest shared-memory carveout so that co-residency is limited by the kernel's
+  // own footprint, not by the driver's default split between L1 and shared memory
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
   if (e != cudaSuccess)
     return fail(FNB_ERR_CUDA, "cudaFuncSetAttribute(%s, %zu) failed: %s", name, bytes,
                 cudaGetErrorString(e));

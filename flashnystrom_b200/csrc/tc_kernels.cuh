@@ -85,34 +85,38 @@ template <int D, int MP>
 struct FwdCSmem {
   static constexpr int kKt = MP * D * 2, kSt = D * MP * 2, kQ = kTile * D * 2, kP = kTile * MP * 2,
                        kO = kTile * D * 2;
-  static constexpr int kBytes = kKt + kSt + 2 * kQ + kP + kO + 256 + 1024;
+  static constexpr int kBytes = kKt + kSt + 2 * kQ + 2 * kP + kO + 256 + 1024;
 };
 
 // O = softmax(Q Kt^T) step2, lse1.   kt16 = s*log2e*Kt (MP x D), st16 = step2^T (D x MP).
+// Two-deep software pipeline: S and O are double-buffered in TMEM and P in shared memory, the
+// MMA thread issues the score product two tiles ahead, and the compute warps run
+// softmax(i) then epilogue(i-1), so they never wait for the tensor core.
 template <class T, int D, int MP>
-__global__ void __launch_bounds__(kTcThreads, 1)
+__global__ void __launch_bounds__(kTcThreads, 2)
 tc_fwd_c_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_o,
                 const __grid_constant__ CUtensorMap tm_kt, const __grid_constant__ CUtensorMap tm_st,
                 float* __restrict__ lse1, const float* __restrict__ st_scale, TcSched sch, int m,
                 int* status) {
   using L = FwdCSmem<D, MP>;
   constexpr int KBD = D / 64, KBM = MP / 64;
-  constexpr uint32_t kTmemCols = (MP + D <= 128) ? 128 : 256;
+  constexpr uint32_t kCols = 2 * MP + 2 * D;
+  constexpr uint32_t kTmemCols = kCols <= 256 ? 256 : 512;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* base = align1024(smem_raw);
   uint8_t* s_kt = base;
   uint8_t* s_st = s_kt + L::kKt;
   uint8_t* s_q = s_st + L::kSt;          // two stages
-  uint8_t* s_p = s_q + 2 * L::kQ;
-  uint8_t* s_o = s_p + L::kP;
+  uint8_t* s_p = s_q + 2 * L::kQ;        // two buffers
+  uint8_t* s_o = s_p + 2 * L::kP;
   uint64_t* bars = reinterpret_cast<uint64_t*>(s_o + L::kO);
   uint64_t* small_full = bars + 0;
   uint64_t* q_full = bars + 1;           // [2]
   uint64_t* q_empty = bars + 3;          // [2]
-  uint64_t* s_full = bars + 5;
-  uint64_t* p_full = bars + 6;
-  uint64_t* o_full = bars + 7;
-  uint64_t* o_free = bars + 8;
+  uint64_t* s_full = bars + 5;           // [2]
+  uint64_t* p_full = bars + 7;           // [2]
+  uint64_t* o_full = bars + 9;           // [2]
+  uint64_t* o_free = bars + 11;          // [2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
   int* abort_word = reinterpret_cast<int*>(tmem_slot + 1);
 
@@ -125,11 +129,10 @@ tc_fwd_c_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 
   if (threadIdx.x == 0) {
     mbar_init(small_full, 1);
-    for (int s = 0; s < 2; ++s) { mbar_init(q_full + s, 1); mbar_init(q_empty + s, 1); }
-    mbar_init(s_full, 1);
-    mbar_init(p_full, kTile);
-    mbar_init(o_full, 1);
-    mbar_init(o_free, kTile);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(q_full + s, 1); mbar_init(q_empty + s, 1); mbar_init(s_full + s, 1);
+      mbar_init(p_full + s, kTile); mbar_init(o_full + s, 1); mbar_init(o_free + s, kTile);
+    }
     *abort_word = 0;
     fence_mbar_init();
   }
@@ -141,7 +144,6 @@ tc_fwd_c_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + MP;
   Abort ab{abort_word, status};
 
   if (warp == 4) {
@@ -169,80 +171,60 @@ tc_fwd_c_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     if (lane == 0) {
       constexpr uint32_t idesc1 = make_idesc<T>(kTile, MP, false, false);
       constexpr uint32_t idesc2 = make_idesc<T>(kTile, D, false, false);
-      const uint32_t a_kt = smem_u32(s_kt), a_st = smem_u32(s_st), a_p = smem_u32(s_p);
-      bool ok = mbar_wait(small_full, 0, ab, 0x200);
-      for (int i = 0; ok && i < count; ++i) {
+      const uint32_t a_kt = smem_u32(s_kt), a_st = smem_u32(s_st);
+      // score product of tile i into S[i & 1]; the buffer was released when the MMA thread
+      // passed p_full of tile i-2, which precedes this call in program order
+      auto front = [&](int i) -> bool {
         const int st = i & 1;
-        if (!mbar_wait(q_full + st, (i >> 1) & 1, ab, 0x300 + i)) break;
+        if (!mbar_wait(q_full + st, (i >> 1) & 1, ab, 0x300 + i)) return false;
         tc_fence_after();
         const uint32_t a_q = smem_u32(s_q + st * L::kQ);
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           uint64_t ad = smem_desc_sw128(a_q + (k >> 2) * (kTile * 128) + (k & 3) * 32, 16, 1024);
           uint64_t bd = smem_desc_sw128(a_kt + (k >> 2) * (MP * 128) + (k & 3) * 32, 16, 1024);
-          umma(tmem_s, ad, bd, idesc1, k > 0);
+          umma(tmem_base + st * MP, ad, bd, idesc1, k > 0);
         }
         umma_commit(q_empty + st);
-        umma_commit(s_full);
-        if (!mbar_wait(p_full, i & 1, ab, 0x400 + i)) break;
-        if (!mbar_wait(o_free, (i & 1) ^ 1, ab, 0x500 + i)) break;
+        umma_commit(s_full + st);
+        return true;
+      };
+      bool ok = mbar_wait(small_full, 0, ab, 0x200);
+      ok = ok && front(0);
+      if (ok && count > 1) ok = front(1);
+      for (int i = 0; ok && i < count; ++i) {
+        const int st = i & 1;
+        if (!mbar_wait(p_full + st, (i >> 1) & 1, ab, 0x400 + i)) break;
+        if (!mbar_wait(o_free + st, ((i >> 1) & 1) ^ 1, ab, 0x500 + i)) break;
         tc_fence_after();
+        const uint32_t a_p = smem_u32(s_p + st * L::kP);
 #pragma unroll
         for (int k = 0; k < MP / 16; ++k) {
           uint64_t ad = smem_desc_sw128(a_p + (k >> 2) * (kTile * 128) + (k & 3) * 32, 16, 1024);
           uint64_t bd = smem_desc_sw128(a_st + (k >> 2) * (D * 128) + (k & 3) * 32, 16, 1024);
-          umma(tmem_o, ad, bd, idesc2, k > 0);
+          umma(tmem_base + 2 * MP + st * D, ad, bd, idesc2, k > 0);
         }
-        umma_commit(o_full);
+        umma_commit(o_full + st);
+        if (i + 2 < count) ok = front(i + 2);
       }
     }
   } else {
     const int r = threadIdx.x;  // tile row == TMEM lane
     const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
     const float osc = st_scale[bh];
-    for (int i = 0; i < count; ++i) {
-      if (!mbar_wait(s_full, i & 1, ab, 0x600 + i)) break;
-      __syncwarp();
-      tc_fence_after();
-      float s[MP];
-#pragma unroll
-      for (int c0 = 0; c0 < MP; c0 += 32) tmem_ld32(tmem_s + lane_base + c0, s + c0);
-      tmem_ld_wait();
-      float mx = -INFINITY;
-#pragma unroll
-      for (int j = 0; j < MP; ++j) if (j < m) mx = fmaxf(mx, s[j]);
-      float sum = 0.f;
-#pragma unroll
-      for (int j = 0; j < MP; ++j) {
-        float e = (j < m) ? fast_exp2(s[j] - mx) : 0.f;
-        s[j] = e;
-        sum += e;
-      }
-      const float inv = 1.f / sum;
-#pragma unroll
-      for (int c = 0; c < MP / 8; ++c) {
-        uint4 v;
-        v.x = pack2<T>(s[8 * c + 0] * inv, s[8 * c + 1] * inv);
-        v.y = pack2<T>(s[8 * c + 2] * inv, s[8 * c + 3] * inv);
-        v.z = pack2<T>(s[8 * c + 4] * inv, s[8 * c + 5] * inv);
-        v.w = pack2<T>(s[8 * c + 6] * inv, s[8 * c + 7] * inv);
-        *reinterpret_cast<uint4*>(s_p + (c >> 3) * (kTile * 128) + sw128_offset(r, c & 7)) = v;
-      }
-      fence_proxy_async();
-      tc_fence_before();
-      mbar_arrive(p_full);
-      const int64_t row = (int64_t)(tile0 + i) * kTile + r;
-      if (row < sch.N) lse1[bh * sch.N + row] = (mx + log2f(sum)) * kLn2;
-
-      if (!mbar_wait(o_full, i & 1, ab, 0x700 + i)) break;
+    bool alive = true;
+    // epilogue of tile j: O[j & 1] -> 16-bit -> staging -> TMA store
+    auto epilogue = [&](int j) -> bool {
+      const int st = j & 1;
+      if (!mbar_wait(o_full + st, (j >> 1) & 1, ab, 0x700 + j)) return false;
       __syncwarp();
       tc_fence_after();
       float o[D];
 #pragma unroll
-      for (int c0 = 0; c0 < D; c0 += 32) tmem_ld32(tmem_o + lane_base + c0, o + c0);
+      for (int c0 = 0; c0 < D; c0 += 32) tmem_ld32(tmem_base + 2 * MP + st * D + lane_base + c0, o + c0);
       tmem_ld_wait();
       tc_fence_before();
-      mbar_arrive(o_free);
+      mbar_arrive(o_free + st);
       if (r == 0) tma_store_wait_read();
       named_barrier(1, kTile);
 #pragma unroll
@@ -258,10 +240,51 @@ tc_fwd_c_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       named_barrier(1, kTile);
       if (r == 0) {
         for (int kb = 0; kb < KBD; ++kb)
-          tma_store_3d(&tm_o, s_o + kb * (kTile * 128), kb * 64, (tile0 + i) * kTile, (int)bh);
+          tma_store_3d(&tm_o, s_o + kb * (kTile * 128), kb * 64, (tile0 + j) * kTile, (int)bh);
         tma_store_commit();
       }
+      return true;
+    };
+    for (int i = 0; i < count; ++i) {
+      const int st = i & 1;
+      if (!mbar_wait(s_full + st, (i >> 1) & 1, ab, 0x600 + i)) { alive = false; break; }
+      __syncwarp();
+      tc_fence_after();
+      float s[MP];
+#pragma unroll
+      for (int c0 = 0; c0 < MP; c0 += 32) tmem_ld32(tmem_base + st * MP + lane_base + c0, s + c0);
+      tmem_ld_wait();
+      float mx = -INFINITY;
+#pragma unroll
+      for (int j = 0; j < MP; ++j) if (j < m) mx = fmaxf(mx, s[j]);
+      float sum = 0.f;
+#pragma unroll
+      for (int j = 0; j < MP; ++j) {
+        float e = (j < m) ? fast_exp2(s[j] - mx) : 0.f;
+        s[j] = e;
+        sum += e;
+      }
+      const float inv = 1.f / sum;
+      // P[st] was last read by the output product of tile i-2, whose completion (o_full) the
+      // epilogue of tile i-2 has already waited for
+      uint8_t* pbuf = s_p + st * L::kP;
+#pragma unroll
+      for (int c = 0; c < MP / 8; ++c) {
+        uint4 v;
+        v.x = pack2<T>(s[8 * c + 0] * inv, s[8 * c + 1] * inv);
+        v.y = pack2<T>(s[8 * c + 2] * inv, s[8 * c + 3] * inv);
+        v.z = pack2<T>(s[8 * c + 4] * inv, s[8 * c + 5] * inv);
+        v.w = pack2<T>(s[8 * c + 6] * inv, s[8 * c + 7] * inv);
+        *reinterpret_cast<uint4*>(pbuf + (c >> 3) * (kTile * 128) + sw128_offset(r, c & 7)) = v;
+      }
+      fence_proxy_async();
+      tc_fence_before();
+      mbar_arrive(p_full + st);
+      const int64_t row = (int64_t)(tile0 + i) * kTile + r;
+      if (row < sch.N) lse1[bh * sch.N + row] = (mx + log2f(sum)) * kLn2;
+      if (i > 0 && !epilogue(i - 1)) { alive = false; break; }
     }
+    if (alive) epilogue(count - 1);
     if (r == 0) tma_store_wait_all();
   }
   tc_fence_before();
@@ -289,7 +312,7 @@ struct BwdAcSmem {
 };
 
 template <class T, int D, int MP, int MODE>
-__global__ void __launch_bounds__(kTcThreads, 1)
+__global__ void __launch_bounds__(kTcThreads, 2)
 tc_bwd_ac_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_g,
                  const __grid_constant__ CUtensorMap tm_kt, const __grid_constant__ CUtensorMap tm_st,
                  const __grid_constant__ CUtensorMap tm_ktT, const __grid_constant__ CUtensorMap tm_dq,
@@ -595,7 +618,7 @@ struct BwdBSmem {
 };
 
 template <class T, int D, int MP>
-__global__ void __launch_bounds__(kTcThreads, 1)
+__global__ void __launch_bounds__(kTcThreads, 2)
 tc_bwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                 const __grid_constant__ CUtensorMap tm_qt, const __grid_constant__ CUtensorMap tm_do3,
                 const __grid_constant__ CUtensorMap tm_do3T, const __grid_constant__ CUtensorMap tm_qtT,
@@ -892,7 +915,7 @@ struct FwdBSmem {
 };
 
 template <class T, int D, int MP>
-__global__ void __launch_bounds__(kTcThreads, 1)
+__global__ void __launch_bounds__(kTcThreads, 2)
 tc_fwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                 const __grid_constant__ CUtensorMap tm_qt, float* __restrict__ part_acc,
                 float* __restrict__ part_max, float* __restrict__ part_sum, TcSched sch, int m,
