@@ -124,10 +124,11 @@ struct DeviceGuard {
   }
 };
 
-static int device_limits(int device, int* max_smem, int* cc_major) {
+static int device_limits(int device, int* max_smem, int* cc_major, int* sm_count) {
   // attribute queries are cheap and keep the call free of cached, thread-affine state
   FNB_CUDA(cudaDeviceGetAttribute(max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, device));
   FNB_CUDA(cudaDeviceGetAttribute(cc_major, cudaDevAttrComputeCapabilityMajor, device));
+  FNB_CUDA(cudaDeviceGetAttribute(sm_count, cudaDevAttrMultiProcessorCount, device));
   if (*cc_major != 10)
     return fail(FNB_ERR_UNSUPPORTED_DEVICE,
                 "device %d has compute capability %d.x; this library is built for sm_100a only",
@@ -189,7 +190,7 @@ static FwdWs carve_fwd(const Plan& p, void* base) {
 struct BwdWs {
   float *partA, *partB, *dstep2, *dkt_a, *dO3, *dqt_ns, *dkt_tot, *dqt_tot, *D3, *G, *dK2, *pinv;
   void* op16[8];              // 16-bit operand copies for the tensor-core kernels
-  float *st_scale, *do3_scale;
+  float *st_scale, *do3_scale, *rows_q, *rows_k;
   size_t bytes;
 };
 static BwdWs carve_bwd(const Plan& p, void* base) {
@@ -209,6 +210,7 @@ static BwdWs carve_bwd(const Plan& p, void* base) {
   const size_t op16 = ((size_t)p.BH * MP * p.D + 1) / 2;
   for (int i = 0; i < 8; ++i) w.op16[i] = take(op16);
   w.st_scale = take((size_t)p.BH); w.do3_scale = take((size_t)p.BH);
+  w.rows_q = take(md); w.rows_k = take(md);
   w.bytes = off;
   return w;
 }
@@ -221,12 +223,12 @@ static Plan plan_of(const fnb_shape& s) {
 // Forward: pooling pass -> landmarks -> [pseudoinverse | softmax-3 column pass] -> combine ->
 // output row pass.
 template <class T>
-static int forward_impl(const fnb_fwd_args& a, const Plan& p, const FwdWs& w, int max_smem,
+static int forward_impl(const fnb_fwd_args& a, const Plan& p, const FwdWs& w, int max_smem, int sms,
                         cudaStream_t st) {
   Launcher L(st, a.device);
   const float scale = powf((float)p.D, -0.25f);
   constexpr bool k16 = !std::is_same<T, float>::value;
-  const tc::TcSched sch = tc::make_sched(p.BH, p.N, 296);
+  const tc::TcSched sch = tc::make_sched(p.BH, p.N, 2 * sms);   // two CTAs per SM
   const bool use_tc = k16 && tc::tc_supported(a.shape.dtype, p.D, p.m, a.shape.flags) && sch.nchunk <= p.nchunk;
   const int MP = p.m <= 64 ? 64 : 128;
   const bool smem_ns = p.m <= ns::kN;
@@ -348,12 +350,12 @@ static int forward_impl(const fnb_fwd_args& a, const Plan& p, const FwdWs& w, in
 // Backward: softmax-1 row pass (partials) -> landmark-sized middle (dO3, dK2inv, pseudoinverse
 // backward) -> softmax-3 column pass (dK, dV, dQt partials) -> dQ row pass.
 template <class T>
-static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, int max_smem,
+static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, int max_smem, int sms,
                          cudaStream_t st) {
   Launcher L(st, a.device);
   const float scale = powf((float)p.D, -0.25f);
   constexpr bool k16 = !std::is_same<T, float>::value;
-  const tc::TcSched sch = tc::make_sched(p.BH, p.N, 296);
+  const tc::TcSched sch = tc::make_sched(p.BH, p.N, 2 * sms);   // two CTAs per SM
   const bool use_tc = k16 && tc::tc_supported(a.shape.dtype, p.D, p.m, a.shape.flags) && sch.nchunk <= p.nchunk;
   const int MP = p.m <= 64 ? 64 : 128;
   const bool smem_ns = p.m <= ns::kN;
@@ -374,9 +376,8 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
   const size_t gsmem = bwd_ac_smem(p.mpad, p.D);
   const int nchunk_used = use_tc ? sch.nchunk : p.nchunk;
 
-  void* kt16 = w.op16[0]; void* st16 = w.op16[1]; void* ktT16 = w.op16[2]; void* qt16 = w.op16[3];
-  void* qtT16 = w.op16[4]; void* do3n = w.op16[5]; void* do3T = w.op16[6];
-  CUtensorMap tm_q, tm_g, tm_kt, tm_st, tm_ktT, tm_dq;
+  void* kt16 = w.op16[0]; void* st16 = w.op16[1]; void* qt16 = w.op16[3]; void* do3n = w.op16[5];
+  CUtensorMap tm_q, tm_g, tm_kt, tm_st, tm_dq;
 
   // ---- pass A ---------------------------------------------------------------------------------
   if constexpr (k16) {
@@ -385,7 +386,7 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
       L.begin();
       {
         PackBwdAcParams pp;
-        pp.k_landmarks = a.k_landmarks; pp.step2 = a.step2; pp.kt16 = kt16; pp.ktT16 = ktT16; pp.st16 = st16;
+        pp.k_landmarks = a.k_landmarks; pp.step2 = a.step2; pp.kt16 = kt16; pp.ktT16 = nullptr; pp.st16 = st16;
         pp.st_scale = w.st_scale; pp.m = p.m; pp.D = p.D; pp.MP = MP; pp.dtype = a.shape.dtype;
         pp.kt_mul = scale * tc::kLog2e; pp.ktT_mul = scale;
         pack_bwd_ac_kernel<<<(unsigned)p.BH, kThreads, 0, st>>>(pp);
@@ -395,15 +396,14 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
           !tc::make_map_3d(&tm_g, a.d_out, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
           !tc::make_map_3d(&tm_dq, a.dq, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
           !tc::make_map_2d(&tm_kt, kt16, a.shape.dtype, p.BH * MPc, D, MPc) ||
-          !tc::make_map_2d(&tm_st, st16, a.shape.dtype, p.BH * MPc, D, MPc) ||
-          !tc::make_map_2d(&tm_ktT, ktT16, a.shape.dtype, p.BH * D, MPc, D))
+          !tc::make_map_2d(&tm_st, st16, a.shape.dtype, p.BH * MPc, D, MPc))
         return fail(FNB_ERR_CUDA, "cuTensorMapEncodeTiled failed for the backward row passes");
       L.begin();
       auto kern = tc::tc_bwd_ac_kernel<T, D, MPc, tc::kModeA>;
       size_t sm = tc::BwdAcSmem<D, MPc, tc::kModeA>::kBytes;
       if (int rc = set_smem(kern, sm, max_smem, "tc_bwd_a")) return rc;
-      kern<<<tgrid, tc::kTcThreads, sm, st>>>(tm_q, tm_g, tm_kt, tm_st, tm_ktT, tm_dq, a.lse1, w.st_scale, nullptr,
-                                             nullptr, 0, w.partA, sch, p.m, scale, a.device_status);
+      kern<<<tgrid, tc::kTcThreads, sm, st>>>(tm_q, tm_g, tm_kt, tm_st, tm_dq, a.lse1, w.st_scale, nullptr, w.partA,
+                                             sch, p.m, scale, a.device_status);
       if (L.end("tc_bwd_a")) return L.status;
     }
   }
@@ -422,7 +422,7 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
       mp.partA = w.partA; mp.nchunk = nchunk_used; mp.k2inv = a.k2_inv; mp.bmat = a.bmat;
       mp.q_landmarks = a.q_landmarks; mp.dkt_a = w.dkt_a; mp.dO3 = w.dO3; mp.D3 = w.D3; mp.G = w.G;
       mp.m = p.m; mp.D = p.D; mp.dtype = use_tc ? a.shape.dtype : 0; mp.MP = MP;
-      mp.qt16 = qt16; mp.qtT16 = qtT16; mp.do3n = do3n; mp.do3T = do3T; mp.do3_scale = w.do3_scale;
+      mp.qt16 = qt16; mp.qtT16 = nullptr; mp.do3n = do3n; mp.do3T = nullptr; mp.do3_scale = w.do3_scale;
       mp.qt_mul = scale * tc::kLog2e; mp.qtT_mul = scale;
       size_t sm = bwd_mid1_smem(p.m, p.D);
       if (int rc = set_smem(bwd_mid1_kernel, sm, max_smem, "bwd_mid1")) return rc;
@@ -435,6 +435,7 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
       np.k2 = a.k2; np.iterates = a.ns_iterates; np.G = w.G; np.qt = a.q_landmarks; np.kt = a.k_landmarks;
       np.dkt_a = w.dkt_a; np.dqt_ns = w.dqt_ns; np.dkt_tot = w.dkt_tot; np.spill = w.dK2;
       np.m = p.m; np.D = p.D; np.J = p.J; np.kappa = a.shape.kappa_star;
+      np.rows_k = use_tc ? w.rows_k : nullptr; np.N = p.N; np.scale = scale;
       if (int rc = set_smem(ns::ns_bwd_kernel, ns::kBwdSmem, max_smem, "ns_bwd")) return rc;
       ns::ns_bwd_kernel<<<(unsigned)p.BH, kThreads, ns::kBwdSmem, st>>>(np);
     }
@@ -458,15 +459,13 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
   if constexpr (k16) {
     if (use_tc) {
       constexpr int D = 64, MPc = 64;
-      CUtensorMap tm_k, tm_v, tm_qt, tm_do3, tm_do3T, tm_qtT, tm_dk, tm_dv;
+      CUtensorMap tm_k, tm_v, tm_qt, tm_do3, tm_dk, tm_dv;
       if (!tc::make_map_3d(&tm_k, a.k, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
           !tc::make_map_3d(&tm_v, a.v, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
           !tc::make_map_3d(&tm_dk, a.dk, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
           !tc::make_map_3d(&tm_dv, a.dv, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
           !tc::make_map_2d(&tm_qt, qt16, a.shape.dtype, p.BH * MPc, D, MPc) ||
-          !tc::make_map_2d(&tm_do3, do3n, a.shape.dtype, p.BH * MPc, D, MPc) ||
-          !tc::make_map_2d(&tm_do3T, do3T, a.shape.dtype, p.BH * D, MPc, D) ||
-          !tc::make_map_2d(&tm_qtT, qtT16, a.shape.dtype, p.BH * D, MPc, D))
+          !tc::make_map_2d(&tm_do3, do3n, a.shape.dtype, p.BH * MPc, D, MPc))
         return fail(FNB_ERR_CUDA, "cuTensorMapEncodeTiled failed for the backward column pass");
       int kshift = 0;
       while ((int64_t(2) << kshift) <= p.N && kshift < 14) ++kshift;   // floor(log2 N), at most 14
@@ -474,9 +473,8 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
       auto kern = tc::tc_bwd_b_kernel<T, D, MPc>;
       size_t sm = tc::BwdBSmem<D, MPc>::kBytes;
       if (int rc = set_smem(kern, sm, max_smem, "tc_bwd_b")) return rc;
-      kern<<<tgrid, tc::kTcThreads, sm, st>>>(tm_k, tm_v, tm_qt, tm_do3, tm_do3T, tm_qtT, tm_dk, tm_dv, a.lse3, w.D3,
-                                             w.do3_scale, w.dkt_tot, w.partB, sch, p.m, scale, kshift,
-                                             a.device_status);
+      kern<<<tgrid, tc::kTcThreads, sm, st>>>(tm_k, tm_v, tm_qt, tm_do3, tm_dk, tm_dv, a.lse3, w.D3, w.do3_scale,
+                                             w.rows_k, w.partB, sch, p.m, scale, kshift, a.device_status);
       if (L.end("tc_bwd_b")) return L.status;
     }
   }
@@ -492,11 +490,19 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
     if (use_tc) {
       constexpr int D = 64, MPc = 64;
       L.begin();
+      {
+        const int md = p.m * p.D;
+        dim3 grid((unsigned)((md / 4 + kThreads - 1) / kThreads), (unsigned)p.BH);
+        dqt_reduce2_kernel<<<grid, kThreads, 0, st>>>(w.partB, sch.nchunk, w.dqt_ns, nullptr, w.rows_q, p.m, p.D, p.N,
+                                                     scale);
+      }
+      if (L.end("dqt_rows")) return L.status;
+      L.begin();
       auto kern = tc::tc_bwd_ac_kernel<T, D, MPc, tc::kModeC>;
       size_t sm = tc::BwdAcSmem<D, MPc, tc::kModeC>::kBytes;
       if (int rc = set_smem(kern, sm, max_smem, "tc_bwd_c")) return rc;
-      kern<<<tgrid, tc::kTcThreads, sm, st>>>(tm_q, tm_g, tm_kt, tm_st, tm_ktT, tm_dq, a.lse1, w.st_scale, w.dqt_ns,
-                                             w.partB, sch.nchunk, nullptr, sch, p.m, scale, a.device_status);
+      kern<<<tgrid, tc::kTcThreads, sm, st>>>(tm_q, tm_g, tm_kt, tm_st, tm_dq, a.lse1, w.st_scale, w.rows_q, nullptr,
+                                             sch, p.m, scale, a.device_status);
       if (L.end("tc_bwd_c")) return L.status;
       return 0;
     }
@@ -505,7 +511,8 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
   {
     const int md = p.m * p.D;
     dim3 grid((unsigned)((md / 4 + kThreads - 1) / kThreads), (unsigned)p.BH);
-    dqt_reduce2_kernel<<<grid, kThreads, 0, st>>>(w.partB, p.nchunk, w.dqt_ns, w.dqt_tot, md);
+    dqt_reduce2_kernel<<<grid, kThreads, 0, st>>>(w.partB, p.nchunk, w.dqt_ns, w.dqt_tot, nullptr, p.m, p.D, p.N,
+                                                 scale);
   }
   if (L.end("dqt_reduce")) return L.status;
   L.begin();
@@ -571,13 +578,13 @@ int fnb_forward(const fnb_fwd_args* a) {
                 w.bytes, a->workspace_bytes);
   DeviceGuard g(a->device);
   if (!g.ok) return fail(FNB_ERR_CUDA, "cannot select CUDA device %d", a->device);
-  int max_smem = 0, cc = 0;
-  if (int rc = device_limits(a->device, &max_smem, &cc)) return rc;
+  int max_smem = 0, cc = 0, sms = 0;
+  if (int rc = device_limits(a->device, &max_smem, &cc, &sms)) return rc;
   cudaStream_t st = (cudaStream_t)a->stream;
   switch (a->shape.dtype) {
-    case FNB_F32: return forward_impl<float>(*a, p, w, max_smem, st);
-    case FNB_F16: return forward_impl<__half>(*a, p, w, max_smem, st);
-    default: return forward_impl<__nv_bfloat16>(*a, p, w, max_smem, st);
+    case FNB_F32: return forward_impl<float>(*a, p, w, max_smem, sms, st);
+    case FNB_F16: return forward_impl<__half>(*a, p, w, max_smem, sms, st);
+    default: return forward_impl<__nv_bfloat16>(*a, p, w, max_smem, sms, st);
   }
 }
 
@@ -599,13 +606,13 @@ int fnb_backward(const fnb_bwd_args* a) {
                 w.bytes, a->workspace_bytes);
   DeviceGuard g(a->device);
   if (!g.ok) return fail(FNB_ERR_CUDA, "cannot select CUDA device %d", a->device);
-  int max_smem = 0, cc = 0;
-  if (int rc = device_limits(a->device, &max_smem, &cc)) return rc;
+  int max_smem = 0, cc = 0, sms = 0;
+  if (int rc = device_limits(a->device, &max_smem, &cc, &sms)) return rc;
   cudaStream_t st = (cudaStream_t)a->stream;
   switch (a->shape.dtype) {
-    case FNB_F32: return backward_impl<float>(*a, p, w, max_smem, st);
-    case FNB_F16: return backward_impl<__half>(*a, p, w, max_smem, st);
-    default: return backward_impl<__nv_bfloat16>(*a, p, w, max_smem, st);
+    case FNB_F32: return backward_impl<float>(*a, p, w, max_smem, sms, st);
+    case FNB_F16: return backward_impl<__half>(*a, p, w, max_smem, sms, st);
+    default: return backward_impl<__nv_bfloat16>(*a, p, w, max_smem, sms, st);
   }
 }
 

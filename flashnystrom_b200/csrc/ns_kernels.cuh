@@ -397,6 +397,9 @@ struct NsBwdParams {
   const float* qt; const float* kt; const float* dkt_a;     // [BH][m][D]
   float* dqt_ns; float* dkt_tot;                            // [BH][m][D]
   float* spill;                                             // [BH][m][m]
+  float* rows_k;                                            // optional [BH][m][D]: scale * dkt_tot / len
+  int64_t N;
+  float scale;
   int m, D, J;
   float kappa;
 };
@@ -441,6 +444,11 @@ __global__ void __launch_bounds__(kThreads, 1) ns_bwd_kernel(NsBwdParams p) {
     }
     *reinterpret_cast<float4*>(dqt_ns + l * D + d) = a;
     *reinterpret_cast<float4*>(dkt_tot + l * D + d) = b;
+    if (p.rows_k) {
+      Segments sg(p.N, m);
+      const float f = p.scale / (float)sg.len(l);
+      *reinterpret_cast<float4*>(p.rows_k + bh * md + l * D + d) = make_float4(b.x * f, b.y * f, b.z * f, b.w * f);
+    }
   }
 }
 

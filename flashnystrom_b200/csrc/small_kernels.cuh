@@ -282,13 +282,14 @@ __global__ void __launch_bounds__(kThreads) bwd_mid1_kernel(BwdMid1Params p) {
   const size_t ob = (size_t)bh * MP * D * 2;
   for (int idx = t; idx < MP * D; idx += kThreads)
     store16(reinterpret_cast<char*>(p.do3n) + ob, p.dtype, idx, (idx / D) < m ? do3[idx] * inv_sc : 0.f);
-  for (int idx = t; idx < D * MP; idx += kThreads) {
-    int d = idx / MP, l = idx - d * MP;
-    store16(reinterpret_cast<char*>(p.do3T) + ob, p.dtype, idx, l < m ? do3[l * D + d] * inv_sc : 0.f);
-  }
+  if (p.do3T)
+    for (int idx = t; idx < D * MP; idx += kThreads) {
+      int d = idx / MP, l = idx - d * MP;
+      store16(reinterpret_cast<char*>(p.do3T) + ob, p.dtype, idx, l < m ? do3[l * D + d] * inv_sc : 0.f);
+    }
   const float* qt = p.q_landmarks + bh * (int64_t)md;
   pack_pair(qt, reinterpret_cast<char*>(p.qt16) + ob, nullptr, p.dtype, m, D, MP, p.qt_mul);
-  pack_pair(qt, nullptr, reinterpret_cast<char*>(p.qtT16) + ob, p.dtype, m, D, MP, p.qtT_mul);
+  if (p.qtT16) pack_pair(qt, nullptr, reinterpret_cast<char*>(p.qtT16) + ob, p.dtype, m, D, MP, p.qtT_mul);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -315,14 +316,17 @@ __global__ void __launch_bounds__(kThreads) pack_bwd_ac_kernel(PackBwdAcParams p
   if (threadIdx.x == 0) p.st_scale[bh] = sc;
   pack_pair(st, reinterpret_cast<char*>(p.st16) + ob, nullptr, p.dtype, p.m, p.D, p.MP, 1.f / sc);
   pack_pair(kt, reinterpret_cast<char*>(p.kt16) + ob, nullptr, p.dtype, p.m, p.D, p.MP, p.kt_mul);
-  pack_pair(kt, nullptr, reinterpret_cast<char*>(p.ktT16) + ob, p.dtype, p.m, p.D, p.MP, p.ktT_mul);
+  if (p.ktT16) pack_pair(kt, nullptr, reinterpret_cast<char*>(p.ktT16) + ob, p.dtype, p.m, p.D, p.MP, p.ktT_mul);
 }
 
-// dqt_tot = dqt_ns + sum over chunks of the column-pass partials (CUDA-core path only; the
-// tensor-core dQ pass folds this reduction into its prologue)
+// dqt_tot = dqt_ns + sum over chunks of the column-pass partials, summed in a fixed order.
+// rows_q (optional) = scale * dqt_tot / len(landmark): the per-landmark row the dQ pass adds to
+// every token of that landmark's segment.
 __global__ void __launch_bounds__(kThreads)
-dqt_reduce2_kernel(const float* partB, int nchunk, const float* dqt_ns, float* dqt_tot, int md) {
+dqt_reduce2_kernel(const float* partB, int nchunk, const float* dqt_ns, float* dqt_tot, float* rows_q, int m,
+                   int D, int64_t N, float scale) {
   const int64_t bh = blockIdx.y;
+  const int md = m * D;
   const int idx4 = (blockIdx.x * kThreads + threadIdx.x) * 4;
   if (idx4 >= md) return;
   float4 s = *reinterpret_cast<const float4*>(dqt_ns + bh * md + idx4);
@@ -331,7 +335,12 @@ dqt_reduce2_kernel(const float* partB, int nchunk, const float* dqt_ns, float* d
     const float4 x = *reinterpret_cast<const float4*>(src + (size_t)c * md);
     s.x += x.x; s.y += x.y; s.z += x.z; s.w += x.w;
   }
-  *reinterpret_cast<float4*>(dqt_tot + bh * md + idx4) = s;
+  if (dqt_tot) *reinterpret_cast<float4*>(dqt_tot + bh * md + idx4) = s;
+  if (rows_q) {
+    Segments sg(N, m);
+    const float f = scale / (float)sg.len(idx4 / D);
+    *reinterpret_cast<float4*>(rows_q + bh * md + idx4) = make_float4(s.x * f, s.y * f, s.z * f, s.w * f);
+  }
 }
 
 }  // namespace fnb

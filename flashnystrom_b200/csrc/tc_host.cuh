@@ -3,7 +3,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <mutex>
-#include "tc_kernels.cuh"
+#include "tc_stream.cuh"
 
 namespace fnb {
 namespace tc {
@@ -59,11 +59,13 @@ inline bool make_map_2d(CUtensorMap* map, const void* ptr, int dtype, int64_t ro
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-inline TcSched make_sched(int64_t BH, int64_t N, int ctas_target) {
+// One wave: at most `slots` CTAs (co-resident CTAs per SM x SM count) in total, so that no CTA
+// waits for a slot while the others are already done.  Slices are cut into equal runs of tiles.
+inline TcSched make_sched(int64_t BH, int64_t N, int slots) {
   TcSched s;
   s.N = N;
   int64_t tiles = (N + kTile - 1) / kTile;
-  int64_t want = (ctas_target + BH - 1) / BH;
+  int64_t want = slots / BH;            // floor: BH * want <= slots
   if (want > tiles) want = tiles;
   if (want < 1) want = 1;
   int64_t tpc = (tiles + want - 1) / want;

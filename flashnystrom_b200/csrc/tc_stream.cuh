@@ -1,0 +1,1067 @@
+// sm_100a tensor-core streaming kernels (fp16 / bf16 I/O, FP32 accumulation in TMEM).
+//
+// Common structure: a CTA of 10 warps owns a run of consecutive 128-row tiles of one (b,h)
+// slice.  Warp 8 is the TMA producer, warp 9 issues tcgen05.mma (one thread), warps 0-7 are
+// the compute warps.  Compute thread t owns tile row r = t & 127 (= TMEM lane r) and column half
+// h = t >> 7 of every per-row vector, so per-thread state is half a row and a row-wise reduction
+// costs one exchange through shared memory between the two threads of a row.  Tiles of Q/K/V/dO
+// are staged by TMA with the 128-byte swizzle; probabilities and softmax gradients go back to
+// shared memory in the same swizzled [128 x 64] blocks and serve directly as UMMA operands
+// (K-major when contracted over landmarks, MN-major when contracted over the tile's rows).  The
+// landmark-sized operands (m x D, padded to MP = 64 or 128 landmarks) are packed once per call
+// into 16-bit copies and stay resident in shared memory for the whole CTA.
+#pragma once
+#include "common.cuh"
+#include "tc_common.cuh"
+
+namespace fnb {
+namespace tc {
+
+constexpr int kTile = 128;
+constexpr int kComputeThreads = 256;
+constexpr int kProducerWarp = 8, kMmaWarp = 9;
+constexpr int kTcThreads = 320;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+
+__device__ __forceinline__ uint8_t* align1024(uint8_t* p) {
+  return reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(p) + 1023) & ~(uintptr_t)1023);
+}
+
+struct TcSched {
+  int64_t N;
+  int nchunk;            // CTAs per (b,h) slice
+  int tiles_per_chunk;   // 128-row tiles per CTA
+};
+
+// NC consecutive FP32 TMEM columns of this thread's lane -> registers
+template <int NC>
+__device__ __forceinline__ void ld_cols(uint32_t taddr, float* v) {
+#pragma unroll
+  for (int c0 = 0; c0 < NC; c0 += 32) tmem_ld32(taddr + c0, v + c0);
+}
+// NC values (columns col0 .. col0+NC-1 of row r) -> 16-bit, into a swizzled tile made of
+// [128 x 64] blocks
+template <class T, int NC>
+__device__ __forceinline__ void store_cols(uint8_t* tile, int r, int col0, const float* v) {
+#pragma unroll
+  for (int c = 0; c < NC / 8; ++c) {
+    uint4 w;
+    w.x = pack2<T>(v[8 * c + 0], v[8 * c + 1]);
+    w.y = pack2<T>(v[8 * c + 2], v[8 * c + 3]);
+    w.z = pack2<T>(v[8 * c + 4], v[8 * c + 5]);
+    w.w = pack2<T>(v[8 * c + 6], v[8 * c + 7]);
+    const int cc = (col0 >> 3) + c;
+    *reinterpret_cast<uint4*>(tile + (cc >> 3) * (kTile * 128) + sw128_offset(r, cc & 7)) = w;
+  }
+}
+// K-major operand: advance by k 16-element steps along K inside [rows x 64] blocks
+__device__ __forceinline__ uint64_t kdesc(uint32_t base, int k, int rows) {
+  return smem_desc_sw128(base + (k >> 2) * (rows * 128) + (k & 3) * 32, 16, 1024);
+}
+// MN-major operand staged as [128 rows(K) x 64] blocks: advance by k 16-row steps along K
+__device__ __forceinline__ uint64_t mndesc(uint32_t base, int k) {
+  return smem_desc_sw128(base + k * 2048, kTile * 128, 1024);
+}
+
+struct TileRange { int64_t bh; int chunk, tile0, count; };
+__device__ __forceinline__ TileRange tile_range(const TcSched& sch) {
+  TileRange t;
+  t.bh = blockIdx.x / sch.nchunk;
+  t.chunk = (int)(blockIdx.x - t.bh * sch.nchunk);
+  const int total_tiles = (int)((sch.N + kTile - 1) / kTile);
+  t.tile0 = t.chunk * sch.tiles_per_chunk;
+  t.count = min(sch.tiles_per_chunk, total_tiles - t.tile0);
+  return t;
+}
+
+// ------------------------------------------------------------------------------------------
+// Forward output pass:  O = softmax(Q Kt^T) step2, lse1.
+//   kt16 = s*log2e*Kt (MP x D), st16 = step2^T / 2^e (D x MP), st_scale[bh] = 2^e.
+// Two-deep pipeline: S and O are double-buffered in TMEM and P in shared memory; the MMA thread
+// issues the score product two tiles ahead; the compute warps run softmax(i), epilogue(i-1).
+template <int D, int MP>
+struct FwdCSmem {
+  static constexpr int kKt = MP * D * 2, kSt = D * MP * 2, kQ = kTile * D * 2, kP = kTile * MP * 2,
+                       kO = kTile * D * 2, kX = 2 * 2 * kTile * 8;
+  static constexpr int kBytes = kKt + kSt + 2 * kQ + 2 * kP + kO + kX + 256 + 1024;
+};
+
+template <class T, int D, int MP>
+__global__ void __launch_bounds__(kTcThreads, 2)
+tc_fwd_c_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_o,
+                const __grid_constant__ CUtensorMap tm_kt, const __grid_constant__ CUtensorMap tm_st,
+                float* __restrict__ lse1, const float* __restrict__ st_scale, TcSched sch, int m,
+                int* status) {
+  using L = FwdCSmem<D, MP>;
+  constexpr int KBD = D / 64, KBM = MP / 64, HC = MP / 2, HD = D / 2;
+  constexpr uint32_t kCols = 2 * MP + 2 * D;
+  constexpr uint32_t kTmemCols = kCols <= 256 ? 256 : 512;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* base = align1024(smem_raw);
+  uint8_t* s_kt = base;
+  uint8_t* s_st = s_kt + L::kKt;
+  uint8_t* s_q = s_st + L::kSt;          // two stages
+  uint8_t* s_p = s_q + 2 * L::kQ;        // two buffers
+  uint8_t* s_o = s_p + 2 * L::kP;
+  float2* s_x = reinterpret_cast<float2*>(s_o + L::kO);   // [2][2][128] (max, sum) exchange
+  uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(s_x) + L::kX);
+  uint64_t* small_full = bars + 0;
+  uint64_t* q_full = bars + 1;           // [2]
+  uint64_t* q_empty = bars + 3;          // [2]
+  uint64_t* s_full = bars + 5;           // [2]
+  uint64_t* p_full = bars + 7;           // [2]
+  uint64_t* o_full = bars + 9;           // [2]
+  uint64_t* o_free = bars + 11;          // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+  int* abort_word = reinterpret_cast<int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const TileRange tr = tile_range(sch);
+  const int64_t bh = tr.bh;
+  const int tile0 = tr.tile0, count = tr.count;
+
+  if (threadIdx.x == 0) {
+    mbar_init(small_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(q_full + s, 1); mbar_init(q_empty + s, 1); mbar_init(s_full + s, 1);
+      mbar_init(p_full + s, kComputeThreads); mbar_init(o_full + s, 1); mbar_init(o_free + s, kComputeThreads);
+    }
+    *abort_word = 0;
+    fence_mbar_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  Abort ab{abort_word, status};
+
+  if (warp == kProducerWarp) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tm_q);
+      tma_prefetch_desc(&tm_o);
+      mbar_expect_tx(small_full, L::kKt + L::kSt);
+      for (int kb = 0; kb < KBD; ++kb) tma_load_2d(s_kt + kb * (MP * 128), &tm_kt, small_full, kb * 64, (int)(bh * MP));
+      for (int kb = 0; kb < KBM; ++kb) tma_load_2d(s_st + kb * (D * 128), &tm_st, small_full, kb * 64, (int)(bh * D));
+      int armed = 0;
+      for (int i = 0; i < count; ++i) {
+        const int st = i & 1;
+        if (!mbar_wait(q_empty + st, ((i >> 1) & 1) ^ 1, ab, 0x100 + i)) break;
+        mbar_expect_tx(q_full + st, L::kQ);
+        for (int kb = 0; kb < KBD; ++kb)
+          tma_load_3d(s_q + st * L::kQ + kb * (kTile * 128), &tm_q, q_full + st, kb * 64, (tile0 + i) * kTile, (int)bh);
+        armed = i + 1;
+      }
+      if (ab.raised())   // let copies already in flight land before the shared memory is released
+        for (int i = max(0, armed - 2); i < armed; ++i) mbar_drain(q_full + (i & 1), (i >> 1) & 1);
+    }
+  } else if (warp == kMmaWarp) {
+    if (lane == 0) {
+      constexpr uint32_t idesc1 = make_idesc<T>(kTile, MP, false, false);
+      constexpr uint32_t idesc2 = make_idesc<T>(kTile, D, false, false);
+      const uint32_t a_kt = smem_u32(s_kt), a_st = smem_u32(s_st);
+      // Score product of tile i into S[i & 1].  That buffer was released when this thread passed
+      // p_full of tile i-2, which precedes this call in program order.
+      auto front = [&](int i) -> bool {
+        const int st = i & 1;
+        if (!mbar_wait(q_full + st, (i >> 1) & 1, ab, 0x300 + i)) return false;
+        tc_fence_after();
+        const uint32_t a_q = smem_u32(s_q + st * L::kQ);
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k)
+          umma(tmem_base + st * MP, kdesc(a_q, k, kTile), kdesc(a_kt, k, MP), idesc1, k > 0);
+        umma_commit(q_empty + st);
+        umma_commit(s_full + st);
+        return true;
+      };
+      bool ok = mbar_wait(small_full, 0, ab, 0x200);
+      ok = ok && front(0);
+      if (ok && count > 1) ok = front(1);
+      for (int i = 0; ok && i < count; ++i) {
+        const int st = i & 1;
+        if (!mbar_wait(p_full + st, (i >> 1) & 1, ab, 0x400 + i)) break;
+        if (!mbar_wait(o_free + st, ((i >> 1) & 1) ^ 1, ab, 0x500 + i)) break;
+        tc_fence_after();
+        const uint32_t a_p = smem_u32(s_p + st * L::kP);
+#pragma unroll
+        for (int k = 0; k < MP / 16; ++k)
+          umma(tmem_base + 2 * MP + st * D, kdesc(a_p, k, kTile), kdesc(a_st, k, D), idesc2, k > 0);
+        umma_commit(o_full + st);
+        if (i + 2 < count) ok = front(i + 2);
+      }
+    }
+  } else {
+    const int r = threadIdx.x & 127, h = threadIdx.x >> 7;   // tile row (TMEM lane), column half
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    const float osc = st_scale[bh];
+    float inv_tot[2] = {0.f, 0.f};
+    bool alive = true;
+    auto epilogue = [&](int j) -> bool {
+      const int st = j & 1;
+      if (!mbar_wait(o_full + st, (j >> 1) & 1, ab, 0x700 + j)) return false;
+      __syncwarp();
+      tc_fence_after();
+      float o[HD];
+      ld_cols<HD>(tmem_base + 2 * MP + st * D + lane_base + h * HD, o);
+      tmem_ld_wait();
+      tc_fence_before();
+      mbar_arrive(o_free + st);
+      if (threadIdx.x == 0) tma_store_wait_read();
+      named_barrier(1, kComputeThreads);
+      const float mul = st ? inv_tot[1] : inv_tot[0];
+#pragma unroll
+      for (int j2 = 0; j2 < HD; ++j2) o[j2] *= mul;
+      store_cols<T, HD>(s_o, r, h * HD, o);
+      fence_proxy_async();
+      named_barrier(1, kComputeThreads);
+      if (threadIdx.x == 0) {
+        for (int kb = 0; kb < KBD; ++kb)
+          tma_store_3d(&tm_o, s_o + kb * (kTile * 128), kb * 64, (tile0 + j) * kTile, (int)bh);
+        tma_store_commit();
+      }
+      return true;
+    };
+    for (int i = 0; i < count; ++i) {
+      const int st = i & 1;
+      if (!mbar_wait(s_full + st, (i >> 1) & 1, ab, 0x600 + i)) { alive = false; break; }
+      __syncwarp();
+      tc_fence_after();
+      float s[HC];
+      ld_cols<HC>(tmem_base + st * MP + lane_base + h * HC, s);
+      tmem_ld_wait();
+      const int c0 = h * HC;
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int j = 0; j < HC; ++j) if (c0 + j < m) mx4[j & 3] = fmaxf(mx4[j & 3], s[j]);
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      float sm4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int j = 0; j < HC; ++j) {
+        const float e = (c0 + j < m) ? fast_exp2(s[j] - mx) : 0.f;
+        s[j] = e;
+        sm4[j & 3] += e;
+      }
+      const float sum = (sm4[0] + sm4[1]) + (sm4[2] + sm4[3]);
+      s_x[(st * 2 + h) * kTile + r] = make_float2(mx, sum);
+      named_barrier(1, kComputeThreads);
+      const float2 other = s_x[(st * 2 + (h ^ 1)) * kTile + r];
+      const float M = fmaxf(mx, other.x);
+      const float f = (mx == -INFINITY) ? 0.f : fast_exp2(mx - M);
+      const float fo = (other.x == -INFINITY) ? 0.f : fast_exp2(other.x - M);
+      const float tot = sum * f + other.y * fo;
+#pragma unroll
+      for (int j = 0; j < HC; ++j) s[j] *= f;
+      // P[st] was last read by the output product of tile i-2, whose completion (o_full) the
+      // epilogue of tile i-2 has already waited for
+      store_cols<T, HC>(s_p + st * L::kP, r, c0, s);
+      fence_proxy_async();
+      tc_fence_before();
+      mbar_arrive(p_full + st);
+      if (st) inv_tot[1] = osc / tot; else inv_tot[0] = osc / tot;
+      const int64_t row = (int64_t)(tile0 + i) * kTile + r;
+      if (h == 0 && row < sch.N) lse1[bh * sch.N + row] = (M + log2f(tot)) * kLn2;
+      if (i > 0 && !epilogue(i - 1)) { alive = false; break; }
+    }
+    if (alive) epilogue(count - 1);
+    if (threadIdx.x == 0) tma_store_wait_all();
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem_base, kTmemCols);
+}
+
+// ------------------------------------------------------------------------------------------
+// Softmax-1 backward, both row passes.  Per 128-row tile of Q and dO:
+//   S1 = Q kt16^T (log2 domain), dP1 = dO st16^T (step2 normalised by 2^-e, undone by sc),
+//   P1 = exp2(S1 - lse1*log2e), D1 = rowsum(P1 o dP1), dS1 = P1 o (dP1 - D1)        [FP32]
+// kModeA: accumulate dstep2 += P1^T dO and dKt += dS1^T Q in TMEM over all of the CTA's tiles
+//         (UMMA with both operands MN-major: the staged tiles are contracted over their rows)
+//         and write one FP32 partial pair per CTA.
+// kModeC: dQ = s dS1 Kt + rows_q[l(n)], written once through a TMA store; rows_q holds
+//         s * dQt_tot / len per landmark.  Kt is read from the same kt16 copy as an MN-major
+//         operand (its s*log2e factor is undone by ln2 in the epilogue).
+constexpr int kModeA = 0, kModeC = 1;
+
+template <int D, int MP, int MODE>
+struct BwdAcSmem {
+  static constexpr int kKt = MP * D * 2, kSt = MP * D * 2, kIn = kTile * D * 2,
+                       kP = (MODE == kModeA) ? kTile * MP * 2 : 0, kDs = kTile * (MP > D ? MP : D) * 2,
+                       kX = (MODE == kModeC) ? 2 * kTile * 4 * 2 : 0;
+  // mode A relies on the dynamic shared window being 1024-byte aligned (checked at run time)
+  static constexpr int kBytes = kKt + kSt + 4 * kIn + kP + kDs + kX + 256 + (MODE == kModeC ? 1024 : 0);
+};
+
+template <class T, int D, int MP, int MODE>
+__global__ void __launch_bounds__(kTcThreads, 2)
+tc_bwd_ac_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_g,
+                 const __grid_constant__ CUtensorMap tm_kt, const __grid_constant__ CUtensorMap tm_st,
+                 const __grid_constant__ CUtensorMap tm_dq,
+                 const float* __restrict__ lse1, const float* __restrict__ st_scale,
+                 const float* __restrict__ rows_q, float* __restrict__ partA, TcSched sch, int m,
+                 float scale, int* status) {
+  using L = BwdAcSmem<D, MP, MODE>;
+  constexpr int KBD = D / 64, HC = MP / 2, HD = D / 2;
+  constexpr uint32_t kCols = (MODE == kModeA) ? 2 * MP + 2 * D : 4 * MP;
+  constexpr uint32_t kTmemCols = kCols <= 256 ? 256 : 512;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* base = (MODE == kModeC) ? align1024(smem_raw) : smem_raw;
+  if (MODE == kModeA && (smem_u32(smem_raw) & 1023u)) {
+    if (threadIdx.x == 0 && status) atomicCAS(status, 0, (2 << 24) | 0x1000);
+    return;
+  }
+  uint8_t* s_kt = base;
+  uint8_t* s_st = s_kt + L::kKt;
+  uint8_t* s_q = s_st + L::kSt;          // two stages
+  uint8_t* s_g = s_q + 2 * L::kIn;       // two stages
+  uint8_t* s_p = s_g + 2 * L::kIn;       // mode A: P tile (its head doubles as the D1 exchange)
+  uint8_t* s_ds = s_p + L::kP;           // dS tile; mode C: afterwards the staging of the dQ tile
+  float* s_x = (MODE == kModeA) ? reinterpret_cast<float*>(s_p) : reinterpret_cast<float*>(s_ds + L::kDs);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(s_ds + L::kDs + L::kX);
+  uint64_t* small_full = bars + 0;
+  uint64_t* in_full = bars + 1;          // [2]
+  uint64_t* in_empty = bars + 3;         // [2]
+  uint64_t* sdp_full = bars + 5;         // [2] (mode A uses [0] only)
+  uint64_t* pds_full = bars + 7;         // [2] (mode A uses [0] only)
+  uint64_t* acc_done = bars + 9;         // mode A: accumulation of a tile complete; mode C [2]: dQ tile complete
+  uint64_t* o_free = bars + 11;          // [2] mode C: dQ accumulator read back
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+  int* abort_word = reinterpret_cast<int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const TileRange tr = tile_range(sch);
+  const int64_t bh = tr.bh;
+  const int tile0 = tr.tile0, count = tr.count;
+
+  if (threadIdx.x == 0) {
+    mbar_init(small_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(in_full + s, 1); mbar_init(in_empty + s, 1); mbar_init(sdp_full + s, 1);
+      mbar_init(pds_full + s, kComputeThreads); mbar_init(acc_done + s, 1); mbar_init(o_free + s, kComputeThreads);
+    }
+    *abort_word = 0;
+    fence_mbar_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  Abort ab{abort_word, status};
+
+  if (warp == kProducerWarp) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tm_q);
+      tma_prefetch_desc(&tm_g);
+      mbar_expect_tx(small_full, L::kKt + L::kSt);
+      for (int kb = 0; kb < KBD; ++kb) {
+        tma_load_2d(s_kt + kb * (MP * 128), &tm_kt, small_full, kb * 64, (int)(bh * MP));
+        tma_load_2d(s_st + kb * (MP * 128), &tm_st, small_full, kb * 64, (int)(bh * MP));
+      }
+      int armed = 0;
+      for (int i = 0; i < count; ++i) {
+        const int st = i & 1;
+        if (!mbar_wait(in_empty + st, ((i >> 1) & 1) ^ 1, ab, 0x1100 + i)) break;
+        mbar_expect_tx(in_full + st, 2 * L::kIn);
+        for (int kb = 0; kb < KBD; ++kb) {
+          tma_load_3d(s_q + st * L::kIn + kb * (kTile * 128), &tm_q, in_full + st, kb * 64, (tile0 + i) * kTile, (int)bh);
+          tma_load_3d(s_g + st * L::kIn + kb * (kTile * 128), &tm_g, in_full + st, kb * 64, (tile0 + i) * kTile, (int)bh);
+        }
+        armed = i + 1;
+      }
+      if (ab.raised())
+        for (int i = max(0, armed - 2); i < armed; ++i) mbar_drain(in_full + (i & 1), (i >> 1) & 1);
+    }
+  } else if (warp == kMmaWarp) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = make_idesc<T>(kTile, MP, false, false);
+      constexpr uint32_t idesc_acc = make_idesc<T>(MP, D, true, true);
+      constexpr uint32_t idesc_dq = make_idesc<T>(kTile, D, false, true);
+      const uint32_t a_kt = smem_u32(s_kt), a_st = smem_u32(s_st), a_p = smem_u32(s_p), a_ds = smem_u32(s_ds);
+      // S and dP of tile i into TMEM buffer b (mode A: always buffer 0)
+      auto front = [&](int i, int b) -> bool {
+        const int st = i & 1;
+        if (!mbar_wait(in_full + st, (i >> 1) & 1, ab, 0x1300 + i)) return false;
+        tc_fence_after();
+        const uint32_t a_q = smem_u32(s_q + st * L::kIn), a_g = smem_u32(s_g + st * L::kIn);
+        const uint32_t t_s = tmem_base + b * 2 * MP;
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) umma(t_s, kdesc(a_q, k, kTile), kdesc(a_kt, k, MP), idesc_s, k > 0);
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) umma(t_s + MP, kdesc(a_g, k, kTile), kdesc(a_st, k, MP), idesc_s, k > 0);
+        if (MODE == kModeC) umma_commit(in_empty + st);
+        umma_commit(sdp_full + b);
+        return true;
+      };
+      bool ok = mbar_wait(small_full, 0, ab, 0x1200);
+      ok = ok && front(0, 0);
+      if (MODE == kModeC && ok && count > 1) ok = front(1, 1);
+      for (int i = 0; ok && i < count; ++i) {
+        if (MODE == kModeA) {
+          if (!mbar_wait(pds_full, i & 1, ab, 0x1400 + i)) break;
+          // S / dP of tile i are consumed: start the next tile's scores before this tile's
+          // accumulation so that the compute warps find them ready
+          if (i + 1 < count && !front(i + 1, 0)) break;
+          tc_fence_after();
+          const int st = i & 1;
+          const uint32_t a_q = smem_u32(s_q + st * L::kIn), a_g = smem_u32(s_g + st * L::kIn);
+#pragma unroll
+          for (int k = 0; k < kTile / 16; ++k)
+            umma(tmem_base + 2 * MP, mndesc(a_p, k), mndesc(a_g, k), idesc_acc, (i > 0 || k > 0));
+#pragma unroll
+          for (int k = 0; k < kTile / 16; ++k)
+            umma(tmem_base + 2 * MP + D, mndesc(a_ds, k), mndesc(a_q, k), idesc_acc, (i > 0 || k > 0));
+          umma_commit(in_empty + st);
+          umma_commit(acc_done);
+        } else {
+          const int b = i & 1;
+          if (!mbar_wait(pds_full + b, (i >> 1) & 1, ab, 0x1400 + i)) break;
+          tc_fence_after();
+          // dQ = dS (128 x MP, K-major) * Kt (MP x D, MN-major view of kt16)
+#pragma unroll
+          for (int k = 0; k < MP / 16; ++k)
+            umma(tmem_base + b * 2 * MP, kdesc(a_ds, k, kTile),
+                 smem_desc_sw128(a_kt + k * 2048, MP * 128, 1024), idesc_dq, k > 0);
+          umma_commit(acc_done + b);
+          if (i + 2 < count) {
+            if (!mbar_wait(o_free + b, (i >> 1) & 1, ab, 0x1380 + i)) break;
+            ok = front(i + 2, b);
+          }
+        }
+      }
+    }
+  } else {
+    const int r = threadIdx.x & 127, h = threadIdx.x >> 7;
+    const int quarter = warp & 3;
+    const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+    const float sc = st_scale[bh];
+    const int c0 = h * HC;
+    Segments sg(sch.N, m);
+    bool alive = true;
+    for (int i = 0; i < count; ++i) {
+      const int b = (MODE == kModeC) ? (i & 1) : 0;
+      const uint32_t ph = (MODE == kModeC) ? ((i >> 1) & 1) : (i & 1);
+      const int64_t row = (int64_t)(tile0 + i) * kTile + r;
+      const bool valid = row < sch.N;
+      const float lse = valid ? lse1[bh * sch.N + row] * kLog2e : 0.f;
+      if (!mbar_wait(sdp_full + b, ph, ab, 0x1600 + i)) { alive = false; break; }
+      __syncwarp();
+      tc_fence_after();
+      float p[HC], g[HC];
+      const uint32_t t_s = tmem_base + b * 2 * MP + lane_base;
+      ld_cols<HC>(t_s + c0, p);
+      ld_cols<HC>(t_s + MP + c0, g);
+      tmem_ld_wait();
+      float d4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int j = 0; j < HC; ++j) {
+        p[j] = (valid && c0 + j < m) ? fast_exp2(p[j] - lse) : 0.f;
+        d4[j & 3] = fmaf(p[j], g[j], d4[j & 3]);
+      }
+      const float dpart = (d4[0] + d4[1]) + (d4[2] + d4[3]);
+      if (MODE == kModeA) {
+        // the previous tile's P / dS are still being read by its accumulation MMAs
+        if (i > 0 && !mbar_wait(acc_done, (i - 1) & 1, ab, 0x1700 + i)) { alive = false; break; }
+        __syncwarp();
+      } else {
+        if (threadIdx.x == 0) tma_store_wait_read();   // staging of the previous dQ tile shares s_ds
+      }
+      s_x[h * kTile + r] = dpart;
+      named_barrier(1, kComputeThreads);
+      const float d1 = dpart + s_x[(h ^ 1) * kTile + r];
+      if (MODE == kModeA) {
+        named_barrier(1, kComputeThreads);   // exchange words live in the head of the P tile
+        store_cols<T, HC>(s_p, r, c0, p);
+      }
+#pragma unroll
+      for (int j = 0; j < HC; ++j) g[j] = p[j] * (g[j] - d1);
+      store_cols<T, HC>(s_ds, r, c0, g);
+      fence_proxy_async();
+      tc_fence_before();
+      mbar_arrive(pds_full + b);
+
+      if (MODE == kModeC) {
+        if (!mbar_wait(acc_done + b, ph, ab, 0x1800 + i)) { alive = false; break; }
+        __syncwarp();
+        tc_fence_after();
+        float o[HD];
+        ld_cols<HD>(tmem_base + b * 2 * MP + lane_base + h * HD, o);
+        tmem_ld_wait();
+        tc_fence_before();
+        mbar_arrive(o_free + b);
+        const int l = valid ? sg.landmark_of(row) : 0;
+        const float4* add = reinterpret_cast<const float4*>(rows_q + (bh * m + l) * D + h * HD);
+        const float mul = sc * kLn2;
+#pragma unroll
+        for (int j = 0; j < HD; j += 4) {
+          const float4 a = add[j >> 2];
+          o[j + 0] = fmaf(o[j + 0], mul, a.x); o[j + 1] = fmaf(o[j + 1], mul, a.y);
+          o[j + 2] = fmaf(o[j + 2], mul, a.z); o[j + 3] = fmaf(o[j + 3], mul, a.w);
+        }
+        // acc_done means the dQ product has finished reading the dS tile: reuse it as staging
+        store_cols<T, HD>(s_ds, r, h * HD, o);
+        fence_proxy_async();
+        named_barrier(1, kComputeThreads);
+        if (threadIdx.x == 0) {
+          for (int kb = 0; kb < KBD; ++kb)
+            tma_store_3d(&tm_dq, s_ds + kb * (kTile * 128), kb * 64, (tile0 + i) * kTile, (int)bh);
+          tma_store_commit();
+        }
+      }
+    }
+    if (MODE == kModeC) {
+      if (threadIdx.x == 0) tma_store_wait_all();
+    } else if (alive && mbar_wait(acc_done, (count - 1) & 1, ab, 0x1900)) {
+      __syncwarp();
+      tc_fence_after();
+      // accumulator row -> TMEM lane: M = 128 uses lane = row; M = 64 keeps 16 rows per 32-lane
+      // quarter in its lanes 0..15
+      const int l = (MP == 128) ? r : (quarter * 16 + lane);
+      const bool owner = (MP == 128) ? true : (lane < 16);
+      float* dst = partA + ((size_t)bh * sch.nchunk + tr.chunk) * 2 * m * D;
+#pragma unroll
+      for (int which = 0; which < 2; ++which) {
+        const float mul = which ? sc * scale : 1.f;
+        float o[HD];
+        ld_cols<HD>(tmem_base + 2 * MP + which * D + lane_base + h * HD, o);
+        tmem_ld_wait();
+        if (owner && l < m) {
+#pragma unroll
+          for (int j = 0; j < HD; j += 4)
+            *reinterpret_cast<float4*>(dst + (size_t)which * m * D + l * D + h * HD + j) =
+                make_float4(o[j] * mul, o[j + 1] * mul, o[j + 2] * mul, o[j + 3] * mul);
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem_base, kTmemCols);
+}
+
+// ------------------------------------------------------------------------------------------
+// Softmax-3 backward (column pass).  Per 128-row tile of K and V (thread = row n, half the
+// landmark columns):
+//   S3^T = K qt16^T (log2 domain), dP3^T = V do3n^T (dO3 normalised by 2^-e, undone by dsc)
+//   P' = 2^k exp(S3 - lse3) , dS' = P' o (dP3 - D3)     (2^k keeps the 16-bit operand copies of
+//                                                         the ~1/N probabilities out of the
+//                                                         subnormal range; undone in FP32)
+//   dV = P' dO3                     -> written once (dO3 read as the MN-major view of do3n)
+//   dK = s dS' Qt + rows_k[l(n)]    -> written once (Qt read as the MN-major view of qt16;
+//                                      rows_k holds s * dKt_tot / len per landmark)
+//   dQt partial += dS'^T (sK)       -> TMEM accumulator over the CTA's tiles
+// K is double-buffered (it is needed until the tile's last product), V single-buffered.
+template <int D, int MP>
+struct BwdBSmem {
+  static constexpr int kOp = MP * D * 2, kVec = 1024, kIn = kTile * D * 2,
+                       kPd = kTile * (MP > D ? MP : D) * 2;
+  static constexpr int kBytes = 2 * kOp + kVec + 3 * kIn + 2 * kPd + 256 + 1024;
+};
+
+template <class T, int D, int MP>
+__global__ void __launch_bounds__(kTcThreads, 2)
+tc_bwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                const __grid_constant__ CUtensorMap tm_qt, const __grid_constant__ CUtensorMap tm_do3,
+                const __grid_constant__ CUtensorMap tm_dk, const __grid_constant__ CUtensorMap tm_dv,
+                const float* __restrict__ lse3, const float* __restrict__ D3,
+                const float* __restrict__ do3_scale, const float* __restrict__ rows_k,
+                float* __restrict__ partB, TcSched sch, int m, float scale, int kshift, int* status) {
+  using L = BwdBSmem<D, MP>;
+  constexpr int KBD = D / 64, HC = MP / 2, HD = D / 2;
+  constexpr int W = MP > D ? MP : D;
+  constexpr uint32_t kCols = 2 * W + D;
+  constexpr uint32_t kTmemCols = kCols <= 256 ? 256 : 512;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* base = align1024(smem_raw);
+  uint8_t* s_qt = base;
+  uint8_t* s_do3 = s_qt + L::kOp;
+  float* s_c3 = reinterpret_cast<float*>(s_do3 + L::kOp);
+  float* s_d3 = s_c3 + MP;
+  uint8_t* s_k = reinterpret_cast<uint8_t*>(s_c3) + L::kVec;   // two stages
+  uint8_t* s_v = s_k + 2 * L::kIn;
+  uint8_t* s_p = s_v + L::kIn;      // P' tile, then staging of the dV tile
+  uint8_t* s_ds = s_p + L::kPd;     // dS' tile, then staging of the dK tile
+  uint64_t* bars = reinterpret_cast<uint64_t*>(s_ds + L::kPd);
+  uint64_t* small_full = bars + 0;
+  uint64_t* k_full = bars + 1;      // [2]
+  uint64_t* k_empty = bars + 3;     // [2]
+  uint64_t* v_full = bars + 5;
+  uint64_t* v_empty = bars + 6;
+  uint64_t* sdp_full = bars + 7;
+  uint64_t* pds_full = bars + 8;
+  uint64_t* out_full = bars + 9;
+  uint64_t* o_free = bars + 10;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+  int* abort_word = reinterpret_cast<int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const TileRange tr = tile_range(sch);
+  const int64_t bh = tr.bh;
+  const int tile0 = tr.tile0, count = tr.count;
+
+  if (threadIdx.x == 0) {
+    mbar_init(small_full, 1);
+    for (int s = 0; s < 2; ++s) { mbar_init(k_full + s, 1); mbar_init(k_empty + s, 1); }
+    mbar_init(v_full, 1); mbar_init(v_empty, 1);
+    mbar_init(sdp_full, 1);
+    mbar_init(pds_full, kComputeThreads);
+    mbar_init(out_full, 1);
+    mbar_init(o_free, kComputeThreads);
+    *abort_word = 0;
+    fence_mbar_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_s = tmem_base, tmem_dp = tmem_base + W, tmem_acc = tmem_base + 2 * W;
+  const uint32_t tmem_dv = tmem_s, tmem_dk = tmem_dp;
+  Abort ab{abort_word, status};
+
+  if (warp == kProducerWarp) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tm_k);
+      tma_prefetch_desc(&tm_v);
+      mbar_expect_tx(small_full, 2 * L::kOp);
+      for (int kb = 0; kb < KBD; ++kb) {
+        tma_load_2d(s_qt + kb * (MP * 128), &tm_qt, small_full, kb * 64, (int)(bh * MP));
+        tma_load_2d(s_do3 + kb * (MP * 128), &tm_do3, small_full, kb * 64, (int)(bh * MP));
+      }
+      int armed = 0;
+      for (int i = 0; i < count; ++i) {
+        const int st = i & 1;
+        if (!mbar_wait(k_empty + st, ((i >> 1) & 1) ^ 1, ab, 0x2100 + i)) break;
+        mbar_expect_tx(k_full + st, L::kIn);
+        for (int kb = 0; kb < KBD; ++kb)
+          tma_load_3d(s_k + st * L::kIn + kb * (kTile * 128), &tm_k, k_full + st, kb * 64, (tile0 + i) * kTile, (int)bh);
+        if (!mbar_wait(v_empty, (i & 1) ^ 1, ab, 0x2180 + i)) { armed = -(i + 1); break; }
+        mbar_expect_tx(v_full, L::kIn);
+        for (int kb = 0; kb < KBD; ++kb)
+          tma_load_3d(s_v + kb * (kTile * 128), &tm_v, v_full, kb * 64, (tile0 + i) * kTile, (int)bh);
+        armed = i + 1;
+      }
+      if (ab.raised()) {
+        const int nk = armed < 0 ? -armed : armed, nv = armed < 0 ? -armed - 1 : armed;
+        for (int i = max(0, nk - 2); i < nk; ++i) mbar_drain(k_full + (i & 1), (i >> 1) & 1);
+        if (nv > 0) mbar_drain(v_full, (nv - 1) & 1);
+      }
+    }
+  } else if (warp == kMmaWarp) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = make_idesc<T>(kTile, MP, false, false);
+      constexpr uint32_t idesc_o = make_idesc<T>(kTile, D, false, true);
+      constexpr uint32_t idesc_acc = make_idesc<T>(MP, D, true, true);
+      const uint32_t a_qt = smem_u32(s_qt), a_do3 = smem_u32(s_do3), a_v = smem_u32(s_v), a_p = smem_u32(s_p),
+                     a_ds = smem_u32(s_ds);
+      bool ok = mbar_wait(small_full, 0, ab, 0x2200);
+      for (int i = 0; ok && i < count; ++i) {
+        const int st = i & 1;
+        const uint32_t a_k = smem_u32(s_k + st * L::kIn);
+        if (!mbar_wait(k_full + st, (i >> 1) & 1, ab, 0x2300 + i)) break;
+        if (!mbar_wait(v_full, i & 1, ab, 0x2340 + i)) break;
+        if (!mbar_wait(o_free, (i & 1) ^ 1, ab, 0x2380 + i)) break;   // dV / dK alias S / dP
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) umma(tmem_s, kdesc(a_k, k, kTile), kdesc(a_qt, k, MP), idesc_s, k > 0);
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) umma(tmem_dp, kdesc(a_v, k, kTile), kdesc(a_do3, k, MP), idesc_s, k > 0);
+        umma_commit(v_empty);
+        umma_commit(sdp_full);
+        if (!mbar_wait(pds_full, i & 1, ab, 0x2400 + i)) break;
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < MP / 16; ++k)
+          umma(tmem_dv, kdesc(a_p, k, kTile), smem_desc_sw128(a_do3 + k * 2048, MP * 128, 1024), idesc_o, k > 0);
+#pragma unroll
+        for (int k = 0; k < MP / 16; ++k)
+          umma(tmem_dk, kdesc(a_ds, k, kTile), smem_desc_sw128(a_qt + k * 2048, MP * 128, 1024), idesc_o, k > 0);
+#pragma unroll
+        for (int k = 0; k < kTile / 16; ++k)
+          umma(tmem_acc, mndesc(a_ds, k), mndesc(a_k, k), idesc_acc, (i > 0 || k > 0));
+        umma_commit(k_empty + st);
+        umma_commit(out_full);
+      }
+    }
+  } else {
+    const int r = threadIdx.x & 127, h = threadIdx.x >> 7;
+    const int quarter = warp & 3;
+    const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+    const float dsc = do3_scale[bh];
+    const float unshift = exp2f(-(float)kshift);
+    const int c0 = h * HC;
+    Segments sg(sch.N, m);
+    if (threadIdx.x < MP) {
+      const int j = threadIdx.x;
+      s_c3[j] = (j < m) ? lse3[bh * m + j] * kLog2e - (float)kshift : INFINITY;
+      s_d3[j] = (j < m) ? D3[bh * m + j] : 0.f;
+    }
+    named_barrier(1, kComputeThreads);
+    bool alive = true;
+    for (int i = 0; i < count; ++i) {
+      const int64_t row = (int64_t)(tile0 + i) * kTile + r;
+      const bool valid = row < sch.N;
+      if (!mbar_wait(sdp_full, i & 1, ab, 0x2600 + i)) { alive = false; break; }
+      __syncwarp();
+      tc_fence_after();
+      float p[HC], g[HC];
+      ld_cols<HC>(tmem_s + lane_base + c0, p);
+      ld_cols<HC>(tmem_dp + lane_base + c0, g);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < HC; j += 4) {
+        const float4 c = *reinterpret_cast<const float4*>(s_c3 + c0 + j);
+        const float4 d = *reinterpret_cast<const float4*>(s_d3 + c0 + j);
+        p[j + 0] = valid ? fast_exp2(p[j + 0] - c.x) : 0.f;
+        p[j + 1] = valid ? fast_exp2(p[j + 1] - c.y) : 0.f;
+        p[j + 2] = valid ? fast_exp2(p[j + 2] - c.z) : 0.f;
+        p[j + 3] = valid ? fast_exp2(p[j + 3] - c.w) : 0.f;
+        g[j + 0] = fminf(fmaxf(p[j + 0] * fmaf(g[j + 0], dsc, -d.x), -60000.f), 60000.f);
+        g[j + 1] = fminf(fmaxf(p[j + 1] * fmaf(g[j + 1], dsc, -d.y), -60000.f), 60000.f);
+        g[j + 2] = fminf(fmaxf(p[j + 2] * fmaf(g[j + 2], dsc, -d.z), -60000.f), 60000.f);
+        g[j + 3] = fminf(fmaxf(p[j + 3] * fmaf(g[j + 3], dsc, -d.w), -60000.f), 60000.f);
+      }
+      // the staging copies of the previous tile's dV / dK share these buffers
+      if (threadIdx.x == 0) tma_store_wait_read();
+      named_barrier(1, kComputeThreads);
+      store_cols<T, HC>(s_p, r, c0, p);
+      store_cols<T, HC>(s_ds, r, c0, g);
+      fence_proxy_async();
+      tc_fence_before();
+      mbar_arrive(pds_full);
+
+      if (!mbar_wait(out_full, i & 1, ab, 0x2800 + i)) { alive = false; break; }
+      __syncwarp();
+      tc_fence_after();
+      float o[HD], o2[HD];
+      ld_cols<HD>(tmem_dv + lane_base + h * HD, o);
+      ld_cols<HD>(tmem_dk + lane_base + h * HD, o2);
+      tmem_ld_wait();
+      tc_fence_before();
+      mbar_arrive(o_free);
+      const int l = valid ? sg.landmark_of(row) : 0;
+      const float4* add = reinterpret_cast<const float4*>(rows_k + (bh * m + l) * D + h * HD);
+      const float vmul = dsc * unshift, kmul = unshift * kLn2;
+#pragma unroll
+      for (int j = 0; j < HD; j += 4) {
+        const float4 a = add[j >> 2];
+        o[j + 0] *= vmul; o[j + 1] *= vmul; o[j + 2] *= vmul; o[j + 3] *= vmul;
+        o2[j + 0] = fmaf(o2[j + 0], kmul, a.x); o2[j + 1] = fmaf(o2[j + 1], kmul, a.y);
+        o2[j + 2] = fmaf(o2[j + 2], kmul, a.z); o2[j + 3] = fmaf(o2[j + 3], kmul, a.w);
+      }
+      // out_full: every product that read the P' / dS' tiles is complete, so they can hold the
+      // outgoing tiles now
+      store_cols<T, HD>(s_p, r, h * HD, o);
+      store_cols<T, HD>(s_ds, r, h * HD, o2);
+      fence_proxy_async();
+      named_barrier(1, kComputeThreads);
+      if (threadIdx.x == 0) {
+        for (int kb = 0; kb < KBD; ++kb) {
+          tma_store_3d(&tm_dv, s_p + kb * (kTile * 128), kb * 64, (tile0 + i) * kTile, (int)bh);
+          tma_store_3d(&tm_dk, s_ds + kb * (kTile * 128), kb * 64, (tile0 + i) * kTile, (int)bh);
+        }
+        tma_store_commit();
+      }
+    }
+    if (threadIdx.x == 0) tma_store_wait_all();
+    if (alive) {
+      // out_full of the last tile was waited above, so the accumulator is final
+      const int l = (MP == 128) ? r : (quarter * 16 + lane);
+      const bool owner = (MP == 128) ? true : (lane < 16);
+      float* dst = partB + ((size_t)bh * sch.nchunk + tr.chunk) * m * D;
+      const float mul = scale * unshift;
+      float o[HD];
+      ld_cols<HD>(tmem_acc + lane_base + h * HD, o);
+      tmem_ld_wait();
+      if (owner && l < m) {
+#pragma unroll
+        for (int j = 0; j < HD; j += 4)
+          *reinterpret_cast<float4*>(dst + l * D + h * HD + j) =
+              make_float4(o[j] * mul, o[j + 1] * mul, o[j + 2] * mul, o[j + 3] * mul);
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem_base, kTmemCols);
+}
+
+// ------------------------------------------------------------------------------------------
+// Softmax-3 forward (column pass): per-CTA partial of Bmat = softmax(Qt (sK)^T) V with a running
+// reference exponent per landmark.  Thread = row n of the K/V tile and half the landmark columns,
+// so the per-landmark maximum over the tile is a reduction across threads: 31 warp shuffles per
+// thread fold the 32 rows of a warp, shared memory folds the 4 row quarters.  The reference only
+// moves when a tile exceeds it by more than 2^8 (then the TMEM accumulators are rescaled in
+// place), so probabilities stay <= 256 in the 16-bit operand copy and rescales are rare.  Row
+// sums come from the tensor core too (P'^T times a block of ones).  S is double-buffered in
+// TMEM, K and V have separate two-stage rings (K is free after the score product, V after the
+// accumulation).
+template <int D, int MP>
+struct FwdBSmem {
+  static constexpr int kQt = MP * D * 2, kOnes = 2048, kIn = kTile * D * 2, kP = kTile * MP * 2,
+                       kAux = 1024 * ((7 * MP * 4 + 64 + 1023) / 1024);
+  static constexpr int kBytes = kQt + kOnes + 4 * kIn + kP + kAux + 256 + 1024;
+};
+
+template <class T, int D, int MP>
+__global__ void __launch_bounds__(kTcThreads, 2)
+tc_fwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                const __grid_constant__ CUtensorMap tm_qt, float* __restrict__ part_acc,
+                float* __restrict__ part_max, float* __restrict__ part_sum, TcSched sch, int m,
+                int* status) {
+  using L = FwdBSmem<D, MP>;
+  constexpr int KBD = D / 64, HC = MP / 2;
+  constexpr int CPL = HC / 32;                 // columns per lane after the warp fold
+  constexpr int NCK = (D + 32) / 32;           // 32-column chunks of accumulator + row sums
+  constexpr uint32_t kCols = 2 * MP + D + 32;
+  constexpr uint32_t kTmemCols = kCols <= 256 ? 256 : 512;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* base = align1024(smem_raw);
+  uint8_t* s_qt = base;
+  uint8_t* s_ones = s_qt + L::kQt;
+  uint8_t* s_k = s_ones + L::kOnes;            // two stages
+  uint8_t* s_v = s_k + 2 * L::kIn;             // two stages
+  uint8_t* s_p = s_v + 2 * L::kIn;
+  float* s_wmax = reinterpret_cast<float*>(s_p + L::kP);   // [4][MP]
+  float* s_ref = s_wmax + 4 * MP;                          // [MP] running reference (log2 domain)
+  float* s_fac = s_ref + MP;                               // [MP] rescale factor of this tile
+  float* s_new = s_fac + MP;                               // [MP] scratch
+  int* s_flag = reinterpret_cast<int*>(s_new + MP);        // [3], rotating
+  uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(s_wmax) + L::kAux);
+  uint64_t* small_full = bars + 0;
+  uint64_t* k_full = bars + 1;      // [2]
+  uint64_t* k_empty = bars + 3;     // [2]
+  uint64_t* v_full = bars + 5;      // [2]
+  uint64_t* v_empty = bars + 7;     // [2]
+  uint64_t* s_full = bars + 9;      // [2]
+  uint64_t* p_full = bars + 11;
+  uint64_t* acc_done = bars + 12;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+  int* abort_word = reinterpret_cast<int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const TileRange tr = tile_range(sch);
+  const int64_t bh = tr.bh;
+  const int tile0 = tr.tile0, count = tr.count;
+
+  if (threadIdx.x == 0) {
+    mbar_init(small_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(k_full + s, 1); mbar_init(k_empty + s, 1); mbar_init(v_full + s, 1); mbar_init(v_empty + s, 1);
+      mbar_init(s_full + s, 1);
+    }
+    mbar_init(p_full, kComputeThreads);
+    mbar_init(acc_done, 1);
+    *abort_word = 0;
+    s_flag[0] = 0; s_flag[1] = 0; s_flag[2] = 0;
+    fence_mbar_init();
+  }
+  // block of 16-bit ones read by the row-sum MMA (any operand layout reads all-ones from it)
+  for (int idx = threadIdx.x; idx < L::kOnes / 4; idx += kTcThreads)
+    reinterpret_cast<uint32_t*>(s_ones)[idx] = pack2<T>(1.f, 1.f);
+  fence_proxy_async();
+  if (warp == 0) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_acc = tmem_base + 2 * MP;   // D accumulator columns, then 32 for the row sums
+  Abort ab{abort_word, status};
+
+  if (warp == kProducerWarp) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tm_k);
+      tma_prefetch_desc(&tm_v);
+      mbar_expect_tx(small_full, L::kQt);
+      for (int kb = 0; kb < KBD; ++kb)
+        tma_load_2d(s_qt + kb * (MP * 128), &tm_qt, small_full, kb * 64, (int)(bh * MP));
+      int nk = 0, nv = 0;
+      for (int i = 0; i < count; ++i) {
+        const int st = i & 1;
+        if (!mbar_wait(k_empty + st, ((i >> 1) & 1) ^ 1, ab, 0x3100 + i)) break;
+        mbar_expect_tx(k_full + st, L::kIn);
+        for (int kb = 0; kb < KBD; ++kb)
+          tma_load_3d(s_k + st * L::kIn + kb * (kTile * 128), &tm_k, k_full + st, kb * 64, (tile0 + i) * kTile, (int)bh);
+        nk = i + 1;
+        if (!mbar_wait(v_empty + st, ((i >> 1) & 1) ^ 1, ab, 0x3180 + i)) break;
+        mbar_expect_tx(v_full + st, L::kIn);
+        for (int kb = 0; kb < KBD; ++kb)
+          tma_load_3d(s_v + st * L::kIn + kb * (kTile * 128), &tm_v, v_full + st, kb * 64, (tile0 + i) * kTile, (int)bh);
+        nv = i + 1;
+      }
+      if (ab.raised()) {
+        for (int i = max(0, nk - 2); i < nk; ++i) mbar_drain(k_full + (i & 1), (i >> 1) & 1);
+        for (int i = max(0, nv - 2); i < nv; ++i) mbar_drain(v_full + (i & 1), (i >> 1) & 1);
+      }
+    }
+  } else if (warp == kMmaWarp) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = make_idesc<T>(kTile, MP, false, false);
+      constexpr uint32_t idesc_acc = make_idesc<T>(MP, D, true, true);
+      constexpr uint32_t idesc_sum = make_idesc<T>(MP, 16, true, false);
+      const uint32_t a_qt = smem_u32(s_qt), a_p = smem_u32(s_p), a_ones = smem_u32(s_ones);
+      auto front = [&](int i) -> bool {
+        const int st = i & 1;
+        if (!mbar_wait(k_full + st, (i >> 1) & 1, ab, 0x3300 + i)) return false;
+        tc_fence_after();
+        const uint32_t a_k = smem_u32(s_k + st * L::kIn);
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k)
+          umma(tmem_base + st * MP, kdesc(a_k, k, kTile), kdesc(a_qt, k, MP), idesc_s, k > 0);
+        umma_commit(k_empty + st);
+        umma_commit(s_full + st);
+        return true;
+      };
+      bool ok = mbar_wait(small_full, 0, ab, 0x3200);
+      ok = ok && front(0);
+      if (ok && count > 1) ok = front(1);
+      for (int i = 0; ok && i < count; ++i) {
+        const int st = i & 1;
+        if (!mbar_wait(p_full, i & 1, ab, 0x3400 + i)) break;
+        if (!mbar_wait(v_full + st, (i >> 1) & 1, ab, 0x3480 + i)) break;
+        tc_fence_after();
+        const uint32_t a_v = smem_u32(s_v + st * L::kIn);
+#pragma unroll
+        for (int k = 0; k < kTile / 16; ++k)
+          umma(tmem_acc, mndesc(a_p, k), mndesc(a_v, k), idesc_acc, (i > 0 || k > 0));
+#pragma unroll
+        for (int k = 0; k < kTile / 16; ++k)
+          umma(tmem_acc + D, mndesc(a_p, k), smem_desc_sw128(a_ones + (k & 3) * 32, 16, 1024), idesc_sum,
+               (i > 0 || k > 0));
+        umma_commit(v_empty + st);
+        umma_commit(acc_done);
+        if (i + 2 < count) ok = front(i + 2);
+      }
+    }
+  } else {
+    const int r = threadIdx.x & 127, h = threadIdx.x >> 7;
+    const int quarter = warp & 3;
+    const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+    const int c0 = h * HC;
+    const int lrow = (MP == 128) ? r : (quarter * 16 + lane);          // accumulator row of this lane
+    const bool owner = (MP == 128) ? true : (lane < 16);
+    if (threadIdx.x < MP) s_ref[threadIdx.x] = -INFINITY;
+    bool alive = true;
+    for (int i = 0; i < count; ++i) {
+      const int st = i & 1;
+      const int64_t row = (int64_t)(tile0 + i) * kTile + r;
+      const bool valid = row < sch.N;
+      if (!mbar_wait(s_full + st, (i >> 1) & 1, ab, 0x3600 + i)) { alive = false; break; }
+      __syncwarp();
+      tc_fence_after();
+      float s[HC], v[HC];
+      ld_cols<HC>(tmem_base + st * MP + lane_base + c0, s);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < HC; ++j) { s[j] = valid ? s[j] : -INFINITY; v[j] = s[j]; }
+      // fold the 32 rows of this warp: afterwards lane L holds columns c0 + CPL*L .. +CPL-1
+#pragma unroll
+      for (int off = 16, cnt = HC / 2; off >= 1; off >>= 1, cnt >>= 1) {
+        const bool upper = (lane & off) != 0;
+#pragma unroll
+        for (int j = 0; j < cnt; ++j) {
+          const float send = upper ? v[j] : v[j + cnt];
+          const float keep = upper ? v[j + cnt] : v[j];
+          v[j] = fmaxf(keep, __shfl_xor_sync(0xffffffffu, send, off));
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < CPL; ++j) s_wmax[quarter * MP + c0 + CPL * lane + j] = v[j];
+      if (threadIdx.x == 0) s_flag[(i + 1) % 3] = 0;   // last read two tiles ago
+      named_barrier(1, kComputeThreads);
+      if (threadIdx.x < MP) {
+        const int c = threadIdx.x;
+        const float tmax = fmaxf(fmaxf(s_wmax[c], s_wmax[MP + c]), fmaxf(s_wmax[2 * MP + c], s_wmax[3 * MP + c]));
+        const float old = s_ref[c];
+        s_new[c] = fmaxf(old, tmax);
+        if (c < m && tmax > old + 8.f) s_flag[i % 3] = 1;
+      }
+      named_barrier(1, kComputeThreads);
+      const bool move = s_flag[i % 3] != 0;     // CTA-uniform
+      if (i > 0) {
+        // previous tile's accumulation still reads the P' tile and writes the accumulators
+        if (!mbar_wait(acc_done, (i - 1) & 1, ab, 0x3700 + i)) { alive = false; break; }
+        __syncwarp();
+        tc_fence_after();
+      }
+      if (move) {
+        if (threadIdx.x < MP) {
+          const int c = threadIdx.x;
+          const float old = s_ref[c], nw = s_new[c];
+          s_fac[c] = (old == -INFINITY) ? 0.f : fast_exp2(old - nw);
+          s_ref[c] = nw;
+        }
+        named_barrier(1, kComputeThreads);
+        if (i > 0) {
+          const float f = s_fac[owner ? lrow : 0];
+#pragma unroll
+          for (int ck = 0; ck < NCK; ++ck) {
+            if ((ck & 1) == h) {
+              float o[32];
+              tmem_ld32(tmem_acc + lane_base + ck * 32, o);
+              tmem_ld_wait();
+#pragma unroll
+              for (int j = 0; j < 32; ++j) o[j] *= f;
+              tmem_st32(tmem_acc + lane_base + ck * 32, o);
+            }
+          }
+          tmem_st_wait();
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < HC; j += 4) {
+        const float4 c = *reinterpret_cast<const float4*>(s_ref + c0 + j);
+        s[j + 0] = fast_exp2(s[j + 0] - c.x);
+        s[j + 1] = fast_exp2(s[j + 1] - c.y);
+        s[j + 2] = fast_exp2(s[j + 2] - c.z);
+        s[j + 3] = fast_exp2(s[j + 3] - c.w);
+      }
+      store_cols<T, HC>(s_p, r, c0, s);
+      fence_proxy_async();
+      tc_fence_before();
+      mbar_arrive(p_full);
+    }
+    if (alive && mbar_wait(acc_done, (count - 1) & 1, ab, 0x3900)) {
+      __syncwarp();
+      tc_fence_after();
+      const size_t slot = (size_t)bh * sch.nchunk + tr.chunk;
+      float* dst = part_acc + slot * m * D;
+#pragma unroll
+      for (int ck = 0; ck < NCK; ++ck) {
+        if ((ck & 1) == h) {
+          float o[32];
+          tmem_ld32(tmem_acc + lane_base + ck * 32, o);
+          tmem_ld_wait();
+          if (owner && lrow < m) {
+            if (ck < D / 32) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4)
+                *reinterpret_cast<float4*>(dst + lrow * D + ck * 32 + j) = make_float4(o[j], o[j + 1], o[j + 2], o[j + 3]);
+            } else {
+              part_sum[slot * m + lrow] = o[0];
+              part_max[slot * m + lrow] = s_ref[lrow] * kLn2;
+            }
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem_base, kTmemCols);
+}
+
+}  // namespace tc
+}  // namespace fnb

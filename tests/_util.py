@@ -15,6 +15,8 @@ def run_cuda(q, k, v, dO, m, J, kappa=0.0, device="cuda"):
              "iterates", "K2", "bmat"]
     d = {n: t for n, t in zip(names, res)}
     d.update(dq=grads[0], dk=grads[1], dv=grads[2])
+    torch.cuda.synchronize()
+    _C.check_device_status()   # a bounded device-side wait that expired fails the test
     return d
 
 
