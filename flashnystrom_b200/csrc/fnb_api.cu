@@ -17,6 +17,7 @@
 #include "tc_host.cuh"
 #include "ns_kernels.cuh"
 #include <type_traits>
+#include <algorithm>
 
 namespace fnb {
 
@@ -93,6 +94,44 @@ struct Launcher {
     }
     return 0;
   }
+};
+
+// Side stream for work that can run beside the caller's stream inside one call.  One side stream
+// and two events per host thread and device, created on first use and kept for the life of the
+// thread; fork/join are event record + wait pairs, so a caller capturing its stream into a CUDA
+// graph captures the fork as well.
+struct SideStream {
+  int device = -1;
+  cudaStream_t stream = nullptr;
+  cudaEvent_t fork = nullptr, join = nullptr;
+  bool get(int dev) {
+    if (dev == device && stream) return true;
+    if (stream) { cudaStreamDestroy(stream); cudaEventDestroy(fork); cudaEventDestroy(join); stream = nullptr; }
+    if (cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking) != cudaSuccess) { stream = nullptr; return false; }
+    cudaEventCreateWithFlags(&fork, cudaEventDisableTiming);
+    cudaEventCreateWithFlags(&join, cudaEventDisableTiming);
+    device = dev;
+    return true;
+  }
+};
+static thread_local SideStream g_side;
+
+struct Fork {
+  cudaStream_t main;
+  bool enabled, forked = false;
+  Fork(cudaStream_t st, int dev, bool want) : main(st), enabled(want && g_side.get(dev)) {}
+  cudaStream_t begin() {            // work launched on the returned stream runs beside `main`
+    if (!enabled) return main;
+    cudaEventRecord(g_side.fork, main);
+    cudaStreamWaitEvent(g_side.stream, g_side.fork, 0);
+    forked = true;
+    return g_side.stream;
+  }
+  void end() { if (forked) cudaEventRecord(g_side.join, g_side.stream); }
+  void join() {                     // `main` waits for the side work
+    if (forked) { cudaStreamWaitEvent(main, g_side.join, 0); forked = false; }
+  }
+  ~Fork() { join(); }
 };
 
 template <class K>
@@ -224,7 +263,7 @@ static Plan plan_of(const fnb_shape& s) {
 // output row pass.
 template <class T>
 static int forward_impl(const fnb_fwd_args& a, const Plan& p, const FwdWs& w, int max_smem, int sms,
-                        cudaStream_t st) {
+                        cudaStream_t st, bool allow_inner_fork) {
   Launcher L(st, a.device);
   const float scale = powf((float)p.D, -0.25f);
   constexpr bool k16 = !std::is_same<T, float>::value;
@@ -241,30 +280,41 @@ static int forward_impl(const fnb_fwd_args& a, const Plan& p, const FwdWs& w, in
   }
   if (L.end("landmark_partial")) return L.status;
 
-  L.begin();
-  {
-    MidFwdParams mp;
-    mp.land_partial = w.land_partial; mp.C = p.lm_chunks;
-    mp.qt = a.q_landmarks; mp.kt = a.k_landmarks; mp.k2 = a.k2; mp.lse2 = a.lse2;
-    mp.iterates = a.ns_iterates; mp.k2inv = a.k2_inv; mp.scratch = w.pinv;
-    mp.BH = p.BH; mp.N = p.N; mp.m = p.m; mp.D = p.D; mp.J = p.J;
-    mp.kappa = a.shape.kappa_star; mp.scale = scale;
-    mp.landmarks_only = smem_ns ? 1 : 0;
-    mp.qt16 = use_tc ? w.qt16 : nullptr; mp.dtype = a.shape.dtype; mp.MP = MP;
-    mp.qt16_mul = scale * tc::kLog2e;
-    mid_fwd_kernel<<<(unsigned)p.BH, kThreads, 0, st>>>(mp);
-  }
-  if (L.end("mid_fwd")) return L.status;
-
+  Fork fork(st, a.device, smem_ns && !L.prof && allow_inner_fork);   // side stream for the pseudoinverse (off while profiling)
   if (smem_ns) {
+    L.begin();
+    {
+      LandmarkFinalizeParams lp;
+      lp.land_partial = w.land_partial; lp.C = p.lm_chunks; lp.qt = a.q_landmarks; lp.kt = a.k_landmarks;
+      lp.BH = p.BH; lp.N = p.N; lp.m = p.m; lp.D = p.D; lp.scale = scale;
+      lp.qt16 = use_tc ? w.qt16 : nullptr; lp.dtype = a.shape.dtype; lp.MP = MP; lp.qt16_mul = scale * tc::kLog2e;
+      landmark_finalize_kernel<<<dim3((unsigned)p.BH, 8), kThreads, 0, st>>>(lp);
+    }
+    if (L.end("landmark_finalize")) return L.status;
+    // The pseudoinverse only feeds the combine step, so it runs beside the column pass.
+    cudaStream_t ns_stream = fork.begin();
     L.begin();
     ns::NsFwdParams np;
     np.qt = a.q_landmarks; np.kt = a.k_landmarks; np.k2 = a.k2; np.lse2 = a.lse2;
     np.iterates = a.ns_iterates; np.k2inv = a.k2_inv; np.m = p.m; np.D = p.D; np.J = p.J;
     np.kappa = a.shape.kappa_star;
     if (int rc = set_smem(ns::ns_fwd_kernel, ns::kFwdSmem, max_smem, "ns_fwd")) return rc;
-    ns::ns_fwd_kernel<<<(unsigned)p.BH, kThreads, ns::kFwdSmem, st>>>(np);
+    ns::ns_fwd_kernel<<<(unsigned)p.BH, kThreads, ns::kFwdSmem, ns_stream>>>(np);
     if (L.end("ns_fwd")) return L.status;
+    fork.end();
+  } else {
+    L.begin();
+    MidFwdParams mp;
+    mp.land_partial = w.land_partial; mp.C = p.lm_chunks;
+    mp.qt = a.q_landmarks; mp.kt = a.k_landmarks; mp.k2 = a.k2; mp.lse2 = a.lse2;
+    mp.iterates = a.ns_iterates; mp.k2inv = a.k2_inv; mp.scratch = w.pinv;
+    mp.BH = p.BH; mp.N = p.N; mp.m = p.m; mp.D = p.D; mp.J = p.J;
+    mp.kappa = a.shape.kappa_star; mp.scale = scale;
+    mp.landmarks_only = 0;
+    mp.qt16 = use_tc ? w.qt16 : nullptr; mp.dtype = a.shape.dtype; mp.MP = MP;
+    mp.qt16_mul = scale * tc::kLog2e;
+    mid_fwd_kernel<<<(unsigned)p.BH, kThreads, 0, st>>>(mp);
+    if (L.end("mid_fwd")) return L.status;
   }
 
   StreamParams sp;
@@ -303,6 +353,7 @@ static int forward_impl(const fnb_fwd_args& a, const Plan& p, const FwdWs& w, in
     if (L.end("gen_fwd_b")) return L.status;
   }
 
+  fork.join();
   L.begin();
   {
     Combine2Params cp;
@@ -522,6 +573,116 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
   return 0;
 }
 
+
+// ---- (b,h) group pipelining ------------------------------------------------------------------
+// Slices are independent, so one call may be cut into groups of consecutive slices that run the
+// whole kernel chain on alternating streams: while one group sits in its landmark-sized,
+// latency-bound kernels (one CTA per slice), the other group's streaming passes fill the SMs.
+// Measured on B200 at BH = 16, N = 65536: two groups are slower than one (each streaming kernel is
+// sized to fill every SM in one wave, so two of them collide, and a 209 KB pseudoinverse CTA
+// cannot share an SM with streaming CTAs), so grouping is off; the mechanism stays for shapes
+// where the landmark-sized kernels dominate.
+constexpr int kMaxGroups = 1;
+static int group_count(int64_t BH) { return (kMaxGroups > 1 && BH >= 8) ? kMaxGroups : 1; }
+static int64_t group_size(int64_t BH) { int G = group_count(BH); return (BH + G - 1) / G; }
+static Plan group_plan(const fnb_shape& s, int64_t bh) {
+  return make_plan(bh, s.seq_len, s.head_dim, s.num_landmarks, s.newton_iter);
+}
+static size_t esize(int dtype) { return dtype == FNB_F32 ? 4 : 2; }
+template <class P> static P* off(P* p, size_t elems) { return p ? p + elems : p; }
+static const void* offb(const void* p, size_t bytes) { return p ? (const char*)p + bytes : p; }
+static void* offb(void* p, size_t bytes) { return p ? (char*)p + bytes : p; }
+
+static fnb_fwd_args fwd_group(const fnb_fwd_args& a, int64_t bh0, int64_t n, void* ws, size_t ws_bytes) {
+  fnb_fwd_args g = a;
+  const fnb_shape& s = a.shape;
+  const size_t nd = (size_t)s.seq_len * s.head_dim, md = (size_t)s.num_landmarks * s.head_dim,
+               mm = (size_t)s.num_landmarks * s.num_landmarks, es = esize(s.dtype);
+  g.shape.batch = n; g.shape.heads = 1;
+  g.q = offb(a.q, bh0 * nd * es); g.k = offb(a.k, bh0 * nd * es); g.v = offb(a.v, bh0 * nd * es);
+  g.out = offb(a.out, bh0 * nd * es);
+  g.lse1 = off(a.lse1, bh0 * (size_t)s.seq_len);
+  g.q_landmarks = off(a.q_landmarks, bh0 * md); g.k_landmarks = off(a.k_landmarks, bh0 * md);
+  g.k2 = off(a.k2, bh0 * mm); g.lse2 = off(a.lse2, bh0 * (size_t)s.num_landmarks);
+  g.ns_iterates = off(a.ns_iterates, bh0 * mm * (s.newton_iter + 1));
+  g.k2_inv = off(a.k2_inv, bh0 * mm); g.bmat = off(a.bmat, bh0 * md);
+  g.lse3 = off(a.lse3, bh0 * (size_t)s.num_landmarks); g.step2 = off(a.step2, bh0 * md);
+  g.workspace = ws; g.workspace_bytes = ws_bytes;
+  return g;
+}
+static fnb_bwd_args bwd_group(const fnb_bwd_args& a, int64_t bh0, int64_t n, void* ws, size_t ws_bytes) {
+  fnb_bwd_args g = a;
+  const fnb_shape& s = a.shape;
+  const size_t nd = (size_t)s.seq_len * s.head_dim, md = (size_t)s.num_landmarks * s.head_dim,
+               mm = (size_t)s.num_landmarks * s.num_landmarks, es = esize(s.dtype);
+  g.shape.batch = n; g.shape.heads = 1;
+  g.q = offb(a.q, bh0 * nd * es); g.k = offb(a.k, bh0 * nd * es); g.v = offb(a.v, bh0 * nd * es);
+  g.d_out = offb(a.d_out, bh0 * nd * es);
+  g.dq = offb(a.dq, bh0 * nd * es); g.dk = offb(a.dk, bh0 * nd * es); g.dv = offb(a.dv, bh0 * nd * es);
+  g.lse1 = off(a.lse1, bh0 * (size_t)s.seq_len);
+  g.q_landmarks = off(a.q_landmarks, bh0 * md); g.k_landmarks = off(a.k_landmarks, bh0 * md);
+  g.k2 = off(a.k2, bh0 * mm); g.ns_iterates = off(a.ns_iterates, bh0 * mm * (s.newton_iter + 1));
+  g.k2_inv = off(a.k2_inv, bh0 * mm); g.bmat = off(a.bmat, bh0 * md);
+  g.lse3 = off(a.lse3, bh0 * (size_t)s.num_landmarks); g.step2 = off(a.step2, bh0 * md);
+  g.workspace = ws; g.workspace_bytes = ws_bytes;
+  return g;
+}
+
+template <class T>
+static int forward_groups(const fnb_fwd_args& a, int max_smem, int sms, cudaStream_t st) {
+  const int64_t BH = a.shape.batch * a.shape.heads;
+  const int G = g_profile ? 1 : group_count(BH);
+  const int64_t per = G == 1 ? BH : group_size(BH);
+  const size_t sub = carve_fwd(group_plan(a.shape, per), nullptr).bytes;
+  Fork fork(st, a.device, G > 1);
+  int rc = 0;
+  for (int g = 0; g < G && rc == 0; ++g) {
+    const int64_t bh0 = g * per, n = std::min<int64_t>(per, BH - bh0);
+    if (n <= 0) break;
+    fnb_fwd_args ga = fwd_group(a, bh0, n, (char*)a.workspace + g * sub, sub);
+    Plan p = group_plan(a.shape, n);
+    FwdWs w = carve_fwd(p, ga.workspace);
+    cudaStream_t s = (g & 1) ? fork.begin() : st;
+    rc = forward_impl<T>(ga, p, w, max_smem, sms, s, /*allow_inner_fork=*/G == 1);
+    if (g & 1) fork.end();
+  }
+  fork.join();
+  return rc;
+}
+template <class T>
+static int backward_groups(const fnb_bwd_args& a, int max_smem, int sms, cudaStream_t st) {
+  const int64_t BH = a.shape.batch * a.shape.heads;
+  const int G = g_profile ? 1 : group_count(BH);
+  const int64_t per = G == 1 ? BH : group_size(BH);
+  const size_t sub = carve_bwd(group_plan(a.shape, per), nullptr).bytes;
+  Fork fork(st, a.device, G > 1);
+  int rc = 0;
+  for (int g = 0; g < G && rc == 0; ++g) {
+    const int64_t bh0 = g * per, n = std::min<int64_t>(per, BH - bh0);
+    if (n <= 0) break;
+    fnb_bwd_args ga = bwd_group(a, bh0, n, (char*)a.workspace + g * sub, sub);
+    Plan p = group_plan(a.shape, n);
+    BwdWs w = carve_bwd(p, ga.workspace);
+    cudaStream_t s = (g & 1) ? fork.begin() : st;
+    rc = backward_impl<T>(ga, p, w, max_smem, sms, s);
+    if (g & 1) fork.end();
+  }
+  fork.join();
+  return rc;
+}
+static size_t fwd_ws_total(const fnb_shape& s) {
+  const int64_t BH = s.batch * s.heads;
+  const size_t whole = carve_fwd(group_plan(s, BH), nullptr).bytes;
+  const size_t grouped = group_count(BH) * carve_fwd(group_plan(s, group_size(BH)), nullptr).bytes;
+  return whole > grouped ? whole : grouped;
+}
+static size_t bwd_ws_total(const fnb_shape& s) {
+  const int64_t BH = s.batch * s.heads;
+  const size_t whole = carve_bwd(group_plan(s, BH), nullptr).bytes;
+  const size_t grouped = group_count(BH) * carve_bwd(group_plan(s, group_size(BH)), nullptr).bytes;
+  return whole > grouped ? whole : grouped;
+}
+
 }  // namespace fnb
 
 using namespace fnb;
@@ -553,11 +714,11 @@ int fnb_check_shape(const fnb_shape* shape) { return check_shape(shape); }
 
 size_t fnb_fwd_workspace_bytes(const fnb_shape* shape) {
   if (check_shape(shape)) return 0;
-  return carve_fwd(plan_of(*shape), nullptr).bytes;
+  return fwd_ws_total(*shape);
 }
 size_t fnb_bwd_workspace_bytes(const fnb_shape* shape) {
   if (check_shape(shape)) return 0;
-  return carve_bwd(plan_of(*shape), nullptr).bytes;
+  return bwd_ws_total(*shape);
 }
 
 int fnb_forward(const fnb_fwd_args* a) {
@@ -571,20 +732,19 @@ int fnb_forward(const fnb_fwd_args* a) {
                          a->k2_inv, a->bmat, a->lse3, a->step2};
   for (const void* ptr : small)
     if (!ptr) return fail(FNB_ERR_INVALID_ARGUMENT, "a saved-tensor output pointer is NULL");
-  Plan p = plan_of(a->shape);
-  FwdWs w = carve_fwd(p, a->workspace);
-  if (!a->workspace || a->workspace_bytes < w.bytes || (reinterpret_cast<uintptr_t>(a->workspace) & 255u))
+  const size_t need = fwd_ws_total(a->shape);
+  if (!a->workspace || a->workspace_bytes < need || (reinterpret_cast<uintptr_t>(a->workspace) & 255u))
     return fail(FNB_ERR_WORKSPACE, "forward workspace must be 256-byte aligned and >= %zu bytes (got %zu)",
-                w.bytes, a->workspace_bytes);
+                need, a->workspace_bytes);
   DeviceGuard g(a->device);
   if (!g.ok) return fail(FNB_ERR_CUDA, "cannot select CUDA device %d", a->device);
   int max_smem = 0, cc = 0, sms = 0;
   if (int rc = device_limits(a->device, &max_smem, &cc, &sms)) return rc;
   cudaStream_t st = (cudaStream_t)a->stream;
   switch (a->shape.dtype) {
-    case FNB_F32: return forward_impl<float>(*a, p, w, max_smem, sms, st);
-    case FNB_F16: return forward_impl<__half>(*a, p, w, max_smem, sms, st);
-    default: return forward_impl<__nv_bfloat16>(*a, p, w, max_smem, sms, st);
+    case FNB_F32: return forward_groups<float>(*a, max_smem, sms, st);
+    case FNB_F16: return forward_groups<__half>(*a, max_smem, sms, st);
+    default: return forward_groups<__nv_bfloat16>(*a, max_smem, sms, st);
   }
 }
 
@@ -599,20 +759,19 @@ int fnb_backward(const fnb_bwd_args* a) {
                          a->bmat, a->lse3, a->step2};
   for (const void* ptr : small)
     if (!ptr) return fail(FNB_ERR_INVALID_ARGUMENT, "a saved-tensor input pointer is NULL");
-  Plan p = plan_of(a->shape);
-  BwdWs w = carve_bwd(p, a->workspace);
-  if (!a->workspace || a->workspace_bytes < w.bytes || (reinterpret_cast<uintptr_t>(a->workspace) & 255u))
+  const size_t need = bwd_ws_total(a->shape);
+  if (!a->workspace || a->workspace_bytes < need || (reinterpret_cast<uintptr_t>(a->workspace) & 255u))
     return fail(FNB_ERR_WORKSPACE, "backward workspace must be 256-byte aligned and >= %zu bytes (got %zu)",
-                w.bytes, a->workspace_bytes);
+                need, a->workspace_bytes);
   DeviceGuard g(a->device);
   if (!g.ok) return fail(FNB_ERR_CUDA, "cannot select CUDA device %d", a->device);
   int max_smem = 0, cc = 0, sms = 0;
   if (int rc = device_limits(a->device, &max_smem, &cc, &sms)) return rc;
   cudaStream_t st = (cudaStream_t)a->stream;
   switch (a->shape.dtype) {
-    case FNB_F32: return backward_impl<float>(*a, p, w, max_smem, sms, st);
-    case FNB_F16: return backward_impl<__half>(*a, p, w, max_smem, sms, st);
-    default: return backward_impl<__nv_bfloat16>(*a, p, w, max_smem, sms, st);
+    case FNB_F32: return backward_groups<float>(*a, max_smem, sms, st);
+    case FNB_F16: return backward_groups<__half>(*a, max_smem, sms, st);
+    default: return backward_groups<__nv_bfloat16>(*a, max_smem, sms, st);
   }
 }
 

@@ -22,14 +22,22 @@ enum { NN = 0, NT = 1, TN = 2 };
 //   TN: C = A^T B    rows 4ty+i,  cols 4tx+j
 // epi(r, c, acc) is called once per owned element after a barrier, so outputs may alias inputs;
 // a second barrier follows the stores.
+// Packed FP32 FMA (two independent IEEE fused multiply-adds per instruction on sm_100).
+__device__ __forceinline__ void fma2(float2& acc, float a, float2 b) {
+  acc = __ffma2_rn(make_float2(a, a), b, acc);
+}
+__device__ __forceinline__ void fma2v(float2& acc, float2 a, float2 b) { acc = __ffma2_rn(a, b, acc); }
+
 template <int MODE, class Epi>
 __device__ __forceinline__ void mm(const float* __restrict__ A, const float* __restrict__ B, Epi epi) {
   const int t = threadIdx.x, tx = t & 15, ty = t >> 4;
-  float acc[4][4];
+  // NN / TN: acc[i][0] = columns (0,1), acc[i][1] = columns (2,3) of the 4x4 tile.
+  // NT: acc[i][j] holds the even-k and odd-k partial sums of element (i, j).
+  float2 acc[4][4];
 #pragma unroll
   for (int i = 0; i < 4; ++i)
 #pragma unroll
-    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+    for (int j = 0; j < 4; ++j) acc[i][j] = make_float2(0.f, 0.f);
   if (MODE == NN) {
 #pragma unroll 4
     for (int k = 0; k < kN; k += 4) {
@@ -43,10 +51,8 @@ __device__ __forceinline__ void mm(const float* __restrict__ A, const float* __r
         const float av[4] = {a[i].x, a[i].y, a[i].z, a[i].w};
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) {
-          acc[i][0] = fmaf(av[kk], b[kk].x, acc[i][0]);
-          acc[i][1] = fmaf(av[kk], b[kk].y, acc[i][1]);
-          acc[i][2] = fmaf(av[kk], b[kk].z, acc[i][2]);
-          acc[i][3] = fmaf(av[kk], b[kk].w, acc[i][3]);
+          fma2(acc[i][0], av[kk], make_float2(b[kk].x, b[kk].y));
+          fma2(acc[i][1], av[kk], make_float2(b[kk].z, b[kk].w));
         }
       }
     }
@@ -62,10 +68,8 @@ __device__ __forceinline__ void mm(const float* __restrict__ A, const float* __r
       for (int i = 0; i < 4; ++i)
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          acc[i][j] = fmaf(a[i].x, b[j].x, acc[i][j]);
-          acc[i][j] = fmaf(a[i].y, b[j].y, acc[i][j]);
-          acc[i][j] = fmaf(a[i].z, b[j].z, acc[i][j]);
-          acc[i][j] = fmaf(a[i].w, b[j].w, acc[i][j]);
+          fma2v(acc[i][j], make_float2(a[i].x, a[i].y), make_float2(b[j].x, b[j].y));
+          fma2v(acc[i][j], make_float2(a[i].z, a[i].w), make_float2(b[j].z, b[j].w));
         }
     }
   } else {
@@ -76,10 +80,8 @@ __device__ __forceinline__ void mm(const float* __restrict__ A, const float* __r
       const float av[4] = {a.x, a.y, a.z, a.w};
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        acc[i][0] = fmaf(av[i], b.x, acc[i][0]);
-        acc[i][1] = fmaf(av[i], b.y, acc[i][1]);
-        acc[i][2] = fmaf(av[i], b.z, acc[i][2]);
-        acc[i][3] = fmaf(av[i], b.w, acc[i][3]);
+        fma2(acc[i][0], av[i], make_float2(b.x, b.y));
+        fma2(acc[i][1], av[i], make_float2(b.z, b.w));
       }
     }
   }
@@ -90,7 +92,10 @@ __device__ __forceinline__ void mm(const float* __restrict__ A, const float* __r
     for (int j = 0; j < 4; ++j) {
       const int r = (MODE == TN) ? 4 * ty + i : ty + 16 * i;
       const int c = (MODE == NT) ? tx + 16 * j : 4 * tx + j;
-      epi(r, c, acc[i][j]);
+      float val;
+      if (MODE == NT) val = acc[i][j].x + acc[i][j].y;
+      else val = (j & 1) ? acc[i][j >> 1].y : acc[i][j >> 1].x;
+      epi(r, c, val);
     }
   __syncthreads();
 }

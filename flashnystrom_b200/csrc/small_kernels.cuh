@@ -74,11 +74,13 @@ __global__ void __launch_bounds__(kThreads) combine2_kernel(Combine2Params p) {
   const float* pacc = p.part_acc + bh * (int64_t)nc * m * D;
   for (int l = t >> 2; l < m; l += kThreads / 4) {
     float M = -INFINITY;
+#pragma unroll 6
     for (int c = 0; c < nc; ++c) M = fmaxf(M, pmax[c * m + l]);
     float Lsum = 0.f;
     float4 acc[8];
 #pragma unroll
     for (int v = 0; v < 8; ++v) acc[v] = make_float4(0, 0, 0, 0);
+#pragma unroll 6
     for (int c = 0; c < nc; ++c) {
       const float w = expf(pmax[c * m + l] - M);
       Lsum = fmaf(w, psum[c * m + l], Lsum);
@@ -115,6 +117,7 @@ __global__ void __launch_bounds__(kThreads) combine2_kernel(Combine2Params p) {
 #pragma unroll
     for (int v = 0; v < 8; ++v) acc[v] = make_float4(0, 0, 0, 0);
     if (l < m) {
+#pragma unroll 4
       for (int k = 0; k < m; ++k) {
         const float a = k2inv[l * m + k];
         const float4* b = reinterpret_cast<const float4*>(sm + k * D + d0);
@@ -204,6 +207,7 @@ __global__ void __launch_bounds__(kThreads) bwd_mid1_kernel(BwdMid1Params p) {
     float4 a0[8], a1[8];
 #pragma unroll
     for (int v = 0; v < 8; ++v) { a0[v] = make_float4(0, 0, 0, 0); a1[v] = make_float4(0, 0, 0, 0); }
+#pragma unroll 6
     for (int c = 0; c < nc; ++c) {
       const float4* s0 = reinterpret_cast<const float4*>(partA + (size_t)c * 2 * md + l * D + d0);
       const float4* s1 = reinterpret_cast<const float4*>(partA + (size_t)c * 2 * md + md + l * D + d0);
@@ -235,6 +239,7 @@ __global__ void __launch_bounds__(kThreads) bwd_mid1_kernel(BwdMid1Params p) {
     float4 acc[8];
 #pragma unroll
     for (int v = 0; v < 8; ++v) acc[v] = make_float4(0, 0, 0, 0);
+#pragma unroll 4
     for (int k = 0; k < m; ++k) {
       const float a = k2inv[k * m + l];
       const float4* b = reinterpret_cast<const float4*>(ds + k * D + d0);
@@ -331,6 +336,7 @@ dqt_reduce2_kernel(const float* partB, int nchunk, const float* dqt_ns, float* d
   if (idx4 >= md) return;
   float4 s = *reinterpret_cast<const float4*>(dqt_ns + bh * md + idx4);
   const float* src = partB + bh * (size_t)nchunk * md + idx4;
+#pragma unroll 6
   for (int c = 0; c < nchunk; ++c) {
     const float4 x = *reinterpret_cast<const float4*>(src + (size_t)c * md);
     s.x += x.x; s.y += x.y; s.z += x.z; s.w += x.w;
@@ -340,6 +346,40 @@ dqt_reduce2_kernel(const float* partB, int nchunk, const float* dqt_ns, float* d
     Segments sg(N, m);
     const float f = scale / (float)sg.len(idx4 / D);
     *reinterpret_cast<float4*>(rows_q + bh * md + idx4) = make_float4(s.x * f, s.y * f, s.z * f, s.w * f);
+  }
+}
+
+// Landmarks from the pooling pass's raw segment sums: qt / kt [BH][m][D] = scale * sum / len,
+// plus the 16-bit copy of qt_mul * qt (rows m..MP-1 zero) for the tensor-core column pass.
+// grid (BH, slices): slice y owns landmark rows y, y + slices, ...
+struct LandmarkFinalizeParams {
+  const float* land_partial;  // [2][BH][m][C][D]
+  int C;
+  float* qt; float* kt;
+  int64_t BH, N;
+  int m, D;
+  float scale;
+  void* qt16; int dtype, MP; float qt16_mul;
+};
+
+__global__ void __launch_bounds__(kThreads) landmark_finalize_kernel(LandmarkFinalizeParams p) {
+  const int64_t bh = blockIdx.x;
+  const int m = p.m, D = p.D, rows = p.qt16 ? p.MP : m;
+  Segments sg(p.N, m);
+  for (int l = blockIdx.y; l < rows; l += gridDim.y) {
+    for (int e = threadIdx.x; e < 2 * D; e += kThreads) {
+      const int which = e / D, d = e - which * D;
+      float val = 0.f;
+      if (l < m) {
+        const float* src = p.land_partial + ((((size_t)which * p.BH + bh) * m + l) * p.C) * D + d;
+        float s = 0.f;
+        for (int c = 0; c < p.C; ++c) s += src[(size_t)c * D];
+        val = s * (p.scale / (float)sg.len(l));
+        (which ? p.kt : p.qt)[(bh * m + l) * D + d] = val;
+      }
+      if (which == 0 && p.qt16)
+        store16(reinterpret_cast<char*>(p.qt16) + (size_t)bh * p.MP * D * 2, p.dtype, (size_t)l * D + d, val * p.qt16_mul);
+    }
   }
 }
 
