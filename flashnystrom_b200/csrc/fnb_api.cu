@@ -155,7 +155,10 @@ struct DeviceGuard {
   bool ok = true;
   explicit DeviceGuard(int dev) {
     if (cudaGetDevice(&prev) != cudaSuccess) { ok = false; return; }
-    if (prev != dev && cudaSetDevice(dev) != cudaSuccess) ok = false;
+    // Always (re)select: besides switching devices this binds the device's primary context to
+    // the calling thread, which the driver-level tensor-map encoder needs (an autograd worker
+    // thread may not have touched the runtime yet).
+    if (cudaSetDevice(dev) != cudaSuccess) ok = false;
   }
   ~DeviceGuard() {
     int cur = -1;
@@ -258,35 +261,72 @@ static Plan plan_of(const fnb_shape& s) {
   return make_plan(s.batch * s.heads, s.seq_len, s.head_dim, s.num_landmarks, s.newton_iter);
 }
 
+// Sequence-parallel context.  stage < 0: ordinary single-device call.  Otherwise the call runs one
+// stage of the sharded pipeline (the collectives between stages belong to the caller):
+//   forward  0: local segment sums -> xfer [2][BH][m][D]                     (all-reduce, sum)
+//            1: landmarks, pseudoinverse, column pass, local merge -> xfer    (all-gather)
+//               [BH*m*D acc | BH*m max | BH*m sum]
+//            2: merge of the gathered partials (xfer = world x that), step2, output pass
+//   backward 0: row pass partials, local sum -> xfer [BH][2][m][D]            (all-reduce, sum)
+//            1: middle (from xfer), pseudoinverse backward, column pass, local dQt sum
+//               -> xfer [BH][m][D]                                            (all-reduce, sum)
+//            2: dQ pass (dQt_tot = Newton-Schulz part + xfer)
+struct SpCtx {
+  int stage = -1, rank = 0, world = 1;
+  int64_t N_global = 0;
+  float* xfer = nullptr;
+  bool on() const { return stage >= 0; }
+  bool run(int k) const { return stage < 0 || stage == k; }
+};
+
 // ------------------------------------------------------------------------------------------
 // Forward: pooling pass -> landmarks -> [pseudoinverse | softmax-3 column pass] -> combine ->
 // output row pass.
 template <class T>
 static int forward_impl(const fnb_fwd_args& a, const Plan& p, const FwdWs& w, int max_smem, int sms,
-                        cudaStream_t st, bool allow_inner_fork) {
+                        cudaStream_t st, bool allow_inner_fork, const SpCtx& S = SpCtx()) {
   Launcher L(st, a.device);
   const float scale = powf((float)p.D, -0.25f);
   constexpr bool k16 = !std::is_same<T, float>::value;
-  const tc::TcSched sch = tc::make_sched(p.BH, p.N, 2 * sms);   // two CTAs per SM
+  tc::TcSched sch = tc::make_sched(p.BH, p.N, 2 * sms);   // two CTAs per SM
   const bool use_tc = k16 && tc::tc_supported(a.shape.dtype, p.D, p.m, a.shape.flags) && sch.nchunk <= p.nchunk;
   const int MP = p.m <= 64 ? 64 : 128;
   const bool smem_ns = p.m <= ns::kN;
+  const int64_t seg_N = S.on() ? S.N_global : p.N, row_offset = S.on() ? (int64_t)S.rank * p.N : 0;
+  sch.seg_N = seg_N; sch.row_offset = row_offset;
+  const int lmC = S.on() ? 1 : p.lm_chunks;
+  float* land = S.on() ? S.xfer : w.land_partial;
+  const int nchunk_b = use_tc ? sch.nchunk : p.nchunk;
+  const size_t md_all = (size_t)p.BH * p.m * p.D, m_all = (size_t)p.BH * p.m;
 
-  L.begin();
-  {
-    int64_t grid = 2 * p.BH * p.m * p.lm_chunks;
+  if (S.run(0)) {
+    L.begin();
+    int64_t grid = 2 * p.BH * p.m * lmC;
     landmark_partial_kernel<T><<<(unsigned)grid, kThreads, 0, st>>>(
-        (const T*)a.q, (const T*)a.k, w.land_partial, p.BH, p.N, p.D, p.m, p.lm_chunks);
+        (const T*)a.q, (const T*)a.k, land, p.BH, p.N, p.D, p.m, lmC, seg_N, row_offset);
+    if (L.end("landmark_partial")) return L.status;
   }
-  if (L.end("landmark_partial")) return L.status;
+  if (S.stage == 0) return 0;
 
+  StreamParams sp;
+  memset(&sp, 0, sizeof(sp));
+  sp.q = a.q; sp.k = a.k; sp.v = a.v; sp.out = a.out; sp.lse1 = a.lse1;
+  sp.qt = a.q_landmarks; sp.kt = a.k_landmarks; sp.step2 = a.step2;
+  sp.part_acc = w.part_acc; sp.part_max = w.part_max; sp.part_sum = w.part_sum;
+  sp.N = p.N; sp.rows_per_chunk = p.rows_per_chunk; sp.D = p.D; sp.m = p.m; sp.mpad = p.mpad;
+  sp.nchunk = p.nchunk; sp.scale = scale; sp.seg_N = seg_N; sp.row_offset = row_offset;
+  const unsigned sgrid = (unsigned)(p.BH * p.nchunk);
+  auto combine_kern = p.D == 16 ? combine2_kernel<1> : p.D == 32 ? combine2_kernel<2> : p.D == 64 ? combine2_kernel<4>
+                                                                                                : combine2_kernel<8>;
+
+  if (S.run(1)) {
   Fork fork(st, a.device, smem_ns && !L.prof && allow_inner_fork);   // side stream for the pseudoinverse (off while profiling)
   if (smem_ns) {
     L.begin();
     {
       LandmarkFinalizeParams lp;
-      lp.land_partial = w.land_partial; lp.C = p.lm_chunks; lp.qt = a.q_landmarks; lp.kt = a.k_landmarks;
-      lp.BH = p.BH; lp.N = p.N; lp.m = p.m; lp.D = p.D; lp.scale = scale;
+      lp.land_partial = land; lp.C = lmC; lp.qt = a.q_landmarks; lp.kt = a.k_landmarks;
+      lp.BH = p.BH; lp.N = seg_N; lp.m = p.m; lp.D = p.D; lp.scale = scale;
       lp.qt16 = use_tc ? w.qt16 : nullptr; lp.dtype = a.shape.dtype; lp.MP = MP; lp.qt16_mul = scale * tc::kLog2e;
       landmark_finalize_kernel<<<dim3((unsigned)p.BH, 8), kThreads, 0, st>>>(lp);
     }
@@ -305,10 +345,10 @@ static int forward_impl(const fnb_fwd_args& a, const Plan& p, const FwdWs& w, in
   } else {
     L.begin();
     MidFwdParams mp;
-    mp.land_partial = w.land_partial; mp.C = p.lm_chunks;
+    mp.land_partial = land; mp.C = lmC;
     mp.qt = a.q_landmarks; mp.kt = a.k_landmarks; mp.k2 = a.k2; mp.lse2 = a.lse2;
     mp.iterates = a.ns_iterates; mp.k2inv = a.k2_inv; mp.scratch = w.pinv;
-    mp.BH = p.BH; mp.N = p.N; mp.m = p.m; mp.D = p.D; mp.J = p.J;
+    mp.BH = p.BH; mp.N = seg_N; mp.m = p.m; mp.D = p.D; mp.J = p.J;
     mp.kappa = a.shape.kappa_star; mp.scale = scale;
     mp.landmarks_only = 0;
     mp.qt16 = use_tc ? w.qt16 : nullptr; mp.dtype = a.shape.dtype; mp.MP = MP;
@@ -316,16 +356,6 @@ static int forward_impl(const fnb_fwd_args& a, const Plan& p, const FwdWs& w, in
     mid_fwd_kernel<<<(unsigned)p.BH, kThreads, 0, st>>>(mp);
     if (L.end("mid_fwd")) return L.status;
   }
-
-  StreamParams sp;
-  memset(&sp, 0, sizeof(sp));
-  sp.q = a.q; sp.k = a.k; sp.v = a.v; sp.out = a.out; sp.lse1 = a.lse1;
-  sp.qt = a.q_landmarks; sp.kt = a.k_landmarks; sp.step2 = a.step2;
-  sp.part_acc = w.part_acc; sp.part_max = w.part_max; sp.part_sum = w.part_sum;
-  sp.N = p.N; sp.rows_per_chunk = p.rows_per_chunk; sp.D = p.D; sp.m = p.m; sp.mpad = p.mpad;
-  sp.nchunk = p.nchunk; sp.scale = scale;
-  const unsigned sgrid = (unsigned)(p.BH * p.nchunk);
-  int nchunk_b = p.nchunk;
 
   if constexpr (k16) {
     if (use_tc) {
@@ -342,7 +372,6 @@ static int forward_impl(const fnb_fwd_args& a, const Plan& p, const FwdWs& w, in
       kern<<<(unsigned)(p.BH * sch.nchunk), tc::kTcThreads, smem, st>>>(tm_k, tm_v, tm_qt, w.part_acc, w.part_max,
                                                                       w.part_sum, sch, p.m, a.device_status);
       if (L.end("tc_fwd_b")) return L.status;
-      nchunk_b = sch.nchunk;
     }
   }
   if (!use_tc) {
@@ -354,17 +383,46 @@ static int forward_impl(const fnb_fwd_args& a, const Plan& p, const FwdWs& w, in
   }
 
   fork.join();
+  if (S.on()) {
+    // merge this rank's per-CTA partials into one un-normalised partial for the all-gather
+    L.begin();
+    Combine2Params cp;
+    memset(&cp, 0, sizeof(cp));
+    cp.part_acc = w.part_acc; cp.part_max = w.part_max; cp.part_sum = w.part_sum; cp.nchunk = nchunk_b;
+    cp.m = p.m; cp.D = p.D;
+    cp.acc_bh_stride = (int64_t)nchunk_b * p.m * p.D; cp.acc_chunk_stride = (int64_t)p.m * p.D;
+    cp.vec_bh_stride = (int64_t)nchunk_b * p.m; cp.vec_chunk_stride = p.m;
+    cp.partial_only = 1; cp.out_acc = S.xfer; cp.out_max = S.xfer + md_all; cp.out_sum = S.xfer + md_all + m_all;
+    if (int rc = set_smem(combine_kern, 16, max_smem, "combine_local")) return rc;
+    combine_kern<<<(unsigned)p.BH, kThreads, 16, st>>>(cp);
+    if (L.end("combine_local")) return L.status;
+  }
+  }  // stage 1
+  if (S.stage == 1) return 0;
+
   L.begin();
   {
     Combine2Params cp;
-    cp.part_acc = w.part_acc; cp.part_max = w.part_max; cp.part_sum = w.part_sum; cp.nchunk = nchunk_b;
+    memset(&cp, 0, sizeof(cp));
+    if (S.on()) {
+      // gathered layout: world x [BH*m*D acc | BH*m max | BH*m sum]
+      const int64_t per_rank = (int64_t)(md_all + 2 * m_all);
+      cp.part_acc = S.xfer; cp.part_max = S.xfer + md_all; cp.part_sum = S.xfer + md_all + m_all;
+      cp.nchunk = S.world;
+      cp.acc_bh_stride = (int64_t)p.m * p.D; cp.acc_chunk_stride = per_rank;
+      cp.vec_bh_stride = p.m; cp.vec_chunk_stride = per_rank;
+    } else {
+      cp.part_acc = w.part_acc; cp.part_max = w.part_max; cp.part_sum = w.part_sum; cp.nchunk = nchunk_b;
+      cp.acc_bh_stride = (int64_t)nchunk_b * p.m * p.D; cp.acc_chunk_stride = (int64_t)p.m * p.D;
+      cp.vec_bh_stride = (int64_t)nchunk_b * p.m; cp.vec_chunk_stride = p.m;
+    }
     cp.k2inv = a.k2_inv; cp.k_landmarks = a.k_landmarks; cp.bmat = a.bmat; cp.lse3 = a.lse3;
     cp.step2 = a.step2; cp.m = p.m; cp.D = p.D;
     cp.dtype = use_tc ? a.shape.dtype : 0; cp.MP = MP; cp.kt16 = w.kt16; cp.st16T = w.st16;
     cp.st_scale = w.st_scale; cp.kt_mul = scale * tc::kLog2e;
     size_t smem = sizeof(float) * (size_t)p.m * p.D;
-    if (int rc = set_smem(combine2_kernel, smem, max_smem, "combine")) return rc;
-    combine2_kernel<<<(unsigned)p.BH, kThreads, smem, st>>>(cp);
+    if (int rc = set_smem(combine_kern, smem, max_smem, "combine")) return rc;
+    combine_kern<<<(unsigned)p.BH, kThreads, smem, st>>>(cp);
   }
   if (L.end("combine")) return L.status;
 
@@ -402,11 +460,13 @@ static int forward_impl(const fnb_fwd_args& a, const Plan& p, const FwdWs& w, in
 // backward) -> softmax-3 column pass (dK, dV, dQt partials) -> dQ row pass.
 template <class T>
 static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, int max_smem, int sms,
-                         cudaStream_t st) {
+                         cudaStream_t st, const SpCtx& S = SpCtx()) {
   Launcher L(st, a.device);
   const float scale = powf((float)p.D, -0.25f);
   constexpr bool k16 = !std::is_same<T, float>::value;
-  const tc::TcSched sch = tc::make_sched(p.BH, p.N, 2 * sms);   // two CTAs per SM
+  tc::TcSched sch = tc::make_sched(p.BH, p.N, 2 * sms);   // two CTAs per SM
+  const int64_t seg_N = S.on() ? S.N_global : p.N, row_offset = S.on() ? (int64_t)S.rank * p.N : 0;
+  sch.seg_N = seg_N; sch.row_offset = row_offset;
   const bool use_tc = k16 && tc::tc_supported(a.shape.dtype, p.D, p.m, a.shape.flags) && sch.nchunk <= p.nchunk;
   const int MP = p.m <= 64 ? 64 : 128;
   const bool smem_ns = p.m <= ns::kN;
@@ -421,7 +481,7 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
   sp.dqt_tot = w.dqt_tot; sp.dkt_tot = w.dkt_tot;
   sp.partA = w.partA; sp.partB = w.partB;
   sp.N = p.N; sp.rows_per_chunk = p.rows_per_chunk; sp.D = p.D; sp.m = p.m; sp.mpad = p.mpad;
-  sp.nchunk = p.nchunk; sp.scale = scale;
+  sp.nchunk = p.nchunk; sp.scale = scale; sp.seg_N = seg_N; sp.row_offset = row_offset;
   const unsigned sgrid = (unsigned)(p.BH * p.nchunk);
   const unsigned tgrid = (unsigned)(p.BH * sch.nchunk);
   const size_t gsmem = bwd_ac_smem(p.mpad, p.D);
@@ -429,8 +489,22 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
 
   void* kt16 = w.op16[0]; void* st16 = w.op16[1]; void* qt16 = w.op16[3]; void* do3n = w.op16[5];
   CUtensorMap tm_q, tm_g, tm_kt, tm_st, tm_dq;
+  if (use_tc) {
+    constexpr int D = 64, MPc = 64;
+    if (!tc::make_map_3d(&tm_q, a.q, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
+        !tc::make_map_3d(&tm_g, a.d_out, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
+        !tc::make_map_3d(&tm_dq, a.dq, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
+        !tc::make_map_2d(&tm_kt, kt16, a.shape.dtype, p.BH * MPc, D, MPc) ||
+        !tc::make_map_2d(&tm_st, st16, a.shape.dtype, p.BH * MPc, D, MPc))
+      return fail(FNB_ERR_CUDA, "cuTensorMapEncodeTiled failed for the backward row passes");
+  }
+  auto reduce_chunks = [&](const float* in, int nchunk, int elems, float* out) {
+    dim3 grid((unsigned)((elems / 4 + kThreads - 1) / kThreads), (unsigned)p.BH);
+    reduce_chunks_kernel<<<grid, kThreads, 0, st>>>(in, nchunk, elems, out);
+  };
 
   // ---- pass A ---------------------------------------------------------------------------------
+  if (S.run(0)) {
   if constexpr (k16) {
     if (use_tc) {
       constexpr int D = 64, MPc = 64;
@@ -443,12 +517,6 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
         pack_bwd_ac_kernel<<<(unsigned)p.BH, kThreads, 0, st>>>(pp);
       }
       if (L.end("pack_bwd_ac")) return L.status;
-      if (!tc::make_map_3d(&tm_q, a.q, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
-          !tc::make_map_3d(&tm_g, a.d_out, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
-          !tc::make_map_3d(&tm_dq, a.dq, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
-          !tc::make_map_2d(&tm_kt, kt16, a.shape.dtype, p.BH * MPc, D, MPc) ||
-          !tc::make_map_2d(&tm_st, st16, a.shape.dtype, p.BH * MPc, D, MPc))
-        return fail(FNB_ERR_CUDA, "cuTensorMapEncodeTiled failed for the backward row passes");
       L.begin();
       auto kern = tc::tc_bwd_ac_kernel<T, D, MPc, tc::kModeA>;
       size_t sm = tc::BwdAcSmem<D, MPc, tc::kModeA>::kBytes;
@@ -464,20 +532,32 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
     gen_bwd_a_kernel<T><<<sgrid, kThreads, gsmem, st>>>(sp);
     if (L.end("gen_bwd_a")) return L.status;
   }
+  if (S.on()) {
+    L.begin();
+    reduce_chunks(w.partA, nchunk_used, 2 * p.m * p.D, S.xfer);
+    if (L.end("reduce_partA")) return L.status;
+  }
+  }  // stage 0
+  if (S.stage == 0) return 0;
+  const float* partA_src = S.on() ? S.xfer : w.partA;
+  const int partA_chunks = S.on() ? 1 : nchunk_used;
 
   // ---- landmark-sized middle ------------------------------------------------------------------
+  if (S.run(1)) {
   if (smem_ns) {
     L.begin();
     {
       BwdMid1Params mp;
-      mp.partA = w.partA; mp.nchunk = nchunk_used; mp.k2inv = a.k2_inv; mp.bmat = a.bmat;
+      mp.partA = partA_src; mp.nchunk = partA_chunks; mp.k2inv = a.k2_inv; mp.bmat = a.bmat;
       mp.q_landmarks = a.q_landmarks; mp.dkt_a = w.dkt_a; mp.dO3 = w.dO3; mp.D3 = w.D3; mp.G = w.G;
       mp.m = p.m; mp.D = p.D; mp.dtype = use_tc ? a.shape.dtype : 0; mp.MP = MP;
       mp.qt16 = qt16; mp.qtT16 = nullptr; mp.do3n = do3n; mp.do3T = nullptr; mp.do3_scale = w.do3_scale;
       mp.qt_mul = scale * tc::kLog2e; mp.qtT_mul = scale;
       size_t sm = bwd_mid1_smem(p.m, p.D);
-      if (int rc = set_smem(bwd_mid1_kernel, sm, max_smem, "bwd_mid1")) return rc;
-      bwd_mid1_kernel<<<(unsigned)p.BH, kThreads, sm, st>>>(mp);
+      auto kern = p.D == 16 ? bwd_mid1_kernel<1> : p.D == 32 ? bwd_mid1_kernel<2> : p.D == 64 ? bwd_mid1_kernel<4>
+                                                                                            : bwd_mid1_kernel<8>;
+      if (int rc = set_smem(kern, sm, max_smem, "bwd_mid1")) return rc;
+      kern<<<(unsigned)p.BH, kThreads, sm, st>>>(mp);
     }
     if (L.end("bwd_mid1")) return L.status;
     L.begin();
@@ -486,7 +566,7 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
       np.k2 = a.k2; np.iterates = a.ns_iterates; np.G = w.G; np.qt = a.q_landmarks; np.kt = a.k_landmarks;
       np.dkt_a = w.dkt_a; np.dqt_ns = w.dqt_ns; np.dkt_tot = w.dkt_tot; np.spill = w.dK2;
       np.m = p.m; np.D = p.D; np.J = p.J; np.kappa = a.shape.kappa_star;
-      np.rows_k = use_tc ? w.rows_k : nullptr; np.N = p.N; np.scale = scale;
+      np.rows_k = use_tc ? w.rows_k : nullptr; np.N = seg_N; np.scale = scale;
       if (int rc = set_smem(ns::ns_bwd_kernel, ns::kBwdSmem, max_smem, "ns_bwd")) return rc;
       ns::ns_bwd_kernel<<<(unsigned)p.BH, kThreads, ns::kBwdSmem, st>>>(np);
     }
@@ -495,7 +575,7 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
     L.begin();
     {
       MidBwdParams mp;
-      mp.partA = w.partA; mp.nchunk = nchunk_used;
+      mp.partA = partA_src; mp.nchunk = partA_chunks;
       mp.qt = a.q_landmarks; mp.kt = a.k_landmarks; mp.k2 = a.k2; mp.iterates = a.ns_iterates;
       mp.k2inv = a.k2_inv; mp.bmat = a.bmat;
       mp.dstep2 = w.dstep2; mp.dkt_a = w.dkt_a; mp.dO3 = w.dO3; mp.D3 = w.D3;
@@ -519,7 +599,7 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
           !tc::make_map_2d(&tm_do3, do3n, a.shape.dtype, p.BH * MPc, D, MPc))
         return fail(FNB_ERR_CUDA, "cuTensorMapEncodeTiled failed for the backward column pass");
       int kshift = 0;
-      while ((int64_t(2) << kshift) <= p.N && kshift < 14) ++kshift;   // floor(log2 N), at most 14
+      while ((int64_t(2) << kshift) <= seg_N && kshift < 14) ++kshift;   // floor(log2 N), at most 14
       L.begin();
       auto kern = tc::tc_bwd_b_kernel<T, D, MPc>;
       size_t sm = tc::BwdBSmem<D, MPc>::kBytes;
@@ -535,6 +615,15 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
     gen_bwd_b_kernel<T><<<sgrid, kThreads, gsmem, st>>>(sp);
     if (L.end("gen_bwd_b")) return L.status;
   }
+  if (S.on()) {
+    L.begin();
+    reduce_chunks(w.partB, nchunk_used, p.m * p.D, S.xfer);
+    if (L.end("reduce_partB")) return L.status;
+  }
+  }  // stage 1
+  if (S.stage == 1) return 0;
+  const float* partB_src = S.on() ? S.xfer : w.partB;
+  const int partB_chunks = S.on() ? 1 : nchunk_used;
 
   // ---- pass C ---------------------------------------------------------------------------------
   if constexpr (k16) {
@@ -544,8 +633,8 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
       {
         const int md = p.m * p.D;
         dim3 grid((unsigned)((md / 4 + kThreads - 1) / kThreads), (unsigned)p.BH);
-        dqt_reduce2_kernel<<<grid, kThreads, 0, st>>>(w.partB, sch.nchunk, w.dqt_ns, nullptr, w.rows_q, p.m, p.D, p.N,
-                                                     scale);
+        dqt_reduce2_kernel<<<grid, kThreads, 0, st>>>(partB_src, partB_chunks, w.dqt_ns, nullptr, w.rows_q, p.m, p.D,
+                                                     seg_N, scale);
       }
       if (L.end("dqt_rows")) return L.status;
       L.begin();
@@ -562,8 +651,8 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
   {
     const int md = p.m * p.D;
     dim3 grid((unsigned)((md / 4 + kThreads - 1) / kThreads), (unsigned)p.BH);
-    dqt_reduce2_kernel<<<grid, kThreads, 0, st>>>(w.partB, p.nchunk, w.dqt_ns, w.dqt_tot, nullptr, p.m, p.D, p.N,
-                                                 scale);
+    dqt_reduce2_kernel<<<grid, kThreads, 0, st>>>(partB_src, partB_chunks, w.dqt_ns, w.dqt_tot, nullptr, p.m, p.D,
+                                                 seg_N, scale);
   }
   if (L.end("dqt_reduce")) return L.status;
   L.begin();

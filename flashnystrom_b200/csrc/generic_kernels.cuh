@@ -77,7 +77,7 @@ __device__ __forceinline__ void load_small(float* dst, int ld, const float* src,
 template <class T>
 __global__ void __launch_bounds__(kThreads)
 landmark_partial_kernel(const T* __restrict__ q, const T* __restrict__ k, float* __restrict__ out,
-                        int64_t BH, int64_t N, int D, int m, int C) {
+                        int64_t BH, int64_t N, int D, int m, int C, int64_t seg_N, int64_t row_offset) {
   constexpr int V = Vec16<T>::n;
   __shared__ float red[kThreads * 8];
   const int64_t per_which = BH * m * C;
@@ -87,8 +87,12 @@ landmark_partial_kernel(const T* __restrict__ q, const T* __restrict__ k, float*
   const int lc = (int)(rest - bh * (m * C));
   const int l = lc / C, c = lc - l * C;
   const T* slice = (which ? k : q) + bh * N * D;
-  Segments sg(N, m);
-  const int64_t start = sg.start(l), len = sg.len(l);
+  // segment l in global rows, clipped to the rows this rank holds, in local row numbers
+  Segments sg(seg_N, m);
+  int64_t start = sg.start(l) - row_offset, end = sg.end(l) - row_offset;
+  if (start < 0) start = 0;
+  if (end > N) end = N;
+  const int64_t len = end > start ? end - start : 0;
   const int64_t per = (len + C - 1) / C;
   const int64_t r0 = start + c * per;
   int64_t r1 = r0 + per;
@@ -98,7 +102,18 @@ landmark_partial_kernel(const T* __restrict__ q, const T* __restrict__ k, float*
   float acc[V];
 #pragma unroll
   for (int e = 0; e < V; ++e) acc[e] = 0.f;
-  for (int64_t r = r0 + ro; r < r1; r += rows_per_iter) {
+  // four independent 16-byte loads in flight per thread
+  int64_t r = r0 + ro;
+  for (; r + 3 * rows_per_iter < r1; r += 4 * rows_per_iter) {
+    float x[4][V];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) load16<T>(slice + (r + u * rows_per_iter) * D + cv * V, x[u]);
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+#pragma unroll
+      for (int e = 0; e < V; ++e) acc[e] += x[u][e];
+  }
+  for (; r < r1; r += rows_per_iter) {
     float x[V];
     load16<T>(slice + r * D + cv * V, x);
 #pragma unroll
@@ -128,6 +143,7 @@ struct StreamParams {
   int64_t N, rows_per_chunk;
   int D, m, mpad, nchunk;
   float scale;
+  int64_t seg_N, row_offset;   // landmark-segment geometry (global length, first global row)
 };
 
 __host__ __device__ inline size_t fwd_b_smem(int mpad, int D) {
@@ -411,7 +427,7 @@ __global__ void __launch_bounds__(kThreads, 1) gen_bwd_c_kernel(StreamParams p) 
   T* dq = (T*)p.dq + bh * N * D;
   const float* lse1 = p.lse1 + bh * N;
   const float* dqt = p.dqt_tot + bh * m * D;
-  Segments sg(N, m);
+  Segments sg(p.seg_N, m);
   load_small(Kt, ldk, p.kt + bh * m * D, m, mpad, D);
   load_small(St, ldk, p.step2 + bh * m * D, m, mpad, D);
   __syncthreads();
@@ -430,7 +446,7 @@ __global__ void __launch_bounds__(kThreads, 1) gen_bwd_c_kernel(StreamParams p) 
     for (int i = 0; i < 2; ++i) {
       int64_t row = r0 + ty + 16 * i;
       if (row < re) {
-        int l = sg.landmark_of(row);
+        int l = sg.landmark_of(p.row_offset + row);
         float inv = 1.f / (float)sg.len(l);
 #pragma unroll
         for (int j = 0; j < 8; ++j)
@@ -468,7 +484,7 @@ __global__ void __launch_bounds__(kThreads, 1) gen_bwd_b_kernel(StreamParams p) 
   T* dk = (T*)p.dk + bh * N * D;
   T* dv = (T*)p.dv + bh * N * D;
   const float* dkt = p.dkt_tot + bh * m * D;
-  Segments sg(N, m);
+  Segments sg(p.seg_N, m);
   load_small(Qt, ldk, p.qt + bh * m * D, m, mpad, D);
   load_small(Gt, ldk, p.dO3 + bh * m * D, m, mpad, D);
   float lse3[8], d3[8];
@@ -532,7 +548,7 @@ __global__ void __launch_bounds__(kThreads, 1) gen_bwd_b_kernel(StreamParams p) 
       for (int i = 0; i < 2; ++i) {
         int64_t row = r0 + ty + 16 * i;
         if (row < re) {
-          int l = sg.landmark_of(row);
+          int l = sg.landmark_of(p.row_offset + row);
           float inv = 1.f / (float)sg.len(l);
 #pragma unroll
           for (int j = 0; j < 8; ++j)

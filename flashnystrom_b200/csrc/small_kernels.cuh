@@ -61,37 +61,70 @@ struct Combine2Params {
   void* st16T;                // [BH][D][MP]  = step2^T / st_scale
   float* st_scale;            // [BH]
   float kt_mul;
+  // element strides between slices and between chunks of the partial arrays (acc_*: the m x D
+  // accumulators, vec_*: the per-landmark max / sum vectors); lets the kernel read partials gathered from ranks
+  int64_t acc_bh_stride, acc_chunk_stride, vec_bh_stride, vec_chunk_stride;
+  // partial_only: write the merged, still un-normalised partial (acc, max, sum) of this rank
+  // into out_acc [BH][m][D], out_max / out_sum [BH][m] and stop
+  int partial_only;
+  float* out_acc; float* out_max; float* out_sum;
 };
 
+template <int NV>
 __global__ void __launch_bounds__(kThreads) combine2_kernel(Combine2Params p) {
   extern __shared__ float sm[];            // bmat then step2: [m][D]
   __shared__ float red[8];
   const int64_t bh = blockIdx.x;
   const int m = p.m, D = p.D, t = threadIdx.x, nc = p.nchunk;
-  const int q = t & 3, dpt = D >> 2, nv = dpt >> 2, d0 = q * dpt;
-  const float* pmax = p.part_max + bh * (int64_t)nc * m;
-  const float* psum = p.part_sum + bh * (int64_t)nc * m;
-  const float* pacc = p.part_acc + bh * (int64_t)nc * m * D;
+  constexpr int nv = NV;                      // float4 per thread per row: D = 16 * NV
+  constexpr int CB = NV <= 2 ? 8 : (NV == 4 ? 4 : 2);   // chunks whose loads are in flight together
+  const int q = t & 3, dpt = D >> 2, d0 = q * dpt;
+  const int64_t cs = p.acc_chunk_stride, csv = p.vec_chunk_stride;
+  const float* pmax = p.part_max + bh * p.vec_bh_stride;
+  const float* psum = p.part_sum + bh * p.vec_bh_stride;
+  const float* pacc = p.part_acc + bh * p.acc_bh_stride;
   for (int l = t >> 2; l < m; l += kThreads / 4) {
     float M = -INFINITY;
-#pragma unroll 6
-    for (int c = 0; c < nc; ++c) M = fmaxf(M, pmax[c * m + l]);
+    for (int c0 = 0; c0 < nc; c0 += 8) {
+      float pm[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) pm[i] = (c0 + i < nc) ? pmax[(c0 + i) * csv + l] : -INFINITY;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) M = fmaxf(M, pm[i]);
+    }
     float Lsum = 0.f;
     float4 acc[8];
 #pragma unroll
     for (int v = 0; v < 8; ++v) acc[v] = make_float4(0, 0, 0, 0);
-#pragma unroll 6
-    for (int c = 0; c < nc; ++c) {
-      const float w = expf(pmax[c * m + l] - M);
-      Lsum = fmaf(w, psum[c * m + l], Lsum);
-      const float4* src = reinterpret_cast<const float4*>(pacc + ((size_t)c * m + l) * D + d0);
+    for (int c0 = 0; c0 < nc; c0 += CB) {
+      float pm[CB], ps[CB];
+      float4 x[CB][NV];
 #pragma unroll
-      for (int v = 0; v < 8; ++v)
-        if (v < nv) {
-          const float4 x = src[v];
-          acc[v].x = fmaf(w, x.x, acc[v].x); acc[v].y = fmaf(w, x.y, acc[v].y);
-          acc[v].z = fmaf(w, x.z, acc[v].z); acc[v].w = fmaf(w, x.w, acc[v].w);
+      for (int i = 0; i < CB; ++i) {
+        const int c = min(c0 + i, nc - 1);
+        pm[i] = pmax[c * csv + l];
+        ps[i] = psum[c * csv + l];
+        const float4* src = reinterpret_cast<const float4*>(pacc + (size_t)c * cs + (size_t)l * D + d0);
+#pragma unroll
+        for (int v = 0; v < NV; ++v) x[i][v] = src[v];
+      }
+#pragma unroll
+      for (int i = 0; i < CB; ++i) {
+        const float w = (c0 + i < nc) ? expf(pm[i] - M) : 0.f;
+        Lsum = fmaf(w, ps[i], Lsum);
+#pragma unroll
+        for (int v = 0; v < NV; ++v) {
+          acc[v].x = fmaf(w, x[i][v].x, acc[v].x); acc[v].y = fmaf(w, x[i][v].y, acc[v].y);
+          acc[v].z = fmaf(w, x[i][v].z, acc[v].z); acc[v].w = fmaf(w, x[i][v].w, acc[v].w);
         }
+      }
+    }
+    if (p.partial_only) {
+      float4* dst = reinterpret_cast<float4*>(p.out_acc + (bh * m + l) * D + d0);
+#pragma unroll
+      for (int v = 0; v < 8; ++v) if (v < nv) dst[v] = acc[v];
+      if (q == 0) { p.out_max[bh * m + l] = M; p.out_sum[bh * m + l] = Lsum; }
+      continue;
     }
     const float inv = 1.f / Lsum;
     float4* dst_s = reinterpret_cast<float4*>(sm + l * D + d0);
@@ -105,6 +138,7 @@ __global__ void __launch_bounds__(kThreads) combine2_kernel(Combine2Params p) {
       }
     if (q == 0) p.lse3[bh * m + l] = M + logf(Lsum);
   }
+  if (p.partial_only) return;
   __syncthreads();
   // step2 = K2inv Bmat
   const float* k2inv = p.k2inv + bh * m * m;
@@ -192,12 +226,15 @@ __host__ __device__ inline size_t bwd_mid1_smem(int m, int D) {
   return sizeof(float) * ((size_t)m * D + (size_t)m * (D + 4) + (size_t)m * D);
 }
 
+template <int NV>
 __global__ void __launch_bounds__(kThreads) bwd_mid1_kernel(BwdMid1Params p) {
   extern __shared__ float sm[];
   __shared__ float red[8];
   const int64_t bh = blockIdx.x;
   const int m = p.m, D = p.D, t = threadIdx.x, nc = p.nchunk, md = m * D, ldb = D + 4;
-  const int q = t & 3, dpt = D >> 2, nv = dpt >> 2, d0 = q * dpt;
+  constexpr int nv = NV;
+  constexpr int CB = NV <= 2 ? 8 : (NV == 4 ? 4 : 2);
+  const int q = t & 3, dpt = D >> 2, d0 = q * dpt;
   float* ds = sm;                    // dstep2 [m][D]
   float* bm = ds + md;               // Bmat   [m][D+4]
   float* do3 = bm + m * ldb;         // dO3    [m][D]
@@ -207,17 +244,26 @@ __global__ void __launch_bounds__(kThreads) bwd_mid1_kernel(BwdMid1Params p) {
     float4 a0[8], a1[8];
 #pragma unroll
     for (int v = 0; v < 8; ++v) { a0[v] = make_float4(0, 0, 0, 0); a1[v] = make_float4(0, 0, 0, 0); }
-#pragma unroll 6
-    for (int c = 0; c < nc; ++c) {
-      const float4* s0 = reinterpret_cast<const float4*>(partA + (size_t)c * 2 * md + l * D + d0);
-      const float4* s1 = reinterpret_cast<const float4*>(partA + (size_t)c * 2 * md + md + l * D + d0);
+    for (int c0 = 0; c0 < nc; c0 += CB) {
+      float4 x[CB][NV], y[CB][NV];
 #pragma unroll
-      for (int v = 0; v < 8; ++v)
-        if (v < nv) {
-          const float4 x = s0[v], y = s1[v];
-          a0[v].x += x.x; a0[v].y += x.y; a0[v].z += x.z; a0[v].w += x.w;
-          a1[v].x += y.x; a1[v].y += y.y; a1[v].z += y.z; a1[v].w += y.w;
+      for (int i = 0; i < CB; ++i) {
+        const int c = min(c0 + i, nc - 1);
+        const float4* s0 = reinterpret_cast<const float4*>(partA + (size_t)c * 2 * md + l * D + d0);
+        const float4* s1 = reinterpret_cast<const float4*>(partA + (size_t)c * 2 * md + md + l * D + d0);
+#pragma unroll
+        for (int v = 0; v < NV; ++v) { x[i][v] = s0[v]; y[i][v] = s1[v]; }
+      }
+#pragma unroll
+      for (int i = 0; i < CB; ++i) {
+        if (c0 + i < nc) {
+#pragma unroll
+          for (int v = 0; v < NV; ++v) {
+            a0[v].x += x[i][v].x; a0[v].y += x[i][v].y; a0[v].z += x[i][v].z; a0[v].w += x[i][v].w;
+            a1[v].x += y[i][v].x; a1[v].y += y[i][v].y; a1[v].z += y[i][v].z; a1[v].w += y[i][v].w;
+          }
         }
+      }
     }
     float4* dd = reinterpret_cast<float4*>(ds + l * D + d0);
     float4* dk = reinterpret_cast<float4*>(p.dkt_a + bh * md + l * D + d0);
@@ -381,6 +427,22 @@ __global__ void __launch_bounds__(kThreads) landmark_finalize_kernel(LandmarkFin
         store16(reinterpret_cast<char*>(p.qt16) + (size_t)bh * p.MP * D * 2, p.dtype, (size_t)l * D + d, val * p.qt16_mul);
     }
   }
+}
+
+// out[bh][e] = sum over chunks of in[bh][chunk][e], fixed order (e < elems, elems % 4 == 0).
+__global__ void __launch_bounds__(kThreads)
+reduce_chunks_kernel(const float* in, int nchunk, int elems, float* out) {
+  const int64_t bh = blockIdx.y;
+  const int idx4 = (blockIdx.x * kThreads + threadIdx.x) * 4;
+  if (idx4 >= elems) return;
+  const float* src = in + bh * (size_t)nchunk * elems + idx4;
+  float4 s = make_float4(0, 0, 0, 0);
+#pragma unroll 6
+  for (int c = 0; c < nchunk; ++c) {
+    const float4 x = *reinterpret_cast<const float4*>(src + (size_t)c * elems);
+    s.x += x.x; s.y += x.y; s.z += x.z; s.w += x.w;
+  }
+  *reinterpret_cast<float4*>(out + bh * (size_t)elems + idx4) = s;
 }
 
 }  // namespace fnb

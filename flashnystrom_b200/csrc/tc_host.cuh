@@ -64,6 +64,8 @@ inline bool make_map_2d(CUtensorMap* map, const void* ptr, int dtype, int64_t ro
 inline TcSched make_sched(int64_t BH, int64_t N, int slots) {
   TcSched s;
   s.N = N;
+  s.seg_N = N;
+  s.row_offset = 0;
   int64_t tiles = (N + kTile - 1) / kTile;
   int64_t want = slots / BH;            // floor: BH * want <= slots
   if (want > tiles) want = tiles;

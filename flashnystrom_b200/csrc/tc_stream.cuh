@@ -29,9 +29,12 @@ __device__ __forceinline__ uint8_t* align1024(uint8_t* p) {
 }
 
 struct TcSched {
-  int64_t N;
+  int64_t N;             // rows of this rank's slice
   int nchunk;            // CTAs per (b,h) slice
   int tiles_per_chunk;   // 128-row tiles per CTA
+  int64_t seg_N;         // sequence length the landmark segments are defined on (== N unless the
+  int64_t row_offset;    //   sequence is sharded over ranks: then the global length and this
+                         //   rank's first global row)
 };
 
 // NC consecutive FP32 TMEM columns of this thread's lane -> registers
@@ -442,7 +445,7 @@ tc_bwd_ac_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
     const float sc = st_scale[bh];
     const int c0 = h * HC;
-    Segments sg(sch.N, m);
+    Segments sg(sch.seg_N, m);
     bool alive = true;
     for (int i = 0; i < count; ++i) {
       const int b = (MODE == kModeC) ? (i & 1) : 0;
@@ -495,7 +498,7 @@ tc_bwd_ac_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         tmem_ld_wait();
         tc_fence_before();
         mbar_arrive(o_free + b);
-        const int l = valid ? sg.landmark_of(row) : 0;
+        const int l = valid ? sg.landmark_of(sch.row_offset + row) : 0;
         const float4* add = reinterpret_cast<const float4*>(rows_q + (bh * m + l) * D + h * HD);
         const float mul = sc * kLn2;
 #pragma unroll
@@ -699,7 +702,7 @@ tc_bwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
     const float dsc = do3_scale[bh];
     const float unshift = exp2f(-(float)kshift);
     const int c0 = h * HC;
-    Segments sg(sch.N, m);
+    Segments sg(sch.seg_N, m);
     if (threadIdx.x < MP) {
       const int j = threadIdx.x;
       s_c3[j] = (j < m) ? lse3[bh * m + j] * kLog2e - (float)kshift : INFINITY;
@@ -748,7 +751,7 @@ tc_bwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
       tmem_ld_wait();
       tc_fence_before();
       mbar_arrive(o_free);
-      const int l = valid ? sg.landmark_of(row) : 0;
+      const int l = valid ? sg.landmark_of(sch.row_offset + row) : 0;
       const float4* add = reinterpret_cast<const float4*>(rows_k + (bh * m + l) * D + h * HD);
       const float vmul = dsc * unshift, kmul = unshift * kLn2;
 #pragma unroll
