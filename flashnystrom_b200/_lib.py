@@ -43,6 +43,11 @@ class BwdArgs(C.Structure):
                 ("device", C.c_int32), ("stream", C.c_void_p), ("device_status", C.c_void_p)]
 
 
+class SpInfo(C.Structure):
+    _fields_ = [("rank", C.c_int32), ("world", C.c_int32), ("stage", C.c_int32),
+                ("seq_len_global", C.c_int64), ("xfer", C.c_void_p), ("xfer_floats", C.c_size_t)]
+
+
 class Caps(C.Structure):
     _fields_ = [("abi_version", C.c_int32), ("cc_major", C.c_int32), ("cc_minor", C.c_int32),
                 ("sm_count", C.c_int32), ("max_smem_per_block", C.c_int32),
@@ -63,6 +68,9 @@ SIGNATURES = {
     "fnb_check_shape": (C.c_int, [C.POINTER(Shape)]),
     "fnb_forward": (C.c_int, [C.POINTER(FwdArgs)]),
     "fnb_backward": (C.c_int, [C.POINTER(BwdArgs)]),
+    "fnb_sp_xfer_floats": (C.c_size_t, [C.POINTER(Shape), C.c_int, C.c_int, C.c_int]),
+    "fnb_sp_forward": (C.c_int, [C.POINTER(FwdArgs), C.POINTER(SpInfo)]),
+    "fnb_sp_backward": (C.c_int, [C.POINTER(BwdArgs), C.POINTER(SpInfo)]),
     "fnb_debug_pinv_forward": (C.c_int, [C.c_int64, C.c_int32, C.c_int32, C.c_float, C.c_void_p,
                                          C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t,
                                          C.c_int32, C.c_void_p]),

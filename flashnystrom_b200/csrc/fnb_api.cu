@@ -864,6 +864,82 @@ int fnb_backward(const fnb_bwd_args* a) {
   }
 }
 
+static int check_sp(const fnb_shape& s, const fnb_sp_info* sp, int is_backward) {
+  if (!sp) return fail(FNB_ERR_INVALID_ARGUMENT, "sp is NULL");
+  if (sp->world < 1 || sp->rank < 0 || sp->rank >= sp->world)
+    return fail(FNB_ERR_INVALID_ARGUMENT, "sequence parallel: rank %d / world %d out of range", sp->rank, sp->world);
+  if (sp->stage < 0 || sp->stage > 2) return fail(FNB_ERR_INVALID_ARGUMENT, "sequence parallel: stage must be 0, 1 or 2");
+  if (sp->seq_len_global != (int64_t)sp->world * s.seq_len)
+    return fail(FNB_ERR_INVALID_ARGUMENT, "sequence parallel: seq_len_global (%lld) must equal world (%d) x local seq_len (%lld)",
+                (long long)sp->seq_len_global, sp->world, (long long)s.seq_len);
+  if (s.num_landmarks % sp->world != 0 || sp->seq_len_global % s.num_landmarks != 0)
+    return fail(FNB_ERR_INVALID_ARGUMENT,
+                "sequence parallel: num_landmarks (%d) must be a multiple of world (%d) and divide seq_len_global (%lld)",
+                s.num_landmarks, sp->world, (long long)sp->seq_len_global);
+  const size_t need = fnb_sp_xfer_floats(&s, sp->world, is_backward, sp->stage);
+  if (!sp->xfer || sp->xfer_floats < need)
+    return fail(FNB_ERR_WORKSPACE, "sequence parallel: xfer must hold %zu floats (got %zu)", need, sp->xfer_floats);
+  return 0;
+}
+
+size_t fnb_sp_xfer_floats(const fnb_shape* s, int world, int is_backward, int stage) {
+  if (check_shape(s) || world < 1) return 0;
+  const size_t md = (size_t)s->batch * s->heads * s->num_landmarks * s->head_dim;
+  const size_t mv = (size_t)s->batch * s->heads * s->num_landmarks;
+  if (is_backward) return stage == 0 ? 2 * md : md;
+  if (stage == 0) return 2 * md;
+  if (stage == 1) return md + 2 * mv;
+  return (size_t)world * (md + 2 * mv);
+}
+
+int fnb_sp_forward(const fnb_fwd_args* a, const fnb_sp_info* sp) {
+  if (!a) return fail(FNB_ERR_INVALID_ARGUMENT, "args is NULL");
+  if (int rc = check_shape(&a->shape)) return rc;
+  if (int rc = check_sp(a->shape, sp, 0)) return rc;
+  const size_t need = fwd_ws_total(a->shape);
+  if (!a->workspace || a->workspace_bytes < need || (reinterpret_cast<uintptr_t>(a->workspace) & 255u))
+    return fail(FNB_ERR_WORKSPACE, "forward workspace must be 256-byte aligned and >= %zu bytes (got %zu)", need,
+                a->workspace_bytes);
+  DeviceGuard g(a->device);
+  if (!g.ok) return fail(FNB_ERR_CUDA, "cannot select CUDA device %d", a->device);
+  int max_smem = 0, cc = 0, sms = 0;
+  if (int rc = device_limits(a->device, &max_smem, &cc, &sms)) return rc;
+  cudaStream_t st = (cudaStream_t)a->stream;
+  Plan p = plan_of(a->shape);
+  FwdWs w = carve_fwd(p, a->workspace);
+  SpCtx S;
+  S.stage = sp->stage; S.rank = sp->rank; S.world = sp->world; S.N_global = sp->seq_len_global; S.xfer = sp->xfer;
+  switch (a->shape.dtype) {
+    case FNB_F32: return forward_impl<float>(*a, p, w, max_smem, sms, st, true, S);
+    case FNB_F16: return forward_impl<__half>(*a, p, w, max_smem, sms, st, true, S);
+    default: return forward_impl<__nv_bfloat16>(*a, p, w, max_smem, sms, st, true, S);
+  }
+}
+
+int fnb_sp_backward(const fnb_bwd_args* a, const fnb_sp_info* sp) {
+  if (!a) return fail(FNB_ERR_INVALID_ARGUMENT, "args is NULL");
+  if (int rc = check_shape(&a->shape)) return rc;
+  if (int rc = check_sp(a->shape, sp, 1)) return rc;
+  const size_t need = bwd_ws_total(a->shape);
+  if (!a->workspace || a->workspace_bytes < need || (reinterpret_cast<uintptr_t>(a->workspace) & 255u))
+    return fail(FNB_ERR_WORKSPACE, "backward workspace must be 256-byte aligned and >= %zu bytes (got %zu)", need,
+                a->workspace_bytes);
+  DeviceGuard g(a->device);
+  if (!g.ok) return fail(FNB_ERR_CUDA, "cannot select CUDA device %d", a->device);
+  int max_smem = 0, cc = 0, sms = 0;
+  if (int rc = device_limits(a->device, &max_smem, &cc, &sms)) return rc;
+  cudaStream_t st = (cudaStream_t)a->stream;
+  Plan p = plan_of(a->shape);
+  BwdWs w = carve_bwd(p, a->workspace);
+  SpCtx S;
+  S.stage = sp->stage; S.rank = sp->rank; S.world = sp->world; S.N_global = sp->seq_len_global; S.xfer = sp->xfer;
+  switch (a->shape.dtype) {
+    case FNB_F32: return backward_impl<float>(*a, p, w, max_smem, sms, st, S);
+    case FNB_F16: return backward_impl<__half>(*a, p, w, max_smem, sms, st, S);
+    default: return backward_impl<__nv_bfloat16>(*a, p, w, max_smem, sms, st, S);
+  }
+}
+
 size_t fnb_debug_pinv_workspace_bytes(int64_t bh, int32_t m) {
   if (bh <= 0 || m < 1 || m > kMaxM) return 0;
   return align256((size_t)bh * kPinvBwdBufs * m * m * sizeof(float));

@@ -148,6 +148,31 @@ FNB_API int fnb_check_shape(const fnb_shape* shape);
 FNB_API int fnb_forward(const fnb_fwd_args* args);
 FNB_API int fnb_backward(const fnb_bwd_args* args);
 
+/* ---- sequence parallelism (no counterpart in the reference) -------------------------------
+ * The sequence of every (b,h) slice is cut into `world` equal contiguous shards, one per rank;
+ * shape.seq_len is the LOCAL length, seq_len_global = world * seq_len.  Requirements:
+ * num_landmarks % world == 0 and seq_len_global % num_landmarks == 0, so every landmark
+ * segment lives on one rank.  A forward or backward is three calls (stage 0, 1, 2) with the
+ * same arguments and workspace; between stages the caller runs one collective on `xfer`
+ * (FP32, device memory):
+ *   forward  after stage 0: all-reduce(sum) of xfer[0 .. 2*BH*m*D)
+ *            after stage 1: all-gather of this rank's BH*m*(D+2) floats into world * that many,
+ *                           rank-major, passed as xfer of stage 2
+ *   backward after stage 0: all-reduce(sum) of xfer[0 .. 2*BH*m*D)
+ *            after stage 1: all-reduce(sum) of xfer[0 .. BH*m*D)
+ * Saved tensors are replicated (identical on every rank) except lse1, which is per local row.
+ * The collectives carry m x D tiles per slice: they are latency-bound, not bandwidth-bound. */
+typedef struct fnb_sp_info {
+  int32_t rank, world, stage;
+  int64_t seq_len_global;
+  float* xfer;
+  size_t xfer_floats;    /* capacity of xfer, checked against fnb_sp_xfer_floats */
+} fnb_sp_info;
+/* Floats needed in xfer for (is_backward, stage); stage 2 of the forward wants world x stage 1. */
+FNB_API size_t fnb_sp_xfer_floats(const fnb_shape* shape, int world, int is_backward, int stage);
+FNB_API int fnb_sp_forward(const fnb_fwd_args* args, const fnb_sp_info* sp);
+FNB_API int fnb_sp_backward(const fnb_bwd_args* args, const fnb_sp_info* sp);
+
 /* Isolation hooks for the Newton-Schulz kernels; (BH,m,m) FP32 device tensors.
  * Stand in for debug_kernel2_inv_bwd_full / debug_ns_bwd_* (csrc/flash_nystrom.cu:629-690).
  *
