@@ -206,6 +206,25 @@ def debug_pinv_backward(k2, ns_iterates, d_k2_inv, kappa_star=0.0):
     return dk2
 
 
+def pinv_backward_noalloc(k2, ns_iterates, d_k2_inv, out, kappa_star=0.0):
+    """Pseudoinverse gradient into the caller's `out` tensor through the entry point that
+    allocates nothing (scratch is a fixed array inside the library).  For hosts that may not
+    allocate device memory after start-up; at most 64 slices and num_landmarks <= 64 per call.
+    Calls must not overlap on the GPU: they share the scratch."""
+    lib = _lib.load()
+    _check_big(k2, "k2", dtype=torch.float32)
+    BH, m, _ = k2.shape
+    J = ns_iterates.shape[1] - 1
+    _check_big(ns_iterates, "ns_iterates", (BH, J + 1, m, m), torch.float32)
+    _check_big(d_k2_inv, "d_k2_inv", (BH, m, m), torch.float32)
+    _check_big(out, "out", (BH, m, m), torch.float32)
+    dev = k2.device
+    _lib.check(lib.fnb_pinv_backward_noalloc(BH, m, J, float(kappa_star), _ptr(k2), _ptr(ns_iterates),
+                                             _ptr(d_k2_inv), _ptr(out), dev.index,
+                                             C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)))
+    return out
+
+
 def query_sm_limits(device=0):
     """Device facts, like the reference's query_sm_limits (csrc/flash_nystrom.cu:693-726)."""
     lib = _lib.load()

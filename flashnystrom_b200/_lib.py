@@ -77,6 +77,8 @@ SIGNATURES = {
     "fnb_debug_pinv_backward": (C.c_int, [C.c_int64, C.c_int32, C.c_int32, C.c_float, C.c_void_p,
                                           C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                           C.c_size_t, C.c_int32, C.c_void_p]),
+    "fnb_pinv_backward_noalloc": (C.c_int, [C.c_int64, C.c_int32, C.c_int32, C.c_float, C.c_void_p,
+                                            C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p]),
     "fnb_debug_pinv_workspace_bytes": (C.c_size_t, [C.c_int64, C.c_int32]),
     "fnb_set_profiling": (C.c_int, [C.c_int]),
     "fnb_last_profile": (C.c_int, [C.POINTER(KernelTime), C.c_int]),

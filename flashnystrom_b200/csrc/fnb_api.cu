@@ -21,6 +21,12 @@
 
 namespace fnb {
 
+// Scratch of fnb_pinv_backward_noalloc: one (64 x 64) FP32 matrix per slice for up to 64 slices
+// (1 MiB), resident in every device that loads this library until the process exits.
+constexpr int kNoAllocMaxSlices = 64;
+constexpr int kNoAllocMaxM = 64;
+static __device__ __align__(256) float g_noalloc_scratch[kNoAllocMaxSlices * kNoAllocMaxM * kNoAllocMaxM];
+
 static thread_local char g_err[512] = "";
 static int fail(int code, const char* fmt, ...) {
   va_list ap;
@@ -992,6 +998,52 @@ int fnb_debug_pinv_backward(int64_t bh, int32_t m, int32_t J, float kappa, const
     pinv_bwd_debug_kernel<<<(unsigned)bh, kThreads, 0, (cudaStream_t)stream>>>(
         k2, ns_iterates, d_k2_inv, d_k2, (float*)workspace, m, J, kappa);
   }
+  FNB_CUDA(cudaPeekAtLastError());
+  return 0;
+}
+
+// Device address of g_noalloc_scratch on `device`.  In host code the array's name is only a
+// stand-in; the address a kernel can use comes from cudaGetSymbolAddress, asked once per device
+// while that device is current.
+static int noalloc_scratch(int device, float** out) {
+  constexpr int kMaxDevices = 64;
+  static std::mutex mu;
+  static float* table[kMaxDevices] = {};
+  if (device < 0 || device >= kMaxDevices) return fail(FNB_ERR_INVALID_ARGUMENT, "device ordinal %d out of range", device);
+  std::lock_guard<std::mutex> lock(mu);
+  if (!table[device]) {
+    void* ptr = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);   // the caller made `device` current
+    if (e != cudaSuccess || !ptr)
+      return fail(FNB_ERR_CUDA, "cudaGetSymbolAddress(scratch) failed on device %d: %s", device, cudaGetErrorString(e));
+    table[device] = static_cast<float*>(ptr);
+  }
+  *out = table[device];
+  return 0;
+}
+
+int fnb_pinv_backward_noalloc(int64_t bh, int32_t m, int32_t J, float kappa, const float* k2,
+                              const float* ns_iterates, const float* d_k2_inv, float* d_k2, int32_t device,
+                              void* stream) {
+  if (bh < 1 || bh > kNoAllocMaxSlices)
+    return fail(FNB_ERR_INVALID_ARGUMENT, "fnb_pinv_backward_noalloc handles 1..%d slices per call, got %lld",
+                kNoAllocMaxSlices, (long long)bh);
+  if (m < 1 || m > kNoAllocMaxM)
+    return fail(FNB_ERR_INVALID_ARGUMENT, "fnb_pinv_backward_noalloc handles num_landmarks in [1, %d], got %d",
+                kNoAllocMaxM, m);
+  if (J < 1 || J > 20) return fail(FNB_ERR_INVALID_ARGUMENT, "newton_iter must be in [1, 20], got %d", J);
+  if (!std::isfinite(kappa) || kappa < 0.f) return fail(FNB_ERR_INVALID_ARGUMENT, "kappa_star must be finite and >= 0");
+  if (!k2 || !ns_iterates || !d_k2_inv || !d_k2) return fail(FNB_ERR_INVALID_ARGUMENT, "NULL tensor pointer");
+  DeviceGuard g(device);
+  if (!g.ok) return fail(FNB_ERR_CUDA, "cannot select CUDA device %d", device);
+  float* scratch = nullptr;
+  if (int rc = noalloc_scratch(device, &scratch)) return rc;
+  FNB_CUDA(cudaFuncSetAttribute(ns::ns_pinv_bwd_debug_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                (int)ns::kBwdSmem));
+  // Nothing in the scratch has to start at zero: with the ridge each slice's (m x m) block is
+  // fully written (G^T Z_J) before it is read back; without the ridge it is not touched.
+  ns::ns_pinv_bwd_debug_kernel<<<(unsigned)bh, kThreads, ns::kBwdSmem, (cudaStream_t)stream>>>(
+      k2, ns_iterates, d_k2_inv, d_k2, scratch, m, J, kappa);
   FNB_CUDA(cudaPeekAtLastError());
   return 0;
 }

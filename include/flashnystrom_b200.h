@@ -189,6 +189,24 @@ FNB_API int fnb_debug_pinv_backward(int64_t bh, int32_t m, int32_t newton_iter, 
                             int32_t device, void* stream);
 FNB_API size_t fnb_debug_pinv_workspace_bytes(int64_t bh, int32_t m);
 
+/* Gradient of the pseudoinverse for callers that must not allocate: same result as
+ * fnb_debug_pinv_backward, but without a workspace argument.  It has no counterpart in the
+ * reference.  It is meant for hosts whose device memory is handed out once at start-up and
+ * then frozen - a plugin inside a serving process with a fixed memory plan, say - where a
+ * cudaMalloc in the request path is forbidden (it may fail, and it stalls the device).  The
+ * scratch the kernel needs (one m x m FP32 block per slice, used with the ridge) lives in a
+ * 1 MiB array compiled into the library; every GPU that loads the library carries it until the
+ * process exits.  Limits: at most 64 slices per call and num_landmarks <= 64; larger requests
+ * are refused with FNB_ERR_INVALID_ARGUMENT.  The call allocates and frees nothing.  The first
+ * call on a device looks up the array's device address (cudaGetSymbolAddress, with that device
+ * current); make that first call before any stream capture begins.  All calls share the one
+ * array and it keeps whatever the last call left in it (nothing needs clearing: every block is
+ * written before it is read); two calls whose kernels overlap on the GPU - different streams -
+ * would race on it, so keep them ordered. */
+FNB_API int fnb_pinv_backward_noalloc(int64_t bh, int32_t m, int32_t newton_iter, float kappa_star,
+                                      const float* k2, const float* ns_iterates, const float* d_k2_inv,
+                                      float* d_k2, int32_t device, void* stream);
+
 /* Per-kernel timing.  Off unless the environment variable FNB_PROFILE=1 was set when the
  * library was loaded or fnb_set_profiling(1) was called (process-wide switch; returns the
  * previous mode).  While on, fnb_forward / fnb_backward bracket every kernel with CUDA events on

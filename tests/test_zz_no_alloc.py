@@ -1,0 +1,45 @@
+"""The allocation-free pseudoinverse gradient (fnb_pinv_backward_noalloc) against the ordinary
+entry point that takes a workspace.  Some hosts - a serving plugin whose device memory is fixed
+at start-up - may not call cudaMalloc per request, so this entry point keeps its scratch in an
+array inside the library.  Two calls in a row must both reproduce the reference entry point
+(the shared scratch keeps the first call's contents), the ridge case is the one that uses the
+scratch, and oversize requests must be refused.  Collected last on purpose."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _case(BH, m, J, seed):
+    g = torch.Generator().manual_seed(seed)
+    k2 = torch.softmax(torch.randn(BH, m, m, generator=g) * 1.5, dim=-1).cuda()
+    G = torch.randn(BH, m, m, generator=g).cuda()
+    return k2, G
+
+
+@pytest.mark.parametrize("kappa", [5.0, 0.0])
+def test_noalloc_matches_workspace_entry_point_twice(cuda_device, kappa):
+    from flashnystrom_b200 import _C
+    for call, (BH, m, J, seed) in enumerate([(7, 64, 6, 1), (3, 33, 8, 2)]):
+        k2, G = _case(BH, m, J, seed)
+        iters, _ = _C.debug_pinv_forward(k2, J, kappa)
+        want = _C.debug_pinv_backward(k2, iters, G, kappa)
+        got = torch.full_like(k2, float("nan"))
+        _C.pinv_backward_noalloc(k2, iters, G, got, kappa)
+        torch.cuda.synchronize()
+        assert torch.isfinite(got).all(), f"call {call}"
+        # same kernel, same summation order: the tolerance of the other pinv tests is ample
+        err = float((got - want).abs().max() / want.abs().max())
+        assert err <= 5e-4, f"call {call}: rel_max {err}"
+
+
+def test_noalloc_rejects_oversize(cuda_device):
+    from flashnystrom_b200 import _C
+    k2, G = _case(65, 16, 6, 3)
+    iters, _ = _C.debug_pinv_forward(k2, 6, 0.0)
+    with pytest.raises(RuntimeError, match="slices per call"):
+        _C.pinv_backward_noalloc(k2, iters, G, torch.empty_like(k2))
+    k2, G = _case(2, 96, 6, 4)
+    iters, _ = _C.debug_pinv_forward(k2, 6, 0.0)
+    with pytest.raises(RuntimeError, match="num_landmarks in"):
+        _C.pinv_backward_noalloc(k2, iters, G, torch.empty_like(k2))
