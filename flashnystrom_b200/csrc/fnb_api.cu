@@ -16,6 +16,7 @@
 #include "generic_kernels.cuh"
 #include "tc_host.cuh"
 #include "ns_kernels.cuh"
+#include "ns_tc_kernels.cuh"
 #include <type_traits>
 #include <algorithm>
 
@@ -288,6 +289,17 @@ struct SpCtx {
 // ------------------------------------------------------------------------------------------
 // Forward: pooling pass -> landmarks -> [pseudoinverse | softmax-3 column pass] -> combine ->
 // output row pass.
+// The Newton-Schulz kernels for num_landmarks <= 64 run on the tensor cores (three-term bf16
+// split, FP32-equivalent) unless the caller forces the CUDA-core path or FNB_NS_CUDA_CORES=1 is
+// set in the environment (kept for A/B measurements).
+static bool ns_on_tensor_cores(uint32_t flags) {
+  static const bool env_off = [] {
+    const char* e = getenv("FNB_NS_CUDA_CORES");
+    return e && e[0] == '1';
+  }();
+  return !env_off && !(flags & FNB_FLAG_FORCE_GENERIC);
+}
+
 template <class T>
 static int forward_impl(const fnb_fwd_args& a, const Plan& p, const FwdWs& w, int max_smem, int sms,
                         cudaStream_t st, bool allow_inner_fork, const SpCtx& S = SpCtx()) {
@@ -344,8 +356,13 @@ static int forward_impl(const fnb_fwd_args& a, const Plan& p, const FwdWs& w, in
     np.qt = a.q_landmarks; np.kt = a.k_landmarks; np.k2 = a.k2; np.lse2 = a.lse2;
     np.iterates = a.ns_iterates; np.k2inv = a.k2_inv; np.m = p.m; np.D = p.D; np.J = p.J;
     np.kappa = a.shape.kappa_star;
-    if (int rc = set_smem(ns::ns_fwd_kernel, ns::kFwdSmem, max_smem, "ns_fwd")) return rc;
-    ns::ns_fwd_kernel<<<(unsigned)p.BH, kThreads, ns::kFwdSmem, ns_stream>>>(np);
+    if (ns_on_tensor_cores(a.shape.flags)) {
+      if (int rc = set_smem(nstc::ns_fwd_tc_kernel, nstc::kFwdSmem, max_smem, "ns_fwd")) return rc;
+      nstc::ns_fwd_tc_kernel<<<(unsigned)p.BH, nstc::kNsTcThreads, nstc::kFwdSmem, ns_stream>>>(np, a.device_status);
+    } else {
+      if (int rc = set_smem(ns::ns_fwd_kernel, ns::kFwdSmem, max_smem, "ns_fwd")) return rc;
+      ns::ns_fwd_kernel<<<(unsigned)p.BH, kThreads, ns::kFwdSmem, ns_stream>>>(np);
+    }
     if (L.end("ns_fwd")) return L.status;
     fork.end();
   } else {
@@ -573,8 +590,13 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
       np.dkt_a = w.dkt_a; np.dqt_ns = w.dqt_ns; np.dkt_tot = w.dkt_tot; np.spill = w.dK2;
       np.m = p.m; np.D = p.D; np.J = p.J; np.kappa = a.shape.kappa_star;
       np.rows_k = use_tc ? w.rows_k : nullptr; np.N = seg_N; np.scale = scale;
-      if (int rc = set_smem(ns::ns_bwd_kernel, ns::kBwdSmem, max_smem, "ns_bwd")) return rc;
-      ns::ns_bwd_kernel<<<(unsigned)p.BH, kThreads, ns::kBwdSmem, st>>>(np);
+      if (p.J >= 1 && ns_on_tensor_cores(a.shape.flags)) {
+        if (int rc = set_smem(nstc::ns_bwd_tc_kernel, nstc::kBwdSmem, max_smem, "ns_bwd")) return rc;
+        nstc::ns_bwd_tc_kernel<<<(unsigned)p.BH, nstc::kNsTcThreads, nstc::kBwdSmem, st>>>(np, a.device_status);
+      } else {
+        if (int rc = set_smem(ns::ns_bwd_kernel, ns::kBwdSmem, max_smem, "ns_bwd")) return rc;
+        ns::ns_bwd_kernel<<<(unsigned)p.BH, kThreads, ns::kBwdSmem, st>>>(np);
+      }
     }
     if (L.end("ns_bwd")) return L.status;
   } else {
@@ -969,7 +991,12 @@ int fnb_debug_pinv_forward(int64_t bh, int32_t m, int32_t J, float kappa, const 
   if (!k2 || !ns_iterates || !k2_inv) return fail(FNB_ERR_INVALID_ARGUMENT, "NULL tensor pointer");
   DeviceGuard g(device);
   if (!g.ok) return fail(FNB_ERR_CUDA, "cannot select CUDA device %d", device);
-  if (m <= ns::kN) {
+  if (m <= ns::kN && ns_on_tensor_cores(0)) {
+    FNB_CUDA(cudaFuncSetAttribute(nstc::ns_pinv_fwd_tc_debug_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  (int)nstc::kFwdSmem));
+    nstc::ns_pinv_fwd_tc_debug_kernel<<<(unsigned)bh, nstc::kNsTcThreads, nstc::kFwdSmem, (cudaStream_t)stream>>>(
+        k2, ns_iterates, k2_inv, m, J, kappa, nullptr);
+  } else if (m <= ns::kN) {
     FNB_CUDA(cudaFuncSetAttribute(ns::ns_pinv_fwd_debug_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                   (int)ns::kFwdSmem));
     ns::ns_pinv_fwd_debug_kernel<<<(unsigned)bh, kThreads, ns::kFwdSmem, (cudaStream_t)stream>>>(
@@ -989,7 +1016,12 @@ int fnb_debug_pinv_backward(int64_t bh, int32_t m, int32_t J, float kappa, const
   if (!k2 || !ns_iterates || !d_k2_inv || !d_k2) return fail(FNB_ERR_INVALID_ARGUMENT, "NULL tensor pointer");
   DeviceGuard g(device);
   if (!g.ok) return fail(FNB_ERR_CUDA, "cannot select CUDA device %d", device);
-  if (m <= ns::kN) {
+  if (m <= ns::kN && ns_on_tensor_cores(0)) {
+    FNB_CUDA(cudaFuncSetAttribute(nstc::ns_pinv_bwd_tc_debug_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  (int)nstc::kBwdSmem));
+    nstc::ns_pinv_bwd_tc_debug_kernel<<<(unsigned)bh, nstc::kNsTcThreads, nstc::kBwdSmem, (cudaStream_t)stream>>>(
+        k2, ns_iterates, d_k2_inv, d_k2, (float*)workspace, m, J, kappa, nullptr);
+  } else if (m <= ns::kN) {
     FNB_CUDA(cudaFuncSetAttribute(ns::ns_pinv_bwd_debug_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                   (int)ns::kBwdSmem));
     ns::ns_pinv_bwd_debug_kernel<<<(unsigned)bh, kThreads, ns::kBwdSmem, (cudaStream_t)stream>>>(

@@ -16,6 +16,11 @@ constexpr int kBuf = kN * kLd;  // floats per buffer
 
 enum { NN = 0, NT = 1, TN = 2 };
 
+// Barrier over the 256 threads that run the code of this file.  In the kernels of this file that
+// is the whole CTA; the tensor-core kernels add a ninth warp that only issues MMAs and must not
+// be counted, so a named barrier is used instead of __syncthreads().
+__device__ __forceinline__ void ns_sync() { asm volatile("bar.sync 7, 256;" ::: "memory"); }
+
 // C-tile of this thread for op(A) * op(B), all operands 64 x 64 in shared memory.
 //   NN: C = A B      rows ty+16i, cols 4tx+j
 //   NT: C = A B^T    rows ty+16i, cols tx+16j
@@ -85,7 +90,7 @@ __device__ __forceinline__ void mm(const float* __restrict__ A, const float* __r
       }
     }
   }
-  __syncthreads();
+  ns_sync();
 #pragma unroll
   for (int i = 0; i < 4; ++i)
 #pragma unroll
@@ -97,7 +102,7 @@ __device__ __forceinline__ void mm(const float* __restrict__ A, const float* __r
       else val = (j & 1) ? acc[i][j >> 1].y : acc[i][j >> 1].x;
       epi(r, c, val);
     }
-  __syncthreads();
+  ns_sync();
 }
 
 __device__ __forceinline__ void zero_buf(float* X) {
@@ -131,7 +136,7 @@ __device__ inline Norms norms(const float* X, int m, float* red) {
     for (int j = 0; j < m; ++j) rs += fabsf(X[i * kLd + j]);
     red[t] = rs;
   }
-  __syncthreads();
+  ns_sync();
   Norms out;
   {
     float best = red[0]; int bi = 0;
@@ -141,7 +146,7 @@ __device__ inline Norms norms(const float* X, int m, float* red) {
     for (int i = 1; i < m; ++i) if (red[kN + i] > best) { best = red[kN + i]; bi = i; }
     out.ninf = best; out.ir = bi;
   }
-  __syncthreads();
+  ns_sync();
   return out;
 }
 
@@ -174,7 +179,7 @@ __device__ inline void pinv_forward_smem(float* sm, float* red, float* iterates,
     bZ[r * kLd + c] = z;
     if (r < m && c < m) iterates[r * m + c] = z;
   }
-  __syncthreads();
+  ns_sync();
   for (int j = 0; j < J; ++j) {
     float* Zn = iterates + (size_t)(j + 1) * mm_;
     mm<NN>(A, bZ, [&](int r, int c, float acc) {
@@ -193,7 +198,7 @@ __device__ inline void pinv_forward_smem(float* sm, float* red, float* iterates,
     mm<NT>(bZ, bK2, [&](int r, int c, float acc) { if (r < m && c < m) k2inv[r * m + c] = acc; });
   } else {
     store_mat(k2inv, bZ, m);
-    __syncthreads();
+    ns_sync();
   }
 }
 
@@ -206,12 +211,9 @@ struct NsFwdParams {
   float kappa;
 };
 
-__global__ void __launch_bounds__(kThreads, 1) ns_fwd_kernel(NsFwdParams p) {
-  extern __shared__ float sm[];
-  __shared__ float red[2 * kN];
-  const int64_t bh = blockIdx.x;
+// S2 = Qt Kt^T straight from global memory, row softmax -> K2 (padded, in bK2 and in global), lse2.
+__device__ inline void s2_softmax(float* bK2, const NsFwdParams& p, int64_t bh) {
   const int m = p.m, D = p.D, t = threadIdx.x, tx = t & 15, ty = t >> 4;
-  float* bK2 = sm;
   const float* qt = p.qt + bh * m * D;
   const float* kt = p.kt + bh * m * D;
   // S2 tile straight from global (L2): rows ty+16i, cols tx+16j
@@ -244,7 +246,7 @@ __global__ void __launch_bounds__(kThreads, 1) ns_fwd_kernel(NsFwdParams p) {
 #pragma unroll
       for (int j = 0; j < 4; ++j) bK2[(ty + 16 * i) * kLd + tx + 16 * j] = acc[i][j];
   }
-  __syncthreads();
+  ns_sync();
   // row softmax, one warp per row; padded rows / columns become zero
   const int w = t >> 5, lane = t & 31;
   float* k2g = p.k2 + bh * m * m;
@@ -266,7 +268,15 @@ __global__ void __launch_bounds__(kThreads, 1) ns_fwd_kernel(NsFwdParams p) {
       if (lane == 0) p.lse2[bh * m + r] = mx + logf(sum);
     }
   }
-  __syncthreads();
+  ns_sync();
+}
+
+__global__ void __launch_bounds__(kThreads, 1) ns_fwd_kernel(NsFwdParams p) {
+  extern __shared__ float sm[];
+  __shared__ float red[2 * kN];
+  const int64_t bh = blockIdx.x;
+  const int m = p.m;
+  s2_softmax(sm, p, bh);
   pinv_forward_smem(sm, red, p.iterates + bh * (size_t)(p.J + 1) * m * m, p.k2inv + bh * m * m, m, p.J,
                     p.kappa);
 }
@@ -277,13 +287,68 @@ ns_pinv_fwd_debug_kernel(const float* k2, float* iterates, float* k2inv, int m, 
   __shared__ float red[2 * kN];
   const int64_t bh = blockIdx.x;
   load_mat(sm, k2 + bh * m * m, m);
-  __syncthreads();
+  ns_sync();
   pinv_forward_smem(sm, red, iterates + bh * (size_t)(J + 1) * m * m, k2inv + bh * m * m, m, J, kappa);
 }
 
 // ------------------------------------------------------------------------------------------
 constexpr int kBwdBufs = 12;
 constexpr size_t kBwdSmem = (size_t)kBwdBufs * kBuf * sizeof(float) + 1024;
+
+// Tail of the pseudoinverse backward, shared by the CUDA-core and the tensor-core loop: gradient
+// through Z0 = A^T / (||A||_1 ||A||_inf) (norm terms at the first-occurrence argmax), then through
+// the ridge wrap.  In: bdZ = dL/dZ_0, bdA = dL/dA accumulated over the iterations.  Out: dK2 in bdA.
+// bdM, bdT: scratch buffers.
+__device__ inline float* pinv_backward_tail(const float* bK2, const float* A, float* bdZ, float* bdA, float* bdM,
+                                            float* bdT, float* red, const float* spill, int m, float kappa) {
+  // Z0 = A^T / c,  c = ||A||_1 ||A||_inf
+  Norms na = norms(A, m, red);
+  const float craw = na.n1 * na.ninf;
+  const float cden = fmaxf(craw, 1e-12f);
+  float part = 0.f;
+  for (int idx = threadIdx.x; idx < kN * kN; idx += kThreads) {
+    int a = idx >> 6, b = idx & 63;
+    part += bdZ[a * kLd + b] * A[b * kLd + a];
+  }
+  for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = part;
+  ns_sync();
+  float S = 0.f;
+  for (int w = 0; w < kThreads / 32; ++w) S += red[w];
+  ns_sync();
+  const bool clamped = !(craw > 1e-12f);
+  const float col_term = clamped ? 0.f : -S * na.ninf / (cden * cden);
+  const float row_term = clamped ? 0.f : -S * na.n1 / (cden * cden);
+  for (int idx = threadIdx.x; idx < kN * kN; idx += kThreads) {
+    int r = idx >> 6, c = idx & 63;
+    if (r < m && c < m) {
+      const float a = A[r * kLd + c];
+      const float sg = a > 0.f ? 1.f : (a < 0.f ? -1.f : 0.f);
+      float g = bdA[r * kLd + c] + bdZ[c * kLd + r] / cden;
+      if (c == na.jc) g += sg * col_term;
+      if (r == na.ir) g += sg * row_term;
+      bdM[r * kLd + c] = g;              // dA complete (staged in bdM to avoid the transpose hazard)
+    } else {
+      bdM[r * kLd + c] = 0.f;
+    }
+  }
+  ns_sync();
+  if (kappa > 0.f) {
+    // dK2 = dK2_a + K2 (dA + dA^T)
+    for (int idx = threadIdx.x; idx < kN * kN; idx += kThreads) {
+      int r = idx >> 6, c = idx & 63;
+      bdT[r * kLd + c] = bdM[r * kLd + c] + bdM[c * kLd + r];
+    }
+    ns_sync();
+    mm<NN>(bK2, bdT, [&](int r, int c, float acc) {
+      bdA[r * kLd + c] = (r < m && c < m) ? acc + spill[r * m + c] : 0.f;
+    });
+  } else {
+    for (int idx = threadIdx.x; idx < kBuf; idx += kThreads) bdA[idx] = bdM[idx];
+    ns_sync();
+  }
+  return bdA;
+}
 
 // G = dL/d k2inv (global) -> dK2 = dL/d K2 left in shared buffer bdA (returned pointer).
 // spill: (m x m) floats of global scratch, used only with the ridge.
@@ -305,7 +370,7 @@ __device__ inline float* pinv_backward_smem(float* sm, float* red, const float* 
   load_mat(bK2, k2g, m);
   load_mat(bdZ, G, m);          // holds G until dZ_J is formed
   zero_buf(bdA);
-  __syncthreads();
+  ns_sync();
   const float* A = bK2;
   if (kappa > 0.f) {
     Norms nk = norms(bK2, m, red);
@@ -313,14 +378,14 @@ __device__ inline float* pinv_backward_smem(float* sm, float* red, const float* 
     mm<TN>(bK2, bK2, [&](int r, int c, float acc) { bA[r * kLd + c] = acc + ((r == c && r < m) ? lam : 0.f); });
     A = bA;
     load_mat(bZ, iterates + (size_t)J * mm_, m);
-    __syncthreads();
+    ns_sync();
     // dK2_a = G^T Z_J -> global spill; dZ_J = G K2
     mm<TN>(bdZ, bZ, [&](int r, int c, float acc) { if (r < m && c < m) spill[r * m + c] = acc; });
     mm<NN>(bdZ, bK2, [&](int r, int c, float acc) { bdZ[r * kLd + c] = acc; });
   }
   for (int j = J - 1; j >= 0; --j) {
     load_mat(bZ, iterates + (size_t)j * mm_, m);
-    __syncthreads();
+    ns_sync();
     mm<NN>(A, bZ, [&](int r, int c, float acc) {
       bM[r * kLd + c] = acc;
       bU[r * kLd + c] = ((r == c && r < m) ? 7.f : 0.f) - acc;
@@ -336,53 +401,7 @@ __device__ inline float* pinv_backward_smem(float* sm, float* red, const float* 
     mm<NT>(bdM, bZ, [&](int r, int c, float acc) { bdA[r * kLd + c] += acc; });                  // dA += dM Z^T
     mm<TN>(A, bdM, [&](int r, int c, float acc) { bdZ[r * kLd + c] = bT[r * kLd + c] + acc; });  // dZ_outer + A^T dM
   }
-  // Z0 = A^T / c,  c = ||A||_1 ||A||_inf
-  Norms na = norms(A, m, red);
-  const float craw = na.n1 * na.ninf;
-  const float cden = fmaxf(craw, 1e-12f);
-  float part = 0.f;
-  for (int idx = threadIdx.x; idx < kN * kN; idx += kThreads) {
-    int a = idx >> 6, b = idx & 63;
-    part += bdZ[a * kLd + b] * A[b * kLd + a];
-  }
-  for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
-  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = part;
-  __syncthreads();
-  float S = 0.f;
-  for (int w = 0; w < kThreads / 32; ++w) S += red[w];
-  __syncthreads();
-  const bool clamped = !(craw > 1e-12f);
-  const float col_term = clamped ? 0.f : -S * na.ninf / (cden * cden);
-  const float row_term = clamped ? 0.f : -S * na.n1 / (cden * cden);
-  for (int idx = threadIdx.x; idx < kN * kN; idx += kThreads) {
-    int r = idx >> 6, c = idx & 63;
-    if (r < m && c < m) {
-      const float a = A[r * kLd + c];
-      const float sg = a > 0.f ? 1.f : (a < 0.f ? -1.f : 0.f);
-      float g = bdA[r * kLd + c] + bdZ[c * kLd + r] / cden;
-      if (c == na.jc) g += sg * col_term;
-      if (r == na.ir) g += sg * row_term;
-      bdM[r * kLd + c] = g;              // dA complete (staged in bdM to avoid the transpose hazard)
-    } else {
-      bdM[r * kLd + c] = 0.f;
-    }
-  }
-  __syncthreads();
-  if (kappa > 0.f) {
-    // dK2 = dK2_a + K2 (dA + dA^T)
-    for (int idx = threadIdx.x; idx < kN * kN; idx += kThreads) {
-      int r = idx >> 6, c = idx & 63;
-      bdT[r * kLd + c] = bdM[r * kLd + c] + bdM[c * kLd + r];
-    }
-    __syncthreads();
-    mm<NN>(bK2, bdT, [&](int r, int c, float acc) {
-      bdA[r * kLd + c] = (r < m && c < m) ? acc + spill[r * m + c] : 0.f;
-    });
-  } else {
-    for (int idx = threadIdx.x; idx < kBuf; idx += kThreads) bdA[idx] = bdM[idx];
-    __syncthreads();
-  }
-  return bdA;
+  return pinv_backward_tail(bK2, A, bdZ, bdA, bdM, bdT, red, spill, m, kappa);
 }
 
 __global__ void __launch_bounds__(kThreads, 1)
@@ -409,14 +428,10 @@ struct NsBwdParams {
   float kappa;
 };
 
-__global__ void __launch_bounds__(kThreads, 1) ns_bwd_kernel(NsBwdParams p) {
-  extern __shared__ float sm[];
-  __shared__ float red[2 * kN];
-  const int64_t bh = blockIdx.x;
-  const int m = p.m, D = p.D, t = threadIdx.x, mm_ = m * m, md = m * D;
-  float* dK2 = pinv_backward_smem(sm, red, p.k2 + bh * mm_, p.iterates + bh * (size_t)(p.J + 1) * mm_,
-                                  p.G + bh * mm_, p.spill + bh * mm_, m, p.J, p.kappa);
-  const float* bK2 = sm;
+// After the pseudoinverse backward: softmax-2 Jacobian and the landmark gradients.
+// bK2: K2 (padded shared buffer); dK2: dL/dK2 (padded shared buffer, overwritten with dS2).
+__device__ inline void ns_bwd_finish(const NsBwdParams& p, int64_t bh, const float* bK2, float* dK2) {
+  const int m = p.m, D = p.D, t = threadIdx.x, md = m * D;
   // softmax-2 Jacobian in place: dS2 = K2 o (dK2 - rowsum(dK2 o K2))
   const int w = t >> 5, lane = t & 31;
   for (int r = w; r < kN; r += kThreads / 32) {
@@ -427,7 +442,7 @@ __global__ void __launch_bounds__(kThreads, 1) ns_bwd_kernel(NsBwdParams p) {
     dK2[r * kLd + lane] = k0 * (a0 - s);
     dK2[r * kLd + lane + 32] = k1 * (a1 - s);
   }
-  __syncthreads();
+  ns_sync();
   // dqt_ns = dS2 Kt ; dkt_tot = dkt_a + dS2^T Qt.  Thread owns 4 consecutive d of one landmark row.
   const float* kt = p.kt + bh * md;
   const float* qt = p.qt + bh * md;
@@ -455,6 +470,17 @@ __global__ void __launch_bounds__(kThreads, 1) ns_bwd_kernel(NsBwdParams p) {
       *reinterpret_cast<float4*>(p.rows_k + bh * md + l * D + d) = make_float4(b.x * f, b.y * f, b.z * f, b.w * f);
     }
   }
+}
+
+
+__global__ void __launch_bounds__(kThreads, 1) ns_bwd_kernel(NsBwdParams p) {
+  extern __shared__ float sm[];
+  __shared__ float red[2 * kN];
+  const int64_t bh = blockIdx.x;
+  const int m = p.m, mm_ = m * m;
+  float* dK2 = pinv_backward_smem(sm, red, p.k2 + bh * mm_, p.iterates + bh * (size_t)(p.J + 1) * mm_,
+                                  p.G + bh * mm_, p.spill + bh * mm_, m, p.J, p.kappa);
+  ns_bwd_finish(p, bh, sm, dK2);
 }
 
 }  // namespace ns
