@@ -568,6 +568,10 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
   // ---- landmark-sized middle ------------------------------------------------------------------
   if (S.run(1)) {
   if (smem_ns) {
+    // With head_dim 64 on the tensor-core path the reduction of the pass-A partials and the two
+    // products that follow run inside the Newton-Schulz backward kernel.
+    const bool fused_mid = use_tc && p.D == 64 && p.J >= 1 && ns_on_tensor_cores(a.shape.flags);
+    if (!fused_mid) {
     L.begin();
     {
       BwdMid1Params mp;
@@ -583,6 +587,7 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
       kern<<<(unsigned)p.BH, kThreads, sm, st>>>(mp);
     }
     if (L.end("bwd_mid1")) return L.status;
+    }
     L.begin();
     {
       ns::NsBwdParams np;
@@ -592,7 +597,13 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
       np.rows_k = use_tc ? w.rows_k : nullptr; np.N = seg_N; np.scale = scale;
       if (p.J >= 1 && ns_on_tensor_cores(a.shape.flags)) {
         if (int rc = set_smem(nstc::ns_bwd_tc_kernel, nstc::kBwdSmem, max_smem, "ns_bwd")) return rc;
-        nstc::ns_bwd_tc_kernel<<<(unsigned)p.BH, nstc::kNsTcThreads, nstc::kBwdSmem, st>>>(np, a.device_status);
+        nstc::BwdHeadParams hp{};
+        if (fused_mid) {
+          hp.partA = partA_src; hp.nchunk = partA_chunks; hp.k2inv = a.k2_inv; hp.bmat = a.bmat;
+          hp.dkt_a = w.dkt_a; hp.D3 = w.D3; hp.do3n = do3n; hp.do3_scale = w.do3_scale; hp.qt16 = qt16;
+          hp.qt_mul = scale * tc::kLog2e; hp.dtype = a.shape.dtype; hp.MP = MP;
+        }
+        nstc::ns_bwd_tc_kernel<<<(unsigned)p.BH, nstc::kNsTcThreads, nstc::kBwdSmem, st>>>(np, hp, a.device_status);
       } else {
         if (int rc = set_smem(ns::ns_bwd_kernel, ns::kBwdSmem, max_smem, "ns_bwd")) return rc;
         ns::ns_bwd_kernel<<<(unsigned)p.BH, kThreads, ns::kBwdSmem, st>>>(np);

@@ -123,29 +123,56 @@ __device__ __forceinline__ void store_mat(float* g, const float* X, int m) {
 }
 
 struct Norms { float n1, ninf; int jc, ir; };
-// max column / row abs-sum with first-occurrence argmax; red: 128 floats of shared scratch
+constexpr int kRedFloats = 6 * kN;   // shared scratch of norms()
+// Max column / row abs-sum of the padded buffer X (zero outside the leading m x m block) with
+// first-occurrence argmax.  All 256 threads take part; red: kRedFloats floats of shared scratch.
 __device__ inline Norms norms(const float* X, int m, float* red) {
-  const int t = threadIdx.x;
-  if (t < kN) {
-    float cs = 0.f;
-    for (int i = 0; i < m; ++i) cs += fabsf(X[i * kLd + t]);
-    red[t] = cs;
-  } else if (t < 2 * kN) {
-    const int i = t - kN;
+  const int t = threadIdx.x, lane = t & 31, w = t >> 5;
+  {
+    // row sums: thread = (row, 16-column quarter); the four quarters sit in adjacent lanes
+    const int r = t >> 2, q = t & 3;
     float rs = 0.f;
-    for (int j = 0; j < m; ++j) rs += fabsf(X[i * kLd + j]);
-    red[t] = rs;
+#pragma unroll
+    for (int i = 0; i < 16; i += 4) {
+      const float4 x = *reinterpret_cast<const float4*>(X + r * kLd + 16 * q + i);
+      rs += fabsf(x.x) + fabsf(x.y) + fabsf(x.z) + fabsf(x.w);
+    }
+    rs += __shfl_xor_sync(0xffffffffu, rs, 1);
+    rs += __shfl_xor_sync(0xffffffffu, rs, 2);
+    if (q == 0) red[kN + r] = rs;
+    // column sums: thread = (column, 16-row block), partial sums combined below
+    const int c = t & 63, blk = t >> 6;
+    float cs = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) cs += fabsf(X[(16 * blk + i) * kLd + c]);
+    red[2 * kN + blk * kN + c] = cs;
+  }
+  ns_sync();
+  if (w < 2) {
+    // warp 0: columns, warp 1: rows; each lane owns entries lane and lane + 32
+    float v0, v1;
+    if (w == 0) {
+      v0 = red[2 * kN + lane] + red[3 * kN + lane] + red[4 * kN + lane] + red[5 * kN + lane];
+      v1 = red[2 * kN + lane + 32] + red[3 * kN + lane + 32] + red[4 * kN + lane + 32] + red[5 * kN + lane + 32];
+    } else {
+      v0 = red[kN + lane];
+      v1 = red[kN + lane + 32];
+    }
+    float best = (lane < m) ? v0 : -1.f;
+    int bi = lane;
+    if (lane + 32 < m && v1 > best) { best = v1; bi = lane + 32; }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+    }
+    if (lane == 0) { red[2 * w] = best; red[2 * w + 1] = __int_as_float(bi); }
   }
   ns_sync();
   Norms out;
-  {
-    float best = red[0]; int bi = 0;
-    for (int j = 1; j < m; ++j) if (red[j] > best) { best = red[j]; bi = j; }
-    out.n1 = best; out.jc = bi;
-    best = red[kN]; bi = 0;
-    for (int i = 1; i < m; ++i) if (red[kN + i] > best) { best = red[kN + i]; bi = i; }
-    out.ninf = best; out.ir = bi;
-  }
+  out.n1 = red[0]; out.jc = __float_as_int(red[1]);
+  out.ninf = red[2]; out.ir = __float_as_int(red[3]);
   ns_sync();
   return out;
 }
@@ -211,6 +238,8 @@ struct NsFwdParams {
   float kappa;
 };
 
+__device__ inline void softmax_rows(float* bK2, const NsFwdParams& p, int64_t bh);
+
 // S2 = Qt Kt^T straight from global memory, row softmax -> K2 (padded, in bK2 and in global), lse2.
 __device__ inline void s2_softmax(float* bK2, const NsFwdParams& p, int64_t bh) {
   const int m = p.m, D = p.D, t = threadIdx.x, tx = t & 15, ty = t >> 4;
@@ -247,7 +276,13 @@ __device__ inline void s2_softmax(float* bK2, const NsFwdParams& p, int64_t bh) 
       for (int j = 0; j < 4; ++j) bK2[(ty + 16 * i) * kLd + tx + 16 * j] = acc[i][j];
   }
   ns_sync();
-  // row softmax, one warp per row; padded rows / columns become zero
+  softmax_rows(bK2, p, bh);
+}
+
+// Row softmax of the scores in bK2 (one warp per row; padded rows / columns become zero)
+// -> K2 in bK2 and in global memory, lse2.
+__device__ inline void softmax_rows(float* bK2, const NsFwdParams& p, int64_t bh) {
+  const int m = p.m, t = threadIdx.x;
   const int w = t >> 5, lane = t & 31;
   float* k2g = p.k2 + bh * m * m;
   for (int r = w; r < kN; r += kThreads / 32) {
@@ -273,7 +308,7 @@ __device__ inline void s2_softmax(float* bK2, const NsFwdParams& p, int64_t bh) 
 
 __global__ void __launch_bounds__(kThreads, 1) ns_fwd_kernel(NsFwdParams p) {
   extern __shared__ float sm[];
-  __shared__ float red[2 * kN];
+  __shared__ float red[kRedFloats];
   const int64_t bh = blockIdx.x;
   const int m = p.m;
   s2_softmax(sm, p, bh);
@@ -284,7 +319,7 @@ __global__ void __launch_bounds__(kThreads, 1) ns_fwd_kernel(NsFwdParams p) {
 __global__ void __launch_bounds__(kThreads, 1)
 ns_pinv_fwd_debug_kernel(const float* k2, float* iterates, float* k2inv, int m, int J, float kappa) {
   extern __shared__ float sm[];
-  __shared__ float red[2 * kN];
+  __shared__ float red[kRedFloats];
   const int64_t bh = blockIdx.x;
   load_mat(sm, k2 + bh * m * m, m);
   ns_sync();
@@ -408,7 +443,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 ns_pinv_bwd_debug_kernel(const float* k2, const float* iterates, const float* G, float* dK2, float* spill,
                          int m, int J, float kappa) {
   extern __shared__ float sm[];
-  __shared__ float red[2 * kN];
+  __shared__ float red[kRedFloats];
   const int64_t bh = blockIdx.x;
   float* out = pinv_backward_smem(sm, red, k2 + bh * m * m, iterates + bh * (size_t)(J + 1) * m * m,
                                   G + bh * m * m, spill + bh * m * m, m, J, kappa);
@@ -475,7 +510,7 @@ __device__ inline void ns_bwd_finish(const NsBwdParams& p, int64_t bh, const flo
 
 __global__ void __launch_bounds__(kThreads, 1) ns_bwd_kernel(NsBwdParams p) {
   extern __shared__ float sm[];
-  __shared__ float red[2 * kN];
+  __shared__ float red[kRedFloats];
   const int64_t bh = blockIdx.x;
   const int m = p.m, mm_ = m * m;
   float* dK2 = pinv_backward_smem(sm, red, p.k2 + bh * mm_, p.iterates + bh * (size_t)(p.J + 1) * mm_,

@@ -25,6 +25,7 @@
 // FP32 CUDA-core code of ns_kernels.cuh, run on FP32 staging buffers that alias the tile slots.
 #pragma once
 #include "ns_kernels.cuh"
+#include "small_kernels.cuh"
 #include "tc_common.cuh"
 
 namespace fnb {
@@ -189,9 +190,11 @@ __device__ __forceinline__ void tiles_ready(Ctx& c) {
 }
 // compute side: wait for MMA group g (0 or 1) of the current batch
 __device__ __forceinline__ void wait_group(Ctx& c, int g, int where) {
+  NS_TRACE2();
   if (!mbar_wait(c.bar + g, c.phase[g], c.ab, where)) c.failed = true;
   c.phase[g] ^= 1u;
   tc_fence_after();
+  NS_TRACE2();
 }
 // issuing thread: wait for the operands, issue two groups of products, one commit each
 template <class IssueA, class IssueB>
@@ -218,14 +221,19 @@ __device__ __forceinline__ void mma_single(Ctx& c, int where, Issue issue) {
 // Result of the accumulator at TMEM column `col`: after the call v[0..15] holds columns
 // c.col0 .. c.col0+15 of row c.row.  Every thread must call (warp-wide TMEM loads, pair barriers).
 __device__ __forceinline__ void acc_result(const Ctx& c, uint32_t col, float* v) {
-  float s[32], t[32], u[32];
+  float s[32], t[32];
   const uint32_t a = c.tmem + col + c.lane_off;
   tmem_ld32(a, s);                          // lanes 0..63: x1y1 ; lanes 64..127: x0y1
   tmem_ld32(a + 64, t);                     //              x1y0 ;                x0y0
-  tmem_ld32(a + (c.part ? 128 : 192), u);   //              x0y2 ;                x2y0
   tmem_ld_wait();
 #pragma unroll
-  for (int i = 0; i < 32; ++i) s[i] += t[i] + u[i];
+  for (int i = 0; i < 32; ++i) s[i] += t[i];
+  NS_TRACE2();
+  tmem_ld32(a + (c.part ? 128 : 192), t);   //              x0y2 ;                x2y0
+  tmem_ld_wait();
+#pragma unroll
+  for (int i = 0; i < 32; ++i) s[i] += t[i];
+  NS_TRACE2();
   // hand the 16 columns the partner finalises over, take the partner's share of mine
   // (part is warp-uniform; the two branches keep every register index a constant)
   float* rowp = c.xch + c.row * kLd + c.c32;
@@ -253,6 +261,7 @@ __device__ __forceinline__ void acc_result(const Ctx& c, uint32_t col, float* v)
     }
   }
   named_barrier(c.pair_bar, 64);   // the partner has read: the exchange buffer may be reused
+  NS_TRACE2();
 }
 
 // v[i] = s * v[i] + (diagonal ? d : 0), diagonal restricted to the leading m x m block
@@ -331,10 +340,11 @@ __device__ __forceinline__ void ctx_close(Ctx& c, uint32_t cols) {
 __device__ __forceinline__ float* fwd_staging(const Ctx& c) { return reinterpret_cast<float*>(c.slot(2)); }
 
 // issuing thread: the products of the forward in the order the compute warps consume them
-__device__ inline void pinv_forward_issue(Ctx& c, int J, float kappa) {
+__device__ inline void pinv_forward_issue(Ctx& c, int J, float kappa, bool scores) {
   const uint32_t sA = c.slot_addr(0), sZ = c.slot_addr(1), sM = c.slot_addr(2), sU = c.slot_addr(3),
                  sV = c.slot_addr(4), sT = c.slot_addr(5), sK2 = c.slot_addr(6);
   const uint32_t acc0 = c.tmem + kAcc0;
+  if (scores) mma_single(c, 0x20ff, [&] { issue_product(acc0, left(sA), right_t(sZ), false); });   // Qt Kt^T
   for (int j = 0; j < J; ++j) {
     mma_single(c, 0x2100, [&] { issue_product(acc0, left(sA), right(sZ), false); });
     mma_single(c, 0x2101, [&] { issue_product(acc0, left(sM), right(sU), false); });
@@ -417,21 +427,40 @@ __device__ inline void pinv_forward_tc(Ctx& c, float* red, float* iterates, floa
   }
 }
 
+// Scores S2 = Qt Kt^T for head_dim 64 as one split product (Qt in slot 0, Kt in slot 1, both
+// overwritten afterwards), then the FP32 row softmax.
+__device__ inline void s2_softmax_tc(Ctx& c, const ns::NsFwdParams& p, int64_t bh) {
+  const int m = p.m, D = p.D;
+  float q[16], k[16], v[16];
+  load_global16(p.qt + bh * m * D, m, D, D, q);
+  load_global16(p.kt + bh * m * D, m, D, D, k);
+  store_set16(c.slot(0), q);
+  store_set16(c.slot(1), k);
+  tiles_ready(c);
+  wait_group(c, 0, 0x210f);
+  acc_result(c, kAcc0, v);
+  store_row16(c, fwd_staging(c), v);
+  ns::ns_sync();
+  ns::softmax_rows(fwd_staging(c), p, bh);
+}
+
 __global__ void __launch_bounds__(kNsTcThreads, 1) ns_fwd_tc_kernel(ns::NsFwdParams p, int* status) {
   extern __shared__ uint8_t dyn_smem[];
-  __shared__ float red[2 * kN];
+  __shared__ float red[ns::kRedFloats];
   __shared__ Shared sh;
   Ctx c;
   ctx_open(c, sh, dyn_smem, kFwdSlots, status, kFwdTmemCols);
   const int64_t bh = blockIdx.x;
   const int m = p.m;
+  const bool scores_tc = p.D == kN;
   if (is_compute()) {
     NS_TRACE();
-    ns::s2_softmax(fwd_staging(c), p, bh);
+    if (scores_tc) s2_softmax_tc(c, p, bh);
+    else ns::s2_softmax(fwd_staging(c), p, bh);
     NS_TRACE();
     pinv_forward_tc(c, red, p.iterates + bh * (size_t)(p.J + 1) * m * m, p.k2inv + bh * m * m, m, p.J, p.kappa);
   } else if (is_issuer()) {
-    pinv_forward_issue(c, p.J, p.kappa);
+    pinv_forward_issue(c, p.J, p.kappa, scores_tc);
   }
   ctx_close(c, kFwdTmemCols);
 }
@@ -440,7 +469,7 @@ __global__ void __launch_bounds__(kNsTcThreads, 1)
 ns_pinv_fwd_tc_debug_kernel(const float* k2, float* iterates, float* k2inv, int m, int J, float kappa,
                             int* status) {
   extern __shared__ uint8_t dyn_smem[];
-  __shared__ float red[2 * kN];
+  __shared__ float red[ns::kRedFloats];
   __shared__ Shared sh;
   Ctx c;
   ctx_open(c, sh, dyn_smem, kFwdSlots, status, kFwdTmemCols);
@@ -450,7 +479,7 @@ ns_pinv_fwd_tc_debug_kernel(const float* k2, float* iterates, float* k2inv, int 
     ns::ns_sync();
     pinv_forward_tc(c, red, iterates + bh * (size_t)(J + 1) * m * m, k2inv + bh * m * m, m, J, kappa);
   } else if (is_issuer()) {
-    pinv_forward_issue(c, J, kappa);
+    pinv_forward_issue(c, J, kappa, false);
   }
   ctx_close(c, kFwdTmemCols);
 }
@@ -477,7 +506,13 @@ __device__ __forceinline__ float* bwd_tail(const Ctx& c, int i) {
 }
 
 // issuing thread
-__device__ inline void pinv_backward_issue(Ctx& c, int J, bool finish) {
+__device__ inline void pinv_backward_issue(Ctx& c, int J, bool finish, bool head) {
+  if (head) {
+    // dO3 = K2inv^T dstep2 | dK2inv = dstep2 Bmat^T   (slots 3 K2inv, 4 dstep2, 6 Bmat)
+    const uint32_t sKi = c.slot_addr(3), sDs = c.slot_addr(4), sBm = c.slot_addr(6);
+    mma_batch(c, 0x21f0, [&] { issue_product(c.tmem + kAcc0, left_t(sKi), right(sDs), false); },
+              [&] { issue_product(c.tmem + kAcc1, left(sDs), right_t(sBm), false); });
+  }
   const uint32_t sA = c.slot_addr(0), sZ = c.slot_addr(1), sdZ = c.slot_addr(2), sM = c.slot_addr(3),
                  sU = c.slot_addr(4), sdT = c.slot_addr(5), sV = c.slot_addr(6), sT = c.slot_addr(6),
                  sdV = c.slot_addr(7), sdM = c.slot_addr(7);
@@ -509,8 +544,13 @@ __device__ inline void pinv_backward_issue(Ctx& c, int J, bool finish) {
 }
 
 // compute warps.  Requires J >= 1.  Returns dK2 (padded FP32 buffer); K2 is left in bwd_tail(c, 0).
-__device__ inline float* pinv_backward_tc(Ctx& c, float* red, const float* k2g, const float* iterates,
-                                          const float* G, float* spill, int m, int J, float kappa) {
+// before_tail() runs between the iterations and the FP32 tail (a place to start global loads
+// whose latency the tail hides).
+template <class BeforeTail>
+__device__ __forceinline__ float* pinv_backward_tc(Ctx& c, float* red, const float* k2g, const float* iterates,
+                                                   const float* G, float* spill, int m, int J, float kappa,
+                                                   BeforeTail before_tail) {
+  // G == nullptr: dL/dk2inv is already in place (slot 2 without the ridge, staging buffer 3 with it)
   const int mm_ = m * m;
   float znext[16];
   load_global16(iterates + (size_t)(J - 1) * mm_, m, m, m, znext);
@@ -520,7 +560,7 @@ __device__ inline float* pinv_backward_tc(Ctx& c, float* red, const float* k2g, 
     float* bZ = bwd_stage(c, 2);
     float* bdZ = bwd_stage(c, 3);
     ns::load_mat(bK2, k2g, m);
-    ns::load_mat(bdZ, G, m);
+    if (G) ns::load_mat(bdZ, G, m);
     ns::ns_sync();
     Norms nk = ns::norms(bK2, m, red);
     const float lam = nk.n1 * nk.ninf / kappa;
@@ -534,21 +574,24 @@ __device__ inline float* pinv_backward_tc(Ctx& c, float* red, const float* k2g, 
     convert_buf(c.slot(2), bdZ);
   } else {
     // A = K2 and dZ_J = G go straight from global memory into their tiles
-    float a[16], g[16];
+    float a[16];
     load_global16(k2g, m, m, m, a);
-    load_global16(G, m, m, m, g);
+    if (G) {
+      float g[16];
+      load_global16(G, m, m, m, g);
+      store_set16(c.slot(2), g);
+    }
     store_set16(c.slot(0), a);
-    store_set16(c.slot(2), g);
   }
   store_set16(c.slot(1), znext);
   NS_TRACE();
-  float v[16], dA[16], k2r[16];
+  float v[16], dA[16];
 #pragma unroll
   for (int i = 0; i < 16; ++i) dA[i] = 0.f;
   for (int j = J - 1; j >= 0; --j) {
     tiles_ready(c);
-    if (j > 0) load_global16(iterates + (size_t)(j - 1) * mm_, m, m, m, znext);
-    else load_global16(k2g, m, m, m, k2r);          // K2 for the FP32 tail
+    // next iterate; in the last iteration K2 for the FP32 tail instead
+    load_global16(j > 0 ? iterates + (size_t)(j - 1) * mm_ : k2g, m, m, m, znext);
     wait_group(c, 0, 0x2210);
     acc_result(c, kAcc0, v);
     split_store16(c.slot(3), c.row, c.col0, v);
@@ -591,10 +634,11 @@ __device__ inline float* pinv_backward_tc(Ctx& c, float* red, const float* k2g, 
     if (j > 0) store_set16(c.slot(1), znext);
     NS_TRACE();
   }
+  before_tail();
   store_row16(c, bwd_tail(c, 3), dA);
   float* bK2 = bwd_tail(c, 0);
   float* bA = bwd_tail(c, 1);
-  store_buf16(bK2, k2r);
+  store_buf16(bK2, znext);
   ns::ns_sync();
   NS_TRACE();
   const float* A = bK2;
@@ -612,17 +656,17 @@ __global__ void __launch_bounds__(kNsTcThreads, 1)
 ns_pinv_bwd_tc_debug_kernel(const float* k2, const float* iterates, const float* G, float* dK2, float* spill,
                             int m, int J, float kappa, int* status) {
   extern __shared__ uint8_t dyn_smem[];
-  __shared__ float red[2 * kN];
+  __shared__ float red[ns::kRedFloats];
   __shared__ Shared sh;
   Ctx c;
   ctx_open(c, sh, dyn_smem, kBwdSlots, status, kBwdTmemCols);
   const int64_t bh = blockIdx.x;
   if (is_compute()) {
     float* out = pinv_backward_tc(c, red, k2 + bh * m * m, iterates + bh * (size_t)(J + 1) * m * m, G + bh * m * m,
-                                  spill + bh * m * m, m, J, kappa);
+                                  spill + bh * m * m, m, J, kappa, [] {});
     if (!c.failed) ns::store_mat(dK2 + bh * m * m, out, m);
   } else if (is_issuer()) {
-    pinv_backward_issue(c, J, false);
+    pinv_backward_issue(c, J, false, false);
   }
   ctx_close(c, kBwdTmemCols);
 }
@@ -630,21 +674,25 @@ ns_pinv_bwd_tc_debug_kernel(const float* k2, const float* iterates, const float*
 // Softmax-2 Jacobian and the landmark gradients after the pseudoinverse backward, for head_dim 64:
 // dqt_ns = dS2 Kt and dkt_tot = dkt_a + dS2^T Qt as one more batch of split products.
 // bK2, dK2: padded FP32 buffers inside the tail area (slots 0..4); slots 5..7 take the operands.
-__device__ inline void ns_bwd_finish_tc(Ctx& c, const ns::NsBwdParams& p, int64_t bh, const float* bK2, float* dK2) {
-  const int m = p.m, D = p.D, md = m * D, t = threadIdx.x;
-  float kt[16], qt[16], da[16];
-  load_global16(p.kt + bh * md, m, D, D, kt);
-  load_global16(p.qt + bh * md, m, D, D, qt);
-  {
-    // dkt_a for the row segment this thread finalises
-    const float* src = p.dkt_a + bh * md + (size_t)c.row * D + c.col0;
+struct FinishOperands { float kt[16], qt[16], da[16]; };
+// global loads of the finishing step, issued early so that their latency hides behind the tail
+__device__ __forceinline__ void finish_load(const Ctx& c, const ns::NsBwdParams& p, int64_t bh, FinishOperands& f) {
+  const int m = p.m, D = p.D, md = m * D;
+  load_global16(p.kt + bh * md, m, D, D, f.kt);
+  load_global16(p.qt + bh * md, m, D, D, f.qt);
+  // dkt_a for the row segment this thread finalises
+  const float* src = p.dkt_a + bh * md + (size_t)c.row * D + c.col0;
 #pragma unroll
-    for (int i = 0; i < 16; i += 4) {
-      float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (c.row < m) x = *reinterpret_cast<const float4*>(src + i);
-      da[i] = x.x; da[i + 1] = x.y; da[i + 2] = x.z; da[i + 3] = x.w;
-    }
+  for (int i = 0; i < 16; i += 4) {
+    float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (c.row < m) x = *reinterpret_cast<const float4*>(src + i);
+    f.da[i] = x.x; f.da[i + 1] = x.y; f.da[i + 2] = x.z; f.da[i + 3] = x.w;
   }
+}
+__device__ inline void ns_bwd_finish_tc(Ctx& c, const ns::NsBwdParams& p, int64_t bh, const float* bK2, float* dK2,
+                                        const FinishOperands& f) {
+  const int m = p.m, D = p.D, md = m * D, t = threadIdx.x;
+  const float* kt = f.kt; const float* qt = f.qt; const float* da = f.da;
   // softmax-2 Jacobian in place: dS2 = K2 o (dK2 - rowsum(dK2 o K2))
   const int w = t >> 5, lane = t & 31;
   for (int r = w; r < kN; r += kComputeThreads / 32) {
@@ -679,9 +727,130 @@ __device__ inline void ns_bwd_finish_tc(Ctx& c, const ns::NsBwdParams& p, int64_
   }
 }
 
-__global__ void __launch_bounds__(kNsTcThreads, 1) ns_bwd_tc_kernel(ns::NsBwdParams p, int* status) {
+// Head of the fused backward middle stage (head_dim 64): reduce the per-CTA partials of the
+// softmax-1 pass, then dO3 = K2inv^T dstep2 (-> D3, normalised 16-bit copy for the column pass) and
+// dK2inv = dstep2 Bmat^T, which lands where the pseudoinverse backward expects dL/dk2inv.
+struct BwdHeadParams {
+  const float* partA;         // [BH][nchunk][2][m][D]: dstep2 partials, dKt partials
+  int nchunk;
+  const float* k2inv; const float* bmat;
+  float* dkt_a;               // [BH][m][D] out
+  float* D3;                  // [BH][m] out
+  void* do3n;                 // [BH][MP][D] 16-bit out = dO3 / do3_scale
+  float* do3_scale;           // [BH] out
+  void* qt16;                 // [BH][MP][D] 16-bit out = qt_mul * Qt
+  float qt_mul;
+  int dtype, MP;
+};
+
+__device__ inline void bwd_head_tc(Ctx& c, float* red, const ns::NsBwdParams& p, const BwdHeadParams& h, int64_t bh) {
+  const int m = p.m, D = p.D, md = m * D, t = threadIdx.x;
+  const int r = t >> 2, c0 = (t & 3) * 16;
+  NS_TRACE();
+  // reduce the partials: this thread owns row r, columns c0 .. c0+15 of both sums
+  float ds[16], dk[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) { ds[i] = 0.f; dk[i] = 0.f; }
+  if (r < m) {
+    const float* base = h.partA + bh * (int64_t)h.nchunk * 2 * md + (size_t)r * D + c0;
+    constexpr int CB = 3;
+    for (int ch0 = 0; ch0 < h.nchunk; ch0 += CB) {
+      float4 x[CB][4], y[CB][4];
+#pragma unroll
+      for (int i = 0; i < CB; ++i) {
+        const int ch = min(ch0 + i, h.nchunk - 1);
+        const float4* s0 = reinterpret_cast<const float4*>(base + (size_t)ch * 2 * md);
+        const float4* s1 = reinterpret_cast<const float4*>(base + (size_t)ch * 2 * md + md);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) { x[i][q] = s0[q]; y[i][q] = s1[q]; }
+      }
+#pragma unroll
+      for (int i = 0; i < CB; ++i)
+        if (ch0 + i < h.nchunk) {
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            ds[4 * q] += x[i][q].x; ds[4 * q + 1] += x[i][q].y; ds[4 * q + 2] += x[i][q].z; ds[4 * q + 3] += x[i][q].w;
+            dk[4 * q] += y[i][q].x; dk[4 * q + 1] += y[i][q].y; dk[4 * q + 2] += y[i][q].z; dk[4 * q + 3] += y[i][q].w;
+          }
+        }
+    }
+    float4* out = reinterpret_cast<float4*>(h.dkt_a + bh * md + (size_t)r * D + c0);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) out[q] = make_float4(dk[4 * q], dk[4 * q + 1], dk[4 * q + 2], dk[4 * q + 3]);
+  }
+  NS_TRACE();
+  store_set16(c.slot(4), ds);
+  {
+    float ki[16], bm[16];
+    load_global16(h.k2inv + bh * m * m, m, m, m, ki);
+    load_global16(h.bmat + bh * md, m, D, D, bm);
+    store_set16(c.slot(3), ki);
+    store_set16(c.slot(6), bm);
+  }
+  tiles_ready(c);
+  NS_TRACE();
+  // operands of this thread's share of the epilogue: Bmat segment for D3, Qt row for the copy
+  float bseg[16], qrow[16];
+  {
+    const float* src = h.bmat + bh * md + (size_t)c.row * D + c.col0;
+#pragma unroll
+    for (int i = 0; i < 16; i += 4) {
+      float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (c.row < m) x = *reinterpret_cast<const float4*>(src + i);
+      bseg[i] = x.x; bseg[i + 1] = x.y; bseg[i + 2] = x.z; bseg[i + 3] = x.w;
+    }
+  }
+  load_global16(p.qt + bh * md, m, D, D, qrow);
+  float v[16];
+  wait_group(c, 0, 0x21f1);
+  acc_result(c, kAcc0, v);                       // dO3
+  float d3 = 0.f, amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) { d3 = fmaf(v[i], bseg[i], d3); amax = fmaxf(amax, fabsf(v[i])); }
+  float* do3f = bwd_tail(c, 0);                  // FP32 dO3 until the scale is known (slots 0, 1 are still free)
+  store_row16(c, do3f, v);
+  // red: [0..255] D3 partials (4 per row), [256..263] per-warp maxima
+  red[c.row * 4 + (c.c32 >> 5) * 2 + c.part] = d3;
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  if ((t & 31) == 0) red[256 + (t >> 5)] = amax;
+  wait_group(c, 1, 0x21f2);
+  acc_result(c, kAcc1, v);                       // dK2inv
+  if (p.kappa > 0.f) store_row16(c, bwd_stage(c, 3), v);
+  else split_store16(c.slot(2), c.row, c.col0, v);
+  ns::ns_sync();
+  float cmax = red[256];
+#pragma unroll
+  for (int w = 1; w < kComputeThreads / 32; ++w) cmax = fmaxf(cmax, red[256 + w]);
+  const float sc = pow2_scale(cmax), inv_sc = 1.f / sc;
+  if (t == 0) h.do3_scale[bh] = sc;
+  if (t < m) h.D3[bh * m + t] = (red[4 * t] + red[4 * t + 1]) + (red[4 * t + 2] + red[4 * t + 3]);
+  {
+    // 16-bit copies, rows >= m zero: dO3 / scale and qt_mul * Qt
+    const size_t ob = (size_t)bh * h.MP * D;
+    uint32_t w0[8], w1[8];
+#pragma unroll
+    for (int i = 0; i < 16; i += 2) {
+      const float a = (r < m) ? do3f[r * kLd + c0 + i] * inv_sc : 0.f;
+      const float b = (r < m) ? do3f[r * kLd + c0 + i + 1] * inv_sc : 0.f;
+      w0[i >> 1] = h.dtype == 1 ? pack2<__half>(a, b) : pack2<__nv_bfloat16>(a, b);
+      w1[i >> 1] = h.dtype == 1 ? pack2<__half>(qrow[i] * h.qt_mul, qrow[i + 1] * h.qt_mul)
+                                : pack2<__nv_bfloat16>(qrow[i] * h.qt_mul, qrow[i + 1] * h.qt_mul);
+    }
+    if (r < h.MP) {
+      uint4* d0 = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(h.do3n) + ob + (size_t)r * D + c0);
+      uint4* d1 = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(h.qt16) + ob + (size_t)r * D + c0);
+      d0[0] = make_uint4(w0[0], w0[1], w0[2], w0[3]); d0[1] = make_uint4(w0[4], w0[5], w0[6], w0[7]);
+      d1[0] = make_uint4(w1[0], w1[1], w1[2], w1[3]); d1[1] = make_uint4(w1[4], w1[5], w1[6], w1[7]);
+    }
+  }
+  ns::ns_sync();   // do3f (slots 0, 1) is free again
+  NS_TRACE();
+}
+
+__global__ void __launch_bounds__(kNsTcThreads, 1)
+ns_bwd_tc_kernel(ns::NsBwdParams p, BwdHeadParams h, int* status) {
   extern __shared__ uint8_t dyn_smem[];
-  __shared__ float red[2 * kN];
+  __shared__ float red[ns::kRedFloats];
   __shared__ Shared sh;
   Ctx c;
   NS_TRACE();
@@ -690,15 +859,19 @@ __global__ void __launch_bounds__(kNsTcThreads, 1) ns_bwd_tc_kernel(ns::NsBwdPar
   const int64_t bh = blockIdx.x;
   const int m = p.m, mm_ = m * m;
   const bool finish_tc = p.D == kN;
+  const bool head = h.partA != nullptr;      // fused middle stage (head_dim 64 only)
   if (is_compute()) {
-    float* dK2 = pinv_backward_tc(c, red, p.k2 + bh * mm_, p.iterates + bh * (size_t)(p.J + 1) * mm_, p.G + bh * mm_,
-                                  p.spill + bh * mm_, m, p.J, p.kappa);
+    if (head) bwd_head_tc(c, red, p, h, bh);
+    FinishOperands fo;
+    float* dK2 = pinv_backward_tc(c, red, p.k2 + bh * mm_, p.iterates + bh * (size_t)(p.J + 1) * mm_,
+                                  head ? nullptr : p.G + bh * mm_,
+                                  p.spill + bh * mm_, m, p.J, p.kappa, [&] { if (finish_tc) finish_load(c, p, bh, fo); });
     NS_TRACE();
-    if (finish_tc) ns_bwd_finish_tc(c, p, bh, bwd_tail(c, 0), dK2);
+    if (finish_tc) ns_bwd_finish_tc(c, p, bh, bwd_tail(c, 0), dK2, fo);
     else if (!c.failed) ns::ns_bwd_finish(p, bh, bwd_tail(c, 0), dK2);
     NS_TRACE();
   } else if (is_issuer()) {
-    pinv_backward_issue(c, p.J, finish_tc);
+    pinv_backward_issue(c, p.J, finish_tc, head);
   }
   ctx_close(c, kBwdTmemCols);
   NS_TRACE();
