@@ -81,13 +81,17 @@ __device__ __forceinline__ TileRange tile_range(const TcSched& sch) {
 // ------------------------------------------------------------------------------------------
 // Forward output pass:  O = softmax(Q Kt^T) step2, lse1.
 //   kt16 = s*log2e*Kt (MP x D), st16 = step2^T / 2^e (D x MP), st_scale[bh] = 2^e.
-// Two-deep pipeline: S and O are double-buffered in TMEM and P in shared memory; the MMA thread
-// issues the score product two tiles ahead; the compute warps run softmax(i), epilogue(i-1).
+// The eight compute warps form two groups of 128 threads (one thread per tile row, all landmark
+// columns).  Group g owns tiles g, g+2, ... with its own S and O accumulators in TMEM and its own
+// P buffer in shared memory, so two tiles are always in different phases (softmax of one while
+// the products of the other run); the output tile is staged in the group's P buffer once the
+// product that read it has completed.  The MMA thread issues the score product two tiles ahead.
 template <int D, int MP>
 struct FwdCSmem {
   static constexpr int kKt = MP * D * 2, kSt = D * MP * 2, kQ = kTile * D * 2, kP = kTile * MP * 2,
-                       kO = kTile * D * 2, kX = 2 * 2 * kTile * 8;
-  static constexpr int kBytes = kKt + kSt + 2 * kQ + 2 * kP + kO + kX + 256 + 1024;
+                       kO = kTile * D * 2;
+  static_assert(kO <= kP, "the output tile is staged in the probability buffer");
+  static constexpr int kBytes = kKt + kSt + 2 * kQ + 2 * kP + 256 + 1024;
 };
 
 template <class T, int D, int MP>
@@ -97,7 +101,8 @@ tc_fwd_c_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 float* __restrict__ lse1, const float* __restrict__ st_scale, TcSched sch, int m,
                 int* status) {
   using L = FwdCSmem<D, MP>;
-  constexpr int KBD = D / 64, KBM = MP / 64, HC = MP / 2, HD = D / 2;
+  constexpr int KBD = D / 64, KBM = MP / 64;
+  constexpr int kGroup = kComputeThreads / 2;
   constexpr uint32_t kCols = 2 * MP + 2 * D;
   constexpr uint32_t kTmemCols = kCols <= 256 ? 256 : 512;
   extern __shared__ uint8_t smem_raw[];
@@ -105,10 +110,8 @@ tc_fwd_c_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   uint8_t* s_kt = base;
   uint8_t* s_st = s_kt + L::kKt;
   uint8_t* s_q = s_st + L::kSt;          // two stages
-  uint8_t* s_p = s_q + 2 * L::kQ;        // two buffers
-  uint8_t* s_o = s_p + 2 * L::kP;
-  float2* s_x = reinterpret_cast<float2*>(s_o + L::kO);   // [2][2][128] (max, sum) exchange
-  uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(s_x) + L::kX);
+  uint8_t* s_p = s_q + 2 * L::kQ;        // one buffer per compute group
+  uint64_t* bars = reinterpret_cast<uint64_t*>(s_p + 2 * L::kP);
   uint64_t* small_full = bars + 0;
   uint64_t* q_full = bars + 1;           // [2]
   uint64_t* q_empty = bars + 3;          // [2]
@@ -128,7 +131,7 @@ tc_fwd_c_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     mbar_init(small_full, 1);
     for (int s = 0; s < 2; ++s) {
       mbar_init(q_full + s, 1); mbar_init(q_empty + s, 1); mbar_init(s_full + s, 1);
-      mbar_init(p_full + s, kComputeThreads); mbar_init(o_full + s, 1); mbar_init(o_free + s, kComputeThreads);
+      mbar_init(p_full + s, kGroup); mbar_init(o_full + s, 1); mbar_init(o_free + s, kGroup);
     }
     *abort_word = 0;
     fence_mbar_init();
@@ -198,79 +201,75 @@ tc_fwd_c_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
     }
   } else {
-    const int r = threadIdx.x & 127, h = threadIdx.x >> 7;   // tile row (TMEM lane), column half
+    const int g = warp >> 2;                                  // compute group
+    const int r = threadIdx.x & 127;                           // tile row = TMEM lane
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     const float osc = st_scale[bh];
-    float inv_tot[2] = {0.f, 0.f};
-    bool alive = true;
-    auto epilogue = [&](int j) -> bool {
-      const int st = j & 1;
-      if (!mbar_wait(o_full + st, (j >> 1) & 1, ab, 0x700 + j)) return false;
+    uint8_t* my_p = s_p + g * L::kP;
+    const bool leader = r == 0;
+    const bool full_m = m == MP;
+    for (int i = g; i < count; i += 2) {
+      const uint32_t par = (uint32_t)(i >> 1) & 1u;
+      if (!mbar_wait(s_full + g, par, ab, 0x600 + i)) break;
       __syncwarp();
       tc_fence_after();
-      float o[HD];
-      ld_cols<HD>(tmem_base + 2 * MP + st * D + lane_base + h * HD, o);
+      float s[MP];
+      ld_cols<MP>(tmem_base + g * MP + lane_base, s);
+      tmem_ld_wait();
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      float sm4[4] = {0.f, 0.f, 0.f, 0.f};
+      float mx;
+      if (full_m) {
+#pragma unroll
+        for (int j = 0; j < MP; ++j) mx4[j & 3] = fmaxf(mx4[j & 3], s[j]);
+        mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+#pragma unroll
+        for (int j = 0; j < MP; ++j) {
+          s[j] = fast_exp2(s[j] - mx);
+          sm4[j & 3] += s[j];
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < MP; ++j) if (j < m) mx4[j & 3] = fmaxf(mx4[j & 3], s[j]);
+        mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+#pragma unroll
+        for (int j = 0; j < MP; ++j) {
+          s[j] = (j < m) ? fast_exp2(s[j] - mx) : 0.f;
+          sm4[j & 3] += s[j];
+        }
+      }
+      const float tot = (sm4[0] + sm4[1]) + (sm4[2] + sm4[3]);
+      // this group's previous output tile was stored from my_p: wait until the copy has read it
+      if (leader) tma_store_wait_read();
+      named_barrier(1 + g, kGroup);
+      store_cols<T, MP>(my_p, r, 0, s);
+      fence_proxy_async();
+      tc_fence_before();
+      mbar_arrive(p_full + g);
+      const float mul = osc / tot;
+      const int64_t row = (int64_t)(tile0 + i) * kTile + r;
+      if (row < sch.N) lse1[bh * sch.N + row] = (mx + log2f(tot)) * kLn2;
+      // output product of the same tile
+      if (!mbar_wait(o_full + g, par, ab, 0x700 + i)) break;
+      __syncwarp();
+      tc_fence_after();
+      float o[D];
+      ld_cols<D>(tmem_base + 2 * MP + g * D + lane_base, o);
       tmem_ld_wait();
       tc_fence_before();
-      mbar_arrive(o_free + st);
-      if (threadIdx.x == 0) tma_store_wait_read();
-      named_barrier(1, kComputeThreads);
-      const float mul = st ? inv_tot[1] : inv_tot[0];
+      mbar_arrive(o_free + g);
 #pragma unroll
-      for (int j2 = 0; j2 < HD; ++j2) o[j2] *= mul;
-      store_cols<T, HD>(s_o, r, h * HD, o);
+      for (int j = 0; j < D; ++j) o[j] *= mul;
+      store_cols<T, D>(my_p, r, 0, o);        // the product that read P from my_p has completed
       fence_proxy_async();
-      named_barrier(1, kComputeThreads);
-      if (threadIdx.x == 0) {
+      named_barrier(1 + g, kGroup);
+      if (leader) {
         for (int kb = 0; kb < KBD; ++kb)
-          tma_store_3d(&tm_o, s_o + kb * (kTile * 128), kb * 64, (tile0 + j) * kTile, (int)bh);
+          tma_store_3d(&tm_o, my_p + kb * (kTile * 128), kb * 64, (tile0 + i) * kTile, (int)bh);
         tma_store_commit();
       }
-      return true;
-    };
-    for (int i = 0; i < count; ++i) {
-      const int st = i & 1;
-      if (!mbar_wait(s_full + st, (i >> 1) & 1, ab, 0x600 + i)) { alive = false; break; }
-      __syncwarp();
-      tc_fence_after();
-      float s[HC];
-      ld_cols<HC>(tmem_base + st * MP + lane_base + h * HC, s);
-      tmem_ld_wait();
-      const int c0 = h * HC;
-      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-      for (int j = 0; j < HC; ++j) if (c0 + j < m) mx4[j & 3] = fmaxf(mx4[j & 3], s[j]);
-      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-      float sm4[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-      for (int j = 0; j < HC; ++j) {
-        const float e = (c0 + j < m) ? fast_exp2(s[j] - mx) : 0.f;
-        s[j] = e;
-        sm4[j & 3] += e;
-      }
-      const float sum = (sm4[0] + sm4[1]) + (sm4[2] + sm4[3]);
-      s_x[(st * 2 + h) * kTile + r] = make_float2(mx, sum);
-      named_barrier(1, kComputeThreads);
-      const float2 other = s_x[(st * 2 + (h ^ 1)) * kTile + r];
-      const float M = fmaxf(mx, other.x);
-      const float f = (mx == -INFINITY) ? 0.f : fast_exp2(mx - M);
-      const float fo = (other.x == -INFINITY) ? 0.f : fast_exp2(other.x - M);
-      const float tot = sum * f + other.y * fo;
-#pragma unroll
-      for (int j = 0; j < HC; ++j) s[j] *= f;
-      // P[st] was last read by the output product of tile i-2, whose completion (o_full) the
-      // epilogue of tile i-2 has already waited for
-      store_cols<T, HC>(s_p + st * L::kP, r, c0, s);
-      fence_proxy_async();
-      tc_fence_before();
-      mbar_arrive(p_full + st);
-      if (st) inv_tot[1] = osc / tot; else inv_tot[0] = osc / tot;
-      const int64_t row = (int64_t)(tile0 + i) * kTile + r;
-      if (h == 0 && row < sch.N) lse1[bh * sch.N + row] = (M + log2f(tot)) * kLn2;
-      if (i > 0 && !epilogue(i - 1)) { alive = false; break; }
     }
-    if (alive) epilogue(count - 1);
-    if (threadIdx.x == 0) tma_store_wait_all();
+    if (leader) tma_store_wait_all();
   }
   tc_fence_before();
   __syncthreads();
