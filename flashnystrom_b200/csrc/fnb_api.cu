@@ -677,11 +677,11 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
       }
       if (L.end("dqt_rows")) return L.status;
       L.begin();
-      auto kern = tc::tc_bwd_ac_kernel<T, D, MPc, tc::kModeC>;
-      size_t sm = tc::BwdAcSmem<D, MPc, tc::kModeC>::kBytes;
+      auto kern = tc::tc_bwd_c_kernel<T, D, MPc>;
+      size_t sm = tc::BwdCSmem<D, MPc>::kBytes;
       if (int rc = set_smem(kern, sm, max_smem, "tc_bwd_c")) return rc;
-      kern<<<tgrid, tc::kTcThreads, sm, st>>>(tm_q, tm_g, tm_kt, tm_st, tm_dq, a.lse1, w.st_scale, w.rows_q, nullptr,
-                                             sch, p.m, scale, a.device_status);
+      kern<<<tgrid, tc::kTcThreads, sm, st>>>(tm_q, tm_g, tm_kt, tm_st, tm_dq, a.lse1, w.st_scale, w.rows_q, sch, p.m,
+                                             a.device_status);
       if (L.end("tc_bwd_c")) return L.status;
       return 0;
     }

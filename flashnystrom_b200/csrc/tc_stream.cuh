@@ -548,6 +548,234 @@ tc_bwd_ac_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 }
 
 // ------------------------------------------------------------------------------------------
+// Softmax-1 backward, second row pass (dQ), two ping-pong compute groups.
+//   S1 = Q kt16^T (log2 domain), dP1 = dO st16^T, P1 = exp2(S1 - lse1*log2e),
+//   D1 = rowsum(P1 o dP1), dS1 = P1 o (dP1 - D1), dQ = s dS1 Kt + rows_q[l(n)].
+// Group g (128 threads, one per tile row) owns tiles g, g+2, ... with its own S / dP accumulators
+// (whose first half is reused for the dQ product) and its own dS tile, which also stages the dQ
+// tile for the TMA store.  A row is handled in two 32-column halves to stay inside the register
+// budget of two CTAs per SM: the first sweep turns S into P in place in tensor memory and forms
+// D1, the second sweep reads P and dP back and writes dS.
+template <int D, int MP>
+struct BwdCSmem {
+  static constexpr int kKt = MP * D * 2, kSt = MP * D * 2, kIn = kTile * D * 2,
+                       kDs = kTile * (MP > D ? MP : D) * 2;
+  // relies on the dynamic shared window being 1024-byte aligned (checked at run time)
+  static constexpr int kBytes = kKt + kSt + 4 * kIn + 2 * kDs + 256;
+};
+
+template <class T, int D, int MP>
+__global__ void __launch_bounds__(kTcThreads, 2)
+tc_bwd_c_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_g,
+                const __grid_constant__ CUtensorMap tm_kt, const __grid_constant__ CUtensorMap tm_st,
+                const __grid_constant__ CUtensorMap tm_dq,
+                const float* __restrict__ lse1, const float* __restrict__ st_scale,
+                const float* __restrict__ rows_q, TcSched sch, int m, int* status) {
+  using L = BwdCSmem<D, MP>;
+  static_assert(D == 64 && MP == 64, "written for 64 x 64 landmark operands");
+  constexpr int KBD = D / 64;
+  constexpr int kGroup = kComputeThreads / 2;
+  constexpr uint32_t kTmemCols = 256;
+  extern __shared__ uint8_t smem_raw[];
+  if (smem_u32(smem_raw) & 1023u) {
+    if (threadIdx.x == 0 && status) atomicCAS(status, 0, (2 << 24) | 0x2000);
+    return;
+  }
+  uint8_t* s_kt = smem_raw;
+  uint8_t* s_st = s_kt + L::kKt;
+  uint8_t* s_q = s_st + L::kSt;          // two stages
+  uint8_t* s_g = s_q + 2 * L::kIn;       // two stages
+  uint8_t* s_ds = s_g + 2 * L::kIn;      // one per group
+  uint64_t* bars = reinterpret_cast<uint64_t*>(s_ds + 2 * L::kDs);
+  uint64_t* small_full = bars + 0;
+  uint64_t* in_full = bars + 1;          // [2]
+  uint64_t* in_empty = bars + 3;         // [2]
+  uint64_t* sdp_full = bars + 5;         // [2]
+  uint64_t* pds_full = bars + 7;         // [2]
+  uint64_t* acc_done = bars + 9;         // [2]
+  uint64_t* o_free = bars + 11;          // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+  int* abort_word = reinterpret_cast<int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const TileRange tr = tile_range(sch);
+  const int64_t bh = tr.bh;
+  const int tile0 = tr.tile0, count = tr.count;
+
+  if (threadIdx.x == 0) {
+    mbar_init(small_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(in_full + s, 1); mbar_init(in_empty + s, 1); mbar_init(sdp_full + s, 1);
+      mbar_init(pds_full + s, kGroup); mbar_init(acc_done + s, 1); mbar_init(o_free + s, kGroup);
+    }
+    *abort_word = 0;
+    fence_mbar_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  Abort ab{abort_word, status};
+
+  if (warp == kProducerWarp) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tm_q);
+      tma_prefetch_desc(&tm_g);
+      tma_prefetch_desc(&tm_dq);
+      mbar_expect_tx(small_full, L::kKt + L::kSt);
+      for (int kb = 0; kb < KBD; ++kb) {
+        tma_load_2d(s_kt + kb * (MP * 128), &tm_kt, small_full, kb * 64, (int)(bh * MP));
+        tma_load_2d(s_st + kb * (MP * 128), &tm_st, small_full, kb * 64, (int)(bh * MP));
+      }
+      int armed = 0;
+      for (int i = 0; i < count; ++i) {
+        const int st = i & 1;
+        if (!mbar_wait(in_empty + st, ((i >> 1) & 1) ^ 1, ab, 0x2100 + i)) break;
+        mbar_expect_tx(in_full + st, 2 * L::kIn);
+        for (int kb = 0; kb < KBD; ++kb) {
+          tma_load_3d(s_q + st * L::kIn + kb * (kTile * 128), &tm_q, in_full + st, kb * 64, (tile0 + i) * kTile, (int)bh);
+          tma_load_3d(s_g + st * L::kIn + kb * (kTile * 128), &tm_g, in_full + st, kb * 64, (tile0 + i) * kTile, (int)bh);
+        }
+        armed = i + 1;
+      }
+      if (ab.raised())
+        for (int i = max(0, armed - 2); i < armed; ++i) mbar_drain(in_full + (i & 1), (i >> 1) & 1);
+    }
+  } else if (warp == kMmaWarp) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = make_idesc<T>(kTile, MP, false, false);
+      constexpr uint32_t idesc_dq = make_idesc<T>(kTile, D, false, true);
+      const uint32_t a_kt = smem_u32(s_kt), a_st = smem_u32(s_st);
+      // S and dP of tile i into the accumulators of group b = i & 1
+      auto front = [&](int i) -> bool {
+        const int b = i & 1;
+        if (!mbar_wait(in_full + b, (i >> 1) & 1, ab, 0x2300 + i)) return false;
+        tc_fence_after();
+        const uint32_t a_q = smem_u32(s_q + b * L::kIn), a_g = smem_u32(s_g + b * L::kIn);
+        const uint32_t t_s = tmem_base + b * 2 * MP;
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) umma(t_s, kdesc(a_q, k, kTile), kdesc(a_kt, k, MP), idesc_s, k > 0);
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) umma(t_s + MP, kdesc(a_g, k, kTile), kdesc(a_st, k, MP), idesc_s, k > 0);
+        umma_commit(in_empty + b);
+        umma_commit(sdp_full + b);
+        return true;
+      };
+      bool ok = mbar_wait(small_full, 0, ab, 0x2200);
+      ok = ok && front(0);
+      if (ok && count > 1) ok = front(1);
+      for (int i = 0; ok && i < count; ++i) {
+        const int b = i & 1;
+        if (!mbar_wait(pds_full + b, (i >> 1) & 1, ab, 0x2400 + i)) break;
+        tc_fence_after();
+        const uint32_t a_ds = smem_u32(s_ds + b * L::kDs);
+        // dQ = dS (128 x MP, K-major) * Kt (MP x D, MN-major view of kt16)
+#pragma unroll
+        for (int k = 0; k < MP / 16; ++k)
+          umma(tmem_base + b * 2 * MP, kdesc(a_ds, k, kTile), smem_desc_sw128(a_kt + k * 2048, MP * 128, 1024),
+               idesc_dq, k > 0);
+        umma_commit(acc_done + b);
+        if (i + 2 < count) {
+          if (!mbar_wait(o_free + b, (i >> 1) & 1, ab, 0x2380 + i)) break;
+          ok = front(i + 2);
+        }
+      }
+    }
+  } else {
+    const int g = warp >> 2;
+    const int r = threadIdx.x & 127;
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    const float mul = st_scale[bh] * kLn2;
+    uint8_t* my_ds = s_ds + g * L::kDs;
+    const uint32_t t_s = tmem_base + g * 2 * MP + lane_base;
+    const bool leader = r == 0;
+    Segments sg(sch.seg_N, m);
+    for (int i = g; i < count; i += 2) {
+      const uint32_t par = (uint32_t)(i >> 1) & 1u;
+      const int64_t row = (int64_t)(tile0 + i) * kTile + r;
+      const bool valid = row < sch.N;
+      const float lse = valid ? lse1[bh * sch.N + row] * kLog2e : 0.f;
+      if (!mbar_wait(sdp_full + g, par, ab, 0x2600 + i)) break;
+      __syncwarp();
+      tc_fence_after();
+      // sweep 1: S -> P in place, D1
+      float d4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int hf = 0; hf < 2; ++hf) {
+        float pv[32], gv[32];
+        tmem_ld32(t_s + hf * 32, pv);
+        tmem_ld32(t_s + MP + hf * 32, gv);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          pv[j] = (valid && hf * 32 + j < m) ? fast_exp2(pv[j] - lse) : 0.f;
+          d4[j & 3] = fmaf(pv[j], gv[j], d4[j & 3]);
+        }
+        tmem_st32(t_s + hf * 32, pv);
+      }
+      tmem_st_wait();
+      const float d1 = (d4[0] + d4[1]) + (d4[2] + d4[3]);
+      // the previous dQ tile of this group was stored from my_ds: wait until the copy has read it
+      if (leader) tma_store_wait_read();
+      named_barrier(1 + g, kGroup);
+      // sweep 2: dS = P o (dP - D1)
+#pragma unroll
+      for (int hf = 0; hf < 2; ++hf) {
+        float pv[32], gv[32];
+        tmem_ld32(t_s + hf * 32, pv);
+        tmem_ld32(t_s + MP + hf * 32, gv);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) gv[j] = pv[j] * (gv[j] - d1);
+        store_cols<T, 32>(my_ds, r, hf * 32, gv);
+      }
+      fence_proxy_async();
+      tc_fence_before();
+      mbar_arrive(pds_full + g);
+      // dQ tile of the same rows
+      const int l = valid ? sg.landmark_of(sch.row_offset + row) : 0;
+      const float4* add = reinterpret_cast<const float4*>(rows_q + (bh * m + l) * D);
+      if (!mbar_wait(acc_done + g, par, ab, 0x2800 + i)) break;
+      __syncwarp();
+      tc_fence_after();
+      // acc_done also means the product has finished reading the dS tile: reuse it as staging
+#pragma unroll
+      for (int hf = 0; hf < 2; ++hf) {
+        float o[32];
+        tmem_ld32(t_s + hf * 32, o);
+        tmem_ld_wait();
+        if (hf == 1) {
+          tc_fence_before();
+          mbar_arrive(o_free + g);
+        }
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) {
+          const float4 a = add[(hf * 32 + j) >> 2];
+          o[j + 0] = fmaf(o[j + 0], mul, a.x); o[j + 1] = fmaf(o[j + 1], mul, a.y);
+          o[j + 2] = fmaf(o[j + 2], mul, a.z); o[j + 3] = fmaf(o[j + 3], mul, a.w);
+        }
+        store_cols<T, 32>(my_ds, r, hf * 32, o);
+      }
+      fence_proxy_async();
+      named_barrier(1 + g, kGroup);
+      if (leader) {
+        for (int kb = 0; kb < KBD; ++kb)
+          tma_store_3d(&tm_dq, my_ds + kb * (kTile * 128), kb * 64, (tile0 + i) * kTile, (int)bh);
+        tma_store_commit();
+      }
+    }
+    if (leader) tma_store_wait_all();
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem_base, kTmemCols);
+}
+
+// ------------------------------------------------------------------------------------------
 // Softmax-3 backward (column pass).  Per 128-row tile of K and V (thread = row n, half the
 // landmark columns):
 //   S3^T = K qt16^T (log2 domain), dP3^T = V do3n^T (dO3 normalised by 2^-e, undone by dsc)
