@@ -240,6 +240,7 @@ struct BwdWs {
   float *partA, *partB, *dstep2, *dkt_a, *dO3, *dqt_ns, *dkt_tot, *dqt_tot, *D3, *G, *dK2, *pinv;
   void* op16[8];              // 16-bit operand copies for the tensor-core kernels
   float *st_scale, *do3_scale, *rows_q, *rows_k;
+  float* d1;                  // [BH][N]: softmax-1 row terms D1, written by pass A for pass C
   size_t bytes;
 };
 static BwdWs carve_bwd(const Plan& p, void* base) {
@@ -260,6 +261,7 @@ static BwdWs carve_bwd(const Plan& p, void* base) {
   for (int i = 0; i < 8; ++i) w.op16[i] = take(op16);
   w.st_scale = take((size_t)p.BH); w.do3_scale = take((size_t)p.BH);
   w.rows_q = take(md); w.rows_k = take(md);
+  w.d1 = take((size_t)p.BH * p.N);
   w.bytes = off;
   return w;
 }
@@ -510,15 +512,13 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
   const size_t gsmem = bwd_ac_smem(p.mpad, p.D);
   const int nchunk_used = use_tc ? sch.nchunk : p.nchunk;
 
-  void* kt16 = w.op16[0]; void* st16 = w.op16[1]; void* qt16 = w.op16[3]; void* do3n = w.op16[5];
-  CUtensorMap tm_q, tm_g, tm_kt, tm_st, tm_dq;
+  void* qt16 = w.op16[3]; void* do3n = w.op16[5];
+  CUtensorMap tm_q, tm_g, tm_dq;
   if (use_tc) {
-    constexpr int D = 64, MPc = 64;
+    constexpr int D = 64;
     if (!tc::make_map_3d(&tm_q, a.q, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
         !tc::make_map_3d(&tm_g, a.d_out, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
-        !tc::make_map_3d(&tm_dq, a.dq, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
-        !tc::make_map_2d(&tm_kt, kt16, a.shape.dtype, p.BH * MPc, D, MPc) ||
-        !tc::make_map_2d(&tm_st, st16, a.shape.dtype, p.BH * MPc, D, MPc))
+        !tc::make_map_3d(&tm_dq, a.dq, a.shape.dtype, p.BH, p.N, D, tc::kTile))
       return fail(FNB_ERR_CUDA, "cuTensorMapEncodeTiled failed for the backward row passes");
   }
   auto reduce_chunks = [&](const float* in, int nchunk, int elems, float* out) {
@@ -532,19 +532,10 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
     if (use_tc) {
       constexpr int D = 64, MPc = 64;
       L.begin();
-      {
-        PackBwdAcParams pp;
-        pp.k_landmarks = a.k_landmarks; pp.step2 = a.step2; pp.kt16 = kt16; pp.ktT16 = nullptr; pp.st16 = st16;
-        pp.st_scale = w.st_scale; pp.m = p.m; pp.D = p.D; pp.MP = MP; pp.dtype = a.shape.dtype;
-        pp.kt_mul = scale * tc::kLog2e; pp.ktT_mul = scale;
-        pack_bwd_ac_kernel<<<(unsigned)p.BH, kThreads, 0, st>>>(pp);
-      }
-      if (L.end("pack_bwd_ac")) return L.status;
-      L.begin();
       auto kern = tc::tc_bwd_ac_kernel<T, D, MPc, tc::kModeA>;
       size_t sm = tc::BwdAcSmem<D, MPc, tc::kModeA>::kBytes;
       if (int rc = set_smem(kern, sm, max_smem, "tc_bwd_a")) return rc;
-      kern<<<tgrid, tc::kTcThreads, sm, st>>>(tm_q, tm_g, tm_kt, tm_st, tm_dq, a.lse1, w.st_scale, nullptr, w.partA,
+      kern<<<tgrid, tc::kTcThreads, sm, st>>>(tm_q, tm_g, tm_dq, a.k_landmarks, a.step2, a.lse1, nullptr, w.partA, w.d1,
                                              sch, p.m, scale, a.device_status);
       if (L.end("tc_bwd_a")) return L.status;
     }
@@ -680,8 +671,8 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
       auto kern = tc::tc_bwd_c_kernel<T, D, MPc>;
       size_t sm = tc::BwdCSmem<D, MPc>::kBytes;
       if (int rc = set_smem(kern, sm, max_smem, "tc_bwd_c")) return rc;
-      kern<<<tgrid, tc::kTcThreads, sm, st>>>(tm_q, tm_g, tm_kt, tm_st, tm_dq, a.lse1, w.st_scale, w.rows_q, sch, p.m,
-                                             a.device_status);
+      kern<<<tgrid, tc::kTcThreads, sm, st>>>(tm_q, tm_g, tm_dq, a.k_landmarks, a.step2, a.lse1, w.d1, w.rows_q, sch,
+                                             p.m, scale, a.device_status);
       if (L.end("tc_bwd_c")) return L.status;
       return 0;
     }

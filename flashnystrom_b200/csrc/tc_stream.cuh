@@ -12,6 +12,7 @@
 // into 16-bit copies and stay resident in shared memory for the whole CTA.
 #pragma once
 #include "common.cuh"
+#include "small_kernels.cuh"
 #include "tc_common.cuh"
 
 namespace fnb {
@@ -65,6 +66,50 @@ __device__ __forceinline__ uint64_t kdesc(uint32_t base, int k, int rows) {
 // MN-major operand staged as [128 rows(K) x 64] blocks: advance by k 16-row steps along K
 __device__ __forceinline__ uint64_t mndesc(uint32_t base, int k) {
   return smem_desc_sw128(base + k * 2048, kTile * 128, 1024);
+}
+
+// Compute warps (256 threads), head_dim 64: 16-bit swizzled operand tiles of two landmark matrices
+// of one slice straight from their FP32 originals (rows >= m zero):
+//   tile_a = mul_a * A,   tile_b = B / sc  with sc the power of two >= max |B|   (returned).
+// Thread t packs row t >> 2, columns 16 (t & 3) .. +15.  scratch: 8 floats of shared memory;
+// named barrier 3 is used once.  The caller fences and signals the MMA thread.
+template <class T>
+__device__ __forceinline__ float pack_landmark_operands(uint8_t* tile_a, uint8_t* tile_b, const float* A,
+                                                        const float* B, int m, float mul_a, float* scratch) {
+  const int t = threadIdx.x, r = t >> 2, c0 = (t & 3) * 16;
+  float a[16], b[16];
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    float4 x = make_float4(0.f, 0.f, 0.f, 0.f), y = x;
+    if (r < m) {
+      x = *reinterpret_cast<const float4*>(A + r * 64 + c0 + 4 * q);
+      y = *reinterpret_cast<const float4*>(B + r * 64 + c0 + 4 * q);
+    }
+    a[4 * q] = x.x; a[4 * q + 1] = x.y; a[4 * q + 2] = x.z; a[4 * q + 3] = x.w;
+    b[4 * q] = y.x; b[4 * q + 1] = y.y; b[4 * q + 2] = y.z; b[4 * q + 3] = y.w;
+  }
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(b[i]));
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  if ((t & 31) == 0) scratch[t >> 5] = amax;
+  named_barrier(3, kComputeThreads);
+  float cmax = scratch[0];
+#pragma unroll
+  for (int w = 1; w < kComputeThreads / 32; ++w) cmax = fmaxf(cmax, scratch[w]);
+  const float sc = pow2_scale(cmax), inv = 1.f / sc;
+#pragma unroll
+  for (int c = 0; c < 2; ++c) {
+    uint4 wa, wb;
+    wa.x = pack2<T>(a[8 * c + 0] * mul_a, a[8 * c + 1] * mul_a); wa.y = pack2<T>(a[8 * c + 2] * mul_a, a[8 * c + 3] * mul_a);
+    wa.z = pack2<T>(a[8 * c + 4] * mul_a, a[8 * c + 5] * mul_a); wa.w = pack2<T>(a[8 * c + 6] * mul_a, a[8 * c + 7] * mul_a);
+    wb.x = pack2<T>(b[8 * c + 0] * inv, b[8 * c + 1] * inv); wb.y = pack2<T>(b[8 * c + 2] * inv, b[8 * c + 3] * inv);
+    wb.z = pack2<T>(b[8 * c + 4] * inv, b[8 * c + 5] * inv); wb.w = pack2<T>(b[8 * c + 6] * inv, b[8 * c + 7] * inv);
+    const uint32_t off = sw128_offset(r, (c0 >> 3) + c);
+    *reinterpret_cast<uint4*>(tile_a + off) = wa;
+    *reinterpret_cast<uint4*>(tile_b + off) = wb;
+  }
+  return sc;
 }
 
 struct TileRange { int64_t bh; int chunk, tile0, count; };
@@ -300,11 +345,12 @@ struct BwdAcSmem {
 template <class T, int D, int MP, int MODE>
 __global__ void __launch_bounds__(kTcThreads, 2)
 tc_bwd_ac_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_g,
-                 const __grid_constant__ CUtensorMap tm_kt, const __grid_constant__ CUtensorMap tm_st,
                  const __grid_constant__ CUtensorMap tm_dq,
-                 const float* __restrict__ lse1, const float* __restrict__ st_scale,
-                 const float* __restrict__ rows_q, float* __restrict__ partA, TcSched sch, int m,
-                 float scale, int* status) {
+                 const float* __restrict__ k_landmarks, const float* __restrict__ step2,
+                 const float* __restrict__ lse1,
+                 const float* __restrict__ rows_q, float* __restrict__ partA, float* __restrict__ d1_out,
+                 TcSched sch, int m, float scale, int* status) {
+  static_assert(D == 64 && MP == 64, "the in-kernel operand packing is written for 64 x 64 landmark operands");
   using L = BwdAcSmem<D, MP, MODE>;
   constexpr int KBD = D / 64, HC = MP / 2, HD = D / 2;
   constexpr uint32_t kCols = (MODE == kModeA) ? 2 * MP + 2 * D : 4 * MP;
@@ -339,7 +385,7 @@ tc_bwd_ac_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   const int tile0 = tr.tile0, count = tr.count;
 
   if (threadIdx.x == 0) {
-    mbar_init(small_full, 1);
+    mbar_init(small_full, kComputeThreads);
     for (int s = 0; s < 2; ++s) {
       mbar_init(in_full + s, 1); mbar_init(in_empty + s, 1); mbar_init(sdp_full + s, 1);
       mbar_init(pds_full + s, kComputeThreads); mbar_init(acc_done + s, 1); mbar_init(o_free + s, kComputeThreads);
@@ -361,11 +407,6 @@ tc_bwd_ac_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     if (lane == 0) {
       tma_prefetch_desc(&tm_q);
       tma_prefetch_desc(&tm_g);
-      mbar_expect_tx(small_full, L::kKt + L::kSt);
-      for (int kb = 0; kb < KBD; ++kb) {
-        tma_load_2d(s_kt + kb * (MP * 128), &tm_kt, small_full, kb * 64, (int)(bh * MP));
-        tma_load_2d(s_st + kb * (MP * 128), &tm_st, small_full, kb * 64, (int)(bh * MP));
-      }
       int armed = 0;
       for (int i = 0; i < count; ++i) {
         const int st = i & 1;
@@ -442,7 +483,11 @@ tc_bwd_ac_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const int r = threadIdx.x & 127, h = threadIdx.x >> 7;
     const int quarter = warp & 3;
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
-    const float sc = st_scale[bh];
+    // operand copies of Kt and step2 for this slice (the dS tile is free until the first tile)
+    const float sc = pack_landmark_operands<T>(s_kt, s_st, k_landmarks + bh * m * D, step2 + bh * m * D, m,
+                                               scale * kLog2e, reinterpret_cast<float*>(s_ds));
+    fence_proxy_async();
+    mbar_arrive(small_full);
     const int c0 = h * HC;
     Segments sg(sch.seg_N, m);
     bool alive = true;
@@ -478,6 +523,8 @@ tc_bwd_ac_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       named_barrier(1, kComputeThreads);
       const float d1 = dpart + s_x[(h ^ 1) * kTile + r];
       if (MODE == kModeA) {
+        // D1 (in the domain of the normalised step2 copy) is reused by the dQ pass
+        if (d1_out && h == 0 && valid) d1_out[bh * sch.N + row] = d1;
         named_barrier(1, kComputeThreads);   // exchange words live in the head of the P tile
         store_cols<T, HC>(s_p, r, c0, p);
       }
@@ -550,12 +597,12 @@ tc_bwd_ac_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 // ------------------------------------------------------------------------------------------
 // Softmax-1 backward, second row pass (dQ), two ping-pong compute groups.
 //   S1 = Q kt16^T (log2 domain), dP1 = dO st16^T, P1 = exp2(S1 - lse1*log2e),
-//   D1 = rowsum(P1 o dP1), dS1 = P1 o (dP1 - D1), dQ = s dS1 Kt + rows_q[l(n)].
+//   dS1 = P1 o (dP1 - D1), dQ = s dS1 Kt + rows_q[l(n)];  D1 = rowsum(P1 o dP1) was written per
+//   row by the first row pass.
 // Group g (128 threads, one per tile row) owns tiles g, g+2, ... with its own S / dP accumulators
 // (whose first half is reused for the dQ product) and its own dS tile, which also stages the dQ
 // tile for the TMA store.  A row is handled in two 32-column halves to stay inside the register
-// budget of two CTAs per SM: the first sweep turns S into P in place in tensor memory and forms
-// D1, the second sweep reads P and dP back and writes dS.
+// budget of two CTAs per SM.
 template <int D, int MP>
 struct BwdCSmem {
   static constexpr int kKt = MP * D * 2, kSt = MP * D * 2, kIn = kTile * D * 2,
@@ -567,10 +614,10 @@ struct BwdCSmem {
 template <class T, int D, int MP>
 __global__ void __launch_bounds__(kTcThreads, 2)
 tc_bwd_c_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_g,
-                const __grid_constant__ CUtensorMap tm_kt, const __grid_constant__ CUtensorMap tm_st,
                 const __grid_constant__ CUtensorMap tm_dq,
-                const float* __restrict__ lse1, const float* __restrict__ st_scale,
-                const float* __restrict__ rows_q, TcSched sch, int m, int* status) {
+                const float* __restrict__ k_landmarks, const float* __restrict__ step2,
+                const float* __restrict__ lse1, const float* __restrict__ d1_in,
+                const float* __restrict__ rows_q, TcSched sch, int m, float scale, int* status) {
   using L = BwdCSmem<D, MP>;
   static_assert(D == 64 && MP == 64, "written for 64 x 64 landmark operands");
   constexpr int KBD = D / 64;
@@ -603,7 +650,7 @@ tc_bwd_c_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const int tile0 = tr.tile0, count = tr.count;
 
   if (threadIdx.x == 0) {
-    mbar_init(small_full, 1);
+    mbar_init(small_full, kComputeThreads);
     for (int s = 0; s < 2; ++s) {
       mbar_init(in_full + s, 1); mbar_init(in_empty + s, 1); mbar_init(sdp_full + s, 1);
       mbar_init(pds_full + s, kGroup); mbar_init(acc_done + s, 1); mbar_init(o_free + s, kGroup);
@@ -626,11 +673,6 @@ tc_bwd_c_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       tma_prefetch_desc(&tm_q);
       tma_prefetch_desc(&tm_g);
       tma_prefetch_desc(&tm_dq);
-      mbar_expect_tx(small_full, L::kKt + L::kSt);
-      for (int kb = 0; kb < KBD; ++kb) {
-        tma_load_2d(s_kt + kb * (MP * 128), &tm_kt, small_full, kb * 64, (int)(bh * MP));
-        tma_load_2d(s_st + kb * (MP * 128), &tm_st, small_full, kb * 64, (int)(bh * MP));
-      }
       int armed = 0;
       for (int i = 0; i < count; ++i) {
         const int st = i & 1;
@@ -689,7 +731,12 @@ tc_bwd_c_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const int g = warp >> 2;
     const int r = threadIdx.x & 127;
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-    const float mul = st_scale[bh] * kLn2;
+    // operand copies of Kt and step2 for this slice (the dS tiles are free until the first tile)
+    const float sc = pack_landmark_operands<T>(s_kt, s_st, k_landmarks + bh * m * D, step2 + bh * m * D, m,
+                                               scale * kLog2e, reinterpret_cast<float*>(s_ds));
+    fence_proxy_async();
+    mbar_arrive(small_full);
+    const float mul = sc * kLn2;
     uint8_t* my_ds = s_ds + g * L::kDs;
     const uint32_t t_s = tmem_base + g * 2 * MP + lane_base;
     const bool leader = r == 0;
@@ -699,11 +746,13 @@ tc_bwd_c_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const int64_t row = (int64_t)(tile0 + i) * kTile + r;
       const bool valid = row < sch.N;
       const float lse = valid ? lse1[bh * sch.N + row] * kLog2e : 0.f;
+      const float d1 = valid ? d1_in[bh * sch.N + row] : 0.f;
       if (!mbar_wait(sdp_full + g, par, ab, 0x2600 + i)) break;
       __syncwarp();
       tc_fence_after();
-      // sweep 1: S -> P in place, D1
-      float d4[4] = {0.f, 0.f, 0.f, 0.f};
+      // the previous dQ tile of this group was stored from my_ds: wait until the copy has read it
+      if (leader) tma_store_wait_read();
+      named_barrier(1 + g, kGroup);
 #pragma unroll
       for (int hf = 0; hf < 2; ++hf) {
         float pv[32], gv[32];
@@ -712,25 +761,9 @@ tc_bwd_c_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         tmem_ld_wait();
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
-          pv[j] = (valid && hf * 32 + j < m) ? fast_exp2(pv[j] - lse) : 0.f;
-          d4[j & 3] = fmaf(pv[j], gv[j], d4[j & 3]);
+          const float pj = (valid && hf * 32 + j < m) ? fast_exp2(pv[j] - lse) : 0.f;
+          gv[j] = pj * (gv[j] - d1);
         }
-        tmem_st32(t_s + hf * 32, pv);
-      }
-      tmem_st_wait();
-      const float d1 = (d4[0] + d4[1]) + (d4[2] + d4[3]);
-      // the previous dQ tile of this group was stored from my_ds: wait until the copy has read it
-      if (leader) tma_store_wait_read();
-      named_barrier(1 + g, kGroup);
-      // sweep 2: dS = P o (dP - D1)
-#pragma unroll
-      for (int hf = 0; hf < 2; ++hf) {
-        float pv[32], gv[32];
-        tmem_ld32(t_s + hf * 32, pv);
-        tmem_ld32(t_s + MP + hf * 32, gv);
-        tmem_ld_wait();
-#pragma unroll
-        for (int j = 0; j < 32; ++j) gv[j] = pv[j] * (gv[j] - d1);
         store_cols<T, 32>(my_ds, r, hf * 32, gv);
       }
       fence_proxy_async();
