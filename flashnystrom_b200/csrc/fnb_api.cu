@@ -441,31 +441,40 @@ static int forward_impl(const fnb_fwd_args& a, const Plan& p, const FwdWs& w, in
       cp.acc_bh_stride = (int64_t)nchunk_b * p.m * p.D; cp.acc_chunk_stride = (int64_t)p.m * p.D;
       cp.vec_bh_stride = (int64_t)nchunk_b * p.m; cp.vec_chunk_stride = p.m;
     }
-    cp.k2inv = a.k2_inv; cp.k_landmarks = a.k_landmarks; cp.bmat = a.bmat; cp.lse3 = a.lse3;
-    cp.step2 = a.step2; cp.m = p.m; cp.D = p.D;
-    cp.dtype = use_tc ? a.shape.dtype : 0; cp.MP = MP; cp.kt16 = w.kt16; cp.st16T = w.st16;
-    cp.st_scale = w.st_scale; cp.kt_mul = scale * tc::kLog2e;
-    size_t smem = sizeof(float) * (size_t)p.m * p.D;
-    if (int rc = set_smem(combine_kern, smem, max_smem, "combine")) return rc;
-    combine_kern<<<(unsigned)p.BH, kThreads, smem, st>>>(cp);
+    if (use_tc && p.m <= 64 && p.D % 16 == 0) {
+      // the tensor-core output pass packs its own operand copies: merge + step2 only, spread over
+      // D / 16 CTAs per slice
+      CombineSlabParams sp2;
+      sp2.part_acc = cp.part_acc; sp2.part_max = cp.part_max; sp2.part_sum = cp.part_sum; sp2.nchunk = cp.nchunk;
+      sp2.acc_bh_stride = cp.acc_bh_stride; sp2.acc_chunk_stride = cp.acc_chunk_stride;
+      sp2.vec_bh_stride = cp.vec_bh_stride; sp2.vec_chunk_stride = cp.vec_chunk_stride;
+      sp2.k2inv = a.k2_inv; sp2.bmat = a.bmat; sp2.lse3 = a.lse3; sp2.step2 = a.step2; sp2.m = p.m; sp2.D = p.D;
+      combine_slab_kernel<<<dim3((unsigned)p.BH, (unsigned)(p.D / 16)), kThreads, 0, st>>>(sp2);
+    } else {
+      cp.k2inv = a.k2_inv; cp.k_landmarks = a.k_landmarks; cp.bmat = a.bmat; cp.lse3 = a.lse3;
+      cp.step2 = a.step2; cp.m = p.m; cp.D = p.D;
+      cp.dtype = 0; cp.MP = MP; cp.kt16 = w.kt16; cp.st16T = w.st16;
+      cp.st_scale = w.st_scale; cp.kt_mul = scale * tc::kLog2e;
+      size_t smem = sizeof(float) * (size_t)p.m * p.D;
+      if (int rc = set_smem(combine_kern, smem, max_smem, "combine")) return rc;
+      combine_kern<<<(unsigned)p.BH, kThreads, smem, st>>>(cp);
+    }
   }
   if (L.end("combine")) return L.status;
 
   if constexpr (k16) {
     if (use_tc) {
       constexpr int D = 64, MPc = 64;
-      CUtensorMap tm_q, tm_o, tm_kt, tm_st;
+      CUtensorMap tm_q, tm_o;
       if (!tc::make_map_3d(&tm_q, a.q, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
-          !tc::make_map_3d(&tm_o, a.out, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
-          !tc::make_map_2d(&tm_kt, w.kt16, a.shape.dtype, p.BH * MPc, D, MPc) ||
-          !tc::make_map_2d(&tm_st, w.st16, a.shape.dtype, p.BH * D, MPc, D))
+          !tc::make_map_3d(&tm_o, a.out, a.shape.dtype, p.BH, p.N, D, tc::kTile))
         return fail(FNB_ERR_CUDA, "cuTensorMapEncodeTiled failed for the forward output pass");
       L.begin();
       auto kern = tc::tc_fwd_c_kernel<T, D, MPc>;
       size_t smem = tc::FwdCSmem<D, MPc>::kBytes;
       if (int rc = set_smem(kern, smem, max_smem, "tc_fwd_c")) return rc;
-      kern<<<(unsigned)(p.BH * sch.nchunk), tc::kTcThreads, smem, st>>>(tm_q, tm_o, tm_kt, tm_st, a.lse1,
-                                                                      w.st_scale, sch, p.m, a.device_status);
+      kern<<<(unsigned)(p.BH * sch.nchunk), tc::kTcThreads, smem, st>>>(tm_q, tm_o, a.k_landmarks, a.step2, a.lse1, sch,
+                                                                      p.m, scale, a.device_status);
       if (L.end("tc_fwd_c")) return L.status;
       return 0;
     }

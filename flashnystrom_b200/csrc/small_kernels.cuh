@@ -344,6 +344,77 @@ __global__ void __launch_bounds__(kThreads) bwd_mid1_kernel(BwdMid1Params p) {
 }
 
 // ------------------------------------------------------------------------------------------
+// Column-slab version of the combine step for head_dim a multiple of 16 and num_landmarks <= 64:
+// grid (BH, D / 16).  A CTA merges the softmax-3 partials of its 16 head-dim columns for every
+// landmark (thread = landmark row x 4 columns, all chunk loads in flight at once), writes those
+// columns of Bmat (and lse3 from slab 0), then forms the same columns of step2 = K2inv Bmat from
+// shared memory.  No operand copies: the output pass packs its own.
+struct CombineSlabParams {
+  const float* part_acc; const float* part_max; const float* part_sum;
+  int nchunk;
+  int64_t acc_bh_stride, acc_chunk_stride, vec_bh_stride, vec_chunk_stride;
+  const float* k2inv;
+  float* bmat; float* lse3; float* step2;
+  int m, D;
+};
+
+constexpr int kSlabMaxChunks = 20;   // chunks merged with every load in flight; more run in rounds
+
+__global__ void __launch_bounds__(kThreads) combine_slab_kernel(CombineSlabParams p) {
+  __shared__ float sK[64 * 64];
+  __shared__ __align__(16) float sB[64 * 16];
+  const int64_t bh = blockIdx.x;
+  const int slab = blockIdx.y, t = threadIdx.x, l = t >> 2, q = t & 3;
+  const int m = p.m, D = p.D, nc = p.nchunk, d0 = 16 * slab + 4 * q;
+  const float* k2inv = p.k2inv + bh * m * m;
+  for (int idx = t; idx < m * m; idx += kThreads) sK[idx] = k2inv[idx];
+  float4 b = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (l < m) {
+    const float* pacc = p.part_acc + bh * p.acc_bh_stride + (size_t)l * D + d0;
+    const float* pmax = p.part_max + bh * p.vec_bh_stride + l;
+    const float* psum = p.part_sum + bh * p.vec_bh_stride + l;
+    float M = -INFINITY;
+    for (int c = 0; c < nc; ++c) M = fmaxf(M, pmax[c * p.vec_chunk_stride]);
+    float Lsum = 0.f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int c0 = 0; c0 < nc; c0 += kSlabMaxChunks) {
+      float4 x[kSlabMaxChunks];
+      float wgt[kSlabMaxChunks], ps[kSlabMaxChunks];
+#pragma unroll
+      for (int i = 0; i < kSlabMaxChunks; ++i) {
+        const int c = min(c0 + i, nc - 1);
+        x[i] = *reinterpret_cast<const float4*>(pacc + (size_t)c * p.acc_chunk_stride);
+        wgt[i] = pmax[c * p.vec_chunk_stride];
+        ps[i] = psum[c * p.vec_chunk_stride];
+      }
+#pragma unroll
+      for (int i = 0; i < kSlabMaxChunks; ++i) {
+        const float w = (c0 + i < nc) ? expf(wgt[i] - M) : 0.f;
+        Lsum = fmaf(w, ps[i], Lsum);
+        acc.x = fmaf(w, x[i].x, acc.x); acc.y = fmaf(w, x[i].y, acc.y);
+        acc.z = fmaf(w, x[i].z, acc.z); acc.w = fmaf(w, x[i].w, acc.w);
+      }
+    }
+    const float inv = 1.f / Lsum;
+    b = make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
+    *reinterpret_cast<float4*>(p.bmat + (bh * m + l) * D + d0) = b;
+    if (slab == 0 && q == 0) p.lse3[bh * m + l] = M + logf(Lsum);
+  }
+  *reinterpret_cast<float4*>(sB + l * 16 + 4 * q) = b;
+  __syncthreads();
+  if (l < m) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
+    for (int k = 0; k < m; ++k) {
+      const float a = sK[l * m + k];
+      const float4 x = *reinterpret_cast<const float4*>(sB + k * 16 + 4 * q);
+      acc.x = fmaf(a, x.x, acc.x); acc.y = fmaf(a, x.y, acc.y); acc.z = fmaf(a, x.z, acc.z); acc.w = fmaf(a, x.w, acc.w);
+    }
+    *reinterpret_cast<float4*>(p.step2 + (bh * m + l) * D + d0) = acc;
+  }
+}
+
+// ------------------------------------------------------------------------------------------
 struct PackBwdAcParams {
   const float* k_landmarks; const float* step2;
   void* kt16;      // [BH][MP][D] = kt_mul * Kt

@@ -142,11 +142,11 @@ struct FwdCSmem {
 template <class T, int D, int MP>
 __global__ void __launch_bounds__(kTcThreads, 2)
 tc_fwd_c_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_o,
-                const __grid_constant__ CUtensorMap tm_kt, const __grid_constant__ CUtensorMap tm_st,
-                float* __restrict__ lse1, const float* __restrict__ st_scale, TcSched sch, int m,
-                int* status) {
+                const float* __restrict__ k_landmarks, const float* __restrict__ step2,
+                float* __restrict__ lse1, TcSched sch, int m, float scale, int* status) {
   using L = FwdCSmem<D, MP>;
-  constexpr int KBD = D / 64, KBM = MP / 64;
+  static_assert(D == 64 && MP == 64, "the in-kernel operand packing is written for 64 x 64 landmark operands");
+  constexpr int KBD = D / 64;
   constexpr int kGroup = kComputeThreads / 2;
   constexpr uint32_t kCols = 2 * MP + 2 * D;
   constexpr uint32_t kTmemCols = kCols <= 256 ? 256 : 512;
@@ -173,7 +173,7 @@ tc_fwd_c_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const int tile0 = tr.tile0, count = tr.count;
 
   if (threadIdx.x == 0) {
-    mbar_init(small_full, 1);
+    mbar_init(small_full, kComputeThreads);
     for (int s = 0; s < 2; ++s) {
       mbar_init(q_full + s, 1); mbar_init(q_empty + s, 1); mbar_init(s_full + s, 1);
       mbar_init(p_full + s, kGroup); mbar_init(o_full + s, 1); mbar_init(o_free + s, kGroup);
@@ -195,9 +195,6 @@ tc_fwd_c_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     if (lane == 0) {
       tma_prefetch_desc(&tm_q);
       tma_prefetch_desc(&tm_o);
-      mbar_expect_tx(small_full, L::kKt + L::kSt);
-      for (int kb = 0; kb < KBD; ++kb) tma_load_2d(s_kt + kb * (MP * 128), &tm_kt, small_full, kb * 64, (int)(bh * MP));
-      for (int kb = 0; kb < KBM; ++kb) tma_load_2d(s_st + kb * (D * 128), &tm_st, small_full, kb * 64, (int)(bh * D));
       int armed = 0;
       for (int i = 0; i < count; ++i) {
         const int st = i & 1;
@@ -213,7 +210,7 @@ tc_fwd_c_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   } else if (warp == kMmaWarp) {
     if (lane == 0) {
       constexpr uint32_t idesc1 = make_idesc<T>(kTile, MP, false, false);
-      constexpr uint32_t idesc2 = make_idesc<T>(kTile, D, false, false);
+      constexpr uint32_t idesc2 = make_idesc<T>(kTile, D, false, true);   // step2 (m x D) is read MN-major
       const uint32_t a_kt = smem_u32(s_kt), a_st = smem_u32(s_st);
       // Score product of tile i into S[i & 1].  That buffer was released when this thread passed
       // p_full of tile i-2, which precedes this call in program order.
@@ -240,7 +237,8 @@ tc_fwd_c_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         const uint32_t a_p = smem_u32(s_p + st * L::kP);
 #pragma unroll
         for (int k = 0; k < MP / 16; ++k)
-          umma(tmem_base + 2 * MP + st * D, kdesc(a_p, k, kTile), kdesc(a_st, k, D), idesc2, k > 0);
+          umma(tmem_base + 2 * MP + st * D, kdesc(a_p, k, kTile), smem_desc_sw128(a_st + k * 2048, MP * 128, 1024),
+               idesc2, k > 0);
         umma_commit(o_full + st);
         if (i + 2 < count) ok = front(i + 2);
       }
@@ -249,7 +247,11 @@ tc_fwd_c_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const int g = warp >> 2;                                  // compute group
     const int r = threadIdx.x & 127;                           // tile row = TMEM lane
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-    const float osc = st_scale[bh];
+    // operand copies of Kt and step2 for this slice (the P buffers are free until the first tile)
+    const float osc = pack_landmark_operands<T>(s_kt, s_st, k_landmarks + bh * m * D, step2 + bh * m * D, m,
+                                                scale * kLog2e, reinterpret_cast<float*>(s_p));
+    fence_proxy_async();
+    mbar_arrive(small_full);
     uint8_t* my_p = s_p + g * L::kP;
     const bool leader = r == 0;
     const bool full_m = m == MP;
