@@ -69,9 +69,9 @@ inline Plan make_plan(int64_t BH, int64_t N, int D, int m, int J) {
   p.mpad = (m + 15) / 16 * 16;
   const int64_t target = 592;  // 4 CTAs per SM on a 148-SM part
   int64_t seg = N / m;
-  // pooling pass: one CTA per (tensor, slice, landmark) unless that leaves the GPU under-filled
-  // (measured: cutting config 3's 2048 CTAs into 10240 smaller ones is slower, 84 vs 61 us)
-  int64_t c = (target + 2 * BH * m - 1) / (2 * BH * m);
+  // pooling pass: a persistent grid of 4 CTAs per SM walks (tensor, slice, landmark, chunk) items;
+  // about six items per CTA keep the last round of the walk short
+  int64_t c = (6 * target + 2 * BH * m - 1) / (2 * BH * m);
   int64_t cmax = (seg + 63) / 64;
   if (c > cmax) c = cmax;
   if (c < 1) c = 1;

@@ -321,7 +321,7 @@ static int forward_impl(const fnb_fwd_args& a, const Plan& p, const FwdWs& w, in
 
   if (S.run(0)) {
     L.begin();
-    int64_t grid = 2 * p.BH * p.m * lmC;
+    int64_t grid = std::min<int64_t>(2 * p.BH * p.m * lmC, (int64_t)sms * 4);
     landmark_partial_kernel<T><<<(unsigned)grid, kThreads, 0, st>>>(
         (const T*)a.q, (const T*)a.k, land, p.BH, p.N, p.D, p.m, lmC, seg_N, row_offset);
     if (L.end("landmark_partial")) return L.status;

@@ -73,59 +73,86 @@ __device__ __forceinline__ void load_small(float* dst, int ld, const float* src,
 
 // ------------------------------------------------------------------------------------------
 // Pass 1: raw segment sums of Q and K (landmark pooling).
-// 1-D grid of 2 * BH * m * C CTAs.  out[which][bh][l][c][D]
+// Work items (which, bh, landmark, chunk) are walked by a grid-stride loop, so the grid can be
+// sized to the machine.  out[which][bh][l][c][D]
 template <class T>
 __global__ void __launch_bounds__(kThreads)
 landmark_partial_kernel(const T* __restrict__ q, const T* __restrict__ k, float* __restrict__ out,
                         int64_t BH, int64_t N, int D, int m, int C, int64_t seg_N, int64_t row_offset) {
   constexpr int V = Vec16<T>::n;
   __shared__ float red[kThreads * 8];
-  const int64_t per_which = BH * m * C;
-  const int which = (int)(blockIdx.x / per_which);
-  const int64_t rest = blockIdx.x - which * per_which;
-  const int64_t bh = rest / (m * C);
-  const int lc = (int)(rest - bh * (m * C));
-  const int l = lc / C, c = lc - l * C;
-  const T* slice = (which ? k : q) + bh * N * D;
-  // segment l in global rows, clipped to the rows this rank holds, in local row numbers
-  Segments sg(seg_N, m);
-  int64_t start = sg.start(l) - row_offset, end = sg.end(l) - row_offset;
-  if (start < 0) start = 0;
-  if (end > N) end = N;
-  const int64_t len = end > start ? end - start : 0;
-  const int64_t per = (len + C - 1) / C;
-  const int64_t r0 = start + c * per;
-  int64_t r1 = r0 + per;
-  if (r1 > start + len) r1 = start + len;
+  const int64_t per_which = BH * m * C, items = 2 * per_which;
   const int vpr = D / V, rows_per_iter = kThreads / vpr;
   const int cv = threadIdx.x % vpr, ro = threadIdx.x / vpr;
-  float acc[V];
+  // lanes that hold the same columns are vpr apart: fold them with shuffles when that tiles a warp
+  const bool warp_fold = vpr <= 32 && (vpr & (vpr - 1)) == 0;
+  Segments sg(seg_N, m);
+  for (int64_t item = blockIdx.x; item < items; item += gridDim.x) {
+    const int which = (int)(item / per_which);
+    const int64_t rest = item - which * per_which;
+    const int64_t bh = rest / (m * C);
+    const int lc = (int)(rest - bh * (m * C));
+    const int l = lc / C, c = lc - l * C;
+    const T* slice = (which ? k : q) + bh * N * D;
+    // segment l in global rows, clipped to the rows this rank holds, in local row numbers
+    int64_t start = sg.start(l) - row_offset, end = sg.end(l) - row_offset;
+    if (start < 0) start = 0;
+    if (end > N) end = N;
+    const int64_t len = end > start ? end - start : 0;
+    const int64_t per = (len + C - 1) / C;
+    const int64_t r0 = start + c * per;
+    int64_t r1 = r0 + per;
+    if (r1 > start + len) r1 = start + len;
+    float acc[V];
 #pragma unroll
-  for (int e = 0; e < V; ++e) acc[e] = 0.f;
-  // four independent 16-byte loads in flight per thread
-  int64_t r = r0 + ro;
-  for (; r + 3 * rows_per_iter < r1; r += 4 * rows_per_iter) {
-    float x[4][V];
+    for (int e = 0; e < V; ++e) acc[e] = 0.f;
+    // eight independent 16-byte loads in flight per thread
+    int64_t r = r0 + ro;
+    for (; r + 7 * rows_per_iter < r1; r += 8 * rows_per_iter) {
+      uint4 raw[8];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) load16<T>(slice + (r + u * rows_per_iter) * D + cv * V, x[u]);
+      for (int u = 0; u < 8; ++u)
+        raw[u] = __ldcs(reinterpret_cast<const uint4*>(slice + (r + u * rows_per_iter) * D + cv * V));
 #pragma unroll
-    for (int u = 0; u < 4; ++u)
+      for (int u = 0; u < 8; ++u) {
+        const T* e16 = reinterpret_cast<const T*>(&raw[u]);
 #pragma unroll
-      for (int e = 0; e < V; ++e) acc[e] += x[u][e];
-  }
-  for (; r < r1; r += rows_per_iter) {
-    float x[V];
-    load16<T>(slice + r * D + cv * V, x);
+        for (int e = 0; e < V; ++e) acc[e] += to_f<T>(e16[e]);
+      }
+    }
+    for (; r < r1; r += rows_per_iter) {
+      float x[V];
+      load16<T>(slice + r * D + cv * V, x);
 #pragma unroll
-    for (int e = 0; e < V; ++e) acc[e] += x[e];
-  }
+      for (int e = 0; e < V; ++e) acc[e] += x[e];
+    }
+    float* dst = out + ((((size_t)which * BH + bh) * m + l) * C + c) * D;
+    if (warp_fold) {
+      for (int o = vpr; o < 32; o <<= 1)
 #pragma unroll
-  for (int e = 0; e < V; ++e) red[ro * D + cv * V + e] = acc[e];
-  __syncthreads();
-  if (threadIdx.x < D) {
-    float s = 0.f;
-    for (int r = 0; r < rows_per_iter; ++r) s += red[r * D + threadIdx.x];
-    out[((((size_t)which * BH + bh) * m + l) * C + c) * D + threadIdx.x] = s;
+        for (int e = 0; e < V; ++e) acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], o);
+      const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+      if (lane < vpr)
+#pragma unroll
+        for (int e = 0; e < V; ++e) red[w * D + lane * V + e] = acc[e];
+      __syncthreads();
+      if (threadIdx.x < D) {
+        float s = 0.f;
+#pragma unroll
+        for (int ww = 0; ww < kThreads / 32; ++ww) s += red[ww * D + threadIdx.x];
+        dst[threadIdx.x] = s;
+      }
+    } else {
+#pragma unroll
+      for (int e = 0; e < V; ++e) red[ro * D + cv * V + e] = acc[e];
+      __syncthreads();
+      if (threadIdx.x < D) {
+        float s = 0.f;
+        for (int rr = 0; rr < rows_per_iter; ++rr) s += red[rr * D + threadIdx.x];
+        dst[threadIdx.x] = s;
+      }
+    }
+    __syncthreads();   // red is reused by the next item
   }
 }
 
