@@ -86,6 +86,31 @@ inline Plan make_plan(int64_t BH, int64_t N, int D, int m, int J) {
   return p;
 }
 
+#ifdef __CUDACC__
+// Scaled landmark row from the raw segment sums of the pooling pass.
+//   land: [2][BH][m][C][D] partial sums (which = 0: Q, 1: K), head_dim D = 64.
+// Thread t returns columns 16 (t & 3) .. +15 of landmark row t >> 2 (zeros for rows >= m):
+// scale * sum / len(row), len from the floor-division segments of a length-seg_N sequence.
+__device__ __forceinline__ void pooled_row16(const float* land, int which, int64_t BH, int64_t bh, int m, int C,
+                                             int64_t seg_N, float scale, float* v) {
+  const int r = (threadIdx.x >> 2) & 63, c0 = (threadIdx.x & 3) * 16;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = 0.f;
+  if (r >= m) return;
+  const float* src = land + ((((size_t)which * BH + bh) * m + r) * C) * 64 + c0;
+  for (int c = 0; c < C; ++c) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const float4 x = *reinterpret_cast<const float4*>(src + (size_t)c * 64 + 4 * q);
+      v[4 * q] += x.x; v[4 * q + 1] += x.y; v[4 * q + 2] += x.z; v[4 * q + 3] += x.w;
+    }
+  }
+  const float f = scale / (float)Segments(seg_N, m).len(r);
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] *= f;
+}
+#endif
+
 inline size_t align256(size_t x) { return (x + 255) / 256 * 256; }
 
 }  // namespace fnb

@@ -341,7 +341,12 @@ static int forward_impl(const fnb_fwd_args& a, const Plan& p, const FwdWs& w, in
 
   if (S.run(1)) {
   Fork fork(st, a.device, smem_ns && !L.prof && allow_inner_fork);   // side stream for the pseudoinverse (off while profiling)
+  // With the tensor-core kernels the landmarks are formed from the raw segment sums inside their
+  // two consumers (the Newton-Schulz forward writes the FP32 copies, the column pass packs its own
+  // 16-bit operand), so the finalize kernel is skipped.
+  const bool fused_landmarks = smem_ns && use_tc && p.D == 64 && ns_on_tensor_cores(a.shape.flags);
   if (smem_ns) {
+    if (!fused_landmarks) {
     L.begin();
     {
       LandmarkFinalizeParams lp;
@@ -351,6 +356,7 @@ static int forward_impl(const fnb_fwd_args& a, const Plan& p, const FwdWs& w, in
       landmark_finalize_kernel<<<dim3((unsigned)p.BH, 8), kThreads, 0, st>>>(lp);
     }
     if (L.end("landmark_finalize")) return L.status;
+    }
     // The pseudoinverse only feeds the combine step, so it runs beside the column pass.
     cudaStream_t ns_stream = fork.begin();
     L.begin();
@@ -358,6 +364,8 @@ static int forward_impl(const fnb_fwd_args& a, const Plan& p, const FwdWs& w, in
     np.qt = a.q_landmarks; np.kt = a.k_landmarks; np.k2 = a.k2; np.lse2 = a.lse2;
     np.iterates = a.ns_iterates; np.k2inv = a.k2_inv; np.m = p.m; np.D = p.D; np.J = p.J;
     np.kappa = a.shape.kappa_star;
+    np.land = fused_landmarks ? land : nullptr; np.C = lmC; np.BH = p.BH; np.seg_N = seg_N; np.scale = scale;
+    np.qt_out = a.q_landmarks; np.kt_out = a.k_landmarks;
     if (ns_on_tensor_cores(a.shape.flags)) {
       if (int rc = set_smem(nstc::ns_fwd_tc_kernel, nstc::kFwdSmem, max_smem, "ns_fwd")) return rc;
       nstc::ns_fwd_tc_kernel<<<(unsigned)p.BH, nstc::kNsTcThreads, nstc::kFwdSmem, ns_stream>>>(np, a.device_status);
@@ -394,8 +402,9 @@ static int forward_impl(const fnb_fwd_args& a, const Plan& p, const FwdWs& w, in
       auto kern = tc::tc_fwd_b_kernel<T, D, MPc>;
       size_t smem = tc::FwdBSmem<D, MPc>::kBytes;
       if (int rc = set_smem(kern, smem, max_smem, "tc_fwd_b")) return rc;
-      kern<<<(unsigned)(p.BH * sch.nchunk), tc::kTcThreads, smem, st>>>(tm_k, tm_v, tm_qt, w.part_acc, w.part_max,
-                                                                      w.part_sum, sch, p.m, a.device_status);
+      kern<<<(unsigned)(p.BH * sch.nchunk), tc::kTcThreads, smem, st>>>(
+          tm_k, tm_v, tm_qt, fused_landmarks ? land : (const float*)nullptr, lmC, p.BH, scale, w.part_acc, w.part_max,
+          w.part_sum, sch, p.m, a.device_status);
       if (L.end("tc_fwd_b")) return L.status;
     }
   }

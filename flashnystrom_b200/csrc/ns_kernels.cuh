@@ -236,6 +236,10 @@ struct NsFwdParams {
   float* k2; float* lse2; float* iterates; float* k2inv;
   int m, D, J;
   float kappa;
+  // Optional (tensor-core kernel, head_dim 64): form the landmarks here from the raw segment sums
+  // of the pooling pass, land [2][BH][m][C][D], and write them to qt_out / kt_out.
+  const float* land; int C; int64_t BH; int64_t seg_N; float scale;
+  float* qt_out; float* kt_out;
 };
 
 __device__ inline void softmax_rows(float* bK2, const NsFwdParams& p, int64_t bh);

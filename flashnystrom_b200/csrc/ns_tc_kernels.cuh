@@ -432,8 +432,23 @@ __device__ inline void pinv_forward_tc(Ctx& c, float* red, float* iterates, floa
 __device__ inline void s2_softmax_tc(Ctx& c, const ns::NsFwdParams& p, int64_t bh) {
   const int m = p.m, D = p.D;
   float q[16], k[16], v[16];
-  load_global16(p.qt + bh * m * D, m, D, D, q);
-  load_global16(p.kt + bh * m * D, m, D, D, k);
+  if (p.land) {
+    pooled_row16(p.land, 0, p.BH, bh, m, p.C, p.seg_N, p.scale, q);
+    pooled_row16(p.land, 1, p.BH, bh, m, p.C, p.seg_N, p.scale, k);
+    const int r = threadIdx.x >> 2, c0 = (threadIdx.x & 3) * 16;
+    if (r < m) {
+      float4* dq = reinterpret_cast<float4*>(p.qt_out + (bh * m + r) * D + c0);
+      float4* dk = reinterpret_cast<float4*>(p.kt_out + (bh * m + r) * D + c0);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        dq[i] = make_float4(q[4 * i], q[4 * i + 1], q[4 * i + 2], q[4 * i + 3]);
+        dk[i] = make_float4(k[4 * i], k[4 * i + 1], k[4 * i + 2], k[4 * i + 3]);
+      }
+    }
+  } else {
+    load_global16(p.qt + bh * m * D, m, D, D, q);
+    load_global16(p.kt + bh * m * D, m, D, D, k);
+  }
   store_set16(c.slot(0), q);
   store_set16(c.slot(1), k);
   tiles_ready(c);

@@ -1080,7 +1080,8 @@ struct FwdBSmem {
 template <class T, int D, int MP>
 __global__ void __launch_bounds__(kTcThreads, 2)
 tc_fwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
-                const __grid_constant__ CUtensorMap tm_qt, float* __restrict__ part_acc,
+                const __grid_constant__ CUtensorMap tm_qt, const float* __restrict__ land, int land_chunks,
+                int64_t land_bh, float scale, float* __restrict__ part_acc,
                 float* __restrict__ part_max, float* __restrict__ part_sum, TcSched sch, int m,
                 int* status) {
   using L = FwdBSmem<D, MP>;
@@ -1119,7 +1120,7 @@ tc_fwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
   const int tile0 = tr.tile0, count = tr.count;
 
   if (threadIdx.x == 0) {
-    mbar_init(small_full, 1);
+    mbar_init(small_full, land ? kComputeThreads : 1);
     for (int s = 0; s < 2; ++s) {
       mbar_init(k_full + s, 1); mbar_init(k_empty + s, 1); mbar_init(v_full + s, 1); mbar_init(v_empty + s, 1);
       mbar_init(s_full + s, 1);
@@ -1149,9 +1150,11 @@ tc_fwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
     if (lane == 0) {
       tma_prefetch_desc(&tm_k);
       tma_prefetch_desc(&tm_v);
-      mbar_expect_tx(small_full, L::kQt);
-      for (int kb = 0; kb < KBD; ++kb)
-        tma_load_2d(s_qt + kb * (MP * 128), &tm_qt, small_full, kb * 64, (int)(bh * MP));
+      if (!land) {
+        mbar_expect_tx(small_full, L::kQt);
+        for (int kb = 0; kb < KBD; ++kb)
+          tma_load_2d(s_qt + kb * (MP * 128), &tm_qt, small_full, kb * 64, (int)(bh * MP));
+      }
       int nk = 0, nv = 0;
       for (int i = 0; i < count; ++i) {
         const int st = i & 1;
@@ -1218,6 +1221,22 @@ tc_fwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
     const int lrow = (MP == 128) ? r : (quarter * 16 + lane);          // accumulator row of this lane
     const bool owner = (MP == 128) ? true : (lane < 16);
     if (threadIdx.x < MP) s_ref[threadIdx.x] = -INFINITY;
+    if (land) {
+      // 16-bit landmark operand s*log2e*Qt straight from the raw segment sums of the pooling pass
+      float qv[16];
+      pooled_row16(land, 0, land_bh, bh, m, land_chunks, sch.seg_N, scale, qv);
+      const float mul = scale * kLog2e;
+      const int pr = threadIdx.x >> 2, pc = (threadIdx.x & 3) * 2;
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint4 wq;
+        wq.x = pack2<T>(qv[8 * c + 0] * mul, qv[8 * c + 1] * mul); wq.y = pack2<T>(qv[8 * c + 2] * mul, qv[8 * c + 3] * mul);
+        wq.z = pack2<T>(qv[8 * c + 4] * mul, qv[8 * c + 5] * mul); wq.w = pack2<T>(qv[8 * c + 6] * mul, qv[8 * c + 7] * mul);
+        *reinterpret_cast<uint4*>(s_qt + sw128_offset(pr, pc + c)) = wq;
+      }
+      fence_proxy_async();
+      mbar_arrive(small_full);
+    }
     bool alive = true;
     for (int i = 0; i < count; ++i) {
       const int st = i & 1;
