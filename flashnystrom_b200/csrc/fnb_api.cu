@@ -241,6 +241,7 @@ struct BwdWs {
   void* op16[8];              // 16-bit operand copies for the tensor-core kernels
   float *st_scale, *do3_scale, *rows_q, *rows_k;
   float* d1;                  // [BH][N]: softmax-1 row terms D1, written by pass A for pass C
+  float* partA_red;           // [BH][2][m][D]: pass-A partials summed over the chunks
   size_t bytes;
 };
 static BwdWs carve_bwd(const Plan& p, void* base) {
@@ -262,6 +263,7 @@ static BwdWs carve_bwd(const Plan& p, void* base) {
   w.st_scale = take((size_t)p.BH); w.do3_scale = take((size_t)p.BH);
   w.rows_q = take(md); w.rows_k = take(md);
   w.d1 = take((size_t)p.BH * p.N);
+  w.partA_red = take(2 * md);
   w.bytes = off;
   return w;
 }
@@ -608,7 +610,16 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
         if (int rc = set_smem(nstc::ns_bwd_tc_kernel, nstc::kBwdSmem, max_smem, "ns_bwd")) return rc;
         nstc::BwdHeadParams hp{};
         if (fused_mid) {
-          hp.partA = partA_src; hp.nchunk = partA_chunks; hp.k2inv = a.k2_inv; hp.bmat = a.bmat;
+          // one SM per slice is slow at summing many chunk partials (L2 -> SM bandwidth): a wide
+          // reduction first, then the fused stage reads a single chunk
+          const float* pa = partA_src;
+          int pa_chunks = partA_chunks;
+          if (pa_chunks > 4) {
+            reduce_chunks(pa, pa_chunks, 2 * p.m * p.D, w.partA_red);
+            pa = w.partA_red;
+            pa_chunks = 1;
+          }
+          hp.partA = pa; hp.nchunk = pa_chunks; hp.k2inv = a.k2_inv; hp.bmat = a.bmat;
           hp.dkt_a = w.dkt_a; hp.D3 = w.D3; hp.do3n = do3n; hp.do3_scale = w.do3_scale; hp.qt16 = qt16;
           hp.qt_mul = scale * tc::kLog2e; hp.dtype = a.shape.dtype; hp.MP = MP;
         }
