@@ -49,6 +49,7 @@ constexpr uint32_t kAcc0 = 0, kAcc1 = 256;  // TMEM column of the two accumulato
 
 // Optional phase timestamps of CTA 0 (profiling builds only).
 #ifdef FNB_NS_TRACE
+__device__ unsigned long long g_ns_span[2 * 64];   // per-CTA kernel entry / exit times
 __device__ unsigned long long g_ns_trace[160];
 __device__ int g_ns_trace_n;
 #define NS_TRACE()                                                                                  \
@@ -865,6 +866,9 @@ __device__ inline void bwd_head_tc(Ctx& c, float* red, const ns::NsBwdParams& p,
 __global__ void __launch_bounds__(kNsTcThreads, 1)
 ns_bwd_tc_kernel(ns::NsBwdParams p, BwdHeadParams h, int* status) {
   extern __shared__ uint8_t dyn_smem[];
+#ifdef FNB_NS_TRACE
+  if (threadIdx.x == 0 && blockIdx.x < 64) g_ns_span[2 * blockIdx.x] = global_ns();
+#endif
   __shared__ float red[ns::kRedFloats];
   __shared__ Shared sh;
   Ctx c;
@@ -890,6 +894,9 @@ ns_bwd_tc_kernel(ns::NsBwdParams p, BwdHeadParams h, int* status) {
   }
   ctx_close(c, kBwdTmemCols);
   NS_TRACE();
+#ifdef FNB_NS_TRACE
+  if (threadIdx.x == 0 && blockIdx.x < 64) g_ns_span[2 * blockIdx.x + 1] = global_ns();
+#endif
 }
 
 }  // namespace nstc
