@@ -599,6 +599,17 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
     }
     if (L.end("bwd_mid1")) return L.status;
     }
+    // One SM per slice is slow at summing many chunk partials (L2 -> SM bandwidth): a wide
+    // reduction first, then the fused stage reads a single chunk.
+    const float* fused_pa = partA_src;
+    int fused_pa_chunks = partA_chunks;
+    if (fused_mid && partA_chunks > 4) {
+      L.begin();
+      reduce_chunks(partA_src, partA_chunks, 2 * p.m * p.D, w.partA_red);
+      if (L.end("reduce_partA")) return L.status;
+      fused_pa = w.partA_red;
+      fused_pa_chunks = 1;
+    }
     L.begin();
     {
       ns::NsBwdParams np;
@@ -610,16 +621,7 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
         if (int rc = set_smem(nstc::ns_bwd_tc_kernel, nstc::kBwdSmem, max_smem, "ns_bwd")) return rc;
         nstc::BwdHeadParams hp{};
         if (fused_mid) {
-          // one SM per slice is slow at summing many chunk partials (L2 -> SM bandwidth): a wide
-          // reduction first, then the fused stage reads a single chunk
-          const float* pa = partA_src;
-          int pa_chunks = partA_chunks;
-          if (pa_chunks > 4) {
-            reduce_chunks(pa, pa_chunks, 2 * p.m * p.D, w.partA_red);
-            pa = w.partA_red;
-            pa_chunks = 1;
-          }
-          hp.partA = pa; hp.nchunk = pa_chunks; hp.k2inv = a.k2_inv; hp.bmat = a.bmat;
+          hp.partA = fused_pa; hp.nchunk = fused_pa_chunks; hp.k2inv = a.k2_inv; hp.bmat = a.bmat;
           hp.dkt_a = w.dkt_a; hp.D3 = w.D3; hp.do3n = do3n; hp.do3_scale = w.do3_scale; hp.qt16 = qt16;
           hp.qt_mul = scale * tc::kLog2e; hp.dtype = a.shape.dtype; hp.MP = MP;
         }
