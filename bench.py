@@ -359,12 +359,12 @@ def main():
     hout, hdq, hdk, hdv = (torch.empty_like(hq).pin_memory() for _ in range(4))
 
     # A caller whose tensors live in host memory pipelines over the independent (b,h) slices:
-    # groups of heads go through copy-in -> forward+backward -> copy-out on a few streams, so the
+    # groups of heads go through copy-in -> forward+backward -> copy-out on their own streams, so the
     # two PCIe directions and the kernels overlap.  Every step still moves all inputs in and all
     # results out, and the step ends only when the last result has landed in host memory.
-    n_groups = 8 if (B == 1 and H % 8 == 0) else 1
+    n_groups = H if B == 1 else 1            # one head per group: short ramp-up and drain
     hpg = H // n_groups
-    streams = [torch.cuda.Stream(device=dev) for _ in range(min(4, n_groups))]
+    streams = [torch.cuda.Stream(device=dev) for _ in range(n_groups)]   # no group waits behind another's copy-out
 
     def group_e2e(g):
         h0, h1 = g * hpg, (g + 1) * hpg

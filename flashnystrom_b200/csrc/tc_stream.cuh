@@ -1069,13 +1069,14 @@ tc_bwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
 // moves when a tile exceeds it by more than 2^8 (then the TMEM accumulators are rescaled in
 // place), so probabilities stay <= 256 in the 16-bit operand copy and rescales are rare.  Row
 // sums come from the tensor core too (P'^T times a block of ones).  S is double-buffered in
-// TMEM, K and V have separate two-stage rings (K is free after the score product, V after the
-// accumulation).
+// TMEM and P' in shared memory (a tile's probabilities are written while the previous tile's
+// accumulation still reads its own copy); K and V have separate two-stage rings (K is free
+// after the score product, V after the accumulation).
 template <int D, int MP>
 struct FwdBSmem {
   static constexpr int kQt = MP * D * 2, kOnes = 2048, kIn = kTile * D * 2, kP = kTile * MP * 2,
                        kAux = 1024 * ((7 * MP * 4 + 64 + 1023) / 1024);
-  static constexpr int kBytes = kQt + kOnes + 4 * kIn + kP + kAux + 256 + 1024;
+  static constexpr int kBytes = kQt + kOnes + 4 * kIn + 2 * kP + kAux + 256 + 1024;
 };
 
 template <class T, int D, int MP>
@@ -1097,8 +1098,8 @@ tc_fwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
   uint8_t* s_ones = s_qt + L::kQt;
   uint8_t* s_k = s_ones + L::kOnes;            // two stages
   uint8_t* s_v = s_k + 2 * L::kIn;             // two stages
-  uint8_t* s_p = s_v + 2 * L::kIn;
-  float* s_wmax = reinterpret_cast<float*>(s_p + L::kP);   // [4][MP]
+  uint8_t* s_p = s_v + 2 * L::kIn;             // two buffers, tile parity
+  float* s_wmax = reinterpret_cast<float*>(s_p + 2 * L::kP);   // [4][MP]
   float* s_ref = s_wmax + 4 * MP;                          // [MP] running reference (log2 domain)
   float* s_fac = s_ref + MP;                               // [MP] rescale factor of this tile
   float* s_new = s_fac + MP;                               // [MP] scratch
@@ -1110,8 +1111,8 @@ tc_fwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
   uint64_t* v_full = bars + 5;      // [2]
   uint64_t* v_empty = bars + 7;     // [2]
   uint64_t* s_full = bars + 9;      // [2]
-  uint64_t* p_full = bars + 11;
-  uint64_t* acc_done = bars + 12;
+  uint64_t* p_full = bars + 11;     // [2], tile parity
+  uint64_t* acc_done = bars + 13;   // [2], tile parity
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
   int* abort_word = reinterpret_cast<int*>(tmem_slot + 1);
 
@@ -1127,7 +1128,9 @@ tc_fwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
       mbar_init(s_full + s, 1);
     }
     mbar_init(p_full, kComputeThreads);
+    mbar_init(p_full + 1, kComputeThreads);
     mbar_init(acc_done, 1);
+    mbar_init(acc_done + 1, 1);
     *abort_word = 0;
     s_flag[0] = 0; s_flag[1] = 0; s_flag[2] = 0;
     fence_mbar_init();
@@ -1198,19 +1201,20 @@ tc_fwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
       if (ok && count > 1) ok = front(1);
       for (int i = 0; ok && i < count; ++i) {
         const int st = i & 1;
-        if (!mbar_wait(p_full, i & 1, ab, 0x3400 + i)) break;
+        if (!mbar_wait(p_full + st, (i >> 1) & 1, ab, 0x3400 + i)) break;
         if (!mbar_wait(v_full + st, (i >> 1) & 1, ab, 0x3480 + i)) break;
         tc_fence_after();
         const uint32_t a_v = smem_u32(s_v + st * L::kIn);
+        const uint32_t a_pi = a_p + st * L::kP;
 #pragma unroll
         for (int k = 0; k < kTile / 16; ++k)
-          umma(tmem_acc, mndesc(a_p, k), mndesc(a_v, k), idesc_acc, (i > 0 || k > 0));
+          umma(tmem_acc, mndesc(a_pi, k), mndesc(a_v, k), idesc_acc, (i > 0 || k > 0));
 #pragma unroll
         for (int k = 0; k < kTile / 16; ++k)
-          umma(tmem_acc + D, mndesc(a_p, k), smem_desc_sw128(a_ones + (k & 3) * 32, 16, 1024), idesc_sum,
+          umma(tmem_acc + D, mndesc(a_pi, k), smem_desc_sw128(a_ones + (k & 3) * 32, 16, 1024), idesc_sum,
                (i > 0 || k > 0));
         umma_commit(v_empty + st);
-        umma_commit(acc_done);
+        umma_commit(acc_done + st);
         if (i + 2 < count) ok = front(i + 2);
       }
     }
@@ -1275,9 +1279,14 @@ tc_fwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
       }
       named_barrier(1, kComputeThreads);
       const bool move = s_flag[i % 3] != 0;     // CTA-uniform
-      if (i > 0) {
-        // previous tile's accumulation still reads the P' tile and writes the accumulators
-        if (!mbar_wait(acc_done, (i - 1) & 1, ab, 0x3700 + i)) { alive = false; break; }
+      if (i > 1) {
+        // the accumulation of tile i-2 read the P' buffer this tile is about to fill
+        if (!mbar_wait(acc_done + st, (uint32_t)((i - 2) >> 1) & 1u, ab, 0x3700 + i)) { alive = false; break; }
+        __syncwarp();
+      }
+      if (move && i > 0) {
+        // the accumulators are rescaled in place: every accumulation issued so far must be complete
+        if (!mbar_wait(acc_done + (st ^ 1), (uint32_t)((i - 1) >> 1) & 1u, ab, 0x3780 + i)) { alive = false; break; }
         __syncwarp();
         tc_fence_after();
       }
@@ -1313,12 +1322,12 @@ tc_fwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
         s[j + 2] = fast_exp2(s[j + 2] - c.z);
         s[j + 3] = fast_exp2(s[j + 3] - c.w);
       }
-      store_cols<T, HC>(s_p, r, c0, s);
+      store_cols<T, HC>(s_p + st * L::kP, r, c0, s);
       fence_proxy_async();
       tc_fence_before();
-      mbar_arrive(p_full);
+      mbar_arrive(p_full + st);
     }
-    if (alive && mbar_wait(acc_done, (count - 1) & 1, ab, 0x3900)) {
+    if (alive && mbar_wait(acc_done + ((count - 1) & 1), (uint32_t)((count - 1) >> 1) & 1u, ab, 0x3900)) {
       __syncwarp();
       tc_fence_after();
       const size_t slot = (size_t)bh * sch.nchunk + tr.chunk;
