@@ -130,15 +130,22 @@ class _SeqParallelFunction(torch.autograd.Function):
         rank, world = dist.get_rank(group), dist.get_world_size(group)
         c = CudaContext(q, k, v, num_landmarks, newton_iter, kappa_star, rank, world)
         forward_collectives(c, group)
+        # The backward does not read the output.  Keeping it on the context would tie the returned
+        # tensor to its own grad_fn (out -> grad_fn -> ctx -> context -> out): such a cycle is only
+        # collected by the garbage collector, and every step would allocate fresh device memory.
+        out, c.out = c.out, None
+        c.ws_f = None
         ctx.sp, ctx.group = c, group
-        return c.out
+        return out
 
     @staticmethod
     def backward(ctx, grad_output):
         c = ctx.sp
         c.begin_backward(grad_output)
         backward_collectives(c, ctx.group)
-        return c.dq, c.dk, c.dv, None, None, None, None
+        dq, dk, dv = c.dq, c.dk, c.dv
+        c.dq = c.dk = c.dv = c.d_out = c.ws_b = None      # the context may outlive this call
+        return dq, dk, dv, None, None, None, None
 
 
 def seq_parallel_nystrom_attention(q, k, v, num_landmarks=64, newton_iter=6, kappa_star=0.0, group=None):
