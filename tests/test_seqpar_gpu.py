@@ -75,3 +75,60 @@ def test_world_one_equals_plain_call(cuda_device):
     g = _C.backward(dO.cuda(), *res[1:13], v.cuda(), res[0], 64, 6)
     for a, b in ((out, res[0]), (dq, g[0]), (dk, g[1]), (dv, g[2])):
         assert O.rel_max(a, b.cpu()) < 2e-3
+
+
+_NCCL_CHILD = r"""
+import os, sys, torch, torch.distributed as dist
+sys.path.insert(0, sys.argv[1])
+from flashnystrom_b200 import _C, flash_nystrom_attention
+from flashnystrom_b200.seqpar import seq_parallel_nystrom_attention
+os.environ["MASTER_ADDR"] = "127.0.0.1"
+os.environ["MASTER_PORT"] = sys.argv[2]
+torch.cuda.set_device(0)
+dist.init_process_group("nccl", rank=0, world_size=1, device_id=torch.device("cuda", 0))
+g = torch.Generator(device="cuda").manual_seed(3)
+q, k, v = (torch.randn(1, 2, 4096, 64, device="cuda", dtype=torch.float16, generator=g).requires_grad_(True)
+           for _ in range(3))
+dO = torch.randn(1, 2, 4096, 64, device="cuda", dtype=torch.float16, generator=g)
+def step():
+    q.grad = k.grad = v.grad = None
+    out = seq_parallel_nystrom_attention(q, k, v, 64, 6)
+    out.backward(dO)
+    return out
+for _ in range(3):
+    out = step()
+torch.cuda.synchronize()
+allocs = torch.cuda.memory_stats()["num_device_alloc"]
+for _ in range(6):
+    out = step()
+torch.cuda.synchronize()
+_C.check_device_status()
+grew = torch.cuda.memory_stats()["num_device_alloc"] - allocs
+sp = [t.detach().float().cpu() for t in (out, q.grad, k.grad, v.grad)]
+q.grad = k.grad = v.grad = None
+ref_out = flash_nystrom_attention(q, k, v, num_landmarks=64, newton_iter=6)
+ref_out.backward(dO)
+ref = [t.detach().float().cpu() for t in (ref_out, q.grad, k.grad, v.grad)]
+err = max(float((a - b).abs().max() / b.abs().max()) for a, b in zip(sp, ref))
+dist.destroy_process_group()
+print("RESULT", grew, err)
+"""
+
+
+def test_nccl_world1_autograd_path(cuda_device, tmp_path):
+    """The real torch.distributed (NCCL) path on one GPU, world size 1, in a child process: same
+    results as the unsharded call, and steady-state steps allocate no new device memory (the
+    autograd context must not keep the returned output alive through a reference cycle)."""
+    import os
+    import subprocess
+    import sys
+    script = tmp_path / "nccl_child.py"
+    script.write_text(_NCCL_CHILD)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    port = str(29600 + os.getpid() % 300)
+    res = subprocess.run([sys.executable, str(script), root, port], capture_output=True, text=True, timeout=240)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
+    line = [ln for ln in res.stdout.splitlines() if ln.startswith("RESULT")][-1].split()
+    grew, err = int(line[1]), float(line[2])
+    assert grew == 0, f"{grew} new device allocations over 6 steady-state steps"
+    assert err <= 2e-3, f"sequence-parallel (world 1) vs unsharded rel_max {err}"
