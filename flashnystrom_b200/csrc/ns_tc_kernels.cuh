@@ -70,7 +70,7 @@ struct Ctx {
   uint8_t* base;        // 1024-byte aligned start of the tile slots
   float* xch;           // exchange buffer (row stride kLd)
   uint64_t* bar;        // two completion barriers (MMA groups -> compute warps)
-  uint64_t* ready;      // operand tiles written (256 compute threads -> issuing thread)
+  uint64_t* ready;      // operand tiles written (one arrival per compute warp -> issuing thread)
   uint32_t phase[2];    // parity the next wait on each completion barrier uses
   uint32_t rphase;      // parity the next wait on `ready` uses
   bool failed;          // a wait of this thread gave up
@@ -187,7 +187,7 @@ __device__ __forceinline__ bool is_issuer() { return threadIdx.x == kComputeThre
 __device__ __forceinline__ void tiles_ready(Ctx& c) {
   fence_proxy_async();
   tc_fence_before();
-  mbar_arrive(c.ready);
+  mbar_arrive_warp(c.ready);
 }
 // compute side: wait for MMA group g (0 or 1) of the current batch
 __device__ __forceinline__ void wait_group(Ctx& c, int g, int where) {
@@ -317,7 +317,7 @@ __device__ __forceinline__ void ctx_open(Ctx& c, Shared& sh, uint8_t* dyn, int s
     sh.abort_word = 0;
     mbar_init(&sh.bar[0], 1);
     mbar_init(&sh.bar[1], 1);
-    mbar_init(&sh.ready, kComputeThreads);
+    mbar_init(&sh.ready, kComputeThreads / 32);
     fence_mbar_init();
   }
   if (threadIdx.x < 32) {

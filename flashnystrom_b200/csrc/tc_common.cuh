@@ -42,6 +42,14 @@ __device__ __forceinline__ void fence_mbar_init() {
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// One arrival per warp: every lane has already fenced its own shared-memory stores and TMEM
+// loads, the warp converges (which orders the lanes' memory operations), and one lane arrives
+// for all 32.  A barrier fed this way is initialised with the number of arriving WARPS; 8 or 4
+// arrivals instead of 256 or 128 serialised ones shorten the hand-over to the MMA thread.
+__device__ __forceinline__ void mbar_arrive_warp(uint64_t* bar) {
+  __syncwarp();
+  if ((threadIdx.x & 31) == 0) mbar_arrive(bar);
+}
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
                : "memory");

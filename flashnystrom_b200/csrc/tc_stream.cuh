@@ -173,10 +173,10 @@ tc_fwd_c_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const int tile0 = tr.tile0, count = tr.count;
 
   if (threadIdx.x == 0) {
-    mbar_init(small_full, kComputeThreads);
+    mbar_init(small_full, kComputeThreads / 32);
     for (int s = 0; s < 2; ++s) {
       mbar_init(q_full + s, 1); mbar_init(q_empty + s, 1); mbar_init(s_full + s, 1);
-      mbar_init(p_full + s, kGroup); mbar_init(o_full + s, 1); mbar_init(o_free + s, kGroup);
+      mbar_init(p_full + s, kGroup / 32); mbar_init(o_full + s, 1); mbar_init(o_free + s, kGroup / 32);
     }
     *abort_word = 0;
     fence_mbar_init();
@@ -251,7 +251,7 @@ tc_fwd_c_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const float osc = pack_landmark_operands<T>(s_kt, s_st, k_landmarks + bh * m * D, step2 + bh * m * D, m,
                                                 scale * kLog2e, reinterpret_cast<float*>(s_p));
     fence_proxy_async();
-    mbar_arrive(small_full);
+    mbar_arrive_warp(small_full);
     uint8_t* my_p = s_p + g * L::kP;
     const bool leader = r == 0;
     const bool full_m = m == MP;
@@ -292,7 +292,7 @@ tc_fwd_c_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       store_cols<T, MP>(my_p, r, 0, s);
       fence_proxy_async();
       tc_fence_before();
-      mbar_arrive(p_full + g);
+      mbar_arrive_warp(p_full + g);
       const float mul = osc / tot;
       const int64_t row = (int64_t)(tile0 + i) * kTile + r;
       if (row < sch.N) lse1[bh * sch.N + row] = (mx + log2f(tot)) * kLn2;
@@ -304,7 +304,7 @@ tc_fwd_c_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       ld_cols<D>(tmem_base + 2 * MP + g * D + lane_base, o);
       tmem_ld_wait();
       tc_fence_before();
-      mbar_arrive(o_free + g);
+      mbar_arrive_warp(o_free + g);
 #pragma unroll
       for (int j = 0; j < D; ++j) o[j] *= mul;
       store_cols<T, D>(my_p, r, 0, o);        // the product that read P from my_p has completed
@@ -387,10 +387,10 @@ tc_bwd_ac_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   const int tile0 = tr.tile0, count = tr.count;
 
   if (threadIdx.x == 0) {
-    mbar_init(small_full, kComputeThreads);
+    mbar_init(small_full, kComputeThreads / 32);
     for (int s = 0; s < 2; ++s) {
       mbar_init(in_full + s, 1); mbar_init(in_empty + s, 1); mbar_init(sdp_full + s, 1);
-      mbar_init(pds_full + s, kComputeThreads); mbar_init(acc_done + s, 1); mbar_init(o_free + s, kComputeThreads);
+      mbar_init(pds_full + s, kComputeThreads / 32); mbar_init(acc_done + s, 1); mbar_init(o_free + s, kComputeThreads / 32);
     }
     *abort_word = 0;
     fence_mbar_init();
@@ -493,7 +493,7 @@ tc_bwd_ac_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const float sc = pack_landmark_operands<T>(s_kt, s_st, k_landmarks + bh * m * D, step2 + bh * m * D, m,
                                                scale * kLog2e, reinterpret_cast<float*>(s_ds));
     fence_proxy_async();
-    mbar_arrive(small_full);
+    mbar_arrive_warp(small_full);
     const int c0 = h * HC;
     Segments sg(sch.seg_N, m);
     bool alive = true;
@@ -539,7 +539,7 @@ tc_bwd_ac_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       store_cols<T, HC>(s_ds, r, c0, g);
       fence_proxy_async();
       tc_fence_before();
-      mbar_arrive(pds_full + b);
+      mbar_arrive_warp(pds_full + b);
 
       if (MODE == kModeC) {
         if (!mbar_wait(acc_done + b, ph, ab, 0x1800 + i)) { alive = false; break; }
@@ -549,7 +549,7 @@ tc_bwd_ac_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         ld_cols<HD>(tmem_base + b * 2 * MP + lane_base + h * HD, o);
         tmem_ld_wait();
         tc_fence_before();
-        mbar_arrive(o_free + b);
+        mbar_arrive_warp(o_free + b);
         const int l = valid ? sg.landmark_of(sch.row_offset + row) : 0;
         const float4* add = reinterpret_cast<const float4*>(rows_q + (bh * m + l) * D + h * HD);
         const float mul = sc * kLn2;
@@ -653,10 +653,10 @@ tc_bwd_c_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const int tile0 = tr.tile0, count = tr.count;
 
   if (threadIdx.x == 0) {
-    mbar_init(small_full, kComputeThreads);
+    mbar_init(small_full, kComputeThreads / 32);
     for (int s = 0; s < 2; ++s) {
       mbar_init(in_full + s, 1); mbar_init(in_empty + s, 1); mbar_init(sdp_full + s, 1);
-      mbar_init(pds_full + s, kGroup); mbar_init(acc_done + s, 1); mbar_init(o_free + s, kGroup);
+      mbar_init(pds_full + s, kGroup / 32); mbar_init(acc_done + s, 1); mbar_init(o_free + s, kGroup / 32);
     }
     *abort_word = 0;
     fence_mbar_init();
@@ -738,7 +738,7 @@ tc_bwd_c_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const float sc = pack_landmark_operands<T>(s_kt, s_st, k_landmarks + bh * m * D, step2 + bh * m * D, m,
                                                scale * kLog2e, reinterpret_cast<float*>(s_ds));
     fence_proxy_async();
-    mbar_arrive(small_full);
+    mbar_arrive_warp(small_full);
     const float mul = sc * kLn2;
     uint8_t* my_ds = s_ds + g * L::kDs;
     const uint32_t t_s = tmem_base + g * 2 * MP + lane_base;
@@ -771,7 +771,7 @@ tc_bwd_c_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
       fence_proxy_async();
       tc_fence_before();
-      mbar_arrive(pds_full + g);
+      mbar_arrive_warp(pds_full + g);
       // dQ tile of the same rows
       const int l = valid ? sg.landmark_of(sch.row_offset + row) : 0;
       const float4* add = reinterpret_cast<const float4*>(rows_q + (bh * m + l) * D);
@@ -786,7 +786,7 @@ tc_bwd_c_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         tmem_ld_wait();
         if (hf == 1) {
           tc_fence_before();
-          mbar_arrive(o_free + g);
+          mbar_arrive_warp(o_free + g);
         }
 #pragma unroll
         for (int j = 0; j < 32; j += 4) {
@@ -876,9 +876,9 @@ tc_bwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
     for (int s = 0; s < 2; ++s) { mbar_init(k_full + s, 1); mbar_init(k_empty + s, 1); }
     mbar_init(v_full, 1); mbar_init(v_empty, 1);
     mbar_init(sdp_full, 1);
-    mbar_init(pds_full, kComputeThreads);
+    mbar_init(pds_full, kComputeThreads / 32);
     mbar_init(out_full, 1);
-    mbar_init(o_free, kComputeThreads);
+    mbar_init(o_free, kComputeThreads / 32);
     *abort_word = 0;
     fence_mbar_init();
   }
@@ -1003,7 +1003,7 @@ tc_bwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
       store_cols<T, HC>(s_ds, r, c0, g);
       fence_proxy_async();
       tc_fence_before();
-      mbar_arrive(pds_full);
+      mbar_arrive_warp(pds_full);
 
       if (!mbar_wait(out_full, i & 1, ab, 0x2800 + i)) { alive = false; break; }
       __syncwarp();
@@ -1013,7 +1013,7 @@ tc_bwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
       ld_cols<HD>(tmem_dk + lane_base + h * HD, o2);
       tmem_ld_wait();
       tc_fence_before();
-      mbar_arrive(o_free);
+      mbar_arrive_warp(o_free);
       const int l = valid ? sg.landmark_of(sch.row_offset + row) : 0;
       const float4* add = reinterpret_cast<const float4*>(rows_k + (bh * m + l) * D + h * HD);
       const float vmul = dsc * unshift, kmul = unshift * kLn2;
@@ -1122,13 +1122,13 @@ tc_fwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
   const int tile0 = tr.tile0, count = tr.count;
 
   if (threadIdx.x == 0) {
-    mbar_init(small_full, land ? kComputeThreads : 1);
+    mbar_init(small_full, land ? kComputeThreads / 32 : 1);
     for (int s = 0; s < 2; ++s) {
       mbar_init(k_full + s, 1); mbar_init(k_empty + s, 1); mbar_init(v_full + s, 1); mbar_init(v_empty + s, 1);
       mbar_init(s_full + s, 1);
     }
-    mbar_init(p_full, kComputeThreads);
-    mbar_init(p_full + 1, kComputeThreads);
+    mbar_init(p_full, kComputeThreads / 32);
+    mbar_init(p_full + 1, kComputeThreads / 32);
     mbar_init(acc_done, 1);
     mbar_init(acc_done + 1, 1);
     *abort_word = 0;
@@ -1240,7 +1240,7 @@ tc_fwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
         *reinterpret_cast<uint4*>(s_qt + sw128_offset(pr, pc + c)) = wq;
       }
       fence_proxy_async();
-      mbar_arrive(small_full);
+      mbar_arrive_warp(small_full);
     }
     bool alive = true;
     for (int i = 0; i < count; ++i) {
@@ -1325,7 +1325,7 @@ tc_fwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
       store_cols<T, HC>(s_p + st * L::kP, r, c0, s);
       fence_proxy_async();
       tc_fence_before();
-      mbar_arrive(p_full + st);
+      mbar_arrive_warp(p_full + st);
     }
     if (alive && mbar_wait(acc_done + ((count - 1) & 1), (uint32_t)((count - 1) >> 1) & 1u, ab, 0x3900)) {
       __syncwarp();
