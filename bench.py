@@ -244,6 +244,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true",
+                    help="skip the host-buffer end-to-end section (used for the ncu launch list, so that only\n"
+                         "the device-resident steps are listed)")
     ap.add_argument("--heads", type=int, default=None, help="override H (debug only)")
     args = ap.parse_args()
 
@@ -355,57 +358,60 @@ def main():
                  "frac": step_bytes / (ms_step * 1e-3) / 1e9 / peak},
     }
 
-    # ---- end to end through the public API with pinned host buffers ---------------------------
-    hout, hdq, hdk, hdv = (torch.empty_like(hq).pin_memory() for _ in range(4))
+    e2e = None
+    if not args.no_e2e:
+        # ---- end to end through the public API with pinned host buffers ---------------------------
+        hout, hdq, hdk, hdv = (torch.empty_like(hq).pin_memory() for _ in range(4))
 
-    # A caller whose tensors live in host memory pipelines over the independent (b,h) slices:
-    # groups of heads go through copy-in -> forward+backward -> copy-out on a few streams, so the
-    # two PCIe directions and the kernels overlap.  Every step still moves all inputs in and all
-    # results out, and the step ends only when the last result has landed in host memory.
-    # measured on a B200 (ms per step): 16 groups / 4 streams 12.7, 8 / 4 13.7, 4 / 4 16.2, 8 / 8 17.8,
-    # 16 / 16 17.2, unpipelined 19.7
-    n_groups = int(os.environ.get("FNB_BENCH_E2E_GROUPS", "16")) if (B == 1 and H % 16 == 0) else 1
-    hpg = H // n_groups
-    n_streams = min(n_groups, int(os.environ.get("FNB_BENCH_E2E_STREAMS", "4")))
-    streams = [torch.cuda.Stream(device=dev) for _ in range(n_streams)]
+        # A caller whose tensors live in host memory pipelines over the independent (b,h) slices:
+        # groups of heads go through copy-in -> forward+backward -> copy-out on a few streams, so the
+        # two PCIe directions and the kernels overlap.  Every step still moves all inputs in and all
+        # results out, and the step ends only when the last result has landed in host memory.
+        # measured on a B200 (ms per step): 16 groups / 4 streams 12.7, 8 / 4 13.7, 4 / 4 16.2, 8 / 8 17.8,
+        # 16 / 16 17.2, unpipelined 19.7
+        n_groups = int(os.environ.get("FNB_BENCH_E2E_GROUPS", "16")) if (B == 1 and H % 16 == 0) else 1
+        hpg = H // n_groups
+        n_streams = min(n_groups, int(os.environ.get("FNB_BENCH_E2E_STREAMS", "4")))
+        streams = [torch.cuda.Stream(device=dev) for _ in range(n_streams)]
 
-    def group_e2e(g):
-        h0, h1 = g * hpg, (g + 1) * hpg
-        a, b_, c, go = (t[:, h0:h1].to(dev, non_blocking=True) for t in (hq, hk, hv, hdO))
-        a.requires_grad_(True), b_.requires_grad_(True), c.requires_grad_(True)
-        out = flash_nystrom_attention(a, b_, c, num_landmarks=m, newton_iter=J)
-        out.backward(go)
-        hout[:, h0:h1].copy_(out.detach(), non_blocking=True)
-        hdq[:, h0:h1].copy_(a.grad, non_blocking=True)
-        hdk[:, h0:h1].copy_(b_.grad, non_blocking=True)
-        hdv[:, h0:h1].copy_(c.grad, non_blocking=True)
+        def group_e2e(g):
+            h0, h1 = g * hpg, (g + 1) * hpg
+            a, b_, c, go = (t[:, h0:h1].to(dev, non_blocking=True) for t in (hq, hk, hv, hdO))
+            a.requires_grad_(True), b_.requires_grad_(True), c.requires_grad_(True)
+            out = flash_nystrom_attention(a, b_, c, num_landmarks=m, newton_iter=J)
+            out.backward(go)
+            hout[:, h0:h1].copy_(out.detach(), non_blocking=True)
+            hdq[:, h0:h1].copy_(a.grad, non_blocking=True)
+            hdk[:, h0:h1].copy_(b_.grad, non_blocking=True)
+            hdv[:, h0:h1].copy_(c.grad, non_blocking=True)
 
-    def step_e2e():
-        main = torch.cuda.current_stream(dev)
-        for st_ in streams:
-            st_.wait_stream(main)
-        for g in range(n_groups):
-            with torch.cuda.stream(streams[g % len(streams)]):
-                group_e2e(g)
-        for st_ in streams:
-            main.wait_stream(st_)
+        def step_e2e():
+            main = torch.cuda.current_stream(dev)
+            for st_ in streams:
+                st_.wait_stream(main)
+            for g in range(n_groups):
+                with torch.cuda.stream(streams[g % len(streams)]):
+                    group_e2e(g)
+            for st_ in streams:
+                main.wait_stream(st_)
 
-    for _ in range(3):
-        step_e2e()
-    barrier()
-    e2e_steps = max(3, min(steps, 10))
-    e0.record()
-    for _ in range(e2e_steps):
-        step_e2e()
-    e1.record()
-    barrier()
-    e2e_ms = max_over_ranks(e0.elapsed_time(e1)) / e2e_steps
-    e2e = {"value": world * B * N / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
-           "h2d_bytes_per_step": 4 * elem_bytes, "d2h_bytes_per_step": 4 * elem_bytes,
-           "pipeline": f"{n_groups} head groups on {len(streams)} streams"}
+        for _ in range(3):
+            step_e2e()
+        barrier()
+        e2e_steps = max(3, min(steps, 10))
+        e0.record()
+        for _ in range(e2e_steps):
+            step_e2e()
+        e1.record()
+        barrier()
+        e2e_ms = max_over_ranks(e0.elapsed_time(e1)) / e2e_steps
+        e2e = {"value": world * B * N / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
+               "h2d_bytes_per_step": 4 * elem_bytes, "d2h_bytes_per_step": 4 * elem_bytes,
+               "pipeline": f"{n_groups} head groups on {len(streams)} streams"}
 
-    # ---- CPU baseline (rank 0, N=1 only; bounded sample) ---------------------------------------
-    cpu_baseline = None
+        # ---- CPU baseline (rank 0, N=1 only; bounded sample) ---------------------------------------
+        cpu_baseline = None
+
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         heads = 2
         dt, tps, cores, threads = time_cpu(w, heads, 2, 1)
