@@ -409,9 +409,8 @@ def main():
                "h2d_bytes_per_step": 4 * elem_bytes, "d2h_bytes_per_step": 4 * elem_bytes,
                "pipeline": f"{n_groups} head groups on {len(streams)} streams"}
 
-        # ---- CPU baseline (rank 0, N=1 only; bounded sample) ---------------------------------------
-        cpu_baseline = None
-
+    # ---- CPU baseline (rank 0, N=1 only; bounded sample) ---------------------------------------
+    cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         heads = 2
         dt, tps, cores, threads = time_cpu(w, heads, 2, 1)

@@ -542,7 +542,7 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
       return fail(FNB_ERR_CUDA, "cuTensorMapEncodeTiled failed for the backward row passes");
   }
   auto reduce_chunks = [&](const float* in, int nchunk, int elems, float* out) {
-    dim3 grid((unsigned)((elems / 4 + kThreads - 1) / kThreads), (unsigned)p.BH);
+    dim3 grid((unsigned)((elems / 4 + 63) / 64), (unsigned)p.BH);
     reduce_chunks_kernel<<<grid, kThreads, 0, st>>>(in, nchunk, elems, out);
   };
 
@@ -693,7 +693,7 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
       L.begin();
       {
         const int md = p.m * p.D;
-        dim3 grid((unsigned)((md / 4 + kThreads - 1) / kThreads), (unsigned)p.BH);
+        dim3 grid((unsigned)((md / 4 + 63) / 64), (unsigned)p.BH);
         dqt_reduce2_kernel<<<grid, kThreads, 0, st>>>(partB_src, partB_chunks, w.dqt_ns, nullptr, w.rows_q, p.m, p.D,
                                                      seg_N, scale);
       }
@@ -711,7 +711,7 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
   L.begin();
   {
     const int md = p.m * p.D;
-    dim3 grid((unsigned)((md / 4 + kThreads - 1) / kThreads), (unsigned)p.BH);
+    dim3 grid((unsigned)((md / 4 + 63) / 64), (unsigned)p.BH);
     dqt_reduce2_kernel<<<grid, kThreads, 0, st>>>(partB_src, partB_chunks, w.dqt_ns, w.dqt_tot, nullptr, p.m, p.D,
                                                  seg_N, scale);
   }

@@ -447,17 +447,30 @@ __global__ void __launch_bounds__(kThreads) pack_bwd_ac_kernel(PackBwdAcParams p
 __global__ void __launch_bounds__(kThreads)
 dqt_reduce2_kernel(const float* partB, int nchunk, const float* dqt_ns, float* dqt_tot, float* rows_q, int m,
                    int D, int64_t N, float scale) {
+  // 64 float4 columns x 4 chunk lanes per CTA: lane cl sums chunks cl, cl + 4, ...; the four
+  // partial sums are then added in a fixed order through shared memory.
+  __shared__ float4 part[3][64];
   const int64_t bh = blockIdx.y;
   const int md = m * D;
-  const int idx4 = (blockIdx.x * kThreads + threadIdx.x) * 4;
-  if (idx4 >= md) return;
-  float4 s = *reinterpret_cast<const float4*>(dqt_ns + bh * md + idx4);
-  const float* src = partB + bh * (size_t)nchunk * md + idx4;
-#pragma unroll 6
-  for (int c = 0; c < nchunk; ++c) {
-    const float4 x = *reinterpret_cast<const float4*>(src + (size_t)c * md);
-    s.x += x.x; s.y += x.y; s.z += x.z; s.w += x.w;
+  const int el = threadIdx.x & 63, cl = threadIdx.x >> 6;
+  const int idx4 = (blockIdx.x * 64 + el) * 4;
+  const bool in = idx4 < md;
+  float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (in) {
+    const float* src = partB + bh * (size_t)nchunk * md + idx4;
+#pragma unroll 5
+    for (int c = cl; c < nchunk; c += 4) {
+      const float4 x = *reinterpret_cast<const float4*>(src + (size_t)c * md);
+      s.x += x.x; s.y += x.y; s.z += x.z; s.w += x.w;
+    }
   }
+  if (cl > 0) part[cl - 1][el] = s;
+  __syncthreads();
+  if (cl > 0 || !in) return;
+  const float4 n0 = *reinterpret_cast<const float4*>(dqt_ns + bh * md + idx4);
+#pragma unroll
+  for (int k = 0; k < 3; ++k) { const float4 x = part[k][el]; s.x += x.x; s.y += x.y; s.z += x.z; s.w += x.w; }
+  s.x += n0.x; s.y += n0.y; s.z += n0.z; s.w += n0.w;
   if (dqt_tot) *reinterpret_cast<float4*>(dqt_tot + bh * md + idx4) = s;
   if (rows_q) {
     Segments sg(N, m);
@@ -503,16 +516,26 @@ __global__ void __launch_bounds__(kThreads) landmark_finalize_kernel(LandmarkFin
 // out[bh][e] = sum over chunks of in[bh][chunk][e], fixed order (e < elems, elems % 4 == 0).
 __global__ void __launch_bounds__(kThreads)
 reduce_chunks_kernel(const float* in, int nchunk, int elems, float* out) {
+  // same split as dqt_reduce2_kernel: 64 float4 columns x 4 chunk lanes per CTA
+  __shared__ float4 part[3][64];
   const int64_t bh = blockIdx.y;
-  const int idx4 = (blockIdx.x * kThreads + threadIdx.x) * 4;
-  if (idx4 >= elems) return;
-  const float* src = in + bh * (size_t)nchunk * elems + idx4;
-  float4 s = make_float4(0, 0, 0, 0);
-#pragma unroll 6
-  for (int c = 0; c < nchunk; ++c) {
-    const float4 x = *reinterpret_cast<const float4*>(src + (size_t)c * elems);
-    s.x += x.x; s.y += x.y; s.z += x.z; s.w += x.w;
+  const int el = threadIdx.x & 63, cl = threadIdx.x >> 6;
+  const int idx4 = (blockIdx.x * 64 + el) * 4;
+  const bool inr = idx4 < elems;
+  float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (inr) {
+    const float* src = in + bh * (size_t)nchunk * elems + idx4;
+#pragma unroll 5
+    for (int c = cl; c < nchunk; c += 4) {
+      const float4 x = *reinterpret_cast<const float4*>(src + (size_t)c * elems);
+      s.x += x.x; s.y += x.y; s.z += x.z; s.w += x.w;
+    }
   }
+  if (cl > 0) part[cl - 1][el] = s;
+  __syncthreads();
+  if (cl > 0 || !inr) return;
+#pragma unroll
+  for (int k = 0; k < 3; ++k) { const float4 x = part[k][el]; s.x += x.x; s.y += x.y; s.z += x.z; s.w += x.w; }
   *reinterpret_cast<float4*>(out + bh * (size_t)elems + idx4) = s;
 }
 
