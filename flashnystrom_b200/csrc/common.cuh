@@ -86,6 +86,16 @@ inline Plan make_plan(int64_t BH, int64_t N, int D, int m, int J) {
   return p;
 }
 
+// Programmatic dependent launch: a kernel launched with the stream-serialization attribute may
+// start while its predecessor in the stream is still running.  pdl_trigger() lets the successor of
+// this kernel be scheduled early; pdl_wait() returns once the predecessor grid has completed and
+// its writes are visible, so it must precede every access to global memory that another kernel
+// of the stream writes or reads.  Both are no-ops for a kernel launched the ordinary way.
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+#endif
+
 #ifdef __CUDACC__
 // Scaled landmark row from the raw segment sums of the pooling pass.
 //   land: [2][BH][m][C][D] partial sums (which = 0: Q, 1: K), head_dim D = 64.

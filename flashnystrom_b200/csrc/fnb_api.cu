@@ -293,6 +293,21 @@ struct SpCtx {
 // ------------------------------------------------------------------------------------------
 // Forward: pooling pass -> landmarks -> [pseudoinverse | softmax-3 column pass] -> combine ->
 // output row pass.
+// Launch with programmatic stream serialization: the kernel may be scheduled while its
+// predecessor in the stream is still running (every kernel launched this way calls pdl_wait()
+// before it touches global memory that other kernels of the stream produce or consume).
+template <class... KArgs, class... Args>
+static cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                              Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at; cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, std::forward<Args>(args)...);
+}
+
 // The Newton-Schulz kernels for num_landmarks <= 64 run on the tensor cores (three-term bf16
 // split, FP32-equivalent) unless the caller forces the CUDA-core path or FNB_NS_CUDA_CORES=1 is
 // set in the environment (kept for A/B measurements).
@@ -324,7 +339,7 @@ static int forward_impl(const fnb_fwd_args& a, const Plan& p, const FwdWs& w, in
   if (S.run(0)) {
     L.begin();
     int64_t grid = std::min<int64_t>(2 * p.BH * p.m * lmC, (int64_t)sms * 4);
-    landmark_partial_kernel<T><<<(unsigned)grid, kThreads, 0, st>>>(
+    launch_pdl(landmark_partial_kernel<T>, dim3((unsigned)grid), dim3(kThreads), 0, st, 
         (const T*)a.q, (const T*)a.k, land, p.BH, p.N, p.D, p.m, lmC, seg_N, row_offset);
     if (L.end("landmark_partial")) return L.status;
   }
@@ -404,7 +419,7 @@ static int forward_impl(const fnb_fwd_args& a, const Plan& p, const FwdWs& w, in
       auto kern = tc::tc_fwd_b_kernel<T, D, MPc>;
       size_t smem = tc::FwdBSmem<D, MPc>::kBytes;
       if (int rc = set_smem(kern, smem, max_smem, "tc_fwd_b")) return rc;
-      kern<<<(unsigned)(p.BH * sch.nchunk), tc::kTcThreads, smem, st>>>(
+      launch_pdl(kern, dim3((unsigned)(p.BH * sch.nchunk)), dim3(tc::kTcThreads), smem, st,
           tm_k, tm_v, tm_qt, fused_landmarks ? land : (const float*)nullptr, lmC, p.BH, scale, w.part_acc, w.part_max,
           w.part_sum, sch, p.m, a.device_status);
       if (L.end("tc_fwd_b")) return L.status;
@@ -460,7 +475,7 @@ static int forward_impl(const fnb_fwd_args& a, const Plan& p, const FwdWs& w, in
       sp2.acc_bh_stride = cp.acc_bh_stride; sp2.acc_chunk_stride = cp.acc_chunk_stride;
       sp2.vec_bh_stride = cp.vec_bh_stride; sp2.vec_chunk_stride = cp.vec_chunk_stride;
       sp2.k2inv = a.k2_inv; sp2.bmat = a.bmat; sp2.lse3 = a.lse3; sp2.step2 = a.step2; sp2.m = p.m; sp2.D = p.D;
-      combine_slab_kernel<<<dim3((unsigned)p.BH, (unsigned)(p.D / 16)), kThreads, 0, st>>>(sp2);
+      launch_pdl(combine_slab_kernel, dim3((unsigned)p.BH, (unsigned)(p.D / 16)), dim3(kThreads), 0, st, sp2);
     } else {
       cp.k2inv = a.k2_inv; cp.k_landmarks = a.k_landmarks; cp.bmat = a.bmat; cp.lse3 = a.lse3;
       cp.step2 = a.step2; cp.m = p.m; cp.D = p.D;
@@ -484,7 +499,7 @@ static int forward_impl(const fnb_fwd_args& a, const Plan& p, const FwdWs& w, in
       auto kern = tc::tc_fwd_c_kernel<T, D, MPc>;
       size_t smem = tc::FwdCSmem<D, MPc>::kBytes;
       if (int rc = set_smem(kern, smem, max_smem, "tc_fwd_c")) return rc;
-      kern<<<(unsigned)(p.BH * sch.nchunk), tc::kTcThreads, smem, st>>>(tm_q, tm_o, a.k_landmarks, a.step2, a.lse1, sch,
+      launch_pdl(kern, dim3((unsigned)(p.BH * sch.nchunk)), dim3(tc::kTcThreads), smem, st, tm_q, tm_o, a.k_landmarks, a.step2, a.lse1, sch,
                                                                       p.m, scale, a.device_status);
       if (L.end("tc_fwd_c")) return L.status;
       return 0;
@@ -543,7 +558,7 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
   }
   auto reduce_chunks = [&](const float* in, int nchunk, int elems, float* out) {
     dim3 grid((unsigned)((elems / 4 + 63) / 64), (unsigned)p.BH);
-    reduce_chunks_kernel<<<grid, kThreads, 0, st>>>(in, nchunk, elems, out);
+    launch_pdl(reduce_chunks_kernel, dim3(grid), dim3(kThreads), 0, st, in, nchunk, elems, out);
   };
 
   // ---- pass A ---------------------------------------------------------------------------------
@@ -555,7 +570,8 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
       auto kern = tc::tc_bwd_ac_kernel<T, D, MPc, tc::kModeA>;
       size_t sm = tc::BwdAcSmem<D, MPc, tc::kModeA>::kBytes;
       if (int rc = set_smem(kern, sm, max_smem, "tc_bwd_a")) return rc;
-      kern<<<tgrid, tc::kTcThreads, sm, st>>>(tm_q, tm_g, tm_dq, a.k_landmarks, a.step2, a.lse1, nullptr, w.partA, w.d1,
+      launch_pdl(kern, dim3(tgrid), dim3(tc::kTcThreads), sm, st, tm_q, tm_g, tm_dq, a.k_landmarks, a.step2, a.lse1,
+                 (const float*)nullptr, w.partA, w.d1,
                                              sch, p.m, scale, a.device_status);
       if (L.end("tc_bwd_a")) return L.status;
     }
@@ -625,7 +641,7 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
           hp.dkt_a = w.dkt_a; hp.D3 = w.D3; hp.do3n = do3n; hp.do3_scale = w.do3_scale; hp.qt16 = qt16;
           hp.qt_mul = scale * tc::kLog2e; hp.dtype = a.shape.dtype; hp.MP = MP;
         }
-        nstc::ns_bwd_tc_kernel<<<(unsigned)p.BH, nstc::kNsTcThreads, nstc::kBwdSmem, st>>>(np, hp, a.device_status);
+        launch_pdl(nstc::ns_bwd_tc_kernel, dim3((unsigned)p.BH), dim3(nstc::kNsTcThreads), nstc::kBwdSmem, st, np, hp, a.device_status);
       } else {
         if (int rc = set_smem(ns::ns_bwd_kernel, ns::kBwdSmem, max_smem, "ns_bwd")) return rc;
         ns::ns_bwd_kernel<<<(unsigned)p.BH, kThreads, ns::kBwdSmem, st>>>(np);
@@ -665,7 +681,7 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
       auto kern = tc::tc_bwd_b_kernel<T, D, MPc>;
       size_t sm = tc::BwdBSmem<D, MPc>::kBytes;
       if (int rc = set_smem(kern, sm, max_smem, "tc_bwd_b")) return rc;
-      kern<<<tgrid, tc::kTcThreads, sm, st>>>(tm_k, tm_v, tm_qt, tm_do3, tm_dk, tm_dv, a.lse3, w.D3, w.do3_scale,
+      launch_pdl(kern, dim3(tgrid), dim3(tc::kTcThreads), sm, st, tm_k, tm_v, tm_qt, tm_do3, tm_dk, tm_dv, a.lse3, w.D3, w.do3_scale,
                                              w.rows_k, w.partB, sch, p.m, scale, kshift, a.device_status);
       if (L.end("tc_bwd_b")) return L.status;
     }
@@ -694,7 +710,7 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
       {
         const int md = p.m * p.D;
         dim3 grid((unsigned)((md / 4 + 63) / 64), (unsigned)p.BH);
-        dqt_reduce2_kernel<<<grid, kThreads, 0, st>>>(partB_src, partB_chunks, w.dqt_ns, nullptr, w.rows_q, p.m, p.D,
+        launch_pdl(dqt_reduce2_kernel, grid, dim3(kThreads), 0, st, partB_src, partB_chunks, w.dqt_ns, (float*)nullptr, w.rows_q, p.m, p.D,
                                                      seg_N, scale);
       }
       if (L.end("dqt_rows")) return L.status;
@@ -702,7 +718,7 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
       auto kern = tc::tc_bwd_c_kernel<T, D, MPc>;
       size_t sm = tc::BwdCSmem<D, MPc>::kBytes;
       if (int rc = set_smem(kern, sm, max_smem, "tc_bwd_c")) return rc;
-      kern<<<tgrid, tc::kTcThreads, sm, st>>>(tm_q, tm_g, tm_dq, a.k_landmarks, a.step2, a.lse1, w.d1, w.rows_q, sch,
+      launch_pdl(kern, dim3(tgrid), dim3(tc::kTcThreads), sm, st, tm_q, tm_g, tm_dq, a.k_landmarks, a.step2, a.lse1, w.d1, w.rows_q, sch,
                                              p.m, scale, a.device_status);
       if (L.end("tc_bwd_c")) return L.status;
       return 0;

@@ -81,6 +81,8 @@ landmark_partial_kernel(const T* __restrict__ q, const T* __restrict__ k, float*
                         int64_t BH, int64_t N, int D, int m, int C, int64_t seg_N, int64_t row_offset) {
   constexpr int V = Vec16<T>::n;
   __shared__ float red[kThreads * 8];
+  pdl_trigger();
+  pdl_wait();
   const int64_t per_which = BH * m * C, items = 2 * per_which;
   const int vpr = D / V, rows_per_iter = kThreads / vpr;
   const int cv = threadIdx.x % vpr, ro = threadIdx.x / vpr;

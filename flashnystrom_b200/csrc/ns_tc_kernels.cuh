@@ -873,7 +873,9 @@ ns_bwd_tc_kernel(ns::NsBwdParams p, BwdHeadParams h, int* status) {
   __shared__ Shared sh;
   Ctx c;
   NS_TRACE();
+  pdl_trigger();
   ctx_open(c, sh, dyn_smem, kBwdSlots, status, kBwdTmemCols);
+  pdl_wait();
   NS_TRACE();
   const int64_t bh = blockIdx.x;
   const int m = p.m, mm_ = m * m;

@@ -363,6 +363,8 @@ constexpr int kSlabMaxChunks = 20;   // chunks merged with every load in flight;
 __global__ void __launch_bounds__(kThreads) combine_slab_kernel(CombineSlabParams p) {
   __shared__ float sK[64 * 64];
   __shared__ __align__(16) float sB[64 * 16];
+  pdl_trigger();
+  pdl_wait();
   const int64_t bh = blockIdx.x;
   const int slab = blockIdx.y, t = threadIdx.x, l = t >> 2, q = t & 3;
   const int m = p.m, D = p.D, nc = p.nchunk, d0 = 16 * slab + 4 * q;
@@ -450,6 +452,8 @@ dqt_reduce2_kernel(const float* partB, int nchunk, const float* dqt_ns, float* d
   // 64 float4 columns x 4 chunk lanes per CTA: lane cl sums chunks cl, cl + 4, ...; the four
   // partial sums are then added in a fixed order through shared memory.
   __shared__ float4 part[3][64];
+  pdl_trigger();
+  pdl_wait();
   const int64_t bh = blockIdx.y;
   const int md = m * D;
   const int el = threadIdx.x & 63, cl = threadIdx.x >> 6;
@@ -518,6 +522,8 @@ __global__ void __launch_bounds__(kThreads)
 reduce_chunks_kernel(const float* in, int nchunk, int elems, float* out) {
   // same split as dqt_reduce2_kernel: 64 float4 columns x 4 chunk lanes per CTA
   __shared__ float4 part[3][64];
+  pdl_trigger();
+  pdl_wait();
   const int64_t bh = blockIdx.y;
   const int el = threadIdx.x & 63, cl = threadIdx.x >> 6;
   const int idx4 = (blockIdx.x * 64 + el) * 4;

@@ -151,6 +151,7 @@ tc_fwd_c_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   constexpr uint32_t kCols = 2 * MP + 2 * D;
   constexpr uint32_t kTmemCols = kCols <= 256 ? 256 : 512;
   extern __shared__ uint8_t smem_raw[];
+  pdl_trigger();
   uint8_t* base = align1024(smem_raw);
   uint8_t* s_kt = base;
   uint8_t* s_st = s_kt + L::kKt;
@@ -188,6 +189,7 @@ tc_fwd_c_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  pdl_wait();   // everything above overlaps the tail of the previous kernel of the stream
   const uint32_t tmem_base = *tmem_slot;
   Abort ab{abort_word, status};
 
@@ -358,6 +360,7 @@ tc_bwd_ac_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   constexpr uint32_t kCols = (MODE == kModeA) ? 2 * MP + 2 * D : 4 * MP;
   constexpr uint32_t kTmemCols = kCols <= 256 ? 256 : 512;
   extern __shared__ uint8_t smem_raw[];
+  pdl_trigger();
   uint8_t* base = (MODE == kModeC) ? align1024(smem_raw) : smem_raw;
   if (MODE == kModeA && (smem_u32(smem_raw) & 1023u)) {
     if (threadIdx.x == 0 && status) atomicCAS(status, 0, (2 << 24) | 0x1000);
@@ -402,6 +405,7 @@ tc_bwd_ac_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  pdl_wait();   // everything above overlaps the tail of the previous kernel of the stream
   const uint32_t tmem_base = *tmem_slot;
   Abort ab{abort_word, status};
 
@@ -627,6 +631,7 @@ tc_bwd_c_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   constexpr int kGroup = kComputeThreads / 2;
   constexpr uint32_t kTmemCols = 256;
   extern __shared__ uint8_t smem_raw[];
+  pdl_trigger();
   if (smem_u32(smem_raw) & 1023u) {
     if (threadIdx.x == 0 && status) atomicCAS(status, 0, (2 << 24) | 0x2000);
     return;
@@ -668,6 +673,7 @@ tc_bwd_c_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  pdl_wait();   // everything above overlaps the tail of the previous kernel of the stream
   const uint32_t tmem_base = *tmem_slot;
   Abort ab{abort_word, status};
 
@@ -844,6 +850,7 @@ tc_bwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
   constexpr uint32_t kCols = 2 * W + D;
   constexpr uint32_t kTmemCols = kCols <= 256 ? 256 : 512;
   extern __shared__ uint8_t smem_raw[];
+  pdl_trigger();
   uint8_t* base = align1024(smem_raw);
   uint8_t* s_qt = base;
   uint8_t* s_do3 = s_qt + L::kOp;
@@ -889,6 +896,7 @@ tc_bwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  pdl_wait();   // everything above overlaps the tail of the previous kernel of the stream
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tmem_s = tmem_base, tmem_dp = tmem_base + W, tmem_acc = tmem_base + 2 * W;
   const uint32_t tmem_dv = tmem_s, tmem_dk = tmem_dp;
@@ -1093,6 +1101,7 @@ tc_fwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
   constexpr uint32_t kCols = 2 * MP + D + 32;
   constexpr uint32_t kTmemCols = kCols <= 256 ? 256 : 512;
   extern __shared__ uint8_t smem_raw[];
+  pdl_trigger();
   uint8_t* base = align1024(smem_raw);
   uint8_t* s_qt = base;
   uint8_t* s_ones = s_qt + L::kQt;
@@ -1146,6 +1155,7 @@ tc_fwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  pdl_wait();   // everything above overlaps the tail of the previous kernel of the stream
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tmem_acc = tmem_base + 2 * MP;   // D accumulator columns, then 32 for the row sums
   Abort ab{abort_word, status};
