@@ -571,7 +571,7 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
       size_t sm = tc::BwdAcSmem<D, MPc, tc::kModeA>::kBytes;
       if (int rc = set_smem(kern, sm, max_smem, "tc_bwd_a")) return rc;
       launch_pdl(kern, dim3(tgrid), dim3(tc::kTcThreads), sm, st, tm_q, tm_g, tm_dq, a.k_landmarks, a.step2, a.lse1,
-                 (const float*)nullptr, w.partA, w.d1,
+                 (const float*)nullptr, w.partA, (float*)nullptr, 1,
                                              sch, p.m, scale, a.device_status);
       if (L.end("tc_bwd_a")) return L.status;
     }
@@ -718,7 +718,7 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
       auto kern = tc::tc_bwd_c_kernel<T, D, MPc>;
       size_t sm = tc::BwdCSmem<D, MPc>::kBytes;
       if (int rc = set_smem(kern, sm, max_smem, "tc_bwd_c")) return rc;
-      launch_pdl(kern, dim3(tgrid), dim3(tc::kTcThreads), sm, st, tm_q, tm_g, tm_dq, a.k_landmarks, a.step2, a.lse1, w.d1, w.rows_q, sch,
+      launch_pdl(kern, dim3(tgrid), dim3(tc::kTcThreads), sm, st, tm_dq, a.k_landmarks, a.step2, w.rows_q, sch,
                                              p.m, scale, a.device_status);
       if (L.end("tc_bwd_c")) return L.status;
       return 0;

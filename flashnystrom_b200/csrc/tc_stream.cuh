@@ -353,7 +353,7 @@ tc_bwd_ac_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                  const float* __restrict__ k_landmarks, const float* __restrict__ step2,
                  const float* __restrict__ lse1,
                  const float* __restrict__ rows_q, float* __restrict__ partA, float* __restrict__ d1_out,
-                 TcSched sch, int m, float scale, int* status) {
+                 int ds_to_dq, TcSched sch, int m, float scale, int* status) {
   static_assert(D == 64 && MP == 64, "the in-kernel operand packing is written for 64 x 64 landmark operands");
   using L = BwdAcSmem<D, MP, MODE>;
   constexpr int KBD = D / 64, HC = MP / 2, HD = D / 2;
@@ -432,6 +432,7 @@ tc_bwd_ac_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       constexpr uint32_t idesc_s = make_idesc<T>(kTile, MP, false, false);
       constexpr uint32_t idesc_acc2 = make_idesc<T>(128, 128, true, true);
       constexpr uint32_t idesc_dq = make_idesc<T>(kTile, D, false, true);
+      const bool store_ds = MODE == kModeA && ds_to_dq != 0;
       const uint32_t a_kt = smem_u32(s_kt), a_st = smem_u32(s_st), a_p = smem_u32(s_p), a_ds = smem_u32(s_ds);
       static_assert(MODE != kModeA || (MP == 64 && D == 64), "the merged accumulation assumes 64 x 64 landmark operands");
       // S and dP of tile i into TMEM buffer b (mode A: always buffer 0)
@@ -455,6 +456,12 @@ tc_bwd_ac_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       for (int i = 0; ok && i < count; ++i) {
         if (MODE == kModeA) {
           if (!mbar_wait(pds_full, i & 1, ab, 0x1400 + i)) break;
+          // The dS tile also goes to global memory, into the dQ tile of the same rows (same
+          // footprint): the dQ pass turns it into dQ in place and never reads Q or dO.
+          if (store_ds) {
+            tma_store_3d(&tm_dq, s_ds, 0, (tile0 + i) * kTile, (int)bh);
+            tma_store_commit();
+          }
           // S / dP of tile i are consumed: start the next tile's scores before this tile's
           // accumulation so that the compute warps find them ready
           if (i + 1 < count && !front(i + 1, 0)) break;
@@ -471,6 +478,8 @@ tc_bwd_ac_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             umma(tmem_base + 2 * MP, smem_desc_sw128(a_p + k * 2048, L::kP, 1024),
                  smem_desc_sw128(a_q + k * 2048, 2 * L::kIn, 1024), idesc_acc2, (i > 0 || k > 0));
           umma_commit(in_empty + st);
+          // acc_done lets the compute warps overwrite the dS tile: the copy must have read it
+          if (store_ds) tma_store_wait_read();
           umma_commit(acc_done);
         } else {
           const int b = i & 1;
@@ -488,6 +497,7 @@ tc_bwd_ac_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           }
         }
       }
+      if (store_ds) tma_store_wait_all();
     }
   } else {
     const int r = threadIdx.x & 127, h = threadIdx.x >> 7;
@@ -602,34 +612,34 @@ tc_bwd_ac_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 }
 
 // ------------------------------------------------------------------------------------------
-// Softmax-1 backward, second row pass (dQ), two ping-pong compute groups.
-//   S1 = Q kt16^T (log2 domain), dP1 = dO st16^T, P1 = exp2(S1 - lse1*log2e),
-//   dS1 = P1 o (dP1 - D1), dQ = s dS1 Kt + rows_q[l(n)];  D1 = rowsum(P1 o dP1) was written per
-//   row by the first row pass.
-// Group g (128 threads, one per tile row) owns tiles g, g+2, ... with its own S / dP accumulators
-// (whose first half is reused for the dQ product) and its own dS tile, which also stages the dQ
-// tile for the TMA store.  A row is handled in two 32-column halves to stay inside the register
-// budget of two CTAs per SM.
+// Softmax-1 backward, second row pass (dQ).  The first row pass leaves its 16-bit dS1 tiles
+// (dS1 = P1 o (dP1 - D1), scaled by 1/sc with sc the power-of-two scale of step2) in the dQ buffer
+// itself: with 64 landmark columns and head_dim 64 a dS1 tile has exactly the footprint of the dQ
+// tile of the same rows.  This pass turns every tile in place:
+//   dQ = (sc ln2) dS1 (s log2e Kt) + rows_q[l(n)]
+// One TMA load, one product and one TMA store per tile; no exponentials, Q and dO are not read
+// again.  Four input stages per CTA (released by the product's commit), four accumulators, two
+// compute groups of 128 threads (one thread per tile row) that take alternate tiles and stage
+// their output tile in a buffer of their own.
 template <int D, int MP>
 struct BwdCSmem {
-  static constexpr int kKt = MP * D * 2, kSt = MP * D * 2, kIn = kTile * D * 2,
-                       kDs = kTile * (MP > D ? MP : D) * 2;
+  static constexpr int kStages = 4;
+  static constexpr int kKt = MP * D * 2, kIn = kTile * MP * 2, kOut = kTile * D * 2;
   // relies on the dynamic shared window being 1024-byte aligned (checked at run time)
-  static constexpr int kBytes = kKt + kSt + 4 * kIn + 2 * kDs + 256;
+  static constexpr int kBytes = kKt + kStages * kIn + 2 * kOut + 256;
 };
 
 template <class T, int D, int MP>
 __global__ void __launch_bounds__(kTcThreads, 2)
-tc_bwd_c_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_g,
-                const __grid_constant__ CUtensorMap tm_dq,
-                const float* __restrict__ k_landmarks, const float* __restrict__ step2,
-                const float* __restrict__ lse1, const float* __restrict__ d1_in,
-                const float* __restrict__ rows_q, TcSched sch, int m, float scale, int* status) {
+tc_bwd_c_kernel(const __grid_constant__ CUtensorMap tm_dq, const float* __restrict__ k_landmarks,
+                const float* __restrict__ step2, const float* __restrict__ rows_q, TcSched sch, int m,
+                float scale, int* status) {
   using L = BwdCSmem<D, MP>;
-  static_assert(D == 64 && MP == 64, "written for 64 x 64 landmark operands");
-  constexpr int KBD = D / 64;
+  static_assert(D == 64 && MP == 64, "a dS1 tile must have the footprint of a dQ tile");
   constexpr int kGroup = kComputeThreads / 2;
-  constexpr uint32_t kTmemCols = 256;
+  constexpr int kStages = L::kStages;
+  constexpr uint32_t kTmemCols = kStages * D;
+  static_assert(kTmemCols == 256, "TMEM allocation must be a power of two");
   extern __shared__ uint8_t smem_raw[];
   pdl_trigger();
   if (smem_u32(smem_raw) & 1023u) {
@@ -637,20 +647,17 @@ tc_bwd_c_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     return;
   }
   uint8_t* s_kt = smem_raw;
-  uint8_t* s_st = s_kt + L::kKt;
-  uint8_t* s_q = s_st + L::kSt;          // two stages
-  uint8_t* s_g = s_q + 2 * L::kIn;       // two stages
-  uint8_t* s_ds = s_g + 2 * L::kIn;      // one per group
-  uint64_t* bars = reinterpret_cast<uint64_t*>(s_ds + 2 * L::kDs);
+  uint8_t* s_in = s_kt + L::kKt;               // kStages dS1 tiles
+  uint8_t* s_out = s_in + kStages * L::kIn;    // one dQ staging tile per group
+  uint64_t* bars = reinterpret_cast<uint64_t*>(s_out + 2 * L::kOut);
   uint64_t* small_full = bars + 0;
-  uint64_t* in_full = bars + 1;          // [2]
-  uint64_t* in_empty = bars + 3;         // [2]
-  uint64_t* sdp_full = bars + 5;         // [2]
-  uint64_t* pds_full = bars + 7;         // [2]
-  uint64_t* acc_done = bars + 9;         // [2]
-  uint64_t* o_free = bars + 11;          // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+  uint64_t* in_full = bars + 1;                // [kStages]
+  uint64_t* in_empty = bars + 1 + kStages;     // [kStages]
+  uint64_t* acc_done = bars + 1 + 2 * kStages; // [kStages]
+  uint64_t* o_free = bars + 1 + 3 * kStages;   // [kStages]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 1 + 4 * kStages);
   int* abort_word = reinterpret_cast<int*>(tmem_slot + 1);
+  static_assert((1 + 4 * kStages) * 8 + 8 <= 256, "barrier area");
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const TileRange tr = tile_range(sch);
@@ -659,9 +666,9 @@ tc_bwd_c_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 
   if (threadIdx.x == 0) {
     mbar_init(small_full, kComputeThreads / 32);
-    for (int s = 0; s < 2; ++s) {
-      mbar_init(in_full + s, 1); mbar_init(in_empty + s, 1); mbar_init(sdp_full + s, 1);
-      mbar_init(pds_full + s, kGroup / 32); mbar_init(acc_done + s, 1); mbar_init(o_free + s, kGroup / 32);
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(in_full + s, 1); mbar_init(in_empty + s, 1);
+      mbar_init(acc_done + s, 1); mbar_init(o_free + s, kGroup / 32);
     }
     *abort_word = 0;
     fence_mbar_init();
@@ -679,120 +686,77 @@ tc_bwd_c_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 
   if (warp == kProducerWarp) {
     if (lane == 0) {
-      tma_prefetch_desc(&tm_q);
-      tma_prefetch_desc(&tm_g);
       tma_prefetch_desc(&tm_dq);
       int armed = 0;
       for (int i = 0; i < count; ++i) {
-        const int st = i & 1;
-        if (!mbar_wait(in_empty + st, ((i >> 1) & 1) ^ 1, ab, 0x2100 + i)) break;
-        mbar_expect_tx(in_full + st, 2 * L::kIn);
-        for (int kb = 0; kb < KBD; ++kb) {
-          tma_load_3d(s_q + st * L::kIn + kb * (kTile * 128), &tm_q, in_full + st, kb * 64, (tile0 + i) * kTile, (int)bh);
-          tma_load_3d(s_g + st * L::kIn + kb * (kTile * 128), &tm_g, in_full + st, kb * 64, (tile0 + i) * kTile, (int)bh);
-        }
+        const int s = i % kStages;
+        if (!mbar_wait(in_empty + s, ((i / kStages) & 1) ^ 1, ab, 0x2100 + i)) break;
+        mbar_expect_tx(in_full + s, L::kIn);
+        tma_load_3d(s_in + s * L::kIn, &tm_dq, in_full + s, 0, (tile0 + i) * kTile, (int)bh);
         armed = i + 1;
       }
       if (ab.raised())
-        for (int i = max(0, armed - 2); i < armed; ++i) mbar_drain(in_full + (i & 1), (i >> 1) & 1);
+        for (int i = max(0, armed - kStages); i < armed; ++i) mbar_drain(in_full + (i % kStages), (i / kStages) & 1);
     }
   } else if (warp == kMmaWarp) {
     if (lane == 0) {
-      constexpr uint32_t idesc_s = make_idesc<T>(kTile, MP, false, false);
       constexpr uint32_t idesc_dq = make_idesc<T>(kTile, D, false, true);
-      const uint32_t a_kt = smem_u32(s_kt), a_st = smem_u32(s_st);
-      // S and dP of tile i into the accumulators of group b = i & 1
-      auto front = [&](int i) -> bool {
-        const int b = i & 1;
-        if (!mbar_wait(in_full + b, (i >> 1) & 1, ab, 0x2300 + i)) return false;
-        tc_fence_after();
-        const uint32_t a_q = smem_u32(s_q + b * L::kIn), a_g = smem_u32(s_g + b * L::kIn);
-        const uint32_t t_s = tmem_base + b * 2 * MP;
-#pragma unroll
-        for (int k = 0; k < D / 16; ++k) umma(t_s, kdesc(a_q, k, kTile), kdesc(a_kt, k, MP), idesc_s, k > 0);
-#pragma unroll
-        for (int k = 0; k < D / 16; ++k) umma(t_s + MP, kdesc(a_g, k, kTile), kdesc(a_st, k, MP), idesc_s, k > 0);
-        umma_commit(in_empty + b);
-        umma_commit(sdp_full + b);
-        return true;
-      };
+      const uint32_t a_kt = smem_u32(s_kt);
       bool ok = mbar_wait(small_full, 0, ab, 0x2200);
-      ok = ok && front(0);
-      if (ok && count > 1) ok = front(1);
       for (int i = 0; ok && i < count; ++i) {
-        const int b = i & 1;
-        if (!mbar_wait(pds_full + b, (i >> 1) & 1, ab, 0x2400 + i)) break;
+        const int s = i % kStages;
+        const uint32_t par = (uint32_t)(i / kStages) & 1u;
+        // the accumulator of this stage was last read by tile i - kStages
+        if (!mbar_wait(o_free + s, par ^ 1, ab, 0x2380 + i)) break;
+        if (!mbar_wait(in_full + s, par, ab, 0x2300 + i)) break;
         tc_fence_after();
-        const uint32_t a_ds = smem_u32(s_ds + b * L::kDs);
+        const uint32_t a_ds = smem_u32(s_in + s * L::kIn);
         // dQ = dS (128 x MP, K-major) * Kt (MP x D, MN-major view of kt16)
 #pragma unroll
         for (int k = 0; k < MP / 16; ++k)
-          umma(tmem_base + b * 2 * MP, kdesc(a_ds, k, kTile), smem_desc_sw128(a_kt + k * 2048, MP * 128, 1024),
+          umma(tmem_base + s * D, kdesc(a_ds, k, kTile), smem_desc_sw128(a_kt + k * 2048, MP * 128, 1024),
                idesc_dq, k > 0);
-        umma_commit(acc_done + b);
-        if (i + 2 < count) {
-          if (!mbar_wait(o_free + b, (i >> 1) & 1, ab, 0x2380 + i)) break;
-          ok = front(i + 2);
-        }
+        umma_commit(in_empty + s);
+        umma_commit(acc_done + s);
       }
     }
   } else {
     const int g = warp >> 2;
     const int r = threadIdx.x & 127;
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-    // operand copies of Kt and step2 for this slice (the dS tiles are free until the first tile)
-    const float sc = pack_landmark_operands<T>(s_kt, s_st, k_landmarks + bh * m * D, step2 + bh * m * D, m,
-                                               scale * kLog2e, reinterpret_cast<float*>(s_ds));
+    // operand copy of Kt and the scale of step2 for this slice (the staging tiles are free until
+    // the first tile; the step2 copy itself is not used by this pass)
+    const float sc = pack_landmark_operands<T>(s_kt, s_out, k_landmarks + bh * m * D, step2 + bh * m * D, m,
+                                               scale * kLog2e, reinterpret_cast<float*>(s_out + L::kOut));
     fence_proxy_async();
     mbar_arrive_warp(small_full);
+    named_barrier(3, kComputeThreads);   // the step2 copy in the staging tile of group 0 is dead from here on
     const float mul = sc * kLn2;
-    uint8_t* my_ds = s_ds + g * L::kDs;
-    const uint32_t t_s = tmem_base + g * 2 * MP + lane_base;
+    uint8_t* my_out = s_out + g * L::kOut;
     const bool leader = r == 0;
     Segments sg(sch.seg_N, m);
     for (int i = g; i < count; i += 2) {
-      const uint32_t par = (uint32_t)(i >> 1) & 1u;
+      const int s = i % kStages;
+      const uint32_t par = (uint32_t)(i / kStages) & 1u;
       const int64_t row = (int64_t)(tile0 + i) * kTile + r;
       const bool valid = row < sch.N;
-      const float lse = valid ? lse1[bh * sch.N + row] * kLog2e : 0.f;
-      const float d1 = valid ? d1_in[bh * sch.N + row] : 0.f;
-      if (!mbar_wait(sdp_full + g, par, ab, 0x2600 + i)) break;
+      const int l = valid ? sg.landmark_of(sch.row_offset + row) : 0;
+      const float4* add = reinterpret_cast<const float4*>(rows_q + (bh * m + l) * D);
+      const uint32_t t_o = tmem_base + s * D + lane_base;
+      if (!mbar_wait(acc_done + s, par, ab, 0x2800 + i)) break;
       __syncwarp();
       tc_fence_after();
-      // the previous dQ tile of this group was stored from my_ds: wait until the copy has read it
+      // the previous dQ tile of this group was stored from my_out: wait until the copy has read it
       if (leader) tma_store_wait_read();
       named_barrier(1 + g, kGroup);
 #pragma unroll
       for (int hf = 0; hf < 2; ++hf) {
-        float pv[32], gv[32];
-        tmem_ld32(t_s + hf * 32, pv);
-        tmem_ld32(t_s + MP + hf * 32, gv);
-        tmem_ld_wait();
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const float pj = (valid && hf * 32 + j < m) ? fast_exp2(pv[j] - lse) : 0.f;
-          gv[j] = pj * (gv[j] - d1);
-        }
-        store_cols<T, 32>(my_ds, r, hf * 32, gv);
-      }
-      fence_proxy_async();
-      tc_fence_before();
-      mbar_arrive_warp(pds_full + g);
-      // dQ tile of the same rows
-      const int l = valid ? sg.landmark_of(sch.row_offset + row) : 0;
-      const float4* add = reinterpret_cast<const float4*>(rows_q + (bh * m + l) * D);
-      if (!mbar_wait(acc_done + g, par, ab, 0x2800 + i)) break;
-      __syncwarp();
-      tc_fence_after();
-      // acc_done also means the product has finished reading the dS tile: reuse it as staging
-#pragma unroll
-      for (int hf = 0; hf < 2; ++hf) {
         float o[32];
-        tmem_ld32(t_s + hf * 32, o);
+        tmem_ld32(t_o + hf * 32, o);
         tmem_ld_wait();
         if (hf == 1) {
           tc_fence_before();
-          mbar_arrive_warp(o_free + g);
+          mbar_arrive_warp(o_free + s);
         }
 #pragma unroll
         for (int j = 0; j < 32; j += 4) {
@@ -800,13 +764,12 @@ tc_bwd_c_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           o[j + 0] = fmaf(o[j + 0], mul, a.x); o[j + 1] = fmaf(o[j + 1], mul, a.y);
           o[j + 2] = fmaf(o[j + 2], mul, a.z); o[j + 3] = fmaf(o[j + 3], mul, a.w);
         }
-        store_cols<T, 32>(my_ds, r, hf * 32, o);
+        store_cols<T, 32>(my_out, r, hf * 32, o);
       }
       fence_proxy_async();
       named_barrier(1 + g, kGroup);
       if (leader) {
-        for (int kb = 0; kb < KBD; ++kb)
-          tma_store_3d(&tm_dq, my_ds + kb * (kTile * 128), kb * 64, (tile0 + i) * kTile, (int)bh);
+        tma_store_3d(&tm_dq, my_out, 0, (tile0 + i) * kTile, (int)bh);
         tma_store_commit();
       }
     }
