@@ -520,7 +520,7 @@ static int forward_impl(const fnb_fwd_args& a, const Plan& p, const FwdWs& w, in
 // backward) -> softmax-3 column pass (dK, dV, dQt partials) -> dQ row pass.
 template <class T>
 static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, int max_smem, int sms,
-                         cudaStream_t st, const SpCtx& S = SpCtx()) {
+                         cudaStream_t st, bool allow_inner_fork, const SpCtx& S = SpCtx()) {
   Launcher L(st, a.device);
   const float scale = powf((float)p.D, -0.25f);
   constexpr bool k16 = !std::is_same<T, float>::value;
@@ -530,6 +530,21 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
   const bool use_tc = k16 && tc::tc_supported(a.shape.dtype, p.D, p.m, a.shape.flags) && sch.nchunk <= p.nchunk;
   const int MP = p.m <= 64 ? 64 : 128;
   const bool smem_ns = p.m <= ns::kN;
+  // With head_dim 64 on the tensor-core path the reduction of the pass-A partials and the two
+  // products that follow run inside the Newton-Schulz backward kernel.
+  const bool fused_mid = smem_ns && use_tc && p.D == 64 && p.J >= 1 && ns_on_tensor_cores(a.shape.flags);
+  // The column pass does not need the pseudoinverse backward (it leaves dS3' tiles for the in-place
+  // pass, which is the first consumer of the landmark gradients), so the two run side by side:
+  // the Newton-Schulz kernel on a side stream with one SM per slice, the column pass on the rest.
+  // Off while profiling (kernels are timed one by one).
+  const bool side_ns = fused_mid && !L.prof && allow_inner_fork && p.BH * 4 <= sms;
+  tc::TcSched sch_b = sch;
+  if (side_ns) {
+    sch_b = tc::make_sched(p.BH, p.N, 2 * (sms - (int)p.BH));
+    sch_b.seg_N = seg_N; sch_b.row_offset = row_offset;
+  }
+  int kshift = 0;
+  while ((int64_t(2) << kshift) <= seg_N && kshift < 14) ++kshift;   // floor(log2 N), at most 14
 
   StreamParams sp;
   memset(&sp, 0, sizeof(sp));
@@ -545,15 +560,17 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
   const unsigned sgrid = (unsigned)(p.BH * p.nchunk);
   const unsigned tgrid = (unsigned)(p.BH * sch.nchunk);
   const size_t gsmem = bwd_ac_smem(p.mpad, p.D);
-  const int nchunk_used = use_tc ? sch.nchunk : p.nchunk;
+  const int nchunk_used = use_tc ? sch.nchunk : p.nchunk;        // pass A partials
+  const int nchunk_colpass = use_tc ? sch_b.nchunk : p.nchunk;   // column pass partials
 
   void* qt16 = w.op16[3]; void* do3n = w.op16[5];
-  CUtensorMap tm_q, tm_g, tm_dq;
+  CUtensorMap tm_q, tm_g, tm_dq, tm_dk;
   if (use_tc) {
     constexpr int D = 64;
     if (!tc::make_map_3d(&tm_q, a.q, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
         !tc::make_map_3d(&tm_g, a.d_out, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
-        !tc::make_map_3d(&tm_dq, a.dq, a.shape.dtype, p.BH, p.N, D, tc::kTile))
+        !tc::make_map_3d(&tm_dq, a.dq, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
+        !tc::make_map_3d(&tm_dk, a.dk, a.shape.dtype, p.BH, p.N, D, tc::kTile))
       return fail(FNB_ERR_CUDA, "cuTensorMapEncodeTiled failed for the backward row passes");
   }
   auto reduce_chunks = [&](const float* in, int nchunk, int elems, float* out) {
@@ -571,7 +588,7 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
       size_t sm = tc::BwdAcSmem<D, MPc, tc::kModeA>::kBytes;
       if (int rc = set_smem(kern, sm, max_smem, "tc_bwd_a")) return rc;
       launch_pdl(kern, dim3(tgrid), dim3(tc::kTcThreads), sm, st, tm_q, tm_g, tm_dq, a.k_landmarks, a.step2, a.lse1,
-                 (const float*)nullptr, w.partA, (float*)nullptr, 1,
+                 (const float*)nullptr, w.partA, w.st_scale, 1,
                                              sch, p.m, scale, a.device_status);
       if (L.end("tc_bwd_a")) return L.status;
     }
@@ -594,10 +611,8 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
 
   // ---- landmark-sized middle ------------------------------------------------------------------
   if (S.run(1)) {
+  Fork fork(st, a.device, side_ns);
   if (smem_ns) {
-    // With head_dim 64 on the tensor-core path the reduction of the pass-A partials and the two
-    // products that follow run inside the Newton-Schulz backward kernel.
-    const bool fused_mid = use_tc && p.D == 64 && p.J >= 1 && ns_on_tensor_cores(a.shape.flags);
     if (!fused_mid) {
     L.begin();
     {
@@ -626,6 +641,7 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
       fused_pa = w.partA_red;
       fused_pa_chunks = 1;
     }
+    cudaStream_t ns_stream = fork.begin();   // the caller's stream unless side_ns
     L.begin();
     {
       ns::NsBwdParams np;
@@ -638,16 +654,34 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
         nstc::BwdHeadParams hp{};
         if (fused_mid) {
           hp.partA = fused_pa; hp.nchunk = fused_pa_chunks; hp.k2inv = a.k2_inv; hp.bmat = a.bmat;
-          hp.dkt_a = w.dkt_a; hp.D3 = w.D3; hp.do3n = do3n; hp.do3_scale = w.do3_scale; hp.qt16 = qt16;
-          hp.qt_mul = scale * tc::kLog2e; hp.dtype = a.shape.dtype; hp.MP = MP;
+          hp.dkt_a = w.dkt_a; hp.D3 = side_ns ? nullptr : w.D3; hp.do3n = do3n; hp.do3_scale = w.do3_scale;
+          hp.qt16 = qt16; hp.qt_mul = scale * tc::kLog2e; hp.dtype = a.shape.dtype; hp.MP = MP;
         }
-        launch_pdl(nstc::ns_bwd_tc_kernel, dim3((unsigned)p.BH), dim3(nstc::kNsTcThreads), nstc::kBwdSmem, st, np, hp, a.device_status);
+        if (side_ns)
+          nstc::ns_bwd_tc_kernel<<<(unsigned)p.BH, nstc::kNsTcThreads, nstc::kBwdSmem, ns_stream>>>(np, hp, a.device_status);
+        else
+          launch_pdl(nstc::ns_bwd_tc_kernel, dim3((unsigned)p.BH), dim3(nstc::kNsTcThreads), nstc::kBwdSmem, st, np, hp, a.device_status);
       } else {
         if (int rc = set_smem(ns::ns_bwd_kernel, ns::kBwdSmem, max_smem, "ns_bwd")) return rc;
         ns::ns_bwd_kernel<<<(unsigned)p.BH, kThreads, ns::kBwdSmem, st>>>(np);
       }
     }
     if (L.end("ns_bwd")) return L.status;
+    fork.end();
+    if (side_ns) {
+      // what the column pass needs from the middle stage (dO3 -> D3, its 16-bit copy and scale, the
+      // 16-bit Qt operand), on the caller's stream; the Newton-Schulz kernel, enqueued first, is
+      // resident on its SMs by the time the column pass starts
+      BwdMid1Params mp;
+      mp.partA = fused_pa; mp.nchunk = fused_pa_chunks; mp.k2inv = a.k2_inv; mp.bmat = a.bmat;
+      mp.q_landmarks = a.q_landmarks; mp.dkt_a = nullptr; mp.dO3 = nullptr; mp.D3 = w.D3; mp.G = nullptr;
+      mp.m = p.m; mp.D = p.D; mp.dtype = a.shape.dtype; mp.MP = MP;
+      mp.qt16 = qt16; mp.qtT16 = nullptr; mp.do3n = do3n; mp.do3T = nullptr; mp.do3_scale = w.do3_scale;
+      mp.qt_mul = scale * tc::kLog2e; mp.qtT_mul = scale;
+      size_t sm = bwd_mid1_smem(p.m, p.D);
+      if (int rc = set_smem(bwd_mid1_kernel<4>, sm, max_smem, "bwd_mid1")) return rc;
+      bwd_mid1_kernel<4><<<(unsigned)p.BH, kThreads, sm, st>>>(mp);
+    }
   } else {
     L.begin();
     {
@@ -667,22 +701,24 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
   if constexpr (k16) {
     if (use_tc) {
       constexpr int D = 64, MPc = 64;
-      CUtensorMap tm_k, tm_v, tm_qt, tm_do3, tm_dk, tm_dv;
+      CUtensorMap tm_k, tm_v, tm_qt, tm_do3, tm_dv;
       if (!tc::make_map_3d(&tm_k, a.k, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
           !tc::make_map_3d(&tm_v, a.v, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
-          !tc::make_map_3d(&tm_dk, a.dk, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
           !tc::make_map_3d(&tm_dv, a.dv, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
           !tc::make_map_2d(&tm_qt, qt16, a.shape.dtype, p.BH * MPc, D, MPc) ||
           !tc::make_map_2d(&tm_do3, do3n, a.shape.dtype, p.BH * MPc, D, MPc))
         return fail(FNB_ERR_CUDA, "cuTensorMapEncodeTiled failed for the backward column pass");
-      int kshift = 0;
-      while ((int64_t(2) << kshift) <= seg_N && kshift < 14) ++kshift;   // floor(log2 N), at most 14
       L.begin();
       auto kern = tc::tc_bwd_b_kernel<T, D, MPc>;
       size_t sm = tc::BwdBSmem<D, MPc>::kBytes;
       if (int rc = set_smem(kern, sm, max_smem, "tc_bwd_b")) return rc;
-      launch_pdl(kern, dim3(tgrid), dim3(tc::kTcThreads), sm, st, tm_k, tm_v, tm_qt, tm_do3, tm_dk, tm_dv, a.lse3, w.D3, w.do3_scale,
-                                             w.rows_k, w.partB, sch, p.m, scale, kshift, a.device_status);
+      const dim3 bgrid((unsigned)(p.BH * sch_b.nchunk));
+      if (side_ns)   // an ordinary launch: it must not claim SMs before the Newton-Schulz kernel has its own
+        kern<<<bgrid, tc::kTcThreads, sm, st>>>(tm_k, tm_v, tm_qt, tm_do3, tm_dk, tm_dv, a.lse3, w.D3, w.do3_scale, w.partB,
+                                                sch_b, p.m, scale, kshift, a.device_status);
+      else
+        launch_pdl(kern, bgrid, dim3(tc::kTcThreads), sm, st, tm_k, tm_v, tm_qt, tm_do3, tm_dk, tm_dv, a.lse3, w.D3, w.do3_scale,
+                   w.partB, sch_b, p.m, scale, kshift, a.device_status);
       if (L.end("tc_bwd_b")) return L.status;
     }
   }
@@ -694,13 +730,14 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
   }
   if (S.on()) {
     L.begin();
-    reduce_chunks(w.partB, nchunk_used, p.m * p.D, S.xfer);
+    reduce_chunks(w.partB, nchunk_colpass, p.m * p.D, S.xfer);
     if (L.end("reduce_partB")) return L.status;
   }
+  fork.join();
   }  // stage 1
   if (S.stage == 1) return 0;
   const float* partB_src = S.on() ? S.xfer : w.partB;
-  const int partB_chunks = S.on() ? 1 : nchunk_used;
+  const int partB_chunks = S.on() ? 1 : nchunk_colpass;
 
   // ---- pass C ---------------------------------------------------------------------------------
   if constexpr (k16) {
@@ -710,16 +747,23 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
       {
         const int md = p.m * p.D;
         dim3 grid((unsigned)((md / 4 + 63) / 64), (unsigned)p.BH);
-        launch_pdl(dqt_reduce2_kernel, grid, dim3(kThreads), 0, st, partB_src, partB_chunks, w.dqt_ns, (float*)nullptr, w.rows_q, p.m, p.D,
-                                                     seg_N, scale);
+        if (side_ns)   // follows the join with the side stream: an ordinary launch
+          dqt_reduce2_kernel<<<grid, kThreads, 0, st>>>(partB_src, partB_chunks, w.dqt_ns, (float*)nullptr, w.rows_q, p.m, p.D,
+                                                       seg_N, scale);
+        else
+          launch_pdl(dqt_reduce2_kernel, grid, dim3(kThreads), 0, st, partB_src, partB_chunks, w.dqt_ns, (float*)nullptr, w.rows_q,
+                     p.m, p.D, seg_N, scale);
       }
       if (L.end("dqt_rows")) return L.status;
       L.begin();
-      auto kern = tc::tc_bwd_c_kernel<T, D, MPc>;
-      size_t sm = tc::BwdCSmem<D, MPc>::kBytes;
+      auto kern = tc::tc_rows_inplace_kernel<T, D, MPc>;
+      size_t sm = tc::RowsSmem<D, MPc>::kBytes;
       if (int rc = set_smem(kern, sm, max_smem, "tc_bwd_c")) return rc;
-      launch_pdl(kern, dim3(tgrid), dim3(tc::kTcThreads), sm, st, tm_dq, a.k_landmarks, a.step2, w.rows_q, sch,
-                                             p.m, scale, a.device_status);
+      // dQ from the dS1 tiles pass A left in dq, dK from the dS3' tiles the column pass left in dk
+      tc::RowsSide side_q{a.k_landmarks, w.rows_q, w.st_scale, tc::kLn2};
+      tc::RowsSide side_k{a.q_landmarks, w.rows_k, nullptr, exp2f(-(float)kshift) * tc::kLn2};
+      launch_pdl(kern, dim3(tgrid), dim3(tc::kTcThreads), sm, st, tm_dq, tm_dk, side_q, side_k, 2, scale * tc::kLog2e, sch,
+                 p.m, a.device_status);
       if (L.end("tc_bwd_c")) return L.status;
       return 0;
     }
@@ -830,7 +874,7 @@ static int backward_groups(const fnb_bwd_args& a, int max_smem, int sms, cudaStr
     Plan p = group_plan(a.shape, n);
     BwdWs w = carve_bwd(p, ga.workspace);
     cudaStream_t s = (g & 1) ? fork.begin() : st;
-    rc = backward_impl<T>(ga, p, w, max_smem, sms, s);
+    rc = backward_impl<T>(ga, p, w, max_smem, sms, s, /*allow_inner_fork=*/G == 1);
     if (g & 1) fork.end();
   }
   fork.join();
@@ -1011,9 +1055,9 @@ int fnb_sp_backward(const fnb_bwd_args* a, const fnb_sp_info* sp) {
   SpCtx S;
   S.stage = sp->stage; S.rank = sp->rank; S.world = sp->world; S.N_global = sp->seq_len_global; S.xfer = sp->xfer;
   switch (a->shape.dtype) {
-    case FNB_F32: return backward_impl<float>(*a, p, w, max_smem, sms, st, S);
-    case FNB_F16: return backward_impl<__half>(*a, p, w, max_smem, sms, st, S);
-    default: return backward_impl<__nv_bfloat16>(*a, p, w, max_smem, sms, st, S);
+    case FNB_F32: return backward_impl<float>(*a, p, w, max_smem, sms, st, true, S);
+    case FNB_F16: return backward_impl<__half>(*a, p, w, max_smem, sms, st, true, S);
+    default: return backward_impl<__nv_bfloat16>(*a, p, w, max_smem, sms, st, true, S);
   }
 }
 

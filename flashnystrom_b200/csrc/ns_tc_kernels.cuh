@@ -751,6 +751,8 @@ struct BwdHeadParams {
   int nchunk;
   const float* k2inv; const float* bmat;
   float* dkt_a;               // [BH][m][D] out
+  // The four outputs below feed the column pass; all are skipped when D3 is null (the column pass
+  // then runs beside this kernel and takes them from a separate small kernel).
   float* D3;                  // [BH][m] out
   void* do3n;                 // [BH][MP][D] 16-bit out = dO3 / do3_scale
   float* do3_scale;           // [BH] out
@@ -838,6 +840,7 @@ __device__ inline void bwd_head_tc(Ctx& c, float* red, const ns::NsBwdParams& p,
 #pragma unroll
   for (int w = 1; w < kComputeThreads / 32; ++w) cmax = fmaxf(cmax, red[256 + w]);
   const float sc = pow2_scale(cmax), inv_sc = 1.f / sc;
+  if (h.D3) {
   if (t == 0) h.do3_scale[bh] = sc;
   if (t < m) h.D3[bh * m + t] = (red[4 * t] + red[4 * t + 1]) + (red[4 * t + 2] + red[4 * t + 3]);
   {
@@ -858,6 +861,7 @@ __device__ inline void bwd_head_tc(Ctx& c, float* red, const ns::NsBwdParams& p,
       d0[0] = make_uint4(w0[0], w0[1], w0[2], w0[3]); d0[1] = make_uint4(w0[4], w0[5], w0[6], w0[7]);
       d1[0] = make_uint4(w1[0], w1[1], w1[2], w1[3]); d1[1] = make_uint4(w1[4], w1[5], w1[6], w1[7]);
     }
+  }
   }
   ns::ns_sync();   // do3f (slots 0, 1) is free again
   NS_TRACE();

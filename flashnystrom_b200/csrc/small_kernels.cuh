@@ -208,10 +208,10 @@ struct BwdMid1Params {
   const float* partA;         // [BH][nchunk][2][m][D]
   int nchunk;
   const float* k2inv; const float* bmat; const float* q_landmarks;
-  float* dkt_a;               // [BH][m][D]
-  float* dO3;                 // [BH][m][D]
+  float* dkt_a;               // [BH][m][D]    (null: not written)
+  float* dO3;                 // [BH][m][D]    (null: not written)
   float* D3;                  // [BH][m]
-  float* G;                   // [BH][m][m]  dK2inv
+  float* G;                   // [BH][m][m]  dK2inv  (null: not computed)
   int m, D;
   int dtype, MP;
   void* qt16;                 // [BH][MP][D] = qt_mul * Qt
@@ -271,7 +271,10 @@ __global__ void __launch_bounds__(kThreads) bwd_mid1_kernel(BwdMid1Params p) {
     const float4* sb = reinterpret_cast<const float4*>(bmat + l * D + d0);
 #pragma unroll
     for (int v = 0; v < 8; ++v)
-      if (v < nv) { dd[v] = a0[v]; dk[v] = a1[v]; db[v] = sb[v]; }
+      if (v < nv) {
+        dd[v] = a0[v]; db[v] = sb[v];
+        if (p.dkt_a) dk[v] = a1[v];
+      }
   }
   __syncthreads();
   const float* k2inv = p.k2inv + bh * m * m;
@@ -304,7 +307,10 @@ __global__ void __launch_bounds__(kThreads) bwd_mid1_kernel(BwdMid1Params p) {
 #pragma unroll
     for (int v = 0; v < 8; ++v)
       if (v < nv) {
-        if (act) { dg[v] = acc[v]; dsm[v] = acc[v]; }
+        if (act) {
+          dsm[v] = acc[v];
+          if (p.dO3) dg[v] = acc[v];
+        }
         const float4 x = bb[v];
         d3 += acc[v].x * x.x + acc[v].y * x.y + acc[v].z * x.z + acc[v].w * x.w;
         amax = fmaxf(amax, fmaxf(fmaxf(fabsf(acc[v].x), fabsf(acc[v].y)), fmaxf(fabsf(acc[v].z), fabsf(acc[v].w))));
@@ -314,7 +320,7 @@ __global__ void __launch_bounds__(kThreads) bwd_mid1_kernel(BwdMid1Params p) {
     if (q == 0 && act) p.D3[bh * m + l] = d3;
     // G[l][j] = sum_d dstep2[l][d] Bmat[j][d],  j = q, q+4, ...
     float* Gr = p.G + bh * m * m + l * m;
-    for (int j = q; j < m; j += 4) {
+    for (int j = q; p.G && j < m; j += 4) {
       const float4* a = reinterpret_cast<const float4*>(ds + l * D);
       const float4* b = reinterpret_cast<const float4*>(bm + j * ldb);
       float s = 0.f;

@@ -352,7 +352,7 @@ tc_bwd_ac_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                  const __grid_constant__ CUtensorMap tm_dq,
                  const float* __restrict__ k_landmarks, const float* __restrict__ step2,
                  const float* __restrict__ lse1,
-                 const float* __restrict__ rows_q, float* __restrict__ partA, float* __restrict__ d1_out,
+                 const float* __restrict__ rows_q, float* __restrict__ partA, float* __restrict__ sc_out,
                  int ds_to_dq, TcSched sch, int m, float scale, int* status) {
   static_assert(D == 64 && MP == 64, "the in-kernel operand packing is written for 64 x 64 landmark operands");
   using L = BwdAcSmem<D, MP, MODE>;
@@ -508,6 +508,8 @@ tc_bwd_ac_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                                                scale * kLog2e, reinterpret_cast<float*>(s_ds));
     fence_proxy_async();
     mbar_arrive_warp(small_full);
+    // the in-place dQ pass rescales the dS tiles by the same power of two
+    if (MODE == kModeA && sc_out && threadIdx.x == 0) sc_out[bh] = sc;
     const int c0 = h * HC;
     Segments sg(sch.seg_N, m);
     bool alive = true;
@@ -543,8 +545,6 @@ tc_bwd_ac_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       named_barrier(1, kComputeThreads);
       const float d1 = dpart + s_x[(h ^ 1) * kTile + r];
       if (MODE == kModeA) {
-        // D1 (in the domain of the normalised step2 copy) is reused by the dQ pass
-        if (d1_out && h == 0 && valid) d1_out[bh * sch.N + row] = d1;
         named_barrier(1, kComputeThreads);   // exchange words live in the head of the P tile
         store_cols<T, HC>(s_p, r, c0, p);
       }
@@ -612,30 +612,58 @@ tc_bwd_ac_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 }
 
 // ------------------------------------------------------------------------------------------
-// Softmax-1 backward, second row pass (dQ).  The first row pass leaves its 16-bit dS1 tiles
+// Last backward pass: dQ and dK in place.  The first row pass leaves its 16-bit dS1 tiles
 // (dS1 = P1 o (dP1 - D1), scaled by 1/sc with sc the power-of-two scale of step2) in the dQ buffer
-// itself: with 64 landmark columns and head_dim 64 a dS1 tile has exactly the footprint of the dQ
-// tile of the same rows.  This pass turns every tile in place:
-//   dQ = (sc ln2) dS1 (s log2e Kt) + rows_q[l(n)]
-// One TMA load, one product and one TMA store per tile; no exponentials, Q and dO are not read
-// again.  Four input stages per CTA (released by the product's commit), four accumulators, two
-// compute groups of 128 threads (one thread per tile row) that take alternate tiles and stage
-// their output tile in a buffer of their own.
-template <int D, int MP>
-struct BwdCSmem {
-  static constexpr int kStages = 4;
-  static constexpr int kKt = MP * D * 2, kIn = kTile * MP * 2, kOut = kTile * D * 2;
-  // relies on the dynamic shared window being 1024-byte aligned (checked at run time)
-  static constexpr int kBytes = kKt + kStages * kIn + 2 * kOut + 256;
+// and the column pass its dS3' tiles in the dK buffer: with 64 landmark columns and head_dim 64
+// such a tile has exactly the footprint of the gradient tile of the same rows.  Each tile becomes
+//   side 0:  dQ = (sc ln2)  dS1  (s log2e Kt) + rows_q[l(n)]
+//   side 1:  dK = (2^-k ln2) dS3' (s log2e Qt) + rows_k[l(n)]
+// with one TMA load, one product and one TMA store; no exponentials, and Q, K, dO are not read
+// again.  A CTA takes its run of tiles on side 0, then the same run on side 1.  Four input stages
+// (released by the product's commit), four accumulators, two compute groups of 128 threads (one
+// thread per tile row) that take alternate tiles and stage their output tile in a buffer of their
+// own.
+struct RowsSide {
+  const float* landmarks;   // [BH][m][D] FP32: the landmark matrix the tile is multiplied by
+  const float* rows;        // [BH][m][D] FP32: per-landmark term added to every row of its segment
+  const float* out_scale;   // [BH] or null: per-slice factor of the product
+  float out_mul;            // constant factor of the product
 };
+
+template <int D, int MP>
+struct RowsSmem {
+  static constexpr int kStages = 4;
+  static constexpr int kOp = MP * D * 2, kIn = kTile * MP * 2, kOut = kTile * D * 2;
+  // relies on the dynamic shared window being 1024-byte aligned (checked at run time)
+  static constexpr int kBytes = 2 * kOp + kStages * kIn + 2 * kOut + 256;
+};
+
+// 16-bit swizzled operand tile of one FP32 landmark matrix (rows >= m zero), times mul; compute
+// warps (256 threads), head_dim 64: thread t packs row t >> 2, columns 16 (t & 3) .. +15
+template <class T>
+__device__ __forceinline__ void pack_landmark_operand(uint8_t* tile, const float* A, int m, float mul) {
+  const int t = threadIdx.x, r = t >> 2, c0 = (t & 3) * 16;
+#pragma unroll
+  for (int c = 0; c < 2; ++c) {
+    float4 x = make_float4(0.f, 0.f, 0.f, 0.f), y = x;
+    if (r < m) {
+      x = *reinterpret_cast<const float4*>(A + r * 64 + c0 + 8 * c);
+      y = *reinterpret_cast<const float4*>(A + r * 64 + c0 + 8 * c + 4);
+    }
+    uint4 w;
+    w.x = pack2<T>(x.x * mul, x.y * mul); w.y = pack2<T>(x.z * mul, x.w * mul);
+    w.z = pack2<T>(y.x * mul, y.y * mul); w.w = pack2<T>(y.z * mul, y.w * mul);
+    *reinterpret_cast<uint4*>(tile + sw128_offset(r, (c0 >> 3) + c)) = w;
+  }
+}
 
 template <class T, int D, int MP>
 __global__ void __launch_bounds__(kTcThreads, 2)
-tc_bwd_c_kernel(const __grid_constant__ CUtensorMap tm_dq, const float* __restrict__ k_landmarks,
-                const float* __restrict__ step2, const float* __restrict__ rows_q, TcSched sch, int m,
-                float scale, int* status) {
-  using L = BwdCSmem<D, MP>;
-  static_assert(D == 64 && MP == 64, "a dS1 tile must have the footprint of a dQ tile");
+tc_rows_inplace_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                       RowsSide side_a, RowsSide side_b, int nsides, float op_mul, TcSched sch, int m,
+                       int* status) {
+  using L = RowsSmem<D, MP>;
+  static_assert(D == 64 && MP == 64, "a dS tile must have the footprint of a gradient tile");
   constexpr int kGroup = kComputeThreads / 2;
   constexpr int kStages = L::kStages;
   constexpr uint32_t kTmemCols = kStages * D;
@@ -646,9 +674,9 @@ tc_bwd_c_kernel(const __grid_constant__ CUtensorMap tm_dq, const float* __restri
     if (threadIdx.x == 0 && status) atomicCAS(status, 0, (2 << 24) | 0x2000);
     return;
   }
-  uint8_t* s_kt = smem_raw;
-  uint8_t* s_in = s_kt + L::kKt;               // kStages dS1 tiles
-  uint8_t* s_out = s_in + kStages * L::kIn;    // one dQ staging tile per group
+  uint8_t* s_op = smem_raw;                    // one operand tile per side
+  uint8_t* s_in = s_op + 2 * L::kOp;           // kStages dS tiles
+  uint8_t* s_out = s_in + kStages * L::kIn;    // one staging tile per group
   uint64_t* bars = reinterpret_cast<uint64_t*>(s_out + 2 * L::kOut);
   uint64_t* small_full = bars + 0;
   uint64_t* in_full = bars + 1;                // [kStages]
@@ -662,7 +690,7 @@ tc_bwd_c_kernel(const __grid_constant__ CUtensorMap tm_dq, const float* __restri
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const TileRange tr = tile_range(sch);
   const int64_t bh = tr.bh;
-  const int tile0 = tr.tile0, count = tr.count;
+  const int tile0 = tr.tile0, count = tr.count, total = nsides * tr.count;
 
   if (threadIdx.x == 0) {
     mbar_init(small_full, kComputeThreads / 32);
@@ -686,13 +714,16 @@ tc_bwd_c_kernel(const __grid_constant__ CUtensorMap tm_dq, const float* __restri
 
   if (warp == kProducerWarp) {
     if (lane == 0) {
-      tma_prefetch_desc(&tm_dq);
+      tma_prefetch_desc(&tm_a);
+      if (nsides > 1) tma_prefetch_desc(&tm_b);
       int armed = 0;
-      for (int i = 0; i < count; ++i) {
+      for (int i = 0; i < total; ++i) {
         const int s = i % kStages;
+        const bool second = i >= count;
         if (!mbar_wait(in_empty + s, ((i / kStages) & 1) ^ 1, ab, 0x2100 + i)) break;
         mbar_expect_tx(in_full + s, L::kIn);
-        tma_load_3d(s_in + s * L::kIn, &tm_dq, in_full + s, 0, (tile0 + i) * kTile, (int)bh);
+        tma_load_3d(s_in + s * L::kIn, second ? &tm_b : &tm_a, in_full + s, 0,
+                    (tile0 + (second ? i - count : i)) * kTile, (int)bh);
         armed = i + 1;
       }
       if (ab.raised())
@@ -700,22 +731,23 @@ tc_bwd_c_kernel(const __grid_constant__ CUtensorMap tm_dq, const float* __restri
     }
   } else if (warp == kMmaWarp) {
     if (lane == 0) {
-      constexpr uint32_t idesc_dq = make_idesc<T>(kTile, D, false, true);
-      const uint32_t a_kt = smem_u32(s_kt);
+      constexpr uint32_t idesc_o = make_idesc<T>(kTile, D, false, true);
+      const uint32_t a_op = smem_u32(s_op);
       bool ok = mbar_wait(small_full, 0, ab, 0x2200);
-      for (int i = 0; ok && i < count; ++i) {
+      for (int i = 0; ok && i < total; ++i) {
         const int s = i % kStages;
         const uint32_t par = (uint32_t)(i / kStages) & 1u;
+        const uint32_t a_b = a_op + (i >= count ? L::kOp : 0);
         // the accumulator of this stage was last read by tile i - kStages
         if (!mbar_wait(o_free + s, par ^ 1, ab, 0x2380 + i)) break;
         if (!mbar_wait(in_full + s, par, ab, 0x2300 + i)) break;
         tc_fence_after();
         const uint32_t a_ds = smem_u32(s_in + s * L::kIn);
-        // dQ = dS (128 x MP, K-major) * Kt (MP x D, MN-major view of kt16)
+        // (128 x MP, K-major) * (MP x D, MN-major view of the landmark operand)
 #pragma unroll
         for (int k = 0; k < MP / 16; ++k)
-          umma(tmem_base + s * D, kdesc(a_ds, k, kTile), smem_desc_sw128(a_kt + k * 2048, MP * 128, 1024),
-               idesc_dq, k > 0);
+          umma(tmem_base + s * D, kdesc(a_ds, k, kTile), smem_desc_sw128(a_b + k * 2048, MP * 128, 1024),
+               idesc_o, k > 0);
         umma_commit(in_empty + s);
         umma_commit(acc_done + s);
       }
@@ -724,29 +756,30 @@ tc_bwd_c_kernel(const __grid_constant__ CUtensorMap tm_dq, const float* __restri
     const int g = warp >> 2;
     const int r = threadIdx.x & 127;
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-    // operand copy of Kt and the scale of step2 for this slice (the staging tiles are free until
-    // the first tile; the step2 copy itself is not used by this pass)
-    const float sc = pack_landmark_operands<T>(s_kt, s_out, k_landmarks + bh * m * D, step2 + bh * m * D, m,
-                                               scale * kLog2e, reinterpret_cast<float*>(s_out + L::kOut));
+    pack_landmark_operand<T>(s_op, side_a.landmarks + bh * m * D, m, op_mul);
+    if (nsides > 1) pack_landmark_operand<T>(s_op + L::kOp, side_b.landmarks + bh * m * D, m, op_mul);
     fence_proxy_async();
     mbar_arrive_warp(small_full);
-    named_barrier(3, kComputeThreads);   // the step2 copy in the staging tile of group 0 is dead from here on
-    const float mul = sc * kLn2;
+    const float mul_a = (side_a.out_scale ? side_a.out_scale[bh] : 1.f) * side_a.out_mul;
+    const float mul_b = nsides > 1 ? (side_b.out_scale ? side_b.out_scale[bh] : 1.f) * side_b.out_mul : 0.f;
     uint8_t* my_out = s_out + g * L::kOut;
     const bool leader = r == 0;
     Segments sg(sch.seg_N, m);
-    for (int i = g; i < count; i += 2) {
+    for (int i = g; i < total; i += 2) {
       const int s = i % kStages;
       const uint32_t par = (uint32_t)(i / kStages) & 1u;
-      const int64_t row = (int64_t)(tile0 + i) * kTile + r;
+      const bool second = i >= count;
+      const int tile = tile0 + (second ? i - count : i);
+      const int64_t row = (int64_t)tile * kTile + r;
       const bool valid = row < sch.N;
       const int l = valid ? sg.landmark_of(sch.row_offset + row) : 0;
-      const float4* add = reinterpret_cast<const float4*>(rows_q + (bh * m + l) * D);
+      const float4* add = reinterpret_cast<const float4*>((second ? side_b.rows : side_a.rows) + (bh * m + l) * D);
+      const float mul = second ? mul_b : mul_a;
       const uint32_t t_o = tmem_base + s * D + lane_base;
       if (!mbar_wait(acc_done + s, par, ab, 0x2800 + i)) break;
       __syncwarp();
       tc_fence_after();
-      // the previous dQ tile of this group was stored from my_out: wait until the copy has read it
+      // the previous tile of this group was stored from my_out: wait until the copy has read it
       if (leader) tma_store_wait_read();
       named_barrier(1 + g, kGroup);
 #pragma unroll
@@ -769,7 +802,7 @@ tc_bwd_c_kernel(const __grid_constant__ CUtensorMap tm_dq, const float* __restri
       fence_proxy_async();
       named_barrier(1 + g, kGroup);
       if (leader) {
-        tma_store_3d(&tm_dq, my_out, 0, (tile0 + i) * kTile, (int)bh);
+        tma_store_3d(second ? &tm_b : &tm_a, my_out, 0, tile * kTile, (int)bh);
         tma_store_commit();
       }
     }
@@ -788,8 +821,11 @@ tc_bwd_c_kernel(const __grid_constant__ CUtensorMap tm_dq, const float* __restri
 //                                                         the ~1/N probabilities out of the
 //                                                         subnormal range; undone in FP32)
 //   dV = P' dO3                     -> written once (dO3 read as the MN-major view of do3n)
-//   dK = s dS' Qt + rows_k[l(n)]    -> written once (Qt read as the MN-major view of qt16;
-//                                      rows_k holds s * dKt_tot / len per landmark)
+//   dS' tile                        -> written as it is into the dK tile of the same rows (same
+//                                      footprint); the in-place pass turns it into
+//                                      dK = s dS' Qt + rows_k[l(n)] once the landmark gradients
+//                                      are known, so this pass does not wait for the
+//                                      pseudoinverse backward
 //   dQt partial += dS'^T (sK)       -> TMEM accumulator over the CTA's tiles
 // K is double-buffered (it is needed until the tile's last product), V single-buffered.
 template <int D, int MP>
@@ -805,7 +841,7 @@ tc_bwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
                 const __grid_constant__ CUtensorMap tm_qt, const __grid_constant__ CUtensorMap tm_do3,
                 const __grid_constant__ CUtensorMap tm_dk, const __grid_constant__ CUtensorMap tm_dv,
                 const float* __restrict__ lse3, const float* __restrict__ D3,
-                const float* __restrict__ do3_scale, const float* __restrict__ rows_k,
+                const float* __restrict__ do3_scale,
                 float* __restrict__ partB, TcSched sch, int m, float scale, int kshift, int* status) {
   using L = BwdBSmem<D, MP>;
   constexpr int KBD = D / 64, HC = MP / 2, HD = D / 2;
@@ -822,7 +858,7 @@ tc_bwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
   uint8_t* s_k = reinterpret_cast<uint8_t*>(s_c3) + L::kVec;   // two stages
   uint8_t* s_v = s_k + 2 * L::kIn;
   uint8_t* s_p = s_v + L::kIn;      // P' tile, then staging of the dV tile
-  uint8_t* s_ds = s_p + L::kPd;     // dS' tile, then staging of the dK tile
+  uint8_t* s_ds = s_p + L::kPd;     // dS' tile
   uint64_t* bars = reinterpret_cast<uint64_t*>(s_ds + L::kPd);
   uint64_t* small_full = bars + 0;
   uint64_t* k_full = bars + 1;      // [2]
@@ -862,7 +898,7 @@ tc_bwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
   pdl_wait();   // everything above overlaps the tail of the previous kernel of the stream
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tmem_s = tmem_base, tmem_dp = tmem_base + W, tmem_acc = tmem_base + 2 * W;
-  const uint32_t tmem_dv = tmem_s, tmem_dk = tmem_dp;
+  const uint32_t tmem_dv = tmem_s;
   Abort ab{abort_word, status};
 
   if (warp == kProducerWarp) {
@@ -906,7 +942,7 @@ tc_bwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
         const uint32_t a_k = smem_u32(s_k + st * L::kIn);
         if (!mbar_wait(k_full + st, (i >> 1) & 1, ab, 0x2300 + i)) break;
         if (!mbar_wait(v_full, i & 1, ab, 0x2340 + i)) break;
-        if (!mbar_wait(o_free, (i & 1) ^ 1, ab, 0x2380 + i)) break;   // dV / dK alias S / dP
+        if (!mbar_wait(o_free, (i & 1) ^ 1, ab, 0x2380 + i)) break;   // dV aliases S
         tc_fence_after();
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) umma(tmem_s, kdesc(a_k, k, kTile), kdesc(a_qt, k, MP), idesc_s, k > 0);
@@ -915,19 +951,21 @@ tc_bwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
         umma_commit(v_empty);
         umma_commit(sdp_full);
         if (!mbar_wait(pds_full, i & 1, ab, 0x2400 + i)) break;
+        tma_store_3d(&tm_dk, s_ds, 0, (tile0 + i) * kTile, (int)bh);
+        tma_store_commit();
         tc_fence_after();
 #pragma unroll
         for (int k = 0; k < MP / 16; ++k)
           umma(tmem_dv, kdesc(a_p, k, kTile), smem_desc_sw128(a_do3 + k * 2048, MP * 128, 1024), idesc_o, k > 0);
 #pragma unroll
-        for (int k = 0; k < MP / 16; ++k)
-          umma(tmem_dk, kdesc(a_ds, k, kTile), smem_desc_sw128(a_qt + k * 2048, MP * 128, 1024), idesc_o, k > 0);
-#pragma unroll
         for (int k = 0; k < kTile / 16; ++k)
           umma(tmem_acc, mndesc(a_ds, k), mndesc(a_k, k), idesc_acc, (i > 0 || k > 0));
         umma_commit(k_empty + st);
+        // out_full lets the compute warps move on to the next dS' tile: the copy must have read it
+        tma_store_wait_read();
         umma_commit(out_full);
       }
+      tma_store_wait_all();
     }
   } else {
     const int r = threadIdx.x & 127, h = threadIdx.x >> 7;
@@ -979,33 +1017,22 @@ tc_bwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
       if (!mbar_wait(out_full, i & 1, ab, 0x2800 + i)) { alive = false; break; }
       __syncwarp();
       tc_fence_after();
-      float o[HD], o2[HD];
+      float o[HD];
       ld_cols<HD>(tmem_dv + lane_base + h * HD, o);
-      ld_cols<HD>(tmem_dk + lane_base + h * HD, o2);
       tmem_ld_wait();
       tc_fence_before();
       mbar_arrive_warp(o_free);
-      const int l = valid ? sg.landmark_of(sch.row_offset + row) : 0;
-      const float4* add = reinterpret_cast<const float4*>(rows_k + (bh * m + l) * D + h * HD);
-      const float vmul = dsc * unshift, kmul = unshift * kLn2;
+      const float vmul = dsc * unshift;
 #pragma unroll
-      for (int j = 0; j < HD; j += 4) {
-        const float4 a = add[j >> 2];
-        o[j + 0] *= vmul; o[j + 1] *= vmul; o[j + 2] *= vmul; o[j + 3] *= vmul;
-        o2[j + 0] = fmaf(o2[j + 0], kmul, a.x); o2[j + 1] = fmaf(o2[j + 1], kmul, a.y);
-        o2[j + 2] = fmaf(o2[j + 2], kmul, a.z); o2[j + 3] = fmaf(o2[j + 3], kmul, a.w);
-      }
-      // out_full: every product that read the P' / dS' tiles is complete, so they can hold the
-      // outgoing tiles now
+      for (int j = 0; j < HD; ++j) o[j] *= vmul;
+      // out_full: every product that read the P' tile is complete, so it can hold the outgoing
+      // dV tile now
       store_cols<T, HD>(s_p, r, h * HD, o);
-      store_cols<T, HD>(s_ds, r, h * HD, o2);
       fence_proxy_async();
       named_barrier(1, kComputeThreads);
       if (threadIdx.x == 0) {
-        for (int kb = 0; kb < KBD; ++kb) {
+        for (int kb = 0; kb < KBD; ++kb)
           tma_store_3d(&tm_dv, s_p + kb * (kTile * 128), kb * 64, (tile0 + i) * kTile, (int)bh);
-          tma_store_3d(&tm_dk, s_ds + kb * (kTile * 128), kb * 64, (tile0 + i) * kTile, (int)bh);
-        }
         tma_store_commit();
       }
     }
