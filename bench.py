@@ -40,7 +40,9 @@ FALLBACK_HBM_GBS = 6650.0
 KERNEL_PASSES = {
     "landmark_partial": 2, "gen_fwd_b": 2, "gen_fwd_c": 2, "gen_bwd_a": 2, "gen_bwd_b": 4,
     "gen_bwd_c": 3,
-    "tc_pool_q": 1, "tc_fwd_b": 2, "tc_fwd_c": 2, "tc_bwd_a": 2, "tc_bwd_b": 4, "tc_bwd_c": 3,
+    # tc_bwd_a also writes its dS1 tiles (into dq), tc_bwd_b writes dS3' tiles (into dk) and dV,
+    # tc_bwd_c reads both sets of tiles and writes dQ and dK in place
+    "tc_pool_q": 1, "tc_fwd_b": 2, "tc_fwd_c": 2, "tc_bwd_a": 3, "tc_bwd_b": 4, "tc_bwd_c": 4,
 }
 
 

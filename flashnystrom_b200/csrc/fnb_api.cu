@@ -240,7 +240,6 @@ struct BwdWs {
   float *partA, *partB, *dstep2, *dkt_a, *dO3, *dqt_ns, *dkt_tot, *dqt_tot, *D3, *G, *dK2, *pinv;
   void* op16[8];              // 16-bit operand copies for the tensor-core kernels
   float *st_scale, *do3_scale, *rows_q, *rows_k;
-  float* d1;                  // [BH][N]: softmax-1 row terms D1, written by pass A for pass C
   float* partA_red;           // [BH][2][m][D]: pass-A partials summed over the chunks
   size_t bytes;
 };
@@ -262,7 +261,6 @@ static BwdWs carve_bwd(const Plan& p, void* base) {
   for (int i = 0; i < 8; ++i) w.op16[i] = take(op16);
   w.st_scale = take((size_t)p.BH); w.do3_scale = take((size_t)p.BH);
   w.rows_q = take(md); w.rows_k = take(md);
-  w.d1 = take((size_t)p.BH * p.N);
   w.partA_red = take(2 * md);
   w.bytes = off;
   return w;
@@ -584,12 +582,11 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
     if (use_tc) {
       constexpr int D = 64, MPc = 64;
       L.begin();
-      auto kern = tc::tc_bwd_ac_kernel<T, D, MPc, tc::kModeA>;
-      size_t sm = tc::BwdAcSmem<D, MPc, tc::kModeA>::kBytes;
+      auto kern = tc::tc_bwd_a_kernel<T, D, MPc>;
+      size_t sm = tc::BwdASmem<D, MPc>::kBytes;
       if (int rc = set_smem(kern, sm, max_smem, "tc_bwd_a")) return rc;
       launch_pdl(kern, dim3(tgrid), dim3(tc::kTcThreads), sm, st, tm_q, tm_g, tm_dq, a.k_landmarks, a.step2, a.lse1,
-                 (const float*)nullptr, w.partA, w.st_scale, 1,
-                                             sch, p.m, scale, a.device_status);
+                 w.partA, w.st_scale, sch, p.m, scale, a.device_status);
       if (L.end("tc_bwd_a")) return L.status;
     }
   }

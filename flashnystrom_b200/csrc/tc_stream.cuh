@@ -326,62 +326,54 @@ tc_fwd_c_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 }
 
 // ------------------------------------------------------------------------------------------
-// Softmax-1 backward, both row passes.  Per 128-row tile of Q and dO:
+// Softmax-1 backward, first row pass.  Per 128-row tile of Q and dO (thread = row n, half the
+// landmark columns):
 //   S1 = Q kt16^T (log2 domain), dP1 = dO st16^T (step2 normalised by 2^-e, undone by sc),
 //   P1 = exp2(S1 - lse1*log2e), D1 = rowsum(P1 o dP1), dS1 = P1 o (dP1 - D1)        [FP32]
-// kModeA: accumulate dstep2 += P1^T dO and dKt += dS1^T Q in TMEM over all of the CTA's tiles
-//         (UMMA with both operands MN-major: the staged tiles are contracted over their rows)
-//         and write one FP32 partial pair per CTA.
-// kModeC: dQ = s dS1 Kt + rows_q[l(n)], written once through a TMA store; rows_q holds
-//         s * dQt_tot / len per landmark.  Kt is read from the same kt16 copy as an MN-major
-//         operand (its s*log2e factor is undone by ln2 in the epilogue).
-constexpr int kModeA = 0, kModeC = 1;
-
-template <int D, int MP, int MODE>
-struct BwdAcSmem {
-  static constexpr int kKt = MP * D * 2, kSt = MP * D * 2, kIn = kTile * D * 2,
-                       kP = (MODE == kModeA) ? kTile * MP * 2 : 0, kDs = kTile * (MP > D ? MP : D) * 2,
-                       kX = (MODE == kModeC) ? 2 * kTile * 4 * 2 : 0;
-  // mode A relies on the dynamic shared window being 1024-byte aligned (checked at run time)
-  static constexpr int kBytes = kKt + kSt + 4 * kIn + kP + kDs + kX + 256 + (MODE == kModeC ? 1024 : 0);
+//   dstep2 += P1^T dO and dKt += dS1^T Q accumulate in TMEM over all of the CTA's tiles (UMMA with
+//   both operands MN-major: the staged tiles are contracted over their rows); one FP32 partial
+//   pair per CTA.  The 16-bit dS1 tile also goes to global memory as it is, into the dQ tile of
+//   the same rows (same footprint), where the in-place pass finishes dQ.
+template <int D, int MP>
+struct BwdASmem {
+  static constexpr int kKt = MP * D * 2, kSt = MP * D * 2, kIn = kTile * D * 2, kP = kTile * MP * 2,
+                       kDs = kTile * MP * 2;
+  // relies on the dynamic shared window being 1024-byte aligned (checked at run time)
+  static constexpr int kBytes = kKt + kSt + 4 * kIn + kP + kDs + 256;
 };
 
-template <class T, int D, int MP, int MODE>
+template <class T, int D, int MP>
 __global__ void __launch_bounds__(kTcThreads, 2)
-tc_bwd_ac_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_g,
-                 const __grid_constant__ CUtensorMap tm_dq,
-                 const float* __restrict__ k_landmarks, const float* __restrict__ step2,
-                 const float* __restrict__ lse1,
-                 const float* __restrict__ rows_q, float* __restrict__ partA, float* __restrict__ sc_out,
-                 int ds_to_dq, TcSched sch, int m, float scale, int* status) {
-  static_assert(D == 64 && MP == 64, "the in-kernel operand packing is written for 64 x 64 landmark operands");
-  using L = BwdAcSmem<D, MP, MODE>;
-  constexpr int KBD = D / 64, HC = MP / 2, HD = D / 2;
-  constexpr uint32_t kCols = (MODE == kModeA) ? 2 * MP + 2 * D : 4 * MP;
-  constexpr uint32_t kTmemCols = kCols <= 256 ? 256 : 512;
+tc_bwd_a_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_g,
+                const __grid_constant__ CUtensorMap tm_dq,
+                const float* __restrict__ k_landmarks, const float* __restrict__ step2,
+                const float* __restrict__ lse1, float* __restrict__ partA, float* __restrict__ sc_out,
+                TcSched sch, int m, float scale, int* status) {
+  static_assert(D == 64 && MP == 64, "written for 64 x 64 landmark operands");
+  using L = BwdASmem<D, MP>;
+  constexpr int HC = MP / 2, HD = D / 2;
+  constexpr uint32_t kTmemCols = 256;    // S, dP, and the 128-column accumulator
   extern __shared__ uint8_t smem_raw[];
   pdl_trigger();
-  uint8_t* base = (MODE == kModeC) ? align1024(smem_raw) : smem_raw;
-  if (MODE == kModeA && (smem_u32(smem_raw) & 1023u)) {
+  if (smem_u32(smem_raw) & 1023u) {
     if (threadIdx.x == 0 && status) atomicCAS(status, 0, (2 << 24) | 0x1000);
     return;
   }
-  uint8_t* s_kt = base;
+  uint8_t* s_kt = smem_raw;
   uint8_t* s_st = s_kt + L::kKt;
   uint8_t* s_q = s_st + L::kSt;          // two stages
   uint8_t* s_g = s_q + 2 * L::kIn;       // two stages
-  uint8_t* s_p = s_g + 2 * L::kIn;       // mode A: P tile (its head doubles as the D1 exchange)
-  uint8_t* s_ds = s_p + L::kP;           // dS tile; mode C: afterwards the staging of the dQ tile
-  float* s_x = (MODE == kModeA) ? reinterpret_cast<float*>(s_p) : reinterpret_cast<float*>(s_ds + L::kDs);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(s_ds + L::kDs + L::kX);
+  uint8_t* s_p = s_g + 2 * L::kIn;       // P tile (its head doubles as the D1 exchange)
+  uint8_t* s_ds = s_p + L::kP;           // dS tile
+  float* s_x = reinterpret_cast<float*>(s_p);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(s_ds + L::kDs);
   uint64_t* small_full = bars + 0;
   uint64_t* in_full = bars + 1;          // [2]
   uint64_t* in_empty = bars + 3;         // [2]
-  uint64_t* sdp_full = bars + 5;         // [2] (mode A uses [0] only)
-  uint64_t* pds_full = bars + 7;         // [2] (mode A uses [0] only)
-  uint64_t* acc_done = bars + 9;         // mode A: accumulation of a tile complete; mode C [2]: dQ tile complete
-  uint64_t* o_free = bars + 11;          // [2] mode C: dQ accumulator read back
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+  uint64_t* sdp_full = bars + 5;
+  uint64_t* pds_full = bars + 6;
+  uint64_t* acc_done = bars + 7;         // accumulation of a tile complete, its dS copy read
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
   int* abort_word = reinterpret_cast<int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -391,10 +383,10 @@ tc_bwd_ac_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 
   if (threadIdx.x == 0) {
     mbar_init(small_full, kComputeThreads / 32);
-    for (int s = 0; s < 2; ++s) {
-      mbar_init(in_full + s, 1); mbar_init(in_empty + s, 1); mbar_init(sdp_full + s, 1);
-      mbar_init(pds_full + s, kComputeThreads / 32); mbar_init(acc_done + s, 1); mbar_init(o_free + s, kComputeThreads / 32);
-    }
+    for (int s = 0; s < 2; ++s) { mbar_init(in_full + s, 1); mbar_init(in_empty + s, 1); }
+    mbar_init(sdp_full, 1);
+    mbar_init(pds_full, kComputeThreads / 32);
+    mbar_init(acc_done, 1);
     *abort_word = 0;
     fence_mbar_init();
   }
@@ -418,10 +410,8 @@ tc_bwd_ac_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         const int st = i & 1;
         if (!mbar_wait(in_empty + st, ((i >> 1) & 1) ^ 1, ab, 0x1100 + i)) break;
         mbar_expect_tx(in_full + st, 2 * L::kIn);
-        for (int kb = 0; kb < KBD; ++kb) {
-          tma_load_3d(s_q + st * L::kIn + kb * (kTile * 128), &tm_q, in_full + st, kb * 64, (tile0 + i) * kTile, (int)bh);
-          tma_load_3d(s_g + st * L::kIn + kb * (kTile * 128), &tm_g, in_full + st, kb * 64, (tile0 + i) * kTile, (int)bh);
-        }
+        tma_load_3d(s_q + st * L::kIn, &tm_q, in_full + st, 0, (tile0 + i) * kTile, (int)bh);
+        tma_load_3d(s_g + st * L::kIn, &tm_g, in_full + st, 0, (tile0 + i) * kTile, (int)bh);
         armed = i + 1;
       }
       if (ab.raised())
@@ -431,73 +421,46 @@ tc_bwd_ac_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     if (lane == 0) {
       constexpr uint32_t idesc_s = make_idesc<T>(kTile, MP, false, false);
       constexpr uint32_t idesc_acc2 = make_idesc<T>(128, 128, true, true);
-      constexpr uint32_t idesc_dq = make_idesc<T>(kTile, D, false, true);
-      const bool store_ds = MODE == kModeA && ds_to_dq != 0;
-      const uint32_t a_kt = smem_u32(s_kt), a_st = smem_u32(s_st), a_p = smem_u32(s_p), a_ds = smem_u32(s_ds);
-      static_assert(MODE != kModeA || (MP == 64 && D == 64), "the merged accumulation assumes 64 x 64 landmark operands");
-      // S and dP of tile i into TMEM buffer b (mode A: always buffer 0)
-      auto front = [&](int i, int b) -> bool {
+      const uint32_t a_kt = smem_u32(s_kt), a_st = smem_u32(s_st), a_p = smem_u32(s_p);
+      // S and dP of tile i
+      auto front = [&](int i) -> bool {
         const int st = i & 1;
         if (!mbar_wait(in_full + st, (i >> 1) & 1, ab, 0x1300 + i)) return false;
         tc_fence_after();
         const uint32_t a_q = smem_u32(s_q + st * L::kIn), a_g = smem_u32(s_g + st * L::kIn);
-        const uint32_t t_s = tmem_base + b * 2 * MP;
 #pragma unroll
-        for (int k = 0; k < D / 16; ++k) umma(t_s, kdesc(a_q, k, kTile), kdesc(a_kt, k, MP), idesc_s, k > 0);
+        for (int k = 0; k < D / 16; ++k) umma(tmem_base, kdesc(a_q, k, kTile), kdesc(a_kt, k, MP), idesc_s, k > 0);
 #pragma unroll
-        for (int k = 0; k < D / 16; ++k) umma(t_s + MP, kdesc(a_g, k, kTile), kdesc(a_st, k, MP), idesc_s, k > 0);
-        if (MODE == kModeC) umma_commit(in_empty + st);
-        umma_commit(sdp_full + b);
+        for (int k = 0; k < D / 16; ++k) umma(tmem_base + MP, kdesc(a_g, k, kTile), kdesc(a_st, k, MP), idesc_s, k > 0);
+        umma_commit(sdp_full);
         return true;
       };
       bool ok = mbar_wait(small_full, 0, ab, 0x1200);
-      ok = ok && front(0, 0);
-      if (MODE == kModeC && ok && count > 1) ok = front(1, 1);
+      ok = ok && front(0);
       for (int i = 0; ok && i < count; ++i) {
-        if (MODE == kModeA) {
-          if (!mbar_wait(pds_full, i & 1, ab, 0x1400 + i)) break;
-          // The dS tile also goes to global memory, into the dQ tile of the same rows (same
-          // footprint): the dQ pass turns it into dQ in place and never reads Q or dO.
-          if (store_ds) {
-            tma_store_3d(&tm_dq, s_ds, 0, (tile0 + i) * kTile, (int)bh);
-            tma_store_commit();
-          }
-          // S / dP of tile i are consumed: start the next tile's scores before this tile's
-          // accumulation so that the compute warps find them ready
-          if (i + 1 < count && !front(i + 1, 0)) break;
-          tc_fence_after();
-          const int st = i & 1;
-          const uint32_t a_q = smem_u32(s_q + st * L::kIn), a_g = smem_u32(s_g + st * L::kIn);
-          // One 128 x 128 accumulator for both sums: [P | dS]^T [Q | dO] (both operands MN-major,
-          // the second 64-wide block of each is the neighbouring tile).  Rows 0..63 x columns
-          // 64..127 hold P^T dO, rows 64..127 x columns 0..63 hold dS^T Q; the other two quadrants
-          // are not used.  An M = N = 128 MMA takes 35 ns against 2 x 25 ns for two 64 x 64 ones.
-          (void)a_g;
+        if (!mbar_wait(pds_full, i & 1, ab, 0x1400 + i)) break;
+        // the dS tile as it is -> dQ tile of the same rows
+        tma_store_3d(&tm_dq, s_ds, 0, (tile0 + i) * kTile, (int)bh);
+        tma_store_commit();
+        // S / dP of tile i are consumed: start the next tile's scores before this tile's
+        // accumulation so that the compute warps find them ready
+        if (i + 1 < count && !front(i + 1)) break;
+        tc_fence_after();
+        const int st = i & 1;
+        // One 128 x 128 accumulator for both sums: [P | dS]^T [Q | dO] (both operands MN-major,
+        // the second 64-wide block of each is the neighbouring tile).  Rows 0..63 x columns
+        // 64..127 hold P^T dO, rows 64..127 x columns 0..63 hold dS^T Q; the other two quadrants
+        // are not used.  An M = N = 128 MMA takes 35 ns against 2 x 25 ns for two 64 x 64 ones.
 #pragma unroll
-          for (int k = 0; k < kTile / 16; ++k)
-            umma(tmem_base + 2 * MP, smem_desc_sw128(a_p + k * 2048, L::kP, 1024),
-                 smem_desc_sw128(a_q + k * 2048, 2 * L::kIn, 1024), idesc_acc2, (i > 0 || k > 0));
-          umma_commit(in_empty + st);
-          // acc_done lets the compute warps overwrite the dS tile: the copy must have read it
-          if (store_ds) tma_store_wait_read();
-          umma_commit(acc_done);
-        } else {
-          const int b = i & 1;
-          if (!mbar_wait(pds_full + b, (i >> 1) & 1, ab, 0x1400 + i)) break;
-          tc_fence_after();
-          // dQ = dS (128 x MP, K-major) * Kt (MP x D, MN-major view of kt16)
-#pragma unroll
-          for (int k = 0; k < MP / 16; ++k)
-            umma(tmem_base + b * 2 * MP, kdesc(a_ds, k, kTile),
-                 smem_desc_sw128(a_kt + k * 2048, MP * 128, 1024), idesc_dq, k > 0);
-          umma_commit(acc_done + b);
-          if (i + 2 < count) {
-            if (!mbar_wait(o_free + b, (i >> 1) & 1, ab, 0x1380 + i)) break;
-            ok = front(i + 2, b);
-          }
-        }
+        for (int k = 0; k < kTile / 16; ++k)
+          umma(tmem_base + 2 * MP, smem_desc_sw128(a_p + k * 2048, L::kP, 1024),
+               smem_desc_sw128(smem_u32(s_q + st * L::kIn) + k * 2048, 2 * L::kIn, 1024), idesc_acc2, (i > 0 || k > 0));
+        umma_commit(in_empty + st);
+        // acc_done lets the compute warps overwrite the dS tile: the copy must have read it
+        tma_store_wait_read();
+        umma_commit(acc_done);
       }
-      if (store_ds) tma_store_wait_all();
+      tma_store_wait_all();
     }
   } else {
     const int r = threadIdx.x & 127, h = threadIdx.x >> 7;
@@ -509,21 +472,18 @@ tc_bwd_ac_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     fence_proxy_async();
     mbar_arrive_warp(small_full);
     // the in-place dQ pass rescales the dS tiles by the same power of two
-    if (MODE == kModeA && sc_out && threadIdx.x == 0) sc_out[bh] = sc;
+    if (sc_out && threadIdx.x == 0) sc_out[bh] = sc;
     const int c0 = h * HC;
-    Segments sg(sch.seg_N, m);
     bool alive = true;
     for (int i = 0; i < count; ++i) {
-      const int b = (MODE == kModeC) ? (i & 1) : 0;
-      const uint32_t ph = (MODE == kModeC) ? ((i >> 1) & 1) : (i & 1);
       const int64_t row = (int64_t)(tile0 + i) * kTile + r;
       const bool valid = row < sch.N;
       const float lse = valid ? lse1[bh * sch.N + row] * kLog2e : 0.f;
-      if (!mbar_wait(sdp_full + b, ph, ab, 0x1600 + i)) { alive = false; break; }
+      if (!mbar_wait(sdp_full, i & 1, ab, 0x1600 + i)) { alive = false; break; }
       __syncwarp();
       tc_fence_after();
       float p[HC], g[HC];
-      const uint32_t t_s = tmem_base + b * 2 * MP + lane_base;
+      const uint32_t t_s = tmem_base + lane_base;
       ld_cols<HC>(t_s + c0, p);
       ld_cols<HC>(t_s + MP + c0, g);
       tmem_ld_wait();
@@ -534,59 +494,22 @@ tc_bwd_ac_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         d4[j & 3] = fmaf(p[j], g[j], d4[j & 3]);
       }
       const float dpart = (d4[0] + d4[1]) + (d4[2] + d4[3]);
-      if (MODE == kModeA) {
-        // the previous tile's P / dS are still being read by its accumulation MMAs
-        if (i > 0 && !mbar_wait(acc_done, (i - 1) & 1, ab, 0x1700 + i)) { alive = false; break; }
-        __syncwarp();
-      } else {
-        if (threadIdx.x == 0) tma_store_wait_read();   // staging of the previous dQ tile shares s_ds
-      }
+      // the previous tile's P / dS are still being read by its accumulation MMAs and its dS copy
+      if (i > 0 && !mbar_wait(acc_done, (i - 1) & 1, ab, 0x1700 + i)) { alive = false; break; }
+      __syncwarp();
       s_x[h * kTile + r] = dpart;
       named_barrier(1, kComputeThreads);
       const float d1 = dpart + s_x[(h ^ 1) * kTile + r];
-      if (MODE == kModeA) {
-        named_barrier(1, kComputeThreads);   // exchange words live in the head of the P tile
-        store_cols<T, HC>(s_p, r, c0, p);
-      }
+      named_barrier(1, kComputeThreads);   // exchange words live in the head of the P tile
+      store_cols<T, HC>(s_p, r, c0, p);
 #pragma unroll
       for (int j = 0; j < HC; ++j) g[j] = p[j] * (g[j] - d1);
       store_cols<T, HC>(s_ds, r, c0, g);
       fence_proxy_async();
       tc_fence_before();
-      mbar_arrive_warp(pds_full + b);
-
-      if (MODE == kModeC) {
-        if (!mbar_wait(acc_done + b, ph, ab, 0x1800 + i)) { alive = false; break; }
-        __syncwarp();
-        tc_fence_after();
-        float o[HD];
-        ld_cols<HD>(tmem_base + b * 2 * MP + lane_base + h * HD, o);
-        tmem_ld_wait();
-        tc_fence_before();
-        mbar_arrive_warp(o_free + b);
-        const int l = valid ? sg.landmark_of(sch.row_offset + row) : 0;
-        const float4* add = reinterpret_cast<const float4*>(rows_q + (bh * m + l) * D + h * HD);
-        const float mul = sc * kLn2;
-#pragma unroll
-        for (int j = 0; j < HD; j += 4) {
-          const float4 a = add[j >> 2];
-          o[j + 0] = fmaf(o[j + 0], mul, a.x); o[j + 1] = fmaf(o[j + 1], mul, a.y);
-          o[j + 2] = fmaf(o[j + 2], mul, a.z); o[j + 3] = fmaf(o[j + 3], mul, a.w);
-        }
-        // acc_done means the dQ product has finished reading the dS tile: reuse it as staging
-        store_cols<T, HD>(s_ds, r, h * HD, o);
-        fence_proxy_async();
-        named_barrier(1, kComputeThreads);
-        if (threadIdx.x == 0) {
-          for (int kb = 0; kb < KBD; ++kb)
-            tma_store_3d(&tm_dq, s_ds + kb * (kTile * 128), kb * 64, (tile0 + i) * kTile, (int)bh);
-          tma_store_commit();
-        }
-      }
+      mbar_arrive_warp(pds_full);
     }
-    if (MODE == kModeC) {
-      if (threadIdx.x == 0) tma_store_wait_all();
-    } else if (alive && mbar_wait(acc_done, (count - 1) & 1, ab, 0x1900)) {
+    if (alive && mbar_wait(acc_done, (count - 1) & 1, ab, 0x1900)) {
       __syncwarp();
       tc_fence_after();
       // 128-row accumulator: TMEM lane = row.  Quarters 0, 1 hold the dstep2 rows (columns

@@ -91,7 +91,12 @@ typedef struct fnb_fwd_args {
 /* Backward.  Replaces nystrom_bwd + run_nystrom_bwd_impl (csrc/flash_nystrom.cu:177-415,
  * csrc/flash_nystrom_kernels.cu:313-391), including the cuBLAS + CUDA-graph
  * Newton-Schulz backward (csrc/kernels/backward/kernel2_inv_bwd.cu:794-1058).
- * dq, dk, dv are written exactly once each; they need not be zeroed. */
+ * dq, dk, dv need not be zeroed and must not alias any input.  dv is written once; on the
+ * tensor-core path (16-bit dtypes, head_dim 64, num_landmarks <= 64) dq and dk first hold the
+ * 16-bit softmax-Jacobian tiles of their rows and are turned into the gradients in place by the
+ * last kernel of the call, so their contents are defined only when the call's work on `stream`
+ * has completed.  Kernels of one call may also run on a library-owned side stream, forked from
+ * and joined back into `stream` with events (capturable into a CUDA graph). */
 typedef struct fnb_bwd_args {
   fnb_shape shape;
   const void* q;
