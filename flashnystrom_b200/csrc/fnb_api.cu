@@ -631,7 +631,7 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
     // reduction first, then the fused stage reads a single chunk.
     const float* fused_pa = partA_src;
     int fused_pa_chunks = partA_chunks;
-    if (fused_mid && partA_chunks > 4) {
+    if (fused_mid && partA_chunks > (side_ns ? 1 : 4)) {
       L.begin();
       reduce_chunks(partA_src, partA_chunks, 2 * p.m * p.D, w.partA_red);
       if (L.end("reduce_partA")) return L.status;
@@ -669,15 +669,12 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
       // what the column pass needs from the middle stage (dO3 -> D3, its 16-bit copy and scale, the
       // 16-bit Qt operand), on the caller's stream; the Newton-Schulz kernel, enqueued first, is
       // resident on its SMs by the time the column pass starts
-      BwdMid1Params mp;
-      mp.partA = fused_pa; mp.nchunk = fused_pa_chunks; mp.k2inv = a.k2_inv; mp.bmat = a.bmat;
-      mp.q_landmarks = a.q_landmarks; mp.dkt_a = nullptr; mp.dO3 = nullptr; mp.D3 = w.D3; mp.G = nullptr;
-      mp.m = p.m; mp.D = p.D; mp.dtype = a.shape.dtype; mp.MP = MP;
-      mp.qt16 = qt16; mp.qtT16 = nullptr; mp.do3n = do3n; mp.do3T = nullptr; mp.do3_scale = w.do3_scale;
-      mp.qt_mul = scale * tc::kLog2e; mp.qtT_mul = scale;
-      size_t sm = bwd_mid1_smem(p.m, p.D);
-      if (int rc = set_smem(bwd_mid1_kernel<4>, sm, max_smem, "bwd_mid1")) return rc;
-      bwd_mid1_kernel<4><<<(unsigned)p.BH, kThreads, sm, st>>>(mp);
+      ColpassOperandParams cp;
+      cp.dstep2 = fused_pa; cp.bh_stride = 2 * (int64_t)p.m * p.D; cp.k2inv = a.k2_inv; cp.bmat = a.bmat;
+      cp.q_landmarks = a.q_landmarks; cp.D3 = w.D3; cp.do3n = do3n; cp.do3_scale = w.do3_scale; cp.qt16 = qt16;
+      cp.qt_mul = scale * tc::kLog2e; cp.m = p.m; cp.dtype = a.shape.dtype;
+      if (int rc = set_smem(colpass_operands_kernel, (size_t)kColpassOperandSmem, max_smem, "colpass_operands")) return rc;
+      launch_pdl(colpass_operands_kernel, dim3((unsigned)p.BH), dim3(kThreads), (size_t)kColpassOperandSmem, st, cp);
     }
   } else {
     L.begin();

@@ -551,4 +551,136 @@ reduce_chunks_kernel(const float* in, int nchunk, int elems, float* out) {
   *reinterpret_cast<float4*>(out + bh * (size_t)elems + idx4) = s;
 }
 
+// ------------------------------------------------------------------------------------------
+// What the tensor-core column pass of the backward needs from the middle stage, for head_dim 64 and
+// m <= 64, when the pseudoinverse backward runs beside that pass instead of in front of it:
+//   dO3 = K2inv^T dstep2  ->  D3[l] = sum_d dO3[l][d] Bmat[l][d],
+//   do3n = dO3 / 2^e (16-bit, rows >= m zero) with 2^e >= max |dO3|,  qt16 = qt_mul * Qt (16-bit).
+// One CTA per slice: the three 64 x 64 inputs are fetched with every load in flight at once, the
+// product runs from shared memory on 4 x 4 register tiles (two 16-byte shared loads per 16 FMAs).
+struct ColpassOperandParams {
+  const float* dstep2;        // first [m][D] block of each slice; slices bh_stride floats apart
+  int64_t bh_stride;
+  const float* k2inv;         // [BH][m][m]
+  const float* bmat;          // [BH][m][D]
+  const float* q_landmarks;   // [BH][m][D]
+  float* D3;                  // [BH][m]
+  void* do3n;                 // [BH][64][D] 16-bit
+  float* do3_scale;           // [BH]
+  void* qt16;                 // [BH][64][D] 16-bit
+  float qt_mul;
+  int m, dtype;
+};
+constexpr int kColpassOperandSmem = 3 * 64 * 64 * (int)sizeof(float);
+
+__device__ __forceinline__ uint32_t pack2x16(int dtype, float a, float b) {
+  if (dtype == 1) {
+    __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+  }
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+__global__ void __launch_bounds__(kThreads) colpass_operands_kernel(ColpassOperandParams p) {
+  constexpr int D = 64;
+  extern __shared__ float sm[];
+  __shared__ float red[8];
+  float* Ki = sm;               // K2inv [k][l], later dO3 [l][d]
+  float* Ds = sm + 64 * 64;     // dstep2 [k][d]
+  float* Bm = sm + 2 * 64 * 64; // Bmat [l][d]
+  pdl_trigger();
+  pdl_wait();
+  const int64_t bh = blockIdx.x;
+  const int m = p.m, t = threadIdx.x;
+  const float* k2inv = p.k2inv + bh * m * m;
+  const float* ds = p.dstep2 + bh * p.bh_stride;
+  const float* bm = p.bmat + bh * (int64_t)m * D;
+  {
+    float4 a[4], b[4], c[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int e = (t + kThreads * i) * 4, r = e >> 6, col = e & 63;
+      a[i] = b[i] = c[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (r < m) {
+        b[i] = *reinterpret_cast<const float4*>(ds + r * D + col);
+        c[i] = *reinterpret_cast<const float4*>(bm + r * D + col);
+        if (m == 64) {
+          a[i] = *reinterpret_cast<const float4*>(k2inv + r * 64 + col);
+        } else {
+          a[i].x = col + 0 < m ? k2inv[r * m + col + 0] : 0.f;
+          a[i].y = col + 1 < m ? k2inv[r * m + col + 1] : 0.f;
+          a[i].z = col + 2 < m ? k2inv[r * m + col + 2] : 0.f;
+          a[i].w = col + 3 < m ? k2inv[r * m + col + 3] : 0.f;
+        }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int e = (t + kThreads * i) * 4;
+      *reinterpret_cast<float4*>(Ki + e) = a[i];
+      *reinterpret_cast<float4*>(Ds + e) = b[i];
+      *reinterpret_cast<float4*>(Bm + e) = c[i];
+    }
+  }
+  __syncthreads();
+  // dO3[l0..l0+3][d0..d0+3] = sum_k K2inv[k][l0..] dstep2[k][d0..]
+  const int l0 = (t >> 4) * 4, d0 = (t & 15) * 4;
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+#pragma unroll 8
+  for (int k = 0; k < 64; ++k) {
+    const float4 a = *reinterpret_cast<const float4*>(Ki + k * 64 + l0);
+    const float4 b = *reinterpret_cast<const float4*>(Ds + k * 64 + d0);
+    const float av[4] = {a.x, a.y, a.z, a.w}, bv[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+  }
+  float amax = 0.f, d3[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float4 x = *reinterpret_cast<const float4*>(Bm + (l0 + i) * 64 + d0);
+    d3[i] = acc[i][0] * x.x + acc[i][1] * x.y + acc[i][2] * x.z + acc[i][3] * x.w;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) amax = fmaxf(amax, fabsf(acc[i][j]));
+    // the 16 threads that share l0 are 16 consecutive lanes
+    for (int o = 8; o > 0; o >>= 1) d3[i] += __shfl_xor_sync(0xffffffffu, d3[i], o);
+  }
+  if ((t & 15) == 0)
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      if (l0 + i < m) p.D3[bh * m + l0 + i] = d3[i];
+  const float sc = pow2_scale(cta_max(amax, red));   // barriers inside: every read of Ki is done
+  const float inv_sc = 1.f / sc;
+  if (t == 0) p.do3_scale[bh] = sc;
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    *reinterpret_cast<float4*>(Ki + (l0 + i) * 64 + d0) =
+        make_float4(acc[i][0] * inv_sc, acc[i][1] * inv_sc, acc[i][2] * inv_sc, acc[i][3] * inv_sc);
+  __syncthreads();
+  // 16-bit copies: thread t packs row t >> 2, columns 16 (t & 3) .. +15 of both matrices
+  const int r = t >> 2, c0 = (t & 3) * 16;
+  const float* qrow = p.q_landmarks + bh * (int64_t)m * D + (int64_t)r * D + c0;
+  uint32_t w0[8], w1[8];
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    const float4 x = *reinterpret_cast<const float4*>(Ki + r * 64 + c0 + 4 * q);   // rows >= m are zero
+    float4 y = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (r < m) y = *reinterpret_cast<const float4*>(qrow + 4 * q);
+    w0[2 * q] = pack2x16(p.dtype, x.x, x.y); w0[2 * q + 1] = pack2x16(p.dtype, x.z, x.w);
+    w1[2 * q] = pack2x16(p.dtype, y.x * p.qt_mul, y.y * p.qt_mul);
+    w1[2 * q + 1] = pack2x16(p.dtype, y.z * p.qt_mul, y.w * p.qt_mul);
+  }
+  const size_t ob = ((size_t)bh * 64 + r) * D + c0;
+  uint4* o0 = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.do3n) + ob);
+  uint4* o1 = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.qt16) + ob);
+  o0[0] = make_uint4(w0[0], w0[1], w0[2], w0[3]); o0[1] = make_uint4(w0[4], w0[5], w0[6], w0[7]);
+  o1[0] = make_uint4(w1[0], w1[1], w1[2], w1[3]); o1[1] = make_uint4(w1[4], w1[5], w1[6], w1[7]);
+}
+
 }  // namespace fnb
