@@ -738,26 +738,19 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
     if (use_tc) {
       constexpr int D = 64, MPc = 64;
       L.begin();
-      {
-        const int md = p.m * p.D;
-        dim3 grid((unsigned)((md / 4 + 63) / 64), (unsigned)p.BH);
-        if (side_ns)   // follows the join with the side stream: an ordinary launch
-          dqt_reduce2_kernel<<<grid, kThreads, 0, st>>>(partB_src, partB_chunks, w.dqt_ns, (float*)nullptr, w.rows_q, p.m, p.D,
-                                                       seg_N, scale);
-        else
-          launch_pdl(dqt_reduce2_kernel, grid, dim3(kThreads), 0, st, partB_src, partB_chunks, w.dqt_ns, (float*)nullptr, w.rows_q,
-                     p.m, p.D, seg_N, scale);
-      }
-      if (L.end("dqt_rows")) return L.status;
-      L.begin();
       auto kern = tc::tc_rows_inplace_kernel<T, D, MPc>;
       size_t sm = tc::RowsSmem<D, MPc>::kBytes;
       if (int rc = set_smem(kern, sm, max_smem, "tc_bwd_c")) return rc;
-      // dQ from the dS1 tiles pass A left in dq, dK from the dS3' tiles the column pass left in dk
-      tc::RowsSide side_q{a.k_landmarks, w.rows_q, w.st_scale, tc::kLn2};
-      tc::RowsSide side_k{a.q_landmarks, w.rows_k, nullptr, exp2f(-(float)kshift) * tc::kLn2};
-      launch_pdl(kern, dim3(tgrid), dim3(tc::kTcThreads), sm, st, tm_dq, tm_dk, side_q, side_k, 2, scale * tc::kLog2e, sch,
-                 p.m, a.device_status);
+      // dQ from the dS1 tiles pass A left in dq, dK from the dS3' tiles the column pass left in dk.
+      // Every CTA first sums the column-pass partials of the landmark rows its own tiles touch
+      // (rows_q = s (dQt_ns + sum of partials) / len), so no separate reduction kernel runs.
+      tc::RowsSide side_q{a.k_landmarks, w.rows_q, w.st_scale, tc::kLn2, partB_src, w.dqt_ns, partB_chunks, scale};
+      tc::RowsSide side_k{a.q_landmarks, w.rows_k, nullptr, exp2f(-(float)kshift) * tc::kLn2, nullptr, nullptr, 0, 0.f};
+      if (side_ns)   // follows the join with the side stream: an ordinary launch
+        kern<<<tgrid, tc::kTcThreads, sm, st>>>(tm_dq, tm_dk, side_q, side_k, 2, scale * tc::kLog2e, sch, p.m, a.device_status);
+      else
+        launch_pdl(kern, dim3(tgrid), dim3(tc::kTcThreads), sm, st, tm_dq, tm_dk, side_q, side_k, 2, scale * tc::kLog2e, sch,
+                   p.m, a.device_status);
       if (L.end("tc_bwd_c")) return L.status;
       return 0;
     }

@@ -548,9 +548,17 @@ tc_bwd_a_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 // own.
 struct RowsSide {
   const float* landmarks;   // [BH][m][D] FP32: the landmark matrix the tile is multiplied by
-  const float* rows;        // [BH][m][D] FP32: per-landmark term added to every row of its segment
+  float* rows;              // [BH][m][D] FP32: per-landmark term added to every row of its segment
   const float* out_scale;   // [BH] or null: per-slice factor of the product
   float out_mul;            // constant factor of the product
+  // Optional: the CTA first forms the rows its own tiles need,
+  //   rows[l] = rows_scale / len(l) * (base[l] + sum over chunks of part[chunk][l]),
+  // (chunks in ascending order) and stores them into `rows`; CTAs that share a landmark store
+  // identical values.  part == null: `rows` is complete on entry.
+  const float* part;        // [BH][nchunk][m][D]
+  const float* base;        // [BH][m][D]
+  int nchunk;
+  float rows_scale;
 };
 
 template <int D, int MP>
@@ -688,6 +696,25 @@ tc_rows_inplace_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_co
     uint8_t* my_out = s_out + g * L::kOut;
     const bool leader = r == 0;
     Segments sg(sch.seg_N, m);
+    if (side_a.part && count > 0) {
+      // the landmark rows of this CTA's tiles, from the column-pass partials
+      const int64_t first = sch.row_offset + (int64_t)tile0 * kTile;
+      const int64_t last = sch.row_offset + min((int64_t)(tile0 + count) * kTile, sch.N) - 1;
+      const int l_lo = sg.landmark_of(first), nl = sg.landmark_of(last) - l_lo + 1;
+      const int md = m * D;
+      for (int item = threadIdx.x; item < nl * (D / 4); item += kComputeThreads) {
+        const int l = l_lo + item / (D / 4), d = (item % (D / 4)) * 4;
+        const float* src = side_a.part + bh * (int64_t)side_a.nchunk * md + l * D + d;
+        float4 acc = *reinterpret_cast<const float4*>(side_a.base + bh * md + l * D + d);
+        for (int c = 0; c < side_a.nchunk; ++c) {
+          const float4 x = *reinterpret_cast<const float4*>(src + (int64_t)c * md);
+          acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
+        }
+        const float f = side_a.rows_scale / (float)sg.len(l);
+        *reinterpret_cast<float4*>(side_a.rows + bh * md + l * D + d) = make_float4(acc.x * f, acc.y * f, acc.z * f, acc.w * f);
+      }
+      named_barrier(3, kComputeThreads);   // the stores above are visible to the CTA's epilogue reads
+    }
     for (int i = g; i < total; i += 2) {
       const int s = i % kStages;
       const uint32_t par = (uint32_t)(i / kStages) & 1u;
