@@ -33,6 +33,8 @@ SHAPES = [
     (1, 2, 130, 32, 8, 3, 1e3),
     (1, 1, 4096, 64, 64, 6, 0.0),
     (1, 3, 200, 16, 5, 10, 0.0),
+    # more slices than a quarter of the SMs: the backward runs without its side stream
+    (5, 8, 384, 64, 24, 6, 0.0),
 ]
 
 
