@@ -746,11 +746,10 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
       // (rows_q = s (dQt_ns + sum of partials) / len), so no separate reduction kernel runs.
       tc::RowsSide side_q{a.k_landmarks, w.rows_q, w.st_scale, tc::kLn2, partB_src, w.dqt_ns, partB_chunks, scale};
       tc::RowsSide side_k{a.q_landmarks, w.rows_k, nullptr, exp2f(-(float)kshift) * tc::kLn2, nullptr, nullptr, 0, 0.f};
-      if (side_ns)   // follows the join with the side stream: an ordinary launch
-        kern<<<tgrid, tc::kTcThreads, sm, st>>>(tm_dq, tm_dk, side_q, side_k, 2, scale * tc::kLog2e, sch, p.m, a.device_status);
-      else
-        launch_pdl(kern, dim3(tgrid), dim3(tc::kTcThreads), sm, st, tm_dq, tm_dk, side_q, side_k, 2, scale * tc::kLog2e, sch,
-                   p.m, a.device_status);
+      // (after the join with the side stream the event wait stays a full dependency; only the
+      // dependency on the column pass is the programmatic one, as for the combine step of the forward)
+      launch_pdl(kern, dim3(tgrid), dim3(tc::kTcThreads), sm, st, tm_dq, tm_dk, side_q, side_k, 2, scale * tc::kLog2e, sch,
+                 p.m, a.device_status);
       if (L.end("tc_bwd_c")) return L.status;
       return 0;
     }
