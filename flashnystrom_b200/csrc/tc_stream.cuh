@@ -442,9 +442,6 @@ tc_bwd_a_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         // the dS tile as it is -> dQ tile of the same rows
         tma_store_3d(&tm_dq, s_ds, 0, (tile0 + i) * kTile, (int)bh);
         tma_store_commit();
-        // S / dP of tile i are consumed: start the next tile's scores before this tile's
-        // accumulation so that the compute warps find them ready
-        if (i + 1 < count && !front(i + 1)) break;
         tc_fence_after();
         const int st = i & 1;
         // One 128 x 128 accumulator for both sums: [P | dS]^T [Q | dO] (both operands MN-major,
@@ -455,7 +452,10 @@ tc_bwd_a_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         for (int k = 0; k < kTile / 16; ++k)
           umma(tmem_base + 2 * MP, smem_desc_sw128(a_p + k * 2048, L::kP, 1024),
                smem_desc_sw128(smem_u32(s_q + st * L::kIn) + k * 2048, 2 * L::kIn, 1024), idesc_acc2, (i > 0 || k > 0));
+        // the accumulation goes first: its commit frees the (Q, dO) stage, and the pass is bound by
+        // how early the next load is issued; then the scores of the next tile
         umma_commit(in_empty + st);
+        if (i + 1 < count && !front(i + 1)) break;
         // acc_done lets the compute warps overwrite the dS tile: the copy must have read it
         tma_store_wait_read();
         umma_commit(acc_done);
