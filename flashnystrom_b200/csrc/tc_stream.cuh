@@ -439,9 +439,6 @@ tc_bwd_a_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       ok = ok && front(0);
       for (int i = 0; ok && i < count; ++i) {
         if (!mbar_wait(pds_full, i & 1, ab, 0x1400 + i)) break;
-        // the dS tile as it is -> dQ tile of the same rows
-        tma_store_3d(&tm_dq, s_ds, 0, (tile0 + i) * kTile, (int)bh);
-        tma_store_commit();
         tc_fence_after();
         const int st = i & 1;
         // One 128 x 128 accumulator for both sums: [P | dS]^T [Q | dO] (both operands MN-major,
@@ -455,6 +452,9 @@ tc_bwd_a_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         // the accumulation goes first: its commit frees the (Q, dO) stage, and the pass is bound by
         // how early the next load is issued; then the scores of the next tile
         umma_commit(in_empty + st);
+        // the dS tile as it is -> dQ tile of the same rows
+        tma_store_3d(&tm_dq, s_ds, 0, (tile0 + i) * kTile, (int)bh);
+        tma_store_commit();
         if (i + 1 < count && !front(i + 1)) break;
         // acc_done lets the compute warps overwrite the dS tile: the copy must have read it
         tma_store_wait_read();
