@@ -901,8 +901,6 @@ tc_bwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
         umma_commit(v_empty);
         umma_commit(sdp_full);
         if (!mbar_wait(pds_full, i & 1, ab, 0x2400 + i)) break;
-        tma_store_3d(&tm_dk, s_ds, 0, (tile0 + i) * kTile, (int)bh);
-        tma_store_commit();
         tc_fence_after();
 #pragma unroll
         for (int k = 0; k < MP / 16; ++k)
@@ -911,6 +909,10 @@ tc_bwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
         for (int k = 0; k < kTile / 16; ++k)
           umma(tmem_acc, mndesc(a_ds, k), mndesc(a_k, k), idesc_acc, (i > 0 || k > 0));
         umma_commit(k_empty + st);
+        // the dS' tile as it is -> dK tile of the same rows (after the products: their commit
+        // frees the K stage)
+        tma_store_3d(&tm_dk, s_ds, 0, (tile0 + i) * kTile, (int)bh);
+        tma_store_commit();
         // out_full lets the compute warps move on to the next dS' tile: the copy must have read it
         tma_store_wait_read();
         umma_commit(out_full);
