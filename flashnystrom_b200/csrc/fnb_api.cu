@@ -317,6 +317,26 @@ static bool ns_on_tensor_cores(uint32_t flags) {
   return !env_off && !(flags & FNB_FLAG_FORCE_GENERIC);
 }
 
+// How the streaming passes hand data to one another through the L2 cache (bit mask; FNB_L2 in
+// the environment at load overrides the default, kept for A/B measurements):
+//   1  tile order: the output pass, the first backward row pass and the backward column pass walk
+//      their tiles strided, and a pass that re-reads what its predecessor touched walks backwards
+//   2  evict-first hints on everything that is read or written for the last time
+//   4  the in-place pass finishes dK (whose parked tiles the column pass has just written) before dQ
+//   8  the pooling pass reads K with ordinary loads (it is re-read by the column pass), Q streaming
+//  16  evict-last hints on what the next pass of the chain reads back (K in pooling is not a TMA
+//      load and keeps its ordinary priority)
+//  32  the forward column pass walks its tiles strided too
+constexpr int kL2Default = 0;
+static int l2_mode() {
+  static const int mode = [] {
+    const char* e = getenv("FNB_L2");
+    return e ? atoi(e) : kL2Default;
+  }();
+  return mode;
+}
+static int hint_bits(int in0, int in1, int out0, int out1) { return in0 | (in1 << 2) | (out0 << 4) | (out1 << 6); }
+
 template <class T>
 static int forward_impl(const fnb_fwd_args& a, const Plan& p, const FwdWs& w, int max_smem, int sms,
                         cudaStream_t st, bool allow_inner_fork, const SpCtx& S = SpCtx()) {
@@ -331,6 +351,13 @@ static int forward_impl(const fnb_fwd_args& a, const Plan& p, const FwdWs& w, in
   sch.seg_N = seg_N; sch.row_offset = row_offset;
   const int lmC = S.on() ? 1 : p.lm_chunks;
   float* land = S.on() ? S.xfer : w.land_partial;
+  const int l2 = l2_mode();
+  const int ef = (l2 & 2) ? 1 : 0, el = (l2 & 16) ? 2 : 0;
+  tc::TcSched sch_fb = sch, sch_fc = sch;
+  sch_fb.order = (l2 & 32) ? tc::kOrderStrided : 0;
+  sch_fb.hint = hint_bits(ef, ef, 0, 0);                 // K (left in L2 by the pooling pass) and V die here
+  sch_fc.order = (l2 & 1) ? tc::kOrderStrided : 0;
+  sch_fc.hint = hint_bits(el, 0, ef, 0);                 // Q is read again by the backward; O is not
   const int nchunk_b = use_tc ? sch.nchunk : p.nchunk;
   const size_t md_all = (size_t)p.BH * p.m * p.D, m_all = (size_t)p.BH * p.m;
 
@@ -338,7 +365,7 @@ static int forward_impl(const fnb_fwd_args& a, const Plan& p, const FwdWs& w, in
     L.begin();
     int64_t grid = std::min<int64_t>(2 * p.BH * p.m * lmC, (int64_t)sms * 4);
     launch_pdl(landmark_partial_kernel<T>, dim3((unsigned)grid), dim3(kThreads), 0, st, 
-        (const T*)a.q, (const T*)a.k, land, p.BH, p.N, p.D, p.m, lmC, seg_N, row_offset);
+        (const T*)a.q, (const T*)a.k, land, p.BH, p.N, p.D, p.m, lmC, seg_N, row_offset, (l2 & 8) ? 0 : 1);
     if (L.end("landmark_partial")) return L.status;
   }
   if (S.stage == 0) return 0;
@@ -419,7 +446,7 @@ static int forward_impl(const fnb_fwd_args& a, const Plan& p, const FwdWs& w, in
       if (int rc = set_smem(kern, smem, max_smem, "tc_fwd_b")) return rc;
       launch_pdl(kern, dim3((unsigned)(p.BH * sch.nchunk)), dim3(tc::kTcThreads), smem, st,
           tm_k, tm_v, tm_qt, fused_landmarks ? land : (const float*)nullptr, lmC, p.BH, scale, w.part_acc, w.part_max,
-          w.part_sum, sch, p.m, a.device_status);
+          w.part_sum, sch_fb, p.m, a.device_status);
       if (L.end("tc_fwd_b")) return L.status;
     }
   }
@@ -497,7 +524,7 @@ static int forward_impl(const fnb_fwd_args& a, const Plan& p, const FwdWs& w, in
       auto kern = tc::tc_fwd_c_kernel<T, D, MPc>;
       size_t smem = tc::FwdCSmem<D, MPc>::kBytes;
       if (int rc = set_smem(kern, smem, max_smem, "tc_fwd_c")) return rc;
-      launch_pdl(kern, dim3((unsigned)(p.BH * sch.nchunk)), dim3(tc::kTcThreads), smem, st, tm_q, tm_o, a.k_landmarks, a.step2, a.lse1, sch,
+      launch_pdl(kern, dim3((unsigned)(p.BH * sch.nchunk)), dim3(tc::kTcThreads), smem, st, tm_q, tm_o, a.k_landmarks, a.step2, a.lse1, sch_fc,
                                                                       p.m, scale, a.device_status);
       if (L.end("tc_fwd_c")) return L.status;
       return 0;
@@ -543,6 +570,14 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
   }
   int kshift = 0;
   while ((int64_t(2) << kshift) <= seg_N && kshift < 14) ++kshift;   // floor(log2 N), at most 14
+  const int l2 = l2_mode();
+  const int ef = (l2 & 2) ? 1 : 0, el = (l2 & 16) ? 2 : 0;
+  const int strided = (l2 & 1) ? tc::kOrderStrided : 0;
+  tc::TcSched sch_a = sch, sch_c = sch;
+  sch_a.order = strided ? (strided | tc::kOrderDescending) : 0;   // starts on the end of Q the output pass left in L2
+  sch_a.hint = hint_bits(ef, ef, el, 0);                          // Q, dO die here; the parked dS1 tiles are read back
+  sch_b.order = strided;
+  sch_b.hint = hint_bits(ef, ef, el, ef);                         // K, V die here, dV is final; parked dS3' tiles are read back
 
   StreamParams sp;
   memset(&sp, 0, sizeof(sp));
@@ -586,7 +621,7 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
       size_t sm = tc::BwdASmem<D, MPc>::kBytes;
       if (int rc = set_smem(kern, sm, max_smem, "tc_bwd_a")) return rc;
       launch_pdl(kern, dim3(tgrid), dim3(tc::kTcThreads), sm, st, tm_q, tm_g, tm_dq, a.k_landmarks, a.step2, a.lse1,
-                 w.partA, w.st_scale, sch, p.m, scale, a.device_status);
+                 w.partA, w.st_scale, sch_a, p.m, scale, a.device_status);
       if (L.end("tc_bwd_a")) return L.status;
     }
   }
@@ -723,6 +758,9 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
     if (L.end("gen_bwd_b")) return L.status;
   }
   if (S.on()) {
+    // the Newton-Schulz kernel on the side stream reads its (dstep2, dKt) input from the transfer
+    // buffer that the reduction below overwrites: wait for it first
+    fork.join();
     L.begin();
     reduce_chunks(w.partB, nchunk_colpass, p.m * p.D, S.xfer);
     if (L.end("reduce_partB")) return L.status;
@@ -744,12 +782,20 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
       // dQ from the dS1 tiles pass A left in dq, dK from the dS3' tiles the column pass left in dk.
       // Every CTA first sums the column-pass partials of the landmark rows its own tiles touch
       // (rows_q = s (dQt_ns + sum of partials) / len), so no separate reduction kernel runs.
-      tc::RowsSide side_q{a.k_landmarks, w.rows_q, w.st_scale, tc::kLn2, partB_src, w.dqt_ns, partB_chunks, scale};
-      tc::RowsSide side_k{a.q_landmarks, w.rows_k, nullptr, exp2f(-(float)kshift) * tc::kLn2, nullptr, nullptr, 0, 0.f};
+      // The dQ side keeps contiguous runs of tiles (a CTA sums the partials of the landmarks its own
+      // run touches); the dK side follows the column pass backwards.
+      tc::RowsSide side_q{a.k_landmarks, w.rows_q, w.st_scale, tc::kLn2, partB_src, w.dqt_ns, partB_chunks, scale, 0};
+      tc::RowsSide side_k{a.q_landmarks, w.rows_k, nullptr, exp2f(-(float)kshift) * tc::kLn2, nullptr, nullptr, 0, 0.f,
+                          ((l2 & 4) ? tc::kOrderDescending : 0) | (((l2 & 4) && strided) ? tc::kOrderStrided : 0)};
+      sch_c.hint = hint_bits(ef, ef, ef, ef);   // parked tiles are dead once read, dQ / dK are final
       // (after the join with the side stream the event wait stays a full dependency; only the
       // dependency on the column pass is the programmatic one, as for the combine step of the forward)
-      launch_pdl(kern, dim3(tgrid), dim3(tc::kTcThreads), sm, st, tm_dq, tm_dk, side_q, side_k, 2, scale * tc::kLog2e, sch,
-                 p.m, a.device_status);
+      if (l2 & 4)
+        launch_pdl(kern, dim3(tgrid), dim3(tc::kTcThreads), sm, st, tm_dk, tm_dq, side_k, side_q, 2, scale * tc::kLog2e, sch_c,
+                   p.m, a.device_status);
+      else
+        launch_pdl(kern, dim3(tgrid), dim3(tc::kTcThreads), sm, st, tm_dq, tm_dk, side_q, side_k, 2, scale * tc::kLog2e, sch_c,
+                   p.m, a.device_status);
       if (L.end("tc_bwd_c")) return L.status;
       return 0;
     }
@@ -1147,10 +1193,11 @@ int fnb_pinv_backward_noalloc(int64_t bh, int32_t m, int32_t J, float kappa, con
   if (!k2 || !ns_iterates || !d_k2_inv || !d_k2) return fail(FNB_ERR_INVALID_ARGUMENT, "NULL tensor pointer");
   DeviceGuard g(device);
   if (!g.ok) return fail(FNB_ERR_CUDA, "cannot select CUDA device %d", device);
+  int max_smem = 0, cc = 0, sms = 0;
+  if (int rc = device_limits(device, &max_smem, &cc, &sms)) return rc;
   float* scratch = nullptr;
   if (int rc = noalloc_scratch(device, &scratch)) return rc;
-  FNB_CUDA(cudaFuncSetAttribute(ns::ns_pinv_bwd_debug_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                (int)ns::kBwdSmem));
+  if (int rc = set_smem(ns::ns_pinv_bwd_debug_kernel, ns::kBwdSmem, max_smem, "ns_pinv_bwd")) return rc;
   // Nothing in the scratch has to start at zero: with the ridge each slice's (m x m) block is
   // fully written (G^T Z_J) before it is read back; without the ridge it is not touched.
   ns::ns_pinv_bwd_debug_kernel<<<(unsigned)bh, kThreads, ns::kBwdSmem, (cudaStream_t)stream>>>(

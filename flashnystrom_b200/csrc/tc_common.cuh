@@ -124,6 +124,41 @@ __device__ __forceinline__ void tma_store_3d(const CUtensorMap* m, const void* s
                ::"l"(m), "r"(smem_u32(src)), "r"(c0), "r"(c1), "r"(c2)
                : "memory");
 }
+// L2 eviction-priority policies for TMA copies.  A policy is a 64-bit register value made by
+// createpolicy; 0 stands for "no hint" in the *_h wrappers below.
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_last() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+// Two bits per operand slot of a kernel (slot 0, 1: its streamed inputs; 2, 3: its streamed
+// outputs): 0 = no hint, 1 = evict first (data nobody reads again soon), 2 = evict last (data the
+// next kernel of the chain reads back).
+__device__ __forceinline__ uint64_t l2_policy_of(int hint, int slot) {
+  const int h = (hint >> (2 * slot)) & 3;
+  return h == 1 ? l2_policy_evict_first() : h == 2 ? l2_policy_evict_last() : 0ull;
+}
+__device__ __forceinline__ void tma_load_3d_h(void* dst, const CUtensorMap* m, uint64_t* bar, int c0, int c1,
+                                              int c2, uint64_t pol) {
+  if (pol == 0) { tma_load_3d(dst, m, bar, c0, c1, c2); return; }
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+      " [%0], [%1, {%3, %4, %5}], [%2], %6;"
+      ::"r"(smem_u32(dst)), "l"(m), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "l"(pol)
+      : "memory");
+}
+__device__ __forceinline__ void tma_store_3d_h(const CUtensorMap* m, const void* src, int c0, int c1, int c2,
+                                               uint64_t pol) {
+  if (pol == 0) { tma_store_3d(m, src, c0, c1, c2); return; }
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group.L2::cache_hint [%0, {%2, %3, %4}], [%1], %5;"
+               ::"l"(m), "r"(smem_u32(src)), "r"(c0), "r"(c1), "r"(c2), "l"(pol)
+               : "memory");
+}
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // wait until the source shared memory of all committed stores may be overwritten
 __device__ __forceinline__ void tma_store_wait_read() {

@@ -66,6 +66,8 @@ inline TcSched make_sched(int64_t BH, int64_t N, int slots) {
   s.N = N;
   s.seg_N = N;
   s.row_offset = 0;
+  s.order = 0;
+  s.hint = 0;
   int64_t tiles = (N + kTile - 1) / kTile;
   int64_t want = slots / BH;            // floor: BH * want <= slots
   if (want > tiles) want = tiles;

@@ -36,7 +36,15 @@ struct TcSched {
   int64_t seg_N;         // sequence length the landmark segments are defined on (== N unless the
   int64_t row_offset;    //   sequence is sharded over ranks: then the global length and this
                          //   rank's first global row)
+  // Order in which a CTA walks its tiles.  kOrderStrided: CTA c of a slice takes tiles c,
+  // c + nchunk, c + 2 nchunk, ... (all CTAs of a slice sweep one moving window of the tensor, so
+  // what the pass leaves in L2 is the end of every slice whatever nchunk is) instead of a
+  // contiguous run.  kOrderDescending: last tile first (a pass that starts where its predecessor
+  // in the stream ended finds that data still in L2).
+  int order;
+  int hint;              // L2 eviction hints, two bits per operand slot (tc_common.cuh: l2_policy_of)
 };
+constexpr int kOrderStrided = 1, kOrderDescending = 2;
 
 // NC consecutive FP32 TMEM columns of this thread's lane -> registers
 template <int NC>
@@ -112,16 +120,33 @@ __device__ __forceinline__ float pack_landmark_operands(uint8_t* tile_a, uint8_t
   return sc;
 }
 
-struct TileRange { int64_t bh; int chunk, tile0, count; };
-__device__ __forceinline__ TileRange tile_range(const TcSched& sch) {
+struct TileRange {
+  int64_t bh;
+  int chunk, first, step, count;
+  bool desc;
+  // i-th tile this CTA works on
+  __device__ __forceinline__ int tile(int i) const { return first + (desc ? count - 1 - i : i) * step; }
+  __device__ __forceinline__ int lowest() const { return first; }
+  __device__ __forceinline__ int highest() const { return first + (count - 1) * step; }
+};
+__device__ __forceinline__ TileRange tile_range(const TcSched& sch, int order) {
   TileRange t;
   t.bh = blockIdx.x / sch.nchunk;
   t.chunk = (int)(blockIdx.x - t.bh * sch.nchunk);
   const int total_tiles = (int)((sch.N + kTile - 1) / kTile);
-  t.tile0 = t.chunk * sch.tiles_per_chunk;
-  t.count = min(sch.tiles_per_chunk, total_tiles - t.tile0);
+  if (order & kOrderStrided) {
+    t.first = t.chunk;
+    t.step = sch.nchunk;
+    t.count = t.chunk < total_tiles ? (total_tiles - t.chunk + sch.nchunk - 1) / sch.nchunk : 0;
+  } else {
+    t.first = t.chunk * sch.tiles_per_chunk;
+    t.step = 1;
+    t.count = max(0, min(sch.tiles_per_chunk, total_tiles - t.first));
+  }
+  t.desc = (order & kOrderDescending) != 0;
   return t;
 }
+__device__ __forceinline__ TileRange tile_range(const TcSched& sch) { return tile_range(sch, sch.order); }
 
 // ------------------------------------------------------------------------------------------
 // Forward output pass:  O = softmax(Q Kt^T) step2, lse1.
@@ -171,7 +196,7 @@ tc_fwd_c_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const TileRange tr = tile_range(sch);
   const int64_t bh = tr.bh;
-  const int tile0 = tr.tile0, count = tr.count;
+  const int count = tr.count;
 
   if (threadIdx.x == 0) {
     mbar_init(small_full, kComputeThreads / 32);
@@ -197,13 +222,14 @@ tc_fwd_c_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     if (lane == 0) {
       tma_prefetch_desc(&tm_q);
       tma_prefetch_desc(&tm_o);
+      const uint64_t pol_q = l2_policy_of(sch.hint, 0);
       int armed = 0;
       for (int i = 0; i < count; ++i) {
         const int st = i & 1;
         if (!mbar_wait(q_empty + st, ((i >> 1) & 1) ^ 1, ab, 0x100 + i)) break;
         mbar_expect_tx(q_full + st, L::kQ);
         for (int kb = 0; kb < KBD; ++kb)
-          tma_load_3d(s_q + st * L::kQ + kb * (kTile * 128), &tm_q, q_full + st, kb * 64, (tile0 + i) * kTile, (int)bh);
+          tma_load_3d_h(s_q + st * L::kQ + kb * (kTile * 128), &tm_q, q_full + st, kb * 64, tr.tile(i) * kTile, (int)bh, pol_q);
         armed = i + 1;
       }
       if (ab.raised())   // let copies already in flight land before the shared memory is released
@@ -256,6 +282,7 @@ tc_fwd_c_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     mbar_arrive_warp(small_full);
     uint8_t* my_p = s_p + g * L::kP;
     const bool leader = r == 0;
+    const uint64_t pol_o = leader ? l2_policy_of(sch.hint, 2) : 0ull;
     const bool full_m = m == MP;
     for (int i = g; i < count; i += 2) {
       const uint32_t par = (uint32_t)(i >> 1) & 1u;
@@ -296,7 +323,7 @@ tc_fwd_c_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       tc_fence_before();
       mbar_arrive_warp(p_full + g);
       const float mul = osc / tot;
-      const int64_t row = (int64_t)(tile0 + i) * kTile + r;
+      const int64_t row = (int64_t)tr.tile(i) * kTile + r;
       if (row < sch.N) lse1[bh * sch.N + row] = (mx + log2f(tot)) * kLn2;
       // output product of the same tile
       if (!mbar_wait(o_full + g, par, ab, 0x700 + i)) break;
@@ -314,7 +341,7 @@ tc_fwd_c_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       named_barrier(1 + g, kGroup);
       if (leader) {
         for (int kb = 0; kb < KBD; ++kb)
-          tma_store_3d(&tm_o, my_p + kb * (kTile * 128), kb * 64, (tile0 + i) * kTile, (int)bh);
+          tma_store_3d_h(&tm_o, my_p + kb * (kTile * 128), kb * 64, tr.tile(i) * kTile, (int)bh, pol_o);
         tma_store_commit();
       }
     }
@@ -379,7 +406,7 @@ tc_bwd_a_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const TileRange tr = tile_range(sch);
   const int64_t bh = tr.bh;
-  const int tile0 = tr.tile0, count = tr.count;
+  const int count = tr.count;
 
   if (threadIdx.x == 0) {
     mbar_init(small_full, kComputeThreads / 32);
@@ -405,13 +432,14 @@ tc_bwd_a_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     if (lane == 0) {
       tma_prefetch_desc(&tm_q);
       tma_prefetch_desc(&tm_g);
+      const uint64_t pol_q = l2_policy_of(sch.hint, 0), pol_g = l2_policy_of(sch.hint, 1);
       int armed = 0;
       for (int i = 0; i < count; ++i) {
         const int st = i & 1;
         if (!mbar_wait(in_empty + st, ((i >> 1) & 1) ^ 1, ab, 0x1100 + i)) break;
         mbar_expect_tx(in_full + st, 2 * L::kIn);
-        tma_load_3d(s_q + st * L::kIn, &tm_q, in_full + st, 0, (tile0 + i) * kTile, (int)bh);
-        tma_load_3d(s_g + st * L::kIn, &tm_g, in_full + st, 0, (tile0 + i) * kTile, (int)bh);
+        tma_load_3d_h(s_q + st * L::kIn, &tm_q, in_full + st, 0, tr.tile(i) * kTile, (int)bh, pol_q);
+        tma_load_3d_h(s_g + st * L::kIn, &tm_g, in_full + st, 0, tr.tile(i) * kTile, (int)bh, pol_g);
         armed = i + 1;
       }
       if (ab.raised())
@@ -422,6 +450,7 @@ tc_bwd_a_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       constexpr uint32_t idesc_s = make_idesc<T>(kTile, MP, false, false);
       constexpr uint32_t idesc_acc2 = make_idesc<T>(128, 128, true, true);
       const uint32_t a_kt = smem_u32(s_kt), a_st = smem_u32(s_st), a_p = smem_u32(s_p);
+      const uint64_t pol_ds = l2_policy_of(sch.hint, 2);
       // S and dP of tile i
       auto front = [&](int i) -> bool {
         const int st = i & 1;
@@ -453,7 +482,7 @@ tc_bwd_a_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         // how early the next load is issued; then the scores of the next tile
         umma_commit(in_empty + st);
         // the dS tile as it is -> dQ tile of the same rows
-        tma_store_3d(&tm_dq, s_ds, 0, (tile0 + i) * kTile, (int)bh);
+        tma_store_3d_h(&tm_dq, s_ds, 0, tr.tile(i) * kTile, (int)bh, pol_ds);
         tma_store_commit();
         if (i + 1 < count && !front(i + 1)) break;
         // acc_done lets the compute warps overwrite the dS tile: the copy must have read it
@@ -476,7 +505,7 @@ tc_bwd_a_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const int c0 = h * HC;
     bool alive = true;
     for (int i = 0; i < count; ++i) {
-      const int64_t row = (int64_t)(tile0 + i) * kTile + r;
+      const int64_t row = (int64_t)tr.tile(i) * kTile + r;
       const bool valid = row < sch.N;
       const float lse = valid ? lse1[bh * sch.N + row] * kLog2e : 0.f;
       if (!mbar_wait(sdp_full, i & 1, ab, 0x1600 + i)) { alive = false; break; }
@@ -559,6 +588,7 @@ struct RowsSide {
   const float* base;        // [BH][m][D]
   int nchunk;
   float rows_scale;
+  int order;                // tile order of this side (kOrderStrided | kOrderDescending)
 };
 
 template <int D, int MP>
@@ -619,9 +649,9 @@ tc_rows_inplace_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_co
   static_assert((1 + 4 * kStages) * 8 + 8 <= 256, "barrier area");
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const TileRange tr = tile_range(sch);
-  const int64_t bh = tr.bh;
-  const int tile0 = tr.tile0, count = tr.count, total = nsides * tr.count;
+  const TileRange tra = tile_range(sch, side_a.order), trb = tile_range(sch, side_b.order);
+  const int64_t bh = tra.bh;
+  const int count = tra.count, total = count + (nsides > 1 ? trb.count : 0);
 
   if (threadIdx.x == 0) {
     mbar_init(small_full, kComputeThreads / 32);
@@ -647,14 +677,15 @@ tc_rows_inplace_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_co
     if (lane == 0) {
       tma_prefetch_desc(&tm_a);
       if (nsides > 1) tma_prefetch_desc(&tm_b);
+      const uint64_t pol_a = l2_policy_of(sch.hint, 0), pol_b = l2_policy_of(sch.hint, 1);
       int armed = 0;
       for (int i = 0; i < total; ++i) {
         const int s = i % kStages;
         const bool second = i >= count;
         if (!mbar_wait(in_empty + s, ((i / kStages) & 1) ^ 1, ab, 0x2100 + i)) break;
         mbar_expect_tx(in_full + s, L::kIn);
-        tma_load_3d(s_in + s * L::kIn, second ? &tm_b : &tm_a, in_full + s, 0,
-                    (tile0 + (second ? i - count : i)) * kTile, (int)bh);
+        tma_load_3d_h(s_in + s * L::kIn, second ? &tm_b : &tm_a, in_full + s, 0,
+                      (second ? trb.tile(i - count) : tra.tile(i)) * kTile, (int)bh, second ? pol_b : pol_a);
         armed = i + 1;
       }
       if (ab.raised())
@@ -695,31 +726,37 @@ tc_rows_inplace_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_co
     const float mul_b = nsides > 1 ? (side_b.out_scale ? side_b.out_scale[bh] : 1.f) * side_b.out_mul : 0.f;
     uint8_t* my_out = s_out + g * L::kOut;
     const bool leader = r == 0;
+    const uint64_t pol_oa = leader ? l2_policy_of(sch.hint, 2) : 0ull, pol_ob = leader ? l2_policy_of(sch.hint, 3) : 0ull;
     Segments sg(sch.seg_N, m);
-    if (side_a.part && count > 0) {
-      // the landmark rows of this CTA's tiles, from the column-pass partials
-      const int64_t first = sch.row_offset + (int64_t)tile0 * kTile;
-      const int64_t last = sch.row_offset + min((int64_t)(tile0 + count) * kTile, sch.N) - 1;
+    // the landmark rows of this CTA's tiles on a side whose rows still wait for the column-pass
+    // partials (all landmarks between its lowest and its highest tile)
+    auto presum = [&](const RowsSide& sd, const TileRange& t) {
+      if (!sd.part || t.count <= 0) return;
+      const int64_t first = sch.row_offset + (int64_t)t.lowest() * kTile;
+      const int64_t last = sch.row_offset + min((int64_t)(t.highest() + 1) * kTile, sch.N) - 1;
       const int l_lo = sg.landmark_of(first), nl = sg.landmark_of(last) - l_lo + 1;
       const int md = m * D;
       for (int item = threadIdx.x; item < nl * (D / 4); item += kComputeThreads) {
         const int l = l_lo + item / (D / 4), d = (item % (D / 4)) * 4;
-        const float* src = side_a.part + bh * (int64_t)side_a.nchunk * md + l * D + d;
-        float4 acc = *reinterpret_cast<const float4*>(side_a.base + bh * md + l * D + d);
-        for (int c = 0; c < side_a.nchunk; ++c) {
+        const float* src = sd.part + bh * (int64_t)sd.nchunk * md + l * D + d;
+        float4 acc = *reinterpret_cast<const float4*>(sd.base + bh * md + l * D + d);
+        for (int c = 0; c < sd.nchunk; ++c) {
           const float4 x = *reinterpret_cast<const float4*>(src + (int64_t)c * md);
           acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
         }
-        const float f = side_a.rows_scale / (float)sg.len(l);
-        *reinterpret_cast<float4*>(side_a.rows + bh * md + l * D + d) = make_float4(acc.x * f, acc.y * f, acc.z * f, acc.w * f);
+        const float f = sd.rows_scale / (float)sg.len(l);
+        *reinterpret_cast<float4*>(sd.rows + bh * md + l * D + d) = make_float4(acc.x * f, acc.y * f, acc.z * f, acc.w * f);
       }
+    };
+    presum(side_a, tra);
+    if (nsides > 1) presum(side_b, trb);
+    if (side_a.part || (nsides > 1 && side_b.part))
       named_barrier(3, kComputeThreads);   // the stores above are visible to the CTA's epilogue reads
-    }
     for (int i = g; i < total; i += 2) {
       const int s = i % kStages;
       const uint32_t par = (uint32_t)(i / kStages) & 1u;
       const bool second = i >= count;
-      const int tile = tile0 + (second ? i - count : i);
+      const int tile = second ? trb.tile(i - count) : tra.tile(i);
       const int64_t row = (int64_t)tile * kTile + r;
       const bool valid = row < sch.N;
       const int l = valid ? sg.landmark_of(sch.row_offset + row) : 0;
@@ -752,7 +789,7 @@ tc_rows_inplace_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_co
       fence_proxy_async();
       named_barrier(1 + g, kGroup);
       if (leader) {
-        tma_store_3d(second ? &tm_b : &tm_a, my_out, 0, tile * kTile, (int)bh);
+        tma_store_3d_h(second ? &tm_b : &tm_a, my_out, 0, tile * kTile, (int)bh, second ? pol_ob : pol_oa);
         tma_store_commit();
       }
     }
@@ -825,7 +862,7 @@ tc_bwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const TileRange tr = tile_range(sch);
   const int64_t bh = tr.bh;
-  const int tile0 = tr.tile0, count = tr.count;
+  const int count = tr.count;
 
   if (threadIdx.x == 0) {
     mbar_init(small_full, 1);
@@ -855,6 +892,7 @@ tc_bwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
     if (lane == 0) {
       tma_prefetch_desc(&tm_k);
       tma_prefetch_desc(&tm_v);
+      const uint64_t pol_k = l2_policy_of(sch.hint, 0), pol_v = l2_policy_of(sch.hint, 1);
       mbar_expect_tx(small_full, 2 * L::kOp);
       for (int kb = 0; kb < KBD; ++kb) {
         tma_load_2d(s_qt + kb * (MP * 128), &tm_qt, small_full, kb * 64, (int)(bh * MP));
@@ -866,11 +904,11 @@ tc_bwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
         if (!mbar_wait(k_empty + st, ((i >> 1) & 1) ^ 1, ab, 0x2100 + i)) break;
         mbar_expect_tx(k_full + st, L::kIn);
         for (int kb = 0; kb < KBD; ++kb)
-          tma_load_3d(s_k + st * L::kIn + kb * (kTile * 128), &tm_k, k_full + st, kb * 64, (tile0 + i) * kTile, (int)bh);
+          tma_load_3d_h(s_k + st * L::kIn + kb * (kTile * 128), &tm_k, k_full + st, kb * 64, tr.tile(i) * kTile, (int)bh, pol_k);
         if (!mbar_wait(v_empty, (i & 1) ^ 1, ab, 0x2180 + i)) { armed = -(i + 1); break; }
         mbar_expect_tx(v_full, L::kIn);
         for (int kb = 0; kb < KBD; ++kb)
-          tma_load_3d(s_v + kb * (kTile * 128), &tm_v, v_full, kb * 64, (tile0 + i) * kTile, (int)bh);
+          tma_load_3d_h(s_v + kb * (kTile * 128), &tm_v, v_full, kb * 64, tr.tile(i) * kTile, (int)bh, pol_v);
         armed = i + 1;
       }
       if (ab.raised()) {
@@ -886,6 +924,7 @@ tc_bwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
       constexpr uint32_t idesc_acc = make_idesc<T>(MP, D, true, true);
       const uint32_t a_qt = smem_u32(s_qt), a_do3 = smem_u32(s_do3), a_v = smem_u32(s_v), a_p = smem_u32(s_p),
                      a_ds = smem_u32(s_ds);
+      const uint64_t pol_ds = l2_policy_of(sch.hint, 2);
       bool ok = mbar_wait(small_full, 0, ab, 0x2200);
       for (int i = 0; ok && i < count; ++i) {
         const int st = i & 1;
@@ -911,7 +950,7 @@ tc_bwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
         umma_commit(k_empty + st);
         // the dS' tile as it is -> dK tile of the same rows (after the products: their commit
         // frees the K stage)
-        tma_store_3d(&tm_dk, s_ds, 0, (tile0 + i) * kTile, (int)bh);
+        tma_store_3d_h(&tm_dk, s_ds, 0, tr.tile(i) * kTile, (int)bh, pol_ds);
         tma_store_commit();
         // out_full lets the compute warps move on to the next dS' tile: the copy must have read it
         tma_store_wait_read();
@@ -925,6 +964,7 @@ tc_bwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
     const float dsc = do3_scale[bh];
     const float unshift = exp2f(-(float)kshift);
+    const uint64_t pol_dv = threadIdx.x == 0 ? l2_policy_of(sch.hint, 3) : 0ull;
     const int c0 = h * HC;
     Segments sg(sch.seg_N, m);
     if (threadIdx.x < MP) {
@@ -935,7 +975,7 @@ tc_bwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
     named_barrier(1, kComputeThreads);
     bool alive = true;
     for (int i = 0; i < count; ++i) {
-      const int64_t row = (int64_t)(tile0 + i) * kTile + r;
+      const int64_t row = (int64_t)tr.tile(i) * kTile + r;
       const bool valid = row < sch.N;
       if (!mbar_wait(sdp_full, i & 1, ab, 0x2600 + i)) { alive = false; break; }
       __syncwarp();
@@ -984,7 +1024,7 @@ tc_bwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
       named_barrier(1, kComputeThreads);
       if (threadIdx.x == 0) {
         for (int kb = 0; kb < KBD; ++kb)
-          tma_store_3d(&tm_dv, s_p + kb * (kTile * 128), kb * 64, (tile0 + i) * kTile, (int)bh);
+          tma_store_3d_h(&tm_dv, s_p + kb * (kTile * 128), kb * 64, tr.tile(i) * kTile, (int)bh, pol_dv);
         tma_store_commit();
       }
     }
@@ -1070,7 +1110,7 @@ tc_fwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const TileRange tr = tile_range(sch);
   const int64_t bh = tr.bh;
-  const int tile0 = tr.tile0, count = tr.count;
+  const int count = tr.count;
 
   if (threadIdx.x == 0) {
     mbar_init(small_full, land ? kComputeThreads / 32 : 1);
@@ -1106,6 +1146,7 @@ tc_fwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
     if (lane == 0) {
       tma_prefetch_desc(&tm_k);
       tma_prefetch_desc(&tm_v);
+      const uint64_t pol_k = l2_policy_of(sch.hint, 0), pol_v = l2_policy_of(sch.hint, 1);
       if (!land) {
         mbar_expect_tx(small_full, L::kQt);
         for (int kb = 0; kb < KBD; ++kb)
@@ -1117,12 +1158,12 @@ tc_fwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
         if (!mbar_wait(k_empty + st, ((i >> 1) & 1) ^ 1, ab, 0x3100 + i)) break;
         mbar_expect_tx(k_full + st, L::kIn);
         for (int kb = 0; kb < KBD; ++kb)
-          tma_load_3d(s_k + st * L::kIn + kb * (kTile * 128), &tm_k, k_full + st, kb * 64, (tile0 + i) * kTile, (int)bh);
+          tma_load_3d_h(s_k + st * L::kIn + kb * (kTile * 128), &tm_k, k_full + st, kb * 64, tr.tile(i) * kTile, (int)bh, pol_k);
         nk = i + 1;
         if (!mbar_wait(v_empty + st, ((i >> 1) & 1) ^ 1, ab, 0x3180 + i)) break;
         mbar_expect_tx(v_full + st, L::kIn);
         for (int kb = 0; kb < KBD; ++kb)
-          tma_load_3d(s_v + st * L::kIn + kb * (kTile * 128), &tm_v, v_full + st, kb * 64, (tile0 + i) * kTile, (int)bh);
+          tma_load_3d_h(s_v + st * L::kIn + kb * (kTile * 128), &tm_v, v_full + st, kb * 64, tr.tile(i) * kTile, (int)bh, pol_v);
         nv = i + 1;
       }
       if (ab.raised()) {
@@ -1197,7 +1238,7 @@ tc_fwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
     bool alive = true;
     for (int i = 0; i < count; ++i) {
       const int st = i & 1;
-      const int64_t row = (int64_t)(tile0 + i) * kTile + r;
+      const int64_t row = (int64_t)tr.tile(i) * kTile + r;
       const bool valid = row < sch.N;
       if (!mbar_wait(s_full + st, (i >> 1) & 1, ab, 0x3600 + i)) { alive = false; break; }
       __syncwarp();

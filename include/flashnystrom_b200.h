@@ -194,8 +194,12 @@ FNB_API int fnb_debug_pinv_backward(int64_t bh, int32_t m, int32_t newton_iter, 
                             int32_t device, void* stream);
 FNB_API size_t fnb_debug_pinv_workspace_bytes(int64_t bh, int32_t m);
 
-/* Gradient of the pseudoinverse for callers that must not allocate: same result as
- * fnb_debug_pinv_backward, but without a workspace argument.  It has no counterpart in the
+/* Gradient of the pseudoinverse for callers that must not allocate: what
+ * fnb_debug_pinv_backward computes, but without a workspace argument.  It always runs the FP32
+ * CUDA-core kernel (fnb_debug_pinv_backward prefers the tensor-core kernel for num_landmarks
+ * <= 64), so the two agree to FP32 rounding, not bit for bit; without the ridge the row of
+ * ||K2||_inf is decided by round-off (row sums of a softmax matrix tie at 1), so compare them
+ * after the softmax Jacobian, which removes that row-constant term.  It has no counterpart in the
  * reference.  It is meant for hosts whose device memory is handed out once at start-up and
  * then frozen - a plugin inside a serving process with a fixed memory plan, say - where a
  * cudaMalloc in the request path is forbidden (it may fail, and it stalls the device).  The

@@ -28,8 +28,18 @@ def test_noalloc_matches_workspace_entry_point_twice(cuda_device, kappa):
         _C.pinv_backward_noalloc(k2, iters, G, got, kappa)
         torch.cuda.synchronize()
         assert torch.isfinite(got).all(), f"call {call}"
-        # same kernel, same summation order: the tolerance of the other pinv tests is ample
-        err = float((got - want).abs().max() / want.abs().max())
+        # The entry point under test always runs the FP32 CUDA-core kernel, the ordinary one the
+        # tensor-core kernel for num_landmarks <= 64: they agree to FP32 rounding (the bar of the
+        # other pseudoinverse tests).  Without the ridge the argmax row of ||K2||_inf is decided
+        # by round-off (the row sums of a softmax matrix tie at 1); the term it steers is constant
+        # along a row and vanishes under the softmax Jacobian that always follows, so compare
+        # after that projection.
+        if kappa == 0.0:
+            jac = lambda d: k2 * (d - (d * k2).sum(-1, keepdim=True))
+            got_c, want_c = jac(got), jac(want)
+        else:
+            got_c, want_c = got, want
+        err = float((got_c - want_c).abs().max() / want_c.abs().max())
         assert err <= 5e-4, f"call {call}: rel_max {err}"
 
 
