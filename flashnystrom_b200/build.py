@@ -13,15 +13,16 @@ import sys
 PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 LIB_DIR = os.path.join(PKG, "lib")
-LIB_PATH = os.path.join(LIB_DIR, "libflashnystrom_b200.so")
+LIB_PATH = os.path.join(LIB_DIR, os.environ.get("FNB_LIB_NAME", "libflashnystrom_b200.so"))
 SOURCES = ["fnb_api.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-    "--use_fast_math" if False else "-DFNB_PRECISE_MATH",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "-shared",
-    "-Xptxas", "-v" if os.environ.get("FNB_PTXAS_VERBOSE") else "-O3",
 ]
+if os.environ.get("FNB_PTXAS_VERBOSE"):      # registers, spills, shared memory per kernel
+    NVCC_FLAGS += ["-Xptxas", "-v"]
+NVCC_FLAGS += os.environ.get("FNB_EXTRA_NVCC_FLAGS", "").split()   # e.g. -DFNB_NS_TRACE for a profiling build
 
 
 def _nvcc():

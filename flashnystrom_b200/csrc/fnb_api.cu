@@ -323,11 +323,11 @@ static bool ns_on_tensor_cores(uint32_t flags) {
 //      their tiles strided, and a pass that re-reads what its predecessor touched walks backwards
 //   2  evict-first hints on everything that is read or written for the last time
 //   4  the in-place pass finishes dK (whose parked tiles the column pass has just written) before dQ
-//   8  the pooling pass reads K with ordinary loads (it is re-read by the column pass), Q streaming
-//  16  evict-last hints on what the next pass of the chain reads back (K in pooling is not a TMA
-//      load and keeps its ordinary priority)
+//  16  evict-last hints on what the next pass of the chain reads back
 //  32  the forward column pass walks its tiles strided too
-constexpr int kL2Default = 0;
+// Measured on a B200 at B=1, H=16, N=65536 (ms per forward + backward): 0: 0.543, 7: 0.524,
+// 23: 0.526, 31: 0.530 (the in-place pass 102 -> 93 us, the first row pass 86 -> 83 us).
+constexpr int kL2Default = 7;
 static int l2_mode() {
   static const int mode = [] {
     const char* e = getenv("FNB_L2");
@@ -365,7 +365,7 @@ static int forward_impl(const fnb_fwd_args& a, const Plan& p, const FwdWs& w, in
     L.begin();
     int64_t grid = std::min<int64_t>(2 * p.BH * p.m * lmC, (int64_t)sms * 4);
     launch_pdl(landmark_partial_kernel<T>, dim3((unsigned)grid), dim3(kThreads), 0, st, 
-        (const T*)a.q, (const T*)a.k, land, p.BH, p.N, p.D, p.m, lmC, seg_N, row_offset, (l2 & 8) ? 0 : 1);
+        (const T*)a.q, (const T*)a.k, land, p.BH, p.N, p.D, p.m, lmC, seg_N, row_offset);
     if (L.end("landmark_partial")) return L.status;
   }
   if (S.stage == 0) return 0;
@@ -1205,6 +1205,14 @@ int fnb_pinv_backward_noalloc(int64_t bh, int32_t m, int32_t J, float kappa, con
   FNB_CUDA(cudaPeekAtLastError());
   return 0;
 }
+
+#ifdef FNB_TC_TRACE
+// profiling builds only: the per-tile timestamps of the traced CTA of the last tc_fwd_b launch
+__attribute__((visibility("default"))) int fnb_debug_tc_trace(long long* out, int cta) {
+  if (cta >= 0) { cudaMemcpyToSymbol(tc::g_tc_trace_cta, &cta, sizeof(int)); return 0; }
+  return cudaMemcpyFromSymbol(out, tc::g_tc_trace, sizeof(long long) * 8 * 256) == cudaSuccess ? 0 : -1;
+}
+#endif
 
 int fnb_set_profiling(int mode) {
   int prev = g_profile;

@@ -25,6 +25,18 @@ constexpr int kTcThreads = 320;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 
+// Optional per-tile timestamps of one CTA (profiling builds only: -DFNB_TC_TRACE).
+#ifdef FNB_TC_TRACE
+__device__ long long g_tc_trace[8][256];
+__device__ int g_tc_trace_cta = 150;
+#define TC_TRACE(role, idx)                                                                    \
+  do {                                                                                         \
+    if (blockIdx.x == g_tc_trace_cta && (idx) < 256) g_tc_trace[role][idx] = clock64();        \
+  } while (0)
+#else
+#define TC_TRACE(role, idx) do {} while (0)
+#endif
+
 __device__ __forceinline__ uint8_t* align1024(uint8_t* p) {
   return reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(p) + 1023) & ~(uintptr_t)1023);
 }
@@ -1159,11 +1171,13 @@ tc_fwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
         mbar_expect_tx(k_full + st, L::kIn);
         for (int kb = 0; kb < KBD; ++kb)
           tma_load_3d_h(s_k + st * L::kIn + kb * (kTile * 128), &tm_k, k_full + st, kb * 64, tr.tile(i) * kTile, (int)bh, pol_k);
+        TC_TRACE(0, i);
         nk = i + 1;
         if (!mbar_wait(v_empty + st, ((i >> 1) & 1) ^ 1, ab, 0x3180 + i)) break;
         mbar_expect_tx(v_full + st, L::kIn);
         for (int kb = 0; kb < KBD; ++kb)
           tma_load_3d_h(s_v + st * L::kIn + kb * (kTile * 128), &tm_v, v_full + st, kb * 64, tr.tile(i) * kTile, (int)bh, pol_v);
+        TC_TRACE(1, i);
         nv = i + 1;
       }
       if (ab.raised()) {
@@ -1180,6 +1194,7 @@ tc_fwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
       auto front = [&](int i) -> bool {
         const int st = i & 1;
         if (!mbar_wait(k_full + st, (i >> 1) & 1, ab, 0x3300 + i)) return false;
+        TC_TRACE(2, i);
         tc_fence_after();
         const uint32_t a_k = smem_u32(s_k + st * L::kIn);
 #pragma unroll
@@ -1195,7 +1210,9 @@ tc_fwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
       for (int i = 0; ok && i < count; ++i) {
         const int st = i & 1;
         if (!mbar_wait(p_full + st, (i >> 1) & 1, ab, 0x3400 + i)) break;
+        TC_TRACE(3, i);
         if (!mbar_wait(v_full + st, (i >> 1) & 1, ab, 0x3480 + i)) break;
+        TC_TRACE(4, i);
         tc_fence_after();
         const uint32_t a_v = smem_u32(s_v + st * L::kIn);
         const uint32_t a_pi = a_p + st * L::kP;
@@ -1241,6 +1258,7 @@ tc_fwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
       const int64_t row = (int64_t)tr.tile(i) * kTile + r;
       const bool valid = row < sch.N;
       if (!mbar_wait(s_full + st, (i >> 1) & 1, ab, 0x3600 + i)) { alive = false; break; }
+      if (threadIdx.x == 0) TC_TRACE(5, i);
       __syncwarp();
       tc_fence_after();
       float s[HC], v[HC];
@@ -1272,6 +1290,7 @@ tc_fwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
       }
       named_barrier(1, kComputeThreads);
       const bool move = s_flag[i % 3] != 0;     // CTA-uniform
+      if (threadIdx.x == 0) TC_TRACE(6, i);
       if (i > 1) {
         // the accumulation of tile i-2 read the P' buffer this tile is about to fill
         if (!mbar_wait(acc_done + st, (uint32_t)((i - 2) >> 1) & 1u, ab, 0x3700 + i)) { alive = false; break; }
@@ -1319,6 +1338,7 @@ tc_fwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
       fence_proxy_async();
       tc_fence_before();
       mbar_arrive_warp(p_full + st);
+      if (threadIdx.x == 0) TC_TRACE(7, i);
     }
     if (alive && mbar_wait(acc_done + ((count - 1) & 1), (uint32_t)((count - 1) >> 1) & 1u, ab, 0x3900)) {
       __syncwarp();
