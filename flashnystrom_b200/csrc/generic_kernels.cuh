@@ -78,8 +78,7 @@ __device__ __forceinline__ void load_small(float* dst, int ld, const float* src,
 template <class T>
 __global__ void __launch_bounds__(kThreads)
 landmark_partial_kernel(const T* __restrict__ q, const T* __restrict__ k, float* __restrict__ out,
-                        int64_t BH, int64_t N, int D, int m, int C, int64_t seg_N, int64_t row_offset,
-                        int k_streaming) {
+                        int64_t BH, int64_t N, int D, int m, int C, int64_t seg_N, int64_t row_offset) {
   constexpr int V = Vec16<T>::n;
   __shared__ float red[kThreads * 8];
   pdl_trigger();
@@ -97,9 +96,6 @@ landmark_partial_kernel(const T* __restrict__ q, const T* __restrict__ k, float*
     const int lc = (int)(rest - bh * (m * C));
     const int l = lc / C, c = lc - l * C;
     const T* slice = (which ? k : q) + bh * N * D;
-    // Q is not read again before the output pass: streaming (evict-first) loads.  K is re-read right
-    // away by the column pass; unless told otherwise it is loaded the ordinary way so it stays in L2.
-    const bool streaming = which == 0 || k_streaming != 0;
     // segment l in global rows, clipped to the rows this rank holds, in local row numbers
     int64_t start = sg.start(l) - row_offset, end = sg.end(l) - row_offset;
     if (start < 0) start = 0;
@@ -118,8 +114,7 @@ landmark_partial_kernel(const T* __restrict__ q, const T* __restrict__ k, float*
       uint4 raw[8];
 #pragma unroll
       for (int u = 0; u < 8; ++u)
-        raw[u] = streaming ? __ldcs(reinterpret_cast<const uint4*>(slice + (r + u * rows_per_iter) * D + cv * V))
-                           : __ldg(reinterpret_cast<const uint4*>(slice + (r + u * rows_per_iter) * D + cv * V));
+        raw[u] = __ldcs(reinterpret_cast<const uint4*>(slice + (r + u * rows_per_iter) * D + cv * V));
 #pragma unroll
       for (int u = 0; u < 8; ++u) {
         const T* e16 = reinterpret_cast<const T*>(&raw[u]);
