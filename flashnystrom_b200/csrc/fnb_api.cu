@@ -337,13 +337,23 @@ static int l2_mode() {
 }
 static int hint_bits(int in0, int in1, int out0, int out1) { return in0 | (in1 << 2) | (out0 << 4) | (out1 << 6); }
 
+// Calls f(std::integral_constant<int, D>) for the head dimensions the tensor-core kernels are
+// instantiated for.
+template <class F>
+static int dispatch_head_dim(int D, F&& f) {
+  if (D == 64) return f(std::integral_constant<int, 64>{});
+  return f(std::integral_constant<int, 128>{});
+}
+// Co-resident tensor-core CTAs per SM: two for head_dim 64, one for head_dim 128 (shared memory).
+static int tc_ctas_per_sm(int D) { return D == 64 ? 2 : 1; }
+
 template <class T>
 static int forward_impl(const fnb_fwd_args& a, const Plan& p, const FwdWs& w, int max_smem, int sms,
                         cudaStream_t st, bool allow_inner_fork, const SpCtx& S = SpCtx()) {
   Launcher L(st, a.device);
   const float scale = powf((float)p.D, -0.25f);
   constexpr bool k16 = !std::is_same<T, float>::value;
-  tc::TcSched sch = tc::make_sched(p.BH, p.N, 2 * sms);   // two CTAs per SM
+  tc::TcSched sch = tc::make_sched(p.BH, p.N, tc_ctas_per_sm(p.D) * sms);   // one wave
   const bool use_tc = k16 && tc::tc_supported(a.shape.dtype, p.D, p.m, a.shape.flags) && sch.nchunk <= p.nchunk;
   const int MP = p.m <= 64 ? 64 : 128;
   const bool smem_ns = p.m <= ns::kN;
@@ -434,20 +444,23 @@ static int forward_impl(const fnb_fwd_args& a, const Plan& p, const FwdWs& w, in
 
   if constexpr (k16) {
     if (use_tc) {
-      constexpr int D = 64, MPc = 64;
-      CUtensorMap tm_k, tm_v, tm_qt;
-      if (!tc::make_map_3d(&tm_k, a.k, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
-          !tc::make_map_3d(&tm_v, a.v, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
-          !tc::make_map_2d(&tm_qt, w.qt16, a.shape.dtype, p.BH * MPc, D, MPc))
-        return fail(FNB_ERR_CUDA, "cuTensorMapEncodeTiled failed for the forward column pass");
-      L.begin();
-      auto kern = tc::tc_fwd_b_kernel<T, D, MPc>;
-      size_t smem = tc::FwdBSmem<D, MPc>::kBytes;
-      if (int rc = set_smem(kern, smem, max_smem, "tc_fwd_b")) return rc;
-      launch_pdl(kern, dim3((unsigned)(p.BH * sch.nchunk)), dim3(tc::kTcThreads), smem, st,
-          tm_k, tm_v, tm_qt, fused_landmarks ? land : (const float*)nullptr, lmC, p.BH, scale, w.part_acc, w.part_max,
-          w.part_sum, sch_fb, p.m, a.device_status);
-      if (L.end("tc_fwd_b")) return L.status;
+      int rc = dispatch_head_dim(p.D, [&](auto dtag) -> int {
+        constexpr int D = decltype(dtag)::value, MPc = 64;
+        CUtensorMap tm_k, tm_v, tm_qt;
+        if (!tc::make_map_3d(&tm_k, a.k, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
+            !tc::make_map_3d(&tm_v, a.v, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
+            !tc::make_map_2d(&tm_qt, w.qt16, a.shape.dtype, p.BH * MPc, D, MPc))
+          return fail(FNB_ERR_CUDA, "cuTensorMapEncodeTiled failed for the forward column pass");
+        L.begin();
+        auto kern = tc::tc_fwd_b_kernel<T, D, MPc>;
+        size_t smem = tc::FwdBSmem<D, MPc>::kBytes;
+        if (int rc2 = set_smem(kern, smem, max_smem, "tc_fwd_b")) return rc2;
+        launch_pdl(kern, dim3((unsigned)(p.BH * sch.nchunk)), dim3(tc::kTcThreads), smem, st,
+            tm_k, tm_v, tm_qt, fused_landmarks ? land : (const float*)nullptr, lmC, p.BH, scale, w.part_acc, w.part_max,
+            w.part_sum, sch_fb, p.m, a.device_status);
+        return L.end("tc_fwd_b");
+      });
+      if (rc) return rc;
     }
   }
   if (!use_tc) {
@@ -515,19 +528,20 @@ static int forward_impl(const fnb_fwd_args& a, const Plan& p, const FwdWs& w, in
 
   if constexpr (k16) {
     if (use_tc) {
-      constexpr int D = 64, MPc = 64;
-      CUtensorMap tm_q, tm_o;
-      if (!tc::make_map_3d(&tm_q, a.q, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
-          !tc::make_map_3d(&tm_o, a.out, a.shape.dtype, p.BH, p.N, D, tc::kTile))
-        return fail(FNB_ERR_CUDA, "cuTensorMapEncodeTiled failed for the forward output pass");
-      L.begin();
-      auto kern = tc::tc_fwd_c_kernel<T, D, MPc>;
-      size_t smem = tc::FwdCSmem<D, MPc>::kBytes;
-      if (int rc = set_smem(kern, smem, max_smem, "tc_fwd_c")) return rc;
-      launch_pdl(kern, dim3((unsigned)(p.BH * sch.nchunk)), dim3(tc::kTcThreads), smem, st, tm_q, tm_o, a.k_landmarks, a.step2, a.lse1, sch_fc,
-                                                                      p.m, scale, a.device_status);
-      if (L.end("tc_fwd_c")) return L.status;
-      return 0;
+      return dispatch_head_dim(p.D, [&](auto dtag) -> int {
+        constexpr int D = decltype(dtag)::value, MPc = 64;
+        CUtensorMap tm_q, tm_o;
+        if (!tc::make_map_3d(&tm_q, a.q, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
+            !tc::make_map_3d(&tm_o, a.out, a.shape.dtype, p.BH, p.N, D, tc::kTile))
+          return fail(FNB_ERR_CUDA, "cuTensorMapEncodeTiled failed for the forward output pass");
+        L.begin();
+        auto kern = tc::tc_fwd_c_kernel<T, D, MPc>;
+        size_t smem = tc::FwdCSmem<D, MPc>::kBytes;
+        if (int rc2 = set_smem(kern, smem, max_smem, "tc_fwd_c")) return rc2;
+        launch_pdl(kern, dim3((unsigned)(p.BH * sch.nchunk)), dim3(tc::kTcThreads), smem, st, tm_q, tm_o, a.k_landmarks,
+                   a.step2, a.lse1, sch_fc, p.m, scale, a.device_status);
+        return L.end("tc_fwd_c");
+      });
     }
   }
   L.begin();
@@ -549,7 +563,7 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
   Launcher L(st, a.device);
   const float scale = powf((float)p.D, -0.25f);
   constexpr bool k16 = !std::is_same<T, float>::value;
-  tc::TcSched sch = tc::make_sched(p.BH, p.N, 2 * sms);   // two CTAs per SM
+  tc::TcSched sch = tc::make_sched(p.BH, p.N, tc_ctas_per_sm(p.D) * sms);   // one wave
   const int64_t seg_N = S.on() ? S.N_global : p.N, row_offset = S.on() ? (int64_t)S.rank * p.N : 0;
   sch.seg_N = seg_N; sch.row_offset = row_offset;
   const bool use_tc = k16 && tc::tc_supported(a.shape.dtype, p.D, p.m, a.shape.flags) && sch.nchunk <= p.nchunk;
@@ -599,7 +613,7 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
   void* qt16 = w.op16[3]; void* do3n = w.op16[5];
   CUtensorMap tm_q, tm_g, tm_dq, tm_dk;
   if (use_tc) {
-    constexpr int D = 64;
+    const int D = p.D;
     if (!tc::make_map_3d(&tm_q, a.q, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
         !tc::make_map_3d(&tm_g, a.d_out, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
         !tc::make_map_3d(&tm_dq, a.dq, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
@@ -615,14 +629,17 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
   if (S.run(0)) {
   if constexpr (k16) {
     if (use_tc) {
-      constexpr int D = 64, MPc = 64;
-      L.begin();
-      auto kern = tc::tc_bwd_a_kernel<T, D, MPc>;
-      size_t sm = tc::BwdASmem<D, MPc>::kBytes;
-      if (int rc = set_smem(kern, sm, max_smem, "tc_bwd_a")) return rc;
-      launch_pdl(kern, dim3(tgrid), dim3(tc::kTcThreads), sm, st, tm_q, tm_g, tm_dq, a.k_landmarks, a.step2, a.lse1,
-                 w.partA, w.st_scale, sch_a, p.m, scale, a.device_status);
-      if (L.end("tc_bwd_a")) return L.status;
+      int rc = dispatch_head_dim(p.D, [&](auto dtag) -> int {
+        constexpr int D = decltype(dtag)::value, MPc = 64;
+        L.begin();
+        auto kern = tc::tc_bwd_a_kernel<T, D, MPc>;
+        size_t sm = tc::BwdASmem<D, MPc>::kBytes;
+        if (int rc2 = set_smem(kern, sm, max_smem, "tc_bwd_a")) return rc2;
+        launch_pdl(kern, dim3(tgrid), dim3(tc::kTcThreads), sm, st, tm_q, tm_g, tm_dq, a.k_landmarks, a.step2, a.lse1,
+                   w.partA, w.st_scale, sch_a, p.m, scale, a.device_status);
+        return L.end("tc_bwd_a");
+      });
+      if (rc) return rc;
     }
   }
   if (!use_tc) {
@@ -729,26 +746,29 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
   // ---- pass B ---------------------------------------------------------------------------------
   if constexpr (k16) {
     if (use_tc) {
-      constexpr int D = 64, MPc = 64;
-      CUtensorMap tm_k, tm_v, tm_qt, tm_do3, tm_dv;
-      if (!tc::make_map_3d(&tm_k, a.k, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
-          !tc::make_map_3d(&tm_v, a.v, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
-          !tc::make_map_3d(&tm_dv, a.dv, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
-          !tc::make_map_2d(&tm_qt, qt16, a.shape.dtype, p.BH * MPc, D, MPc) ||
-          !tc::make_map_2d(&tm_do3, do3n, a.shape.dtype, p.BH * MPc, D, MPc))
-        return fail(FNB_ERR_CUDA, "cuTensorMapEncodeTiled failed for the backward column pass");
-      L.begin();
-      auto kern = tc::tc_bwd_b_kernel<T, D, MPc>;
-      size_t sm = tc::BwdBSmem<D, MPc>::kBytes;
-      if (int rc = set_smem(kern, sm, max_smem, "tc_bwd_b")) return rc;
-      const dim3 bgrid((unsigned)(p.BH * sch_b.nchunk));
-      if (side_ns)   // an ordinary launch: it must not claim SMs before the Newton-Schulz kernel has its own
-        kern<<<bgrid, tc::kTcThreads, sm, st>>>(tm_k, tm_v, tm_qt, tm_do3, tm_dk, tm_dv, a.lse3, w.D3, w.do3_scale, w.partB,
-                                                sch_b, p.m, scale, kshift, a.device_status);
-      else
-        launch_pdl(kern, bgrid, dim3(tc::kTcThreads), sm, st, tm_k, tm_v, tm_qt, tm_do3, tm_dk, tm_dv, a.lse3, w.D3, w.do3_scale,
-                   w.partB, sch_b, p.m, scale, kshift, a.device_status);
-      if (L.end("tc_bwd_b")) return L.status;
+      int rc = dispatch_head_dim(p.D, [&](auto dtag) -> int {
+        constexpr int D = decltype(dtag)::value, MPc = 64;
+        CUtensorMap tm_k, tm_v, tm_qt, tm_do3, tm_dv;
+        if (!tc::make_map_3d(&tm_k, a.k, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
+            !tc::make_map_3d(&tm_v, a.v, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
+            !tc::make_map_3d(&tm_dv, a.dv, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
+            !tc::make_map_2d(&tm_qt, qt16, a.shape.dtype, p.BH * MPc, D, MPc) ||
+            !tc::make_map_2d(&tm_do3, do3n, a.shape.dtype, p.BH * MPc, D, MPc))
+          return fail(FNB_ERR_CUDA, "cuTensorMapEncodeTiled failed for the backward column pass");
+        L.begin();
+        auto kern = tc::tc_bwd_b_kernel<T, D, MPc>;
+        size_t sm = tc::BwdBSmem<D, MPc>::kBytes;
+        if (int rc2 = set_smem(kern, sm, max_smem, "tc_bwd_b")) return rc2;
+        const dim3 bgrid((unsigned)(p.BH * sch_b.nchunk));
+        if (side_ns)   // an ordinary launch: it must not claim SMs before the Newton-Schulz kernel has its own
+          kern<<<bgrid, tc::kTcThreads, sm, st>>>(tm_k, tm_v, tm_qt, tm_do3, tm_dk, tm_dv, a.lse3, w.D3, w.do3_scale, w.partB,
+                                                  sch_b, p.m, scale, kshift, a.device_status);
+        else
+          launch_pdl(kern, bgrid, dim3(tc::kTcThreads), sm, st, tm_k, tm_v, tm_qt, tm_do3, tm_dk, tm_dv, a.lse3, w.D3, w.do3_scale,
+                     w.partB, sch_b, p.m, scale, kshift, a.device_status);
+        return L.end("tc_bwd_b");
+      });
+      if (rc) return rc;
     }
   }
   if (!use_tc) {
@@ -774,11 +794,12 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
   // ---- pass C ---------------------------------------------------------------------------------
   if constexpr (k16) {
     if (use_tc) {
-      constexpr int D = 64, MPc = 64;
+      return dispatch_head_dim(p.D, [&](auto dtag) -> int {
+      constexpr int D = decltype(dtag)::value, MPc = 64;
       L.begin();
       auto kern = tc::tc_rows_inplace_kernel<T, D, MPc>;
       size_t sm = tc::RowsSmem<D, MPc>::kBytes;
-      if (int rc = set_smem(kern, sm, max_smem, "tc_bwd_c")) return rc;
+      if (int rc2 = set_smem(kern, sm, max_smem, "tc_bwd_c")) return rc2;
       // dQ from the dS1 tiles pass A left in dq, dK from the dS3' tiles the column pass left in dk.
       // Every CTA first sums the column-pass partials of the landmark rows its own tiles touch
       // (rows_q = s (dQt_ns + sum of partials) / len), so no separate reduction kernel runs.
@@ -796,8 +817,8 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
       else
         launch_pdl(kern, dim3(tgrid), dim3(tc::kTcThreads), sm, st, tm_dq, tm_dk, side_q, side_k, 2, scale * tc::kLog2e, sch_c,
                    p.m, a.device_status);
-      if (L.end("tc_bwd_c")) return L.status;
-      return 0;
+      return L.end("tc_bwd_c");
+      });
     }
   }
   L.begin();

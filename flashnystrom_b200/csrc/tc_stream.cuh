@@ -88,29 +88,31 @@ __device__ __forceinline__ uint64_t mndesc(uint32_t base, int k) {
   return smem_desc_sw128(base + k * 2048, kTile * 128, 1024);
 }
 
-// Compute warps (256 threads), head_dim 64: 16-bit swizzled operand tiles of two landmark matrices
-// of one slice straight from their FP32 originals (rows >= m zero):
+// Compute warps (256 threads): 16-bit swizzled operand tiles of two (m x D) landmark matrices of one
+// slice straight from their FP32 originals (64 rows, rows >= m zero; D / 64 blocks of
+// [64 rows x 128 B] each):
 //   tile_a = mul_a * A,   tile_b = B / sc  with sc the power of two >= max |B|   (returned).
-// Thread t packs row t >> 2, columns 16 (t & 3) .. +15.  scratch: 8 floats of shared memory;
-// named barrier 3 is used once.  The caller fences and signals the MMA thread.
-template <class T>
+// Thread t packs row t >> 2, columns (D / 4) (t & 3) .. + D / 4 - 1.  scratch: 8 floats of shared
+// memory; named barrier 3 is used once.  The caller fences and signals the MMA thread.
+template <class T, int D>
 __device__ __forceinline__ float pack_landmark_operands(uint8_t* tile_a, uint8_t* tile_b, const float* A,
                                                         const float* B, int m, float mul_a, float* scratch) {
-  const int t = threadIdx.x, r = t >> 2, c0 = (t & 3) * 16;
-  float a[16], b[16];
+  constexpr int CPT = D / 4;
+  const int t = threadIdx.x, r = t >> 2, c0 = (t & 3) * CPT;
+  float a[CPT], b[CPT];
 #pragma unroll
-  for (int q = 0; q < 4; ++q) {
+  for (int q = 0; q < CPT / 4; ++q) {
     float4 x = make_float4(0.f, 0.f, 0.f, 0.f), y = x;
     if (r < m) {
-      x = *reinterpret_cast<const float4*>(A + r * 64 + c0 + 4 * q);
-      y = *reinterpret_cast<const float4*>(B + r * 64 + c0 + 4 * q);
+      x = *reinterpret_cast<const float4*>(A + r * D + c0 + 4 * q);
+      y = *reinterpret_cast<const float4*>(B + r * D + c0 + 4 * q);
     }
     a[4 * q] = x.x; a[4 * q + 1] = x.y; a[4 * q + 2] = x.z; a[4 * q + 3] = x.w;
     b[4 * q] = y.x; b[4 * q + 1] = y.y; b[4 * q + 2] = y.z; b[4 * q + 3] = y.w;
   }
   float amax = 0.f;
 #pragma unroll
-  for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(b[i]));
+  for (int i = 0; i < CPT; ++i) amax = fmaxf(amax, fabsf(b[i]));
   for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
   if ((t & 31) == 0) scratch[t >> 5] = amax;
   named_barrier(3, kComputeThreads);
@@ -119,13 +121,14 @@ __device__ __forceinline__ float pack_landmark_operands(uint8_t* tile_a, uint8_t
   for (int w = 1; w < kComputeThreads / 32; ++w) cmax = fmaxf(cmax, scratch[w]);
   const float sc = pow2_scale(cmax), inv = 1.f / sc;
 #pragma unroll
-  for (int c = 0; c < 2; ++c) {
+  for (int c = 0; c < CPT / 8; ++c) {
     uint4 wa, wb;
     wa.x = pack2<T>(a[8 * c + 0] * mul_a, a[8 * c + 1] * mul_a); wa.y = pack2<T>(a[8 * c + 2] * mul_a, a[8 * c + 3] * mul_a);
     wa.z = pack2<T>(a[8 * c + 4] * mul_a, a[8 * c + 5] * mul_a); wa.w = pack2<T>(a[8 * c + 6] * mul_a, a[8 * c + 7] * mul_a);
     wb.x = pack2<T>(b[8 * c + 0] * inv, b[8 * c + 1] * inv); wb.y = pack2<T>(b[8 * c + 2] * inv, b[8 * c + 3] * inv);
     wb.z = pack2<T>(b[8 * c + 4] * inv, b[8 * c + 5] * inv); wb.w = pack2<T>(b[8 * c + 6] * inv, b[8 * c + 7] * inv);
-    const uint32_t off = sw128_offset(r, (c0 >> 3) + c);
+    const int cc = (c0 >> 3) + c;
+    const uint32_t off = (uint32_t)(cc >> 3) * (64 * 128) + sw128_offset(r, cc & 7);
     *reinterpret_cast<uint4*>(tile_a + off) = wa;
     *reinterpret_cast<uint4*>(tile_b + off) = wb;
   }
@@ -172,17 +175,17 @@ template <int D, int MP>
 struct FwdCSmem {
   static constexpr int kKt = MP * D * 2, kSt = D * MP * 2, kQ = kTile * D * 2, kP = kTile * MP * 2,
                        kO = kTile * D * 2;
-  static_assert(kO <= kP, "the output tile is staged in the probability buffer");
-  static constexpr int kBytes = kKt + kSt + 2 * kQ + 2 * kP + 256 + 1024;
+  static constexpr int kPO = kP > kO ? kP : kO;   // the output tile is staged in the probability buffer
+  static constexpr int kBytes = kKt + kSt + 2 * kQ + 2 * kPO + 256 + 1024;
 };
 
 template <class T, int D, int MP>
-__global__ void __launch_bounds__(kTcThreads, 2)
+__global__ void __launch_bounds__(kTcThreads, (D == 64 ? 2 : 1))
 tc_fwd_c_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_o,
                 const float* __restrict__ k_landmarks, const float* __restrict__ step2,
                 float* __restrict__ lse1, TcSched sch, int m, float scale, int* status) {
   using L = FwdCSmem<D, MP>;
-  static_assert(D == 64 && MP == 64, "the in-kernel operand packing is written for 64 x 64 landmark operands");
+  static_assert((D == 64 || D == 128) && MP == 64, "the in-kernel operand packing is written for 64 landmark rows");
   constexpr int KBD = D / 64;
   constexpr int kGroup = kComputeThreads / 2;
   constexpr uint32_t kCols = 2 * MP + 2 * D;
@@ -194,7 +197,7 @@ tc_fwd_c_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   uint8_t* s_st = s_kt + L::kKt;
   uint8_t* s_q = s_st + L::kSt;          // two stages
   uint8_t* s_p = s_q + 2 * L::kQ;        // one buffer per compute group
-  uint64_t* bars = reinterpret_cast<uint64_t*>(s_p + 2 * L::kP);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(s_p + 2 * L::kPO);
   uint64_t* small_full = bars + 0;
   uint64_t* q_full = bars + 1;           // [2]
   uint64_t* q_empty = bars + 3;          // [2]
@@ -274,7 +277,7 @@ tc_fwd_c_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         if (!mbar_wait(p_full + st, (i >> 1) & 1, ab, 0x400 + i)) break;
         if (!mbar_wait(o_free + st, ((i >> 1) & 1) ^ 1, ab, 0x500 + i)) break;
         tc_fence_after();
-        const uint32_t a_p = smem_u32(s_p + st * L::kP);
+        const uint32_t a_p = smem_u32(s_p + st * L::kPO);
 #pragma unroll
         for (int k = 0; k < MP / 16; ++k)
           umma(tmem_base + 2 * MP + st * D, kdesc(a_p, k, kTile), smem_desc_sw128(a_st + k * 2048, MP * 128, 1024),
@@ -288,11 +291,11 @@ tc_fwd_c_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const int r = threadIdx.x & 127;                           // tile row = TMEM lane
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     // operand copies of Kt and step2 for this slice (the P buffers are free until the first tile)
-    const float osc = pack_landmark_operands<T>(s_kt, s_st, k_landmarks + bh * m * D, step2 + bh * m * D, m,
-                                                scale * kLog2e, reinterpret_cast<float*>(s_p));
+    const float osc = pack_landmark_operands<T, D>(s_kt, s_st, k_landmarks + bh * m * D, step2 + bh * m * D, m,
+                                                   scale * kLog2e, reinterpret_cast<float*>(s_p));
     fence_proxy_async();
     mbar_arrive_warp(small_full);
-    uint8_t* my_p = s_p + g * L::kP;
+    uint8_t* my_p = s_p + g * L::kPO;
     const bool leader = r == 0;
     const uint64_t pol_o = leader ? l2_policy_of(sch.hint, 2) : 0ull;
     const bool full_m = m == MP;
@@ -341,14 +344,20 @@ tc_fwd_c_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       if (!mbar_wait(o_full + g, par, ab, 0x700 + i)) break;
       __syncwarp();
       tc_fence_after();
-      float o[D];
-      ld_cols<D>(tmem_base + 2 * MP + g * D + lane_base, o);
-      tmem_ld_wait();
-      tc_fence_before();
-      mbar_arrive_warp(o_free + g);
+      // (the product that read P from my_p has completed, so the output tile can be staged there)
 #pragma unroll
-      for (int j = 0; j < D; ++j) o[j] *= mul;
-      store_cols<T, D>(my_p, r, 0, o);        // the product that read P from my_p has completed
+      for (int oc = 0; oc < D / 64; ++oc) {
+        float o[64];
+        ld_cols<64>(tmem_base + 2 * MP + g * D + oc * 64 + lane_base, o);
+        tmem_ld_wait();
+        if (oc == D / 64 - 1) {
+          tc_fence_before();
+          mbar_arrive_warp(o_free + g);
+        }
+#pragma unroll
+        for (int j = 0; j < 64; ++j) o[j] *= mul;
+        store_cols<T, 64>(my_p, r, oc * 64, o);
+      }
       fence_proxy_async();
       named_barrier(1 + g, kGroup);
       if (leader) {
@@ -382,16 +391,16 @@ struct BwdASmem {
 };
 
 template <class T, int D, int MP>
-__global__ void __launch_bounds__(kTcThreads, 2)
+__global__ void __launch_bounds__(kTcThreads, (D == 64 ? 2 : 1))
 tc_bwd_a_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_g,
                 const __grid_constant__ CUtensorMap tm_dq,
                 const float* __restrict__ k_landmarks, const float* __restrict__ step2,
                 const float* __restrict__ lse1, float* __restrict__ partA, float* __restrict__ sc_out,
                 TcSched sch, int m, float scale, int* status) {
-  static_assert(D == 64 && MP == 64, "written for 64 x 64 landmark operands");
+  static_assert((D == 64 || D == 128) && MP == 64, "written for 64 landmark rows");
   using L = BwdASmem<D, MP>;
   constexpr int HC = MP / 2, HD = D / 2;
-  constexpr uint32_t kTmemCols = 256;    // S, dP, and the 128-column accumulator
+  constexpr uint32_t kTmemCols = 2 * MP + 2 * D <= 256 ? 256 : 512;    // S, dP, and the 2 D-column accumulator
   extern __shared__ uint8_t smem_raw[];
   pdl_trigger();
   if (smem_u32(smem_raw) & 1023u) {
@@ -400,9 +409,9 @@ tc_bwd_a_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   }
   uint8_t* s_kt = smem_raw;
   uint8_t* s_st = s_kt + L::kKt;
-  uint8_t* s_q = s_st + L::kSt;          // two stages
-  uint8_t* s_g = s_q + 2 * L::kIn;       // two stages
-  uint8_t* s_p = s_g + 2 * L::kIn;       // P tile (its head doubles as the D1 exchange)
+  uint8_t* s_q = s_st + L::kSt;          // two stages of [Q tile | dO tile]
+  uint8_t* s_g = s_q + L::kIn;
+  uint8_t* s_p = s_q + 4 * L::kIn;       // P tile (its head doubles as the D1 exchange)
   uint8_t* s_ds = s_p + L::kP;           // dS tile
   float* s_x = reinterpret_cast<float*>(s_p);
   uint64_t* bars = reinterpret_cast<uint64_t*>(s_ds + L::kDs);
@@ -450,8 +459,10 @@ tc_bwd_a_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         const int st = i & 1;
         if (!mbar_wait(in_empty + st, ((i >> 1) & 1) ^ 1, ab, 0x1100 + i)) break;
         mbar_expect_tx(in_full + st, 2 * L::kIn);
-        tma_load_3d_h(s_q + st * L::kIn, &tm_q, in_full + st, 0, tr.tile(i) * kTile, (int)bh, pol_q);
-        tma_load_3d_h(s_g + st * L::kIn, &tm_g, in_full + st, 0, tr.tile(i) * kTile, (int)bh, pol_g);
+        for (int kb = 0; kb < D / 64; ++kb) {
+          tma_load_3d_h(s_q + st * 2 * L::kIn + kb * (kTile * 128), &tm_q, in_full + st, kb * 64, tr.tile(i) * kTile, (int)bh, pol_q);
+          tma_load_3d_h(s_g + st * 2 * L::kIn + kb * (kTile * 128), &tm_g, in_full + st, kb * 64, tr.tile(i) * kTile, (int)bh, pol_g);
+        }
         armed = i + 1;
       }
       if (ab.raised())
@@ -460,7 +471,7 @@ tc_bwd_a_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   } else if (warp == kMmaWarp) {
     if (lane == 0) {
       constexpr uint32_t idesc_s = make_idesc<T>(kTile, MP, false, false);
-      constexpr uint32_t idesc_acc2 = make_idesc<T>(128, 128, true, true);
+      constexpr uint32_t idesc_acc2 = make_idesc<T>(2 * MP, 2 * D, true, true);
       const uint32_t a_kt = smem_u32(s_kt), a_st = smem_u32(s_st), a_p = smem_u32(s_p);
       const uint64_t pol_ds = l2_policy_of(sch.hint, 2);
       // S and dP of tile i
@@ -468,7 +479,7 @@ tc_bwd_a_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         const int st = i & 1;
         if (!mbar_wait(in_full + st, (i >> 1) & 1, ab, 0x1300 + i)) return false;
         tc_fence_after();
-        const uint32_t a_q = smem_u32(s_q + st * L::kIn), a_g = smem_u32(s_g + st * L::kIn);
+        const uint32_t a_q = smem_u32(s_q + st * 2 * L::kIn), a_g = smem_u32(s_g + st * 2 * L::kIn);
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) umma(tmem_base, kdesc(a_q, k, kTile), kdesc(a_kt, k, MP), idesc_s, k > 0);
 #pragma unroll
@@ -482,14 +493,14 @@ tc_bwd_a_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         if (!mbar_wait(pds_full, i & 1, ab, 0x1400 + i)) break;
         tc_fence_after();
         const int st = i & 1;
-        // One 128 x 128 accumulator for both sums: [P | dS]^T [Q | dO] (both operands MN-major,
-        // the second 64-wide block of each is the neighbouring tile).  Rows 0..63 x columns
-        // 64..127 hold P^T dO, rows 64..127 x columns 0..63 hold dS^T Q; the other two quadrants
-        // are not used.  An M = N = 128 MMA takes 35 ns against 2 x 25 ns for two 64 x 64 ones.
+        // One 128 x 2D accumulator for both sums: [P | dS]^T [Q | dO] (both operands MN-major; the
+        // 64-wide blocks of each follow one another in shared memory, 16 KB apart).  Rows 0..63 x
+        // columns D..2D-1 hold P^T dO, rows 64..127 x columns 0..D-1 hold dS^T Q; the other two
+        // quadrants are not used.  An M = N = 128 MMA takes 35 ns against 2 x 25 ns for two 64 x 64 ones.
 #pragma unroll
         for (int k = 0; k < kTile / 16; ++k)
           umma(tmem_base + 2 * MP, smem_desc_sw128(a_p + k * 2048, L::kP, 1024),
-               smem_desc_sw128(smem_u32(s_q + st * L::kIn) + k * 2048, 2 * L::kIn, 1024), idesc_acc2, (i > 0 || k > 0));
+               smem_desc_sw128(smem_u32(s_q + st * 2 * L::kIn) + k * 2048, kTile * 128, 1024), idesc_acc2, (i > 0 || k > 0));
         // the accumulation goes first: its commit frees the (Q, dO) stage, and the pass is bound by
         // how early the next load is issued; then the scores of the next tile
         umma_commit(in_empty + st);
@@ -508,8 +519,8 @@ tc_bwd_a_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const int quarter = warp & 3;
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
     // operand copies of Kt and step2 for this slice (the dS tile is free until the first tile)
-    const float sc = pack_landmark_operands<T>(s_kt, s_st, k_landmarks + bh * m * D, step2 + bh * m * D, m,
-                                               scale * kLog2e, reinterpret_cast<float*>(s_ds));
+    const float sc = pack_landmark_operands<T, D>(s_kt, s_st, k_landmarks + bh * m * D, step2 + bh * m * D, m,
+                                                  scale * kLog2e, reinterpret_cast<float*>(s_ds));
     fence_proxy_async();
     mbar_arrive_warp(small_full);
     // the in-place dQ pass rescales the dS tiles by the same power of two
@@ -611,36 +622,40 @@ struct RowsSmem {
   static constexpr int kBytes = 2 * kOp + kStages * kIn + 2 * kOut + 256;
 };
 
-// 16-bit swizzled operand tile of one FP32 landmark matrix (rows >= m zero), times mul; compute
-// warps (256 threads), head_dim 64: thread t packs row t >> 2, columns 16 (t & 3) .. +15
-template <class T>
+// 16-bit swizzled operand tile of one FP32 (m x D) landmark matrix (64 rows, rows >= m zero; D / 64
+// blocks of [64 rows x 128 B]), times mul; compute warps (256 threads): thread t packs row t >> 2,
+// columns (D / 4) (t & 3) .. + D / 4 - 1
+template <class T, int D>
 __device__ __forceinline__ void pack_landmark_operand(uint8_t* tile, const float* A, int m, float mul) {
-  const int t = threadIdx.x, r = t >> 2, c0 = (t & 3) * 16;
+  constexpr int CPT = D / 4;
+  const int t = threadIdx.x, r = t >> 2, c0 = (t & 3) * CPT;
 #pragma unroll
-  for (int c = 0; c < 2; ++c) {
+  for (int c = 0; c < CPT / 8; ++c) {
     float4 x = make_float4(0.f, 0.f, 0.f, 0.f), y = x;
     if (r < m) {
-      x = *reinterpret_cast<const float4*>(A + r * 64 + c0 + 8 * c);
-      y = *reinterpret_cast<const float4*>(A + r * 64 + c0 + 8 * c + 4);
+      x = *reinterpret_cast<const float4*>(A + r * D + c0 + 8 * c);
+      y = *reinterpret_cast<const float4*>(A + r * D + c0 + 8 * c + 4);
     }
     uint4 w;
     w.x = pack2<T>(x.x * mul, x.y * mul); w.y = pack2<T>(x.z * mul, x.w * mul);
     w.z = pack2<T>(y.x * mul, y.y * mul); w.w = pack2<T>(y.z * mul, y.w * mul);
-    *reinterpret_cast<uint4*>(tile + sw128_offset(r, (c0 >> 3) + c)) = w;
+    const int cc = (c0 >> 3) + c;
+    *reinterpret_cast<uint4*>(tile + (uint32_t)(cc >> 3) * (64 * 128) + sw128_offset(r, cc & 7)) = w;
   }
 }
 
 template <class T, int D, int MP>
-__global__ void __launch_bounds__(kTcThreads, 2)
+__global__ void __launch_bounds__(kTcThreads, (D == 64 ? 2 : 1))
 tc_rows_inplace_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                        RowsSide side_a, RowsSide side_b, int nsides, float op_mul, TcSched sch, int m,
                        int* status) {
   using L = RowsSmem<D, MP>;
-  static_assert(D == 64 && MP == 64, "a dS tile must have the footprint of a gradient tile");
+  // a parked dS tile (MP = 64 columns) sits in the first 64 columns of the gradient tile of its rows
+  static_assert((D == 64 || D == 128) && MP == 64, "written for 64 landmark columns");
   constexpr int kGroup = kComputeThreads / 2;
   constexpr int kStages = L::kStages;
   constexpr uint32_t kTmemCols = kStages * D;
-  static_assert(kTmemCols == 256, "TMEM allocation must be a power of two");
+  static_assert(kTmemCols == 256 || kTmemCols == 512, "TMEM allocation must be a power of two");
   extern __shared__ uint8_t smem_raw[];
   pdl_trigger();
   if (smem_u32(smem_raw) & 1023u) {
@@ -730,8 +745,8 @@ tc_rows_inplace_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_co
     const int g = warp >> 2;
     const int r = threadIdx.x & 127;
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-    pack_landmark_operand<T>(s_op, side_a.landmarks + bh * m * D, m, op_mul);
-    if (nsides > 1) pack_landmark_operand<T>(s_op + L::kOp, side_b.landmarks + bh * m * D, m, op_mul);
+    pack_landmark_operand<T, D>(s_op, side_a.landmarks + bh * m * D, m, op_mul);
+    if (nsides > 1) pack_landmark_operand<T, D>(s_op + L::kOp, side_b.landmarks + bh * m * D, m, op_mul);
     fence_proxy_async();
     mbar_arrive_warp(small_full);
     const float mul_a = (side_a.out_scale ? side_a.out_scale[bh] : 1.f) * side_a.out_mul;
@@ -782,11 +797,11 @@ tc_rows_inplace_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_co
       if (leader) tma_store_wait_read();
       named_barrier(1 + g, kGroup);
 #pragma unroll
-      for (int hf = 0; hf < 2; ++hf) {
+      for (int hf = 0; hf < D / 32; ++hf) {
         float o[32];
         tmem_ld32(t_o + hf * 32, o);
         tmem_ld_wait();
-        if (hf == 1) {
+        if (hf == D / 32 - 1) {
           tc_fence_before();
           mbar_arrive_warp(o_free + s);
         }
@@ -801,7 +816,9 @@ tc_rows_inplace_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_co
       fence_proxy_async();
       named_barrier(1 + g, kGroup);
       if (leader) {
-        tma_store_3d_h(second ? &tm_b : &tm_a, my_out, 0, tile * kTile, (int)bh, second ? pol_ob : pol_oa);
+        for (int kb = 0; kb < D / 64; ++kb)
+          tma_store_3d_h(second ? &tm_b : &tm_a, my_out + kb * (kTile * 128), kb * 64, tile * kTile, (int)bh,
+                         second ? pol_ob : pol_oa);
         tma_store_commit();
       }
     }

@@ -11,9 +11,20 @@ from tests._util import errs, run_cuda, run_oracle
 
 pytestmark = pytest.mark.gpu
 
-OUT_TOL = {torch.float16: 2e-3, torch.bfloat16: 1.6e-2, torch.float32: 2e-4}
-GRAD_TOL = {torch.float16: 1e-2, torch.bfloat16: 8e-2, torch.float32: 2e-3}
+# bf16 (8-bit mantissa) bars are about twice what a B200 measures on these shapes (6.7e-3 / 1.2e-2)
+OUT_TOL = {torch.float16: 2e-3, torch.bfloat16: 1.4e-2, torch.float32: 2e-4}
+GRAD_TOL = {torch.float16: 1e-2, torch.bfloat16: 2.5e-2, torch.float32: 2e-3}
 STAGES = ["qt", "kt", "K2", "lse2", "k2inv", "bmat", "lse3", "step2", "lse1"]
+# Saved tensors.  Landmarks, K2, lse2 and the pseudoinverse are FP32 whatever the input dtype; Bmat,
+# lse3, step2 and lse1 pass through 16-bit tensor-core operands.  About three times the largest
+# error measured on a B200 over the shapes below.
+STAGE_TOL = {
+    torch.float32: dict.fromkeys(STAGES, 5e-5),
+    torch.float16: {"qt": 1e-5, "kt": 1e-5, "K2": 1e-5, "lse2": 1e-5, "k2inv": 5e-5, "bmat": 1e-3,
+                    "lse3": 2e-4, "step2": 3e-3, "lse1": 6e-4},
+    torch.bfloat16: {"qt": 1e-5, "kt": 1e-5, "K2": 1e-5, "lse2": 1e-5, "k2inv": 5e-5, "bmat": 1e-2,
+                     "lse3": 1e-3, "step2": 2e-2, "lse1": 6e-3},
+}
 
 # (B, H, N, D, m, J, kappa)
 SHAPES = [
@@ -53,6 +64,8 @@ def test_forward_backward_parity(cuda_device, shape, dtype):
     assert e["out"] <= OUT_TOL[dtype], e
     for key in ("dq", "dk", "dv"):
         assert e[key] <= GRAD_TOL[dtype], e
+    for key in STAGES:
+        assert e[key] <= STAGE_TOL[dtype][key], (key, e)
 
 
 def test_config1_fp32(cuda_device):

@@ -73,6 +73,26 @@ def test_config4_full_shape(cuda_device):
     _check_slices(cu, q, k, v, dO, m, J, kap, [0, 7, 12], 2e-3, 1e-2)
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_head_dim_128_full_shape(cuda_device, dtype):
+    """The shape of the reference's own latency tables: B=4, H=16, N=16384, D=128, m=64, J=6
+    (tensor-core path with one CTA per SM, several tiles per CTA); three of the 64 slices."""
+    B, H, N, D, m, J = 4, 16, 16384, 128, 64, 6
+    q, k, v, dO = O.make_inputs(B, H, N, D, seed=4, dtype=dtype)
+    cu = run_cuda(q, k, v, dO, m, J, 0.0)
+    bf = dtype == torch.bfloat16
+    _check_slices(cu, q, k, v, dO, m, J, 0.0, [0, 21, 63], 8e-3 if bf else 2e-3, 4e-2 if bf else 1e-2,
+                  stage_scale=8.0 if bf else 1.0)
+
+
+def test_head_dim_128_ragged_ridge(cuda_device):
+    """head_dim 128 with a ragged sequence, 40 landmarks (padded to 64) and the ridge."""
+    B, H, N, D, m, J, kap = 1, 3, 20011, 128, 40, 6, 5.0
+    q, k, v, dO = O.make_inputs(B, H, N, D, seed=6, dtype=torch.float16)
+    cu = run_cuda(q, k, v, dO, m, J, kap)
+    _check_slices(cu, q, k, v, dO, m, J, kap, [0, 2], 2e-3, 1e-2)
+
+
 def test_ragged_many_tiles(cuda_device):
     """N not a multiple of the tile, of the landmark count or of anything else; 33 landmarks
     (padded to 64 on the tensor-core path); seven slices; about ten tiles per CTA."""
