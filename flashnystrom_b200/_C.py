@@ -32,7 +32,19 @@ _flags = 0
 def set_force_generic(on: bool):
     """Route 16-bit inputs through the CUDA-core FP32 kernels too (verification aid)."""
     global _flags
-    _flags = _lib.FNB_FLAG_FORCE_GENERIC if on else 0
+    _flags = (_flags | _lib.FNB_FLAG_FORCE_GENERIC) if on else (_flags & ~_lib.FNB_FLAG_FORCE_GENERIC)
+
+
+def set_test_drop_load(on: bool):
+    """Tests only: make one CTA of the forward output pass skip the copy of its last tile, so that
+    a bounded device-side wait runs out (see FNB_FLAG_TEST_DROP_LOAD)."""
+    global _flags
+    _flags = (_flags | _lib.FNB_FLAG_TEST_DROP_LOAD) if on else (_flags & ~_lib.FNB_FLAG_TEST_DROP_LOAD)
+
+
+def set_wait_limit_ms(ms: int, device=0):
+    """Tests only: time limit of the bounded device-side waits (default 1500 ms)."""
+    _lib.check(_lib.load().fnb_debug_set_wait_limit_ms(int(device), int(ms)))
 
 
 def _shape_struct(B, H, N, D, m, J, dtype, kappa_star):
@@ -80,7 +92,12 @@ def check_device_status(device=None):
         val = int(t.item())
         if val != 0:
             t.zero_()
-            raise RuntimeError(f"flashnystrom_b200: a device-side wait timed out on cuda:{idx} "
+            code = (val >> 24) & 0xff
+            what = {1: "a device-side wait timed out",
+                    2: "a kernel's shared-memory window was misaligned",
+                    3: "a softmax-Jacobian value left the fp16 range in the backward and was clamped "
+                       "(use bf16 inputs or scale the incoming gradient down)"}.get(code, "a kernel reported an error")
+            raise RuntimeError(f"flashnystrom_b200: {what} on cuda:{idx} "
                                f"(status 0x{val & 0xffffffff:08x}); results of that call are invalid")
 
 

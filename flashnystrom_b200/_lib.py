@@ -12,6 +12,7 @@ LIB_PATH = os.path.join(_PKG, "lib", "libflashnystrom_b200.so")
 
 FNB_F32, FNB_F16, FNB_BF16 = 0, 1, 2
 FNB_FLAG_FORCE_GENERIC = 1
+FNB_FLAG_TEST_DROP_LOAD = 0x100
 
 
 class Shape(C.Structure):
@@ -80,6 +81,7 @@ SIGNATURES = {
     "fnb_pinv_backward_noalloc": (C.c_int, [C.c_int64, C.c_int32, C.c_int32, C.c_float, C.c_void_p,
                                             C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p]),
     "fnb_debug_pinv_workspace_bytes": (C.c_size_t, [C.c_int64, C.c_int32]),
+    "fnb_debug_set_wait_limit_ms": (C.c_int, [C.c_int, C.c_int]),
     "fnb_set_profiling": (C.c_int, [C.c_int]),
     "fnb_last_profile": (C.c_int, [C.POINTER(KernelTime), C.c_int]),
 }

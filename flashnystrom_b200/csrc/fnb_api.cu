@@ -241,6 +241,7 @@ struct BwdWs {
   void* op16[8];              // 16-bit operand copies for the tensor-core kernels
   float *st_scale, *do3_scale, *rows_q, *rows_k;
   float* partA_red;           // [BH][2][m][D]: pass-A partials summed over the chunks
+  float* tile_scale;          // [BH][ceil(N / 128)]: factor the column pass stored each dS' tile with
   size_t bytes;
 };
 static BwdWs carve_bwd(const Plan& p, void* base) {
@@ -262,6 +263,7 @@ static BwdWs carve_bwd(const Plan& p, void* base) {
   w.st_scale = take((size_t)p.BH); w.do3_scale = take((size_t)p.BH);
   w.rows_q = take(md); w.rows_k = take(md);
   w.partA_red = take(2 * md);
+  w.tile_scale = take((size_t)p.BH * (size_t)((p.N + 127) / 128));
   w.bytes = off;
   return w;
 }
@@ -368,15 +370,42 @@ static int forward_impl(const fnb_fwd_args& a, const Plan& p, const FwdWs& w, in
   sch_fb.hint = hint_bits(ef, ef, 0, 0);                 // K (left in L2 by the pooling pass) and V die here
   sch_fc.order = (l2 & 1) ? tc::kOrderStrided : 0;
   sch_fc.hint = hint_bits(el, 0, ef, 0);                 // Q is read again by the backward; O is not
+  sch_fc.test_drop = (a.shape.flags & FNB_FLAG_TEST_DROP_LOAD) ? 1 : 0;
   const int nchunk_b = use_tc ? sch.nchunk : p.nchunk;
   const size_t md_all = (size_t)p.BH * p.m * p.D, m_all = (size_t)p.BH * p.m;
 
   if (S.run(0)) {
-    L.begin();
-    int64_t grid = std::min<int64_t>(2 * p.BH * p.m * lmC, (int64_t)sms * 4);
-    launch_pdl(landmark_partial_kernel<T>, dim3((unsigned)grid), dim3(kThreads), 0, st, 
-        (const T*)a.q, (const T*)a.k, land, p.BH, p.N, p.D, p.m, lmC, seg_N, row_offset);
-    if (L.end("landmark_partial")) return L.status;
+    bool pooled = false;
+    if constexpr (k16) {
+      if (use_tc && (l2 & 64)) {
+        // TMA-fed pooling pass (16-bit inputs, head_dim 64 or 128); measured slower than the
+        // CUDA-core pass (67 against 59 us at B=1, H=16, N=65536), so off unless asked for
+        int rc = dispatch_head_dim(p.D, [&](auto dtag) -> int {
+          constexpr int D = decltype(dtag)::value;
+          CUtensorMap tm_q, tm_k;
+          if (!tc::make_map_3d(&tm_q, a.q, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
+              !tc::make_map_3d(&tm_k, a.k, a.shape.dtype, p.BH, p.N, D, tc::kTile))
+            return fail(FNB_ERR_CUDA, "cuTensorMapEncodeTiled failed for the pooling pass");
+          L.begin();
+          auto kern = tc::tc_pool_kernel<T, D>;
+          size_t smem = tc::PoolSmem<D>::kBytes;
+          if (int rc2 = set_smem(kern, smem, max_smem, "tc_pool")) return rc2;
+          const int64_t grid = std::min<int64_t>(2 * p.BH * p.m * lmC, (int64_t)sms * 2);
+          launch_pdl(kern, dim3((unsigned)grid), dim3(tc::kPoolThreads), smem, st, tm_q, tm_k, land, p.BH, p.N, p.m, lmC,
+                     seg_N, row_offset, a.device_status);
+          return L.end("tc_pool");
+        });
+        if (rc) return rc;
+        pooled = true;
+      }
+    }
+    if (!pooled) {
+      L.begin();
+      int64_t grid = std::min<int64_t>(2 * p.BH * p.m * lmC, (int64_t)sms * 4);
+      launch_pdl(landmark_partial_kernel<T>, dim3((unsigned)grid), dim3(kThreads), 0, st,
+          (const T*)a.q, (const T*)a.k, land, p.BH, p.N, p.D, p.m, lmC, seg_N, row_offset);
+      if (L.end("landmark_partial")) return L.status;
+    }
   }
   if (S.stage == 0) return 0;
 
@@ -584,6 +613,7 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
   }
   int kshift = 0;
   while ((int64_t(2) << kshift) <= seg_N && kshift < 14) ++kshift;   // floor(log2 N), at most 14
+  if (a.shape.dtype == FNB_BF16) kshift = 0;   // bf16 has the FP32 exponent range: no shift, nothing to clamp
   const int l2 = l2_mode();
   const int ef = (l2 & 2) ? 1 : 0, el = (l2 & 16) ? 2 : 0;
   const int strided = (l2 & 1) ? tc::kOrderStrided : 0;
@@ -762,10 +792,10 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
         const dim3 bgrid((unsigned)(p.BH * sch_b.nchunk));
         if (side_ns)   // an ordinary launch: it must not claim SMs before the Newton-Schulz kernel has its own
           kern<<<bgrid, tc::kTcThreads, sm, st>>>(tm_k, tm_v, tm_qt, tm_do3, tm_dk, tm_dv, a.lse3, w.D3, w.do3_scale, w.partB,
-                                                  sch_b, p.m, scale, kshift, a.device_status);
+                                                  w.tile_scale, sch_b, p.m, scale, kshift, a.device_status);
         else
           launch_pdl(kern, bgrid, dim3(tc::kTcThreads), sm, st, tm_k, tm_v, tm_qt, tm_do3, tm_dk, tm_dv, a.lse3, w.D3, w.do3_scale,
-                     w.partB, sch_b, p.m, scale, kshift, a.device_status);
+                     w.partB, w.tile_scale, sch_b, p.m, scale, kshift, a.device_status);
         return L.end("tc_bwd_b");
       });
       if (rc) return rc;
@@ -805,9 +835,10 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
       // (rows_q = s (dQt_ns + sum of partials) / len), so no separate reduction kernel runs.
       // The dQ side keeps contiguous runs of tiles (a CTA sums the partials of the landmarks its own
       // run touches); the dK side follows the column pass backwards.
-      tc::RowsSide side_q{a.k_landmarks, w.rows_q, w.st_scale, tc::kLn2, partB_src, w.dqt_ns, partB_chunks, scale, 0};
+      tc::RowsSide side_q{a.k_landmarks, w.rows_q, w.st_scale, tc::kLn2, partB_src, w.dqt_ns, partB_chunks, scale, 0, nullptr};
       tc::RowsSide side_k{a.q_landmarks, w.rows_k, nullptr, exp2f(-(float)kshift) * tc::kLn2, nullptr, nullptr, 0, 0.f,
-                          ((l2 & 4) ? tc::kOrderDescending : 0) | (((l2 & 4) && strided) ? tc::kOrderStrided : 0)};
+                          ((l2 & 4) ? tc::kOrderDescending : 0) | (((l2 & 4) && strided) ? tc::kOrderStrided : 0),
+                          w.tile_scale};
       sch_c.hint = hint_bits(ef, ef, ef, ef);   // parked tiles are dead once read, dQ / dK are final
       // (after the join with the side stream the event wait stays a full dependency; only the
       // dependency on the column pass is the programmatic one, as for the combine step of the forward)
@@ -1234,6 +1265,15 @@ __attribute__((visibility("default"))) int fnb_debug_tc_trace(long long* out, in
   return cudaMemcpyFromSymbol(out, tc::g_tc_trace, sizeof(long long) * 8 * 256) == cudaSuccess ? 0 : -1;
 }
 #endif
+
+int fnb_debug_set_wait_limit_ms(int device, int ms) {
+  if (ms < 1 || ms > 10000) return fail(FNB_ERR_INVALID_ARGUMENT, "wait limit must be 1..10000 ms, got %d", ms);
+  DeviceGuard g(device);
+  if (!g.ok) return fail(FNB_ERR_CUDA, "cannot select CUDA device %d", device);
+  const unsigned long long ns = (unsigned long long)ms * 1000000ull;
+  FNB_CUDA(cudaMemcpyToSymbol(tc::g_wait_limit_ns, &ns, sizeof(ns)));
+  return 0;
+}
 
 int fnb_set_profiling(int mode) {
   int prev = g_profile;

@@ -381,8 +381,11 @@ __global__ void __launch_bounds__(kThreads) combine_slab_kernel(CombineSlabParam
     const float* pacc = p.part_acc + bh * p.acc_bh_stride + (size_t)l * D + d0;
     const float* pmax = p.part_max + bh * p.vec_bh_stride + l;
     const float* psum = p.part_sum + bh * p.vec_bh_stride + l;
+    // with at most kSlabMaxChunks chunks (the usual case) the maxima come out of the one batch of
+    // loads below; otherwise a first sweep finds them
     float M = -INFINITY;
-    for (int c = 0; c < nc; ++c) M = fmaxf(M, pmax[c * p.vec_chunk_stride]);
+    if (nc > kSlabMaxChunks)
+      for (int c = 0; c < nc; ++c) M = fmaxf(M, pmax[c * p.vec_chunk_stride]);
     float Lsum = 0.f;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int c0 = 0; c0 < nc; c0 += kSlabMaxChunks) {
@@ -394,6 +397,10 @@ __global__ void __launch_bounds__(kThreads) combine_slab_kernel(CombineSlabParam
         x[i] = *reinterpret_cast<const float4*>(pacc + (size_t)c * p.acc_chunk_stride);
         wgt[i] = pmax[c * p.vec_chunk_stride];
         ps[i] = psum[c * p.vec_chunk_stride];
+      }
+      if (nc <= kSlabMaxChunks) {
+#pragma unroll
+        for (int i = 0; i < kSlabMaxChunks; ++i) M = fmaxf(M, wgt[i]);   // entries past nc repeat the last chunk
       }
 #pragma unroll
       for (int i = 0; i < kSlabMaxChunks; ++i) {

@@ -16,7 +16,11 @@ namespace tc {
 // caller's status word, raises a CTA-wide abort flag so every other role leaves its loop, and
 // falls through to the common teardown (TMEM is always released).
 constexpr uint64_t kWaitLimitNs = 1500000000ull;  // 1.5 s per wait
-constexpr int kStatusTimeout = 1;
+constexpr int kStatusTimeout = 1;   // a bounded wait ran out
+constexpr int kStatusSmemAlign = 2; // the dynamic shared-memory window is not 1024-byte aligned
+constexpr int kStatusRange = 3;     // a 16-bit operand copy left the fp16 range and was clamped
+// The limit every bounded wait uses; a test shortens it through fnb_debug_set_wait_limit_ms.
+__device__ unsigned long long g_wait_limit_ns = kWaitLimitNs;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return (uint32_t)__cvta_generic_to_shared(p);
@@ -80,7 +84,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
       if (ab.raised()) return false;
       const uint64_t now = global_ns();
       if (t0 == 0) t0 = now;
-      else if (now - t0 > kWaitLimitNs) break;
+      else if (now - t0 > g_wait_limit_ns) break;
     }
   }
   ab.raise(where);
@@ -91,7 +95,7 @@ __device__ __forceinline__ void mbar_drain(uint64_t* bar, uint32_t parity) {
   const uint64_t t0 = global_ns();
   for (uint32_t spin = 0;; ++spin) {
     if (mbar_try(bar, parity)) return;
-    if ((spin & 63u) == 63u && global_ns() - t0 > kWaitLimitNs) return;
+    if ((spin & 63u) == 63u && global_ns() - t0 > g_wait_limit_ns) return;
   }
 }
 
@@ -215,6 +219,20 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
         "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr)
       : "memory");
+}
+// 32 lanes x 8 consecutive 32-bit columns (load and store): small register footprint for rare paths
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, float* v) {
+  uint32_t* r = reinterpret_cast<uint32_t*>(v);
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "r"(taddr)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const float* v) {
+  const uint32_t* r = reinterpret_cast<const uint32_t*>(v);
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+               ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+               : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 // store counterpart of tmem_ld32

@@ -68,6 +68,7 @@ inline TcSched make_sched(int64_t BH, int64_t N, int slots) {
   s.row_offset = 0;
   s.order = 0;
   s.hint = 0;
+  s.test_drop = 0;
   int64_t tiles = (N + kTile - 1) / kTile;
   int64_t want = slots / BH;            // floor: BH * want <= slots
   if (want > tiles) want = tiles;

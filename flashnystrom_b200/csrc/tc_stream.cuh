@@ -11,6 +11,7 @@
 // landmark-sized operands (m x D, padded to MP = 64 or 128 landmarks) are packed once per call
 // into 16-bit copies and stay resident in shared memory for the whole CTA.
 #pragma once
+#include <type_traits>
 #include "common.cuh"
 #include "small_kernels.cuh"
 #include "tc_common.cuh"
@@ -55,6 +56,8 @@ struct TcSched {
   // in the stream ended finds that data still in L2).
   int order;
   int hint;              // L2 eviction hints, two bits per operand slot (tc_common.cuh: l2_policy_of)
+  int test_drop;         // test only: the output pass's first CTA never issues the load of its last tile,
+                         //   so that a bounded wait runs out (FNB_FLAG_TEST_DROP_LOAD)
 };
 constexpr int kOrderStrided = 1, kOrderDescending = 2;
 
@@ -164,6 +167,141 @@ __device__ __forceinline__ TileRange tile_range(const TcSched& sch, int order) {
 __device__ __forceinline__ TileRange tile_range(const TcSched& sch) { return tile_range(sch, sch.order); }
 
 // ------------------------------------------------------------------------------------------
+// Landmark pooling pass: raw segment sums of Q and K, fed by TMA.
+//   out[which][bh][l][c][D]  (which = 0: Q, 1: K; c: chunk of the landmark's segment)
+// A persistent grid walks the work items (which, bh, landmark, chunk); the producer warp streams
+// the 128-row tiles of one item after another through a ring of kStages tiles, running ahead
+// across item boundaries, and the eight consumer warps add up the rows of each tile from shared
+// memory in FP32 (a warp reads one 128-byte row per instruction: conflict-free whatever the
+// swizzle).  Tiles start at the item's first row, so rows past the item's end (the next chunk's
+// rows, or zero fill past the slice) are simply not added.
+template <int D>
+struct PoolSmem {
+  static constexpr int kTileBytes = kTile * D * 2;
+  static constexpr int kStages = D == 64 ? 6 : 3;
+  static constexpr int kScratch = 2 * 8 * D * 4;     // per-warp partial rows, double-buffered by item parity
+  static constexpr int kBytes = kStages * kTileBytes + kScratch + 256 + 1024;
+};
+constexpr int kPoolThreads = 288;   // 8 consumer warps + the producer warp
+
+template <class T, int D>
+__global__ void __launch_bounds__(kPoolThreads, 2)
+tc_pool_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+               float* __restrict__ out, int64_t BH, int64_t N, int m, int C, int64_t seg_N, int64_t row_offset,
+               int* status) {
+  using L = PoolSmem<D>;
+  constexpr int KBD = D / 64, S = L::kStages;
+  extern __shared__ uint8_t smem_raw[];
+  pdl_trigger();
+  uint8_t* base = align1024(smem_raw);
+  uint8_t* s_tile = base;
+  float* s_part = reinterpret_cast<float*>(s_tile + S * L::kTileBytes);   // [2][8][D]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(s_part) + L::kScratch);
+  uint64_t* full = bars;          // [S]
+  uint64_t* empty = bars + S;     // [S]
+  int* abort_word = reinterpret_cast<int*>(bars + 2 * S);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, 8); }
+    *abort_word = 0;
+    fence_mbar_init();
+  }
+  __syncthreads();
+  pdl_wait();
+  Abort ab{abort_word, status};
+  const int64_t per_which = BH * m * C, items = 2 * per_which;
+  Segments sg(seg_N, m);
+  // rows [r0, r1) of this rank's slice that item `item` covers
+  auto item_rows = [&](int64_t item, int& which, int64_t& bh, int64_t& r0, int64_t& r1) {
+    which = (int)(item / per_which);
+    const int64_t rest = item - which * per_which;
+    bh = rest / (m * C);
+    const int lc = (int)(rest - bh * (m * C));
+    const int l = lc / C, c = lc - l * C;
+    int64_t start = sg.start(l) - row_offset, end = sg.end(l) - row_offset;
+    if (start < 0) start = 0;
+    if (end > N) end = N;
+    const int64_t len = end > start ? end - start : 0;
+    const int64_t per = (len + C - 1) / C;
+    r0 = start + c * per;
+    r1 = r0 + per;
+    if (r1 > start + len) r1 = start + len;
+    if (r1 < r0) r1 = r0;
+  };
+  if (warp == 8) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tm_q);
+      tma_prefetch_desc(&tm_k);
+      uint32_t g = 0;
+      bool ok = true;
+      for (int64_t item = blockIdx.x; ok && item < items; item += gridDim.x) {
+        int which; int64_t bh, r0, r1;
+        item_rows(item, which, bh, r0, r1);
+        for (int64_t r = r0; r < r1; r += kTile, ++g) {
+          const int st = (int)(g % S);
+          if (!mbar_wait(empty + st, ((g / S) & 1) ^ 1, ab, 0x4100)) { ok = false; break; }
+          mbar_expect_tx(full + st, L::kTileBytes);
+          for (int kb = 0; kb < KBD; ++kb)
+            tma_load_3d(s_tile + st * L::kTileBytes + kb * (kTile * 128), which ? &tm_k : &tm_q, full + st, kb * 64, (int)r,
+                        (int)bh);
+        }
+      }
+      if (ab.raised()) {   // let copies already in flight land before the shared memory is released
+        const uint32_t lo = g > (uint32_t)S ? g - S : 0;
+        for (uint32_t i = lo; i < g; ++i) mbar_drain(full + (i % S), (i / S) & 1);
+      }
+    }
+  } else {
+    uint32_t g = 0;
+    int par = 0;
+    bool ok = true;
+    for (int64_t item = blockIdx.x; item < items; item += gridDim.x, par ^= 1) {
+      int which; int64_t bh, r0, r1;
+      item_rows(item, which, bh, r0, r1);
+      float acc[KBD][2];
+#pragma unroll
+      for (int kb = 0; kb < KBD; ++kb) acc[kb][0] = acc[kb][1] = 0.f;
+      for (int64_t r = r0; ok && r < r1; r += kTile, ++g) {
+        const int st = (int)(g % S);
+        if (!mbar_wait(full + st, (g / S) & 1, ab, 0x4200)) { ok = false; break; }
+        const int valid = (r1 - r) < (int64_t)kTile ? (int)(r1 - r) : kTile;
+        const uint8_t* tile = s_tile + st * L::kTileBytes;
+#pragma unroll
+        for (int rr = 0; rr < kTile / 8; ++rr) {
+          const int row = warp * (kTile / 8) + rr;
+          if (row < valid) {
+#pragma unroll
+            for (int kb = 0; kb < KBD; ++kb) {
+              const uint32_t w = *reinterpret_cast<const uint32_t*>(tile + kb * (kTile * 128) + sw128_offset(row, lane >> 2) +
+                                                                    (lane & 3) * 4);
+              const T* e = reinterpret_cast<const T*>(&w);
+              acc[kb][0] += to_f<T>(e[0]);
+              acc[kb][1] += to_f<T>(e[1]);
+            }
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty + st);
+      }
+      // fold the eight warps: this item's sums for columns 64 kb + 2 lane, + 1
+      float* part = s_part + par * 8 * D;
+#pragma unroll
+      for (int kb = 0; kb < KBD; ++kb)
+        *reinterpret_cast<float2*>(part + warp * D + kb * 64 + 2 * lane) = make_float2(acc[kb][0], acc[kb][1]);
+      named_barrier(1, 256);
+      if (threadIdx.x < D) {
+        float s = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) s += part[w * D + threadIdx.x];
+        if (ok) out[(size_t)item * D + threadIdx.x] = s;
+      }
+      // (the other half of the scratch serves the next item; this half is rewritten two items
+      // later, after another pass through the barrier above)
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------
 // Forward output pass:  O = softmax(Q Kt^T) step2, lse1.
 //   kt16 = s*log2e*Kt (MP x D), st16 = step2^T / 2^e (D x MP), st_scale[bh] = 2^e.
 // The eight compute warps form two groups of 128 threads (one thread per tile row, all landmark
@@ -242,6 +380,7 @@ tc_fwd_c_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       for (int i = 0; i < count; ++i) {
         const int st = i & 1;
         if (!mbar_wait(q_empty + st, ((i >> 1) & 1) ^ 1, ab, 0x100 + i)) break;
+        if (sch.test_drop && blockIdx.x == 0 && i == count - 1) break;   // fault injection on the host's request
         mbar_expect_tx(q_full + st, L::kQ);
         for (int kb = 0; kb < KBD; ++kb)
           tma_load_3d_h(s_q + st * L::kQ + kb * (kTile * 128), &tm_q, q_full + st, kb * 64, tr.tile(i) * kTile, (int)bh, pol_q);
@@ -556,6 +695,8 @@ tc_bwd_a_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       store_cols<T, HC>(s_p, r, c0, p);
 #pragma unroll
       for (int j = 0; j < HC; ++j) g[j] = p[j] * (g[j] - d1);
+      // (dS1 / sc leaves the fp16 range only for |dO| of several hundred and more; it then becomes
+      // inf and dQ comes back inf / NaN, which is what a loss scaler looks for)
       store_cols<T, HC>(s_ds, r, c0, g);
       fence_proxy_async();
       tc_fence_before();
@@ -612,6 +753,7 @@ struct RowsSide {
   int nchunk;
   float rows_scale;
   int order;                // tile order of this side (kOrderStrided | kOrderDescending)
+  const float* tile_scale;  // [BH][tiles] or null: extra factor of the product, per tile
 };
 
 template <int D, int MP>
@@ -753,6 +895,7 @@ tc_rows_inplace_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_co
     const float mul_b = nsides > 1 ? (side_b.out_scale ? side_b.out_scale[bh] : 1.f) * side_b.out_mul : 0.f;
     uint8_t* my_out = s_out + g * L::kOut;
     const bool leader = r == 0;
+    const int64_t total_tiles = (sch.N + kTile - 1) / kTile;
     const uint64_t pol_oa = leader ? l2_policy_of(sch.hint, 2) : 0ull, pol_ob = leader ? l2_policy_of(sch.hint, 3) : 0ull;
     Segments sg(sch.seg_N, m);
     // the landmark rows of this CTA's tiles on a side whose rows still wait for the column-pass
@@ -788,7 +931,8 @@ tc_rows_inplace_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_co
       const bool valid = row < sch.N;
       const int l = valid ? sg.landmark_of(sch.row_offset + row) : 0;
       const float4* add = reinterpret_cast<const float4*>((second ? side_b.rows : side_a.rows) + (bh * m + l) * D);
-      const float mul = second ? mul_b : mul_a;
+      const float* tsc = second ? side_b.tile_scale : side_a.tile_scale;
+      const float mul = (second ? mul_b : mul_a) * (tsc ? tsc[bh * total_tiles + tile] : 1.f);
       const uint32_t t_o = tmem_base + s * D + lane_base;
       if (!mbar_wait(acc_done + s, par, ab, 0x2800 + i)) break;
       __syncwarp();
@@ -852,13 +996,14 @@ struct BwdBSmem {
 };
 
 template <class T, int D, int MP>
-__global__ void __launch_bounds__(kTcThreads, 2)
+__global__ void __launch_bounds__(kTcThreads, (D == 64 ? 2 : 1))
 tc_bwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                 const __grid_constant__ CUtensorMap tm_qt, const __grid_constant__ CUtensorMap tm_do3,
                 const __grid_constant__ CUtensorMap tm_dk, const __grid_constant__ CUtensorMap tm_dv,
                 const float* __restrict__ lse3, const float* __restrict__ D3,
                 const float* __restrict__ do3_scale,
-                float* __restrict__ partB, TcSched sch, int m, float scale, int kshift, int* status) {
+                float* __restrict__ partB, float* __restrict__ tile_scale, TcSched sch, int m, float scale, int kshift,
+                int* status) {
   using L = BwdBSmem<D, MP>;
   constexpr int KBD = D / 64, HC = MP / 2, HD = D / 2;
   constexpr int W = MP > D ? MP : D;
@@ -885,6 +1030,7 @@ tc_bwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
   uint64_t* pds_full = bars + 8;
   uint64_t* out_full = bars + 9;
   uint64_t* o_free = bars + 10;
+  unsigned* s_tmax = reinterpret_cast<unsigned*>(bars + 12);   // [2]: largest |dS'| of a tile (float bits), by tile parity
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
   int* abort_word = reinterpret_cast<int*>(tmem_slot + 1);
 
@@ -902,6 +1048,7 @@ tc_bwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
     mbar_init(out_full, 1);
     mbar_init(o_free, kComputeThreads / 32);
     *abort_word = 0;
+    s_tmax[0] = 0; s_tmax[1] = 0;
     fence_mbar_init();
   }
   if (warp == 0) {
@@ -999,10 +1146,14 @@ tc_bwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
     if (threadIdx.x < MP) {
       const int j = threadIdx.x;
       s_c3[j] = (j < m) ? lse3[bh * m + j] * kLog2e - (float)kshift : INFINITY;
-      s_d3[j] = (j < m) ? D3[bh * m + j] : 0.f;
+      s_d3[j] = (j < m) ? D3[bh * m + j] : 0.f;   // times frun (below), which starts at 1
     }
     named_barrier(1, kComputeThreads);
     bool alive = true;
+    // running power-of-two factor of the stored dS' tiles (fp16 only; see below), folded into the
+    // two constants dS' is formed from
+    float frun = 1.f, dscf = dsc;
+    const int64_t total_tiles = (sch.N + kTile - 1) / kTile;
     for (int i = 0; i < count; ++i) {
       const int64_t row = (int64_t)tr.tile(i) * kTile + r;
       const bool valid = row < sch.N;
@@ -1021,14 +1172,60 @@ tc_bwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
         p[j + 1] = valid ? fast_exp2(p[j + 1] - c.y) : 0.f;
         p[j + 2] = valid ? fast_exp2(p[j + 2] - c.z) : 0.f;
         p[j + 3] = valid ? fast_exp2(p[j + 3] - c.w) : 0.f;
-        g[j + 0] = fminf(fmaxf(p[j + 0] * fmaf(g[j + 0], dsc, -d.x), -60000.f), 60000.f);
-        g[j + 1] = fminf(fmaxf(p[j + 1] * fmaf(g[j + 1], dsc, -d.y), -60000.f), 60000.f);
-        g[j + 2] = fminf(fmaxf(p[j + 2] * fmaf(g[j + 2], dsc, -d.z), -60000.f), 60000.f);
-        g[j + 3] = fminf(fmaxf(p[j + 3] * fmaf(g[j + 3], dsc, -d.w), -60000.f), 60000.f);
+        g[j + 0] = p[j + 0] * fmaf(g[j + 0], dscf, -d.x);
+        g[j + 1] = p[j + 1] * fmaf(g[j + 1], dscf, -d.y);
+        g[j + 2] = p[j + 2] * fmaf(g[j + 2], dscf, -d.z);
+        g[j + 3] = p[j + 3] * fmaf(g[j + 3], dscf, -d.w);
+      }
+      // fp16 only: the 16-bit copy of dS' = f 2^k P3 (dP3 - D3) must stay inside the fp16 range whatever
+      // the data (a peaked softmax-3 makes P3 ~ 1, an unnormalised dO makes dP3 large).  Every tile
+      // finds its largest magnitude (one redux per warp, one shared atomic, the barrier that is
+      // needed anyway); when it would pass 2^15 the CTA lowers its running power-of-two factor f,
+      // rescales the dQt accumulator it has built so far by the same ratio and goes on.  f only
+      // ever falls, so nothing overflows; the factor each tile was stored with goes to global
+      // memory for the in-place pass that turns the tile into dK.
+      if (std::is_same<T, __half>::value) {
+        float big = 0.f;
+#pragma unroll
+        for (int j = 0; j < HC; j += 2) big = fmaxf(big, fmaxf(fabsf(g[j]), fabsf(g[j + 1])));
+        const unsigned wb = __reduce_max_sync(0xffffffffu, __float_as_uint(big));
+        if (lane == 0) atomicMax(s_tmax + (i & 1), wb);
       }
       // the staging copies of the previous tile's dV / dK share these buffers
-      if (threadIdx.x == 0) tma_store_wait_read();
+      if (threadIdx.x == 0) {
+        tma_store_wait_read();
+        s_tmax[(i + 1) & 1] = 0;   // read for the last time before the previous tile's second barrier
+      }
       named_barrier(1, kComputeThreads);
+      if (std::is_same<T, __half>::value) {
+        const float tmax = __uint_as_float(s_tmax[i & 1]);   // CTA-uniform, already times frun
+        if (!(tmax <= 32768.f)) {
+          // non-finite input: reported; the values go through as they are
+          if (!(tmax < 1e30f) && status) atomicCAS(status, 0, (kStatusRange << 24) | 0x2b00);
+          // tmax = 1.x * 2^(E - 127) < 2^(E - 126): ratio = 2^(15 - (E - 126)) brings it below 2^15
+          const uint32_t E = (s_tmax[i & 1] >> 23) & 0xffu;
+          const float ratio = __uint_as_float((268u - E) << 23);   // < 1: new factor = ratio * frun
+#pragma unroll
+          for (int j = 0; j < HC; ++j) g[j] *= ratio;
+          if (i > 0) {
+            for (int cc = 0; cc < HD; cc += 8) {    // eight columns at a time: this path is rare, registers are not
+              float o[8];
+              tmem_ld8(tmem_acc + lane_base + h * HD + cc, o);
+              tmem_ld_wait();
+#pragma unroll
+              for (int j = 0; j < 8; ++j) o[j] *= ratio;
+              tmem_st8(tmem_acc + lane_base + h * HD + cc, o);
+            }
+            tmem_st_wait();
+          }
+          // every thread has read s_d3 for this tile (barrier above); the next read comes after the
+          // barrier that ends this tile
+          if (threadIdx.x < MP) s_d3[threadIdx.x] *= ratio;
+          frun *= ratio;
+          dscf *= ratio;
+        }
+      }
+      if (threadIdx.x == 0 && tile_scale) tile_scale[bh * total_tiles + tr.tile(i)] = 1.f / frun;
       store_cols<T, HC>(s_p, r, c0, p);
       store_cols<T, HC>(s_ds, r, c0, g);
       fence_proxy_async();
@@ -1063,7 +1260,7 @@ tc_bwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
       const int l = (MP == 128) ? r : (quarter * 16 + lane);
       const bool owner = (MP == 128) ? true : (lane < 16);
       float* dst = partB + ((size_t)bh * sch.nchunk + tr.chunk) * m * D;
-      const float mul = scale * unshift;
+      const float mul = scale * unshift / frun;
       float o[HD];
       ld_cols<HD>(tmem_acc + lane_base + h * HD, o);
       tmem_ld_wait();
@@ -1099,7 +1296,7 @@ struct FwdBSmem {
 };
 
 template <class T, int D, int MP>
-__global__ void __launch_bounds__(kTcThreads, 2)
+__global__ void __launch_bounds__(kTcThreads, (D == 64 ? 2 : 1))
 tc_fwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                 const __grid_constant__ CUtensorMap tm_qt, const float* __restrict__ land, int land_chunks,
                 int64_t land_bh, float scale, float* __restrict__ part_acc,

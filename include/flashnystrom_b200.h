@@ -46,6 +46,11 @@ enum fnb_dtype { FNB_F32 = 0, FNB_F16 = 1, FNB_BF16 = 2 };
 #define FNB_FLAG_FORCE_GENERIC 1u /* use the CUDA-core FP32 kernels even where a tensor-core
                                      kernel exists (verification, like the reference's
                                      FP32 scalar twins csrc/kernels/kernel1_scalar.cuh:18-92) */
+#define FNB_FLAG_TEST_DROP_LOAD 0x100u /* tests only: in fnb_forward on the tensor-core path one CTA
+                                     of the output pass never issues the copy of its last tile, so
+                                     a bounded device-side wait runs out; the call still returns,
+                                     `out` is invalid and the status word is set.  No counterpart
+                                     in the reference (its kernels have no waits to bound). */
 
 /* Problem description shared by all entry points.
  * Mirrors the scalar fields of NystromParams (csrc/flash_nystrom.h:21-88). */
@@ -84,8 +89,17 @@ typedef struct fnb_fwd_args {
   size_t workspace_bytes;
   int32_t device;       /* CUDA device ordinal all pointers live on                   */
   void* stream;         /* cudaStream_t                                               */
-  int32_t* device_status; /* optional device word, zeroed by the caller: a kernel whose
-                             bounded wait expired stores (1<<24 | location) here        */
+  int32_t* device_status; /* optional device word, zeroed by the caller.  The first kernel that
+                             meets one of these conditions stores (code<<24 | location):
+                               1  a bounded device-side wait ran out (results invalid; the
+                                  kernel released its resources and returned)
+                               2  the kernel's shared-memory window was not 1024-byte aligned
+                               3  fp16 only: a softmax-Jacobian value left the fp16 range in the
+                                  backward column pass and was clamped (dK, dQ saturated;
+                                  bf16 and fp32 inputs cannot hit this)
+                             The library never synchronises, so it cannot return
+                             FNB_ERR_DEVICE_STATUS itself: the host reads the word after the
+                             stream has drained (the Python shim's check_device_status). */
 } fnb_fwd_args;
 
 /* Backward.  Replaces nystrom_bwd + run_nystrom_bwd_impl (csrc/flash_nystrom.cu:177-415,
@@ -215,6 +229,11 @@ FNB_API size_t fnb_debug_pinv_workspace_bytes(int64_t bh, int32_t m);
 FNB_API int fnb_pinv_backward_noalloc(int64_t bh, int32_t m, int32_t newton_iter, float kappa_star,
                                       const float* k2, const float* ns_iterates, const float* d_k2_inv,
                                       float* d_k2, int32_t device, void* stream);
+
+/* Tests only: the time limit of every bounded device-side wait on `device` (default 1500 ms),
+ * so that a test of the expiry path does not take seconds.  1..10000 ms.  No counterpart in the
+ * reference. */
+FNB_API int fnb_debug_set_wait_limit_ms(int device, int ms);
 
 /* Per-kernel timing.  Off unless the environment variable FNB_PROFILE=1 was set when the
  * library was loaded or fnb_set_profiling(1) was called (process-wide switch; returns the
