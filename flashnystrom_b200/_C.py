@@ -20,6 +20,7 @@ All work is enqueued on torch's current stream of the inputs' device; nothing sy
 """
 import ctypes as C
 import math
+import os as _os
 
 import torch
 
@@ -178,6 +179,11 @@ def backward(dO, q_s, k_s, q_tilde, k_tilde, kernel2_inv, step2, lse1, lse2, lse
                             _ptr(dk), _ptr(dv), _ptr(ws), ws.numel(), dev.index,
                             C.c_void_p(torch.cuda.current_stream(dev).cuda_stream), _ptr(_status(dev)))
         _lib.check(lib.fnb_backward(C.byref(args)))
+    if _os.environ.get("FNB_BWD_DEBUG"):   # per-stage statistics, as FN_BWD_DEBUG does in the reference
+        for name, st in tensor_stats(dO=dO, dQ=dq, dK=dk, dV=dv, step2=step2, k2inv=kernel2_inv).items():
+            print(f"[FNB_BWD_DEBUG] {name}: absmax={st['absmax']:.4e} absmean={st['absmean']:.4e} "
+                  f"nonfinite={st['nonfinite']}")
+        check_device_status(dev)
     return [dq, dk, dv]
 
 
@@ -221,6 +227,63 @@ def debug_pinv_backward(k2, ns_iterates, d_k2_inv, kappa_star=0.0):
                                                _ptr(ws), ws.numel(), dev.index,
                                                C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)))
     return dk2
+
+
+def debug_ns_bwd_step(K2, Z_j, dZ_in):
+    """One backward iteration of the Newton-Schulz unroll on the product's tensor-core kernel: the
+    reference's debug_ns_bwd_step (csrc/flash_nystrom.cu:422-456).  (BH, m, m) FP32 tensors,
+    m <= 64.  Returns [dZ_out, dK2_acc]: dL/dZ_j and this iteration's contribution to dL/dK2."""
+    lib = _lib.load()
+    for t, name in ((K2, "K2"), (Z_j, "Z_j"), (dZ_in, "dZ_in")):
+        _check_big(t, name, dtype=torch.float32)
+    if K2.dim() != 3 or K2.shape[1] != K2.shape[2] or Z_j.shape != K2.shape or dZ_in.shape != K2.shape:
+        raise RuntimeError("K2, Z_j, dZ_in must all have shape (BH, m, m)")
+    BH, m, _ = K2.shape
+    dev = K2.device
+    with torch.cuda.device(dev):
+        dZ_out, dK2_acc = torch.empty_like(K2), torch.empty_like(K2)
+        _lib.check(lib.fnb_debug_ns_bwd_step(BH, m, _ptr(K2), _ptr(Z_j), _ptr(dZ_in), _ptr(dZ_out), _ptr(dK2_acc),
+                                             dev.index, C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)))
+    return [dZ_out, dK2_acc]
+
+
+def debug_ns_bwd_final(q_tilde, k_tilde, K2, dZ0, dK2_in):
+    """The tail of the backward in isolation: the reference's debug_ns_bwd_final
+    (csrc/flash_nystrom.cu:474-520).  q_tilde, k_tilde (BH, m, D); K2, dZ0, dK2_in (BH, m, m); FP32,
+    m <= 64.  Returns [dQ_tilde, dK_tilde, dK2] with dK2 = dK2_in plus the Z0 terms."""
+    lib = _lib.load()
+    for t, name in ((q_tilde, "q_tilde"), (k_tilde, "k_tilde"), (K2, "K2"), (dZ0, "dZ0"), (dK2_in, "dK2_in")):
+        _check_big(t, name, dtype=torch.float32)
+    BH, m, D = q_tilde.shape
+    dev = K2.device
+    with torch.cuda.device(dev):
+        dq, dk, dk2 = torch.empty_like(q_tilde), torch.empty_like(k_tilde), torch.empty_like(K2)
+        zeros = torch.zeros(m, D, dtype=torch.float32, device=dev)
+        _lib.check(lib.fnb_debug_ns_bwd_final(BH, m, D, _ptr(q_tilde), _ptr(k_tilde), _ptr(K2), _ptr(dZ0), _ptr(dK2_in),
+                                              _ptr(zeros), _ptr(dq), _ptr(dk), _ptr(dk2), dev.index,
+                                              C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)))
+    return [dq, dk, dk2]
+
+
+def probe_occupancy(device=0):
+    """Registers, shared memory, spill bytes and resident CTAs per SM of the hot-path kernels, like
+    the reference's probe_occupancy (csrc/occupancy_probe.h:89-142).  List of dicts."""
+    lib = _lib.load()
+    buf = (_lib.KernelInfo * 32)()
+    n = lib.fnb_kernel_report(int(device), buf, 32)
+    return [{f: (getattr(buf[i], f).decode() if f == "name" else getattr(buf[i], f)) for f, _ in _lib.KernelInfo._fields_}
+            for i in range(n)]
+
+
+def tensor_stats(**tensors):
+    """abs-max, abs-mean and non-finite count per tensor (synchronises): what the reference prints
+    with FN_BWD_DEBUG set (csrc/flash_nystrom.cu:392-408)."""
+    out = {}
+    for name, t in tensors.items():
+        f = t.detach().float()
+        out[name] = {"absmax": float(f.abs().max()), "absmean": float(f.abs().mean()),
+                     "nonfinite": int((~torch.isfinite(f)).sum())}
+    return out
 
 
 def pinv_backward_noalloc(k2, ns_iterates, d_k2_inv, out, kappa_star=0.0):

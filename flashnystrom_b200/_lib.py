@@ -59,6 +59,12 @@ class KernelTime(C.Structure):
     _fields_ = [("name", C.c_char * 48), ("ms", C.c_float)]
 
 
+class KernelInfo(C.Structure):
+    _fields_ = [("name", C.c_char * 48), ("registers", C.c_int32), ("static_smem_bytes", C.c_int32),
+                ("dynamic_smem_bytes", C.c_int32), ("local_bytes_per_thread", C.c_int32),
+                ("threads", C.c_int32), ("blocks_per_sm", C.c_int32)]
+
+
 # every symbol include/flashnystrom_b200.h declares, with its ctypes signature
 SIGNATURES = {
     "fnb_last_error": (C.c_char_p, []),
@@ -82,6 +88,12 @@ SIGNATURES = {
                                             C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p]),
     "fnb_debug_pinv_workspace_bytes": (C.c_size_t, [C.c_int64, C.c_int32]),
     "fnb_debug_set_wait_limit_ms": (C.c_int, [C.c_int, C.c_int]),
+    "fnb_debug_ns_bwd_step": (C.c_int, [C.c_int64, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                        C.c_void_p, C.c_int32, C.c_void_p]),
+    "fnb_debug_ns_bwd_final": (C.c_int, [C.c_int64, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p,
+                                         C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                         C.c_int32, C.c_void_p]),
+    "fnb_kernel_report": (C.c_int, [C.c_int, C.POINTER(KernelInfo), C.c_int]),
     "fnb_set_profiling": (C.c_int, [C.c_int]),
     "fnb_last_profile": (C.c_int, [C.POINTER(KernelTime), C.c_int]),
 }

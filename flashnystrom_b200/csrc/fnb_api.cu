@@ -1197,7 +1197,7 @@ int fnb_debug_pinv_backward(int64_t bh, int32_t m, int32_t J, float kappa, const
     FNB_CUDA(cudaFuncSetAttribute(nstc::ns_pinv_bwd_tc_debug_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                   (int)nstc::kBwdSmem));
     nstc::ns_pinv_bwd_tc_debug_kernel<<<(unsigned)bh, nstc::kNsTcThreads, nstc::kBwdSmem, (cudaStream_t)stream>>>(
-        k2, ns_iterates, d_k2_inv, d_k2, (float*)workspace, m, J, kappa, nullptr);
+        k2, ns_iterates, d_k2_inv, d_k2, (float*)workspace, m, J, kappa, nullptr, nullptr, nullptr);
   } else if (m <= ns::kN) {
     FNB_CUDA(cudaFuncSetAttribute(ns::ns_pinv_bwd_debug_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                   (int)ns::kBwdSmem));
@@ -1264,7 +1264,101 @@ __attribute__((visibility("default"))) int fnb_debug_tc_trace(long long* out, in
   if (cta >= 0) { cudaMemcpyToSymbol(tc::g_tc_trace_cta, &cta, sizeof(int)); return 0; }
   return cudaMemcpyFromSymbol(out, tc::g_tc_trace, sizeof(long long) * 8 * 256) == cudaSuccess ? 0 : -1;
 }
+__attribute__((visibility("default"))) int fnb_debug_tc_span(unsigned long long* out) {
+  return cudaMemcpyFromSymbol(out, tc::g_tc_span, sizeof(unsigned long long) * 3 * 1024) == cudaSuccess ? 0 : -1;
+}
 #endif
+
+int fnb_debug_ns_bwd_step(int64_t bh, int32_t m, const float* k2, const float* z_j, const float* d_z_next,
+                          float* d_z_out, float* d_k2_acc, int32_t device, void* stream) {
+  if (bh <= 0 || bh > ((int64_t)1 << 24)) return fail(FNB_ERR_INVALID_ARGUMENT, "bh out of range");
+  if (m < 1 || m > ns::kN)
+    return fail(FNB_ERR_INVALID_ARGUMENT, "fnb_debug_ns_bwd_step handles num_landmarks in [1, %d], got %d", ns::kN, m);
+  if (!k2 || !z_j || !d_z_next || !d_z_out || !d_k2_acc) return fail(FNB_ERR_INVALID_ARGUMENT, "NULL tensor pointer");
+  DeviceGuard g(device);
+  if (!g.ok) return fail(FNB_ERR_CUDA, "cannot select CUDA device %d", device);
+  int max_smem = 0, cc = 0, sms = 0;
+  if (int rc = device_limits(device, &max_smem, &cc, &sms)) return rc;
+  if (int rc = set_smem(nstc::ns_pinv_bwd_tc_debug_kernel, nstc::kBwdSmem, max_smem, "ns_pinv_bwd")) return rc;
+  // one iteration of the product kernel's loop (J = 1, no ridge), stopped in front of the Z0 tail
+  nstc::ns_pinv_bwd_tc_debug_kernel<<<(unsigned)bh, nstc::kNsTcThreads, nstc::kBwdSmem, (cudaStream_t)stream>>>(
+      k2, z_j, d_z_next, nullptr, nullptr, m, 1, 0.f, nullptr, d_z_out, d_k2_acc);
+  FNB_CUDA(cudaPeekAtLastError());
+  return 0;
+}
+
+int fnb_debug_ns_bwd_final(int64_t bh, int32_t m, int32_t D, const float* q_landmarks, const float* k_landmarks,
+                           const float* k2, const float* d_z0, const float* d_k2_in, const float* zeros_md,
+                           float* d_q_landmarks, float* d_k_landmarks, float* d_k2_out, int32_t device, void* stream) {
+  if (bh <= 0 || bh > ((int64_t)1 << 24)) return fail(FNB_ERR_INVALID_ARGUMENT, "bh out of range");
+  if (m < 1 || m > ns::kN)
+    return fail(FNB_ERR_INVALID_ARGUMENT, "fnb_debug_ns_bwd_final handles num_landmarks in [1, %d], got %d", ns::kN, m);
+  if (!(D == 16 || D == 32 || D == 64 || D == 128)) return fail(FNB_ERR_INVALID_ARGUMENT, "head_dim must be 16, 32, 64 or 128");
+  if (!q_landmarks || !k_landmarks || !k2 || !d_z0 || !d_k2_in || !zeros_md || !d_q_landmarks || !d_k_landmarks || !d_k2_out)
+    return fail(FNB_ERR_INVALID_ARGUMENT, "NULL tensor pointer");
+  DeviceGuard g(device);
+  if (!g.ok) return fail(FNB_ERR_CUDA, "cannot select CUDA device %d", device);
+  int max_smem = 0, cc = 0, sms = 0;
+  if (int rc = device_limits(device, &max_smem, &cc, &sms)) return rc;
+  if (int rc = set_smem(ns::ns_bwd_final_debug_kernel, ns::kBwdSmem, max_smem, "ns_bwd_final")) return rc;
+  ns::ns_bwd_final_debug_kernel<<<(unsigned)bh, kThreads, ns::kBwdSmem, (cudaStream_t)stream>>>(
+      q_landmarks, k_landmarks, k2, d_z0, d_k2_in, zeros_md, d_q_landmarks, d_k_landmarks, d_k2_out, m, D);
+  FNB_CUDA(cudaPeekAtLastError());
+  return 0;
+}
+
+namespace {
+struct KernelEntry { const char* name; const void* fn; int threads; size_t dyn_smem; };
+}
+int fnb_kernel_report(int device, fnb_kernel_info* out, int cap) {
+  if (!out || cap <= 0) return 0;
+  DeviceGuard g(device);
+  if (!g.ok) return 0;
+  using H = __half;
+  const KernelEntry ks[] = {
+      {"landmark_partial<half>", (const void*)landmark_partial_kernel<H>, kThreads, 0},
+      {"tc_pool<half,64>", (const void*)tc::tc_pool_kernel<H, 64>, tc::kPoolThreads, tc::PoolSmem<64>::kBytes},
+      {"ns_fwd_tc", (const void*)nstc::ns_fwd_tc_kernel, nstc::kNsTcThreads, nstc::kFwdSmem},
+      {"tc_fwd_b<half,64,64>", (const void*)tc::tc_fwd_b_kernel<H, 64, 64>, tc::kTcThreads, tc::FwdBSmem<64, 64>::kBytes},
+      {"combine_slab", (const void*)combine_slab_kernel, kThreads, 0},
+      {"tc_fwd_c<half,64,64>", (const void*)tc::tc_fwd_c_kernel<H, 64, 64>, tc::kTcThreads, tc::FwdCSmem<64, 64>::kBytes},
+      {"tc_bwd_a<half,64,64>", (const void*)tc::tc_bwd_a_kernel<H, 64, 64>, tc::kTcThreads, tc::BwdASmem<64, 64>::kBytes},
+      {"reduce_chunks", (const void*)reduce_chunks_kernel, kThreads, 0},
+      {"ns_bwd_tc", (const void*)nstc::ns_bwd_tc_kernel, nstc::kNsTcThreads, nstc::kBwdSmem},
+      {"colpass_operands", (const void*)colpass_operands_kernel, kThreads, (size_t)kColpassOperandSmem},
+      {"tc_bwd_b<half,64,64>", (const void*)tc::tc_bwd_b_kernel<H, 64, 64>, tc::kTcThreads, tc::BwdBSmem<64, 64>::kBytes},
+      {"tc_rows_inplace<half,64,64>", (const void*)tc::tc_rows_inplace_kernel<H, 64, 64>, tc::kTcThreads, tc::RowsSmem<64, 64>::kBytes},
+      {"tc_fwd_b<half,128,64>", (const void*)tc::tc_fwd_b_kernel<H, 128, 64>, tc::kTcThreads, tc::FwdBSmem<128, 64>::kBytes},
+      {"tc_fwd_c<half,128,64>", (const void*)tc::tc_fwd_c_kernel<H, 128, 64>, tc::kTcThreads, tc::FwdCSmem<128, 64>::kBytes},
+      {"tc_bwd_a<half,128,64>", (const void*)tc::tc_bwd_a_kernel<H, 128, 64>, tc::kTcThreads, tc::BwdASmem<128, 64>::kBytes},
+      {"tc_bwd_b<half,128,64>", (const void*)tc::tc_bwd_b_kernel<H, 128, 64>, tc::kTcThreads, tc::BwdBSmem<128, 64>::kBytes},
+      {"tc_rows_inplace<half,128,64>", (const void*)tc::tc_rows_inplace_kernel<H, 128, 64>, tc::kTcThreads, tc::RowsSmem<128, 64>::kBytes},
+  };
+  int n = 0;
+  for (const KernelEntry& k : ks) {
+    if (n >= cap) break;
+    cudaFuncAttributes at;
+    if (cudaFuncGetAttributes(&at, k.fn) != cudaSuccess) { cudaGetLastError(); continue; }
+    fnb_kernel_info& o = out[n];
+    memset(&o, 0, sizeof(o));
+    strncpy(o.name, k.name, sizeof(o.name) - 1);
+    o.registers = at.numRegs;
+    o.static_smem_bytes = (int)at.sharedSizeBytes;
+    o.dynamic_smem_bytes = (int)k.dyn_smem;
+    o.local_bytes_per_thread = (int)at.localSizeBytes;
+    o.threads = k.threads;
+    int nb = 0;
+    // the same attributes the launches set (set_smem): opt-in dynamic size, largest shared-memory carveout
+    if (k.dyn_smem > 0) {
+      cudaFuncSetAttribute(k.fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)k.dyn_smem);
+      cudaFuncSetAttribute(k.fn, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    }
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, k.fn, k.threads, k.dyn_smem) != cudaSuccess) { cudaGetLastError(); nb = -1; }
+    o.blocks_per_sm = nb;
+    ++n;
+  }
+  return n;
+}
 
 int fnb_debug_set_wait_limit_ms(int device, int ms) {
   if (ms < 1 || ms > 10000) return fail(FNB_ERR_INVALID_ARGUMENT, "wait limit must be 1..10000 ms, got %d", ms);

@@ -522,5 +522,36 @@ __global__ void __launch_bounds__(kThreads, 1) ns_bwd_kernel(NsBwdParams p) {
   ns_bwd_finish(p, bh, sm, dK2);
 }
 
+// Isolation hook for the tail of the backward (the role of the reference's debug_ns_bwd_final,
+// csrc/flash_nystrom.cu:474-520, without the ridge): from dL/dZ_0 and the dL/dK2 accumulated over the
+// iterations to the complete dL/dK2 (Z0 = K2^T / (||K2||_1 ||K2||_inf) with its norm terms), then
+// through the softmax-2 Jacobian to the landmark gradients dQt = dS2 Kt, dKt = dS2^T Qt.
+// zeros: [m][D] floats of zeros (stands in for the softmax-1 contribution the product path adds).
+__global__ void __launch_bounds__(kThreads, 1)
+ns_bwd_final_debug_kernel(const float* qt, const float* kt, const float* k2, const float* dz0, const float* dk2_in,
+                          const float* zeros, float* dqt, float* dkt, float* dk2_out, int m, int D) {
+  extern __shared__ float sm[];
+  __shared__ float red[kRedFloats];
+  const int64_t bh = blockIdx.x;
+  const int mm_ = m * m;
+  float* bK2 = sm;
+  float* bdZ = sm + 1 * kBuf;
+  float* bdA = sm + 2 * kBuf;
+  float* bdM = sm + 3 * kBuf;
+  float* bdT = sm + 4 * kBuf;
+  load_mat(bK2, k2 + bh * mm_, m);
+  load_mat(bdZ, dz0 + bh * mm_, m);
+  load_mat(bdA, dk2_in + bh * mm_, m);
+  ns_sync();
+  float* dK2 = pinv_backward_tail(bK2, bK2, bdZ, bdA, bdM, bdT, red, nullptr, m, 0.f);
+  store_mat(dk2_out + bh * mm_, dK2, m);
+  ns_sync();
+  NsBwdParams p;
+  p.k2 = k2; p.iterates = nullptr; p.G = nullptr; p.qt = qt; p.kt = kt; p.dkt_a = zeros - bh * (int64_t)m * D;
+  p.dqt_ns = dqt; p.dkt_tot = dkt; p.spill = nullptr; p.rows_k = nullptr; p.N = m; p.scale = 1.f;
+  p.m = m; p.D = D; p.J = 0; p.kappa = 0.f;
+  ns_bwd_finish(p, bh, bK2, dK2);
+}
+
 }  // namespace ns
 }  // namespace fnb

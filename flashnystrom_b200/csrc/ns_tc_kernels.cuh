@@ -565,7 +565,8 @@ __device__ inline void pinv_backward_issue(Ctx& c, int J, bool finish, bool head
 template <class BeforeTail>
 __device__ __forceinline__ float* pinv_backward_tc(Ctx& c, float* red, const float* k2g, const float* iterates,
                                                    const float* G, float* spill, int m, int J, float kappa,
-                                                   BeforeTail before_tail) {
+                                                   BeforeTail before_tail, float* step_dz = nullptr,
+                                                   float* step_da = nullptr) {
   // G == nullptr: dL/dk2inv is already in place (slot 2 without the ridge, staging buffer 3 with it)
   const int mm_ = m * m;
   float znext[16];
@@ -650,6 +651,15 @@ __device__ __forceinline__ float* pinv_backward_tc(Ctx& c, float* red, const flo
     if (j > 0) store_set16(c.slot(1), znext);
     NS_TRACE();
   }
+  if (step_dz) {
+    // isolation hook: hand back dL/dZ_0 and the dL/dA accumulated over the iterations, skip the tail
+    ns::ns_sync();
+    if (!c.failed) {
+      ns::store_mat(step_dz, bwd_tail(c, 2), m);
+      store_global16(c, step_da, dA, m, m, m);
+    }
+    return nullptr;
+  }
   before_tail();
   store_row16(c, bwd_tail(c, 3), dA);
   float* bK2 = bwd_tail(c, 0);
@@ -670,7 +680,7 @@ __device__ __forceinline__ float* pinv_backward_tc(Ctx& c, float* red, const flo
 
 __global__ void __launch_bounds__(kNsTcThreads, 1)
 ns_pinv_bwd_tc_debug_kernel(const float* k2, const float* iterates, const float* G, float* dK2, float* spill,
-                            int m, int J, float kappa, int* status) {
+                            int m, int J, float kappa, int* status, float* step_dz, float* step_da) {
   extern __shared__ uint8_t dyn_smem[];
   __shared__ float red[ns::kRedFloats];
   __shared__ Shared sh;
@@ -678,9 +688,11 @@ ns_pinv_bwd_tc_debug_kernel(const float* k2, const float* iterates, const float*
   ctx_open(c, sh, dyn_smem, kBwdSlots, status, kBwdTmemCols);
   const int64_t bh = blockIdx.x;
   if (is_compute()) {
-    float* out = pinv_backward_tc(c, red, k2 + bh * m * m, iterates + bh * (size_t)(J + 1) * m * m, G + bh * m * m,
-                                  spill + bh * m * m, m, J, kappa, [] {});
-    if (!c.failed) ns::store_mat(dK2 + bh * m * m, out, m);
+    // step hook: one iteration (J = 1) whose "iterates" is the single matrix Z_j per slice
+    const float* its = step_dz ? iterates + bh * (size_t)m * m : iterates + bh * (size_t)(J + 1) * m * m;
+    float* out = pinv_backward_tc(c, red, k2 + bh * m * m, its, G + bh * m * m, spill + bh * m * m, m, J, kappa, [] {},
+                                  step_dz ? step_dz + bh * m * m : nullptr, step_da ? step_da + bh * m * m : nullptr);
+    if (out && !c.failed) ns::store_mat(dK2 + bh * m * m, out, m);
   } else if (is_issuer()) {
     pinv_backward_issue(c, J, false, false);
   }

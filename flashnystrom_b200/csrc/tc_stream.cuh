@@ -30,12 +30,27 @@ constexpr float kLn2 = 0.6931471805599453f;
 #ifdef FNB_TC_TRACE
 __device__ long long g_tc_trace[8][256];
 __device__ int g_tc_trace_cta = 150;
+__device__ unsigned long long g_tc_span[3 * 1024];   // per CTA: SM id, entry and exit time (ns)
+__device__ __forceinline__ void tc_span(int which) {
+  if (threadIdx.x == 0 && blockIdx.x < 1024) {
+    if (which == 0) {
+      unsigned smid;
+      asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+      g_tc_span[3 * blockIdx.x] = smid;
+    }
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    g_tc_span[3 * blockIdx.x + 1 + which] = t;
+  }
+}
+#define TC_SPAN(which) tc_span(which)
 #define TC_TRACE(role, idx)                                                                    \
   do {                                                                                         \
     if (blockIdx.x == g_tc_trace_cta && (idx) < 256) g_tc_trace[role][idx] = clock64();        \
   } while (0)
 #else
 #define TC_TRACE(role, idx) do {} while (0)
+#define TC_SPAN(which) do {} while (0)
 #endif
 
 __device__ __forceinline__ uint8_t* align1024(uint8_t* p) {
@@ -1303,6 +1318,7 @@ tc_fwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
                 float* __restrict__ part_max, float* __restrict__ part_sum, TcSched sch, int m,
                 int* status) {
   using L = FwdBSmem<D, MP>;
+  TC_SPAN(0);
   constexpr int KBD = D / 64, HC = MP / 2;
   constexpr int CPL = HC / 32;                 // columns per lane after the warp fold
   constexpr int NCK = (D + 32) / 32;           // 32-column chunks of accumulator + row sums
@@ -1582,6 +1598,7 @@ tc_fwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem_base, kTmemCols);
+  TC_SPAN(1);
 }
 
 }  // namespace tc

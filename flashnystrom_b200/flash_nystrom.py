@@ -7,7 +7,9 @@ import torch.nn.functional as F
 from . import _C
 from .nystrom_config import NystromConfig
 
-HAS_CUDA = True  # the library is the only implementation; kept for API compatibility
+# The reference sets HAS_CUDA when its extension imports (flash_nystrom/__init__.py:38-46).  Here
+# the library is the only implementation: the flag says whether it can run on this machine.
+HAS_CUDA = bool(torch.cuda.is_available())
 
 
 def _depthwise_conv_residual(v, weight):
@@ -63,8 +65,13 @@ def flash_nystrom_attention(q, k, v, num_landmarks=64, newton_iter=6, conv_weigh
     if not (isinstance(q, torch.Tensor) and q.is_cuda):
         raise RuntimeError("flash_nystrom_attention: inputs must be CUDA tensors "
                            "(flashnystrom_b200 has no CPU path)")
-    out = FlashNystromFunction.apply(q, k, v, num_landmarks, newton_iter, fast_dk2inv,
-                                     kappa_star, use_tc_pinv)
+    if torch.compiler.is_compiling():
+        # registered custom operators (fake implementations + autograd formula): no graph break
+        from . import _ops
+        out = _ops.attention_via_ops(q, k, v, num_landmarks, newton_iter, kappa_star)
+    else:
+        out = FlashNystromFunction.apply(q, k, v, num_landmarks, newton_iter, fast_dk2inv,
+                                         kappa_star, use_tc_pinv)
     if conv_weight is not None and conv_kernel_size > 0:
         out = out + _depthwise_conv_residual(v, conv_weight)
     return out

@@ -208,6 +208,32 @@ FNB_API int fnb_debug_pinv_backward(int64_t bh, int32_t m, int32_t newton_iter, 
                             int32_t device, void* stream);
 FNB_API size_t fnb_debug_pinv_workspace_bytes(int64_t bh, int32_t m);
 
+/* One backward iteration of the Newton-Schulz unroll, run by the product's tensor-core kernel
+ * (num_landmarks <= 64, no ridge): from K2, the iterate Z_j and dL/dZ_{j+1} to dL/dZ_j and this
+ * iteration's contribution to dL/dK2.  (BH,m,m) FP32 device tensors.
+ * Stands in for debug_ns_bwd_step (csrc/flash_nystrom.cu:422-456). */
+FNB_API int fnb_debug_ns_bwd_step(int64_t bh, int32_t m, const float* k2, const float* z_j, const float* d_z_next,
+                                  float* d_z_out, float* d_k2_acc, int32_t device, void* stream);
+
+/* The tail of the backward in isolation (num_landmarks <= 64, no ridge): dL/dZ_0 and the dL/dK2
+ * accumulated over the iterations -> complete dL/dK2 (d_k2_out), then through the softmax-2
+ * Jacobian to dQt = dS2 Kt and dKt = dS2^T Qt.  zeros_md: (m, D) floats of zeros.
+ * Stands in for debug_ns_bwd_final (csrc/flash_nystrom.cu:474-520). */
+FNB_API int fnb_debug_ns_bwd_final(int64_t bh, int32_t m, int32_t head_dim, const float* q_landmarks,
+                                   const float* k_landmarks, const float* k2, const float* d_z0, const float* d_k2_in,
+                                   const float* zeros_md, float* d_q_landmarks, float* d_k_landmarks, float* d_k2_out,
+                                   int32_t device, void* stream);
+
+/* Resources and occupancy of the hot-path kernels on `device`: registers per thread, static and
+ * dynamic shared memory, local (spill) bytes per thread, threads per CTA and how many CTAs fit on
+ * one SM.  Writes up to `cap` entries, returns how many.  Stands in for probe_occupancy
+ * (csrc/occupancy_probe.h:89-142). */
+typedef struct fnb_kernel_info {
+  char name[48];
+  int32_t registers, static_smem_bytes, dynamic_smem_bytes, local_bytes_per_thread, threads, blocks_per_sm;
+} fnb_kernel_info;
+FNB_API int fnb_kernel_report(int device, fnb_kernel_info* out, int cap);
+
 /* Gradient of the pseudoinverse for callers that must not allocate: what
  * fnb_debug_pinv_backward computes, but without a workspace argument.  It always runs the FP32
  * CUDA-core kernel (fnb_debug_pinv_backward prefers the tensor-core kernel for num_landmarks

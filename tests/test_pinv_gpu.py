@@ -69,3 +69,64 @@ def test_pinv_same_call_twice_is_bit_identical(cuda_device):
     assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1])
     G = torch.randn(4, 64, 64, device="cuda")
     assert torch.equal(_C.debug_pinv_backward(k2, a[0], G, 5.0), _C.debug_pinv_backward(k2, a[0], G, 5.0))
+
+
+def test_ns_bwd_step_hook(cuda_device):
+    """One backward iteration on the product's kernel against the oracle's algebra
+    (the reference's tests/test_ns_bwd_kernel.py:49-119 does this for its per-step kernel)."""
+    from flashnystrom_b200 import _C
+    BH, m = 3, 48
+    k2 = _softmax_matrix(BH, m, seed=5)
+    its = torch.stack(O.newton_schulz(k2.double(), 3), dim=1)          # (BH, 4, m, m)
+    Zj = its[:, 2].float()
+    g = torch.Generator().manual_seed(6)
+    dZn = torch.randn(BH, m, m, generator=g)
+    dZ_out, dK2_acc = _C.debug_ns_bwd_step(k2.cuda(), Zj.cuda(), dZn.cuda())
+    A, Z, dZ = k2.double(), Zj.double(), dZn.double()
+    I = torch.eye(m, dtype=torch.float64)
+    M = A @ Z; U = 7 * I - M; V = 15 * I - M @ U; T = 13 * I - M @ V
+    Mt = M.transpose(-2, -1)
+    dT = 0.25 * Z.transpose(-2, -1) @ dZ
+    dV = -Mt @ dT
+    dM = -dT @ V.transpose(-2, -1) - dV @ U.transpose(-2, -1) + Mt @ dV
+    ref_dA = dM @ Z.transpose(-2, -1)
+    ref_dZ = 0.25 * dZ @ T.transpose(-2, -1) + A.transpose(-2, -1) @ dM
+    assert O.rel_max(dZ_out.cpu(), ref_dZ) < 2e-5
+    assert O.rel_max(dK2_acc.cpu(), ref_dA) < 2e-5
+
+
+def test_ns_bwd_final_hook(cuda_device):
+    """The tail (Z0 norm terms, softmax-2 Jacobian, landmark gradients) against autograd through the
+    same algebra (the reference's tests/test_ns_bwd_kernel.py:134-229)."""
+    from flashnystrom_b200 import _C
+    BH, m, D = 2, 40, 64
+    g = torch.Generator().manual_seed(8)
+    qt = torch.randn(BH, m, D, generator=g) * 0.3
+    kt = torch.randn(BH, m, D, generator=g) * 0.3
+    dZ0 = torch.randn(BH, m, m, generator=g)
+    dK2_in = torch.randn(BH, m, m, generator=g)
+    q64, k64 = qt.double().requires_grad_(True), kt.double().requires_grad_(True)
+    K2 = torch.softmax(q64 @ k64.transpose(-2, -1), dim=-1)
+    n1, _, ninf, _ = O.norms_1_inf(K2)
+    Z0 = K2.transpose(-2, -1) / (n1 * ninf)[..., None, None]
+    loss = (Z0 * dZ0.double()).sum() + (K2 * dK2_in.double()).sum()
+    loss.backward()
+    dq, dk, dk2 = _C.debug_ns_bwd_final(qt.cuda(), kt.cuda(), K2.detach().float().cuda(), dZ0.cuda(), dK2_in.cuda())
+    assert O.rel_max(dq.cpu(), q64.grad) < 2e-4
+    assert O.rel_max(dk.cpu(), k64.grad) < 2e-4
+
+
+def test_probe_occupancy_lists_the_kernels(cuda_device):
+    from flashnystrom_b200 import _C
+    rep = _C.probe_occupancy(0)
+    names = {r["name"] for r in rep}
+    assert {"tc_fwd_b<half,64,64>", "tc_rows_inplace<half,64,64>", "ns_bwd_tc", "tc_bwd_a<half,128,64>"} <= names
+    by = {r["name"]: r for r in rep}
+    print("\n".join(f"{r['name']:32s} regs {r['registers']:3d}  smem {r['static_smem_bytes'] + r['dynamic_smem_bytes']:6d}  "
+                    f"local {r['local_bytes_per_thread']:3d}  CTAs/SM {r['blocks_per_sm']}" for r in rep))
+    # (blocks_per_sm is what cudaOccupancyMaxActiveBlocksPerMultiprocessor answers; for the 320-thread
+    # tensor-core kernels of head_dim 64 it says 1 although two CTAs are co-resident in practice, as
+    # per-CTA SM ids and lifetimes show, so it is only checked for sanity)
+    assert all(r["registers"] > 0 and r["threads"] > 0 and r["blocks_per_sm"] >= 1 for r in rep)
+    assert by["tc_fwd_c<half,64,64>"]["dynamic_smem_bytes"] * 2 < 227 * 1024
+    assert by["tc_fwd_c<half,64,64>"]["registers"] * 320 * 2 <= 65536
