@@ -63,11 +63,23 @@ struct Plan {
   int64_t rows_per_chunk;
 };
 
+// SM count of the current device (148 when it cannot be asked): workspace sizes and the grids of
+// the CUDA-core kernels follow it, so size a workspace with the device current that will run the call.
+inline int current_sm_count() {
+  int dev = 0, sms = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess ||
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) {
+    cudaGetLastError();
+    return 148;
+  }
+  return sms;
+}
+
 inline Plan make_plan(int64_t BH, int64_t N, int D, int m, int J) {
   Plan p;
   p.BH = BH; p.N = N; p.D = D; p.m = m; p.J = J;
   p.mpad = (m + 15) / 16 * 16;
-  const int64_t target = 592;  // 4 CTAs per SM on a 148-SM part
+  const int64_t target = 4 * (int64_t)current_sm_count();  // 4 CTAs per SM
   int64_t seg = N / m;
   // pooling pass: a persistent grid of 4 CTAs per SM walks (tensor, slice, landmark, chunk) items;
   // about six items per CTA keep the last round of the walk short

@@ -125,7 +125,7 @@ static thread_local SideStream g_side;
 
 struct Fork {
   cudaStream_t main;
-  bool enabled, forked = false;
+  bool enabled, forked = false, ended = false;
   Fork(cudaStream_t st, int dev, bool want) : main(st), enabled(want && g_side.get(dev)) {}
   cudaStream_t begin() {            // work launched on the returned stream runs beside `main`
     if (!enabled) return main;
@@ -134,9 +134,13 @@ struct Fork {
     forked = true;
     return g_side.stream;
   }
-  void end() { if (forked) cudaEventRecord(g_side.join, g_side.stream); }
+  void end() { if (forked && !ended) { cudaEventRecord(g_side.join, g_side.stream); ended = true; } }
   void join() {                     // `main` waits for the side work
-    if (forked) { cudaStreamWaitEvent(main, g_side.join, 0); forked = false; }
+    if (forked) {
+      end();                        // an early error return never reached end(): close the fork now
+      cudaStreamWaitEvent(main, g_side.join, 0);
+      forked = false;
+    }
   }
   ~Fork() { join(); }
 };
@@ -346,6 +350,14 @@ static int dispatch_head_dim(int D, F&& f) {
   if (D == 64) return f(std::integral_constant<int, 64>{});
   return f(std::integral_constant<int, 128>{});
 }
+// Calls f(D, MP as integral constants) for the (head_dim, padded landmark count) pairs the
+// tensor-core kernels are instantiated for: (64, 64), (128, 64), (128, 128).
+template <class F>
+static int dispatch_tc(int D, int MP, F&& f) {
+  if (D == 64) return f(std::integral_constant<int, 64>{}, std::integral_constant<int, 64>{});
+  if (MP == 64) return f(std::integral_constant<int, 128>{}, std::integral_constant<int, 64>{});
+  return f(std::integral_constant<int, 128>{}, std::integral_constant<int, 128>{});
+}
 // Co-resident tensor-core CTAs per SM: two for head_dim 64, one for head_dim 128 (shared memory).
 static int tc_ctas_per_sm(int D) { return D == 64 ? 2 : 1; }
 
@@ -467,14 +479,20 @@ static int forward_impl(const fnb_fwd_args& a, const Plan& p, const FwdWs& w, in
     mp.landmarks_only = 0;
     mp.qt16 = use_tc ? w.qt16 : nullptr; mp.dtype = a.shape.dtype; mp.MP = MP;
     mp.qt16_mul = scale * tc::kLog2e;
-    mid_fwd_kernel<<<(unsigned)p.BH, kThreads, 0, st>>>(mp);
+    // products on the tensor cores unless the caller forces the CUDA-core path
+    mp.use_tc = (a.shape.flags & FNB_FLAG_FORCE_GENERIC) ? 0 : 1;
+    mp.status = a.device_status;
+    const size_t mid_smem = mp.use_tc ? kTcGemmSmem : 0;
+    if (mp.use_tc)
+      if (int rc = set_smem(mid_fwd_kernel, mid_smem, max_smem, "mid_fwd")) return rc;
+    mid_fwd_kernel<<<(unsigned)p.BH, kThreads, mid_smem, st>>>(mp);
     if (L.end("mid_fwd")) return L.status;
   }
 
   if constexpr (k16) {
     if (use_tc) {
-      int rc = dispatch_head_dim(p.D, [&](auto dtag) -> int {
-        constexpr int D = decltype(dtag)::value, MPc = 64;
+      int rc = dispatch_tc(p.D, MP, [&](auto dtag, auto mtag) -> int {
+        constexpr int D = decltype(dtag)::value, MPc = decltype(mtag)::value;
         CUtensorMap tm_k, tm_v, tm_qt;
         if (!tc::make_map_3d(&tm_k, a.k, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
             !tc::make_map_3d(&tm_v, a.v, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
@@ -557,8 +575,8 @@ static int forward_impl(const fnb_fwd_args& a, const Plan& p, const FwdWs& w, in
 
   if constexpr (k16) {
     if (use_tc) {
-      return dispatch_head_dim(p.D, [&](auto dtag) -> int {
-        constexpr int D = decltype(dtag)::value, MPc = 64;
+      return dispatch_tc(p.D, MP, [&](auto dtag, auto mtag) -> int {
+        constexpr int D = decltype(dtag)::value, MPc = decltype(mtag)::value;
         CUtensorMap tm_q, tm_o;
         if (!tc::make_map_3d(&tm_q, a.q, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
             !tc::make_map_3d(&tm_o, a.out, a.shape.dtype, p.BH, p.N, D, tc::kTile))
@@ -659,8 +677,8 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
   if (S.run(0)) {
   if constexpr (k16) {
     if (use_tc) {
-      int rc = dispatch_head_dim(p.D, [&](auto dtag) -> int {
-        constexpr int D = decltype(dtag)::value, MPc = 64;
+      int rc = dispatch_tc(p.D, MP, [&](auto dtag, auto mtag) -> int {
+        constexpr int D = decltype(dtag)::value, MPc = decltype(mtag)::value;
         L.begin();
         auto kern = tc::tc_bwd_a_kernel<T, D, MPc>;
         size_t sm = tc::BwdASmem<D, MPc>::kBytes;
@@ -768,16 +786,31 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
       mp.dstep2 = w.dstep2; mp.dkt_a = w.dkt_a; mp.dO3 = w.dO3; mp.D3 = w.D3;
       mp.dqt_ns = w.dqt_ns; mp.dkt_tot = w.dkt_tot; mp.G = w.G; mp.dK2 = w.dK2; mp.scratch = w.pinv;
       mp.m = p.m; mp.D = p.D; mp.J = p.J; mp.kappa = a.shape.kappa_star; mp.first_half_only = 0;
-      mid_bwd_kernel<<<(unsigned)p.BH, kThreads, 0, st>>>(mp);
+      mp.use_tc = (a.shape.flags & FNB_FLAG_FORCE_GENERIC) ? 0 : 1;
+      mp.status = a.device_status;
+      const size_t mid_smem = mp.use_tc ? kTcGemmSmem : 0;
+      if (mp.use_tc)
+        if (int rc = set_smem(mid_bwd_kernel, mid_smem, max_smem, "mid_bwd")) return rc;
+      mid_bwd_kernel<<<(unsigned)p.BH, kThreads, mid_smem, st>>>(mp);
     }
     if (L.end("mid_bwd")) return L.status;
+    if (use_tc) {
+      // what the tensor-core column pass and the in-place pass need from the middle stage
+      L.begin();
+      MidPackParams pp;
+      pp.dO3 = w.dO3; pp.q_landmarks = a.q_landmarks; pp.dkt_tot = w.dkt_tot; pp.do3n = do3n; pp.do3_scale = w.do3_scale;
+      pp.qt16 = qt16; pp.rows_k = w.rows_k; pp.m = p.m; pp.D = p.D; pp.MP = MP; pp.dtype = a.shape.dtype;
+      pp.qt_mul = scale * tc::kLog2e; pp.scale = scale; pp.N = seg_N;
+      mid_pack_kernel<<<(unsigned)p.BH, kThreads, 0, st>>>(pp);
+      if (L.end("mid_pack")) return L.status;
+    }
   }
 
   // ---- pass B ---------------------------------------------------------------------------------
   if constexpr (k16) {
     if (use_tc) {
-      int rc = dispatch_head_dim(p.D, [&](auto dtag) -> int {
-        constexpr int D = decltype(dtag)::value, MPc = 64;
+      int rc = dispatch_tc(p.D, MP, [&](auto dtag, auto mtag) -> int {
+        constexpr int D = decltype(dtag)::value, MPc = decltype(mtag)::value;
         CUtensorMap tm_k, tm_v, tm_qt, tm_do3, tm_dv;
         if (!tc::make_map_3d(&tm_k, a.k, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
             !tc::make_map_3d(&tm_v, a.v, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
@@ -824,8 +857,8 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
   // ---- pass C ---------------------------------------------------------------------------------
   if constexpr (k16) {
     if (use_tc) {
-      return dispatch_head_dim(p.D, [&](auto dtag) -> int {
-      constexpr int D = decltype(dtag)::value, MPc = 64;
+      return dispatch_tc(p.D, MP, [&](auto dtag, auto mtag) -> int {
+      constexpr int D = decltype(dtag)::value, MPc = decltype(mtag)::value;
       L.begin();
       auto kern = tc::tc_rows_inplace_kernel<T, D, MPc>;
       size_t sm = tc::RowsSmem<D, MPc>::kBytes;
@@ -868,114 +901,8 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
 }
 
 
-// ---- (b,h) group pipelining ------------------------------------------------------------------
-// Slices are independent, so one call may be cut into groups of consecutive slices that run the
-// whole kernel chain on alternating streams: while one group sits in its landmark-sized,
-// latency-bound kernels (one CTA per slice), the other group's streaming passes fill the SMs.
-// Measured on B200 at BH = 16, N = 65536: two groups are slower than one (each streaming kernel is
-// sized to fill every SM in one wave, so two of them collide, and a 209 KB pseudoinverse CTA
-// cannot share an SM with streaming CTAs), so grouping is off; the mechanism stays for shapes
-// where the landmark-sized kernels dominate.
-constexpr int kMaxGroups = 1;
-static int group_count(int64_t BH) { return (kMaxGroups > 1 && BH >= 8) ? kMaxGroups : 1; }
-static int64_t group_size(int64_t BH) { int G = group_count(BH); return (BH + G - 1) / G; }
-static Plan group_plan(const fnb_shape& s, int64_t bh) {
-  return make_plan(bh, s.seq_len, s.head_dim, s.num_landmarks, s.newton_iter);
-}
-static size_t esize(int dtype) { return dtype == FNB_F32 ? 4 : 2; }
-template <class P> static P* off(P* p, size_t elems) { return p ? p + elems : p; }
-static const void* offb(const void* p, size_t bytes) { return p ? (const char*)p + bytes : p; }
-static void* offb(void* p, size_t bytes) { return p ? (char*)p + bytes : p; }
-
-static fnb_fwd_args fwd_group(const fnb_fwd_args& a, int64_t bh0, int64_t n, void* ws, size_t ws_bytes) {
-  fnb_fwd_args g = a;
-  const fnb_shape& s = a.shape;
-  const size_t nd = (size_t)s.seq_len * s.head_dim, md = (size_t)s.num_landmarks * s.head_dim,
-               mm = (size_t)s.num_landmarks * s.num_landmarks, es = esize(s.dtype);
-  g.shape.batch = n; g.shape.heads = 1;
-  g.q = offb(a.q, bh0 * nd * es); g.k = offb(a.k, bh0 * nd * es); g.v = offb(a.v, bh0 * nd * es);
-  g.out = offb(a.out, bh0 * nd * es);
-  g.lse1 = off(a.lse1, bh0 * (size_t)s.seq_len);
-  g.q_landmarks = off(a.q_landmarks, bh0 * md); g.k_landmarks = off(a.k_landmarks, bh0 * md);
-  g.k2 = off(a.k2, bh0 * mm); g.lse2 = off(a.lse2, bh0 * (size_t)s.num_landmarks);
-  g.ns_iterates = off(a.ns_iterates, bh0 * mm * (s.newton_iter + 1));
-  g.k2_inv = off(a.k2_inv, bh0 * mm); g.bmat = off(a.bmat, bh0 * md);
-  g.lse3 = off(a.lse3, bh0 * (size_t)s.num_landmarks); g.step2 = off(a.step2, bh0 * md);
-  g.workspace = ws; g.workspace_bytes = ws_bytes;
-  return g;
-}
-static fnb_bwd_args bwd_group(const fnb_bwd_args& a, int64_t bh0, int64_t n, void* ws, size_t ws_bytes) {
-  fnb_bwd_args g = a;
-  const fnb_shape& s = a.shape;
-  const size_t nd = (size_t)s.seq_len * s.head_dim, md = (size_t)s.num_landmarks * s.head_dim,
-               mm = (size_t)s.num_landmarks * s.num_landmarks, es = esize(s.dtype);
-  g.shape.batch = n; g.shape.heads = 1;
-  g.q = offb(a.q, bh0 * nd * es); g.k = offb(a.k, bh0 * nd * es); g.v = offb(a.v, bh0 * nd * es);
-  g.d_out = offb(a.d_out, bh0 * nd * es);
-  g.dq = offb(a.dq, bh0 * nd * es); g.dk = offb(a.dk, bh0 * nd * es); g.dv = offb(a.dv, bh0 * nd * es);
-  g.lse1 = off(a.lse1, bh0 * (size_t)s.seq_len);
-  g.q_landmarks = off(a.q_landmarks, bh0 * md); g.k_landmarks = off(a.k_landmarks, bh0 * md);
-  g.k2 = off(a.k2, bh0 * mm); g.ns_iterates = off(a.ns_iterates, bh0 * mm * (s.newton_iter + 1));
-  g.k2_inv = off(a.k2_inv, bh0 * mm); g.bmat = off(a.bmat, bh0 * md);
-  g.lse3 = off(a.lse3, bh0 * (size_t)s.num_landmarks); g.step2 = off(a.step2, bh0 * md);
-  g.workspace = ws; g.workspace_bytes = ws_bytes;
-  return g;
-}
-
-template <class T>
-static int forward_groups(const fnb_fwd_args& a, int max_smem, int sms, cudaStream_t st) {
-  const int64_t BH = a.shape.batch * a.shape.heads;
-  const int G = g_profile ? 1 : group_count(BH);
-  const int64_t per = G == 1 ? BH : group_size(BH);
-  const size_t sub = carve_fwd(group_plan(a.shape, per), nullptr).bytes;
-  Fork fork(st, a.device, G > 1);
-  int rc = 0;
-  for (int g = 0; g < G && rc == 0; ++g) {
-    const int64_t bh0 = g * per, n = std::min<int64_t>(per, BH - bh0);
-    if (n <= 0) break;
-    fnb_fwd_args ga = fwd_group(a, bh0, n, (char*)a.workspace + g * sub, sub);
-    Plan p = group_plan(a.shape, n);
-    FwdWs w = carve_fwd(p, ga.workspace);
-    cudaStream_t s = (g & 1) ? fork.begin() : st;
-    rc = forward_impl<T>(ga, p, w, max_smem, sms, s, /*allow_inner_fork=*/G == 1);
-    if (g & 1) fork.end();
-  }
-  fork.join();
-  return rc;
-}
-template <class T>
-static int backward_groups(const fnb_bwd_args& a, int max_smem, int sms, cudaStream_t st) {
-  const int64_t BH = a.shape.batch * a.shape.heads;
-  const int G = g_profile ? 1 : group_count(BH);
-  const int64_t per = G == 1 ? BH : group_size(BH);
-  const size_t sub = carve_bwd(group_plan(a.shape, per), nullptr).bytes;
-  Fork fork(st, a.device, G > 1);
-  int rc = 0;
-  for (int g = 0; g < G && rc == 0; ++g) {
-    const int64_t bh0 = g * per, n = std::min<int64_t>(per, BH - bh0);
-    if (n <= 0) break;
-    fnb_bwd_args ga = bwd_group(a, bh0, n, (char*)a.workspace + g * sub, sub);
-    Plan p = group_plan(a.shape, n);
-    BwdWs w = carve_bwd(p, ga.workspace);
-    cudaStream_t s = (g & 1) ? fork.begin() : st;
-    rc = backward_impl<T>(ga, p, w, max_smem, sms, s, /*allow_inner_fork=*/G == 1);
-    if (g & 1) fork.end();
-  }
-  fork.join();
-  return rc;
-}
-static size_t fwd_ws_total(const fnb_shape& s) {
-  const int64_t BH = s.batch * s.heads;
-  const size_t whole = carve_fwd(group_plan(s, BH), nullptr).bytes;
-  const size_t grouped = group_count(BH) * carve_fwd(group_plan(s, group_size(BH)), nullptr).bytes;
-  return whole > grouped ? whole : grouped;
-}
-static size_t bwd_ws_total(const fnb_shape& s) {
-  const int64_t BH = s.batch * s.heads;
-  const size_t whole = carve_bwd(group_plan(s, BH), nullptr).bytes;
-  const size_t grouped = group_count(BH) * carve_bwd(group_plan(s, group_size(BH)), nullptr).bytes;
-  return whole > grouped ? whole : grouped;
-}
+static size_t fwd_ws_total(const fnb_shape& s) { return carve_fwd(plan_of(s), nullptr).bytes; }
+static size_t bwd_ws_total(const fnb_shape& s) { return carve_bwd(plan_of(s), nullptr).bytes; }
 
 }  // namespace fnb
 
@@ -1015,9 +942,7 @@ size_t fnb_bwd_workspace_bytes(const fnb_shape* shape) {
   return bwd_ws_total(*shape);
 }
 
-int fnb_forward(const fnb_fwd_args* a) {
-  if (!a) return fail(FNB_ERR_INVALID_ARGUMENT, "args is NULL");
-  if (int rc = check_shape(&a->shape)) return rc;
+static int check_fwd_pointers(const fnb_fwd_args* a) {
   const void* big[] = {a->q, a->k, a->v, a->out};
   for (const void* ptr : big)
     if (!ptr || !aligned16(ptr))
@@ -1026,6 +951,24 @@ int fnb_forward(const fnb_fwd_args* a) {
                          a->k2_inv, a->bmat, a->lse3, a->step2};
   for (const void* ptr : small)
     if (!ptr) return fail(FNB_ERR_INVALID_ARGUMENT, "a saved-tensor output pointer is NULL");
+  return 0;
+}
+static int check_bwd_pointers(const fnb_bwd_args* a) {
+  const void* big[] = {a->q, a->k, a->v, a->d_out, a->dq, a->dk, a->dv};
+  for (const void* ptr : big)
+    if (!ptr || !aligned16(ptr))
+      return fail(FNB_ERR_INVALID_ARGUMENT, "q, k, v, d_out, dq, dk, dv must be non-NULL and 16-byte aligned");
+  const void* small[] = {a->lse1, a->q_landmarks, a->k_landmarks, a->k2, a->ns_iterates, a->k2_inv,
+                         a->bmat, a->lse3, a->step2};
+  for (const void* ptr : small)
+    if (!ptr) return fail(FNB_ERR_INVALID_ARGUMENT, "a saved-tensor input pointer is NULL");
+  return 0;
+}
+
+int fnb_forward(const fnb_fwd_args* a) {
+  if (!a) return fail(FNB_ERR_INVALID_ARGUMENT, "args is NULL");
+  if (int rc = check_shape(&a->shape)) return rc;
+  if (int rc = check_fwd_pointers(a)) return rc;
   const size_t need = fwd_ws_total(a->shape);
   if (!a->workspace || a->workspace_bytes < need || (reinterpret_cast<uintptr_t>(a->workspace) & 255u))
     return fail(FNB_ERR_WORKSPACE, "forward workspace must be 256-byte aligned and >= %zu bytes (got %zu)",
@@ -1035,24 +978,19 @@ int fnb_forward(const fnb_fwd_args* a) {
   int max_smem = 0, cc = 0, sms = 0;
   if (int rc = device_limits(a->device, &max_smem, &cc, &sms)) return rc;
   cudaStream_t st = (cudaStream_t)a->stream;
+  Plan p = plan_of(a->shape);
+  FwdWs w = carve_fwd(p, a->workspace);
   switch (a->shape.dtype) {
-    case FNB_F32: return forward_groups<float>(*a, max_smem, sms, st);
-    case FNB_F16: return forward_groups<__half>(*a, max_smem, sms, st);
-    default: return forward_groups<__nv_bfloat16>(*a, max_smem, sms, st);
+    case FNB_F32: return forward_impl<float>(*a, p, w, max_smem, sms, st, true);
+    case FNB_F16: return forward_impl<__half>(*a, p, w, max_smem, sms, st, true);
+    default: return forward_impl<__nv_bfloat16>(*a, p, w, max_smem, sms, st, true);
   }
 }
 
 int fnb_backward(const fnb_bwd_args* a) {
   if (!a) return fail(FNB_ERR_INVALID_ARGUMENT, "args is NULL");
   if (int rc = check_shape(&a->shape)) return rc;
-  const void* big[] = {a->q, a->k, a->v, a->d_out, a->dq, a->dk, a->dv};
-  for (const void* ptr : big)
-    if (!ptr || !aligned16(ptr))
-      return fail(FNB_ERR_INVALID_ARGUMENT, "q, k, v, d_out, dq, dk, dv must be non-NULL and 16-byte aligned");
-  const void* small[] = {a->lse1, a->q_landmarks, a->k_landmarks, a->k2, a->ns_iterates, a->k2_inv,
-                         a->bmat, a->lse3, a->step2};
-  for (const void* ptr : small)
-    if (!ptr) return fail(FNB_ERR_INVALID_ARGUMENT, "a saved-tensor input pointer is NULL");
+  if (int rc = check_bwd_pointers(a)) return rc;
   const size_t need = bwd_ws_total(a->shape);
   if (!a->workspace || a->workspace_bytes < need || (reinterpret_cast<uintptr_t>(a->workspace) & 255u))
     return fail(FNB_ERR_WORKSPACE, "backward workspace must be 256-byte aligned and >= %zu bytes (got %zu)",
@@ -1062,10 +1000,12 @@ int fnb_backward(const fnb_bwd_args* a) {
   int max_smem = 0, cc = 0, sms = 0;
   if (int rc = device_limits(a->device, &max_smem, &cc, &sms)) return rc;
   cudaStream_t st = (cudaStream_t)a->stream;
+  Plan p = plan_of(a->shape);
+  BwdWs w = carve_bwd(p, a->workspace);
   switch (a->shape.dtype) {
-    case FNB_F32: return backward_groups<float>(*a, max_smem, sms, st);
-    case FNB_F16: return backward_groups<__half>(*a, max_smem, sms, st);
-    default: return backward_groups<__nv_bfloat16>(*a, max_smem, sms, st);
+    case FNB_F32: return backward_impl<float>(*a, p, w, max_smem, sms, st, true);
+    case FNB_F16: return backward_impl<__half>(*a, p, w, max_smem, sms, st, true);
+    default: return backward_impl<__nv_bfloat16>(*a, p, w, max_smem, sms, st, true);
   }
 }
 
@@ -1101,6 +1041,7 @@ int fnb_sp_forward(const fnb_fwd_args* a, const fnb_sp_info* sp) {
   if (!a) return fail(FNB_ERR_INVALID_ARGUMENT, "args is NULL");
   if (int rc = check_shape(&a->shape)) return rc;
   if (int rc = check_sp(a->shape, sp, 0)) return rc;
+  if (int rc = check_fwd_pointers(a)) return rc;
   const size_t need = fwd_ws_total(a->shape);
   if (!a->workspace || a->workspace_bytes < need || (reinterpret_cast<uintptr_t>(a->workspace) & 255u))
     return fail(FNB_ERR_WORKSPACE, "forward workspace must be 256-byte aligned and >= %zu bytes (got %zu)", need,
@@ -1125,6 +1066,7 @@ int fnb_sp_backward(const fnb_bwd_args* a, const fnb_sp_info* sp) {
   if (!a) return fail(FNB_ERR_INVALID_ARGUMENT, "args is NULL");
   if (int rc = check_shape(&a->shape)) return rc;
   if (int rc = check_sp(a->shape, sp, 1)) return rc;
+  if (int rc = check_bwd_pointers(a)) return rc;
   const size_t need = bwd_ws_total(a->shape);
   if (!a->workspace || a->workspace_bytes < need || (reinterpret_cast<uintptr_t>(a->workspace) & 255u))
     return fail(FNB_ERR_WORKSPACE, "backward workspace must be 256-byte aligned and >= %zu bytes (got %zu)", need,
@@ -1179,8 +1121,11 @@ int fnb_debug_pinv_forward(int64_t bh, int32_t m, int32_t J, float kappa, const 
     ns::ns_pinv_fwd_debug_kernel<<<(unsigned)bh, kThreads, ns::kFwdSmem, (cudaStream_t)stream>>>(
         k2, ns_iterates, k2_inv, m, J, kappa);
   } else {
-    pinv_fwd_debug_kernel<<<(unsigned)bh, kThreads, 0, (cudaStream_t)stream>>>(
-        k2, ns_iterates, k2_inv, (float*)workspace, m, J, kappa);
+    const int use_tc = ns_on_tensor_cores(0) ? 1 : 0;
+    if (use_tc)
+      FNB_CUDA(cudaFuncSetAttribute(pinv_fwd_debug_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcGemmSmem));
+    pinv_fwd_debug_kernel<<<(unsigned)bh, kThreads, use_tc ? kTcGemmSmem : 0, (cudaStream_t)stream>>>(
+        k2, ns_iterates, k2_inv, (float*)workspace, m, J, kappa, use_tc);
   }
   FNB_CUDA(cudaPeekAtLastError());
   return 0;
@@ -1204,8 +1149,11 @@ int fnb_debug_pinv_backward(int64_t bh, int32_t m, int32_t J, float kappa, const
     ns::ns_pinv_bwd_debug_kernel<<<(unsigned)bh, kThreads, ns::kBwdSmem, (cudaStream_t)stream>>>(
         k2, ns_iterates, d_k2_inv, d_k2, (float*)workspace, m, J, kappa);
   } else {
-    pinv_bwd_debug_kernel<<<(unsigned)bh, kThreads, 0, (cudaStream_t)stream>>>(
-        k2, ns_iterates, d_k2_inv, d_k2, (float*)workspace, m, J, kappa);
+    const int use_tc = ns_on_tensor_cores(0) ? 1 : 0;
+    if (use_tc)
+      FNB_CUDA(cudaFuncSetAttribute(pinv_bwd_debug_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcGemmSmem));
+    pinv_bwd_debug_kernel<<<(unsigned)bh, kThreads, use_tc ? kTcGemmSmem : 0, (cudaStream_t)stream>>>(
+        k2, ns_iterates, d_k2_inv, d_k2, (float*)workspace, m, J, kappa, use_tc);
   }
   FNB_CUDA(cudaPeekAtLastError());
   return 0;

@@ -13,8 +13,199 @@
 #pragma once
 #include "common.cuh"
 #include "small_kernels.cuh"
+#include "tc_common.cuh"
 
 namespace fnb {
+
+// ---- products on the tensor cores ------------------------------------------------------------
+// The (<= 128)^3 FP32 products of the middle stages, with FP32-equivalent arithmetic on tcgen05:
+// each operand is copied from global memory into shared memory as three bf16 terms
+// x = x0 + x1 + x2 (24 significant bits together), stored exactly as it is laid out in memory
+// (rows x columns, 128-byte swizzle, two 64-column blocks of [128 rows x 128 B] per term), so that
+// a transposed use only changes the shared-memory descriptor (K-major or MN-major).  The six
+// partial products x_i y_j with i + j <= 2 accumulate into one 128 x 128 FP32 accumulator in
+// tensor memory (48 MMAs of M = N = 128, K = 16 for a full 128^3 product), and the epilogue applies
+// alpha, beta C and the diagonal term on the way back to global memory.  One CTA of 256 threads per
+// slice; thread 0 issues the MMAs.  A kernel that wants this path gives its GemmWs the tile area
+// (2 x 96 KB of dynamic shared memory, 1024-byte aligned), an mbarrier and 128 columns of tensor
+// memory; with tiles == nullptr the products run on the CUDA cores (cta_gemm below).
+constexpr int kTcGemmTerm = 128 * 256;            // one bf16 term of a 128 x 128 operand
+constexpr int kTcGemmSet = 3 * kTcGemmTerm;       // the three terms
+constexpr size_t kTcGemmSmem = 2 * (size_t)kTcGemmSet + 1024;
+
+struct GemmWs {
+  float* sm;            // staging / reduction scratch of the CUDA-core code (kGemmSmemFloats floats)
+  uint8_t* tiles;       // null: CUDA-core products
+  uint64_t* bar;
+  uint32_t tmem;
+  uint32_t phase;
+  int* status;
+};
+
+// rows x cols FP32 matrix in global memory (leading dimension ld) -> three swizzled bf16 term tiles,
+// zero beyond rows / cols.  All 256 threads.
+__device__ inline void tc_gemm_load(uint8_t* set, const float* src, int ld, int rows, int cols) {
+  // 128 rows x 16 chunks of 8 columns = 2048 items, 8 per thread; all of a thread's global loads are
+  // issued before the first value is used (one round trip to L2 instead of eight)
+  constexpr int kItems = 128 * 16 / kThreads;
+  const bool vec = (ld & 3) == 0 && (cols & 7) == 0 && (reinterpret_cast<uintptr_t>(src) & 15u) == 0;
+  float v[kItems][8];
+#pragma unroll
+  for (int it = 0; it < kItems; ++it) {
+    const int item = threadIdx.x + it * kThreads;
+    const int r = item >> 4, c0 = (item & 15) * 8;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[it][i] = 0.f;
+    if (r < rows && c0 < cols) {
+      const float* g = src + (size_t)r * ld + c0;
+      if (vec) {
+        const float4 a = *reinterpret_cast<const float4*>(g), b = *reinterpret_cast<const float4*>(g + 4);
+        v[it][0] = a.x; v[it][1] = a.y; v[it][2] = a.z; v[it][3] = a.w;
+        v[it][4] = b.x; v[it][5] = b.y; v[it][6] = b.z; v[it][7] = b.w;
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) if (c0 + i < cols) v[it][i] = g[i];
+      }
+    }
+  }
+#pragma unroll
+  for (int it = 0; it < kItems; ++it) {
+    const int item = threadIdx.x + it * kThreads;
+    const int r = item >> 4, ch = item & 15;
+    uint32_t w0[4], w1[4], w2[4];
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+      float a = v[it][2 * p], b = v[it][2 * p + 1];
+      w0[p] = tc::pack2<__nv_bfloat16>(a, b);
+      a -= __uint_as_float(w0[p] << 16);
+      b -= __uint_as_float(w0[p] & 0xffff0000u);
+      w1[p] = tc::pack2<__nv_bfloat16>(a, b);
+      a -= __uint_as_float(w1[p] << 16);
+      b -= __uint_as_float(w1[p] & 0xffff0000u);
+      w2[p] = tc::pack2<__nv_bfloat16>(a, b);
+    }
+    const uint32_t off = (uint32_t)(ch >> 3) * (128 * 128) + tc::sw128_offset(r, ch & 7);
+    *reinterpret_cast<uint4*>(set + off) = make_uint4(w0[0], w0[1], w0[2], w0[3]);
+    *reinterpret_cast<uint4*>(set + kTcGemmTerm + off) = make_uint4(w1[0], w1[1], w1[2], w1[3]);
+    *reinterpret_cast<uint4*>(set + 2 * kTcGemmTerm + off) = make_uint4(w2[0], w2[1], w2[2], w2[3]);
+  }
+}
+
+// descriptor of k-step k (16 elements of the contraction) of a term tile.
+//   along_rows: the contraction index runs along the tile's rows (MN-major operand), else along its
+//   columns (K-major operand)
+__device__ __forceinline__ uint64_t tc_gemm_desc(uint32_t tile, bool along_rows, int k) {
+  return along_rows ? tc::smem_desc_sw128(tile + k * 2048, 128 * 128, 1024)
+                    : tc::smem_desc_sw128(tile + (k >> 2) * (128 * 128) + (k & 3) * 32, 16, 1024);
+}
+
+template <bool TA, bool TB>
+__device__ inline void cta_gemm_tc(float* C, int ldc, const float* A, int lda, const float* B, int ldb, int M, int N,
+                                   int K, float alpha, float beta, float diag, GemmWs& ws) {
+  uint8_t* setA = ws.tiles;
+  uint8_t* setB = ws.tiles + kTcGemmSet;
+  // operands exactly as stored: A is (M x K) or, transposed, (K x M); B is (K x N) or (N x K)
+  tc_gemm_load(setA, A, lda, TA ? K : M, TA ? M : K);
+  tc_gemm_load(setB, B, ldb, TB ? N : K, TB ? K : N);
+  tc::fence_proxy_async();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    tc::tc_fence_after();
+    // A operand: K-major unless stored transposed; B operand: MN-major unless stored transposed
+    const uint32_t idesc = tc::make_idesc<__nv_bfloat16>(128, 128, TA, !TB);
+    const uint32_t a0 = tc::smem_u32(setA), b0 = tc::smem_u32(setB);
+    const int ksteps = (K + 15) >> 4;
+    const int order[6][2] = {{1, 1}, {0, 2}, {2, 0}, {0, 1}, {1, 0}, {0, 0}};   // small terms first
+    uint32_t acc = 0;
+    for (int t = 0; t < 6; ++t) {
+      const uint32_t ta = a0 + order[t][0] * kTcGemmTerm, tb = b0 + order[t][1] * kTcGemmTerm;
+      for (int k = 0; k < ksteps; ++k) {
+        tc::umma(ws.tmem, tc_gemm_desc(ta, TA, k), tc_gemm_desc(tb, !TB, k), idesc, acc);
+        acc = 1;
+      }
+    }
+    tc::umma_commit(ws.bar);
+  }
+  {
+    tc::Abort ab{reinterpret_cast<volatile int*>(ws.bar + 1), ws.status};
+    tc::mbar_wait(ws.bar, ws.phase, ab, 0x5000);
+    ws.phase ^= 1u;
+  }
+  tc::tc_fence_after();
+  // epilogue: warp w reads TMEM lanes 32 (w & 3) .. + 31 (= rows), columns 64 (w >> 2) .. + 63
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int r = (warp & 3) * 32 + lane, cbase = (warp >> 2) * 64;
+  const uint32_t taddr = ws.tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)cbase;
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    float v[32];
+    tc::tmem_ld32(taddr + half * 32, v);
+    tc::tmem_ld_wait();
+    if (r < M) {
+      const int c0 = cbase + half * 32;
+      float* crow = C + (size_t)r * ldc;
+      if ((ldc & 3) == 0 && (N & 3) == 0 && (reinterpret_cast<uintptr_t>(C) & 15u) == 0) {
+        // 16-byte accesses; the old values of C (beta != 0) are fetched in one batch first
+        float4 old[8];
+        if (beta != 0.f) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            old[j] = (c0 + 4 * j < N) ? *reinterpret_cast<const float4*>(crow + c0 + 4 * j) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int c = c0 + 4 * j;
+          if (c < N) {
+            float4 o = make_float4(alpha * v[4 * j], alpha * v[4 * j + 1], alpha * v[4 * j + 2], alpha * v[4 * j + 3]);
+            if (beta != 0.f) { o.x += beta * old[j].x; o.y += beta * old[j].y; o.z += beta * old[j].z; o.w += beta * old[j].w; }
+            if (r >= c && r < c + 4) (&o.x)[r - c] += diag;
+            *reinterpret_cast<float4*>(crow + c) = o;
+          }
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const int c = c0 + j;
+          if (c < N) {
+            float val = alpha * v[j];
+            if (beta != 0.f) val += beta * crow[c];
+            if (r == c) val += diag;
+            crow[c] = val;
+          }
+        }
+      }
+    }
+  }
+  tc::tc_fence_before();
+  __syncthreads();
+}
+
+// set-up / teardown of the tensor-core products inside a 256-thread kernel (all threads call)
+__device__ inline void gemm_ws_open(GemmWs& ws, float* sm, uint8_t* dyn, bool use_tc, uint64_t* bar_and_flag,
+                                    uint32_t* tmem_slot, int* status) {
+  ws.sm = sm; ws.tiles = nullptr; ws.bar = bar_and_flag; ws.tmem = 0; ws.phase = 0; ws.status = status;
+  if (!use_tc) return;
+  ws.tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(dyn) + 1023) & ~(uintptr_t)1023);
+  if (threadIdx.x == 0) {
+    tc::mbar_init(bar_and_flag, 1);
+    *reinterpret_cast<volatile int*>(bar_and_flag + 1) = 0;   // abort flag of the bounded wait
+    tc::fence_mbar_init();
+  }
+  if (threadIdx.x < 32) {
+    tc::tmem_alloc(tmem_slot, 128);
+    tc::tmem_relinquish();
+  }
+  tc::tc_fence_before();
+  __syncthreads();
+  tc::tc_fence_after();
+  ws.tmem = *tmem_slot;
+}
+__device__ inline void gemm_ws_close(GemmWs& ws) {
+  if (!ws.tiles) return;
+  tc::tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x < 32) tc::tmem_dealloc(ws.tmem, 128);
+}
 
 constexpr int kGemmKT = 16;            // k-slab depth
 constexpr int kGemmLd = kMaxM + 4;     // shared row stride of a slab
@@ -28,7 +219,12 @@ constexpr int kGemmSmemFloats = 2 * kGemmKT * kGemmLd;
 // be read through the coherent path.
 template <bool TA, bool TB>
 __device__ __noinline__ void cta_gemm(float* C, int ldc, const float* A, int lda, const float* B, int ldb,
-                         int M, int N, int K, float alpha, float beta, float diag, float* sm) {
+                         int M, int N, int K, float alpha, float beta, float diag, GemmWs& ws) {
+  if (ws.tiles) {
+    cta_gemm_tc<TA, TB>(C, ldc, A, lda, B, ldb, M, N, K, alpha, beta, diag, ws);
+    return;
+  }
+  float* sm = ws.sm;
   float* As = sm;
   float* Bs = sm + kGemmKT * kGemmLd;
   const int t = threadIdx.x, tx = t & 15, ty = t >> 4;
@@ -140,18 +336,18 @@ constexpr int kPinvFwdBufs = 4;
 // Newton-Schulz pseudoinverse of the softmax matrix k2 (optionally ridge-regularised through
 // the normal equations).  Every iterate Z_0..Z_J is stored; k2inv = Z_J or Z_J * k2^T.
 __device__ inline void pinv_forward(const float* k2, float* iterates, float* k2inv,
-                                    float* scratch, int m, int J, float kappa, float* sm) {
+                                    float* scratch, int m, int J, float kappa, GemmWs& ws) {
   const int mm = m * m;
   float* Ab = scratch;            // ridge matrix (only with kappa > 0)
   float* Mb = scratch + mm;
   float* Ub = scratch + 2 * mm;
   float* Vb = scratch + 3 * mm;
-  float* red = sm;                // norms use the first 2*kMaxM floats of the gemm staging area
+  float* red = ws.sm;             // norms use the first 2*kMaxM floats of the gemm staging area
   const float* A = k2;
   if (kappa > 0.f) {
     Norms nk = cta_norms(k2, m, red);
     float lam = nk.n1 * nk.ninf / kappa;
-    cta_gemm<true, false>(Ab, m, k2, m, k2, m, m, m, m, 1.f, 0.f, lam, sm);
+    cta_gemm<true, false>(Ab, m, k2, m, k2, m, m, m, m, 1.f, 0.f, lam, ws);
     A = Ab;
   }
   Norms na = cta_norms(A, m, red);
@@ -164,15 +360,15 @@ __device__ inline void pinv_forward(const float* k2, float* iterates, float* k2i
   for (int j = 0; j < J; ++j) {
     const float* Z = iterates + (size_t)j * mm;
     float* Zn = iterates + (size_t)(j + 1) * mm;
-    cta_gemm<false, false>(Mb, m, A, m, Z, m, m, m, m, 1.f, 0.f, 0.f, sm);        // M = A Z
+    cta_gemm<false, false>(Mb, m, A, m, Z, m, m, m, m, 1.f, 0.f, 0.f, ws);        // M = A Z
     cta_affine(Ub, Mb, -1.f, 7.f, m);                                             // U = 7I - M
-    cta_gemm<false, false>(Vb, m, Mb, m, Ub, m, m, m, m, -1.f, 0.f, 15.f, sm);    // V = 15I - M U
-    cta_gemm<false, false>(Ub, m, Mb, m, Vb, m, m, m, m, -1.f, 0.f, 13.f, sm);    // T = 13I - M V
-    cta_gemm<false, false>(Zn, m, Z, m, Ub, m, m, m, m, 0.25f, 0.f, 0.f, sm);     // Z' = Z T / 4
+    cta_gemm<false, false>(Vb, m, Mb, m, Ub, m, m, m, m, -1.f, 0.f, 15.f, ws);    // V = 15I - M U
+    cta_gemm<false, false>(Ub, m, Mb, m, Vb, m, m, m, m, -1.f, 0.f, 13.f, ws);    // T = 13I - M V
+    cta_gemm<false, false>(Zn, m, Z, m, Ub, m, m, m, m, 0.25f, 0.f, 0.f, ws);     // Z' = Z T / 4
   }
   const float* ZJ = iterates + (size_t)J * mm;
   if (kappa > 0.f) {
-    cta_gemm<false, true>(k2inv, m, ZJ, m, k2, m, m, m, m, 1.f, 0.f, 0.f, sm);
+    cta_gemm<false, true>(k2inv, m, ZJ, m, k2, m, m, m, m, 1.f, 0.f, 0.f, ws);
   } else {
     for (int idx = threadIdx.x; idx < mm; idx += kThreads) k2inv[idx] = ZJ[idx];
     __syncthreads();
@@ -185,7 +381,7 @@ constexpr int kPinvBwdBufs = 12;
 //   G = dL/d k2inv  ->  dK2 = dL/d k2.
 __device__ inline void pinv_backward(const float* k2, const float* iterates, const float* G,
                                      float* dK2, float* scratch, int m, int J, float kappa,
-                                     float* sm) {
+                                     GemmWs& ws) {
   const int mm = m * m;
   float* Ab = scratch;
   float* Mb = scratch + 1 * mm;
@@ -199,16 +395,16 @@ __device__ inline void pinv_backward(const float* k2, const float* iterates, con
   float* dM = scratch + 9 * mm;
   float* dA = scratch + 10 * mm;
   float* dK2a = scratch + 11 * mm;
-  float* red = sm;
+  float* red = ws.sm;
   const float* A = k2;
   const float* ZJ = iterates + (size_t)J * mm;
   if (kappa > 0.f) {
     Norms nk = cta_norms(k2, m, red);
     float lam = nk.n1 * nk.ninf / kappa;
-    cta_gemm<true, false>(Ab, m, k2, m, k2, m, m, m, m, 1.f, 0.f, lam, sm);
+    cta_gemm<true, false>(Ab, m, k2, m, k2, m, m, m, m, 1.f, 0.f, lam, ws);
     A = Ab;
-    cta_gemm<true, false>(dK2a, m, G, m, ZJ, m, m, m, m, 1.f, 0.f, 0.f, sm);   // G^T Z_J
-    cta_gemm<false, false>(dZ, m, G, m, k2, m, m, m, m, 1.f, 0.f, 0.f, sm);    // G K2
+    cta_gemm<true, false>(dK2a, m, G, m, ZJ, m, m, m, m, 1.f, 0.f, 0.f, ws);   // G^T Z_J
+    cta_gemm<false, false>(dZ, m, G, m, k2, m, m, m, m, 1.f, 0.f, 0.f, ws);    // G K2
   } else {
     for (int idx = threadIdx.x; idx < mm; idx += kThreads) dZ[idx] = G[idx];
   }
@@ -217,18 +413,18 @@ __device__ inline void pinv_backward(const float* k2, const float* iterates, con
 
   for (int j = J - 1; j >= 0; --j) {
     const float* Z = iterates + (size_t)j * mm;
-    cta_gemm<false, false>(Mb, m, A, m, Z, m, m, m, m, 1.f, 0.f, 0.f, sm);
+    cta_gemm<false, false>(Mb, m, A, m, Z, m, m, m, m, 1.f, 0.f, 0.f, ws);
     cta_affine(Ub, Mb, -1.f, 7.f, m);
-    cta_gemm<false, false>(Vb, m, Mb, m, Ub, m, m, m, m, -1.f, 0.f, 15.f, sm);
-    cta_gemm<false, false>(Tb, m, Mb, m, Vb, m, m, m, m, -1.f, 0.f, 13.f, sm);
-    cta_gemm<true, false>(dT, m, Z, m, dZ, m, m, m, m, 0.25f, 0.f, 0.f, sm);    // dT = Z^T dZ / 4
-    cta_gemm<false, true>(dZo, m, dZ, m, Tb, m, m, m, m, 0.25f, 0.f, 0.f, sm);  // dZ T^T / 4
-    cta_gemm<false, true>(dM, m, dT, m, Vb, m, m, m, m, -1.f, 0.f, 0.f, sm);    // -dT V^T
-    cta_gemm<true, false>(dV, m, Mb, m, dT, m, m, m, m, -1.f, 0.f, 0.f, sm);    // dV = -M^T dT
-    cta_gemm<false, true>(dM, m, dV, m, Ub, m, m, m, m, -1.f, 1.f, 0.f, sm);    // -= dV U^T
-    cta_gemm<true, false>(dM, m, Mb, m, dV, m, m, m, m, 1.f, 1.f, 0.f, sm);     // += M^T dV
-    cta_gemm<false, true>(dA, m, dM, m, Z, m, m, m, m, 1.f, 1.f, 0.f, sm);      // dA += dM Z^T
-    cta_gemm<true, false>(dZ, m, A, m, dM, m, m, m, m, 1.f, 0.f, 0.f, sm);      // A^T dM
+    cta_gemm<false, false>(Vb, m, Mb, m, Ub, m, m, m, m, -1.f, 0.f, 15.f, ws);
+    cta_gemm<false, false>(Tb, m, Mb, m, Vb, m, m, m, m, -1.f, 0.f, 13.f, ws);
+    cta_gemm<true, false>(dT, m, Z, m, dZ, m, m, m, m, 0.25f, 0.f, 0.f, ws);    // dT = Z^T dZ / 4
+    cta_gemm<false, true>(dZo, m, dZ, m, Tb, m, m, m, m, 0.25f, 0.f, 0.f, ws);  // dZ T^T / 4
+    cta_gemm<false, true>(dM, m, dT, m, Vb, m, m, m, m, -1.f, 0.f, 0.f, ws);    // -dT V^T
+    cta_gemm<true, false>(dV, m, Mb, m, dT, m, m, m, m, -1.f, 0.f, 0.f, ws);    // dV = -M^T dT
+    cta_gemm<false, true>(dM, m, dV, m, Ub, m, m, m, m, -1.f, 1.f, 0.f, ws);    // -= dV U^T
+    cta_gemm<true, false>(dM, m, Mb, m, dV, m, m, m, m, 1.f, 1.f, 0.f, ws);     // += M^T dV
+    cta_gemm<false, true>(dA, m, dM, m, Z, m, m, m, m, 1.f, 1.f, 0.f, ws);      // dA += dM Z^T
+    cta_gemm<true, false>(dZ, m, A, m, dM, m, m, m, m, 1.f, 0.f, 0.f, ws);      // A^T dM
     for (int idx = threadIdx.x; idx < mm; idx += kThreads) dZ[idx] += dZo[idx];
     __syncthreads();
   }
@@ -268,7 +464,7 @@ __device__ inline void pinv_backward(const float* k2, const float* iterates, con
       dM[idx] = dA[idx] + dA[cc * m + r];
     }
     __syncthreads();
-    cta_gemm<false, false>(dK2a, m, k2, m, dM, m, m, m, m, 1.f, 1.f, 0.f, sm);
+    cta_gemm<false, false>(dK2a, m, k2, m, dM, m, m, m, m, 1.f, 1.f, 0.f, ws);
     for (int idx = threadIdx.x; idx < mm; idx += kThreads) dK2[idx] = dK2a[idx];
   } else {
     for (int idx = threadIdx.x; idx < mm; idx += kThreads) dK2[idx] = dA[idx];
@@ -290,10 +486,15 @@ struct MidFwdParams {
   void* qt16;                 // optional [BH][MP][D] 16-bit copy of qt16_mul * qt (tensor-core path)
   int dtype, MP;
   float qt16_mul;
+  int use_tc;                 // products on the tensor cores (needs kTcGemmSmem bytes of dynamic shared memory)
+  int* status;
 };
 
 __global__ void __launch_bounds__(kThreads) mid_fwd_kernel(MidFwdParams p) {
   __shared__ float sm[kGemmSmemFloats];
+  __shared__ uint64_t gemm_bar[2];
+  __shared__ uint32_t gemm_tmem;
+  extern __shared__ uint8_t gemm_dyn[];
   const int64_t bh = blockIdx.x;
   const int m = p.m, D = p.D, t = threadIdx.x;
   Segments sg(p.N, m);
@@ -313,8 +514,10 @@ __global__ void __launch_bounds__(kThreads) mid_fwd_kernel(MidFwdParams p) {
     pack_pair(qt, reinterpret_cast<char*>(p.qt16) + (size_t)bh * p.MP * D * 2, nullptr, p.dtype, m, D, p.MP,
               p.qt16_mul);
   if (p.landmarks_only) return;
+  GemmWs ws;
+  gemm_ws_open(ws, sm, gemm_dyn, p.use_tc != 0, gemm_bar, &gemm_tmem, p.status);
   float* k2 = p.k2 + bh * m * m;
-  cta_gemm<false, true>(k2, m, qt, D, kt, D, m, m, D, 1.f, 0.f, 0.f, sm);
+  cta_gemm<false, true>(k2, m, qt, D, kt, D, m, m, D, 1.f, 0.f, 0.f, ws);
   // row softmax, one warp per row
   const int w = t >> 5, lane = t & 31;
   for (int r = w; r < m; r += kThreads / 32) {
@@ -329,25 +532,38 @@ __global__ void __launch_bounds__(kThreads) mid_fwd_kernel(MidFwdParams p) {
   }
   __syncthreads();
   pinv_forward(k2, p.iterates + bh * (size_t)(p.J + 1) * m * m, p.k2inv + bh * m * m,
-               p.scratch + bh * (size_t)kPinvFwdBufs * m * m, m, p.J, p.kappa, sm);
+               p.scratch + bh * (size_t)kPinvFwdBufs * m * m, m, p.J, p.kappa, ws);
+  gemm_ws_close(ws);
 }
 
 __global__ void __launch_bounds__(kThreads)
 pinv_fwd_debug_kernel(const float* k2, float* iterates, float* k2inv, float* scratch, int m,
-                      int J, float kappa) {
+                      int J, float kappa, int use_tc) {
   __shared__ float sm[kGemmSmemFloats];
+  __shared__ uint64_t gemm_bar[2];
+  __shared__ uint32_t gemm_tmem;
+  extern __shared__ uint8_t gemm_dyn[];
   const int64_t bh = blockIdx.x;
+  GemmWs ws;
+  gemm_ws_open(ws, sm, gemm_dyn, use_tc != 0, gemm_bar, &gemm_tmem, nullptr);
   pinv_forward(k2 + bh * m * m, iterates + bh * (size_t)(J + 1) * m * m, k2inv + bh * m * m,
-               scratch + bh * (size_t)kPinvFwdBufs * m * m, m, J, kappa, sm);
+               scratch + bh * (size_t)kPinvFwdBufs * m * m, m, J, kappa, ws);
+  gemm_ws_close(ws);
 }
 
 __global__ void __launch_bounds__(kThreads)
 pinv_bwd_debug_kernel(const float* k2, const float* iterates, const float* G, float* dK2,
-                      float* scratch, int m, int J, float kappa) {
+                      float* scratch, int m, int J, float kappa, int use_tc) {
   __shared__ float sm[kGemmSmemFloats];
+  __shared__ uint64_t gemm_bar[2];
+  __shared__ uint32_t gemm_tmem;
+  extern __shared__ uint8_t gemm_dyn[];
   const int64_t bh = blockIdx.x;
+  GemmWs ws;
+  gemm_ws_open(ws, sm, gemm_dyn, use_tc != 0, gemm_bar, &gemm_tmem, nullptr);
   pinv_backward(k2 + bh * m * m, iterates + bh * (size_t)(J + 1) * m * m, G + bh * m * m,
-                dK2 + bh * m * m, scratch + bh * (size_t)kPinvBwdBufs * m * m, m, J, kappa, sm);
+                dK2 + bh * m * m, scratch + bh * (size_t)kPinvBwdBufs * m * m, m, J, kappa, ws);
+  gemm_ws_close(ws);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -412,8 +628,10 @@ __global__ void __launch_bounds__(kThreads) combine_kernel(CombineParams p) {
     if (idx < total) bmat[idx] = acc[e] / gsum[idx / D];
   }
   __syncthreads();
+  GemmWs ws;
+  gemm_ws_open(ws, sm, nullptr, false, nullptr, nullptr, nullptr);
   cta_gemm<false, false>(p.step2 + bh * (size_t)total, D, p.k2inv + bh * m * m, m, bmat, D, m, D, m,
-                         1.f, 0.f, 0.f, sm);
+                         1.f, 0.f, 0.f, ws);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -434,10 +652,17 @@ struct MidBwdParams {
   int m, D, J;
   float kappa;
   int first_half_only;       // 1: stop after dO3 / dK2inv / D3 (the shared-memory NS kernel follows)
+  int use_tc;                // products on the tensor cores (needs kTcGemmSmem bytes of dynamic shared memory)
+  int* status;
 };
 
 __global__ void __launch_bounds__(kThreads) mid_bwd_kernel(MidBwdParams p) {
   __shared__ float sm[kGemmSmemFloats];
+  __shared__ uint64_t gemm_bar[2];
+  __shared__ uint32_t gemm_tmem;
+  extern __shared__ uint8_t gemm_dyn[];
+  GemmWs ws;
+  gemm_ws_open(ws, sm, gemm_dyn, p.use_tc != 0 && !p.first_half_only, gemm_bar, &gemm_tmem, p.status);
   const int64_t bh = blockIdx.x;
   const int m = p.m, D = p.D, t = threadIdx.x, mm = m * m, md = m * D;
   float* dstep2 = p.dstep2 + bh * md;
@@ -457,8 +682,8 @@ __global__ void __launch_bounds__(kThreads) mid_bwd_kernel(MidBwdParams p) {
   float* dO3 = p.dO3 + bh * md;
   float* G = p.G + bh * mm;
   float* dK2 = p.dK2 + bh * mm;
-  cta_gemm<true, false>(dO3, D, k2inv, m, dstep2, D, m, D, m, 1.f, 0.f, 0.f, sm);   // K2inv^T dstep2
-  cta_gemm<false, true>(G, m, dstep2, D, bmat, D, m, m, D, 1.f, 0.f, 0.f, sm);      // dstep2 Bmat^T
+  cta_gemm<true, false>(dO3, D, k2inv, m, dstep2, D, m, D, m, 1.f, 0.f, 0.f, ws);   // K2inv^T dstep2
+  cta_gemm<false, true>(G, m, dstep2, D, bmat, D, m, m, D, 1.f, 0.f, 0.f, ws);      // dstep2 Bmat^T
   {
     const int w = t >> 5, lane = t & 31;
     for (int l = w; l < m; l += kThreads / 32) {
@@ -470,7 +695,7 @@ __global__ void __launch_bounds__(kThreads) mid_bwd_kernel(MidBwdParams p) {
   }
   if (p.first_half_only) return;
   pinv_backward(k2, p.iterates + bh * (size_t)(p.J + 1) * mm, G, dK2,
-                p.scratch + bh * (size_t)kPinvBwdBufs * mm, m, p.J, p.kappa, sm);
+                p.scratch + bh * (size_t)kPinvBwdBufs * mm, m, p.J, p.kappa, ws);
   // softmax-2 Jacobian, in place: dS2 = K2 o (dK2 - rowsum(dK2 o K2))
   {
     const int w = t >> 5, lane = t & 31;
@@ -484,10 +709,11 @@ __global__ void __launch_bounds__(kThreads) mid_bwd_kernel(MidBwdParams p) {
   __syncthreads();
   float* dqt_ns = p.dqt_ns + bh * md;
   float* dkt_tot = p.dkt_tot + bh * md;
-  cta_gemm<false, false>(dqt_ns, D, dK2, m, kt, D, m, D, m, 1.f, 0.f, 0.f, sm);      // dS2 Kt
+  cta_gemm<false, false>(dqt_ns, D, dK2, m, kt, D, m, D, m, 1.f, 0.f, 0.f, ws);      // dS2 Kt
   for (int idx = t; idx < md; idx += kThreads) dkt_tot[idx] = dkt_a[idx];
   __syncthreads();
-  cta_gemm<true, false>(dkt_tot, D, dK2, m, qt, D, m, D, m, 1.f, 1.f, 0.f, sm);      // += dS2^T Qt
+  cta_gemm<true, false>(dkt_tot, D, dK2, m, qt, D, m, D, m, 1.f, 1.f, 0.f, ws);      // += dS2^T Qt
+  gemm_ws_close(ws);
 }
 
 // dqt_tot = dqt_ns + sum over chunks of the column-pass partials

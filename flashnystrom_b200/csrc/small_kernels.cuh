@@ -430,6 +430,40 @@ __global__ void __launch_bounds__(kThreads) combine_slab_kernel(CombineSlabParam
 }
 
 // ------------------------------------------------------------------------------------------
+// After the global-memory middle stage of the backward (num_landmarks > 64), what the tensor-core
+// column pass and the in-place pass read: the 16-bit operand copies dO3 / 2^e (with 2^e >= max |dO3|)
+// and qt_mul * Qt, padded to MP rows, and the per-landmark rows scale * dKt_tot / len.
+struct MidPackParams {
+  const float* dO3; const float* q_landmarks; const float* dkt_tot;   // [BH][m][D]
+  void* do3n; float* do3_scale; void* qt16; float* rows_k;
+  int m, D, MP, dtype;
+  float qt_mul, scale;
+  int64_t N;
+};
+__global__ void __launch_bounds__(kThreads) mid_pack_kernel(MidPackParams p) {
+  __shared__ float red[8];
+  const int64_t bh = blockIdx.x;
+  const int md = p.m * p.D, t = threadIdx.x;
+  const float* dO3 = p.dO3 + bh * (int64_t)md;
+  float amax = 0.f;
+  for (int idx = t; idx < md; idx += kThreads) amax = fmaxf(amax, fabsf(dO3[idx]));
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  if ((t & 31) == 0) red[t >> 5] = amax;
+  __syncthreads();
+  float cmax = red[0];
+  for (int w = 1; w < kThreads / 32; ++w) cmax = fmaxf(cmax, red[w]);
+  const float sc = pow2_scale(cmax);
+  if (t == 0) p.do3_scale[bh] = sc;
+  const size_t ob = (size_t)bh * p.MP * p.D * 2;
+  pack_pair(dO3, reinterpret_cast<char*>(p.do3n) + ob, nullptr, p.dtype, p.m, p.D, p.MP, 1.f / sc);
+  pack_pair(p.q_landmarks + bh * (int64_t)md, reinterpret_cast<char*>(p.qt16) + ob, nullptr, p.dtype, p.m, p.D, p.MP,
+            p.qt_mul);
+  Segments sg(p.N, p.m);
+  for (int idx = t; idx < md; idx += kThreads)
+    p.rows_k[bh * (int64_t)md + idx] = p.dkt_tot[bh * (int64_t)md + idx] * (p.scale / (float)sg.len(idx / p.D));
+}
+
+// ------------------------------------------------------------------------------------------
 struct PackBwdAcParams {
   const float* k_landmarks; const float* step2;
   void* kt16;      // [BH][MP][D] = kt_mul * Kt

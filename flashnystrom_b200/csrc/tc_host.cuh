@@ -82,7 +82,7 @@ inline TcSched make_sched(int64_t BH, int64_t N, int slots) {
 inline bool tc_supported(int dtype, int D, int m, uint32_t flags) {
   if (flags & FNB_FLAG_FORCE_GENERIC) return false;
   if (dtype != FNB_F16 && dtype != FNB_BF16) return false;
-  return (D == 64 || D == 128) && m <= 64;
+  return (D == 64 && m <= 64) || (D == 128 && m <= 128);
 }
 
 }  // namespace tc

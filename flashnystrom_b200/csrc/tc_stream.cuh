@@ -107,30 +107,25 @@ __device__ __forceinline__ uint64_t mndesc(uint32_t base, int k) {
 }
 
 // Compute warps (256 threads): 16-bit swizzled operand tiles of two (m x D) landmark matrices of one
-// slice straight from their FP32 originals (64 rows, rows >= m zero; D / 64 blocks of
-// [64 rows x 128 B] each):
+// slice straight from their FP32 originals (MP rows, rows >= m zero; D / 64 blocks of
+// [MP rows x 128 B] each):
 //   tile_a = mul_a * A,   tile_b = B / sc  with sc the power of two >= max |B|   (returned).
-// Thread t packs row t >> 2, columns (D / 4) (t & 3) .. + D / 4 - 1.  scratch: 8 floats of shared
-// memory; named barrier 3 is used once.  The caller fences and signals the MMA thread.
-template <class T, int D>
+// 256 / MP threads share a row; each packs D MP / 256 consecutive columns, eight at a time (B is read
+// twice, once for its maximum).  scratch: 8 floats of shared memory; named barrier 3 is used once.
+// The caller fences and signals the MMA thread.
+template <class T, int D, int MP>
 __device__ __forceinline__ float pack_landmark_operands(uint8_t* tile_a, uint8_t* tile_b, const float* A,
                                                         const float* B, int m, float mul_a, float* scratch) {
-  constexpr int CPT = D / 4;
-  const int t = threadIdx.x, r = t >> 2, c0 = (t & 3) * CPT;
-  float a[CPT], b[CPT];
-#pragma unroll
-  for (int q = 0; q < CPT / 4; ++q) {
-    float4 x = make_float4(0.f, 0.f, 0.f, 0.f), y = x;
-    if (r < m) {
-      x = *reinterpret_cast<const float4*>(A + r * D + c0 + 4 * q);
-      y = *reinterpret_cast<const float4*>(B + r * D + c0 + 4 * q);
-    }
-    a[4 * q] = x.x; a[4 * q + 1] = x.y; a[4 * q + 2] = x.z; a[4 * q + 3] = x.w;
-    b[4 * q] = y.x; b[4 * q + 1] = y.y; b[4 * q + 2] = y.z; b[4 * q + 3] = y.w;
-  }
+  constexpr int TPR = kComputeThreads / MP, CPT = D / TPR;
+  const int t = threadIdx.x, r = t / TPR, c0 = (t % TPR) * CPT;
   float amax = 0.f;
+  if (r < m) {
 #pragma unroll
-  for (int i = 0; i < CPT; ++i) amax = fmaxf(amax, fabsf(b[i]));
+    for (int q = 0; q < CPT / 4; ++q) {
+      const float4 y = *reinterpret_cast<const float4*>(B + r * D + c0 + 4 * q);
+      amax = fmaxf(fmaxf(amax, fmaxf(fabsf(y.x), fabsf(y.y))), fmaxf(fabsf(y.z), fabsf(y.w)));
+    }
+  }
   for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
   if ((t & 31) == 0) scratch[t >> 5] = amax;
   named_barrier(3, kComputeThreads);
@@ -140,13 +135,20 @@ __device__ __forceinline__ float pack_landmark_operands(uint8_t* tile_a, uint8_t
   const float sc = pow2_scale(cmax), inv = 1.f / sc;
 #pragma unroll
   for (int c = 0; c < CPT / 8; ++c) {
+    float4 x0 = make_float4(0.f, 0.f, 0.f, 0.f), x1 = x0, y0 = x0, y1 = x0;
+    if (r < m) {
+      x0 = *reinterpret_cast<const float4*>(A + r * D + c0 + 8 * c);
+      x1 = *reinterpret_cast<const float4*>(A + r * D + c0 + 8 * c + 4);
+      y0 = *reinterpret_cast<const float4*>(B + r * D + c0 + 8 * c);
+      y1 = *reinterpret_cast<const float4*>(B + r * D + c0 + 8 * c + 4);
+    }
     uint4 wa, wb;
-    wa.x = pack2<T>(a[8 * c + 0] * mul_a, a[8 * c + 1] * mul_a); wa.y = pack2<T>(a[8 * c + 2] * mul_a, a[8 * c + 3] * mul_a);
-    wa.z = pack2<T>(a[8 * c + 4] * mul_a, a[8 * c + 5] * mul_a); wa.w = pack2<T>(a[8 * c + 6] * mul_a, a[8 * c + 7] * mul_a);
-    wb.x = pack2<T>(b[8 * c + 0] * inv, b[8 * c + 1] * inv); wb.y = pack2<T>(b[8 * c + 2] * inv, b[8 * c + 3] * inv);
-    wb.z = pack2<T>(b[8 * c + 4] * inv, b[8 * c + 5] * inv); wb.w = pack2<T>(b[8 * c + 6] * inv, b[8 * c + 7] * inv);
+    wa.x = pack2<T>(x0.x * mul_a, x0.y * mul_a); wa.y = pack2<T>(x0.z * mul_a, x0.w * mul_a);
+    wa.z = pack2<T>(x1.x * mul_a, x1.y * mul_a); wa.w = pack2<T>(x1.z * mul_a, x1.w * mul_a);
+    wb.x = pack2<T>(y0.x * inv, y0.y * inv); wb.y = pack2<T>(y0.z * inv, y0.w * inv);
+    wb.z = pack2<T>(y1.x * inv, y1.y * inv); wb.w = pack2<T>(y1.z * inv, y1.w * inv);
     const int cc = (c0 >> 3) + c;
-    const uint32_t off = (uint32_t)(cc >> 3) * (64 * 128) + sw128_offset(r, cc & 7);
+    const uint32_t off = (uint32_t)(cc >> 3) * (MP * 128) + sw128_offset(r, cc & 7);
     *reinterpret_cast<uint4*>(tile_a + off) = wa;
     *reinterpret_cast<uint4*>(tile_b + off) = wb;
   }
@@ -338,7 +340,7 @@ tc_fwd_c_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 const float* __restrict__ k_landmarks, const float* __restrict__ step2,
                 float* __restrict__ lse1, TcSched sch, int m, float scale, int* status) {
   using L = FwdCSmem<D, MP>;
-  static_assert((D == 64 || D == 128) && MP == 64, "the in-kernel operand packing is written for 64 landmark rows");
+  static_assert((D == 64 && MP == 64) || (D == 128 && (MP == 64 || MP == 128)), "head_dim 64 with up to 64 landmarks, 128 with up to 128");
   constexpr int KBD = D / 64;
   constexpr int kGroup = kComputeThreads / 2;
   constexpr uint32_t kCols = 2 * MP + 2 * D;
@@ -445,7 +447,7 @@ tc_fwd_c_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const int r = threadIdx.x & 127;                           // tile row = TMEM lane
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     // operand copies of Kt and step2 for this slice (the P buffers are free until the first tile)
-    const float osc = pack_landmark_operands<T, D>(s_kt, s_st, k_landmarks + bh * m * D, step2 + bh * m * D, m,
+    const float osc = pack_landmark_operands<T, D, MP>(s_kt, s_st, k_landmarks + bh * m * D, step2 + bh * m * D, m,
                                                    scale * kLog2e, reinterpret_cast<float*>(s_p));
     fence_proxy_async();
     mbar_arrive_warp(small_full);
@@ -540,8 +542,10 @@ template <int D, int MP>
 struct BwdASmem {
   static constexpr int kKt = MP * D * 2, kSt = MP * D * 2, kIn = kTile * D * 2, kP = kTile * MP * 2,
                        kDs = kTile * MP * 2;
+  // (Q, dO) stages: two, or one where 128 landmarks leave no room for the second
+  static constexpr int kStages = MP == 128 ? 1 : 2;
   // relies on the dynamic shared window being 1024-byte aligned (checked at run time)
-  static constexpr int kBytes = kKt + kSt + 4 * kIn + kP + kDs + 256;
+  static constexpr int kBytes = kKt + kSt + 2 * kStages * kIn + kP + kDs + 256;
 };
 
 template <class T, int D, int MP>
@@ -551,10 +555,10 @@ tc_bwd_a_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 const float* __restrict__ k_landmarks, const float* __restrict__ step2,
                 const float* __restrict__ lse1, float* __restrict__ partA, float* __restrict__ sc_out,
                 TcSched sch, int m, float scale, int* status) {
-  static_assert((D == 64 || D == 128) && MP == 64, "written for 64 landmark rows");
+  static_assert((D == 64 && MP == 64) || (D == 128 && (MP == 64 || MP == 128)), "head_dim 64 with up to 64 landmarks, 128 with up to 128");
   using L = BwdASmem<D, MP>;
-  constexpr int HC = MP / 2, HD = D / 2;
-  constexpr uint32_t kTmemCols = 2 * MP + 2 * D <= 256 ? 256 : 512;    // S, dP, and the 2 D-column accumulator
+  constexpr int HC = MP / 2, HD = D / 2, NST = L::kStages;
+  constexpr uint32_t kTmemCols = 2 * MP + 2 * D <= 256 ? 256 : 512;    // S, dP, and 2 D accumulator columns
   extern __shared__ uint8_t smem_raw[];
   pdl_trigger();
   if (smem_u32(smem_raw) & 1023u) {
@@ -563,9 +567,9 @@ tc_bwd_a_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   }
   uint8_t* s_kt = smem_raw;
   uint8_t* s_st = s_kt + L::kKt;
-  uint8_t* s_q = s_st + L::kSt;          // two stages of [Q tile | dO tile]
+  uint8_t* s_q = s_st + L::kSt;          // NST stages of [Q tile | dO tile]
   uint8_t* s_g = s_q + L::kIn;
-  uint8_t* s_p = s_q + 4 * L::kIn;       // P tile (its head doubles as the D1 exchange)
+  uint8_t* s_p = s_q + 2 * NST * L::kIn; // P tile (its head doubles as the D1 exchange)
   uint8_t* s_ds = s_p + L::kP;           // dS tile
   float* s_x = reinterpret_cast<float*>(s_p);
   uint64_t* bars = reinterpret_cast<uint64_t*>(s_ds + L::kDs);
@@ -610,8 +614,8 @@ tc_bwd_a_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const uint64_t pol_q = l2_policy_of(sch.hint, 0), pol_g = l2_policy_of(sch.hint, 1);
       int armed = 0;
       for (int i = 0; i < count; ++i) {
-        const int st = i & 1;
-        if (!mbar_wait(in_empty + st, ((i >> 1) & 1) ^ 1, ab, 0x1100 + i)) break;
+        const int st = i % NST;
+        if (!mbar_wait(in_empty + st, ((i / NST) & 1) ^ 1, ab, 0x1100 + i)) break;
         mbar_expect_tx(in_full + st, 2 * L::kIn);
         for (int kb = 0; kb < D / 64; ++kb) {
           tma_load_3d_h(s_q + st * 2 * L::kIn + kb * (kTile * 128), &tm_q, in_full + st, kb * 64, tr.tile(i) * kTile, (int)bh, pol_q);
@@ -620,18 +624,18 @@ tc_bwd_a_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         armed = i + 1;
       }
       if (ab.raised())
-        for (int i = max(0, armed - 2); i < armed; ++i) mbar_drain(in_full + (i & 1), (i >> 1) & 1);
+        for (int i = max(0, armed - NST); i < armed; ++i) mbar_drain(in_full + (i % NST), (i / NST) & 1);
     }
   } else if (warp == kMmaWarp) {
     if (lane == 0) {
       constexpr uint32_t idesc_s = make_idesc<T>(kTile, MP, false, false);
-      constexpr uint32_t idesc_acc2 = make_idesc<T>(2 * MP, 2 * D, true, true);
+      constexpr uint32_t idesc_acc2 = make_idesc<T>(MP == 64 ? 128 : 128, MP == 64 ? 2 * D : D, true, true);
       const uint32_t a_kt = smem_u32(s_kt), a_st = smem_u32(s_st), a_p = smem_u32(s_p);
       const uint64_t pol_ds = l2_policy_of(sch.hint, 2);
       // S and dP of tile i
       auto front = [&](int i) -> bool {
-        const int st = i & 1;
-        if (!mbar_wait(in_full + st, (i >> 1) & 1, ab, 0x1300 + i)) return false;
+        const int st = i % NST;
+        if (!mbar_wait(in_full + st, (i / NST) & 1, ab, 0x1300 + i)) return false;
         tc_fence_after();
         const uint32_t a_q = smem_u32(s_q + st * 2 * L::kIn), a_g = smem_u32(s_g + st * 2 * L::kIn);
 #pragma unroll
@@ -646,20 +650,33 @@ tc_bwd_a_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       for (int i = 0; ok && i < count; ++i) {
         if (!mbar_wait(pds_full, i & 1, ab, 0x1400 + i)) break;
         tc_fence_after();
-        const int st = i & 1;
+        const int st = i % NST;
         // One 128 x 2D accumulator for both sums: [P | dS]^T [Q | dO] (both operands MN-major; the
         // 64-wide blocks of each follow one another in shared memory, 16 KB apart).  Rows 0..63 x
         // columns D..2D-1 hold P^T dO, rows 64..127 x columns 0..D-1 hold dS^T Q; the other two
         // quadrants are not used.  An M = N = 128 MMA takes 35 ns against 2 x 25 ns for two 64 x 64 ones.
+        if (MP == 64) {
 #pragma unroll
-        for (int k = 0; k < kTile / 16; ++k)
-          umma(tmem_base + 2 * MP, smem_desc_sw128(a_p + k * 2048, L::kP, 1024),
-               smem_desc_sw128(smem_u32(s_q + st * 2 * L::kIn) + k * 2048, kTile * 128, 1024), idesc_acc2, (i > 0 || k > 0));
+          for (int k = 0; k < kTile / 16; ++k)
+            umma(tmem_base + 2 * MP, smem_desc_sw128(a_p + k * 2048, L::kP, 1024),
+                 smem_desc_sw128(smem_u32(s_q + st * 2 * L::kIn) + k * 2048, kTile * 128, 1024), idesc_acc2, (i > 0 || k > 0));
+        } else {
+          // 128 landmarks: M = 128 each, so the two sums take an accumulator of their own
+          // (P^T dO in columns 2 MP .. + D - 1, dS^T Q in the D columns after them)
+          const uint32_t a_ds = smem_u32(s_ds);
+#pragma unroll
+          for (int k = 0; k < kTile / 16; ++k)
+            umma(tmem_base + 2 * MP, mndesc(a_p, k), mndesc(smem_u32(s_g + st * 2 * L::kIn), k), idesc_acc2, (i > 0 || k > 0));
+#pragma unroll
+          for (int k = 0; k < kTile / 16; ++k)
+            umma(tmem_base + 2 * MP + D, mndesc(a_ds, k), mndesc(smem_u32(s_q + st * 2 * L::kIn), k), idesc_acc2, (i > 0 || k > 0));
+        }
         // the accumulation goes first: its commit frees the (Q, dO) stage, and the pass is bound by
         // how early the next load is issued; then the scores of the next tile
         umma_commit(in_empty + st);
-        // the dS tile as it is -> dQ tile of the same rows
-        tma_store_3d_h(&tm_dq, s_ds, 0, tr.tile(i) * kTile, (int)bh, pol_ds);
+        // the dS tile as it is -> (the first MP columns of) the dQ tile of the same rows
+        for (int kb = 0; kb < MP / 64; ++kb)
+          tma_store_3d_h(&tm_dq, s_ds + kb * (kTile * 128), kb * 64, tr.tile(i) * kTile, (int)bh, pol_ds);
         tma_store_commit();
         if (i + 1 < count && !front(i + 1)) break;
         // acc_done lets the compute warps overwrite the dS tile: the copy must have read it
@@ -673,7 +690,7 @@ tc_bwd_a_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const int quarter = warp & 3;
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
     // operand copies of Kt and step2 for this slice (the dS tile is free until the first tile)
-    const float sc = pack_landmark_operands<T, D>(s_kt, s_st, k_landmarks + bh * m * D, step2 + bh * m * D, m,
+    const float sc = pack_landmark_operands<T, D, MP>(s_kt, s_st, k_landmarks + bh * m * D, step2 + bh * m * D, m,
                                                   scale * kLog2e, reinterpret_cast<float*>(s_ds));
     fence_proxy_async();
     mbar_arrive_warp(small_full);
@@ -720,20 +737,38 @@ tc_bwd_a_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     if (alive && mbar_wait(acc_done, (count - 1) & 1, ab, 0x1900)) {
       __syncwarp();
       tc_fence_after();
-      // 128-row accumulator: TMEM lane = row.  Quarters 0, 1 hold the dstep2 rows (columns
-      // 64..127), quarters 2, 3 the dKt rows (columns 0..63); this thread takes 32 columns.
-      const int which = quarter >> 1;
-      const int l = (quarter & 1) * 32 + lane;
-      float* dst = partA + ((size_t)bh * sch.nchunk + tr.chunk) * 2 * m * D + (size_t)which * m * D;
-      const float mul = which ? sc * scale : 1.f;
-      float o[HD];
-      ld_cols<HD>(tmem_base + 2 * MP + (which ? 0 : D) + lane_base + h * HD, o);
-      tmem_ld_wait();
-      if (l < m) {
+      if (MP == 64) {
+        // 128-row accumulator: TMEM lane = row.  Quarters 0, 1 hold the dstep2 rows (columns
+        // D..2D-1), quarters 2, 3 the dKt rows (columns 0..D-1); this thread takes half the columns.
+        const int which = quarter >> 1;
+        const int l = (quarter & 1) * 32 + lane;
+        float* dst = partA + ((size_t)bh * sch.nchunk + tr.chunk) * 2 * m * D + (size_t)which * m * D;
+        const float mul = which ? sc * scale : 1.f;
+        float o[HD];
+        ld_cols<HD>(tmem_base + 2 * MP + (which ? 0 : D) + lane_base + h * HD, o);
+        tmem_ld_wait();
+        if (l < m) {
 #pragma unroll
-        for (int j = 0; j < HD; j += 4)
-          *reinterpret_cast<float4*>(dst + l * D + h * HD + j) =
-              make_float4(o[j] * mul, o[j + 1] * mul, o[j + 2] * mul, o[j + 3] * mul);
+          for (int j = 0; j < HD; j += 4)
+            *reinterpret_cast<float4*>(dst + l * D + h * HD + j) =
+                make_float4(o[j] * mul, o[j + 1] * mul, o[j + 2] * mul, o[j + 3] * mul);
+        }
+      } else {
+        // two 128-row accumulators (lane = landmark): dstep2 first, then dKt
+#pragma unroll
+        for (int which = 0; which < 2; ++which) {
+          float* dst = partA + ((size_t)bh * sch.nchunk + tr.chunk) * 2 * m * D + (size_t)which * m * D;
+          const float mul = which ? sc * scale : 1.f;
+          float o[HD];
+          ld_cols<HD>(tmem_base + 2 * MP + which * D + lane_base + h * HD, o);
+          tmem_ld_wait();
+          if (r < m) {
+#pragma unroll
+            for (int j = 0; j < HD; j += 4)
+              *reinterpret_cast<float4*>(dst + r * D + h * HD + j) =
+                  make_float4(o[j] * mul, o[j + 1] * mul, o[j + 2] * mul, o[j + 3] * mul);
+          }
+        }
       }
     }
   }
@@ -773,19 +808,18 @@ struct RowsSide {
 
 template <int D, int MP>
 struct RowsSmem {
-  static constexpr int kStages = 4;
+  static constexpr int kStages = MP == 128 ? 2 : 4;   // 128-landmark tiles are twice as large
   static constexpr int kOp = MP * D * 2, kIn = kTile * MP * 2, kOut = kTile * D * 2;
   // relies on the dynamic shared window being 1024-byte aligned (checked at run time)
   static constexpr int kBytes = 2 * kOp + kStages * kIn + 2 * kOut + 256;
 };
 
-// 16-bit swizzled operand tile of one FP32 (m x D) landmark matrix (64 rows, rows >= m zero; D / 64
-// blocks of [64 rows x 128 B]), times mul; compute warps (256 threads): thread t packs row t >> 2,
-// columns (D / 4) (t & 3) .. + D / 4 - 1
-template <class T, int D>
+// 16-bit swizzled operand tile of one FP32 (m x D) landmark matrix (MP rows, rows >= m zero; D / 64
+// blocks of [MP rows x 128 B]), times mul; compute warps (256 threads): 256 / MP threads share a row
+template <class T, int D, int MP>
 __device__ __forceinline__ void pack_landmark_operand(uint8_t* tile, const float* A, int m, float mul) {
-  constexpr int CPT = D / 4;
-  const int t = threadIdx.x, r = t >> 2, c0 = (t & 3) * CPT;
+  constexpr int TPR = kComputeThreads / MP, CPT = D / TPR;
+  const int t = threadIdx.x, r = t / TPR, c0 = (t % TPR) * CPT;
 #pragma unroll
   for (int c = 0; c < CPT / 8; ++c) {
     float4 x = make_float4(0.f, 0.f, 0.f, 0.f), y = x;
@@ -797,7 +831,7 @@ __device__ __forceinline__ void pack_landmark_operand(uint8_t* tile, const float
     w.x = pack2<T>(x.x * mul, x.y * mul); w.y = pack2<T>(x.z * mul, x.w * mul);
     w.z = pack2<T>(y.x * mul, y.y * mul); w.w = pack2<T>(y.z * mul, y.w * mul);
     const int cc = (c0 >> 3) + c;
-    *reinterpret_cast<uint4*>(tile + (uint32_t)(cc >> 3) * (64 * 128) + sw128_offset(r, cc & 7)) = w;
+    *reinterpret_cast<uint4*>(tile + (uint32_t)(cc >> 3) * (MP * 128) + sw128_offset(r, cc & 7)) = w;
   }
 }
 
@@ -807,12 +841,13 @@ tc_rows_inplace_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_co
                        RowsSide side_a, RowsSide side_b, int nsides, float op_mul, TcSched sch, int m,
                        int* status) {
   using L = RowsSmem<D, MP>;
-  // a parked dS tile (MP = 64 columns) sits in the first 64 columns of the gradient tile of its rows
-  static_assert((D == 64 || D == 128) && MP == 64, "written for 64 landmark columns");
+  // a parked dS tile (MP columns) sits in the first MP columns of the gradient tile of its rows
+  static_assert((D == 64 && MP == 64) || (D == 128 && (MP == 64 || MP == 128)), "head_dim 64 with up to 64 landmarks, 128 with up to 128");
   constexpr int kGroup = kComputeThreads / 2;
   constexpr int kStages = L::kStages;
   constexpr uint32_t kTmemCols = kStages * D;
   static_assert(kTmemCols == 256 || kTmemCols == 512, "TMEM allocation must be a power of two");
+  static_assert(kStages % 2 == 0, "the two compute groups take alternate tiles and stages");
   extern __shared__ uint8_t smem_raw[];
   pdl_trigger();
   if (smem_u32(smem_raw) & 1023u) {
@@ -868,8 +903,9 @@ tc_rows_inplace_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_co
         const bool second = i >= count;
         if (!mbar_wait(in_empty + s, ((i / kStages) & 1) ^ 1, ab, 0x2100 + i)) break;
         mbar_expect_tx(in_full + s, L::kIn);
-        tma_load_3d_h(s_in + s * L::kIn, second ? &tm_b : &tm_a, in_full + s, 0,
-                      (second ? trb.tile(i - count) : tra.tile(i)) * kTile, (int)bh, second ? pol_b : pol_a);
+        for (int kb = 0; kb < MP / 64; ++kb)
+          tma_load_3d_h(s_in + s * L::kIn + kb * (kTile * 128), second ? &tm_b : &tm_a, in_full + s, kb * 64,
+                        (second ? trb.tile(i - count) : tra.tile(i)) * kTile, (int)bh, second ? pol_b : pol_a);
         armed = i + 1;
       }
       if (ab.raised())
@@ -902,8 +938,8 @@ tc_rows_inplace_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_co
     const int g = warp >> 2;
     const int r = threadIdx.x & 127;
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-    pack_landmark_operand<T, D>(s_op, side_a.landmarks + bh * m * D, m, op_mul);
-    if (nsides > 1) pack_landmark_operand<T, D>(s_op + L::kOp, side_b.landmarks + bh * m * D, m, op_mul);
+    pack_landmark_operand<T, D, MP>(s_op, side_a.landmarks + bh * m * D, m, op_mul);
+    if (nsides > 1) pack_landmark_operand<T, D, MP>(s_op + L::kOp, side_b.landmarks + bh * m * D, m, op_mul);
     fence_proxy_async();
     mbar_arrive_warp(small_full);
     const float mul_a = (side_a.out_scale ? side_a.out_scale[bh] : 1.f) * side_a.out_mul;
@@ -1141,7 +1177,8 @@ tc_bwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
         umma_commit(k_empty + st);
         // the dS' tile as it is -> dK tile of the same rows (after the products: their commit
         // frees the K stage)
-        tma_store_3d_h(&tm_dk, s_ds, 0, tr.tile(i) * kTile, (int)bh, pol_ds);
+        for (int kb = 0; kb < MP / 64; ++kb)
+          tma_store_3d_h(&tm_dk, s_ds + kb * (kTile * 128), kb * 64, tr.tile(i) * kTile, (int)bh, pol_ds);
         tma_store_commit();
         // out_full lets the compute warps move on to the next dS' tile: the copy must have read it
         tma_store_wait_read();
@@ -1307,7 +1344,9 @@ template <int D, int MP>
 struct FwdBSmem {
   static constexpr int kQt = MP * D * 2, kOnes = 2048, kIn = kTile * D * 2, kP = kTile * MP * 2,
                        kAux = 1024 * ((7 * MP * 4 + 64 + 1023) / 1024);
-  static constexpr int kBytes = kQt + kOnes + 4 * kIn + 2 * kP + kAux + 256 + 1024;
+  // V is double-buffered unless 128 landmarks x head_dim 128 leave no room for the second stage
+  static constexpr int kVStages = (MP == 128 && D == 128) ? 1 : 2;
+  static constexpr int kBytes = kQt + kOnes + (2 + kVStages) * kIn + 2 * kP + kAux + 256 + 1024;
 };
 
 template <class T, int D, int MP>
@@ -1330,8 +1369,9 @@ tc_fwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
   uint8_t* s_qt = base;
   uint8_t* s_ones = s_qt + L::kQt;
   uint8_t* s_k = s_ones + L::kOnes;            // two stages
-  uint8_t* s_v = s_k + 2 * L::kIn;             // two stages
-  uint8_t* s_p = s_v + 2 * L::kIn;             // two buffers, tile parity
+  constexpr int VS = L::kVStages;
+  uint8_t* s_v = s_k + 2 * L::kIn;             // VS stages
+  uint8_t* s_p = s_v + VS * L::kIn;            // two buffers, tile parity
   float* s_wmax = reinterpret_cast<float*>(s_p + 2 * L::kP);   // [4][MP]
   float* s_ref = s_wmax + 4 * MP;                          // [MP] running reference (log2 domain)
   float* s_fac = s_ref + MP;                               // [MP] rescale factor of this tile
@@ -1403,16 +1443,17 @@ tc_fwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
           tma_load_3d_h(s_k + st * L::kIn + kb * (kTile * 128), &tm_k, k_full + st, kb * 64, tr.tile(i) * kTile, (int)bh, pol_k);
         TC_TRACE(0, i);
         nk = i + 1;
-        if (!mbar_wait(v_empty + st, ((i >> 1) & 1) ^ 1, ab, 0x3180 + i)) break;
-        mbar_expect_tx(v_full + st, L::kIn);
+        const int sv = i % VS;
+        if (!mbar_wait(v_empty + sv, ((i / VS) & 1) ^ 1, ab, 0x3180 + i)) break;
+        mbar_expect_tx(v_full + sv, L::kIn);
         for (int kb = 0; kb < KBD; ++kb)
-          tma_load_3d_h(s_v + st * L::kIn + kb * (kTile * 128), &tm_v, v_full + st, kb * 64, tr.tile(i) * kTile, (int)bh, pol_v);
+          tma_load_3d_h(s_v + sv * L::kIn + kb * (kTile * 128), &tm_v, v_full + sv, kb * 64, tr.tile(i) * kTile, (int)bh, pol_v);
         TC_TRACE(1, i);
         nv = i + 1;
       }
       if (ab.raised()) {
         for (int i = max(0, nk - 2); i < nk; ++i) mbar_drain(k_full + (i & 1), (i >> 1) & 1);
-        for (int i = max(0, nv - 2); i < nv; ++i) mbar_drain(v_full + (i & 1), (i >> 1) & 1);
+        for (int i = max(0, nv - VS); i < nv; ++i) mbar_drain(v_full + (i % VS), (i / VS) & 1);
       }
     }
   } else if (warp == kMmaWarp) {
@@ -1441,10 +1482,11 @@ tc_fwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
         const int st = i & 1;
         if (!mbar_wait(p_full + st, (i >> 1) & 1, ab, 0x3400 + i)) break;
         TC_TRACE(3, i);
-        if (!mbar_wait(v_full + st, (i >> 1) & 1, ab, 0x3480 + i)) break;
+        const int sv = i % VS;
+        if (!mbar_wait(v_full + sv, (i / VS) & 1, ab, 0x3480 + i)) break;
         TC_TRACE(4, i);
         tc_fence_after();
-        const uint32_t a_v = smem_u32(s_v + st * L::kIn);
+        const uint32_t a_v = smem_u32(s_v + sv * L::kIn);
         const uint32_t a_pi = a_p + st * L::kP;
 #pragma unroll
         for (int k = 0; k < kTile / 16; ++k)
@@ -1453,7 +1495,7 @@ tc_fwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
         for (int k = 0; k < kTile / 16; ++k)
           umma(tmem_acc + D, mndesc(a_pi, k), smem_desc_sw128(a_ones + (k & 3) * 32, 16, 1024), idesc_sum,
                (i > 0 || k > 0));
-        umma_commit(v_empty + st);
+        umma_commit(v_empty + sv);
         umma_commit(acc_done + st);
         if (i + 2 < count) ok = front(i + 2);
       }
