@@ -434,7 +434,7 @@ def extra_configs(dev, steps, warmup, timed, peak):
         out[name] = {"shape": f"B={B},H={H},N={N},D={D},m={m},J={J},kappa*={kap} fp16", "ms_per_step": ms,
                      "tokens_per_s": B * N / (ms * 1e-3), "host_enqueue_ms_per_step": host_ms,
                      "frac_of_11_pass": 11 * B * H * N * D * 2 / (ms * 1e-3) / 1e9 / peak,
-                     "path": "tensor cores" if (D in (64, 128) and m <= 64) else "CUDA cores"}
+                     "path": "tensor cores" if ((D == 64 and m <= 64) or (D == 128 and m <= 128)) else "CUDA cores"}
         del q, k, v, dO
     torch.manual_seed(0)
     mod = FlashNystromAttention(512, heads=8, config=NystromConfig(num_landmarks=64, newton_iter=6, conv_kernel_size=3))

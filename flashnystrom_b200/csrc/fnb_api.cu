@@ -552,7 +552,7 @@ static int forward_impl(const fnb_fwd_args& a, const Plan& p, const FwdWs& w, in
       cp.acc_bh_stride = (int64_t)nchunk_b * p.m * p.D; cp.acc_chunk_stride = (int64_t)p.m * p.D;
       cp.vec_bh_stride = (int64_t)nchunk_b * p.m; cp.vec_chunk_stride = p.m;
     }
-    if (use_tc && p.m <= 64 && p.D % 16 == 0) {
+    if (use_tc && p.D % 16 == 0) {
       // the tensor-core output pass packs its own operand copies: merge + step2 only, spread over
       // D / 16 CTAs per slice
       CombineSlabParams sp2;
@@ -560,7 +560,9 @@ static int forward_impl(const fnb_fwd_args& a, const Plan& p, const FwdWs& w, in
       sp2.acc_bh_stride = cp.acc_bh_stride; sp2.acc_chunk_stride = cp.acc_chunk_stride;
       sp2.vec_bh_stride = cp.vec_bh_stride; sp2.vec_chunk_stride = cp.vec_chunk_stride;
       sp2.k2inv = a.k2_inv; sp2.bmat = a.bmat; sp2.lse3 = a.lse3; sp2.step2 = a.step2; sp2.m = p.m; sp2.D = p.D;
-      launch_pdl(combine_slab_kernel, dim3((unsigned)p.BH, (unsigned)(p.D / 16)), dim3(kThreads), 0, st, sp2);
+      const size_t csm = combine_slab_smem(p.m);
+      if (int rc = set_smem(combine_slab_kernel, csm, max_smem, "combine")) return rc;
+      launch_pdl(combine_slab_kernel, dim3((unsigned)p.BH, (unsigned)(p.D / 16)), dim3(kThreads), csm, st, sp2);
     } else {
       cp.k2inv = a.k2_inv; cp.k_landmarks = a.k_landmarks; cp.bmat = a.bmat; cp.lse3 = a.lse3;
       cp.step2 = a.step2; cp.m = p.m; cp.D = p.D;
@@ -1212,6 +1214,10 @@ __attribute__((visibility("default"))) int fnb_debug_tc_trace(long long* out, in
   if (cta >= 0) { cudaMemcpyToSymbol(tc::g_tc_trace_cta, &cta, sizeof(int)); return 0; }
   return cudaMemcpyFromSymbol(out, tc::g_tc_trace, sizeof(long long) * 8 * 256) == cudaSuccess ? 0 : -1;
 }
+__attribute__((visibility("default"))) int fnb_debug_gemm_cycles(unsigned long long* out, int reset) {
+  if (reset) { unsigned long long z[8] = {}; return cudaMemcpyToSymbol(g_gemm_cycles, z, sizeof(z)) == cudaSuccess ? 0 : -1; }
+  return cudaMemcpyFromSymbol(out, g_gemm_cycles, sizeof(unsigned long long) * 8) == cudaSuccess ? 0 : -1;
+}
 __attribute__((visibility("default"))) int fnb_debug_tc_span(unsigned long long* out) {
   return cudaMemcpyFromSymbol(out, tc::g_tc_span, sizeof(unsigned long long) * 3 * 1024) == cudaSuccess ? 0 : -1;
 }
@@ -1268,7 +1274,7 @@ int fnb_kernel_report(int device, fnb_kernel_info* out, int cap) {
       {"tc_pool<half,64>", (const void*)tc::tc_pool_kernel<H, 64>, tc::kPoolThreads, tc::PoolSmem<64>::kBytes},
       {"ns_fwd_tc", (const void*)nstc::ns_fwd_tc_kernel, nstc::kNsTcThreads, nstc::kFwdSmem},
       {"tc_fwd_b<half,64,64>", (const void*)tc::tc_fwd_b_kernel<H, 64, 64>, tc::kTcThreads, tc::FwdBSmem<64, 64>::kBytes},
-      {"combine_slab", (const void*)combine_slab_kernel, kThreads, 0},
+      {"combine_slab", (const void*)combine_slab_kernel, kThreads, combine_slab_smem(64)},
       {"tc_fwd_c<half,64,64>", (const void*)tc::tc_fwd_c_kernel<H, 64, 64>, tc::kTcThreads, tc::FwdCSmem<64, 64>::kBytes},
       {"tc_bwd_a<half,64,64>", (const void*)tc::tc_bwd_a_kernel<H, 64, 64>, tc::kTcThreads, tc::BwdASmem<64, 64>::kBytes},
       {"reduce_chunks", (const void*)reduce_chunks_kernel, kThreads, 0},

@@ -33,6 +33,15 @@ constexpr int kTcGemmTerm = 128 * 256;            // one bf16 term of a 128 x 12
 constexpr int kTcGemmSet = 3 * kTcGemmTerm;       // the three terms
 constexpr size_t kTcGemmSmem = 2 * (size_t)kTcGemmSet + 1024;
 
+#ifdef FNB_TC_TRACE
+__device__ unsigned long long g_gemm_cycles[8];
+#define GEMM_T(i) do { if (blockIdx.x == 0 && threadIdx.x == 0) { long long now_ = clock64(); atomicAdd(&g_gemm_cycles[i], (unsigned long long)(now_ - t_)); t_ = now_; } } while (0)
+#define GEMM_T0() long long t_ = clock64()
+#else
+#define GEMM_T(i) do {} while (0)
+#define GEMM_T0() do {} while (0)
+#endif
+
 struct GemmWs {
   float* sm;            // staging / reduction scratch of the CUDA-core code (kGemmSmemFloats floats)
   uint8_t* tiles;       // null: CUDA-core products
@@ -101,83 +110,110 @@ __device__ __forceinline__ uint64_t tc_gemm_desc(uint32_t tile, bool along_rows,
 
 template <bool TA, bool TB>
 __device__ inline void cta_gemm_tc(float* C, int ldc, const float* A, int lda, const float* B, int ldb, int M, int N,
-                                   int K, float alpha, float beta, float diag, GemmWs& ws) {
+                                   int K, float alpha, float beta, float diag, GemmWs& ws, float* C2, float alpha2,
+                                   float diag2) {
   uint8_t* setA = ws.tiles;
   uint8_t* setB = ws.tiles + kTcGemmSet;
+  GEMM_T0();
   // operands exactly as stored: A is (M x K) or, transposed, (K x M); B is (K x N) or (N x K)
   tc_gemm_load(setA, A, lda, TA ? K : M, TA ? M : K);
   tc_gemm_load(setB, B, ldb, TB ? N : K, TB ? K : N);
   tc::fence_proxy_async();
   __syncthreads();
+  GEMM_T(0);
   if (threadIdx.x == 0) {
     tc::tc_fence_after();
-    // A operand: K-major unless stored transposed; B operand: MN-major unless stored transposed
+    // A operand: K-major unless stored transposed; B operand: MN-major unless stored transposed.
+    // The descriptor of (term, k-step) is the descriptor of (0, 0) plus a compile-time offset in its
+    // 16-byte address field (all tiles lie inside one 256 KB window).
+    constexpr bool AR = TA, BR = !TB;    // contraction index along the tile's rows?
     const uint32_t idesc = tc::make_idesc<__nv_bfloat16>(128, 128, TA, !TB);
-    const uint32_t a0 = tc::smem_u32(setA), b0 = tc::smem_u32(setB);
+    const uint64_t da = tc_gemm_desc(tc::smem_u32(setA), AR, 0), db = tc_gemm_desc(tc::smem_u32(setB), BR, 0);
     const int ksteps = (K + 15) >> 4;
-    const int order[6][2] = {{1, 1}, {0, 2}, {2, 0}, {0, 1}, {1, 0}, {0, 0}};   // small terms first
     uint32_t acc = 0;
+#pragma unroll
     for (int t = 0; t < 6; ++t) {
-      const uint32_t ta = a0 + order[t][0] * kTcGemmTerm, tb = b0 + order[t][1] * kTcGemmTerm;
-      for (int k = 0; k < ksteps; ++k) {
-        tc::umma(ws.tmem, tc_gemm_desc(ta, TA, k), tc_gemm_desc(tb, !TB, k), idesc, acc);
-        acc = 1;
+      // partial products x_i y_j, small terms first: (1,1) (0,2) (2,0) (0,1) (1,0) (0,0)
+      constexpr int oi[6] = {1, 0, 2, 0, 1, 0}, oj[6] = {1, 2, 0, 1, 0, 0};
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        if (k < ksteps) {
+          const uint32_t offa = oi[t] * kTcGemmTerm + (AR ? k * 2048 : (k >> 2) * (128 * 128) + (k & 3) * 32);
+          const uint32_t offb = oj[t] * kTcGemmTerm + (BR ? k * 2048 : (k >> 2) * (128 * 128) + (k & 3) * 32);
+          tc::umma(ws.tmem, da + (offa >> 4), db + (offb >> 4), idesc, acc);
+          acc = 1;
+        }
       }
     }
     tc::umma_commit(ws.bar);
   }
+  GEMM_T(1);
   {
     tc::Abort ab{reinterpret_cast<volatile int*>(ws.bar + 1), ws.status};
     tc::mbar_wait(ws.bar, ws.phase, ab, 0x5000);
     ws.phase ^= 1u;
   }
   tc::tc_fence_after();
-  // epilogue: warp w reads TMEM lanes 32 (w & 3) .. + 31 (= rows), columns 64 (w >> 2) .. + 63
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int r = (warp & 3) * 32 + lane, cbase = (warp >> 2) * 64;
-  const uint32_t taddr = ws.tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)cbase;
+  GEMM_T(2);
+  // epilogue, step 1: accumulator rows -> FP32 staging in shared memory (the operand tiles are dead).
+  // Warp w reads TMEM lanes 32 (w & 3) .. + 31 (= rows), columns 64 (w >> 2) .. + 63.
+  constexpr int kLdS = 132;
+  float* stage = reinterpret_cast<float*>(ws.tiles);
+  {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int r = (warp & 3) * 32 + lane, cbase = (warp >> 2) * 64;
+    const uint32_t taddr = ws.tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)cbase;
 #pragma unroll
-  for (int half = 0; half < 2; ++half) {
-    float v[32];
-    tc::tmem_ld32(taddr + half * 32, v);
-    tc::tmem_ld_wait();
-    if (r < M) {
-      const int c0 = cbase + half * 32;
-      float* crow = C + (size_t)r * ldc;
-      if ((ldc & 3) == 0 && (N & 3) == 0 && (reinterpret_cast<uintptr_t>(C) & 15u) == 0) {
-        // 16-byte accesses; the old values of C (beta != 0) are fetched in one batch first
-        float4 old[8];
-        if (beta != 0.f) {
+    for (int half = 0; half < 2; ++half) {
+      float v[32];
+      tc::tmem_ld32(taddr + half * 32, v);
+      tc::tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 8; ++j)
-            old[j] = (c0 + 4 * j < N) ? *reinterpret_cast<const float4*>(crow + c0 + 4 * j) : make_float4(0.f, 0.f, 0.f, 0.f);
-        }
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const int c = c0 + 4 * j;
-          if (c < N) {
-            float4 o = make_float4(alpha * v[4 * j], alpha * v[4 * j + 1], alpha * v[4 * j + 2], alpha * v[4 * j + 3]);
-            if (beta != 0.f) { o.x += beta * old[j].x; o.y += beta * old[j].y; o.z += beta * old[j].z; o.w += beta * old[j].w; }
-            if (r >= c && r < c + 4) (&o.x)[r - c] += diag;
-            *reinterpret_cast<float4*>(crow + c) = o;
-          }
-        }
-      } else {
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const int c = c0 + j;
-          if (c < N) {
-            float val = alpha * v[j];
-            if (beta != 0.f) val += beta * crow[c];
-            if (r == c) val += diag;
-            crow[c] = val;
-          }
-        }
-      }
+      for (int j = 0; j < 32; j += 4)
+        *reinterpret_cast<float4*>(stage + r * kLdS + cbase + half * 32 + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
     }
   }
   tc::tc_fence_before();
   __syncthreads();
+  // step 2: coalesced rows to global memory with alpha, beta C and the diagonal
+  if ((ldc & 3) == 0 && (N & 3) == 0 && (reinterpret_cast<uintptr_t>(C) & 15u) == 0 &&
+      (!C2 || (reinterpret_cast<uintptr_t>(C2) & 15u) == 0)) {
+    const int n4 = N >> 2;
+#pragma unroll 4
+    for (int f = threadIdx.x; f < M * n4; f += kThreads) {
+      const int r = f / n4, c = (f - r * n4) * 4;
+      const float4 x = *reinterpret_cast<const float4*>(stage + r * kLdS + c);
+      float4 o = make_float4(alpha * x.x, alpha * x.y, alpha * x.z, alpha * x.w);
+      float* dst = C + (size_t)r * ldc + c;
+      if (beta != 0.f) {
+        const float4 old = *reinterpret_cast<const float4*>(dst);
+        o.x += beta * old.x; o.y += beta * old.y; o.z += beta * old.z; o.w += beta * old.w;
+      }
+      const int dg = r - c;   // position of the diagonal element inside this group of four, if any
+      if (dg == 0) o.x += diag; else if (dg == 1) o.y += diag; else if (dg == 2) o.z += diag; else if (dg == 3) o.w += diag;
+      *reinterpret_cast<float4*>(dst) = o;
+      if (C2) {
+        float4 o2 = make_float4(alpha2 * x.x, alpha2 * x.y, alpha2 * x.z, alpha2 * x.w);
+        if (dg == 0) o2.x += diag2; else if (dg == 1) o2.y += diag2; else if (dg == 2) o2.z += diag2; else if (dg == 3) o2.w += diag2;
+        *reinterpret_cast<float4*>(C2 + (size_t)r * ldc + c) = o2;
+      }
+    }
+  } else {
+    for (int idx = threadIdx.x; idx < M * N; idx += kThreads) {
+      const int r = idx / N, c = idx - r * N;
+      const float x = stage[r * kLdS + c];
+      float val = alpha * x;
+      if (beta != 0.f) val += beta * C[(size_t)r * ldc + c];
+      if (r == c) val += diag;
+      C[(size_t)r * ldc + c] = val;
+      if (C2) C2[(size_t)r * ldc + c] = alpha2 * x + (r == c ? diag2 : 0.f);
+    }
+  }
+  __syncthreads();
+  GEMM_T(3);
+#ifdef FNB_TC_TRACE
+  if (blockIdx.x == 0 && threadIdx.x == 0) atomicAdd(&g_gemm_cycles[4], 1ull);
+#endif
 }
 
 // set-up / teardown of the tensor-core products inside a 256-thread kernel (all threads call)
@@ -217,11 +253,14 @@ constexpr int kGemmSmemFloats = 2 * kGemmKT * kGemmLd;
 // C may alias A or B.  All 256 threads must call; ends with a barrier.
 // Pointers are deliberately not __restrict__: operands are produced by this same CTA and must
 // be read through the coherent path.
+// Optional second output C2 = alpha2 * op(A) * op(B) + diag2 * I (same leading dimension as C, must
+// not alias an operand).
 template <bool TA, bool TB>
 __device__ __noinline__ void cta_gemm(float* C, int ldc, const float* A, int lda, const float* B, int ldb,
-                         int M, int N, int K, float alpha, float beta, float diag, GemmWs& ws) {
+                         int M, int N, int K, float alpha, float beta, float diag, GemmWs& ws,
+                         float* C2 = nullptr, float alpha2 = 0.f, float diag2 = 0.f) {
   if (ws.tiles) {
-    cta_gemm_tc<TA, TB>(C, ldc, A, lda, B, ldb, M, N, K, alpha, beta, diag, ws);
+    cta_gemm_tc<TA, TB>(C, ldc, A, lda, B, ldb, M, N, K, alpha, beta, diag, ws, C2, alpha2, diag2);
     return;
   }
   float* sm = ws.sm;
@@ -282,6 +321,7 @@ __device__ __noinline__ void cta_gemm(float* C, int ldc, const float* A, int lda
         if (beta != 0.f) val += beta * C[(size_t)r * ldc + c];
         if (r == c) val += diag;
         C[(size_t)r * ldc + c] = val;
+        if (C2) C2[(size_t)r * ldc + c] = alpha2 * acc[i][j] + (r == c ? diag2 : 0.f);
       }
     }
   }
@@ -293,28 +333,58 @@ __device__ __noinline__ void cta_gemm(float* C, int ldc, const float* A, int lda
 // Results are broadcast through red[0..3] and returned in registers by every thread.
 struct Norms { float n1, ninf; int jc, ir; };
 __device__ inline Norms cta_norms(const float* A, int m, float* red) {
-  const int t = threadIdx.x;
-  if (t < m) {
-    float cs = 0.f;
-    for (int i = 0; i < m; ++i) cs += fabsf(A[i * m + t]);
-    red[t] = cs;
-  } else if (t >= 128 && t - 128 < m) {
-    int i = t - 128;
+  // one pass over A: warp w takes rows w, w + 8, ...; a lane reads columns lane, lane + 32, ... of a
+  // row (coalesced), keeps its column partial sums in registers and folds the row sum with shuffles
+  const int t = threadIdx.x, w = t >> 5, lane = t & 31;
+  float* rowsum = red;                       // [kMaxM]
+  float* colpart = red + kMaxM;              // [8][kMaxM]
+  float cs[kMaxM / 32];
+#pragma unroll
+  for (int q = 0; q < kMaxM / 32; ++q) cs[q] = 0.f;
+  for (int r = w; r < m; r += kThreads / 32) {
+    float x[kMaxM / 32];
+#pragma unroll
+    for (int q = 0; q < kMaxM / 32; ++q) {
+      const int c = lane + 32 * q;
+      x[q] = c < m ? fabsf(A[(size_t)r * m + c]) : 0.f;
+    }
     float rs = 0.f;
-    for (int j = 0; j < m; ++j) rs += fabsf(A[i * m + j]);
-    red[kMaxM + i] = rs;
+#pragma unroll
+    for (int q = 0; q < kMaxM / 32; ++q) { cs[q] += x[q]; rs += x[q]; }
+    for (int o = 16; o > 0; o >>= 1) rs += __shfl_xor_sync(0xffffffffu, rs, o);
+    if (lane == 0) rowsum[r] = rs;
   }
+#pragma unroll
+  for (int q = 0; q < kMaxM / 32; ++q) colpart[w * kMaxM + lane + 32 * q] = cs[q];
   __syncthreads();
   __shared__ float out_n1, out_ninf;
   __shared__ int out_jc, out_ir;
-  if (t == 0) {
-    float best = red[0]; int bi = 0;
-    for (int j = 1; j < m; ++j) if (red[j] > best) { best = red[j]; bi = j; }
-    out_n1 = best; out_jc = bi;
-  } else if (t == 32) {
-    float best = red[kMaxM]; int bi = 0;
-    for (int i = 1; i < m; ++i) if (red[kMaxM + i] > best) { best = red[kMaxM + i]; bi = i; }
-    out_ninf = best; out_ir = bi;
+  if (w == 0) {
+    // column sums: fold the eight warps, then the first-occurrence argmax over columns
+    float best = -1.f; int bi = 0;
+    for (int c = lane; c < m; c += 32) {
+      float s = 0.f;
+      for (int ww = 0; ww < kThreads / 32; ++ww) s += colpart[ww * kMaxM + c];
+      if (s > best) { best = s; bi = c; }
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+    }
+    if (lane == 0) { out_n1 = best; out_jc = bi; }
+  } else if (w == 1) {
+    float best = -1.f; int bi = 0;
+    for (int r = lane; r < m; r += 32) {
+      const float s = rowsum[r];
+      if (s > best) { best = s; bi = r; }
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+    }
+    if (lane == 0) { out_ninf = best; out_ir = bi; }
   }
   __syncthreads();
   Norms r{out_n1, out_ninf, out_jc, out_ir};
@@ -360,8 +430,7 @@ __device__ inline void pinv_forward(const float* k2, float* iterates, float* k2i
   for (int j = 0; j < J; ++j) {
     const float* Z = iterates + (size_t)j * mm;
     float* Zn = iterates + (size_t)(j + 1) * mm;
-    cta_gemm<false, false>(Mb, m, A, m, Z, m, m, m, m, 1.f, 0.f, 0.f, ws);        // M = A Z
-    cta_affine(Ub, Mb, -1.f, 7.f, m);                                             // U = 7I - M
+    cta_gemm<false, false>(Mb, m, A, m, Z, m, m, m, m, 1.f, 0.f, 0.f, ws, Ub, -1.f, 7.f);   // M = A Z, U = 7I - M
     cta_gemm<false, false>(Vb, m, Mb, m, Ub, m, m, m, m, -1.f, 0.f, 15.f, ws);    // V = 15I - M U
     cta_gemm<false, false>(Ub, m, Mb, m, Vb, m, m, m, m, -1.f, 0.f, 13.f, ws);    // T = 13I - M V
     cta_gemm<false, false>(Zn, m, Z, m, Ub, m, m, m, m, 0.25f, 0.f, 0.f, ws);     // Z' = Z T / 4
@@ -408,13 +477,15 @@ __device__ inline void pinv_backward(const float* k2, const float* iterates, con
   } else {
     for (int idx = threadIdx.x; idx < mm; idx += kThreads) dZ[idx] = G[idx];
   }
-  for (int idx = threadIdx.x; idx < mm; idx += kThreads) dA[idx] = 0.f;
   __syncthreads();
+  if (J == 0) {
+    for (int idx = threadIdx.x; idx < mm; idx += kThreads) dA[idx] = 0.f;
+    __syncthreads();
+  }
 
   for (int j = J - 1; j >= 0; --j) {
     const float* Z = iterates + (size_t)j * mm;
-    cta_gemm<false, false>(Mb, m, A, m, Z, m, m, m, m, 1.f, 0.f, 0.f, ws);
-    cta_affine(Ub, Mb, -1.f, 7.f, m);
+    cta_gemm<false, false>(Mb, m, A, m, Z, m, m, m, m, 1.f, 0.f, 0.f, ws, Ub, -1.f, 7.f);   // M and U = 7I - M
     cta_gemm<false, false>(Vb, m, Mb, m, Ub, m, m, m, m, -1.f, 0.f, 15.f, ws);
     cta_gemm<false, false>(Tb, m, Mb, m, Vb, m, m, m, m, -1.f, 0.f, 13.f, ws);
     cta_gemm<true, false>(dT, m, Z, m, dZ, m, m, m, m, 0.25f, 0.f, 0.f, ws);    // dT = Z^T dZ / 4
@@ -423,10 +494,9 @@ __device__ inline void pinv_backward(const float* k2, const float* iterates, con
     cta_gemm<true, false>(dV, m, Mb, m, dT, m, m, m, m, -1.f, 0.f, 0.f, ws);    // dV = -M^T dT
     cta_gemm<false, true>(dM, m, dV, m, Ub, m, m, m, m, -1.f, 1.f, 0.f, ws);    // -= dV U^T
     cta_gemm<true, false>(dM, m, Mb, m, dV, m, m, m, m, 1.f, 1.f, 0.f, ws);     // += M^T dV
-    cta_gemm<false, true>(dA, m, dM, m, Z, m, m, m, m, 1.f, 1.f, 0.f, ws);      // dA += dM Z^T
-    cta_gemm<true, false>(dZ, m, A, m, dM, m, m, m, m, 1.f, 0.f, 0.f, ws);      // A^T dM
-    for (int idx = threadIdx.x; idx < mm; idx += kThreads) dZ[idx] += dZo[idx];
-    __syncthreads();
+    cta_gemm<false, true>(dA, m, dM, m, Z, m, m, m, m, 1.f, j == J - 1 ? 0.f : 1.f, 0.f, ws);   // dA += dM Z^T
+    cta_gemm<true, false>(dZo, m, A, m, dM, m, m, m, m, 1.f, 1.f, 0.f, ws);     // dZ' = dZ T^T / 4 + A^T dM
+    { float* tmp = dZ; dZ = dZo; dZo = tmp; }
   }
   // Z0 = A^T / c with c = ||A||_1 ||A||_inf
   Norms na = cta_norms(A, m, red);

@@ -366,62 +366,68 @@ struct CombineSlabParams {
 
 constexpr int kSlabMaxChunks = 20;   // chunks merged with every load in flight; more run in rounds
 
+// Dynamic shared memory: K2inv with padded rows, m (m + 1) floats (combine_slab_smem).
+__host__ __device__ inline size_t combine_slab_smem(int m) { return sizeof(float) * (size_t)m * (m + 1); }
+
 __global__ void __launch_bounds__(kThreads) combine_slab_kernel(CombineSlabParams p) {
-  __shared__ float sK[64 * 64];
-  __shared__ __align__(16) float sB[64 * 16];
+  extern __shared__ float sK[];                        // [m][m + 1]
+  __shared__ __align__(16) float sB[kMaxM * 16];
   pdl_trigger();
   pdl_wait();
   const int64_t bh = blockIdx.x;
-  const int slab = blockIdx.y, t = threadIdx.x, l = t >> 2, q = t & 3;
-  const int m = p.m, D = p.D, nc = p.nchunk, d0 = 16 * slab + 4 * q;
+  const int slab = blockIdx.y, t = threadIdx.x, q = t & 3;
+  const int m = p.m, D = p.D, nc = p.nchunk, d0 = 16 * slab + 4 * q, ms = m + 1;
   const float* k2inv = p.k2inv + bh * m * m;
-  for (int idx = t; idx < m * m; idx += kThreads) sK[idx] = k2inv[idx];
-  float4 b = make_float4(0.f, 0.f, 0.f, 0.f);
-  if (l < m) {
-    const float* pacc = p.part_acc + bh * p.acc_bh_stride + (size_t)l * D + d0;
-    const float* pmax = p.part_max + bh * p.vec_bh_stride + l;
-    const float* psum = p.part_sum + bh * p.vec_bh_stride + l;
-    // with at most kSlabMaxChunks chunks (the usual case) the maxima come out of the one batch of
-    // loads below; otherwise a first sweep finds them
-    float M = -INFINITY;
-    if (nc > kSlabMaxChunks)
-      for (int c = 0; c < nc; ++c) M = fmaxf(M, pmax[c * p.vec_chunk_stride]);
-    float Lsum = 0.f;
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int c0 = 0; c0 < nc; c0 += kSlabMaxChunks) {
-      float4 x[kSlabMaxChunks];
-      float wgt[kSlabMaxChunks], ps[kSlabMaxChunks];
+  for (int idx = t; idx < m * m; idx += kThreads) sK[(idx / m) * ms + idx % m] = k2inv[idx];
+  // thread t merges landmark rows t >> 2 and, with more than 64 landmarks, (t >> 2) + 64
+  for (int l = t >> 2; l < kMaxM; l += 64) {
+    float4 b = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (l < m) {
+      const float* pacc = p.part_acc + bh * p.acc_bh_stride + (size_t)l * D + d0;
+      const float* pmax = p.part_max + bh * p.vec_bh_stride + l;
+      const float* psum = p.part_sum + bh * p.vec_bh_stride + l;
+      // with at most kSlabMaxChunks chunks (the usual case) the maxima come out of the one batch of
+      // loads below; otherwise a first sweep finds them
+      float M = -INFINITY;
+      if (nc > kSlabMaxChunks)
+        for (int c = 0; c < nc; ++c) M = fmaxf(M, pmax[c * p.vec_chunk_stride]);
+      float Lsum = 0.f;
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int c0 = 0; c0 < nc; c0 += kSlabMaxChunks) {
+        float4 x[kSlabMaxChunks];
+        float wgt[kSlabMaxChunks], ps[kSlabMaxChunks];
 #pragma unroll
-      for (int i = 0; i < kSlabMaxChunks; ++i) {
-        const int c = min(c0 + i, nc - 1);
-        x[i] = *reinterpret_cast<const float4*>(pacc + (size_t)c * p.acc_chunk_stride);
-        wgt[i] = pmax[c * p.vec_chunk_stride];
-        ps[i] = psum[c * p.vec_chunk_stride];
-      }
-      if (nc <= kSlabMaxChunks) {
+        for (int i = 0; i < kSlabMaxChunks; ++i) {
+          const int c = min(c0 + i, nc - 1);
+          x[i] = *reinterpret_cast<const float4*>(pacc + (size_t)c * p.acc_chunk_stride);
+          wgt[i] = pmax[c * p.vec_chunk_stride];
+          ps[i] = psum[c * p.vec_chunk_stride];
+        }
+        if (nc <= kSlabMaxChunks) {
 #pragma unroll
-        for (int i = 0; i < kSlabMaxChunks; ++i) M = fmaxf(M, wgt[i]);   // entries past nc repeat the last chunk
-      }
+          for (int i = 0; i < kSlabMaxChunks; ++i) M = fmaxf(M, wgt[i]);   // entries past nc repeat the last chunk
+        }
 #pragma unroll
-      for (int i = 0; i < kSlabMaxChunks; ++i) {
-        const float w = (c0 + i < nc) ? expf(wgt[i] - M) : 0.f;
-        Lsum = fmaf(w, ps[i], Lsum);
-        acc.x = fmaf(w, x[i].x, acc.x); acc.y = fmaf(w, x[i].y, acc.y);
-        acc.z = fmaf(w, x[i].z, acc.z); acc.w = fmaf(w, x[i].w, acc.w);
+        for (int i = 0; i < kSlabMaxChunks; ++i) {
+          const float w = (c0 + i < nc) ? expf(wgt[i] - M) : 0.f;
+          Lsum = fmaf(w, ps[i], Lsum);
+          acc.x = fmaf(w, x[i].x, acc.x); acc.y = fmaf(w, x[i].y, acc.y);
+          acc.z = fmaf(w, x[i].z, acc.z); acc.w = fmaf(w, x[i].w, acc.w);
+        }
       }
+      const float inv = 1.f / Lsum;
+      b = make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
+      *reinterpret_cast<float4*>(p.bmat + (bh * m + l) * D + d0) = b;
+      if (slab == 0 && q == 0) p.lse3[bh * m + l] = M + logf(Lsum);
     }
-    const float inv = 1.f / Lsum;
-    b = make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
-    *reinterpret_cast<float4*>(p.bmat + (bh * m + l) * D + d0) = b;
-    if (slab == 0 && q == 0) p.lse3[bh * m + l] = M + logf(Lsum);
+    *reinterpret_cast<float4*>(sB + l * 16 + 4 * q) = b;
   }
-  *reinterpret_cast<float4*>(sB + l * 16 + 4 * q) = b;
   __syncthreads();
-  if (l < m) {
+  for (int l = t >> 2; l < m; l += 64) {
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll 8
     for (int k = 0; k < m; ++k) {
-      const float a = sK[l * m + k];
+      const float a = sK[l * ms + k];
       const float4 x = *reinterpret_cast<const float4*>(sB + k * 16 + 4 * q);
       acc.x = fmaf(a, x.x, acc.x); acc.y = fmaf(a, x.y, acc.y); acc.z = fmaf(a, x.z, acc.z); acc.w = fmaf(a, x.w, acc.w);
     }
