@@ -48,21 +48,61 @@ def set_wait_limit_ms(ms: int, device=0):
     _lib.check(_lib.load().fnb_debug_set_wait_limit_ms(int(device), int(ms)))
 
 
-def _shape_struct(B, H, N, D, m, J, dtype, kappa_star):
+def layout_of(t):
+    """FNB_LAYOUT_BHND for a contiguous (B, H, N, D) tensor, FNB_LAYOUT_BNHD for the head-split view
+    of a contiguous (B, N, H * D) tensor (t.transpose(1, 2) is contiguous), None for anything else."""
+    if t.dim() != 4:
+        return None
+    if t.is_contiguous():
+        return _lib.FNB_LAYOUT_BHND
+    if t.transpose(1, 2).is_contiguous():
+        return _lib.FNB_LAYOUT_BNHD
+    return None
+
+
+def tc_eligible(dtype, D, m):
+    """Shapes the tensor-core kernels cover (the only ones that take the (B, N, H, D) layout)."""
+    if _flags & _lib.FNB_FLAG_FORCE_GENERIC or dtype not in (torch.float16, torch.bfloat16):
+        return False
+    return (D == 64 and m <= 64) or (D == 128 and m <= 128)
+
+
+def _empty_like_layout(t, layout):
+    """Uninitialised tensor of t's logical shape (B, H, N, D) in the given memory layout."""
+    if layout == _lib.FNB_LAYOUT_BNHD:
+        B, H, N, D = t.shape
+        return torch.empty(B, N, H, D, dtype=t.dtype, device=t.device).transpose(1, 2)
+    return torch.empty(t.shape, dtype=t.dtype, device=t.device)
+
+
+def _to_layout(t, layout):
+    """t in the given layout (a copy only if it is not already)."""
+    if layout_of(t) == layout:
+        return t
+    if layout == _lib.FNB_LAYOUT_BNHD:
+        return t.transpose(1, 2).contiguous().transpose(1, 2)
+    return t.contiguous()
+
+
+def _shape_struct(B, H, N, D, m, J, dtype, kappa_star, layout=0):
     if dtype not in _DTYPES:
         raise RuntimeError("Supported dtypes: float32, float16, bfloat16")
     if not (isinstance(kappa_star, (int, float)) and math.isfinite(kappa_star) and kappa_star >= 0):
         raise RuntimeError(f"kappa_star must be finite and >= 0 (got {kappa_star}); "
                            "0 disables the Tikhonov ridge")
     return _lib.Shape(int(B), int(H), int(N), int(D), int(m), int(J), _DTYPES[dtype],
-                      float(kappa_star), _flags)
+                      float(kappa_star), _flags, int(layout), 0)
 
 
-def _check_big(t, name, shape=None, dtype=None):
+def _check_big(t, name, shape=None, dtype=None, layout=None):
     if not isinstance(t, torch.Tensor) or not t.is_cuda:
         raise RuntimeError(f"{name} must be a CUDA tensor (flashnystrom_b200 has no CPU path)")
-    if not t.is_contiguous():
-        raise RuntimeError(f"{name} must be contiguous")
+    if layout is None:
+        if not t.is_contiguous():
+            raise RuntimeError(f"{name} must be contiguous")
+    elif layout_of(t) != layout:
+        raise RuntimeError(f"{name} must be contiguous (or, with q, k, v all laid out that way, the head-split "
+                           f"view of a contiguous (B, N, H*D) tensor)")
     if shape is not None and tuple(t.shape) != tuple(shape):
         raise RuntimeError(f"{name} shape mismatch: expected {tuple(shape)}, got {tuple(t.shape)}")
     if dtype is not None and t.dtype != dtype:
@@ -109,22 +149,25 @@ def _workspace(nbytes, device):
 def forward(q, k, v, num_landmarks=64, newton_iter=6, kappa_star=0.0, use_tc_pinv=False,
             need_scaled_qk=True):
     lib = _lib.load()
-    for t, name in ((q, "q"), (k, "k"), (v, "v")):
-        _check_big(t, name)
-    if q.dim() != 4 or k.dim() != 4 or v.dim() != 4:
+    if not all(isinstance(t, torch.Tensor) for t in (q, k, v)) or q.dim() != 4 or k.dim() != 4 or v.dim() != 4:
         raise RuntimeError("q, k, v must be 4D (B, H, N, D)")
     if not (q.dtype == k.dtype == v.dtype):
         raise RuntimeError("q, k, v dtypes must match")
     B, H, N, D = q.shape
-    _check_big(k, "k", (B, H, N, D))
-    _check_big(v, "v", (B, H, N, D))
     m, J = int(num_landmarks), int(newton_iter)
-    shp = _shape_struct(B, H, N, D, m, J, q.dtype, kappa_star)
+    # the head-split view of (B, N, H*D) projection outputs is taken as it is where the tensor-core
+    # kernels run; everything else must be contiguous, as in the reference
+    lay = layout_of(q)
+    if lay != _lib.FNB_LAYOUT_BNHD or not tc_eligible(q.dtype, D, m) or layout_of(k) != lay or layout_of(v) != lay:
+        lay = _lib.FNB_LAYOUT_BHND
+    for t, name in ((q, "q"), (k, "k"), (v, "v")):
+        _check_big(t, name, (B, H, N, D), layout=lay)
+    shp = _shape_struct(B, H, N, D, m, J, q.dtype, kappa_star, lay)
     _lib.check(lib.fnb_check_shape(C.byref(shp)))
     dev = q.device
     f32 = dict(dtype=torch.float32, device=dev)
     with torch.cuda.device(dev):
-        out = torch.empty_like(q)
+        out = _empty_like_layout(q, lay)
         lse1 = torch.empty(B, H, N, **f32)
         qt = torch.empty(B, H, m, D, **f32)
         kt = torch.empty(B, H, m, D, **f32)
@@ -148,18 +191,24 @@ def backward(dO, q_s, k_s, q_tilde, k_tilde, kernel2_inv, step2, lse1, lse2, lse
              k2_softmax, b_saved, v, output, num_landmarks, newton_iter, fast_dk2inv=True,
              kappa_star=0.0):
     lib = _lib.load()
-    _check_big(dO, "dO")
-    if dO.dim() != 4:
-        raise RuntimeError(f"dO must be 4D (B, H, N, D), got {dO.dim()}D")
+    if not isinstance(dO, torch.Tensor) or dO.dim() != 4:
+        raise RuntimeError(f"dO must be 4D (B, H, N, D), got {getattr(dO, 'dim', lambda: '?')()}D")
     B, H, N, D = dO.shape
     m, J = int(num_landmarks), int(newton_iter)
     dt = dO.dtype
-    shp = _shape_struct(B, H, N, D, m, J, dt, kappa_star)
+    # q decides the layout of all eight (B, H, N, D) tensors; dO is brought to it if it differs
+    lay = layout_of(q_s) if isinstance(q_s, torch.Tensor) else None
+    if lay != _lib.FNB_LAYOUT_BNHD or not tc_eligible(dt, D, m):
+        lay = _lib.FNB_LAYOUT_BHND
+    if isinstance(dO, torch.Tensor) and dO.is_cuda:
+        dO = _to_layout(dO, lay)
+    _check_big(dO, "dO", layout=lay)
+    shp = _shape_struct(B, H, N, D, m, J, dt, kappa_star, lay)
     _lib.check(lib.fnb_check_shape(C.byref(shp)))
     f32 = torch.float32
-    _check_big(q_s, "q_s", (B, H, N, D), dt)
-    _check_big(k_s, "k_s", (B, H, N, D), dt)
-    _check_big(v, "v", (B, H, N, D), dt)
+    _check_big(q_s, "q_s", (B, H, N, D), dt, layout=lay)
+    _check_big(k_s, "k_s", (B, H, N, D), dt, layout=lay)
+    _check_big(v, "v", (B, H, N, D), dt, layout=lay)
     _check_big(q_tilde, "q_tilde", (B, H, m, D), f32)
     _check_big(k_tilde, "k_tilde", (B, H, m, D), f32)
     _check_big(step2, "step2", (B, H, m, D), f32)
@@ -171,7 +220,7 @@ def backward(dO, q_s, k_s, q_tilde, k_tilde, kernel2_inv, step2, lse1, lse2, lse
     _check_big(ns_iterates, "ns_iterates", (B, H, J + 1, m, m), f32)
     dev = dO.device
     with torch.cuda.device(dev):
-        dq, dk, dv = torch.empty_like(dO), torch.empty_like(dO), torch.empty_like(dO)
+        dq, dk, dv = (_empty_like_layout(dO, lay) for _ in range(3))
         ws = _workspace(lib.fnb_bwd_workspace_bytes(C.byref(shp)), dev)
         args = _lib.BwdArgs(shp, _ptr(q_s), _ptr(k_s), _ptr(v), _ptr(dO), _ptr(lse1),
                             _ptr(q_tilde), _ptr(k_tilde), _ptr(k2_softmax), _ptr(ns_iterates),

@@ -13,13 +13,15 @@ LIB_PATH = os.path.join(_PKG, "lib", "libflashnystrom_b200.so")
 FNB_F32, FNB_F16, FNB_BF16 = 0, 1, 2
 FNB_FLAG_FORCE_GENERIC = 1
 FNB_FLAG_TEST_DROP_LOAD = 0x100
+FNB_LAYOUT_BHND, FNB_LAYOUT_BNHD = 0, 1
 
 
 class Shape(C.Structure):
     _fields_ = [("batch", C.c_int64), ("heads", C.c_int64), ("seq_len", C.c_int64),
                 ("head_dim", C.c_int32), ("num_landmarks", C.c_int32),
                 ("newton_iter", C.c_int32), ("dtype", C.c_int32),
-                ("kappa_star", C.c_float), ("flags", C.c_uint32)]
+                ("kappa_star", C.c_float), ("flags", C.c_uint32),
+                ("layout", C.c_int32), ("reserved", C.c_int32)]
 
 
 class FwdArgs(C.Structure):

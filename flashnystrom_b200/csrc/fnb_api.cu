@@ -209,6 +209,8 @@ static int check_shape(const fnb_shape* s) {
     return fail(FNB_ERR_INVALID_ARGUMENT,
                 "kappa_star must be finite and >= 0 (got %g); 0 disables the Tikhonov ridge",
                 (double)s->kappa_star);
+  if (s->layout != FNB_LAYOUT_BHND && s->layout != FNB_LAYOUT_BNHD)
+    return fail(FNB_ERR_INVALID_ARGUMENT, "layout must be FNB_LAYOUT_BHND (0) or FNB_LAYOUT_BNHD (1), got %d", s->layout);
   if (s->batch * s->heads > (int64_t)1 << 24)
     return fail(FNB_ERR_INVALID_ARGUMENT, "batch * heads (%lld) exceeds 2^24", (long long)(s->batch * s->heads));
   return 0;
@@ -369,10 +371,14 @@ static int forward_impl(const fnb_fwd_args& a, const Plan& p, const FwdWs& w, in
   constexpr bool k16 = !std::is_same<T, float>::value;
   tc::TcSched sch = tc::make_sched(p.BH, p.N, tc_ctas_per_sm(p.D) * sms);   // one wave
   const bool use_tc = k16 && tc::tc_supported(a.shape.dtype, p.D, p.m, a.shape.flags) && sch.nchunk <= p.nchunk;
+  const tc::BigLayout big{a.shape.batch, a.shape.heads, p.N, p.D, a.shape.layout};
+  if (a.shape.layout != FNB_LAYOUT_BHND && !use_tc)
+    return fail(FNB_ERR_INVALID_ARGUMENT, "the (B,N,H,D) layout needs the tensor-core path (16-bit dtype, head_dim 64 with "
+                "num_landmarks <= 64 or head_dim 128 with num_landmarks <= 128)");
   const int MP = p.m <= 64 ? 64 : 128;
   const bool smem_ns = p.m <= ns::kN;
   const int64_t seg_N = S.on() ? S.N_global : p.N, row_offset = S.on() ? (int64_t)S.rank * p.N : 0;
-  sch.seg_N = seg_N; sch.row_offset = row_offset;
+  sch.seg_N = seg_N; sch.row_offset = row_offset; sch.H = big.map_h();
   const int lmC = S.on() ? 1 : p.lm_chunks;
   float* land = S.on() ? S.xfer : w.land_partial;
   const int l2 = l2_mode();
@@ -395,8 +401,8 @@ static int forward_impl(const fnb_fwd_args& a, const Plan& p, const FwdWs& w, in
         int rc = dispatch_head_dim(p.D, [&](auto dtag) -> int {
           constexpr int D = decltype(dtag)::value;
           CUtensorMap tm_q, tm_k;
-          if (!tc::make_map_3d(&tm_q, a.q, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
-              !tc::make_map_3d(&tm_k, a.k, a.shape.dtype, p.BH, p.N, D, tc::kTile))
+          if (!tc::make_map_big(&tm_q, a.q, a.shape.dtype, big, tc::kTile) ||
+              !tc::make_map_big(&tm_k, a.k, a.shape.dtype, big, tc::kTile))
             return fail(FNB_ERR_CUDA, "cuTensorMapEncodeTiled failed for the pooling pass");
           L.begin();
           auto kern = tc::tc_pool_kernel<T, D>;
@@ -404,7 +410,7 @@ static int forward_impl(const fnb_fwd_args& a, const Plan& p, const FwdWs& w, in
           if (int rc2 = set_smem(kern, smem, max_smem, "tc_pool")) return rc2;
           const int64_t grid = std::min<int64_t>(2 * p.BH * p.m * lmC, (int64_t)sms * 2);
           launch_pdl(kern, dim3((unsigned)grid), dim3(tc::kPoolThreads), smem, st, tm_q, tm_k, land, p.BH, p.N, p.m, lmC,
-                     seg_N, row_offset, a.device_status);
+                     seg_N, row_offset, big.map_h(), a.device_status);
           return L.end("tc_pool");
         });
         if (rc) return rc;
@@ -415,7 +421,8 @@ static int forward_impl(const fnb_fwd_args& a, const Plan& p, const FwdWs& w, in
       L.begin();
       int64_t grid = std::min<int64_t>(2 * p.BH * p.m * lmC, (int64_t)sms * 4);
       launch_pdl(landmark_partial_kernel<T>, dim3((unsigned)grid), dim3(kThreads), 0, st,
-          (const T*)a.q, (const T*)a.k, land, p.BH, p.N, p.D, p.m, lmC, seg_N, row_offset);
+          (const T*)a.q, (const T*)a.k, land, p.BH, p.N, p.D, p.m, lmC, seg_N, row_offset, big.map_h(), big.row_stride(),
+          big.head_stride(), big.batch_stride());
       if (L.end("landmark_partial")) return L.status;
     }
   }
@@ -494,8 +501,8 @@ static int forward_impl(const fnb_fwd_args& a, const Plan& p, const FwdWs& w, in
       int rc = dispatch_tc(p.D, MP, [&](auto dtag, auto mtag) -> int {
         constexpr int D = decltype(dtag)::value, MPc = decltype(mtag)::value;
         CUtensorMap tm_k, tm_v, tm_qt;
-        if (!tc::make_map_3d(&tm_k, a.k, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
-            !tc::make_map_3d(&tm_v, a.v, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
+        if (!tc::make_map_big(&tm_k, a.k, a.shape.dtype, big, tc::kTile) ||
+            !tc::make_map_big(&tm_v, a.v, a.shape.dtype, big, tc::kTile) ||
             !tc::make_map_2d(&tm_qt, w.qt16, a.shape.dtype, p.BH * MPc, D, MPc))
           return fail(FNB_ERR_CUDA, "cuTensorMapEncodeTiled failed for the forward column pass");
         L.begin();
@@ -580,8 +587,8 @@ static int forward_impl(const fnb_fwd_args& a, const Plan& p, const FwdWs& w, in
       return dispatch_tc(p.D, MP, [&](auto dtag, auto mtag) -> int {
         constexpr int D = decltype(dtag)::value, MPc = decltype(mtag)::value;
         CUtensorMap tm_q, tm_o;
-        if (!tc::make_map_3d(&tm_q, a.q, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
-            !tc::make_map_3d(&tm_o, a.out, a.shape.dtype, p.BH, p.N, D, tc::kTile))
+        if (!tc::make_map_big(&tm_q, a.q, a.shape.dtype, big, tc::kTile) ||
+            !tc::make_map_big(&tm_o, a.out, a.shape.dtype, big, tc::kTile))
           return fail(FNB_ERR_CUDA, "cuTensorMapEncodeTiled failed for the forward output pass");
         L.begin();
         auto kern = tc::tc_fwd_c_kernel<T, D, MPc>;
@@ -614,8 +621,12 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
   constexpr bool k16 = !std::is_same<T, float>::value;
   tc::TcSched sch = tc::make_sched(p.BH, p.N, tc_ctas_per_sm(p.D) * sms);   // one wave
   const int64_t seg_N = S.on() ? S.N_global : p.N, row_offset = S.on() ? (int64_t)S.rank * p.N : 0;
-  sch.seg_N = seg_N; sch.row_offset = row_offset;
+  const tc::BigLayout big{a.shape.batch, a.shape.heads, p.N, p.D, a.shape.layout};
+  sch.seg_N = seg_N; sch.row_offset = row_offset; sch.H = big.map_h();
   const bool use_tc = k16 && tc::tc_supported(a.shape.dtype, p.D, p.m, a.shape.flags) && sch.nchunk <= p.nchunk;
+  if (a.shape.layout != FNB_LAYOUT_BHND && !use_tc)
+    return fail(FNB_ERR_INVALID_ARGUMENT, "the (B,N,H,D) layout needs the tensor-core path (16-bit dtype, head_dim 64 with "
+                "num_landmarks <= 64 or head_dim 128 with num_landmarks <= 128)");
   const int MP = p.m <= 64 ? 64 : 128;
   const bool smem_ns = p.m <= ns::kN;
   // With head_dim 64 on the tensor-core path the reduction of the pass-A partials and the two
@@ -629,7 +640,7 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
   tc::TcSched sch_b = sch;
   if (side_ns) {
     sch_b = tc::make_sched(p.BH, p.N, 2 * (sms - (int)p.BH));
-    sch_b.seg_N = seg_N; sch_b.row_offset = row_offset;
+    sch_b.seg_N = seg_N; sch_b.row_offset = row_offset; sch_b.H = big.map_h();
   }
   int kshift = 0;
   while ((int64_t(2) << kshift) <= seg_N && kshift < 14) ++kshift;   // floor(log2 N), at most 14
@@ -663,11 +674,10 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
   void* qt16 = w.op16[3]; void* do3n = w.op16[5];
   CUtensorMap tm_q, tm_g, tm_dq, tm_dk;
   if (use_tc) {
-    const int D = p.D;
-    if (!tc::make_map_3d(&tm_q, a.q, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
-        !tc::make_map_3d(&tm_g, a.d_out, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
-        !tc::make_map_3d(&tm_dq, a.dq, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
-        !tc::make_map_3d(&tm_dk, a.dk, a.shape.dtype, p.BH, p.N, D, tc::kTile))
+    if (!tc::make_map_big(&tm_q, a.q, a.shape.dtype, big, tc::kTile) ||
+        !tc::make_map_big(&tm_g, a.d_out, a.shape.dtype, big, tc::kTile) ||
+        !tc::make_map_big(&tm_dq, a.dq, a.shape.dtype, big, tc::kTile) ||
+        !tc::make_map_big(&tm_dk, a.dk, a.shape.dtype, big, tc::kTile))
       return fail(FNB_ERR_CUDA, "cuTensorMapEncodeTiled failed for the backward row passes");
   }
   auto reduce_chunks = [&](const float* in, int nchunk, int elems, float* out) {
@@ -814,9 +824,9 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
       int rc = dispatch_tc(p.D, MP, [&](auto dtag, auto mtag) -> int {
         constexpr int D = decltype(dtag)::value, MPc = decltype(mtag)::value;
         CUtensorMap tm_k, tm_v, tm_qt, tm_do3, tm_dv;
-        if (!tc::make_map_3d(&tm_k, a.k, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
-            !tc::make_map_3d(&tm_v, a.v, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
-            !tc::make_map_3d(&tm_dv, a.dv, a.shape.dtype, p.BH, p.N, D, tc::kTile) ||
+        if (!tc::make_map_big(&tm_k, a.k, a.shape.dtype, big, tc::kTile) ||
+            !tc::make_map_big(&tm_v, a.v, a.shape.dtype, big, tc::kTile) ||
+            !tc::make_map_big(&tm_dv, a.dv, a.shape.dtype, big, tc::kTile) ||
             !tc::make_map_2d(&tm_qt, qt16, a.shape.dtype, p.BH * MPc, D, MPc) ||
             !tc::make_map_2d(&tm_do3, do3n, a.shape.dtype, p.BH * MPc, D, MPc))
           return fail(FNB_ERR_CUDA, "cuTensorMapEncodeTiled failed for the backward column pass");
@@ -1016,6 +1026,7 @@ static int check_sp(const fnb_shape& s, const fnb_sp_info* sp, int is_backward) 
   if (sp->world < 1 || sp->rank < 0 || sp->rank >= sp->world)
     return fail(FNB_ERR_INVALID_ARGUMENT, "sequence parallel: rank %d / world %d out of range", sp->rank, sp->world);
   if (sp->stage < 0 || sp->stage > 2) return fail(FNB_ERR_INVALID_ARGUMENT, "sequence parallel: stage must be 0, 1 or 2");
+  if (s.layout != FNB_LAYOUT_BHND) return fail(FNB_ERR_INVALID_ARGUMENT, "sequence parallel: only the contiguous (B,H,N,D) layout");
   if (sp->seq_len_global != (int64_t)sp->world * s.seq_len)
     return fail(FNB_ERR_INVALID_ARGUMENT, "sequence parallel: seq_len_global (%lld) must equal world (%d) x local seq_len (%lld)",
                 (long long)sp->seq_len_global, sp->world, (long long)s.seq_len);

@@ -78,7 +78,8 @@ __device__ __forceinline__ void load_small(float* dst, int ld, const float* src,
 template <class T>
 __global__ void __launch_bounds__(kThreads)
 landmark_partial_kernel(const T* __restrict__ q, const T* __restrict__ k, float* __restrict__ out,
-                        int64_t BH, int64_t N, int D, int m, int C, int64_t seg_N, int64_t row_offset) {
+                        int64_t BH, int64_t N, int D, int m, int C, int64_t seg_N, int64_t row_offset,
+                        int H, int64_t row_stride, int64_t head_stride, int64_t batch_stride) {
   constexpr int V = Vec16<T>::n;
   __shared__ float red[kThreads * 8];
   pdl_trigger();
@@ -95,7 +96,8 @@ landmark_partial_kernel(const T* __restrict__ q, const T* __restrict__ k, float*
     const int64_t bh = rest / (m * C);
     const int lc = (int)(rest - bh * (m * C));
     const int l = lc / C, c = lc - l * C;
-    const T* slice = (which ? k : q) + bh * N * D;
+    // slice (bh % H, bh / H); its rows are row_stride elements apart (D for the contiguous layout)
+    const T* slice = (which ? k : q) + (bh / H) * batch_stride + (bh % H) * head_stride;
     // segment l in global rows, clipped to the rows this rank holds, in local row numbers
     int64_t start = sg.start(l) - row_offset, end = sg.end(l) - row_offset;
     if (start < 0) start = 0;
@@ -114,7 +116,7 @@ landmark_partial_kernel(const T* __restrict__ q, const T* __restrict__ k, float*
       uint4 raw[8];
 #pragma unroll
       for (int u = 0; u < 8; ++u)
-        raw[u] = __ldcs(reinterpret_cast<const uint4*>(slice + (r + u * rows_per_iter) * D + cv * V));
+        raw[u] = __ldcs(reinterpret_cast<const uint4*>(slice + (r + u * rows_per_iter) * row_stride + cv * V));
 #pragma unroll
       for (int u = 0; u < 8; ++u) {
         const T* e16 = reinterpret_cast<const T*>(&raw[u]);
@@ -124,7 +126,7 @@ landmark_partial_kernel(const T* __restrict__ q, const T* __restrict__ k, float*
     }
     for (; r < r1; r += rows_per_iter) {
       float x[V];
-      load16<T>(slice + r * D + cv * V, x);
+      load16<T>(slice + r * row_stride + cv * V, x);
 #pragma unroll
       for (int e = 0; e < V; ++e) acc[e] += x[e];
     }

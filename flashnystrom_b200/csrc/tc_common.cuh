@@ -163,6 +163,35 @@ __device__ __forceinline__ void tma_store_3d_h(const CUtensorMap* m, const void*
                ::"l"(m), "r"(smem_u32(src)), "r"(c0), "r"(c1), "r"(c2), "l"(pol)
                : "memory");
 }
+// 4-D copies: the (B, H, N, D) tensors are mapped as (D, N, H, B) with explicit strides, so the same
+// kernels read the contiguous layout and the head-split view of a (B, N, H * D) projection output.
+__device__ __forceinline__ void tma_load_4d_h(void* dst, const CUtensorMap* m, uint64_t* bar, int c0, int c1, int c2,
+                                              int c3, uint64_t pol) {
+  if (pol == 0) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(m), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+  } else {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+        " [%0], [%1, {%3, %4, %5, %6}], [%2], %7;"
+        ::"r"(smem_u32(dst)), "l"(m), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "l"(pol)
+        : "memory");
+  }
+}
+__device__ __forceinline__ void tma_store_4d_h(const CUtensorMap* m, const void* src, int c0, int c1, int c2, int c3,
+                                               uint64_t pol) {
+  if (pol == 0) {
+    asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+                 ::"l"(m), "r"(smem_u32(src)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+                 : "memory");
+  } else {
+    asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group.L2::cache_hint [%0, {%2, %3, %4, %5}], [%1], %6;"
+                 ::"l"(m), "r"(smem_u32(src)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "l"(pol)
+                 : "memory");
+  }
+}
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // wait until the source shared memory of all committed stores may be overwritten
 __device__ __forceinline__ void tma_store_wait_read() {

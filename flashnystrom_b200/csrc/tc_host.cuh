@@ -31,17 +31,31 @@ inline CUtensorMapDataType map_dtype(int dtype) {
   return dtype == FNB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
 }
 
-// (BH, N, D) 16-bit tensor, box = 64 columns x box_rows rows of one slice, 128-byte swizzle.
-// Rows past N read as zero and are clipped on store.
-inline bool make_map_3d(CUtensorMap* map, const void* ptr, int dtype, int64_t BH, int64_t N, int D,
-                        int box_rows) {
+// Where slice (b, h) of a (B, H, N, D) tensor lives.  FNB_LAYOUT_BHND: contiguous (B, H, N, D).
+// FNB_LAYOUT_BNHD: the head-split view of a contiguous (B, N, H * D) tensor, i.e. rows of one slice
+// are H * D elements apart.  The kernels always see a 4-D map (D, N, H', B') and address slice bh as
+// (bh % H', bh / H'); for the contiguous layout H' = B * H and B' = 1.
+struct BigLayout {
+  int64_t B, H, N;
+  int D, layout;
+  int map_h() const { return layout == FNB_LAYOUT_BNHD ? (int)H : (int)(B * H); }
+  int64_t row_stride() const { return layout == FNB_LAYOUT_BNHD ? H * D : D; }                 // elements
+  int64_t head_stride() const { return layout == FNB_LAYOUT_BNHD ? D : N * D; }
+  int64_t batch_stride() const { return layout == FNB_LAYOUT_BNHD ? N * H * D : H * N * D; }
+};
+
+// 16-bit (B, H, N, D) tensor in either layout, box = 64 columns x box_rows rows of one slice,
+// 128-byte swizzle.  Rows past N read as zero and are clipped on store.
+inline bool make_map_big(CUtensorMap* map, const void* ptr, int dtype, const BigLayout& g, int box_rows) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return false;
-  cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)N, (cuuint64_t)BH};
-  cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)N * D * 2};
-  cuuint32_t box[3] = {64, (cuuint32_t)box_rows, 1};
-  cuuint32_t estr[3] = {1, 1, 1};
-  return fn(map, map_dtype(dtype), 3, const_cast<void*>(ptr), dims, strides, box, estr,
+  const bool split = g.layout == FNB_LAYOUT_BNHD;
+  cuuint64_t dims[4] = {(cuuint64_t)g.D, (cuuint64_t)g.N, (cuuint64_t)(split ? g.H : g.B * g.H), (cuuint64_t)(split ? g.B : 1)};
+  cuuint64_t strides[3] = {(cuuint64_t)g.row_stride() * 2, (cuuint64_t)g.head_stride() * 2,
+                           (cuuint64_t)(split ? g.batch_stride() : g.B * g.H * g.N * g.D) * 2};
+  cuuint32_t box[4] = {64, (cuuint32_t)box_rows, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  return fn(map, map_dtype(dtype), 4, const_cast<void*>(ptr), dims, strides, box, estr,
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
@@ -69,6 +83,7 @@ inline TcSched make_sched(int64_t BH, int64_t N, int slots) {
   s.order = 0;
   s.hint = 0;
   s.test_drop = 0;
+  s.H = (int)BH;
   int64_t tiles = (N + kTile - 1) / kTile;
   int64_t want = slots / BH;            // floor: BH * want <= slots
   if (want > tiles) want = tiles;

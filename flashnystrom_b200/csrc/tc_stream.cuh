@@ -71,6 +71,8 @@ struct TcSched {
   // in the stream ended finds that data still in L2).
   int order;
   int hint;              // L2 eviction hints, two bits per operand slot (tc_common.cuh: l2_policy_of)
+  int H;                 // extent of the tensor maps' third dimension (heads; batch * heads for the plain layout):
+                         //   slice bh sits at coordinates (bh % H, bh / H)
   int test_drop;         // test only: the output pass's first CTA never issues the load of its last tile,
                          //   so that a bounded wait runs out (FNB_FLAG_TEST_DROP_LOAD)
 };
@@ -205,7 +207,7 @@ template <class T, int D>
 __global__ void __launch_bounds__(kPoolThreads, 2)
 tc_pool_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                float* __restrict__ out, int64_t BH, int64_t N, int m, int C, int64_t seg_N, int64_t row_offset,
-               int* status) {
+               int H, int* status) {
   using L = PoolSmem<D>;
   constexpr int KBD = D / 64, S = L::kStages;
   extern __shared__ uint8_t smem_raw[];
@@ -259,8 +261,8 @@ tc_pool_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           if (!mbar_wait(empty + st, ((g / S) & 1) ^ 1, ab, 0x4100)) { ok = false; break; }
           mbar_expect_tx(full + st, L::kTileBytes);
           for (int kb = 0; kb < KBD; ++kb)
-            tma_load_3d(s_tile + st * L::kTileBytes + kb * (kTile * 128), which ? &tm_k : &tm_q, full + st, kb * 64, (int)r,
-                        (int)bh);
+            tma_load_4d_h(s_tile + st * L::kTileBytes + kb * (kTile * 128), which ? &tm_k : &tm_q, full + st, kb * 64, (int)r,
+                          (int)(bh % H), (int)(bh / H), 0ull);
         }
       }
       if (ab.raised()) {   // let copies already in flight land before the shared memory is released
@@ -400,7 +402,7 @@ tc_fwd_c_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         if (sch.test_drop && blockIdx.x == 0 && i == count - 1) break;   // fault injection on the host's request
         mbar_expect_tx(q_full + st, L::kQ);
         for (int kb = 0; kb < KBD; ++kb)
-          tma_load_3d_h(s_q + st * L::kQ + kb * (kTile * 128), &tm_q, q_full + st, kb * 64, tr.tile(i) * kTile, (int)bh, pol_q);
+          tma_load_4d_h(s_q + st * L::kQ + kb * (kTile * 128), &tm_q, q_full + st, kb * 64, tr.tile(i) * kTile, (int)(bh % sch.H), (int)(bh / sch.H), pol_q);
         armed = i + 1;
       }
       if (ab.raised())   // let copies already in flight land before the shared memory is released
@@ -518,7 +520,7 @@ tc_fwd_c_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       named_barrier(1 + g, kGroup);
       if (leader) {
         for (int kb = 0; kb < KBD; ++kb)
-          tma_store_3d_h(&tm_o, my_p + kb * (kTile * 128), kb * 64, tr.tile(i) * kTile, (int)bh, pol_o);
+          tma_store_4d_h(&tm_o, my_p + kb * (kTile * 128), kb * 64, tr.tile(i) * kTile, (int)(bh % sch.H), (int)(bh / sch.H), pol_o);
         tma_store_commit();
       }
     }
@@ -618,8 +620,8 @@ tc_bwd_a_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         if (!mbar_wait(in_empty + st, ((i / NST) & 1) ^ 1, ab, 0x1100 + i)) break;
         mbar_expect_tx(in_full + st, 2 * L::kIn);
         for (int kb = 0; kb < D / 64; ++kb) {
-          tma_load_3d_h(s_q + st * 2 * L::kIn + kb * (kTile * 128), &tm_q, in_full + st, kb * 64, tr.tile(i) * kTile, (int)bh, pol_q);
-          tma_load_3d_h(s_g + st * 2 * L::kIn + kb * (kTile * 128), &tm_g, in_full + st, kb * 64, tr.tile(i) * kTile, (int)bh, pol_g);
+          tma_load_4d_h(s_q + st * 2 * L::kIn + kb * (kTile * 128), &tm_q, in_full + st, kb * 64, tr.tile(i) * kTile, (int)(bh % sch.H), (int)(bh / sch.H), pol_q);
+          tma_load_4d_h(s_g + st * 2 * L::kIn + kb * (kTile * 128), &tm_g, in_full + st, kb * 64, tr.tile(i) * kTile, (int)(bh % sch.H), (int)(bh / sch.H), pol_g);
         }
         armed = i + 1;
       }
@@ -676,7 +678,7 @@ tc_bwd_a_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         umma_commit(in_empty + st);
         // the dS tile as it is -> (the first MP columns of) the dQ tile of the same rows
         for (int kb = 0; kb < MP / 64; ++kb)
-          tma_store_3d_h(&tm_dq, s_ds + kb * (kTile * 128), kb * 64, tr.tile(i) * kTile, (int)bh, pol_ds);
+          tma_store_4d_h(&tm_dq, s_ds + kb * (kTile * 128), kb * 64, tr.tile(i) * kTile, (int)(bh % sch.H), (int)(bh / sch.H), pol_ds);
         tma_store_commit();
         if (i + 1 < count && !front(i + 1)) break;
         // acc_done lets the compute warps overwrite the dS tile: the copy must have read it
@@ -904,8 +906,8 @@ tc_rows_inplace_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_co
         if (!mbar_wait(in_empty + s, ((i / kStages) & 1) ^ 1, ab, 0x2100 + i)) break;
         mbar_expect_tx(in_full + s, L::kIn);
         for (int kb = 0; kb < MP / 64; ++kb)
-          tma_load_3d_h(s_in + s * L::kIn + kb * (kTile * 128), second ? &tm_b : &tm_a, in_full + s, kb * 64,
-                        (second ? trb.tile(i - count) : tra.tile(i)) * kTile, (int)bh, second ? pol_b : pol_a);
+          tma_load_4d_h(s_in + s * L::kIn + kb * (kTile * 128), second ? &tm_b : &tm_a, in_full + s, kb * 64,
+                        (second ? trb.tile(i - count) : tra.tile(i)) * kTile, (int)(bh % sch.H), (int)(bh / sch.H), second ? pol_b : pol_a);
         armed = i + 1;
       }
       if (ab.raised())
@@ -1012,8 +1014,8 @@ tc_rows_inplace_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_co
       named_barrier(1 + g, kGroup);
       if (leader) {
         for (int kb = 0; kb < D / 64; ++kb)
-          tma_store_3d_h(second ? &tm_b : &tm_a, my_out + kb * (kTile * 128), kb * 64, tile * kTile, (int)bh,
-                         second ? pol_ob : pol_oa);
+          tma_store_4d_h(second ? &tm_b : &tm_a, my_out + kb * (kTile * 128), kb * 64, tile * kTile, (int)(bh % sch.H),
+                         (int)(bh / sch.H), second ? pol_ob : pol_oa);
         tma_store_commit();
       }
     }
@@ -1131,11 +1133,11 @@ tc_bwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
         if (!mbar_wait(k_empty + st, ((i >> 1) & 1) ^ 1, ab, 0x2100 + i)) break;
         mbar_expect_tx(k_full + st, L::kIn);
         for (int kb = 0; kb < KBD; ++kb)
-          tma_load_3d_h(s_k + st * L::kIn + kb * (kTile * 128), &tm_k, k_full + st, kb * 64, tr.tile(i) * kTile, (int)bh, pol_k);
+          tma_load_4d_h(s_k + st * L::kIn + kb * (kTile * 128), &tm_k, k_full + st, kb * 64, tr.tile(i) * kTile, (int)(bh % sch.H), (int)(bh / sch.H), pol_k);
         if (!mbar_wait(v_empty, (i & 1) ^ 1, ab, 0x2180 + i)) { armed = -(i + 1); break; }
         mbar_expect_tx(v_full, L::kIn);
         for (int kb = 0; kb < KBD; ++kb)
-          tma_load_3d_h(s_v + kb * (kTile * 128), &tm_v, v_full, kb * 64, tr.tile(i) * kTile, (int)bh, pol_v);
+          tma_load_4d_h(s_v + kb * (kTile * 128), &tm_v, v_full, kb * 64, tr.tile(i) * kTile, (int)(bh % sch.H), (int)(bh / sch.H), pol_v);
         armed = i + 1;
       }
       if (ab.raised()) {
@@ -1178,7 +1180,7 @@ tc_bwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
         // the dS' tile as it is -> dK tile of the same rows (after the products: their commit
         // frees the K stage)
         for (int kb = 0; kb < MP / 64; ++kb)
-          tma_store_3d_h(&tm_dk, s_ds + kb * (kTile * 128), kb * 64, tr.tile(i) * kTile, (int)bh, pol_ds);
+          tma_store_4d_h(&tm_dk, s_ds + kb * (kTile * 128), kb * 64, tr.tile(i) * kTile, (int)(bh % sch.H), (int)(bh / sch.H), pol_ds);
         tma_store_commit();
         // out_full lets the compute warps move on to the next dS' tile: the copy must have read it
         tma_store_wait_read();
@@ -1302,7 +1304,7 @@ tc_bwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
       named_barrier(1, kComputeThreads);
       if (threadIdx.x == 0) {
         for (int kb = 0; kb < KBD; ++kb)
-          tma_store_3d_h(&tm_dv, s_p + kb * (kTile * 128), kb * 64, tr.tile(i) * kTile, (int)bh, pol_dv);
+          tma_store_4d_h(&tm_dv, s_p + kb * (kTile * 128), kb * 64, tr.tile(i) * kTile, (int)(bh % sch.H), (int)(bh / sch.H), pol_dv);
         tma_store_commit();
       }
     }
@@ -1440,14 +1442,14 @@ tc_fwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
         if (!mbar_wait(k_empty + st, ((i >> 1) & 1) ^ 1, ab, 0x3100 + i)) break;
         mbar_expect_tx(k_full + st, L::kIn);
         for (int kb = 0; kb < KBD; ++kb)
-          tma_load_3d_h(s_k + st * L::kIn + kb * (kTile * 128), &tm_k, k_full + st, kb * 64, tr.tile(i) * kTile, (int)bh, pol_k);
+          tma_load_4d_h(s_k + st * L::kIn + kb * (kTile * 128), &tm_k, k_full + st, kb * 64, tr.tile(i) * kTile, (int)(bh % sch.H), (int)(bh / sch.H), pol_k);
         TC_TRACE(0, i);
         nk = i + 1;
         const int sv = i % VS;
         if (!mbar_wait(v_empty + sv, ((i / VS) & 1) ^ 1, ab, 0x3180 + i)) break;
         mbar_expect_tx(v_full + sv, L::kIn);
         for (int kb = 0; kb < KBD; ++kb)
-          tma_load_3d_h(s_v + sv * L::kIn + kb * (kTile * 128), &tm_v, v_full + sv, kb * 64, tr.tile(i) * kTile, (int)bh, pol_v);
+          tma_load_4d_h(s_v + sv * L::kIn + kb * (kTile * 128), &tm_v, v_full + sv, kb * 64, tr.tile(i) * kTile, (int)(bh % sch.H), (int)(bh / sch.H), pol_v);
         TC_TRACE(1, i);
         nv = i + 1;
       }

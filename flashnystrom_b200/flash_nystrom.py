@@ -46,7 +46,9 @@ class FlashNystromFunction(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad_output):
         s = ctx.saved_tensors
-        dQ, dK, dV = _C.backward(grad_output.contiguous(), *s[0:12], s[12], s[13],
+        # (the shim brings grad_output to the layout of q: no copy when both are contiguous or both
+        # are head-split views of (B, N, H*D) tensors, which is what the module below produces)
+        dQ, dK, dV = _C.backward(grad_output, *s[0:12], s[12], s[13],
                                  ctx.num_landmarks, ctx.newton_iter, ctx.fast_dk2inv,
                                  ctx.kappa_star)
         return dQ, dK, dV, None, None, None, None, None
@@ -101,13 +103,19 @@ class FlashNystromAttention(nn.Module):
     def forward(self, x):
         B, N, _ = x.shape
         H, D = self.heads, self.head_dim
-        q = self.q_proj(x).view(B, N, H, D).transpose(1, 2).contiguous()
-        k = self.k_proj(x).view(B, N, H, D).transpose(1, 2).contiguous()
-        v = self.v_proj(x).view(B, N, H, D).transpose(1, 2).contiguous()
+        # Head-split views of the projection outputs, no transposing copies: where the tensor-core
+        # kernels run they read this layout through strided tensor maps and write the output and the
+        # gradients the same way; elsewhere the copies the reference always makes
+        # (flash_nystrom/flash_nystrom.py:271-276) are made here.
+        q = self.q_proj(x).view(B, N, H, D).transpose(1, 2)
+        k = self.k_proj(x).view(B, N, H, D).transpose(1, 2)
+        v = self.v_proj(x).view(B, N, H, D).transpose(1, 2)
+        if not (q.is_cuda and _C.tc_eligible(q.dtype, D, self.config.num_landmarks)):
+            q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
         ks = self.config.conv_kernel_size if self.conv_weight is not None else 0
         out = flash_nystrom_attention(
             q, k, v, num_landmarks=self.config.num_landmarks, newton_iter=self.config.newton_iter,
             conv_weight=self.conv_weight, conv_kernel_size=ks,
             fast_dk2inv=self.config.fast_dk2inv, kappa_star=self.config.kappa_star,
             use_tc_pinv=self.config.use_tc_pinv)
-        return self.out_proj(out.transpose(1, 2).contiguous().view(B, N, self.dim))
+        return self.out_proj(out.transpose(1, 2).reshape(B, N, self.dim))

@@ -22,7 +22,7 @@
 extern "C" {
 #endif
 
-#define FNB_ABI_VERSION 1
+#define FNB_ABI_VERSION 2
 
 #if defined(__GNUC__)
 #define FNB_API __attribute__((visibility("default")))
@@ -41,6 +41,17 @@ enum fnb_status {
 };
 
 enum fnb_dtype { FNB_F32 = 0, FNB_F16 = 1, FNB_BF16 = 2 };
+
+/* Memory layout of the (B,H,N,D) tensors q, k, v, out, d_out, dq, dk, dv (all eight share it).
+ * FNB_LAYOUT_BHND: contiguous (B,H,N,D), what the reference's kernels require
+ *   (csrc/flash_nystrom.cu:45-56).
+ * FNB_LAYOUT_BNHD: element (b,h,n,d) at ((b*N + n)*H + h)*D + d, i.e. the head-split view of a
+ *   contiguous (B,N,H*D) projection output.  The reference's module makes four transposing copies
+ *   to get from this to BHND and back (flash_nystrom/flash_nystrom.py:271-292); with this layout
+ *   none is needed.  Tensor-core path only (16-bit dtypes, head_dim 64 with num_landmarks <= 64 or
+ *   head_dim 128 with num_landmarks <= 128); other shapes are refused with
+ *   FNB_ERR_INVALID_ARGUMENT, and so are the sequence-parallel entry points. */
+enum fnb_layout { FNB_LAYOUT_BHND = 0, FNB_LAYOUT_BNHD = 1 };
 
 /* flags */
 #define FNB_FLAG_FORCE_GENERIC 1u /* use the CUDA-core FP32 kernels even where a tensor-core
@@ -64,6 +75,8 @@ typedef struct fnb_shape {
   int32_t dtype;          /* fnb_dtype of q, k, v, out, dO, dQ, dK, dV            */
   float kappa_star;       /* Tikhonov ridge target condition number, 0 = no ridge */
   uint32_t flags;
+  int32_t layout;         /* fnb_layout of the eight (B,H,N,D) tensors            */
+  int32_t reserved;       /* 0                                                    */
 } fnb_shape;
 
 /* Forward.  Replaces nystrom_fwd + run_nystrom_fwd (csrc/flash_nystrom.cu:30-172,

@@ -25,7 +25,7 @@ def test_every_declared_symbol_is_exported_and_bound(lib):
     for name in declared:
         assert hasattr(lib, name), f"{name} declared in the header but not exported"
     assert declared == set(_lib.SIGNATURES), "ctypes binding and header disagree"
-    assert lib.fnb_version() == 1
+    assert lib.fnb_version() == 2
 
 
 def _shape(B=1, H=2, N=256, D=64, m=32, J=6, dtype=_lib.FNB_F16, kappa=0.0):
