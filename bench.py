@@ -50,13 +50,13 @@ KERNEL_PASSES = {
     "gen_bwd_c": 3,
     # tc_bwd_a also writes its dS1 tiles (into dq), tc_bwd_b writes dS3' tiles (into dk) and dV,
     # tc_bwd_c reads both sets of tiles and writes dQ and dK in place
-    "tc_pool": 2, "tc_fwd_b": 2, "tc_fwd_c": 2, "tc_bwd_a": 3, "tc_bwd_b": 4, "tc_bwd_c": 4,
+    "tc_fwd_b": 2, "tc_fwd_c": 2, "tc_bwd_a": 3, "tc_bwd_b": 4, "tc_bwd_c": 4,
 }
 # The same kernels counted in the bytes the algorithm itself needs (reads of Q, K, V, dO once in each
 # direction, writes of O, dQ, dK, dV once): the parked softmax-Jacobian tiles and the second
 # reads of Q and K by the pooling pass are traffic this design adds, not algorithmic bytes.
 ALGORITHMIC_PASSES = {
-    "landmark_partial": 0, "tc_pool": 0, "tc_fwd_b": 2, "tc_fwd_c": 2, "tc_bwd_a": 2, "tc_bwd_b": 3, "tc_bwd_c": 2,
+    "landmark_partial": 0, "tc_fwd_b": 2, "tc_fwd_c": 2, "tc_bwd_a": 2, "tc_bwd_b": 3, "tc_bwd_c": 2,
     "gen_fwd_b": 2, "gen_fwd_c": 2, "gen_bwd_a": 2, "gen_bwd_b": 4, "gen_bwd_c": 1,
 }
 

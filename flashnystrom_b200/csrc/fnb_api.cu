@@ -393,31 +393,7 @@ static int forward_impl(const fnb_fwd_args& a, const Plan& p, const FwdWs& w, in
   const size_t md_all = (size_t)p.BH * p.m * p.D, m_all = (size_t)p.BH * p.m;
 
   if (S.run(0)) {
-    bool pooled = false;
-    if constexpr (k16) {
-      if (use_tc && (l2 & 64)) {
-        // TMA-fed pooling pass (16-bit inputs, head_dim 64 or 128); measured slower than the
-        // CUDA-core pass (67 against 59 us at B=1, H=16, N=65536), so off unless asked for
-        int rc = dispatch_head_dim(p.D, [&](auto dtag) -> int {
-          constexpr int D = decltype(dtag)::value;
-          CUtensorMap tm_q, tm_k;
-          if (!tc::make_map_big(&tm_q, a.q, a.shape.dtype, big, tc::kTile) ||
-              !tc::make_map_big(&tm_k, a.k, a.shape.dtype, big, tc::kTile))
-            return fail(FNB_ERR_CUDA, "cuTensorMapEncodeTiled failed for the pooling pass");
-          L.begin();
-          auto kern = tc::tc_pool_kernel<T, D>;
-          size_t smem = tc::PoolSmem<D>::kBytes;
-          if (int rc2 = set_smem(kern, smem, max_smem, "tc_pool")) return rc2;
-          const int64_t grid = std::min<int64_t>(2 * p.BH * p.m * lmC, (int64_t)sms * 2);
-          launch_pdl(kern, dim3((unsigned)grid), dim3(tc::kPoolThreads), smem, st, tm_q, tm_k, land, p.BH, p.N, p.m, lmC,
-                     seg_N, row_offset, big.map_h(), a.device_status);
-          return L.end("tc_pool");
-        });
-        if (rc) return rc;
-        pooled = true;
-      }
-    }
-    if (!pooled) {
+    {
       L.begin();
       int64_t grid = std::min<int64_t>(2 * p.BH * p.m * lmC, (int64_t)sms * 4);
       launch_pdl(landmark_partial_kernel<T>, dim3((unsigned)grid), dim3(kThreads), 0, st,
@@ -1282,7 +1258,6 @@ int fnb_kernel_report(int device, fnb_kernel_info* out, int cap) {
   using H = __half;
   const KernelEntry ks[] = {
       {"landmark_partial<half>", (const void*)landmark_partial_kernel<H>, kThreads, 0},
-      {"tc_pool<half,64>", (const void*)tc::tc_pool_kernel<H, 64>, tc::kPoolThreads, tc::PoolSmem<64>::kBytes},
       {"ns_fwd_tc", (const void*)nstc::ns_fwd_tc_kernel, nstc::kNsTcThreads, nstc::kFwdSmem},
       {"tc_fwd_b<half,64,64>", (const void*)tc::tc_fwd_b_kernel<H, 64, 64>, tc::kTcThreads, tc::FwdBSmem<64, 64>::kBytes},
       {"combine_slab", (const void*)combine_slab_kernel, kThreads, combine_slab_smem(64)},

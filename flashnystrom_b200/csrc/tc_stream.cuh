@@ -186,141 +186,6 @@ __device__ __forceinline__ TileRange tile_range(const TcSched& sch, int order) {
 __device__ __forceinline__ TileRange tile_range(const TcSched& sch) { return tile_range(sch, sch.order); }
 
 // ------------------------------------------------------------------------------------------
-// Landmark pooling pass: raw segment sums of Q and K, fed by TMA.
-//   out[which][bh][l][c][D]  (which = 0: Q, 1: K; c: chunk of the landmark's segment)
-// A persistent grid walks the work items (which, bh, landmark, chunk); the producer warp streams
-// the 128-row tiles of one item after another through a ring of kStages tiles, running ahead
-// across item boundaries, and the eight consumer warps add up the rows of each tile from shared
-// memory in FP32 (a warp reads one 128-byte row per instruction: conflict-free whatever the
-// swizzle).  Tiles start at the item's first row, so rows past the item's end (the next chunk's
-// rows, or zero fill past the slice) are simply not added.
-template <int D>
-struct PoolSmem {
-  static constexpr int kTileBytes = kTile * D * 2;
-  static constexpr int kStages = D == 64 ? 6 : 3;
-  static constexpr int kScratch = 2 * 8 * D * 4;     // per-warp partial rows, double-buffered by item parity
-  static constexpr int kBytes = kStages * kTileBytes + kScratch + 256 + 1024;
-};
-constexpr int kPoolThreads = 288;   // 8 consumer warps + the producer warp
-
-template <class T, int D>
-__global__ void __launch_bounds__(kPoolThreads, 2)
-tc_pool_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-               float* __restrict__ out, int64_t BH, int64_t N, int m, int C, int64_t seg_N, int64_t row_offset,
-               int H, int* status) {
-  using L = PoolSmem<D>;
-  constexpr int KBD = D / 64, S = L::kStages;
-  extern __shared__ uint8_t smem_raw[];
-  pdl_trigger();
-  uint8_t* base = align1024(smem_raw);
-  uint8_t* s_tile = base;
-  float* s_part = reinterpret_cast<float*>(s_tile + S * L::kTileBytes);   // [2][8][D]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(s_part) + L::kScratch);
-  uint64_t* full = bars;          // [S]
-  uint64_t* empty = bars + S;     // [S]
-  int* abort_word = reinterpret_cast<int*>(bars + 2 * S);
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < S; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, 8); }
-    *abort_word = 0;
-    fence_mbar_init();
-  }
-  __syncthreads();
-  pdl_wait();
-  Abort ab{abort_word, status};
-  const int64_t per_which = BH * m * C, items = 2 * per_which;
-  Segments sg(seg_N, m);
-  // rows [r0, r1) of this rank's slice that item `item` covers
-  auto item_rows = [&](int64_t item, int& which, int64_t& bh, int64_t& r0, int64_t& r1) {
-    which = (int)(item / per_which);
-    const int64_t rest = item - which * per_which;
-    bh = rest / (m * C);
-    const int lc = (int)(rest - bh * (m * C));
-    const int l = lc / C, c = lc - l * C;
-    int64_t start = sg.start(l) - row_offset, end = sg.end(l) - row_offset;
-    if (start < 0) start = 0;
-    if (end > N) end = N;
-    const int64_t len = end > start ? end - start : 0;
-    const int64_t per = (len + C - 1) / C;
-    r0 = start + c * per;
-    r1 = r0 + per;
-    if (r1 > start + len) r1 = start + len;
-    if (r1 < r0) r1 = r0;
-  };
-  if (warp == 8) {
-    if (lane == 0) {
-      tma_prefetch_desc(&tm_q);
-      tma_prefetch_desc(&tm_k);
-      uint32_t g = 0;
-      bool ok = true;
-      for (int64_t item = blockIdx.x; ok && item < items; item += gridDim.x) {
-        int which; int64_t bh, r0, r1;
-        item_rows(item, which, bh, r0, r1);
-        for (int64_t r = r0; r < r1; r += kTile, ++g) {
-          const int st = (int)(g % S);
-          if (!mbar_wait(empty + st, ((g / S) & 1) ^ 1, ab, 0x4100)) { ok = false; break; }
-          mbar_expect_tx(full + st, L::kTileBytes);
-          for (int kb = 0; kb < KBD; ++kb)
-            tma_load_4d_h(s_tile + st * L::kTileBytes + kb * (kTile * 128), which ? &tm_k : &tm_q, full + st, kb * 64, (int)r,
-                          (int)(bh % H), (int)(bh / H), 0ull);
-        }
-      }
-      if (ab.raised()) {   // let copies already in flight land before the shared memory is released
-        const uint32_t lo = g > (uint32_t)S ? g - S : 0;
-        for (uint32_t i = lo; i < g; ++i) mbar_drain(full + (i % S), (i / S) & 1);
-      }
-    }
-  } else {
-    uint32_t g = 0;
-    int par = 0;
-    bool ok = true;
-    for (int64_t item = blockIdx.x; item < items; item += gridDim.x, par ^= 1) {
-      int which; int64_t bh, r0, r1;
-      item_rows(item, which, bh, r0, r1);
-      float acc[KBD][2];
-#pragma unroll
-      for (int kb = 0; kb < KBD; ++kb) acc[kb][0] = acc[kb][1] = 0.f;
-      for (int64_t r = r0; ok && r < r1; r += kTile, ++g) {
-        const int st = (int)(g % S);
-        if (!mbar_wait(full + st, (g / S) & 1, ab, 0x4200)) { ok = false; break; }
-        const int valid = (r1 - r) < (int64_t)kTile ? (int)(r1 - r) : kTile;
-        const uint8_t* tile = s_tile + st * L::kTileBytes;
-#pragma unroll
-        for (int rr = 0; rr < kTile / 8; ++rr) {
-          const int row = warp * (kTile / 8) + rr;
-          if (row < valid) {
-#pragma unroll
-            for (int kb = 0; kb < KBD; ++kb) {
-              const uint32_t w = *reinterpret_cast<const uint32_t*>(tile + kb * (kTile * 128) + sw128_offset(row, lane >> 2) +
-                                                                    (lane & 3) * 4);
-              const T* e = reinterpret_cast<const T*>(&w);
-              acc[kb][0] += to_f<T>(e[0]);
-              acc[kb][1] += to_f<T>(e[1]);
-            }
-          }
-        }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(empty + st);
-      }
-      // fold the eight warps: this item's sums for columns 64 kb + 2 lane, + 1
-      float* part = s_part + par * 8 * D;
-#pragma unroll
-      for (int kb = 0; kb < KBD; ++kb)
-        *reinterpret_cast<float2*>(part + warp * D + kb * 64 + 2 * lane) = make_float2(acc[kb][0], acc[kb][1]);
-      named_barrier(1, 256);
-      if (threadIdx.x < D) {
-        float s = 0.f;
-#pragma unroll
-        for (int w = 0; w < 8; ++w) s += part[w * D + threadIdx.x];
-        if (ok) out[(size_t)item * D + threadIdx.x] = s;
-      }
-      // (the other half of the scratch serves the next item; this half is rewritten two items
-      // later, after another pass through the barrier above)
-    }
-  }
-}
-
-// ------------------------------------------------------------------------------------------
 // Forward output pass:  O = softmax(Q Kt^T) step2, lse1.
 //   kt16 = s*log2e*Kt (MP x D), st16 = step2^T / 2^e (D x MP), st_scale[bh] = 2^e.
 // The eight compute warps form two groups of 128 threads (one thread per tile row, all landmark
