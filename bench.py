@@ -336,7 +336,8 @@ def seqpar_leg(dev, rank, world, w, steps, warmup, timed, peak):
         return {"skipped": f"num_landmarks {m} / N {N} do not split over {world} ranks"}
     Nl = N // world
     rows = slice(rank * Nl, (rank + 1) * Nl)
-    res = {"config": f"B={B},H={H},N={N},D={D},m={m},J={J} fp16, sequence split over {world} ranks", "world": world}
+    res = {"config": f"B={B},H={H},N={N},D={D},m={m},J={J} fp16, sequence split over {world} ranks", "world": world,
+           "dO_loss_scale": 1024}
 
     # (a) small case against the CPU oracle (rank 0 checks its own rows)
     sq, sk, sv, sdO = O.make_inputs(1, 2, 65536, D, seed=5, dtype=torch.float16)
@@ -354,7 +355,10 @@ def seqpar_leg(dev, rank, world, w, steps, warmup, timed, peak):
 
     # (b) the full configuration: head 0 from a seed all ranks share, the others rank-private
     g0 = torch.Generator(device=dev).manual_seed(1234)
-    full = [torch.randn(1, 1, N, D, generator=g0, device=dev, dtype=torch.float32).half() for _ in range(4)]
+    # dO carries a loss scale of 1024, as fp16 training does: at N = 2^20 the gradients of unit-scale
+    # dO are ~1e-6, where fp16 outputs are subnormal and two correct results differ by a quantum
+    full = [torch.randn(1, 1, N, D, generator=g0, device=dev, dtype=torch.float32).mul_(sc).half()
+            for sc in (1.0, 1.0, 1.0, 1024.0)]
     fq, fk, fv = (t.clone().requires_grad_(True) for t in full[:3])
     fo = flash_nystrom_attention(fq, fk, fv, num_landmarks=m, newton_iter=J, kappa_star=kap)
     fo.backward(full[3])
@@ -362,8 +366,8 @@ def seqpar_leg(dev, rank, world, w, steps, warmup, timed, peak):
     del fq, fk, fv, fo
     gr = torch.Generator(device=dev).manual_seed(4321 + rank)
     shard = []
-    for t in full:
-        rest = torch.randn(B, H - 1, Nl, D, generator=gr, device=dev, dtype=torch.float32).half()
+    for t, sc in zip(full, (1.0, 1.0, 1.0, 1024.0)):
+        rest = torch.randn(B, H - 1, Nl, D, generator=gr, device=dev, dtype=torch.float32).mul_(sc).half()
         shard.append(torch.cat([t[:, :, rows], rest], dim=1).contiguous())
     del full, rest
     q, k, v = (t.requires_grad_(True) for t in shard[:3])
