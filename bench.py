@@ -518,13 +518,6 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    def max_over_ranks(x):
-        if world == 1:
-            return x
-        t = torch.tensor([x], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
-
     def timed(fn, n):
         """n calls of fn between two events on the current stream; (device ms per call, max over
         ranks; this rank's host enqueue ms per call)."""
@@ -537,7 +530,14 @@ def main():
         host_ms = (time.perf_counter() - t0) * 1e3 / n
         e1.record()
         barrier()
-        return max_over_ranks(e0.elapsed_time(e1)) / n, host_ms
+        mine = e0.elapsed_time(e1) / n
+        if world > 1:
+            allr = torch.zeros(world, device=dev, dtype=torch.float64)
+            dist.all_gather_into_tensor(allr, torch.tensor([mine], device=dev, dtype=torch.float64))
+            timed.per_rank = [round(float(x), 4) for x in allr.tolist()]
+        else:
+            timed.per_rank = [round(mine, 4)]
+        return max(timed.per_rank) if world > 1 else mine, host_ms
 
     # ---- parity of this very workload, before anything is timed --------------------------------
     parity = None
@@ -562,6 +562,7 @@ def main():
         step_resident()
     with ClockSampler(local) as clocks:
         ms_eager, host_ms = timed(step_resident, steps)
+        eager_per_rank = timed.per_rank
         # the same load a little longer, so that the 20 ms sampler sees the GPU under it
         t_end = time.perf_counter() + 0.25
         while time.perf_counter() < t_end:
@@ -572,7 +573,7 @@ def main():
     # The same step captured once into a CUDA graph and replayed (the library allocates nothing,
     # never synchronises and forks its side stream with events, so a caller may capture it): the
     # host then enqueues one graph launch per step instead of ~11 kernels and ~25 allocations.
-    graph_ms, graph_note = None, None
+    graph_ms, graph_note, graph_per_rank = None, None, None
     if os.environ.get("FNB_BENCH_GRAPH", "1") == "1":
         try:
             side = torch.cuda.Stream(device=dev)
@@ -592,6 +593,7 @@ def main():
             torch.cuda.synchronize()
             _C.check_device_status()
             graph_ms, _ = timed(g.replay, steps)
+            graph_per_rank = timed.per_rank
             if parity is not None:   # the replayed graph must reproduce the eager gradients
                 h = parity["head"]
                 graph_note = "replay matches the float64 oracle: " + str(
@@ -724,8 +726,8 @@ def main():
             "per_gpu_workload": True,
             "l2": "inputs (4 x 134 MB per GPU) exceed the 126 MB L2; no explicit flush",
             "launch_mode": "CUDA graph replay of the captured step" if use_graph else "eager (one API call per pass)",
-            "eager": {"ms_per_step": ms_eager, "host_enqueue_ms_per_step": host_ms},
-            "graph": {"ms_per_step": graph_ms, "note": graph_note},
+            "eager": {"ms_per_step": ms_eager, "host_enqueue_ms_per_step": host_ms, "per_rank_ms": eager_per_rank},
+            "graph": {"ms_per_step": graph_ms, "note": graph_note, "per_rank_ms": graph_per_rank},
             "tokens_per_s_per_gpu": tokens_per_s / world,
             "parity": parity, "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e,
             "sharded": sharded, "seqpar": seqpar, "extras": extras,

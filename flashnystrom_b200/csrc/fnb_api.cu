@@ -396,7 +396,8 @@ static int forward_impl(const fnb_fwd_args& a, const Plan& p, const FwdWs& w, in
     {
       L.begin();
       int64_t grid = std::min<int64_t>(2 * p.BH * p.m * lmC, (int64_t)sms * 4);
-      launch_pdl(landmark_partial_kernel<T>, dim3((unsigned)grid), dim3(kThreads), 0, st,
+      auto pool = (a.shape.layout == FNB_LAYOUT_BNHD) ? landmark_partial_kernel<T, false> : landmark_partial_kernel<T, true>;
+      launch_pdl(pool, dim3((unsigned)grid), dim3(kThreads), 0, st,
           (const T*)a.q, (const T*)a.k, land, p.BH, p.N, p.D, p.m, lmC, seg_N, row_offset, big.map_h(), big.row_stride(),
           big.head_stride(), big.batch_stride());
       if (L.end("landmark_partial")) return L.status;
@@ -1257,7 +1258,7 @@ int fnb_kernel_report(int device, fnb_kernel_info* out, int cap) {
   if (!g.ok) return 0;
   using H = __half;
   const KernelEntry ks[] = {
-      {"landmark_partial<half>", (const void*)landmark_partial_kernel<H>, kThreads, 0},
+      {"landmark_partial<half>", (const void*)landmark_partial_kernel<H, true>, kThreads, 0},
       {"ns_fwd_tc", (const void*)nstc::ns_fwd_tc_kernel, nstc::kNsTcThreads, nstc::kFwdSmem},
       {"tc_fwd_b<half,64,64>", (const void*)tc::tc_fwd_b_kernel<H, 64, 64>, tc::kTcThreads, tc::FwdBSmem<64, 64>::kBytes},
       {"combine_slab", (const void*)combine_slab_kernel, kThreads, combine_slab_smem(64)},

@@ -159,6 +159,7 @@ __device__ __forceinline__ float pack_landmark_operands(uint8_t* tile_a, uint8_t
 
 struct TileRange {
   int64_t bh;
+  int ch, cb;            // tensor-map coordinates of the slice: (bh % H, bh / H)
   int chunk, first, step, count;
   bool desc;
   // i-th tile this CTA works on
@@ -168,8 +169,11 @@ struct TileRange {
 };
 __device__ __forceinline__ TileRange tile_range(const TcSched& sch, int order) {
   TileRange t;
-  t.bh = blockIdx.x / sch.nchunk;
-  t.chunk = (int)(blockIdx.x - t.bh * sch.nchunk);
+  const int bhi = (int)blockIdx.x / sch.nchunk;
+  t.bh = bhi;
+  t.ch = bhi % sch.H;
+  t.cb = bhi / sch.H;
+  t.chunk = (int)blockIdx.x - bhi * sch.nchunk;
   const int total_tiles = (int)((sch.N + kTile - 1) / kTile);
   if (order & kOrderStrided) {
     t.first = t.chunk;
@@ -232,6 +236,7 @@ tc_fwd_c_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const TileRange tr = tile_range(sch);
+  const int tr_ch = tr.ch, tr_cb = tr.cb;
   const int64_t bh = tr.bh;
   const int count = tr.count;
 
@@ -267,7 +272,7 @@ tc_fwd_c_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         if (sch.test_drop && blockIdx.x == 0 && i == count - 1) break;   // fault injection on the host's request
         mbar_expect_tx(q_full + st, L::kQ);
         for (int kb = 0; kb < KBD; ++kb)
-          tma_load_4d_h(s_q + st * L::kQ + kb * (kTile * 128), &tm_q, q_full + st, kb * 64, tr.tile(i) * kTile, (int)(bh % sch.H), (int)(bh / sch.H), pol_q);
+          tma_load_4d_h(s_q + st * L::kQ + kb * (kTile * 128), &tm_q, q_full + st, kb * 64, tr.tile(i) * kTile, tr_ch, tr_cb, pol_q);
         armed = i + 1;
       }
       if (ab.raised())   // let copies already in flight land before the shared memory is released
@@ -385,7 +390,7 @@ tc_fwd_c_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       named_barrier(1 + g, kGroup);
       if (leader) {
         for (int kb = 0; kb < KBD; ++kb)
-          tma_store_4d_h(&tm_o, my_p + kb * (kTile * 128), kb * 64, tr.tile(i) * kTile, (int)(bh % sch.H), (int)(bh / sch.H), pol_o);
+          tma_store_4d_h(&tm_o, my_p + kb * (kTile * 128), kb * 64, tr.tile(i) * kTile, tr_ch, tr_cb, pol_o);
         tma_store_commit();
       }
     }
@@ -451,6 +456,7 @@ tc_bwd_a_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const TileRange tr = tile_range(sch);
+  const int tr_ch = tr.ch, tr_cb = tr.cb;
   const int64_t bh = tr.bh;
   const int count = tr.count;
 
@@ -485,8 +491,8 @@ tc_bwd_a_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         if (!mbar_wait(in_empty + st, ((i / NST) & 1) ^ 1, ab, 0x1100 + i)) break;
         mbar_expect_tx(in_full + st, 2 * L::kIn);
         for (int kb = 0; kb < D / 64; ++kb) {
-          tma_load_4d_h(s_q + st * 2 * L::kIn + kb * (kTile * 128), &tm_q, in_full + st, kb * 64, tr.tile(i) * kTile, (int)(bh % sch.H), (int)(bh / sch.H), pol_q);
-          tma_load_4d_h(s_g + st * 2 * L::kIn + kb * (kTile * 128), &tm_g, in_full + st, kb * 64, tr.tile(i) * kTile, (int)(bh % sch.H), (int)(bh / sch.H), pol_g);
+          tma_load_4d_h(s_q + st * 2 * L::kIn + kb * (kTile * 128), &tm_q, in_full + st, kb * 64, tr.tile(i) * kTile, tr_ch, tr_cb, pol_q);
+          tma_load_4d_h(s_g + st * 2 * L::kIn + kb * (kTile * 128), &tm_g, in_full + st, kb * 64, tr.tile(i) * kTile, tr_ch, tr_cb, pol_g);
         }
         armed = i + 1;
       }
@@ -543,7 +549,7 @@ tc_bwd_a_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         umma_commit(in_empty + st);
         // the dS tile as it is -> (the first MP columns of) the dQ tile of the same rows
         for (int kb = 0; kb < MP / 64; ++kb)
-          tma_store_4d_h(&tm_dq, s_ds + kb * (kTile * 128), kb * 64, tr.tile(i) * kTile, (int)(bh % sch.H), (int)(bh / sch.H), pol_ds);
+          tma_store_4d_h(&tm_dq, s_ds + kb * (kTile * 128), kb * 64, tr.tile(i) * kTile, tr_ch, tr_cb, pol_ds);
         tma_store_commit();
         if (i + 1 < count && !front(i + 1)) break;
         // acc_done lets the compute warps overwrite the dS tile: the copy must have read it
@@ -736,6 +742,7 @@ tc_rows_inplace_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_co
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const TileRange tra = tile_range(sch, side_a.order), trb = tile_range(sch, side_b.order);
+  const int tr_ch = tra.ch, tr_cb = tra.cb;
   const int64_t bh = tra.bh;
   const int count = tra.count, total = count + (nsides > 1 ? trb.count : 0);
 
@@ -772,7 +779,7 @@ tc_rows_inplace_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_co
         mbar_expect_tx(in_full + s, L::kIn);
         for (int kb = 0; kb < MP / 64; ++kb)
           tma_load_4d_h(s_in + s * L::kIn + kb * (kTile * 128), second ? &tm_b : &tm_a, in_full + s, kb * 64,
-                        (second ? trb.tile(i - count) : tra.tile(i)) * kTile, (int)(bh % sch.H), (int)(bh / sch.H), second ? pol_b : pol_a);
+                        (second ? trb.tile(i - count) : tra.tile(i)) * kTile, tr_ch, tr_cb, second ? pol_b : pol_a);
         armed = i + 1;
       }
       if (ab.raised())
@@ -879,8 +886,8 @@ tc_rows_inplace_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_co
       named_barrier(1 + g, kGroup);
       if (leader) {
         for (int kb = 0; kb < D / 64; ++kb)
-          tma_store_4d_h(second ? &tm_b : &tm_a, my_out + kb * (kTile * 128), kb * 64, tile * kTile, (int)(bh % sch.H),
-                         (int)(bh / sch.H), second ? pol_ob : pol_oa);
+          tma_store_4d_h(second ? &tm_b : &tm_a, my_out + kb * (kTile * 128), kb * 64, tile * kTile, tr_ch, tr_cb,
+                         second ? pol_ob : pol_oa);
         tma_store_commit();
       }
     }
@@ -954,6 +961,7 @@ tc_bwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const TileRange tr = tile_range(sch);
+  const int tr_ch = tr.ch, tr_cb = tr.cb;
   const int64_t bh = tr.bh;
   const int count = tr.count;
 
@@ -998,11 +1006,11 @@ tc_bwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
         if (!mbar_wait(k_empty + st, ((i >> 1) & 1) ^ 1, ab, 0x2100 + i)) break;
         mbar_expect_tx(k_full + st, L::kIn);
         for (int kb = 0; kb < KBD; ++kb)
-          tma_load_4d_h(s_k + st * L::kIn + kb * (kTile * 128), &tm_k, k_full + st, kb * 64, tr.tile(i) * kTile, (int)(bh % sch.H), (int)(bh / sch.H), pol_k);
+          tma_load_4d_h(s_k + st * L::kIn + kb * (kTile * 128), &tm_k, k_full + st, kb * 64, tr.tile(i) * kTile, tr_ch, tr_cb, pol_k);
         if (!mbar_wait(v_empty, (i & 1) ^ 1, ab, 0x2180 + i)) { armed = -(i + 1); break; }
         mbar_expect_tx(v_full, L::kIn);
         for (int kb = 0; kb < KBD; ++kb)
-          tma_load_4d_h(s_v + kb * (kTile * 128), &tm_v, v_full, kb * 64, tr.tile(i) * kTile, (int)(bh % sch.H), (int)(bh / sch.H), pol_v);
+          tma_load_4d_h(s_v + kb * (kTile * 128), &tm_v, v_full, kb * 64, tr.tile(i) * kTile, tr_ch, tr_cb, pol_v);
         armed = i + 1;
       }
       if (ab.raised()) {
@@ -1045,7 +1053,7 @@ tc_bwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
         // the dS' tile as it is -> dK tile of the same rows (after the products: their commit
         // frees the K stage)
         for (int kb = 0; kb < MP / 64; ++kb)
-          tma_store_4d_h(&tm_dk, s_ds + kb * (kTile * 128), kb * 64, tr.tile(i) * kTile, (int)(bh % sch.H), (int)(bh / sch.H), pol_ds);
+          tma_store_4d_h(&tm_dk, s_ds + kb * (kTile * 128), kb * 64, tr.tile(i) * kTile, tr_ch, tr_cb, pol_ds);
         tma_store_commit();
         // out_full lets the compute warps move on to the next dS' tile: the copy must have read it
         tma_store_wait_read();
@@ -1169,7 +1177,7 @@ tc_bwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
       named_barrier(1, kComputeThreads);
       if (threadIdx.x == 0) {
         for (int kb = 0; kb < KBD; ++kb)
-          tma_store_4d_h(&tm_dv, s_p + kb * (kTile * 128), kb * 64, tr.tile(i) * kTile, (int)(bh % sch.H), (int)(bh / sch.H), pol_dv);
+          tma_store_4d_h(&tm_dv, s_p + kb * (kTile * 128), kb * 64, tr.tile(i) * kTile, tr_ch, tr_cb, pol_dv);
         tma_store_commit();
       }
     }
@@ -1199,10 +1207,11 @@ tc_bwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
 // ------------------------------------------------------------------------------------------
 // Softmax-3 forward (column pass): per-CTA partial of Bmat = softmax(Qt (sK)^T) V with a running
 // reference exponent per landmark.  Thread = row n of the K/V tile and half the landmark columns,
-// so the per-landmark maximum over the tile is a reduction across threads: 31 warp shuffles per
-// thread fold the 32 rows of a warp, shared memory folds the 4 row quarters.  The reference only
-// moves when a tile exceeds it by more than 2^8 (then the TMEM accumulators are rescaled in
-// place), so probabilities stay <= 256 in the 16-bit operand copy and rescales are rare.  Row
+// so the per-landmark maximum over the tile is a reduction across threads (31 warp shuffles per
+// thread fold the 32 rows of a warp, shared memory folds the 4 row quarters).  The reference only
+// moves when a score exceeds it by more than 2^8 (then the TMEM accumulators are rescaled in
+// place), so probabilities stay <= 256 in the 16-bit operand copy, and whether any score does is
+// one compare per element and one barrier with an OR: the maximum is formed for those tiles only.  Row
 // sums come from the tensor core too (P'^T times a block of ones).  S is double-buffered in
 // TMEM and P' in shared memory (a tile's probabilities are written while the previous tile's
 // accumulation still reads its own copy); K and V have separate two-stage rings (K is free
@@ -1242,8 +1251,6 @@ tc_fwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
   float* s_wmax = reinterpret_cast<float*>(s_p + 2 * L::kP);   // [4][MP]
   float* s_ref = s_wmax + 4 * MP;                          // [MP] running reference (log2 domain)
   float* s_fac = s_ref + MP;                               // [MP] rescale factor of this tile
-  float* s_new = s_fac + MP;                               // [MP] scratch
-  int* s_flag = reinterpret_cast<int*>(s_new + MP);        // [3], rotating
   uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(s_wmax) + L::kAux);
   uint64_t* small_full = bars + 0;
   uint64_t* k_full = bars + 1;      // [2]
@@ -1258,6 +1265,7 @@ tc_fwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const TileRange tr = tile_range(sch);
+  const int tr_ch = tr.ch, tr_cb = tr.cb;
   const int64_t bh = tr.bh;
   const int count = tr.count;
 
@@ -1272,7 +1280,6 @@ tc_fwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
     mbar_init(acc_done, 1);
     mbar_init(acc_done + 1, 1);
     *abort_word = 0;
-    s_flag[0] = 0; s_flag[1] = 0; s_flag[2] = 0;
     fence_mbar_init();
   }
   // block of 16-bit ones read by the row-sum MMA (any operand layout reads all-ones from it)
@@ -1307,14 +1314,14 @@ tc_fwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
         if (!mbar_wait(k_empty + st, ((i >> 1) & 1) ^ 1, ab, 0x3100 + i)) break;
         mbar_expect_tx(k_full + st, L::kIn);
         for (int kb = 0; kb < KBD; ++kb)
-          tma_load_4d_h(s_k + st * L::kIn + kb * (kTile * 128), &tm_k, k_full + st, kb * 64, tr.tile(i) * kTile, (int)(bh % sch.H), (int)(bh / sch.H), pol_k);
+          tma_load_4d_h(s_k + st * L::kIn + kb * (kTile * 128), &tm_k, k_full + st, kb * 64, tr.tile(i) * kTile, tr_ch, tr_cb, pol_k);
         TC_TRACE(0, i);
         nk = i + 1;
         const int sv = i % VS;
         if (!mbar_wait(v_empty + sv, ((i / VS) & 1) ^ 1, ab, 0x3180 + i)) break;
         mbar_expect_tx(v_full + sv, L::kIn);
         for (int kb = 0; kb < KBD; ++kb)
-          tma_load_4d_h(s_v + sv * L::kIn + kb * (kTile * 128), &tm_v, v_full + sv, kb * 64, tr.tile(i) * kTile, (int)(bh % sch.H), (int)(bh / sch.H), pol_v);
+          tma_load_4d_h(s_v + sv * L::kIn + kb * (kTile * 128), &tm_v, v_full + sv, kb * 64, tr.tile(i) * kTile, tr_ch, tr_cb, pol_v);
         TC_TRACE(1, i);
         nv = i + 1;
       }
@@ -1391,6 +1398,7 @@ tc_fwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
       fence_proxy_async();
       mbar_arrive_warp(small_full);
     }
+    named_barrier(1, kComputeThreads);   // s_ref is read before the first barrier of the loop
     bool alive = true;
     for (int i = 0; i < count; ++i) {
       const int st = i & 1;
@@ -1400,51 +1408,56 @@ tc_fwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
       if (threadIdx.x == 0) TC_TRACE(5, i);
       __syncwarp();
       tc_fence_after();
-      float s[HC], v[HC];
+      float s[HC];
       ld_cols<HC>(tmem_base + st * MP + lane_base + c0, s);
       tmem_ld_wait();
+      // s <- s - reference.  Does any difference exceed 8 (a score 2^8 above its landmark's
+      // reference)?  One compare per element and one barrier with an OR; the tile maximum is only
+      // formed when one does, from the scores read out of tensor memory again.
+      bool over = false;
 #pragma unroll
-      for (int j = 0; j < HC; ++j) { s[j] = valid ? s[j] : -INFINITY; v[j] = s[j]; }
-      // fold the 32 rows of this warp: afterwards lane L holds columns c0 + CPL*L .. +CPL-1
-#pragma unroll
-      for (int off = 16, cnt = HC / 2; off >= 1; off >>= 1, cnt >>= 1) {
-        const bool upper = (lane & off) != 0;
-#pragma unroll
-        for (int j = 0; j < cnt; ++j) {
-          const float send = upper ? v[j] : v[j + cnt];
-          const float keep = upper ? v[j + cnt] : v[j];
-          v[j] = fmaxf(keep, __shfl_xor_sync(0xffffffffu, send, off));
-        }
+      for (int j = 0; j < HC; j += 4) {
+        const float4 c = *reinterpret_cast<const float4*>(s_ref + c0 + j);
+        s[j + 0] = (valid ? s[j + 0] : -INFINITY) - c.x; s[j + 1] = (valid ? s[j + 1] : -INFINITY) - c.y;
+        s[j + 2] = (valid ? s[j + 2] : -INFINITY) - c.z; s[j + 3] = (valid ? s[j + 3] : -INFINITY) - c.w;
+        over |= (s[j + 0] > 8.f) | (s[j + 1] > 8.f) | (s[j + 2] > 8.f) | (s[j + 3] > 8.f);
       }
-#pragma unroll
-      for (int j = 0; j < CPL; ++j) s_wmax[quarter * MP + c0 + CPL * lane + j] = v[j];
-      if (threadIdx.x == 0) s_flag[(i + 1) % 3] = 0;   // last read two tiles ago
-      named_barrier(1, kComputeThreads);
-      if (threadIdx.x < MP) {
-        const int c = threadIdx.x;
-        const float tmax = fmaxf(fmaxf(s_wmax[c], s_wmax[MP + c]), fmaxf(s_wmax[2 * MP + c], s_wmax[3 * MP + c]));
-        const float old = s_ref[c];
-        s_new[c] = fmaxf(old, tmax);
-        if (c < m && tmax > old + 8.f) s_flag[i % 3] = 1;
-      }
-      named_barrier(1, kComputeThreads);
-      const bool move = s_flag[i % 3] != 0;     // CTA-uniform
+      const bool move = named_barrier_or(1, kComputeThreads, over);     // CTA-uniform
       if (threadIdx.x == 0) TC_TRACE(6, i);
       if (i > 1) {
         // the accumulation of tile i-2 read the P' buffer this tile is about to fill
         if (!mbar_wait(acc_done + st, (uint32_t)((i - 2) >> 1) & 1u, ab, 0x3700 + i)) { alive = false; break; }
         __syncwarp();
       }
-      if (move && i > 0) {
-        // the accumulators are rescaled in place: every accumulation issued so far must be complete
-        if (!mbar_wait(acc_done + (st ^ 1), (uint32_t)((i - 1) >> 1) & 1u, ab, 0x3780 + i)) { alive = false; break; }
-        __syncwarp();
-        tc_fence_after();
-      }
       if (move) {
+        ld_cols<HC>(tmem_base + st * MP + lane_base + c0, s);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < HC; ++j) s[j] = valid ? s[j] : -INFINITY;
+        // fold the 32 rows of this warp in place: afterwards lane L holds columns c0 + CPL*L .. +CPL-1
+#pragma unroll
+        for (int off = 16, cnt = HC / 2; off >= 1; off >>= 1, cnt >>= 1) {
+          const bool upper = (lane & off) != 0;
+#pragma unroll
+          for (int j = 0; j < cnt; ++j) {
+            const float send = upper ? s[j] : s[j + cnt];
+            const float keep = upper ? s[j + cnt] : s[j];
+            s[j] = fmaxf(keep, __shfl_xor_sync(0xffffffffu, send, off));
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < CPL; ++j) s_wmax[quarter * MP + c0 + CPL * lane + j] = s[j];
+        if (i > 0) {
+          // the accumulators are rescaled in place: every accumulation issued so far must be complete
+          if (!mbar_wait(acc_done + (st ^ 1), (uint32_t)((i - 1) >> 1) & 1u, ab, 0x3780 + i)) { alive = false; break; }
+          __syncwarp();
+          tc_fence_after();
+        }
+        named_barrier(1, kComputeThreads);
         if (threadIdx.x < MP) {
           const int c = threadIdx.x;
-          const float old = s_ref[c], nw = s_new[c];
+          const float tmax = fmaxf(fmaxf(s_wmax[c], s_wmax[MP + c]), fmaxf(s_wmax[2 * MP + c], s_wmax[3 * MP + c]));
+          const float old = s_ref[c], nw = fmaxf(old, tmax);
           s_fac[c] = (old == -INFINITY) ? 0.f : fast_exp2(old - nw);
           s_ref[c] = nw;
         }
@@ -1464,15 +1477,18 @@ tc_fwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
           }
           tmem_st_wait();
         }
+        // the scores once more, against the new reference
+        ld_cols<HC>(tmem_base + st * MP + lane_base + c0, s);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < HC; j += 4) {
+          const float4 c = *reinterpret_cast<const float4*>(s_ref + c0 + j);
+          s[j + 0] = (valid ? s[j + 0] : -INFINITY) - c.x; s[j + 1] = (valid ? s[j + 1] : -INFINITY) - c.y;
+          s[j + 2] = (valid ? s[j + 2] : -INFINITY) - c.z; s[j + 3] = (valid ? s[j + 3] : -INFINITY) - c.w;
+        }
       }
 #pragma unroll
-      for (int j = 0; j < HC; j += 4) {
-        const float4 c = *reinterpret_cast<const float4*>(s_ref + c0 + j);
-        s[j + 0] = fast_exp2(s[j + 0] - c.x);
-        s[j + 1] = fast_exp2(s[j + 1] - c.y);
-        s[j + 2] = fast_exp2(s[j + 2] - c.z);
-        s[j + 3] = fast_exp2(s[j + 3] - c.w);
-      }
+      for (int j = 0; j < HC; ++j) s[j] = fast_exp2(s[j]);
       store_cols<T, HC>(s_p + st * L::kP, r, c0, s);
       fence_proxy_async();
       tc_fence_before();
