@@ -26,13 +26,15 @@ constexpr int kTcThreads = 320;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 
-// Optional per-tile timestamps of one CTA (profiling builds only: -DFNB_TC_TRACE).
+// Optional per-tile timestamps of one CTA and per-CTA lifetimes (profiling builds only:
+// -DFNB_TC_TRACE).  g_tc_trace_cta selects (kernel id << 16) | CTA; kernel ids: 0 forward column
+// pass, 1 first backward row pass, 2 backward column pass, 3 in-place pass, 4 output pass.
 #ifdef FNB_TC_TRACE
 __device__ long long g_tc_trace[8][256];
 __device__ int g_tc_trace_cta = 150;
 __device__ unsigned long long g_tc_span[3 * 1024];   // per CTA: SM id, entry and exit time (ns)
-__device__ __forceinline__ void tc_span(int which) {
-  if (threadIdx.x == 0 && blockIdx.x < 1024) {
+__device__ __forceinline__ void tc_span(int which, int kid) {
+  if (threadIdx.x == 0 && blockIdx.x < 1024 && (g_tc_trace_cta >> 16) == kid) {
     if (which == 0) {
       unsigned smid;
       asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
@@ -43,10 +45,10 @@ __device__ __forceinline__ void tc_span(int which) {
     g_tc_span[3 * blockIdx.x + 1 + which] = t;
   }
 }
-#define TC_SPAN(which) tc_span(which)
+#define TC_SPAN(which) tc_span(which, kTraceId)
 #define TC_TRACE(role, idx)                                                                    \
   do {                                                                                         \
-    if (blockIdx.x == g_tc_trace_cta && (idx) < 256) g_tc_trace[role][idx] = clock64();        \
+    if ((int)blockIdx.x + (kTraceId << 16) == g_tc_trace_cta && (idx) < 256) g_tc_trace[role][idx] = clock64(); \
   } while (0)
 #else
 #define TC_TRACE(role, idx) do {} while (0)
@@ -211,6 +213,8 @@ tc_fwd_c_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 const float* __restrict__ k_landmarks, const float* __restrict__ step2,
                 float* __restrict__ lse1, TcSched sch, int m, float scale, int* status) {
   using L = FwdCSmem<D, MP>;
+  constexpr int kTraceId = 4; (void)kTraceId;
+  TC_SPAN(0);
   static_assert((D == 64 && MP == 64) || (D == 128 && (MP == 64 || MP == 128)), "head_dim 64 with up to 64 landmarks, 128 with up to 128");
   constexpr int KBD = D / 64;
   constexpr int kGroup = kComputeThreads / 2;
@@ -399,6 +403,7 @@ tc_fwd_c_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem_base, kTmemCols);
+  TC_SPAN(1);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -429,6 +434,8 @@ tc_bwd_a_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 TcSched sch, int m, float scale, int* status) {
   static_assert((D == 64 && MP == 64) || (D == 128 && (MP == 64 || MP == 128)), "head_dim 64 with up to 64 landmarks, 128 with up to 128");
   using L = BwdASmem<D, MP>;
+  constexpr int kTraceId = 1; (void)kTraceId;
+  TC_SPAN(0);
   constexpr int HC = MP / 2, HD = D / 2, NST = L::kStages;
   constexpr uint32_t kTmemCols = 2 * MP + 2 * D <= 256 ? 256 : 512;    // S, dP, and 2 D accumulator columns
   extern __shared__ uint8_t smem_raw[];
@@ -494,6 +501,7 @@ tc_bwd_a_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           tma_load_4d_h(s_q + st * 2 * L::kIn + kb * (kTile * 128), &tm_q, in_full + st, kb * 64, tr.tile(i) * kTile, tr_ch, tr_cb, pol_q);
           tma_load_4d_h(s_g + st * 2 * L::kIn + kb * (kTile * 128), &tm_g, in_full + st, kb * 64, tr.tile(i) * kTile, tr_ch, tr_cb, pol_g);
         }
+        TC_TRACE(0, i);
         armed = i + 1;
       }
       if (ab.raised())
@@ -509,6 +517,7 @@ tc_bwd_a_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       auto front = [&](int i) -> bool {
         const int st = i % NST;
         if (!mbar_wait(in_full + st, (i / NST) & 1, ab, 0x1300 + i)) return false;
+        TC_TRACE(1, i);
         tc_fence_after();
         const uint32_t a_q = smem_u32(s_q + st * 2 * L::kIn), a_g = smem_u32(s_g + st * 2 * L::kIn);
 #pragma unroll
@@ -522,6 +531,7 @@ tc_bwd_a_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       ok = ok && front(0);
       for (int i = 0; ok && i < count; ++i) {
         if (!mbar_wait(pds_full, i & 1, ab, 0x1400 + i)) break;
+        TC_TRACE(2, i);
         tc_fence_after();
         const int st = i % NST;
         // One 128 x 2D accumulator for both sums: [P | dS]^T [Q | dO] (both operands MN-major; the
@@ -551,6 +561,7 @@ tc_bwd_a_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         for (int kb = 0; kb < MP / 64; ++kb)
           tma_store_4d_h(&tm_dq, s_ds + kb * (kTile * 128), kb * 64, tr.tile(i) * kTile, tr_ch, tr_cb, pol_ds);
         tma_store_commit();
+        TC_TRACE(3, i);
         if (i + 1 < count && !front(i + 1)) break;
         // acc_done lets the compute warps overwrite the dS tile: the copy must have read it
         tma_store_wait_read();
@@ -576,6 +587,7 @@ tc_bwd_a_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const bool valid = row < sch.N;
       const float lse = valid ? lse1[bh * sch.N + row] * kLog2e : 0.f;
       if (!mbar_wait(sdp_full, i & 1, ab, 0x1600 + i)) { alive = false; break; }
+      if (threadIdx.x == 0) TC_TRACE(4, i);
       __syncwarp();
       tc_fence_after();
       float p[HC], g[HC];
@@ -590,8 +602,10 @@ tc_bwd_a_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         d4[j & 3] = fmaf(p[j], g[j], d4[j & 3]);
       }
       const float dpart = (d4[0] + d4[1]) + (d4[2] + d4[3]);
+      if (threadIdx.x == 0) TC_TRACE(5, i);
       // the previous tile's P / dS are still being read by its accumulation MMAs and its dS copy
       if (i > 0 && !mbar_wait(acc_done, (i - 1) & 1, ab, 0x1700 + i)) { alive = false; break; }
+      if (threadIdx.x == 0) TC_TRACE(6, i);
       __syncwarp();
       s_x[h * kTile + r] = dpart;
       named_barrier(1, kComputeThreads);
@@ -606,6 +620,7 @@ tc_bwd_a_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       fence_proxy_async();
       tc_fence_before();
       mbar_arrive_warp(pds_full);
+      if (threadIdx.x == 0) TC_TRACE(7, i);
     }
     if (alive && mbar_wait(acc_done, (count - 1) & 1, ab, 0x1900)) {
       __syncwarp();
@@ -648,6 +663,7 @@ tc_bwd_a_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem_base, kTmemCols);
+  TC_SPAN(1);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -714,6 +730,8 @@ tc_rows_inplace_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_co
                        RowsSide side_a, RowsSide side_b, int nsides, float op_mul, TcSched sch, int m,
                        int* status) {
   using L = RowsSmem<D, MP>;
+  constexpr int kTraceId = 3; (void)kTraceId;
+  TC_SPAN(0);
   // a parked dS tile (MP columns) sits in the first MP columns of the gradient tile of its rows
   static_assert((D == 64 && MP == 64) || (D == 128 && (MP == 64 || MP == 128)), "head_dim 64 with up to 64 landmarks, 128 with up to 128");
   constexpr int kGroup = kComputeThreads / 2;
@@ -896,6 +914,7 @@ tc_rows_inplace_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_co
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem_base, kTmemCols);
+  TC_SPAN(1);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -930,10 +949,13 @@ tc_bwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
                 float* __restrict__ partB, float* __restrict__ tile_scale, TcSched sch, int m, float scale, int kshift,
                 int* status) {
   using L = BwdBSmem<D, MP>;
+  constexpr int kTraceId = 2; (void)kTraceId;
+  TC_SPAN(0);
   constexpr int KBD = D / 64, HC = MP / 2, HD = D / 2;
   constexpr int W = MP > D ? MP : D;
-  constexpr uint32_t kCols = 2 * W + D;
+  constexpr uint32_t kCols = 2 * W + 2 * D;   // S, dP, the dQt accumulator, dV
   constexpr uint32_t kTmemCols = kCols <= 256 ? 256 : 512;
+  static_assert(kCols <= 512, "tensor memory");
   extern __shared__ uint8_t smem_raw[];
   pdl_trigger();
   uint8_t* base = align1024(smem_raw);
@@ -953,8 +975,8 @@ tc_bwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
   uint64_t* v_empty = bars + 6;
   uint64_t* sdp_full = bars + 7;
   uint64_t* pds_full = bars + 8;
-  uint64_t* out_full = bars + 9;
-  uint64_t* o_free = bars + 10;
+  uint64_t* out_full = bars + 9;    // the products of a tile are complete
+  uint64_t* ds_free = bars + 10;    // the copy of a tile's dS' has read the shared-memory tile
   unsigned* s_tmax = reinterpret_cast<unsigned*>(bars + 12);   // [2]: largest |dS'| of a tile (float bits), by tile parity
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
   int* abort_word = reinterpret_cast<int*>(tmem_slot + 1);
@@ -972,7 +994,7 @@ tc_bwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
     mbar_init(sdp_full, 1);
     mbar_init(pds_full, kComputeThreads / 32);
     mbar_init(out_full, 1);
-    mbar_init(o_free, kComputeThreads / 32);
+    mbar_init(ds_free, 1);
     *abort_word = 0;
     s_tmax[0] = 0; s_tmax[1] = 0;
     fence_mbar_init();
@@ -987,7 +1009,7 @@ tc_bwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
   pdl_wait();   // everything above overlaps the tail of the previous kernel of the stream
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tmem_s = tmem_base, tmem_dp = tmem_base + W, tmem_acc = tmem_base + 2 * W;
-  const uint32_t tmem_dv = tmem_s;
+  const uint32_t tmem_dv = tmem_acc + D;   // columns of its own: the scores of the next tile are formed while dV is read
   Abort ab{abort_word, status};
 
   if (warp == kProducerWarp) {
@@ -1027,21 +1049,30 @@ tc_bwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
       const uint32_t a_qt = smem_u32(s_qt), a_do3 = smem_u32(s_do3), a_v = smem_u32(s_v), a_p = smem_u32(s_p),
                      a_ds = smem_u32(s_ds);
       const uint64_t pol_ds = l2_policy_of(sch.hint, 2);
-      bool ok = mbar_wait(small_full, 0, ab, 0x2200);
-      for (int i = 0; ok && i < count; ++i) {
+      // S and dP of tile i (their tensor-memory columns are free once the compute warps have read
+      // those of tile i - 1, which they have when they hand over its P' and dS')
+      auto front = [&](int i) -> bool {
         const int st = i & 1;
-        const uint32_t a_k = smem_u32(s_k + st * L::kIn);
-        if (!mbar_wait(k_full + st, (i >> 1) & 1, ab, 0x2300 + i)) break;
-        if (!mbar_wait(v_full, i & 1, ab, 0x2340 + i)) break;
-        if (!mbar_wait(o_free, (i & 1) ^ 1, ab, 0x2380 + i)) break;   // dV aliases S
+        if (!mbar_wait(k_full + st, (i >> 1) & 1, ab, 0x2300 + i)) return false;
+        if (!mbar_wait(v_full, i & 1, ab, 0x2340 + i)) return false;
+        TC_TRACE(1, i);
         tc_fence_after();
+        const uint32_t a_k = smem_u32(s_k + st * L::kIn);
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) umma(tmem_s, kdesc(a_k, k, kTile), kdesc(a_qt, k, MP), idesc_s, k > 0);
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) umma(tmem_dp, kdesc(a_v, k, kTile), kdesc(a_do3, k, MP), idesc_s, k > 0);
         umma_commit(v_empty);
         umma_commit(sdp_full);
+        return true;
+      };
+      bool ok = mbar_wait(small_full, 0, ab, 0x2200);
+      ok = ok && front(0);
+      for (int i = 0; ok && i < count; ++i) {
+        const int st = i & 1;
+        const uint32_t a_k = smem_u32(s_k + st * L::kIn);
         if (!mbar_wait(pds_full, i & 1, ab, 0x2400 + i)) break;
+        TC_TRACE(2, i);
         tc_fence_after();
 #pragma unroll
         for (int k = 0; k < MP / 16; ++k)
@@ -1050,14 +1081,17 @@ tc_bwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
         for (int k = 0; k < kTile / 16; ++k)
           umma(tmem_acc, mndesc(a_ds, k), mndesc(a_k, k), idesc_acc, (i > 0 || k > 0));
         umma_commit(k_empty + st);
-        // the dS' tile as it is -> dK tile of the same rows (after the products: their commit
-        // frees the K stage)
+        umma_commit(out_full);
+        // the dS' tile as it is -> dK tile of the same rows
         for (int kb = 0; kb < MP / 64; ++kb)
           tma_store_4d_h(&tm_dk, s_ds + kb * (kTile * 128), kb * 64, tr.tile(i) * kTile, tr_ch, tr_cb, pol_ds);
         tma_store_commit();
-        // out_full lets the compute warps move on to the next dS' tile: the copy must have read it
+        // the scores of the next tile run while the compute warps take this tile's dV out
+        if (i + 1 < count && !front(i + 1)) break;
+        // ds_free lets the compute warps write the next dS' tile: the copy must have read this one
         tma_store_wait_read();
-        umma_commit(out_full);
+        TC_TRACE(3, i);
+        mbar_arrive(ds_free);
       }
       tma_store_wait_all();
     }
@@ -1085,6 +1119,7 @@ tc_bwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
       const int64_t row = (int64_t)tr.tile(i) * kTile + r;
       const bool valid = row < sch.N;
       if (!mbar_wait(sdp_full, i & 1, ab, 0x2600 + i)) { alive = false; break; }
+      if (threadIdx.x == 0) TC_TRACE(4, i);
       __syncwarp();
       tc_fence_after();
       float p[HC], g[HC];
@@ -1120,9 +1155,12 @@ tc_bwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
       }
       // the staging copies of the previous tile's dV / dK share these buffers
       if (threadIdx.x == 0) {
+        TC_TRACE(0, i);
         tma_store_wait_read();
         s_tmax[(i + 1) & 1] = 0;   // read for the last time before the previous tile's second barrier
       }
+      // ... and the copy of the previous dS' tile must have read it
+      if (i > 0 && !mbar_wait(ds_free, (i - 1) & 1, ab, 0x2700 + i)) { alive = false; break; }
       named_barrier(1, kComputeThreads);
       if (std::is_same<T, __half>::value) {
         const float tmax = __uint_as_float(s_tmax[i & 1]);   // CTA-uniform, already times frun
@@ -1153,6 +1191,7 @@ tc_bwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
         }
       }
       if (threadIdx.x == 0 && tile_scale) tile_scale[bh * total_tiles + tr.tile(i)] = 1.f / frun;
+      if (threadIdx.x == 0) TC_TRACE(5, i);
       store_cols<T, HC>(s_p, r, c0, p);
       store_cols<T, HC>(s_ds, r, c0, g);
       fence_proxy_async();
@@ -1160,13 +1199,12 @@ tc_bwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
       mbar_arrive_warp(pds_full);
 
       if (!mbar_wait(out_full, i & 1, ab, 0x2800 + i)) { alive = false; break; }
+      if (threadIdx.x == 0) TC_TRACE(6, i);
       __syncwarp();
       tc_fence_after();
       float o[HD];
       ld_cols<HD>(tmem_dv + lane_base + h * HD, o);
       tmem_ld_wait();
-      tc_fence_before();
-      mbar_arrive_warp(o_free);
       const float vmul = dsc * unshift;
 #pragma unroll
       for (int j = 0; j < HD; ++j) o[j] *= vmul;
@@ -1179,6 +1217,7 @@ tc_bwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
         for (int kb = 0; kb < KBD; ++kb)
           tma_store_4d_h(&tm_dv, s_p + kb * (kTile * 128), kb * 64, tr.tile(i) * kTile, tr_ch, tr_cb, pol_dv);
         tma_store_commit();
+        TC_TRACE(7, i);
       }
     }
     if (threadIdx.x == 0) tma_store_wait_all();
@@ -1202,6 +1241,7 @@ tc_bwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem_base, kTmemCols);
+  TC_SPAN(1);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -1233,6 +1273,7 @@ tc_fwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
                 float* __restrict__ part_max, float* __restrict__ part_sum, TcSched sch, int m,
                 int* status) {
   using L = FwdBSmem<D, MP>;
+  constexpr int kTraceId = 0; (void)kTraceId;
   TC_SPAN(0);
   constexpr int KBD = D / 64, HC = MP / 2;
   constexpr int CPL = HC / 32;                 // columns per lane after the warp fold
