@@ -73,7 +73,7 @@ def hbm_peak():
 def ncu_traffic(kernel):
     """DRAM bytes per launch of `kernel` (dram__bytes_read.sum + dram__bytes_write.sum) from the
     table of the committed ncu summary of this workload, if it is there."""
-    path = os.path.join(ROOT, "profiles", "step_config3_kernels.md")
+    path = os.path.join(ROOT, "profiles", "step_config3_dram_traffic.md")
     try:
         with open(path) as f:
             for line in f:

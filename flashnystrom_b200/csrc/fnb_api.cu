@@ -1207,7 +1207,7 @@ __attribute__((visibility("default"))) int fnb_debug_gemm_cycles(unsigned long l
   return cudaMemcpyFromSymbol(out, g_gemm_cycles, sizeof(unsigned long long) * 8) == cudaSuccess ? 0 : -1;
 }
 __attribute__((visibility("default"))) int fnb_debug_tc_span(unsigned long long* out) {
-  return cudaMemcpyFromSymbol(out, tc::g_tc_span, sizeof(unsigned long long) * 3 * 1024) == cudaSuccess ? 0 : -1;
+  return cudaMemcpyFromSymbol(out, tc::g_tc_span, sizeof(unsigned long long) * 6 * 1024) == cudaSuccess ? 0 : -1;
 }
 #endif
 

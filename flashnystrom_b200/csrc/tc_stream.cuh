@@ -32,17 +32,18 @@ constexpr float kLn2 = 0.6931471805599453f;
 #ifdef FNB_TC_TRACE
 __device__ long long g_tc_trace[8][256];
 __device__ int g_tc_trace_cta = 150;
-__device__ unsigned long long g_tc_span[3 * 1024];   // per CTA: SM id, entry and exit time (ns)
+__device__ unsigned long long g_tc_span[6 * 1024];   // per CTA: SM id, times (ns) of entry, exit, dependency wait over,
+                                                     // first tile done, last tile done
 __device__ __forceinline__ void tc_span(int which, int kid) {
   if (threadIdx.x == 0 && blockIdx.x < 1024 && (g_tc_trace_cta >> 16) == kid) {
     if (which == 0) {
       unsigned smid;
       asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
-      g_tc_span[3 * blockIdx.x] = smid;
+      g_tc_span[6 * blockIdx.x] = smid;
     }
     unsigned long long t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    g_tc_span[3 * blockIdx.x + 1 + which] = t;
+    g_tc_span[6 * blockIdx.x + 1 + which] = t;
   }
 }
 #define TC_SPAN(which) tc_span(which, kTraceId)
@@ -114,16 +115,31 @@ __device__ __forceinline__ uint64_t mndesc(uint32_t base, int k) {
 // slice straight from their FP32 originals (MP rows, rows >= m zero; D / 64 blocks of
 // [MP rows x 128 B] each):
 //   tile_a = mul_a * A,   tile_b = B / sc  with sc the power of two >= max |B|   (returned).
-// 256 / MP threads share a row; each packs D MP / 256 consecutive columns, eight at a time (B is read
-// twice, once for its maximum).  scratch: 8 floats of shared memory; named barrier 3 is used once.
+// 256 / MP threads share a row; each packs D MP / 256 consecutive columns, eight at a time.  scratch: 8 floats of shared memory; named barrier 3 is used once.
 // The caller fences and signals the MMA thread.
 template <class T, int D, int MP>
 __device__ __forceinline__ float pack_landmark_operands(uint8_t* tile_a, uint8_t* tile_b, const float* A,
                                                         const float* B, int m, float mul_a, float* scratch) {
   constexpr int TPR = kComputeThreads / MP, CPT = D / TPR;
   const int t = threadIdx.x, r = t / TPR, c0 = (t % TPR) * CPT;
+  // up to 32 columns per thread: both row segments stay in registers between the maximum and the
+  // packing (one trip to the L2 instead of two); wider segments are read again
+  constexpr bool kKeep = CPT <= 32;
+  float4 xa[kKeep ? CPT / 4 : 1], yb[kKeep ? CPT / 4 : 1];
   float amax = 0.f;
-  if (r < m) {
+  if (kKeep) {
+#pragma unroll
+    for (int q = 0; q < CPT / 4; ++q) {
+      xa[q] = yb[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (r < m) {
+        xa[q] = *reinterpret_cast<const float4*>(A + r * D + c0 + 4 * q);
+        yb[q] = *reinterpret_cast<const float4*>(B + r * D + c0 + 4 * q);
+      }
+    }
+#pragma unroll
+    for (int q = 0; q < CPT / 4; ++q)
+      amax = fmaxf(fmaxf(amax, fmaxf(fabsf(yb[q].x), fabsf(yb[q].y))), fmaxf(fabsf(yb[q].z), fabsf(yb[q].w)));
+  } else if (r < m) {
 #pragma unroll
     for (int q = 0; q < CPT / 4; ++q) {
       const float4 y = *reinterpret_cast<const float4*>(B + r * D + c0 + 4 * q);
@@ -140,7 +156,9 @@ __device__ __forceinline__ float pack_landmark_operands(uint8_t* tile_a, uint8_t
 #pragma unroll
   for (int c = 0; c < CPT / 8; ++c) {
     float4 x0 = make_float4(0.f, 0.f, 0.f, 0.f), x1 = x0, y0 = x0, y1 = x0;
-    if (r < m) {
+    if (kKeep) {
+      x0 = xa[kKeep ? 2 * c : 0]; x1 = xa[kKeep ? 2 * c + 1 : 0]; y0 = yb[kKeep ? 2 * c : 0]; y1 = yb[kKeep ? 2 * c + 1 : 0];
+    } else if (r < m) {
       x0 = *reinterpret_cast<const float4*>(A + r * D + c0 + 8 * c);
       x1 = *reinterpret_cast<const float4*>(A + r * D + c0 + 8 * c + 4);
       y0 = *reinterpret_cast<const float4*>(B + r * D + c0 + 8 * c);
@@ -261,6 +279,7 @@ tc_fwd_c_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   pdl_wait();   // everything above overlaps the tail of the previous kernel of the stream
+  TC_SPAN(2);
   const uint32_t tmem_base = *tmem_slot;
   Abort ab{abort_word, status};
 
@@ -332,6 +351,7 @@ tc_fwd_c_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const uint64_t pol_o = leader ? l2_policy_of(sch.hint, 2) : 0ull;
     const bool full_m = m == MP;
     for (int i = g; i < count; i += 2) {
+      if (i == 2) TC_SPAN(3);
       const uint32_t par = (uint32_t)(i >> 1) & 1u;
       if (!mbar_wait(s_full + g, par, ab, 0x600 + i)) break;
       __syncwarp();
@@ -398,6 +418,7 @@ tc_fwd_c_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         tma_store_commit();
       }
     }
+    TC_SPAN(4);
     if (leader) tma_store_wait_all();
   }
   tc_fence_before();
@@ -484,6 +505,7 @@ tc_bwd_a_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   pdl_wait();   // everything above overlaps the tail of the previous kernel of the stream
+  TC_SPAN(2);
   const uint32_t tmem_base = *tmem_slot;
   Abort ab{abort_word, status};
 
@@ -583,6 +605,7 @@ tc_bwd_a_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const int c0 = h * HC;
     bool alive = true;
     for (int i = 0; i < count; ++i) {
+      if (i == 1) TC_SPAN(3);
       const int64_t row = (int64_t)tr.tile(i) * kTile + r;
       const bool valid = row < sch.N;
       const float lse = valid ? lse1[bh * sch.N + row] * kLog2e : 0.f;
@@ -622,6 +645,7 @@ tc_bwd_a_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       mbar_arrive_warp(pds_full);
       if (threadIdx.x == 0) TC_TRACE(7, i);
     }
+    TC_SPAN(4);
     if (alive && mbar_wait(acc_done, (count - 1) & 1, ab, 0x1900)) {
       __syncwarp();
       tc_fence_after();
@@ -781,6 +805,7 @@ tc_rows_inplace_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_co
   __syncthreads();
   tc_fence_after();
   pdl_wait();   // everything above overlaps the tail of the previous kernel of the stream
+  TC_SPAN(2);
   const uint32_t tmem_base = *tmem_slot;
   Abort ab{abort_word, status};
 
@@ -866,6 +891,7 @@ tc_rows_inplace_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_co
     if (side_a.part || (nsides > 1 && side_b.part))
       named_barrier(3, kComputeThreads);   // the stores above are visible to the CTA's epilogue reads
     for (int i = g; i < total; i += 2) {
+      if (i == 2) TC_SPAN(3);
       const int s = i % kStages;
       const uint32_t par = (uint32_t)(i / kStages) & 1u;
       const bool second = i >= count;
@@ -909,6 +935,7 @@ tc_rows_inplace_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_co
         tma_store_commit();
       }
     }
+    TC_SPAN(4);
     if (leader) tma_store_wait_all();
   }
   tc_fence_before();
@@ -1007,6 +1034,7 @@ tc_bwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   pdl_wait();   // everything above overlaps the tail of the previous kernel of the stream
+  TC_SPAN(2);
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tmem_s = tmem_base, tmem_dp = tmem_base + W, tmem_acc = tmem_base + 2 * W;
   const uint32_t tmem_dv = tmem_acc + D;   // columns of its own: the scores of the next tile are formed while dV is read
@@ -1116,6 +1144,7 @@ tc_bwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
     float frun = 1.f, dscf = dsc;
     const int64_t total_tiles = (sch.N + kTile - 1) / kTile;
     for (int i = 0; i < count; ++i) {
+      if (i == 1) TC_SPAN(3);
       const int64_t row = (int64_t)tr.tile(i) * kTile + r;
       const bool valid = row < sch.N;
       if (!mbar_wait(sdp_full, i & 1, ab, 0x2600 + i)) { alive = false; break; }
@@ -1220,6 +1249,7 @@ tc_bwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
         TC_TRACE(7, i);
       }
     }
+    TC_SPAN(4);
     if (threadIdx.x == 0) tma_store_wait_all();
     if (alive) {
       // out_full of the last tile was waited above, so the accumulator is final
@@ -1335,6 +1365,7 @@ tc_fwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   pdl_wait();   // everything above overlaps the tail of the previous kernel of the stream
+  TC_SPAN(2);
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tmem_acc = tmem_base + 2 * MP;   // D accumulator columns, then 32 for the row sums
   Abort ab{abort_word, status};
@@ -1442,6 +1473,7 @@ tc_fwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
     named_barrier(1, kComputeThreads);   // s_ref is read before the first barrier of the loop
     bool alive = true;
     for (int i = 0; i < count; ++i) {
+      if (i == 1) TC_SPAN(3);
       const int st = i & 1;
       const int64_t row = (int64_t)tr.tile(i) * kTile + r;
       const bool valid = row < sch.N;
@@ -1536,6 +1568,7 @@ tc_fwd_b_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
       mbar_arrive_warp(p_full + st);
       if (threadIdx.x == 0) TC_TRACE(7, i);
     }
+    TC_SPAN(4);
     if (alive && mbar_wait(acc_done + ((count - 1) & 1), (uint32_t)((count - 1) >> 1) & 1u, ab, 0x3900)) {
       __syncwarp();
       tc_fence_after();
