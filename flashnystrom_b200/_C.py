@@ -136,8 +136,8 @@ def check_device_status(device=None):
             code = (val >> 24) & 0xff
             what = {1: "a device-side wait timed out",
                     2: "a kernel's shared-memory window was misaligned",
-                    3: "a softmax-Jacobian value left the fp16 range in the backward and was clamped "
-                       "(use bf16 inputs or scale the incoming gradient down)"}.get(code, "a kernel reported an error")
+                    3: "a non-finite softmax-Jacobian value reached the backward column pass "
+                       "(inf / NaN in the inputs or the incoming gradient)"}.get(code, "a kernel reported an error")
             raise RuntimeError(f"flashnystrom_b200: {what} on cuda:{idx} "
                                f"(status 0x{val & 0xffffffff:08x}); results of that call are invalid")
 

@@ -18,7 +18,7 @@ namespace tc {
 constexpr uint64_t kWaitLimitNs = 1500000000ull;  // 1.5 s per wait
 constexpr int kStatusTimeout = 1;   // a bounded wait ran out
 constexpr int kStatusSmemAlign = 2; // the dynamic shared-memory window is not 1024-byte aligned
-constexpr int kStatusRange = 3;     // a 16-bit operand copy left the fp16 range and was clamped
+constexpr int kStatusRange = 3;     // a non-finite value met the fp16 range rescaling of the backward column pass
 // The limit every bounded wait uses; a test shortens it through fnb_debug_set_wait_limit_ms.
 __device__ unsigned long long g_wait_limit_ns = kWaitLimitNs;
 

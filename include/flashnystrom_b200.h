@@ -107,9 +107,9 @@ typedef struct fnb_fwd_args {
                                1  a bounded device-side wait ran out (results invalid; the
                                   kernel released its resources and returned)
                                2  the kernel's shared-memory window was not 1024-byte aligned
-                               3  fp16 only: a softmax-Jacobian value left the fp16 range in the
-                                  backward column pass and was clamped (dK, dQ saturated;
-                                  bf16 and fp32 inputs cannot hit this)
+                               3  fp16 only: a non-finite softmax-Jacobian value met the range
+                                  rescaling of the backward column pass (inf / NaN in the
+                                  inputs or in dO; the values go through as they are)
                              The library never synchronises, so it cannot return
                              FNB_ERR_DEVICE_STATUS itself: the host reads the word after the
                              stream has drained (the Python shim's check_device_status). */

@@ -1,8 +1,9 @@
 """The device status word: what the host sees when a kernel could not finish its work the ordinary
 way.  Nothing here faults, traps or hangs the GPU: the expiry test makes a bounded wait run out (one
 CTA is told never to issue one copy, the wait limit is shortened to a few milliseconds) and the
-kernel then leaves through its normal teardown; the range test feeds fp16 a softmax-3 so peaked that
-a 16-bit operand copy would overflow, which the kernel clamps and reports."""
+kernel then leaves through its normal teardown; the range tests feed fp16 a softmax-3 so peaked (and a
+dO so large) that a fixed scaling of the 16-bit dS' tiles would overflow: the kernel rescales per tile
+and the gradients stay within the bars."""
 import pytest
 import torch
 
