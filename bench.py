@@ -294,6 +294,32 @@ def _fwd_bwd_fn(q, k, v, dO, m, J, kappa):
     return fn
 
 
+def _graph_replay_ms(fn, dev, timed, steps, warmup):
+    """Device ms per call of fn replayed from a CUDA graph (the library allocates nothing and never
+    synchronises, so a caller may capture it), or None where capture is not available."""
+    import torch
+    try:
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                fn()
+        torch.cuda.current_stream(dev).wait_stream(side)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            fn()
+        for _ in range(max(3, warmup)):
+            g.replay()
+        torch.cuda.synchronize()
+        ms, _ = timed(g.replay, steps)
+        del g
+        return ms
+    except Exception:
+        torch.cuda.synchronize()
+        return None
+
+
 def _device_inputs(shape, dev, seed, dtype):
     import torch
     g = torch.Generator(device=dev).manual_seed(seed)
@@ -313,9 +339,13 @@ def sharded_leg(dev, rank, world, w, steps, warmup, timed, peak, ms_full):
     fn = _fwd_bwd_fn(q, k, v, dO, m, J, w["kappa_star"])
     for _ in range(warmup):
         fn()
-    ms, host_ms = timed(fn, steps)
+    ms_eager, host_ms = timed(fn, steps)
+    # every rank must take the same path through timed() (it holds collectives)
+    ms_graph = _graph_replay_ms(fn, dev, timed, steps, warmup) if os.environ.get("FNB_BENCH_GRAPH", "1") == "1" else None
+    ms = ms_graph if ms_graph is not None and ms_graph < ms_eager else ms_eager
     total_bytes = 11 * B * H * N * D * 2
     return {"heads_per_gpu": hl, "ms_per_step": ms, "tokens_per_s": B * N / (ms * 1e-3),
+            "eager_ms_per_step": ms_eager, "graph_ms_per_step": ms_graph,
             "host_enqueue_ms_per_step": host_ms, "scaling": "strong",
             "frac_of_11_pass": total_bytes / world / (ms * 1e-3) / 1e9 / peak,
             "efficiency_vs_full_workload_on_one_gpu": (ms_full / world) / ms}
@@ -433,9 +463,13 @@ def extra_configs(dev, steps, warmup, timed, peak):
         fn = _fwd_bwd_fn(q, k, v, dO, m, J, kap)
         for _ in range(3):
             fn()
-        ms, host_ms = timed(fn, n)
+        ms_eager, host_ms = timed(fn, n)
+        # small shapes are bound by the host's enqueue time when launched eagerly: the captured step too
+        ms_graph = _graph_replay_ms(fn, dev, timed, n, 3) if os.environ.get("FNB_BENCH_GRAPH", "1") == "1" else None
+        ms = ms_graph if ms_graph is not None and ms_graph < ms_eager else ms_eager
         B, H, N, D = shape
         out[name] = {"shape": f"B={B},H={H},N={N},D={D},m={m},J={J},kappa*={kap} fp16", "ms_per_step": ms,
+                     "eager_ms_per_step": ms_eager, "graph_ms_per_step": ms_graph,
                      "tokens_per_s": B * N / (ms * 1e-3), "host_enqueue_ms_per_step": host_ms,
                      "frac_of_11_pass": 11 * B * H * N * D * 2 / (ms * 1e-3) / 1e9 / peak,
                      "path": "tensor cores" if ((D == 64 and m <= 64) or (D == 128 and m <= 128)) else "CUDA cores"}
@@ -703,7 +737,7 @@ def main():
         del q, k, v, dO
         torch.cuda.empty_cache()
         if world > 1:
-            sharded = sharded_leg(dev, rank, world, w, steps, warmup, timed, peak, ms_eager)
+            sharded = sharded_leg(dev, rank, world, w, steps, warmup, timed, peak, ms_step)
             seqpar = seqpar_leg(dev, rank, world, SEQPAR, steps, warmup, timed, peak)
         else:
             extras = extra_configs(dev, steps, warmup, timed, peak)
