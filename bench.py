@@ -458,8 +458,10 @@ def extra_configs(dev, steps, warmup, timed, peak):
         "reference_table_D128_N65536": ((4, 16, 65536, 128), 64, 6, 5.0),
         "reference_table_D64_m32_N65536": ((1, 4, 65536, 64), 32, 6, 5.0),
     }
+    dtypes = {"config3_bf16": torch.bfloat16}
+    cases["config3_bf16"] = ((1, 16, 65536, 64), 64, 6, 0.0)   # the bench workload with bf16 tensors
     for name, (shape, m, J, kap) in cases.items():
-        q, k, v, dO = _device_inputs(shape, dev, 7, torch.float16)
+        q, k, v, dO = _device_inputs(shape, dev, 7, dtypes.get(name, torch.float16))
         fn = _fwd_bwd_fn(q, k, v, dO, m, J, kap)
         for _ in range(3):
             fn()
@@ -468,7 +470,8 @@ def extra_configs(dev, steps, warmup, timed, peak):
         ms_graph = _graph_replay_ms(fn, dev, timed, n, 3) if os.environ.get("FNB_BENCH_GRAPH", "1") == "1" else None
         ms = ms_graph if ms_graph is not None and ms_graph < ms_eager else ms_eager
         B, H, N, D = shape
-        out[name] = {"shape": f"B={B},H={H},N={N},D={D},m={m},J={J},kappa*={kap} fp16", "ms_per_step": ms,
+        out[name] = {"shape": f"B={B},H={H},N={N},D={D},m={m},J={J},kappa*={kap} " + ("bf16" if name in dtypes else "fp16"),
+                     "ms_per_step": ms,
                      "eager_ms_per_step": ms_eager, "graph_ms_per_step": ms_graph,
                      "tokens_per_s": B * N / (ms * 1e-3), "host_enqueue_ms_per_step": host_ms,
                      "frac_of_11_pass": 11 * B * H * N * D * 2 / (ms * 1e-3) / 1e9 / peak,

@@ -469,7 +469,7 @@ static int forward_impl(const fnb_fwd_args& a, const Plan& p, const FwdWs& w, in
     const size_t mid_smem = mp.use_tc ? kTcGemmSmem : 0;
     if (mp.use_tc)
       if (int rc = set_smem(mid_fwd_kernel, mid_smem, max_smem, "mid_fwd")) return rc;
-    mid_fwd_kernel<<<(unsigned)p.BH, kThreads, mid_smem, st>>>(mp);
+    mid_fwd_kernel<<<(unsigned)p.BH, mp.use_tc ? kMidTcThreads : kThreads, mid_smem, st>>>(mp);
     if (L.end("mid_fwd")) return L.status;
   }
 
@@ -780,7 +780,7 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
       const size_t mid_smem = mp.use_tc ? kTcGemmSmem : 0;
       if (mp.use_tc)
         if (int rc = set_smem(mid_bwd_kernel, mid_smem, max_smem, "mid_bwd")) return rc;
-      mid_bwd_kernel<<<(unsigned)p.BH, kThreads, mid_smem, st>>>(mp);
+      mid_bwd_kernel<<<(unsigned)p.BH, (mp.use_tc && !mp.first_half_only) ? kMidTcThreads : kThreads, mid_smem, st>>>(mp);
     }
     if (L.end("mid_bwd")) return L.status;
     if (use_tc) {
@@ -1114,7 +1114,7 @@ int fnb_debug_pinv_forward(int64_t bh, int32_t m, int32_t J, float kappa, const 
     const int use_tc = ns_on_tensor_cores(0) ? 1 : 0;
     if (use_tc)
       FNB_CUDA(cudaFuncSetAttribute(pinv_fwd_debug_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcGemmSmem));
-    pinv_fwd_debug_kernel<<<(unsigned)bh, kThreads, use_tc ? kTcGemmSmem : 0, (cudaStream_t)stream>>>(
+    pinv_fwd_debug_kernel<<<(unsigned)bh, use_tc ? kMidTcThreads : kThreads, use_tc ? kTcGemmSmem : 0, (cudaStream_t)stream>>>(
         k2, ns_iterates, k2_inv, (float*)workspace, m, J, kappa, use_tc);
   }
   FNB_CUDA(cudaPeekAtLastError());
@@ -1142,7 +1142,7 @@ int fnb_debug_pinv_backward(int64_t bh, int32_t m, int32_t J, float kappa, const
     const int use_tc = ns_on_tensor_cores(0) ? 1 : 0;
     if (use_tc)
       FNB_CUDA(cudaFuncSetAttribute(pinv_bwd_debug_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcGemmSmem));
-    pinv_bwd_debug_kernel<<<(unsigned)bh, kThreads, use_tc ? kTcGemmSmem : 0, (cudaStream_t)stream>>>(
+    pinv_bwd_debug_kernel<<<(unsigned)bh, use_tc ? kMidTcThreads : kThreads, use_tc ? kTcGemmSmem : 0, (cudaStream_t)stream>>>(
         k2, ns_iterates, d_k2_inv, d_k2, (float*)workspace, m, J, kappa, use_tc);
   }
   FNB_CUDA(cudaPeekAtLastError());

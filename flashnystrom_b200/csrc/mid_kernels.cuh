@@ -32,6 +32,10 @@ namespace fnb {
 constexpr int kTcGemmTerm = 128 * 256;            // one bf16 term of a 128 x 128 operand
 constexpr int kTcGemmSet = 3 * kTcGemmTerm;       // the three terms
 constexpr size_t kTcGemmSmem = 2 * (size_t)kTcGemmSet + 1024;
+// CTA size of the kernels of this file when their products run on the tensor cores: every product is a
+// chain of three latency-bound phases (operand copy and split, MMAs, epilogue) that all threads take
+// part in, so twice the warps shorten the first and the last (the CUDA-core products keep 256 threads)
+constexpr int kMidTcThreads = 512;
 
 #ifdef FNB_TC_TRACE
 __device__ unsigned long long g_gemm_cycles[8];
@@ -52,16 +56,17 @@ struct GemmWs {
 };
 
 // rows x cols FP32 matrix in global memory (leading dimension ld) -> three swizzled bf16 term tiles,
-// zero beyond rows / cols.  All 256 threads.
+// zero beyond rows / cols.  All NT threads of the CTA.
+template <int NT>
 __device__ inline void tc_gemm_load(uint8_t* set, const float* src, int ld, int rows, int cols) {
-  // 128 rows x 16 chunks of 8 columns = 2048 items, 8 per thread; all of a thread's global loads are
-  // issued before the first value is used (one round trip to L2 instead of eight)
-  constexpr int kItems = 128 * 16 / kThreads;
+  // 128 rows x 16 chunks of 8 columns = 2048 items, 2048 / NT per thread; all of a thread's global
+  // loads are issued before the first value is used (one round trip to L2)
+  constexpr int kItems = 128 * 16 / NT;
   const bool vec = (ld & 3) == 0 && (cols & 7) == 0 && (reinterpret_cast<uintptr_t>(src) & 15u) == 0;
   float v[kItems][8];
 #pragma unroll
   for (int it = 0; it < kItems; ++it) {
-    const int item = threadIdx.x + it * kThreads;
+    const int item = threadIdx.x + it * NT;
     const int r = item >> 4, c0 = (item & 15) * 8;
 #pragma unroll
     for (int i = 0; i < 8; ++i) v[it][i] = 0.f;
@@ -79,7 +84,7 @@ __device__ inline void tc_gemm_load(uint8_t* set, const float* src, int ld, int 
   }
 #pragma unroll
   for (int it = 0; it < kItems; ++it) {
-    const int item = threadIdx.x + it * kThreads;
+    const int item = threadIdx.x + it * NT;
     const int r = item >> 4, ch = item & 15;
     uint32_t w0[4], w1[4], w2[4];
 #pragma unroll
@@ -108,7 +113,7 @@ __device__ __forceinline__ uint64_t tc_gemm_desc(uint32_t tile, bool along_rows,
                     : tc::smem_desc_sw128(tile + (k >> 2) * (128 * 128) + (k & 3) * 32, 16, 1024);
 }
 
-template <bool TA, bool TB>
+template <bool TA, bool TB, int NT>
 __device__ inline void cta_gemm_tc(float* C, int ldc, const float* A, int lda, const float* B, int ldb, int M, int N,
                                    int K, float alpha, float beta, float diag, GemmWs& ws, float* C2, float alpha2,
                                    float diag2) {
@@ -116,8 +121,8 @@ __device__ inline void cta_gemm_tc(float* C, int ldc, const float* A, int lda, c
   uint8_t* setB = ws.tiles + kTcGemmSet;
   GEMM_T0();
   // operands exactly as stored: A is (M x K) or, transposed, (K x M); B is (K x N) or (N x K)
-  tc_gemm_load(setA, A, lda, TA ? K : M, TA ? M : K);
-  tc_gemm_load(setB, B, ldb, TB ? N : K, TB ? K : N);
+  tc_gemm_load<NT>(setA, A, lda, TA ? K : M, TA ? M : K);
+  tc_gemm_load<NT>(setB, B, ldb, TB ? N : K, TB ? K : N);
   tc::fence_proxy_async();
   __syncthreads();
   GEMM_T(0);
@@ -156,15 +161,16 @@ __device__ inline void cta_gemm_tc(float* C, int ldc, const float* A, int lda, c
   tc::tc_fence_after();
   GEMM_T(2);
   // epilogue, step 1: accumulator rows -> FP32 staging in shared memory (the operand tiles are dead).
-  // Warp w reads TMEM lanes 32 (w & 3) .. + 31 (= rows), columns 64 (w >> 2) .. + 63.
+  // Warp w reads TMEM lanes 32 (w & 3) .. + 31 (= rows) and its share of the 128 columns.
   constexpr int kLdS = 132;
+  constexpr int kColsPerWarp = 128 / (NT / 128);
   float* stage = reinterpret_cast<float*>(ws.tiles);
   {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int r = (warp & 3) * 32 + lane, cbase = (warp >> 2) * 64;
+    const int r = (warp & 3) * 32 + lane, cbase = (warp >> 2) * kColsPerWarp;
     const uint32_t taddr = ws.tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)cbase;
 #pragma unroll
-    for (int half = 0; half < 2; ++half) {
+    for (int half = 0; half < kColsPerWarp / 32; ++half) {
       float v[32];
       tc::tmem_ld32(taddr + half * 32, v);
       tc::tmem_ld_wait();
@@ -180,7 +186,7 @@ __device__ inline void cta_gemm_tc(float* C, int ldc, const float* A, int lda, c
       (!C2 || (reinterpret_cast<uintptr_t>(C2) & 15u) == 0)) {
     const int n4 = N >> 2;
 #pragma unroll 4
-    for (int f = threadIdx.x; f < M * n4; f += kThreads) {
+    for (int f = threadIdx.x; f < M * n4; f += NT) {
       const int r = f / n4, c = (f - r * n4) * 4;
       const float4 x = *reinterpret_cast<const float4*>(stage + r * kLdS + c);
       float4 o = make_float4(alpha * x.x, alpha * x.y, alpha * x.z, alpha * x.w);
@@ -199,7 +205,7 @@ __device__ inline void cta_gemm_tc(float* C, int ldc, const float* A, int lda, c
       }
     }
   } else {
-    for (int idx = threadIdx.x; idx < M * N; idx += kThreads) {
+    for (int idx = threadIdx.x; idx < M * N; idx += NT) {
       const int r = idx / N, c = idx - r * N;
       const float x = stage[r * kLdS + c];
       float val = alpha * x;
@@ -216,11 +222,11 @@ __device__ inline void cta_gemm_tc(float* C, int ldc, const float* A, int lda, c
 #endif
 }
 
-// set-up / teardown of the tensor-core products inside a 256-thread kernel (all threads call)
+// set-up / teardown of the tensor-core products inside a kernel of this file (all threads call)
 __device__ inline void gemm_ws_open(GemmWs& ws, float* sm, uint8_t* dyn, bool use_tc, uint64_t* bar_and_flag,
                                     uint32_t* tmem_slot, int* status) {
   ws.sm = sm; ws.tiles = nullptr; ws.bar = bar_and_flag; ws.tmem = 0; ws.phase = 0; ws.status = status;
-  if (!use_tc) return;
+  if (!use_tc || blockDim.x != kMidTcThreads) return;   // the tensor-core products are written for kMidTcThreads threads
   ws.tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(dyn) + 1023) & ~(uintptr_t)1023);
   if (threadIdx.x == 0) {
     tc::mbar_init(bar_and_flag, 1);
@@ -260,9 +266,12 @@ __device__ __noinline__ void cta_gemm(float* C, int ldc, const float* A, int lda
                          int M, int N, int K, float alpha, float beta, float diag, GemmWs& ws,
                          float* C2 = nullptr, float alpha2 = 0.f, float diag2 = 0.f) {
   if (ws.tiles) {
-    cta_gemm_tc<TA, TB>(C, ldc, A, lda, B, ldb, M, N, K, alpha, beta, diag, ws, C2, alpha2, diag2);
+    // (tiles are only handed out to CTAs of kMidTcThreads threads)
+    cta_gemm_tc<TA, TB, kMidTcThreads>(C, ldc, A, lda, B, ldb, M, N, K, alpha, beta, diag, ws, C2, alpha2, diag2);
     return;
   }
+  // (the CUDA-core product below is written for 256 threads: kernels that take this branch are
+  // launched with kThreads)
   float* sm = ws.sm;
   float* As = sm;
   float* Bs = sm + kGemmKT * kGemmLd;
@@ -333,15 +342,15 @@ __device__ __noinline__ void cta_gemm(float* C, int ldc, const float* A, int lda
 // Results are broadcast through red[0..3] and returned in registers by every thread.
 struct Norms { float n1, ninf; int jc, ir; };
 __device__ inline Norms cta_norms(const float* A, int m, float* red) {
-  // one pass over A: warp w takes rows w, w + 8, ...; a lane reads columns lane, lane + 32, ... of a
+  // one pass over A: warp w takes rows w, w + (number of warps), ...; a lane reads columns lane, lane + 32, ... of a
   // row (coalesced), keeps its column partial sums in registers and folds the row sum with shuffles
   const int t = threadIdx.x, w = t >> 5, lane = t & 31;
   float* rowsum = red;                       // [kMaxM]
-  float* colpart = red + kMaxM;              // [8][kMaxM]
+  float* colpart = red + kMaxM;              // [warps][kMaxM]: up to 17 kMaxM floats of `red` in all
   float cs[kMaxM / 32];
 #pragma unroll
   for (int q = 0; q < kMaxM / 32; ++q) cs[q] = 0.f;
-  for (int r = w; r < m; r += kThreads / 32) {
+  for (int r = w; r < m; r += ((int)blockDim.x >> 5)) {
     float x[kMaxM / 32];
 #pragma unroll
     for (int q = 0; q < kMaxM / 32; ++q) {
@@ -360,11 +369,11 @@ __device__ inline Norms cta_norms(const float* A, int m, float* red) {
   __shared__ float out_n1, out_ninf;
   __shared__ int out_jc, out_ir;
   if (w == 0) {
-    // column sums: fold the eight warps, then the first-occurrence argmax over columns
+    // column sums: fold the warps, then the first-occurrence argmax over columns
     float best = -1.f; int bi = 0;
     for (int c = lane; c < m; c += 32) {
       float s = 0.f;
-      for (int ww = 0; ww < kThreads / 32; ++ww) s += colpart[ww * kMaxM + c];
+      for (int ww = 0; ww < ((int)blockDim.x >> 5); ++ww) s += colpart[ww * kMaxM + c];
       if (s > best) { best = s; bi = c; }
     }
     for (int o = 16; o > 0; o >>= 1) {
@@ -394,7 +403,7 @@ __device__ inline Norms cta_norms(const float* A, int m, float* red) {
 
 // dst = a*X + diag*I   (m x m, elementwise)
 __device__ inline void cta_affine(float* dst, const float* X, float a, float diag, int m) {
-  for (int idx = threadIdx.x; idx < m * m; idx += kThreads) {
+  for (int idx = threadIdx.x; idx < m * m; idx += (int)blockDim.x) {
     int r = idx / m, c = idx - r * m;
     dst[idx] = a * X[idx] + (r == c ? diag : 0.f);
   }
@@ -422,7 +431,7 @@ __device__ inline void pinv_forward(const float* k2, float* iterates, float* k2i
   }
   Norms na = cta_norms(A, m, red);
   const float c = fmaxf(na.n1 * na.ninf, 1e-12f);
-  for (int idx = threadIdx.x; idx < mm; idx += kThreads) {
+  for (int idx = threadIdx.x; idx < mm; idx += (int)blockDim.x) {
     int r = idx / m, cc = idx - r * m;
     iterates[idx] = A[cc * m + r] / c;
   }
@@ -439,7 +448,7 @@ __device__ inline void pinv_forward(const float* k2, float* iterates, float* k2i
   if (kappa > 0.f) {
     cta_gemm<false, true>(k2inv, m, ZJ, m, k2, m, m, m, m, 1.f, 0.f, 0.f, ws);
   } else {
-    for (int idx = threadIdx.x; idx < mm; idx += kThreads) k2inv[idx] = ZJ[idx];
+    for (int idx = threadIdx.x; idx < mm; idx += (int)blockDim.x) k2inv[idx] = ZJ[idx];
     __syncthreads();
   }
 }
@@ -475,11 +484,11 @@ __device__ inline void pinv_backward(const float* k2, const float* iterates, con
     cta_gemm<true, false>(dK2a, m, G, m, ZJ, m, m, m, m, 1.f, 0.f, 0.f, ws);   // G^T Z_J
     cta_gemm<false, false>(dZ, m, G, m, k2, m, m, m, m, 1.f, 0.f, 0.f, ws);    // G K2
   } else {
-    for (int idx = threadIdx.x; idx < mm; idx += kThreads) dZ[idx] = G[idx];
+    for (int idx = threadIdx.x; idx < mm; idx += (int)blockDim.x) dZ[idx] = G[idx];
   }
   __syncthreads();
   if (J == 0) {
-    for (int idx = threadIdx.x; idx < mm; idx += kThreads) dA[idx] = 0.f;
+    for (int idx = threadIdx.x; idx < mm; idx += (int)blockDim.x) dA[idx] = 0.f;
     __syncthreads();
   }
 
@@ -504,7 +513,7 @@ __device__ inline void pinv_backward(const float* k2, const float* iterates, con
   const float c = fmaxf(craw, 1e-12f);
   // S = sum_{a,b} dZ0[a,b] A[b,a]
   float part = 0.f;
-  for (int idx = threadIdx.x; idx < mm; idx += kThreads) {
+  for (int idx = threadIdx.x; idx < mm; idx += (int)blockDim.x) {
     int a = idx / m, b = idx - a * m;
     part += dZ[idx] * A[b * m + a];
   }
@@ -512,12 +521,12 @@ __device__ inline void pinv_backward(const float* k2, const float* iterates, con
   if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = part;
   __syncthreads();
   float S = 0.f;
-  for (int w = 0; w < kThreads / 32; ++w) S += red[w];
+  for (int w = 0; w < ((int)blockDim.x >> 5); ++w) S += red[w];
   __syncthreads();
   const bool clamped = !(craw > 1e-12f);
   const float col_term = clamped ? 0.f : -S * na.ninf / (c * c);
   const float row_term = clamped ? 0.f : -S * na.n1 / (c * c);
-  for (int idx = threadIdx.x; idx < mm; idx += kThreads) {
+  for (int idx = threadIdx.x; idx < mm; idx += (int)blockDim.x) {
     int r = idx / m, cc = idx - r * m;
     float a = A[idx];
     float sg = a > 0.f ? 1.f : (a < 0.f ? -1.f : 0.f);
@@ -529,15 +538,15 @@ __device__ inline void pinv_backward(const float* k2, const float* iterates, con
   __syncthreads();
   if (kappa > 0.f) {
     // dK2 = dK2a + K2 (dA + dA^T)
-    for (int idx = threadIdx.x; idx < mm; idx += kThreads) {
+    for (int idx = threadIdx.x; idx < mm; idx += (int)blockDim.x) {
       int r = idx / m, cc = idx - r * m;
       dM[idx] = dA[idx] + dA[cc * m + r];
     }
     __syncthreads();
     cta_gemm<false, false>(dK2a, m, k2, m, dM, m, m, m, m, 1.f, 1.f, 0.f, ws);
-    for (int idx = threadIdx.x; idx < mm; idx += kThreads) dK2[idx] = dK2a[idx];
+    for (int idx = threadIdx.x; idx < mm; idx += (int)blockDim.x) dK2[idx] = dK2a[idx];
   } else {
-    for (int idx = threadIdx.x; idx < mm; idx += kThreads) dK2[idx] = dA[idx];
+    for (int idx = threadIdx.x; idx < mm; idx += (int)blockDim.x) dK2[idx] = dA[idx];
   }
   __syncthreads();
 }
@@ -560,7 +569,7 @@ struct MidFwdParams {
   int* status;
 };
 
-__global__ void __launch_bounds__(kThreads) mid_fwd_kernel(MidFwdParams p) {
+__global__ void __launch_bounds__(kMidTcThreads) mid_fwd_kernel(MidFwdParams p) {
   __shared__ float sm[kGemmSmemFloats];
   __shared__ uint64_t gemm_bar[2];
   __shared__ uint32_t gemm_tmem;
@@ -570,7 +579,7 @@ __global__ void __launch_bounds__(kThreads) mid_fwd_kernel(MidFwdParams p) {
   Segments sg(p.N, m);
   float* qt = p.qt + bh * m * D;
   float* kt = p.kt + bh * m * D;
-  for (int idx = t; idx < 2 * m * D; idx += kThreads) {
+  for (int idx = t; idx < 2 * m * D; idx += (int)blockDim.x) {
     int which = idx / (m * D), rem = idx - which * m * D;
     int l = rem / D, d = rem - l * D;
     const float* src = p.land_partial + ((((size_t)which * p.BH + bh) * m + l) * p.C) * D + d;
@@ -590,7 +599,7 @@ __global__ void __launch_bounds__(kThreads) mid_fwd_kernel(MidFwdParams p) {
   cta_gemm<false, true>(k2, m, qt, D, kt, D, m, m, D, 1.f, 0.f, 0.f, ws);
   // row softmax, one warp per row
   const int w = t >> 5, lane = t & 31;
-  for (int r = w; r < m; r += kThreads / 32) {
+  for (int r = w; r < m; r += ((int)blockDim.x >> 5)) {
     float mx = -INFINITY;
     for (int c = lane; c < m; c += 32) mx = fmaxf(mx, k2[r * m + c]);
     for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
@@ -606,7 +615,7 @@ __global__ void __launch_bounds__(kThreads) mid_fwd_kernel(MidFwdParams p) {
   gemm_ws_close(ws);
 }
 
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kMidTcThreads)
 pinv_fwd_debug_kernel(const float* k2, float* iterates, float* k2inv, float* scratch, int m,
                       int J, float kappa, int use_tc) {
   __shared__ float sm[kGemmSmemFloats];
@@ -621,7 +630,7 @@ pinv_fwd_debug_kernel(const float* k2, float* iterates, float* k2inv, float* scr
   gemm_ws_close(ws);
 }
 
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kMidTcThreads)
 pinv_bwd_debug_kernel(const float* k2, const float* iterates, const float* G, float* dK2,
                       float* scratch, int m, int J, float kappa, int use_tc) {
   __shared__ float sm[kGemmSmemFloats];
@@ -726,7 +735,7 @@ struct MidBwdParams {
   int* status;
 };
 
-__global__ void __launch_bounds__(kThreads) mid_bwd_kernel(MidBwdParams p) {
+__global__ void __launch_bounds__(kMidTcThreads) mid_bwd_kernel(MidBwdParams p) {
   __shared__ float sm[kGemmSmemFloats];
   __shared__ uint64_t gemm_bar[2];
   __shared__ uint32_t gemm_tmem;
@@ -738,7 +747,7 @@ __global__ void __launch_bounds__(kThreads) mid_bwd_kernel(MidBwdParams p) {
   float* dstep2 = p.dstep2 + bh * md;
   float* dkt_a = p.dkt_a + bh * md;
   const float* partA = p.partA + bh * (size_t)p.nchunk * 2 * md;
-  for (int idx = t; idx < 2 * md; idx += kThreads) {
+  for (int idx = t; idx < 2 * md; idx += (int)blockDim.x) {
     float s = 0.f;
     for (int c = 0; c < p.nchunk; ++c) s += partA[(size_t)c * 2 * md + idx];
     if (idx < md) dstep2[idx] = s; else dkt_a[idx - md] = s;
@@ -756,7 +765,7 @@ __global__ void __launch_bounds__(kThreads) mid_bwd_kernel(MidBwdParams p) {
   cta_gemm<false, true>(G, m, dstep2, D, bmat, D, m, m, D, 1.f, 0.f, 0.f, ws);      // dstep2 Bmat^T
   {
     const int w = t >> 5, lane = t & 31;
-    for (int l = w; l < m; l += kThreads / 32) {
+    for (int l = w; l < m; l += ((int)blockDim.x >> 5)) {
       float s = 0.f;
       for (int d = lane; d < D; d += 32) s += bmat[l * D + d] * dO3[l * D + d];
       for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
@@ -769,7 +778,7 @@ __global__ void __launch_bounds__(kThreads) mid_bwd_kernel(MidBwdParams p) {
   // softmax-2 Jacobian, in place: dS2 = K2 o (dK2 - rowsum(dK2 o K2))
   {
     const int w = t >> 5, lane = t & 31;
-    for (int r = w; r < m; r += kThreads / 32) {
+    for (int r = w; r < m; r += ((int)blockDim.x >> 5)) {
       float s = 0.f;
       for (int c = lane; c < m; c += 32) s += dK2[r * m + c] * k2[r * m + c];
       for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
@@ -780,7 +789,7 @@ __global__ void __launch_bounds__(kThreads) mid_bwd_kernel(MidBwdParams p) {
   float* dqt_ns = p.dqt_ns + bh * md;
   float* dkt_tot = p.dkt_tot + bh * md;
   cta_gemm<false, false>(dqt_ns, D, dK2, m, kt, D, m, D, m, 1.f, 0.f, 0.f, ws);      // dS2 Kt
-  for (int idx = t; idx < md; idx += kThreads) dkt_tot[idx] = dkt_a[idx];
+  for (int idx = t; idx < md; idx += (int)blockDim.x) dkt_tot[idx] = dkt_a[idx];
   __syncthreads();
   cta_gemm<true, false>(dkt_tot, D, dK2, m, qt, D, m, D, m, 1.f, 1.f, 0.f, ws);      // += dS2^T Qt
   gemm_ws_close(ws);
