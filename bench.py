@@ -729,9 +729,37 @@ def main():
         for _ in range(3):
             step_e2e()
         e2e_ms, _ = timed(step_e2e, max(3, min(steps, 10)))
+        torch.cuda.synchronize()
+        e2e_check = None
+        if parity is not None:   # what landed in host memory is the result (same head, same oracle figures)
+            h = parity["head"]
+            e2e_check = {n_: O.rel_max(g[:, h:h + 1], r) for n_, g, r in zip(("out", "dq", "dk", "dv"), (hout, hdq, hdk, hdv), ref)}
+            if not (e2e_check["out"] <= 2e-3 and max(e2e_check["dq"], e2e_check["dk"], e2e_check["dv"]) <= 1e-2):
+                raise SystemExit(f"bench.py: the end-to-end pipeline's results fail parity: {e2e_check}")
+
+        # the same bytes over two copy streams with no call in between: what the PCIe link allows
+        s_in, s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+
+        def step_copies_only():
+            main_s = torch.cuda.current_stream(dev)
+            s_in.wait_stream(main_s), s_out.wait_stream(main_s)
+            for g in range(n_groups):
+                h0, h1 = g * hpg, (g + 1) * hpg
+                with torch.cuda.stream(s_in):
+                    for t in (hq, hk, hv, hdO):
+                        t[:, h0:h1].to(dev, non_blocking=True)
+                with torch.cuda.stream(s_out):
+                    for dst, src in zip((hout, hdq, hdk, hdv), (q, k, v, dO)):
+                        dst[:, h0:h1].copy_(src.detach()[:, h0:h1], non_blocking=True)
+            main_s.wait_stream(s_in), main_s.wait_stream(s_out)
+        step_copies_only()
+        copies_ms, _ = timed(step_copies_only, 5)
+        torch.cuda.synchronize()
         e2e = {"value": world * B * N / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
                "h2d_bytes_per_step": 4 * elem_bytes, "d2h_bytes_per_step": 4 * elem_bytes,
-               "pipeline": f"{n_groups} head groups on {len(streams)} streams", "host_numa": numa}
+               "pipeline": f"{n_groups} head groups on {len(streams)} streams", "host_numa": numa,
+               "rel_max_vs_oracle": e2e_check, "copies_only_ms_per_step": copies_ms,
+               "frac_of_copies_only": copies_ms / e2e_ms}
         del hout, hdq, hdk, hdv
 
     # ---- other legs ------------------------------------------------------------------------------
