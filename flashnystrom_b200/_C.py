@@ -373,3 +373,58 @@ def last_profile():
     buf = (_lib.KernelTime * 32)()
     n = lib.fnb_last_profile(buf, 32)
     return [(buf[i].name.decode(), buf[i].ms) for i in range(n)]
+
+
+# ---- depthwise convolution residual --------------------------------------------------------------
+def _conv_geometry(v):
+    if not isinstance(v, torch.Tensor) or not v.is_cuda or v.dim() != 4:
+        raise RuntimeError("conv residual: v must be a 4-D CUDA tensor (flashnystrom_b200 has no CPU path)")
+    if v.dtype not in _DTYPES:
+        raise RuntimeError("Supported dtypes: float32, float16, bfloat16")
+    layout = layout_of(v)
+    if layout is None:
+        v, layout = v.contiguous(), _lib.FNB_LAYOUT_BHND
+    return v, layout
+
+
+def conv_residual(v, weight, base=None, transposed=False):
+    """base + depthwise_conv(v) (base may be None), or with transposed=True the same with the taps
+    reversed (what the backward applies to the incoming gradient).  v, base: (B, H, N, D) in either
+    layout; weight: (H, kernel_size) FP32 on the device.  Returns a new tensor in v's layout."""
+    lib = _lib.load()
+    v, layout = _conv_geometry(v)
+    B, H, N, D = v.shape
+    w = weight.detach().to(device=v.device, dtype=torch.float32).contiguous()
+    if w.dim() != 2 or w.shape[0] != H:
+        raise RuntimeError(f"conv weight must be (heads, kernel_size) = ({H}, ks), got {tuple(w.shape)}")
+    if base is not None:
+        if base.shape != v.shape or base.dtype != v.dtype:
+            raise RuntimeError("conv residual: base must have the shape and dtype of v")
+        base = _to_layout(base.detach(), layout)
+    result = _empty_like_layout(v, layout)
+    args = _lib.ConvArgs(B, H, N, D, int(w.shape[1]), _DTYPES[v.dtype], int(layout), v.data_ptr(),
+                         base.data_ptr() if base is not None else None, result.data_ptr(), w.data_ptr(),
+                         1 if transposed else 0, v.device.index, torch.cuda.current_stream(v.device).cuda_stream)
+    with torch.cuda.device(v.device):
+        _lib.check(lib.fnb_conv_residual(C.byref(args)))
+    return result
+
+
+def conv_residual_dweight(v, d_out, kernel_size):
+    """Gradient of the convolution residual with respect to its (H, kernel_size) weights, FP32."""
+    lib = _lib.load()
+    v, layout = _conv_geometry(v)
+    B, H, N, D = v.shape
+    if d_out.shape != v.shape or d_out.dtype != v.dtype:
+        raise RuntimeError("conv residual: d_out must have the shape and dtype of v")
+    d_out = _to_layout(d_out.detach(), layout)
+    dw = torch.empty(H, int(kernel_size), dtype=torch.float32, device=v.device)
+    nbytes = lib.fnb_conv_dweight_workspace_bytes(B, H, N, int(kernel_size))
+    ws = torch.empty(max(int(nbytes), 16), dtype=torch.uint8, device=v.device)
+    args = _lib.ConvDwArgs(B, H, N, D, int(kernel_size), _DTYPES[v.dtype], int(layout), v.data_ptr(), d_out.data_ptr(),
+                           dw.data_ptr(), ws.data_ptr(), ws.numel(), v.device.index,
+                           torch.cuda.current_stream(v.device).cuda_stream)
+    with torch.cuda.device(v.device):
+        _lib.check(lib.fnb_conv_residual_dweight(C.byref(args)))
+    return dw
+

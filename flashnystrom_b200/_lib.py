@@ -67,6 +67,21 @@ class KernelInfo(C.Structure):
                 ("threads", C.c_int32), ("blocks_per_sm", C.c_int32)]
 
 
+class ConvArgs(C.Structure):
+    _fields_ = [("batch", C.c_int64), ("heads", C.c_int64), ("seq_len", C.c_int64),
+                ("head_dim", C.c_int32), ("kernel_size", C.c_int32), ("dtype", C.c_int32), ("layout", C.c_int32),
+                ("v", C.c_void_p), ("base", C.c_void_p), ("result", C.c_void_p), ("weight", C.c_void_p),
+                ("transposed", C.c_int32), ("device", C.c_int32), ("stream", C.c_void_p)]
+
+
+class ConvDwArgs(C.Structure):
+    _fields_ = [("batch", C.c_int64), ("heads", C.c_int64), ("seq_len", C.c_int64),
+                ("head_dim", C.c_int32), ("kernel_size", C.c_int32), ("dtype", C.c_int32), ("layout", C.c_int32),
+                ("v", C.c_void_p), ("d_out", C.c_void_p), ("d_weight", C.c_void_p),
+                ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+                ("device", C.c_int32), ("stream", C.c_void_p)]
+
+
 # every symbol include/flashnystrom_b200.h declares, with its ctypes signature
 SIGNATURES = {
     "fnb_last_error": (C.c_char_p, []),
@@ -96,6 +111,9 @@ SIGNATURES = {
                                          C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                          C.c_int32, C.c_void_p]),
     "fnb_kernel_report": (C.c_int, [C.c_int, C.POINTER(KernelInfo), C.c_int]),
+    "fnb_conv_residual": (C.c_int, [C.POINTER(ConvArgs)]),
+    "fnb_conv_dweight_workspace_bytes": (C.c_size_t, [C.c_int64, C.c_int64, C.c_int64, C.c_int32]),
+    "fnb_conv_residual_dweight": (C.c_int, [C.POINTER(ConvDwArgs)]),
     "fnb_set_profiling": (C.c_int, [C.c_int]),
     "fnb_last_profile": (C.c_int, [C.POINTER(KernelTime), C.c_int]),
 }

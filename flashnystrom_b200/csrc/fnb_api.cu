@@ -17,6 +17,7 @@
 #include "tc_host.cuh"
 #include "ns_kernels.cuh"
 #include "ns_tc_kernels.cuh"
+#include "conv_kernels.cuh"
 #include <type_traits>
 #include <algorithm>
 
@@ -1260,6 +1261,8 @@ int fnb_kernel_report(int device, fnb_kernel_info* out, int cap) {
   const KernelEntry ks[] = {
       {"landmark_partial<half>", (const void*)landmark_partial_kernel<H, true>, kThreads, 0},
       {"ns_fwd_tc", (const void*)nstc::ns_fwd_tc_kernel, nstc::kNsTcThreads, nstc::kFwdSmem},
+      {"conv_residual<half>", (const void*)conv_residual_kernel<H>, kThreads, conv_smem_bytes(64, 3)},
+      {"conv_dw_partial<half,2>", (const void*)conv_dw_partial_kernel<H, 2>, kThreads, conv_smem_bytes(64, 3)},
       {"tc_fwd_b<half,64,64>", (const void*)tc::tc_fwd_b_kernel<H, 64, 64>, tc::kTcThreads, tc::FwdBSmem<64, 64>::kBytes},
       {"combine_slab", (const void*)combine_slab_kernel, kThreads, combine_slab_smem(64)},
       {"tc_fwd_c<half,64,64>", (const void*)tc::tc_fwd_c_kernel<H, 64, 64>, tc::kTcThreads, tc::FwdCSmem<64, 64>::kBytes},
@@ -1299,6 +1302,114 @@ int fnb_kernel_report(int device, fnb_kernel_info* out, int cap) {
     ++n;
   }
   return n;
+}
+
+// ---- depthwise convolution residual --------------------------------------------------------
+static int check_conv_shape(int64_t B, int64_t H, int64_t N, int D, int ks, int dtype, int layout) {
+  if (B <= 0 || H <= 0 || N <= 0)
+    return fail(FNB_ERR_INVALID_ARGUMENT, "batch, heads and seq_len must be positive (got %lld, %lld, %lld)",
+                (long long)B, (long long)H, (long long)N);
+  if (B * H > 65535) return fail(FNB_ERR_INVALID_ARGUMENT, "batch * heads (%lld) exceeds 65535", (long long)(B * H));
+  if (!(D == 16 || D == 32 || D == 64 || D == 128))
+    return fail(FNB_ERR_INVALID_ARGUMENT, "head_dim must be 16, 32, 64 or 128, got %d", D);
+  if (ks < 1 || ks > kConvMaxTaps || (ks & 1) == 0)
+    return fail(FNB_ERR_INVALID_ARGUMENT, "conv kernel_size must be odd and in [1, %d], got %d", kConvMaxTaps, ks);
+  if (dtype != FNB_F32 && dtype != FNB_F16 && dtype != FNB_BF16)
+    return fail(FNB_ERR_INVALID_ARGUMENT, "Supported dtypes: float32, float16, bfloat16 (got code %d)", dtype);
+  if (layout != FNB_LAYOUT_BHND && layout != FNB_LAYOUT_BNHD)
+    return fail(FNB_ERR_INVALID_ARGUMENT, "layout must be FNB_LAYOUT_BHND (0) or FNB_LAYOUT_BNHD (1), got %d", layout);
+  return 0;
+}
+
+int fnb_conv_residual(const fnb_conv_args* a) {
+  if (!a) return fail(FNB_ERR_INVALID_ARGUMENT, "args is NULL");
+  if (int rc = check_conv_shape(a->batch, a->heads, a->seq_len, a->head_dim, a->kernel_size, a->dtype, a->layout)) return rc;
+  if (!a->v || !a->result || !a->weight) return fail(FNB_ERR_INVALID_ARGUMENT, "v, result and weight must not be NULL");
+  if (!aligned16(a->v) || !aligned16(a->result) || (a->base && !aligned16(a->base)))
+    return fail(FNB_ERR_INVALID_ARGUMENT, "v, base and result must be 16-byte aligned");
+  if (a->v == a->result) return fail(FNB_ERR_INVALID_ARGUMENT, "result must not alias v");
+  DeviceGuard g(a->device);
+  if (!g.ok) return fail(FNB_ERR_CUDA, "cannot select CUDA device %d", a->device);
+  int max_smem = 0, cc = 0, sms = 0;
+  if (int rc = device_limits(a->device, &max_smem, &cc, &sms)) return rc;
+  tc::BigLayout big{a->batch, a->heads, a->seq_len, a->head_dim, a->layout};
+  ConvParams p;
+  p.v = a->v; p.base = a->base; p.result = a->result; p.w = a->weight; p.N = a->seq_len;
+  p.H = (int)a->heads; p.D = a->head_dim; p.ks = a->kernel_size; p.flip = a->transposed ? 1 : 0;
+  p.row_stride = big.row_stride(); p.head_stride = big.head_stride(); p.batch_stride = big.batch_stride();
+  const size_t smem = conv_smem_bytes(p.D, p.ks);
+  const dim3 grid((unsigned)((a->seq_len + kConvRows - 1) / kConvRows), (unsigned)(a->batch * a->heads));
+  cudaStream_t st = (cudaStream_t)a->stream;
+  auto launch = [&](auto kern) -> int {
+    if (int rc = set_smem(kern, smem, max_smem, "conv_residual")) return rc;
+    kern<<<grid, kThreads, smem, st>>>(p);
+    FNB_CUDA(cudaPeekAtLastError());
+    return 0;
+  };
+  switch (a->dtype) {
+    case FNB_F32: return launch(conv_residual_kernel<float>);
+    case FNB_F16: return launch(conv_residual_kernel<__half>);
+    default: return launch(conv_residual_kernel<__nv_bfloat16>);
+  }
+}
+
+size_t fnb_conv_dweight_workspace_bytes(int64_t batch, int64_t heads, int64_t seq_len, int32_t kernel_size) {
+  if (batch <= 0 || heads <= 0 || seq_len <= 0 || kernel_size < 1 || kernel_size > kConvMaxTaps) return 0;
+  const int64_t tiles = (seq_len + kConvRows - 1) / kConvRows;
+  return align256(sizeof(float) * (size_t)(batch * heads * tiles * kernel_size));
+}
+
+int fnb_conv_residual_dweight(const fnb_conv_dw_args* a) {
+  if (!a) return fail(FNB_ERR_INVALID_ARGUMENT, "args is NULL");
+  if (int rc = check_conv_shape(a->batch, a->heads, a->seq_len, a->head_dim, a->kernel_size, a->dtype, a->layout)) return rc;
+  if (!a->v || !a->d_out || !a->d_weight) return fail(FNB_ERR_INVALID_ARGUMENT, "v, d_out and d_weight must not be NULL");
+  if (!aligned16(a->v) || !aligned16(a->d_out)) return fail(FNB_ERR_INVALID_ARGUMENT, "v and d_out must be 16-byte aligned");
+  const size_t need = fnb_conv_dweight_workspace_bytes(a->batch, a->heads, a->seq_len, a->kernel_size);
+  if (!a->workspace || a->workspace_bytes < need || !aligned16(a->workspace))
+    return fail(FNB_ERR_WORKSPACE, "conv weight-gradient workspace must be 16-byte aligned and >= %zu bytes (got %zu)",
+                need, a->workspace_bytes);
+  DeviceGuard g(a->device);
+  if (!g.ok) return fail(FNB_ERR_CUDA, "cannot select CUDA device %d", a->device);
+  int max_smem = 0, cc = 0, sms = 0;
+  if (int rc = device_limits(a->device, &max_smem, &cc, &sms)) return rc;
+  tc::BigLayout big{a->batch, a->heads, a->seq_len, a->head_dim, a->layout};
+  ConvDwParams p;
+  p.v = a->v; p.g = a->d_out; p.part = (float*)a->workspace; p.N = a->seq_len;
+  p.H = (int)a->heads; p.D = a->head_dim; p.ks = a->kernel_size;
+  p.row_stride = big.row_stride(); p.head_stride = big.head_stride(); p.batch_stride = big.batch_stride();
+  const size_t smem = conv_smem_bytes(p.D, p.ks);
+  const int tiles = (int)((a->seq_len + kConvRows - 1) / kConvRows);
+  const dim3 grid((unsigned)tiles, (unsigned)(a->batch * a->heads));
+  cudaStream_t st = (cudaStream_t)a->stream;
+  auto launch = [&](auto kern) -> int {
+    if (int rc = set_smem(kern, smem, max_smem, "conv_dweight")) return rc;
+    kern<<<grid, kThreads, smem, st>>>(p);
+    FNB_CUDA(cudaPeekAtLastError());
+    return 0;
+  };
+  // rows of a 64-row tile per thread: 64 * (16-byte chunks per row) / 256
+  const int nr = std::max(1, kConvRows * (a->head_dim / (a->dtype == FNB_F32 ? 4 : 8)) / kThreads);
+  auto by_rows = [&](auto tag) -> int {
+    using T = decltype(tag);
+    switch (nr) {
+      case 1: return launch(conv_dw_partial_kernel<T, 1>);
+      case 2: return launch(conv_dw_partial_kernel<T, 2>);
+      case 4: return launch(conv_dw_partial_kernel<T, 4>);
+      default: return launch(conv_dw_partial_kernel<T, 8>);
+    }
+  };
+  int rc;
+  switch (a->dtype) {
+    case FNB_F32: rc = by_rows(float{}); break;
+    case FNB_F16: rc = by_rows(__half{}); break;
+    default: rc = by_rows(__nv_bfloat16{}); break;
+  }
+  if (rc) return rc;
+  const int warps = (int)a->heads * a->kernel_size;
+  conv_dw_reduce_kernel<<<(unsigned)((warps * 32 + kThreads - 1) / kThreads), kThreads, 0, st>>>(
+      p.part, a->d_weight, (int)a->batch, (int)a->heads, tiles, a->kernel_size);
+  FNB_CUDA(cudaPeekAtLastError());
+  return 0;
 }
 
 int fnb_debug_set_wait_limit_ms(int device, int ms) {

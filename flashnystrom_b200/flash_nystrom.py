@@ -14,8 +14,9 @@ HAS_CUDA = bool(torch.cuda.is_available())
 
 def _depthwise_conv_residual(v, weight):
     """Depthwise 1-D conv of V along the sequence, one kernel per head shared by its D
-    channels, zero padding ks//2 (flash_nystrom/flash_nystrom.py:19-55).  Runs through
-    F.conv1d, outside the autograd Function, so PyTorch differentiates it."""
+    channels, zero padding ks//2 (flash_nystrom/flash_nystrom.py:19-55), through F.conv1d as in the
+    reference.  Only used while a compiler is tracing (it differentiates and traces this form);
+    otherwise _ConvResidualFunction runs the library's kernel."""
     B, H, N, D = v.shape
     ks = weight.shape[1]
     if weight.dtype != v.dtype:
@@ -24,6 +25,30 @@ def _depthwise_conv_residual(v, weight):
     w = weight.unsqueeze(1).expand(H, D, ks).contiguous().view(H * D, 1, ks)
     out = F.conv1d(v_in, w, padding=ks // 2, groups=H * D)
     return out.view(B, H, D, N).permute(0, 1, 3, 2).contiguous()
+
+
+class _ConvResidualFunction(torch.autograd.Function):
+    """out + depthwise_conv(v, weight) as one streaming kernel in the tensors' own layout, with its
+    backward (the reference's `out + _depthwise_conv_residual(v, conv_weight)`,
+    flash_nystrom/flash_nystrom.py:19-55, makes two transposing copies around a grouped F.conv1d and
+    leaves the backward to autograd).  The weights take part rounded to the tensors' dtype, as the
+    reference's `weight.to(v.dtype)` has it."""
+
+    @staticmethod
+    def forward(ctx, out, v, weight):
+        w32 = weight.detach().to(v.dtype).float()
+        ctx.save_for_backward(v, w32)
+        ctx.weight_dtype = weight.dtype
+        return _C.conv_residual(v, w32, base=out)
+
+    @staticmethod
+    def backward(ctx, grad):
+        v, w32 = ctx.saved_tensors
+        d_v = _C.conv_residual(grad, w32, transposed=True) if ctx.needs_input_grad[1] else None
+        d_w = None
+        if ctx.needs_input_grad[2]:
+            d_w = _C.conv_residual_dweight(v, grad, w32.shape[1]).to(ctx.weight_dtype)
+        return grad, d_v, d_w
 
 
 class FlashNystromFunction(torch.autograd.Function):
@@ -75,7 +100,12 @@ def flash_nystrom_attention(q, k, v, num_landmarks=64, newton_iter=6, conv_weigh
         out = FlashNystromFunction.apply(q, k, v, num_landmarks, newton_iter, fast_dk2inv,
                                          kappa_star, use_tc_pinv)
     if conv_weight is not None and conv_kernel_size > 0:
-        out = out + _depthwise_conv_residual(v, conv_weight)
+        if torch.compiler.is_compiling():
+            out = out + _depthwise_conv_residual(v, conv_weight)      # traceable form
+        else:
+            if conv_weight.dim() != 2 or conv_weight.shape[1] % 2 == 0:
+                raise ValueError("conv_weight must be (heads, kernel_size) with an odd kernel_size")
+            out = _ConvResidualFunction.apply(out, v, conv_weight)
     return out
 
 

@@ -269,6 +269,49 @@ FNB_API int fnb_pinv_backward_noalloc(int64_t bh, int32_t m, int32_t newton_iter
                                       const float* k2, const float* ns_iterates, const float* d_k2_inv,
                                       float* d_k2, int32_t device, void* stream);
 
+/* ---- depthwise convolution residual of the attention module ----------------------------------
+ * Replaces _depthwise_conv_residual (flash_nystrom/flash_nystrom.py:19-55: two transposing copies
+ * around a grouped F.conv1d) together with the addition to the attention output that follows the
+ * kernel call in flash_nystrom_attention, and what autograd derives from them.  Every head has one
+ * 1-D kernel of odd length kernel_size (<= 127), shared by its head_dim channels; zero padding of
+ * kernel_size / 2 rows on either side of the sequence:
+ *     result[b,h,n,:] = base[b,h,n,:] + sum_j weight[h][j] * v[b,h,n + j - kernel_size/2,:]
+ * with transposed != 0 the taps are reversed (the operator the backward applies to dOut to get the
+ * contribution to dV).  v, base (may be NULL: nothing is added) and result are (B,H,N,D) tensors of
+ * `dtype` in `layout`, 16-byte aligned; result must not alias v (it may alias base).  weight is FP32
+ * [heads][kernel_size] on the device.  head_dim in {16, 32, 64, 128}.  One kernel on `stream`, no
+ * synchronisation, no allocation. */
+typedef struct fnb_conv_args {
+  int64_t batch, heads, seq_len;
+  int32_t head_dim, kernel_size, dtype, layout;
+  const void* v;
+  const void* base;
+  void* result;
+  const float* weight;
+  int32_t transposed;
+  int32_t device;
+  void* stream;
+} fnb_conv_args;
+FNB_API int fnb_conv_residual(const fnb_conv_args* args);
+
+/* Gradient of the convolution residual with respect to the weights:
+ *     d_weight[h][j] = sum over b, n, d of d_out[b,h,n,d] * v[b,h,n + j - kernel_size/2,d]
+ * (FP32, summed in a fixed order: two calls give identical bits).  workspace: device memory of at
+ * least fnb_conv_dweight_workspace_bytes(...) bytes, 16-byte aligned.  Two kernels on `stream`. */
+typedef struct fnb_conv_dw_args {
+  int64_t batch, heads, seq_len;
+  int32_t head_dim, kernel_size, dtype, layout;
+  const void* v;
+  const void* d_out;
+  float* d_weight;
+  void* workspace;
+  size_t workspace_bytes;
+  int32_t device;
+  void* stream;
+} fnb_conv_dw_args;
+FNB_API size_t fnb_conv_dweight_workspace_bytes(int64_t batch, int64_t heads, int64_t seq_len, int32_t kernel_size);
+FNB_API int fnb_conv_residual_dweight(const fnb_conv_dw_args* args);
+
 /* Tests only: the time limit of every bounded device-side wait on `device` (default 1500 ms),
  * so that a test of the expiry path does not take seconds.  1..10000 ms.  No counterpart in the
  * reference. */

@@ -80,3 +80,20 @@ def test_python_face_rejects_cpu_tensors():
 def test_kappa_validated_in_python_face():
     with pytest.raises(RuntimeError, match="kappa_star"):
         _C._shape_struct(1, 1, 64, 64, 16, 6, torch.float16, float("nan"))
+
+
+def test_conv_residual_argument_checks(lib):
+    """Shape and pointer checks of the convolution residual come before any device is touched."""
+    a = _lib.ConvArgs(1, 2, 64, 64, 4, _lib.FNB_F16, 0, 16, None, 32, 48, 0, 0, None)
+    assert lib.fnb_conv_residual(C.byref(a)) == -1 and "must be odd" in _lib.last_error()
+    a = _lib.ConvArgs(1, 2, 64, 48, 3, _lib.FNB_F16, 0, 16, None, 32, 48, 0, 0, None)
+    assert lib.fnb_conv_residual(C.byref(a)) == -1 and "head_dim must be" in _lib.last_error()
+    a = _lib.ConvArgs(1, 2, 64, 64, 3, _lib.FNB_F16, 0, 16, None, 16, 48, 0, 0, None)
+    assert lib.fnb_conv_residual(C.byref(a)) == -1 and "must not alias" in _lib.last_error()
+    a = _lib.ConvArgs(1, 2, 64, 64, 3, _lib.FNB_F16, 0, 8, None, 32, 48, 0, 0, None)
+    assert lib.fnb_conv_residual(C.byref(a)) == -1 and "16-byte aligned" in _lib.last_error()
+    assert lib.fnb_conv_dweight_workspace_bytes(2, 4, 1000, 33) == 256 * ((4 * 2 * 4 * 16 * 33 + 255) // 256)
+    assert lib.fnb_conv_dweight_workspace_bytes(2, 4, 1000, 0) == 0
+    d = _lib.ConvDwArgs(2, 4, 1000, 64, 33, _lib.FNB_F16, 0, 16, 32, 48, 64, 16, 0, None)
+    assert lib.fnb_conv_residual_dweight(C.byref(d)) != 0 and "workspace must be" in _lib.last_error()
+
