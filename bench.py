@@ -513,6 +513,11 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
+        # torchrun exports OMP_NUM_THREADS=1, and an OpenMP thread count set later from Python only
+        # reaches the calling thread, not the autograd engine's: give the CPU arm every core before
+        # the OpenMP runtime starts (torch is imported after this point)
+        os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
+        os.environ.pop("MKL_NUM_THREADS", None)
         run_reference(args, rank)
         return
 
