@@ -55,7 +55,10 @@ def layout_of(t):
         return None
     if t.is_contiguous():
         return _lib.FNB_LAYOUT_BHND
-    if t.transpose(1, 2).is_contiguous():
+    B, H, N, D = t.shape
+    if t.stride() == (N * H * D, D, H * D, 1):      # (strides alone: no view object is made)
+        return _lib.FNB_LAYOUT_BNHD
+    if t.transpose(1, 2).is_contiguous():           # sizes of 1 leave some strides arbitrary
         return _lib.FNB_LAYOUT_BNHD
     return None
 
@@ -82,6 +85,23 @@ def _to_layout(t, layout):
     if layout == _lib.FNB_LAYOUT_BNHD:
         return t.transpose(1, 2).contiguous().transpose(1, 2)
     return t.contiguous()
+
+
+class _NoContext:
+    def __enter__(self):
+        return None
+
+    def __exit__(self, *exc):
+        return False
+
+
+_NO_CONTEXT = _NoContext()
+
+
+def _on_device(dev):
+    """Context that makes `dev` current for the allocations of a call; nothing when it already is
+    (the library selects the device of its own work itself)."""
+    return _NO_CONTEXT if torch.cuda.current_device() == dev.index else torch.cuda.device(dev)
 
 
 def _shape_struct(B, H, N, D, m, J, dtype, kappa_star, layout=0):
@@ -166,7 +186,7 @@ def forward(q, k, v, num_landmarks=64, newton_iter=6, kappa_star=0.0, use_tc_pin
     _lib.check(lib.fnb_check_shape(C.byref(shp)))
     dev = q.device
     f32 = dict(dtype=torch.float32, device=dev)
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         out = _empty_like_layout(q, lay)
         lse1 = torch.empty(B, H, N, **f32)
         qt = torch.empty(B, H, m, D, **f32)
@@ -219,7 +239,7 @@ def backward(dO, q_s, k_s, q_tilde, k_tilde, kernel2_inv, step2, lse1, lse2, lse
     _check_big(lse3, "softmax3_lse", (B, H, m), f32)
     _check_big(ns_iterates, "ns_iterates", (B, H, J + 1, m, m), f32)
     dev = dO.device
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         dq, dk, dv = (_empty_like_layout(dO, lay) for _ in range(3))
         ws = _workspace(lib.fnb_bwd_workspace_bytes(C.byref(shp)), dev)
         args = _lib.BwdArgs(shp, _ptr(q_s), _ptr(k_s), _ptr(v), _ptr(dO), _ptr(lse1),
@@ -249,7 +269,7 @@ def debug_pinv_forward(k2, newton_iter, kappa_star=0.0):
     BH, m, _ = k2.shape
     J = int(newton_iter)
     dev = k2.device
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         iters = torch.empty(BH, J + 1, m, m, dtype=torch.float32, device=dev)
         k2inv = torch.empty_like(k2)
         ws = _workspace(lib.fnb_debug_pinv_workspace_bytes(BH, m), dev)
@@ -268,7 +288,7 @@ def debug_pinv_backward(k2, ns_iterates, d_k2_inv, kappa_star=0.0):
     _check_big(ns_iterates, "ns_iterates", (BH, J + 1, m, m), torch.float32)
     _check_big(d_k2_inv, "d_k2_inv", (BH, m, m), torch.float32)
     dev = k2.device
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         dk2 = torch.empty_like(k2)
         ws = _workspace(lib.fnb_debug_pinv_workspace_bytes(BH, m), dev)
         _lib.check(lib.fnb_debug_pinv_backward(BH, m, J, float(kappa_star), _ptr(k2),
@@ -289,7 +309,7 @@ def debug_ns_bwd_step(K2, Z_j, dZ_in):
         raise RuntimeError("K2, Z_j, dZ_in must all have shape (BH, m, m)")
     BH, m, _ = K2.shape
     dev = K2.device
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         dZ_out, dK2_acc = torch.empty_like(K2), torch.empty_like(K2)
         _lib.check(lib.fnb_debug_ns_bwd_step(BH, m, _ptr(K2), _ptr(Z_j), _ptr(dZ_in), _ptr(dZ_out), _ptr(dK2_acc),
                                              dev.index, C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)))
@@ -305,7 +325,7 @@ def debug_ns_bwd_final(q_tilde, k_tilde, K2, dZ0, dK2_in):
         _check_big(t, name, dtype=torch.float32)
     BH, m, D = q_tilde.shape
     dev = K2.device
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         dq, dk, dk2 = torch.empty_like(q_tilde), torch.empty_like(k_tilde), torch.empty_like(K2)
         zeros = torch.zeros(m, D, dtype=torch.float32, device=dev)
         _lib.check(lib.fnb_debug_ns_bwd_final(BH, m, D, _ptr(q_tilde), _ptr(k_tilde), _ptr(K2), _ptr(dZ0), _ptr(dK2_in),
@@ -405,7 +425,7 @@ def conv_residual(v, weight, base=None, transposed=False):
     args = _lib.ConvArgs(B, H, N, D, int(w.shape[1]), _DTYPES[v.dtype], int(layout), v.data_ptr(),
                          base.data_ptr() if base is not None else None, result.data_ptr(), w.data_ptr(),
                          1 if transposed else 0, v.device.index, torch.cuda.current_stream(v.device).cuda_stream)
-    with torch.cuda.device(v.device):
+    with _on_device(v.device):
         _lib.check(lib.fnb_conv_residual(C.byref(args)))
     return result
 
@@ -424,7 +444,7 @@ def conv_residual_dweight(v, d_out, kernel_size):
     args = _lib.ConvDwArgs(B, H, N, D, int(kernel_size), _DTYPES[v.dtype], int(layout), v.data_ptr(), d_out.data_ptr(),
                            dw.data_ptr(), ws.data_ptr(), ws.numel(), v.device.index,
                            torch.cuda.current_stream(v.device).cuda_stream)
-    with torch.cuda.device(v.device):
+    with _on_device(v.device):
         _lib.check(lib.fnb_conv_residual_dweight(C.byref(args)))
     return dw
 

@@ -9,6 +9,9 @@
 #include <cstring>
 #include <cmath>
 #include <vector>
+#include <map>
+#include <mutex>
+#include <utility>
 #include <string>
 
 #include "common.cuh"
@@ -146,11 +149,24 @@ struct Fork {
   ~Fork() { join(); }
 };
 
+// The two function attributes below are per kernel and device and stay until the context ends:
+// they are set once (again only if a later call needs more), not on every launch.
+static std::mutex g_smem_mutex;
+static std::map<std::pair<const void*, int>, size_t> g_smem_set;
+
 template <class K>
 static int set_smem(K kernel, size_t bytes, int max_optin, const char* name) {
   if ((long long)bytes > (long long)max_optin)
     return fail(FNB_ERR_SMEM, "insufficient smem for %s: needs %zu bytes, device allows %d", name,
                 bytes, max_optin);
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess) device = -1;
+  const std::pair<const void*, int> key(reinterpret_cast<const void*>(kernel), device);
+  if (device >= 0) {
+    std::lock_guard<std::mutex> lock(g_smem_mutex);
+    auto it = g_smem_set.find(key);
+    if (it != g_smem_set.end() && it->second >= bytes) return 0;
+  }
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
   // ask for the largest shared-memory carveout so that co-residency is limited by the kernel's
   // own footprint, not by the driver's default split between L1 and shared memory
@@ -159,6 +175,10 @@ static int set_smem(K kernel, size_t bytes, int max_optin, const char* name) {
   if (e != cudaSuccess)
     return fail(FNB_ERR_CUDA, "cudaFuncSetAttribute(%s, %zu) failed: %s", name, bytes,
                 cudaGetErrorString(e));
+  if (device >= 0) {
+    std::lock_guard<std::mutex> lock(g_smem_mutex);
+    g_smem_set[key] = bytes;
+  }
   return 0;
 }
 
