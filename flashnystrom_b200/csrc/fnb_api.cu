@@ -886,10 +886,10 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
       // (after the join with the side stream the event wait stays a full dependency; only the
       // dependency on the column pass is the programmatic one, as for the combine step of the forward)
       if (l2 & 4)
-        launch_pdl(kern, dim3(tgrid), dim3(tc::kTcThreads), sm, st, tm_dk, tm_dq, side_k, side_q, 2, scale * tc::kLog2e, sch_c,
+        launch_pdl(kern, dim3(tgrid), dim3(tc::RowsSmem<D, MPc>::kThreads), sm, st, tm_dk, tm_dq, side_k, side_q, 2, scale * tc::kLog2e, sch_c,
                    p.m, a.device_status);
       else
-        launch_pdl(kern, dim3(tgrid), dim3(tc::kTcThreads), sm, st, tm_dq, tm_dk, side_q, side_k, 2, scale * tc::kLog2e, sch_c,
+        launch_pdl(kern, dim3(tgrid), dim3(tc::RowsSmem<D, MPc>::kThreads), sm, st, tm_dq, tm_dk, side_q, side_k, 2, scale * tc::kLog2e, sch_c,
                    p.m, a.device_status);
       return L.end("tc_bwd_c");
       });
@@ -1296,7 +1296,7 @@ int fnb_kernel_report(int device, fnb_kernel_info* out, int cap) {
       {"tc_fwd_c<half,128,64>", (const void*)tc::tc_fwd_c_kernel<H, 128, 64>, tc::kTcThreads, tc::FwdCSmem<128, 64>::kBytes},
       {"tc_bwd_a<half,128,64>", (const void*)tc::tc_bwd_a_kernel<H, 128, 64>, tc::kTcThreads, tc::BwdASmem<128, 64>::kBytes},
       {"tc_bwd_b<half,128,64>", (const void*)tc::tc_bwd_b_kernel<H, 128, 64>, tc::kTcThreads, tc::BwdBSmem<128, 64>::kBytes},
-      {"tc_rows_inplace<half,128,64>", (const void*)tc::tc_rows_inplace_kernel<H, 128, 64>, tc::kTcThreads, tc::RowsSmem<128, 64>::kBytes},
+      {"tc_rows_inplace<half,128,64>", (const void*)tc::tc_rows_inplace_kernel<H, 128, 64>, tc::RowsSmem<128, 64>::kThreads, tc::RowsSmem<128, 64>::kBytes},
   };
   int n = 0;
   for (const KernelEntry& k : ks) {

@@ -699,9 +699,9 @@ tc_bwd_a_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 //   side 1:  dK = (2^-k ln2) dS3' (s log2e Qt) + rows_k[l(n)]
 // with one TMA load, one product and one TMA store; no exponentials, and Q, K, dO are not read
 // again.  A CTA takes its run of tiles on side 0, then the same run on side 1.  Four input stages
-// (released by the product's commit), four accumulators, two compute groups of 128 threads (one
-// thread per tile row) that take alternate tiles and stage their output tile in a buffer of their
-// own.
+// (released by the product's commit), four accumulators, compute groups of 128 threads (one thread
+// per tile row; two groups, or four for head_dim 128 with up to 64 landmarks) that take the tiles in
+// turn and stage their output tile in a buffer of their own.
 struct RowsSide {
   const float* landmarks;   // [BH][m][D] FP32: the landmark matrix the tile is multiplied by
   float* rows;              // [BH][m][D] FP32: per-landmark term added to every row of its segment
@@ -722,9 +722,16 @@ struct RowsSide {
 template <int D, int MP>
 struct RowsSmem {
   static constexpr int kStages = MP == 128 ? 2 : 4;   // 128-landmark tiles are twice as large
+  // Compute groups of 128 threads (one thread per tile row) that take tiles in turn.  head_dim 128 with
+  // up to 64 landmarks runs one CTA per SM, whose epilogue per tile is twice that of head_dim 64: four
+  // groups (one per stage) instead of two keep as many tiles in flight as two CTAs of head_dim 64 do.
+  static constexpr int kGroups = (D == 128 && MP == 64) ? 4 : 2;
+  static constexpr int kThreads = (kGroups * 4 + 2) * 32;   // compute warps, TMA producer, MMA issuer
   static constexpr int kOp = MP * D * 2, kIn = kTile * MP * 2, kOut = kTile * D * 2;
   // relies on the dynamic shared window being 1024-byte aligned (checked at run time)
-  static constexpr int kBytes = 2 * kOp + kStages * kIn + 2 * kOut + 256;
+  static constexpr int kBytes = 2 * kOp + kStages * kIn + kGroups * kOut + 256;
+  static_assert(kStages % kGroups == 0, "a group always works on the same stages");
+  static_assert(kBytes <= 227 * 1024, "shared memory");
 };
 
 // 16-bit swizzled operand tile of one FP32 (m x D) landmark matrix (MP rows, rows >= m zero; D / 64
@@ -749,7 +756,7 @@ __device__ __forceinline__ void pack_landmark_operand(uint8_t* tile, const float
 }
 
 template <class T, int D, int MP>
-__global__ void __launch_bounds__(kTcThreads, (D == 64 ? 2 : 1))
+__global__ void __launch_bounds__((RowsSmem<D, MP>::kThreads), (D == 64 ? 2 : 1))
 tc_rows_inplace_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                        RowsSide side_a, RowsSide side_b, int nsides, float op_mul, TcSched sch, int m,
                        int* status) {
@@ -758,11 +765,11 @@ tc_rows_inplace_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_co
   TC_SPAN(0);
   // a parked dS tile (MP columns) sits in the first MP columns of the gradient tile of its rows
   static_assert((D == 64 && MP == 64) || (D == 128 && (MP == 64 || MP == 128)), "head_dim 64 with up to 64 landmarks, 128 with up to 128");
-  constexpr int kGroup = kComputeThreads / 2;
+  constexpr int kGroup = 128, kGroups = L::kGroups, kCompute = kGroups * kGroup;
+  constexpr int kProducer = kGroups * 4, kIssuer = kGroups * 4 + 1;   // warp numbers of the two single-thread roles
   constexpr int kStages = L::kStages;
   constexpr uint32_t kTmemCols = kStages * D;
   static_assert(kTmemCols == 256 || kTmemCols == 512, "TMEM allocation must be a power of two");
-  static_assert(kStages % 2 == 0, "the two compute groups take alternate tiles and stages");
   extern __shared__ uint8_t smem_raw[];
   pdl_trigger();
   if (smem_u32(smem_raw) & 1023u) {
@@ -772,7 +779,7 @@ tc_rows_inplace_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_co
   uint8_t* s_op = smem_raw;                    // one operand tile per side
   uint8_t* s_in = s_op + 2 * L::kOp;           // kStages dS tiles
   uint8_t* s_out = s_in + kStages * L::kIn;    // one staging tile per group
-  uint64_t* bars = reinterpret_cast<uint64_t*>(s_out + 2 * L::kOut);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(s_out + kGroups * L::kOut);
   uint64_t* small_full = bars + 0;
   uint64_t* in_full = bars + 1;                // [kStages]
   uint64_t* in_empty = bars + 1 + kStages;     // [kStages]
@@ -789,7 +796,7 @@ tc_rows_inplace_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_co
   const int count = tra.count, total = count + (nsides > 1 ? trb.count : 0);
 
   if (threadIdx.x == 0) {
-    mbar_init(small_full, kComputeThreads / 32);
+    mbar_init(small_full, kComputeThreads / 32);   // the first eight warps pack the operands
     for (int s = 0; s < kStages; ++s) {
       mbar_init(in_full + s, 1); mbar_init(in_empty + s, 1);
       mbar_init(acc_done + s, 1); mbar_init(o_free + s, kGroup / 32);
@@ -809,7 +816,7 @@ tc_rows_inplace_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_co
   const uint32_t tmem_base = *tmem_slot;
   Abort ab{abort_word, status};
 
-  if (warp == kProducerWarp) {
+  if (warp == kProducer) {
     if (lane == 0) {
       tma_prefetch_desc(&tm_a);
       if (nsides > 1) tma_prefetch_desc(&tm_b);
@@ -828,7 +835,7 @@ tc_rows_inplace_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_co
       if (ab.raised())
         for (int i = max(0, armed - kStages); i < armed; ++i) mbar_drain(in_full + (i % kStages), (i / kStages) & 1);
     }
-  } else if (warp == kMmaWarp) {
+  } else if (warp == kIssuer) {
     if (lane == 0) {
       constexpr uint32_t idesc_o = make_idesc<T>(kTile, D, false, true);
       const uint32_t a_op = smem_u32(s_op);
@@ -855,10 +862,12 @@ tc_rows_inplace_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_co
     const int g = warp >> 2;
     const int r = threadIdx.x & 127;
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-    pack_landmark_operand<T, D, MP>(s_op, side_a.landmarks + bh * m * D, m, op_mul);
-    if (nsides > 1) pack_landmark_operand<T, D, MP>(s_op + L::kOp, side_b.landmarks + bh * m * D, m, op_mul);
-    fence_proxy_async();
-    mbar_arrive_warp(small_full);
+    if (threadIdx.x < kComputeThreads) {   // (uniform per warp)
+      pack_landmark_operand<T, D, MP>(s_op, side_a.landmarks + bh * m * D, m, op_mul);
+      if (nsides > 1) pack_landmark_operand<T, D, MP>(s_op + L::kOp, side_b.landmarks + bh * m * D, m, op_mul);
+      fence_proxy_async();
+      mbar_arrive_warp(small_full);
+    }
     const float mul_a = (side_a.out_scale ? side_a.out_scale[bh] : 1.f) * side_a.out_mul;
     const float mul_b = nsides > 1 ? (side_b.out_scale ? side_b.out_scale[bh] : 1.f) * side_b.out_mul : 0.f;
     uint8_t* my_out = s_out + g * L::kOut;
@@ -874,7 +883,7 @@ tc_rows_inplace_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_co
       const int64_t last = sch.row_offset + min((int64_t)(t.highest() + 1) * kTile, sch.N) - 1;
       const int l_lo = sg.landmark_of(first), nl = sg.landmark_of(last) - l_lo + 1;
       const int md = m * D;
-      for (int item = threadIdx.x; item < nl * (D / 4); item += kComputeThreads) {
+      for (int item = threadIdx.x; item < nl * (D / 4); item += kCompute) {
         const int l = l_lo + item / (D / 4), d = (item % (D / 4)) * 4;
         const float* src = sd.part + bh * (int64_t)sd.nchunk * md + l * D + d;
         float4 acc = *reinterpret_cast<const float4*>(sd.base + bh * md + l * D + d);
@@ -889,9 +898,9 @@ tc_rows_inplace_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_co
     presum(side_a, tra);
     if (nsides > 1) presum(side_b, trb);
     if (side_a.part || (nsides > 1 && side_b.part))
-      named_barrier(3, kComputeThreads);   // the stores above are visible to the CTA's epilogue reads
-    for (int i = g; i < total; i += 2) {
-      if (i == 2) TC_SPAN(3);
+      named_barrier(5, kCompute);   // the stores above are visible to the CTA's epilogue reads
+    for (int i = g; i < total; i += kGroups) {
+      if (i == kGroups) TC_SPAN(3);
       const int s = i % kStages;
       const uint32_t par = (uint32_t)(i / kStages) & 1u;
       const bool second = i >= count;
