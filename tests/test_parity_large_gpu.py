@@ -111,6 +111,16 @@ def test_many_slices_many_tiles_bf16(cuda_device):
     _check_slices(cu, q, k, v, dO, m, J, 0.0, [0, 17, 39], 8e-3, 4e-2, stage_scale=8.0)
 
 
+@pytest.mark.parametrize("D,m", [(64, 64), (128, 64)])
+def test_more_slices_than_resident_ctas(cuda_device, D, m):
+    """B*H = 512 slices: one CTA per slice and more CTAs than the GPU holds at once, so the grid of
+    every tensor-core kernel runs in several waves (the first, the last and two middle slices
+    against the oracle)."""
+    q, k, v, dO = O.make_inputs(32, 16, 2048, D, seed=41, dtype=torch.float16)
+    cu = run_cuda(q, k, v, dO, m, 6, 0.0)
+    _check_slices(cu, q, k, v, dO, m, 6, 0.0, [0, 147, 300, 511], 2e-3, 1e-2)
+
+
 def test_config2_module_full_shape(cuda_device):
     """The module configuration: dim 512, 8 heads (D = 64), B=4, N=4096, num_landmarks 64, conv
     residual k=3, fp16 weights and activations, y.sum().backward(); against the same module
