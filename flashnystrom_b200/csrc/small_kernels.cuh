@@ -223,36 +223,45 @@ struct BwdMid1Params {
 };
 
 __host__ __device__ inline size_t bwd_mid1_smem(int m, int D) {
-  return sizeof(float) * ((size_t)m * D + (size_t)m * (D + 4) + (size_t)m * D);
+  return sizeof(float) * (2 * (size_t)m * (D + 4) + (size_t)m * D + (size_t)m * (m + 1));
 }
 
 template <int NV>
 __global__ void __launch_bounds__(kThreads) bwd_mid1_kernel(BwdMid1Params p) {
+  // NV = D / 16.  Shared memory (bwd_mid1_smem): dstep2 [m][D+4], Bmat [m][D+4], dO3 [m][D],
+  // K2inv [m][m+1].  Both products are register-tiled (thread (ty, tx) of a 16 x 16 grid owns rows
+  // ty + 16 i and columns tx + 16 j), with padded rows so that a warp's shared loads spread over
+  // the banks.
   extern __shared__ float sm[];
   __shared__ float red[8];
   const int64_t bh = blockIdx.x;
-  const int m = p.m, D = p.D, t = threadIdx.x, nc = p.nchunk, md = m * D, ldb = D + 4;
-  constexpr int nv = NV;
+  const int m = p.m, D = p.D, t = threadIdx.x, nc = p.nchunk, md = m * D, ldb = D + 4, ldk = m + 1;
   constexpr int CB = NV <= 2 ? 8 : (NV == 4 ? 4 : 2);
-  const int q = t & 3, dpt = D >> 2, d0 = q * dpt;
-  float* ds = sm;                    // dstep2 [m][D]
-  float* bm = ds + md;               // Bmat   [m][D+4]
+  const int q = t & 3;
+  float* ds = sm;                    // dstep2 [m][ldb]
+  float* bm = ds + m * ldb;          // Bmat   [m][ldb]
   float* do3 = bm + m * ldb;         // dO3    [m][D]
+  float* sK = do3 + md;              // K2inv  [m][ldk]
   const float* partA = p.partA + bh * (int64_t)nc * 2 * md;
   const float* bmat = p.bmat + bh * (int64_t)md;
+  const float* k2inv = p.k2inv + bh * m * m;
+  for (int idx = t; idx < m * m; idx += kThreads) sK[(idx / m) * ldk + idx % m] = k2inv[idx];
+  // chunk sums of (dstep2, dKt): thread = (row l, interleaved float4 columns 4 q + 16 v)
   for (int l = t >> 2; l < m; l += kThreads / 4) {
-    float4 a0[8], a1[8];
+    float4 a0[NV], a1[NV];
 #pragma unroll
-    for (int v = 0; v < 8; ++v) { a0[v] = make_float4(0, 0, 0, 0); a1[v] = make_float4(0, 0, 0, 0); }
+    for (int v = 0; v < NV; ++v) { a0[v] = make_float4(0, 0, 0, 0); a1[v] = make_float4(0, 0, 0, 0); }
     for (int c0 = 0; c0 < nc; c0 += CB) {
       float4 x[CB][NV], y[CB][NV];
 #pragma unroll
       for (int i = 0; i < CB; ++i) {
         const int c = min(c0 + i, nc - 1);
-        const float4* s0 = reinterpret_cast<const float4*>(partA + (size_t)c * 2 * md + l * D + d0);
-        const float4* s1 = reinterpret_cast<const float4*>(partA + (size_t)c * 2 * md + md + l * D + d0);
+        const float* s0 = partA + (size_t)c * 2 * md + l * D + 4 * q;
 #pragma unroll
-        for (int v = 0; v < NV; ++v) { x[i][v] = s0[v]; y[i][v] = s1[v]; }
+        for (int v = 0; v < NV; ++v) {
+          x[i][v] = *reinterpret_cast<const float4*>(s0 + 16 * v);
+          y[i][v] = *reinterpret_cast<const float4*>(s0 + md + 16 * v);
+        }
       }
 #pragma unroll
       for (int i = 0; i < CB; ++i) {
@@ -265,71 +274,96 @@ __global__ void __launch_bounds__(kThreads) bwd_mid1_kernel(BwdMid1Params p) {
         }
       }
     }
-    float4* dd = reinterpret_cast<float4*>(ds + l * D + d0);
-    float4* dk = reinterpret_cast<float4*>(p.dkt_a + bh * md + l * D + d0);
-    float4* db = reinterpret_cast<float4*>(bm + l * ldb + d0);
-    const float4* sb = reinterpret_cast<const float4*>(bmat + l * D + d0);
 #pragma unroll
-    for (int v = 0; v < 8; ++v)
-      if (v < nv) {
-        dd[v] = a0[v]; db[v] = sb[v];
-        if (p.dkt_a) dk[v] = a1[v];
-      }
+    for (int v = 0; v < NV; ++v) {
+      const int d = 4 * q + 16 * v;
+      *reinterpret_cast<float4*>(ds + l * ldb + d) = a0[v];
+      *reinterpret_cast<float4*>(bm + l * ldb + d) = *reinterpret_cast<const float4*>(bmat + l * D + d);
+      if (p.dkt_a) *reinterpret_cast<float4*>(p.dkt_a + bh * md + l * D + d) = a1[v];
+    }
   }
   __syncthreads();
-  const float* k2inv = p.k2inv + bh * m * m;
+  const int tx = t & 15, ty = t >> 4;
+  const int MI = (m + 15) >> 4;
   float amax = 0.f;
+  {
+    // dO3[l][d] = sum_k K2inv[k][l] dstep2[k][d]:  rows l = ty + 16 i, columns d = tx + 16 j
+    float acc[4][NV];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < NV; ++j) acc[i][j] = 0.f;
+#pragma unroll 2
+    for (int k = 0; k < m; ++k) {
+      float a[4], b[NV];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[i] = (i < MI && ty + 16 * i < m) ? sK[k * ldk + ty + 16 * i] : 0.f;
+#pragma unroll
+      for (int j = 0; j < NV; ++j) b[j] = ds[k * ldb + tx + 16 * j];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < NV; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int l = ty + 16 * i;
+      if (l < m) {
+#pragma unroll
+        for (int j = 0; j < NV; ++j) {
+          const int d = tx + 16 * j;
+          do3[l * D + d] = acc[i][j];
+          if (p.dO3) p.dO3[bh * md + l * D + d] = acc[i][j];
+          amax = fmaxf(amax, fabsf(acc[i][j]));
+        }
+      }
+    }
+  }
+  if (p.G) {
+    // G[l][j] = sum_d dstep2[l][d] Bmat[j][d]:  rows l = ty + 16 i, columns j = tx + 16 jj
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+#pragma unroll 2
+    for (int d = 0; d < D; d += 4) {
+      float4 a[4], b[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        a[i] = (ty + 16 * i < m) ? *reinterpret_cast<const float4*>(ds + (ty + 16 * i) * ldb + d) : make_float4(0, 0, 0, 0);
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        b[j] = (tx + 16 * j < m) ? *reinterpret_cast<const float4*>(bm + (tx + 16 * j) * ldb + d) : make_float4(0, 0, 0, 0);
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          acc[i][j] += (a[i].x * b[j].x + a[i].y * b[j].y) + (a[i].z * b[j].z + a[i].w * b[j].w);
+    }
+    float* G = p.G + bh * m * m;
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (ty + 16 * i < m && tx + 16 * j < m) G[(ty + 16 * i) * m + tx + 16 * j] = acc[i][j];
+  }
+  __syncthreads();   // dO3 is complete in shared memory
+  // D3[l] = sum_d dO3[l][d] Bmat[l][d]: four threads per row
   for (int l0 = 0; l0 < m; l0 += kThreads / 4) {
-    // The trip count is uniform across the warp (the row loop contains warp shuffles); lanes
-    // past the last row recompute row m-1 and skip the stores.
     const bool act = l0 + (t >> 2) < m;
     const int l = act ? l0 + (t >> 2) : m - 1;
-    // dO3[l][:] = sum_k K2inv[k][l] dstep2[k][:]
-    float4 acc[8];
-#pragma unroll
-    for (int v = 0; v < 8; ++v) acc[v] = make_float4(0, 0, 0, 0);
-#pragma unroll 4
-    for (int k = 0; k < m; ++k) {
-      const float a = k2inv[k * m + l];
-      const float4* b = reinterpret_cast<const float4*>(ds + k * D + d0);
-#pragma unroll
-      for (int v = 0; v < 8; ++v)
-        if (v < nv) {
-          const float4 x = b[v];
-          acc[v].x = fmaf(a, x.x, acc[v].x); acc[v].y = fmaf(a, x.y, acc[v].y);
-          acc[v].z = fmaf(a, x.z, acc[v].z); acc[v].w = fmaf(a, x.w, acc[v].w);
-        }
-    }
     float d3 = 0.f;
-    float4* dg = reinterpret_cast<float4*>(p.dO3 + bh * md + l * D + d0);
-    float4* dsm = reinterpret_cast<float4*>(do3 + l * D + d0);
-    const float4* bb = reinterpret_cast<const float4*>(bm + l * ldb + d0);
 #pragma unroll
-    for (int v = 0; v < 8; ++v)
-      if (v < nv) {
-        if (act) {
-          dsm[v] = acc[v];
-          if (p.dO3) dg[v] = acc[v];
-        }
-        const float4 x = bb[v];
-        d3 += acc[v].x * x.x + acc[v].y * x.y + acc[v].z * x.z + acc[v].w * x.w;
-        amax = fmaxf(amax, fmaxf(fmaxf(fabsf(acc[v].x), fabsf(acc[v].y)), fmaxf(fabsf(acc[v].z), fabsf(acc[v].w))));
-      }
+    for (int v = 0; v < NV; ++v) {
+      const int d = 4 * q + 16 * v;
+      const float4 x = *reinterpret_cast<const float4*>(do3 + l * D + d);
+      const float4 y = *reinterpret_cast<const float4*>(bm + l * ldb + d);
+      d3 += (x.x * y.x + x.y * y.y) + (x.z * y.z + x.w * y.w);
+    }
     d3 += __shfl_xor_sync(0xffffffffu, d3, 1);
     d3 += __shfl_xor_sync(0xffffffffu, d3, 2);
     if (q == 0 && act) p.D3[bh * m + l] = d3;
-    // G[l][j] = sum_d dstep2[l][d] Bmat[j][d],  j = q, q+4, ...
-    float* Gr = p.G + bh * m * m + l * m;
-    for (int j = q; p.G && j < m; j += 4) {
-      const float4* a = reinterpret_cast<const float4*>(ds + l * D);
-      const float4* b = reinterpret_cast<const float4*>(bm + j * ldb);
-      float s = 0.f;
-      for (int v = 0; v < (D >> 2); ++v) {
-        const float4 x = a[v], y = b[v];
-        s += x.x * y.x + x.y * y.y + x.z * y.z + x.w * y.w;
-      }
-      if (act) Gr[j] = s;
-    }
   }
   if (p.dtype == 0) return;
   const float sc = pow2_scale(cta_max(amax, red));   // barrier inside: do3 is complete
@@ -337,15 +371,34 @@ __global__ void __launch_bounds__(kThreads) bwd_mid1_kernel(BwdMid1Params p) {
   const float inv_sc = 1.f / sc;
   const int MP = p.MP;
   const size_t ob = (size_t)bh * MP * D * 2;
-  for (int idx = t; idx < MP * D; idx += kThreads)
-    store16(reinterpret_cast<char*>(p.do3n) + ob, p.dtype, idx, (idx / D) < m ? do3[idx] * inv_sc : 0.f);
+  const float* qt = p.q_landmarks + bh * (int64_t)md;
+  // 16-bit copies, eight elements (one 16-byte store) at a time: dO3 / scale and qt_mul * Qt, rows >= m zero
+  auto pack8 = [&](const float* x, float mul) {
+    uint4 w;
+    uint32_t* u = reinterpret_cast<uint32_t*>(&w);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float a = x ? x[2 * e] * mul : 0.f, b = x ? x[2 * e + 1] * mul : 0.f;
+      if (p.dtype == 1) { __half2 h = __floats2half2_rn(a, b); u[e] = *reinterpret_cast<uint32_t*>(&h); }
+      else { __nv_bfloat162 h = __floats2bfloat162_rn(a, b); u[e] = *reinterpret_cast<uint32_t*>(&h); }
+    }
+    return w;
+  };
+  for (int idx = t; idx < MP * D / 8; idx += kThreads) {
+    const int r = (idx * 8) / D, c = idx * 8 - r * D;
+    reinterpret_cast<uint4*>(reinterpret_cast<char*>(p.do3n) + ob)[idx] = pack8(r < m ? do3 + r * D + c : nullptr, inv_sc);
+    float qv[8];
+    if (r < m) {
+      const float4 x = *reinterpret_cast<const float4*>(qt + r * D + c), y = *reinterpret_cast<const float4*>(qt + r * D + c + 4);
+      qv[0] = x.x; qv[1] = x.y; qv[2] = x.z; qv[3] = x.w; qv[4] = y.x; qv[5] = y.y; qv[6] = y.z; qv[7] = y.w;
+    }
+    reinterpret_cast<uint4*>(reinterpret_cast<char*>(p.qt16) + ob)[idx] = pack8(r < m ? qv : nullptr, p.qt_mul);
+  }
   if (p.do3T)
     for (int idx = t; idx < D * MP; idx += kThreads) {
       int d = idx / MP, l = idx - d * MP;
       store16(reinterpret_cast<char*>(p.do3T) + ob, p.dtype, idx, l < m ? do3[l * D + d] * inv_sc : 0.f);
     }
-  const float* qt = p.q_landmarks + bh * (int64_t)md;
-  pack_pair(qt, reinterpret_cast<char*>(p.qt16) + ob, nullptr, p.dtype, m, D, MP, p.qt_mul);
   if (p.qtT16) pack_pair(qt, nullptr, reinterpret_cast<char*>(p.qtT16) + ob, p.dtype, m, D, MP, p.qtT_mul);
 }
 
