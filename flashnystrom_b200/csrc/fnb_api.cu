@@ -757,7 +757,8 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
       np.m = p.m; np.D = p.D; np.J = p.J; np.kappa = a.shape.kappa_star;
       np.rows_k = use_tc ? w.rows_k : nullptr; np.N = seg_N; np.scale = scale;
       if (p.J >= 1 && ns_on_tensor_cores(a.shape.flags)) {
-        if (int rc = set_smem(nstc::ns_bwd_tc_kernel, nstc::kBwdSmem, max_smem, "ns_bwd")) return rc;
+        auto ns_kern = p.D == 128 ? nstc::ns_bwd_tc_kernel<2> : nstc::ns_bwd_tc_kernel<1>;
+        if (int rc = set_smem(ns_kern, nstc::kBwdSmem, max_smem, "ns_bwd")) return rc;
         nstc::BwdHeadParams hp{};
         if (fused_mid) {
           hp.partA = fused_pa; hp.nchunk = fused_pa_chunks; hp.k2inv = a.k2_inv; hp.bmat = a.bmat;
@@ -765,9 +766,9 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
           hp.qt16 = qt16; hp.qt_mul = scale * tc::kLog2e; hp.dtype = a.shape.dtype; hp.MP = MP;
         }
         if (side_ns)
-          nstc::ns_bwd_tc_kernel<<<(unsigned)p.BH, nstc::kNsTcThreads, nstc::kBwdSmem, ns_stream>>>(np, hp, a.device_status);
+          ns_kern<<<(unsigned)p.BH, nstc::kNsTcThreads, nstc::kBwdSmem, ns_stream>>>(np, hp, a.device_status);
         else
-          launch_pdl(nstc::ns_bwd_tc_kernel, dim3((unsigned)p.BH), dim3(nstc::kNsTcThreads), nstc::kBwdSmem, st, np, hp, a.device_status);
+          launch_pdl(ns_kern, dim3((unsigned)p.BH), dim3(nstc::kNsTcThreads), nstc::kBwdSmem, st, np, hp, a.device_status);
       } else {
         if (int rc = set_smem(ns::ns_bwd_kernel, ns::kBwdSmem, max_smem, "ns_bwd")) return rc;
         ns::ns_bwd_kernel<<<(unsigned)p.BH, kThreads, ns::kBwdSmem, st>>>(np);
@@ -1288,7 +1289,8 @@ int fnb_kernel_report(int device, fnb_kernel_info* out, int cap) {
       {"tc_fwd_c<half,64,64>", (const void*)tc::tc_fwd_c_kernel<H, 64, 64>, tc::kTcThreads, tc::FwdCSmem<64, 64>::kBytes},
       {"tc_bwd_a<half,64,64>", (const void*)tc::tc_bwd_a_kernel<H, 64, 64>, tc::kTcThreads, tc::BwdASmem<64, 64>::kBytes},
       {"reduce_chunks", (const void*)reduce_chunks_kernel, kThreads, 0},
-      {"ns_bwd_tc", (const void*)nstc::ns_bwd_tc_kernel, nstc::kNsTcThreads, nstc::kBwdSmem},
+      {"ns_bwd_tc", (const void*)nstc::ns_bwd_tc_kernel<1>, nstc::kNsTcThreads, nstc::kBwdSmem},
+      {"ns_bwd_tc_d128", (const void*)nstc::ns_bwd_tc_kernel<2>, nstc::kNsTcThreads, nstc::kBwdSmem},
       {"colpass_operands", (const void*)colpass_operands_kernel, kThreads, (size_t)kColpassOperandSmem},
       {"tc_bwd_b<half,64,64>", (const void*)tc::tc_bwd_b_kernel<H, 64, 64>, tc::kTcThreads, tc::BwdBSmem<64, 64>::kBytes},
       {"tc_rows_inplace<half,64,64>", (const void*)tc::tc_rows_inplace_kernel<H, 64, 64>, tc::kTcThreads, tc::RowsSmem<64, 64>::kBytes},

@@ -512,7 +512,8 @@ ns_pinv_fwd_tc_debug_kernel(const float* k2, float* iterates, float* k2inv, int 
 // tensor core.  The next iterate is fetched into registers a whole iteration ahead.  With the
 // ridge the FP32 set-up (K2, A, Z_J, dZ_J) is staged in slots 5..7; after the loop the tail
 // works in FP32 buffers at the start of the slot area.  A last batch (head_dim 64 only) forms the
-// landmark gradients dqt_ns = dS2 Kt and dS2^T Qt from slots 5 (dS2), 6 (Kt), 7 (Qt).
+// landmark gradients dqt_ns = dS2 Kt and dS2^T Qt from slots 5 (dS2), 6 (Kt), 7 (Qt); head_dim 128
+// runs it twice, once per 64 columns of Kt and Qt.
 constexpr int kBwdStageSlot = 5;
 __device__ __forceinline__ float* bwd_stage(const Ctx& c, int i) {
   return reinterpret_cast<float*>(c.slot(kBwdStageSlot)) + (size_t)i * kBuf;
@@ -522,7 +523,7 @@ __device__ __forceinline__ float* bwd_tail(const Ctx& c, int i) {
 }
 
 // issuing thread
-__device__ inline void pinv_backward_issue(Ctx& c, int J, bool finish, bool head) {
+__device__ inline void pinv_backward_issue(Ctx& c, int J, int finish, bool head) {
   if (head) {
     // dO3 = K2inv^T dstep2 | dK2inv = dstep2 Bmat^T   (slots 3 K2inv, 4 dstep2, 6 Bmat)
     const uint32_t sKi = c.slot_addr(3), sDs = c.slot_addr(4), sBm = c.slot_addr(6);
@@ -552,7 +553,7 @@ __device__ inline void pinv_backward_issue(Ctx& c, int J, bool finish, bool head
               },
               [&] { issue_product(acc1, left(sdM), right_t(sZ), false); });
   }
-  if (finish) {
+  for (int half = 0; half < finish; ++half) {
     const uint32_t sS = c.slot_addr(5), sK = c.slot_addr(6), sQ = c.slot_addr(7);
     mma_batch(c, 0x2204, [&] { issue_product(acc0, left(sS), right(sK), false); },
               [&] { issue_product(acc1, left_t(sS), right(sQ), false); });
@@ -699,17 +700,20 @@ ns_pinv_bwd_tc_debug_kernel(const float* k2, const float* iterates, const float*
   ctx_close(c, kBwdTmemCols);
 }
 
-// Softmax-2 Jacobian and the landmark gradients after the pseudoinverse backward, for head_dim 64:
-// dqt_ns = dS2 Kt and dkt_tot = dkt_a + dS2^T Qt as one more batch of split products.
+// Softmax-2 Jacobian and the landmark gradients after the pseudoinverse backward, for head_dim 64
+// and 128: dqt_ns = dS2 Kt and dkt_tot = dkt_a + dS2^T Qt as one more batch of split products per
+// 64 columns of the landmarks.
 // bK2, dK2: padded FP32 buffers inside the tail area (slots 0..4); slots 5..7 take the operands.
 struct FinishOperands { float kt[16], qt[16], da[16]; };
-// global loads of the finishing step, issued early so that their latency hides behind the tail
-__device__ __forceinline__ void finish_load(const Ctx& c, const ns::NsBwdParams& p, int64_t bh, FinishOperands& f) {
+// global loads of the finishing step for columns [64 half, 64 half + 64); the first half is issued
+// early so that its latency hides behind the tail
+__device__ __forceinline__ void finish_load(const Ctx& c, const ns::NsBwdParams& p, int64_t bh, int half,
+                                            FinishOperands& f) {
   const int m = p.m, D = p.D, md = m * D;
-  load_global16(p.kt + bh * md, m, D, D, f.kt);
-  load_global16(p.qt + bh * md, m, D, D, f.qt);
+  load_global16(p.kt + bh * md + half * kN, m, kN, D, f.kt);
+  load_global16(p.qt + bh * md + half * kN, m, kN, D, f.qt);
   // dkt_a for the row segment this thread finalises
-  const float* src = p.dkt_a + bh * md + (size_t)c.row * D + c.col0;
+  const float* src = p.dkt_a + bh * md + (size_t)c.row * D + half * kN + c.col0;
 #pragma unroll
   for (int i = 0; i < 16; i += 4) {
     float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -717,10 +721,10 @@ __device__ __forceinline__ void finish_load(const Ctx& c, const ns::NsBwdParams&
     f.da[i] = x.x; f.da[i + 1] = x.y; f.da[i + 2] = x.z; f.da[i + 3] = x.w;
   }
 }
+template <int NH>
 __device__ inline void ns_bwd_finish_tc(Ctx& c, const ns::NsBwdParams& p, int64_t bh, const float* bK2, float* dK2,
-                                        const FinishOperands& f) {
+                                        FinishOperands& f) {
   const int m = p.m, D = p.D, md = m * D, t = threadIdx.x;
-  const float* kt = f.kt; const float* qt = f.qt; const float* da = f.da;
   // softmax-2 Jacobian in place: dS2 = K2 o (dK2 - rowsum(dK2 o K2))
   const int w = t >> 5, lane = t & 31;
   for (int r = w; r < kN; r += kComputeThreads / 32) {
@@ -733,25 +737,31 @@ __device__ inline void ns_bwd_finish_tc(Ctx& c, const ns::NsBwdParams& p, int64_
   }
   ns::ns_sync();
   convert_buf(c.slot(5), dK2);
-  store_set16(c.slot(6), kt);
-  store_set16(c.slot(7), qt);
-  tiles_ready(c);
-  float v[16];
-  wait_group(c, 0, 0x2214);
-  acc_result(c, kAcc0, v);
-  if (!c.failed) store_global16(c, p.dqt_ns + bh * md, v, m, D, D);
-  wait_group(c, 1, 0x2224);
-  acc_result(c, kAcc1, v);
-  if (c.failed) return;
 #pragma unroll
-  for (int i = 0; i < 16; ++i) v[i] += da[i];
-  store_global16(c, p.dkt_tot + bh * md, v, m, D, D);
-  if (p.rows_k && c.row < m) {
-    Segments sg(p.N, m);
-    const float f = p.scale / (float)sg.len(c.row);
+  for (int half = 0; half < NH; ++half) {
+    // every product that read slots 6 and 7 has been waited for below
+    if (half > 0) finish_load(c, p, bh, half, f);
+    store_set16(c.slot(6), f.kt);
+    store_set16(c.slot(7), f.qt);
+    tiles_ready(c);
+    const size_t off = (size_t)bh * md + half * kN;
+    float v[16];
+    wait_group(c, 0, 0x2214);
+    acc_result(c, kAcc0, v);
+    if (!c.failed) store_global16(c, p.dqt_ns + off, v, m, kN, D);
+    wait_group(c, 1, 0x2224);
+    acc_result(c, kAcc1, v);
+    if (c.failed) return;
 #pragma unroll
-    for (int i = 0; i < 16; ++i) v[i] *= f;
-    store_global16(c, p.rows_k + bh * md, v, m, D, D);
+    for (int i = 0; i < 16; ++i) v[i] += f.da[i];
+    store_global16(c, p.dkt_tot + off, v, m, kN, D);
+    if (p.rows_k && c.row < m) {
+      Segments sg(p.N, m);
+      const float fk = p.scale / (float)sg.len(c.row);
+#pragma unroll
+      for (int i = 0; i < 16; ++i) v[i] *= fk;
+      store_global16(c, p.rows_k + off, v, m, kN, D);
+    }
   }
 }
 
@@ -879,6 +889,9 @@ __device__ inline void bwd_head_tc(Ctx& c, float* red, const ns::NsBwdParams& p,
   NS_TRACE();
 }
 
+// NH: batches of the finishing step = head_dim / 64 for head_dim 64 and 128 (the instantiation with
+// NH = 1 also serves the smaller head dims, whose finishing step runs on the CUDA cores)
+template <int NH>
 __global__ void __launch_bounds__(kNsTcThreads, 1)
 ns_bwd_tc_kernel(ns::NsBwdParams p, BwdHeadParams h, int* status) {
   extern __shared__ uint8_t dyn_smem[];
@@ -895,16 +908,16 @@ ns_bwd_tc_kernel(ns::NsBwdParams p, BwdHeadParams h, int* status) {
   NS_TRACE();
   const int64_t bh = blockIdx.x;
   const int m = p.m, mm_ = m * m;
-  const bool finish_tc = p.D == kN;
+  const int finish_tc = p.D == NH * kN ? NH : 0;   // batches of the finishing step
   const bool head = h.partA != nullptr;      // fused middle stage (head_dim 64 only)
   if (is_compute()) {
     if (head) bwd_head_tc(c, red, p, h, bh);
     FinishOperands fo;
     float* dK2 = pinv_backward_tc(c, red, p.k2 + bh * mm_, p.iterates + bh * (size_t)(p.J + 1) * mm_,
                                   head ? nullptr : p.G + bh * mm_,
-                                  p.spill + bh * mm_, m, p.J, p.kappa, [&] { if (finish_tc) finish_load(c, p, bh, fo); });
+                                  p.spill + bh * mm_, m, p.J, p.kappa, [&] { if (finish_tc) finish_load(c, p, bh, 0, fo); });
     NS_TRACE();
-    if (finish_tc) ns_bwd_finish_tc(c, p, bh, bwd_tail(c, 0), dK2, fo);
+    if (finish_tc) ns_bwd_finish_tc<NH>(c, p, bh, bwd_tail(c, 0), dK2, fo);
     else if (!c.failed) ns::ns_bwd_finish(p, bh, bwd_tail(c, 0), dK2);
     NS_TRACE();
   } else if (is_issuer()) {
