@@ -46,6 +46,11 @@ SHAPES = [
     (1, 3, 200, 16, 5, 10, 0.0),
     # more slices than a quarter of the SMs: the backward runs without its side stream
     (5, 8, 384, 64, 24, 6, 0.0),
+    # head_dim 128 with the ridge (the shape family of the reference's published table), a landmark
+    # count that is no multiple of 16, and ragged segments
+    (2, 2, 1024, 128, 64, 6, 5.0),
+    (1, 3, 650, 128, 40, 6, 5.0),
+    (1, 2, 777, 128, 51, 4, 0.0),
 ]
 
 
