@@ -335,6 +335,31 @@ static cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, siz
   return cudaLaunchKernelEx(&cfg, kern, std::forward<Args>(args)...);
 }
 
+// Launch as thread-block clusters of `cs` CTAs along x (grid.x = number of clusters * cs).
+template <class... KArgs, class... Args>
+static cudaError_t launch_cluster(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, int cs,
+                                  Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeClusterDimension;
+  at[0].val.clusterDim.x = (unsigned)cs; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+  cfg.attrs = at; cfg.numAttrs = cs > 1 ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, std::forward<Args>(args)...);
+}
+
+// CTAs per slice of the landmark-sized kernels for more than 64 landmarks when their products run on
+// the tensor cores (a thread-block cluster shares every product by output columns).  FNB_MID_CLUSTER
+// in the environment at load overrides the default (1, 2 or 4; kept for A/B measurements).
+static int mid_cluster_size() {
+  static const int cs = [] {
+    const char* e = getenv("FNB_MID_CLUSTER");
+    const int v = e ? atoi(e) : 4;
+    return (v == 1 || v == 2 || v == 4) ? v : 4;
+  }();
+  return cs;
+}
+
 // The Newton-Schulz kernels for num_landmarks <= 64 run on the tensor cores (three-term bf16
 // split, FP32-equivalent) unless the caller forces the CUDA-core path or FNB_NS_CUDA_CORES=1 is
 // set in the environment (kept for A/B measurements).
@@ -490,7 +515,12 @@ static int forward_impl(const fnb_fwd_args& a, const Plan& p, const FwdWs& w, in
     const size_t mid_smem = mp.use_tc ? kTcGemmSmem : 0;
     if (mp.use_tc)
       if (int rc = set_smem(mid_fwd_kernel, mid_smem, max_smem, "mid_fwd")) return rc;
-    mid_fwd_kernel<<<(unsigned)p.BH, mp.use_tc ? kMidTcThreads : kThreads, mid_smem, st>>>(mp);
+    if (mp.use_tc) {
+      const int cs = mid_cluster_size();
+      FNB_CUDA(launch_cluster(mid_fwd_kernel, dim3((unsigned)(p.BH * cs)), dim3(kMidTcThreads), mid_smem, st, cs, mp));
+    } else {
+      mid_fwd_kernel<<<(unsigned)p.BH, kThreads, mid_smem, st>>>(mp);
+    }
     if (L.end("mid_fwd")) return L.status;
   }
 
@@ -802,7 +832,12 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
       const size_t mid_smem = mp.use_tc ? kTcGemmSmem : 0;
       if (mp.use_tc)
         if (int rc = set_smem(mid_bwd_kernel, mid_smem, max_smem, "mid_bwd")) return rc;
-      mid_bwd_kernel<<<(unsigned)p.BH, (mp.use_tc && !mp.first_half_only) ? kMidTcThreads : kThreads, mid_smem, st>>>(mp);
+      if (mp.use_tc && !mp.first_half_only) {
+        const int cs = mid_cluster_size();
+        FNB_CUDA(launch_cluster(mid_bwd_kernel, dim3((unsigned)(p.BH * cs)), dim3(kMidTcThreads), mid_smem, st, cs, mp));
+      } else {
+        mid_bwd_kernel<<<(unsigned)p.BH, kThreads, mid_smem, st>>>(mp);
+      }
     }
     if (L.end("mid_bwd")) return L.status;
     if (use_tc) {
@@ -1136,8 +1171,10 @@ int fnb_debug_pinv_forward(int64_t bh, int32_t m, int32_t J, float kappa, const 
     const int use_tc = ns_on_tensor_cores(0) ? 1 : 0;
     if (use_tc)
       FNB_CUDA(cudaFuncSetAttribute(pinv_fwd_debug_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcGemmSmem));
-    pinv_fwd_debug_kernel<<<(unsigned)bh, use_tc ? kMidTcThreads : kThreads, use_tc ? kTcGemmSmem : 0, (cudaStream_t)stream>>>(
-        k2, ns_iterates, k2_inv, (float*)workspace, m, J, kappa, use_tc);
+    const int cs = use_tc ? mid_cluster_size() : 1;
+    FNB_CUDA(launch_cluster(pinv_fwd_debug_kernel, dim3((unsigned)(bh * cs)), dim3(use_tc ? kMidTcThreads : kThreads),
+                            use_tc ? kTcGemmSmem : 0, (cudaStream_t)stream, cs, k2, ns_iterates, k2_inv, (float*)workspace, m,
+                            J, kappa, use_tc));
   }
   FNB_CUDA(cudaPeekAtLastError());
   return 0;
@@ -1164,8 +1201,10 @@ int fnb_debug_pinv_backward(int64_t bh, int32_t m, int32_t J, float kappa, const
     const int use_tc = ns_on_tensor_cores(0) ? 1 : 0;
     if (use_tc)
       FNB_CUDA(cudaFuncSetAttribute(pinv_bwd_debug_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcGemmSmem));
-    pinv_bwd_debug_kernel<<<(unsigned)bh, use_tc ? kMidTcThreads : kThreads, use_tc ? kTcGemmSmem : 0, (cudaStream_t)stream>>>(
-        k2, ns_iterates, d_k2_inv, d_k2, (float*)workspace, m, J, kappa, use_tc);
+    const int cs = use_tc ? mid_cluster_size() : 1;
+    FNB_CUDA(launch_cluster(pinv_bwd_debug_kernel, dim3((unsigned)(bh * cs)), dim3(use_tc ? kMidTcThreads : kThreads),
+                            use_tc ? kTcGemmSmem : 0, (cudaStream_t)stream, cs, k2, ns_iterates, d_k2_inv, d_k2,
+                            (float*)workspace, m, J, kappa, use_tc));
   }
   FNB_CUDA(cudaPeekAtLastError());
   return 0;

@@ -1,7 +1,11 @@
 // The landmark-sized ("middle") stages: everything that works on (m x m) and (m x D) FP32
-// matrices per (b,h) slice.  One CTA of 256 threads per slice; operands live in global
-// memory (they are a few hundred KB per slice and stay in L2) and are staged through shared
-// memory k-slab by k-slab, so the same code serves every m <= 128.
+// matrices per (b,h) slice.  Operands live in global memory (they are a few hundred KB per slice
+// and stay in L2), so the same code serves every m <= 128.  On the CUDA cores: one CTA of 256
+// threads per slice, products staged through shared memory k-slab by k-slab.  On the tensor
+// cores: 512 threads per CTA and, for mid_fwd_kernel / mid_bwd_kernel, a thread-block cluster of
+// up to four CTAs per slice that shares the products (by output columns; in the backward
+// iterations also as two pairs that take independent products side by side) and the element-wise
+// phases, meeting at cluster barriers.
 //
 //   mid_fwd_kernel     : landmark finalisation, softmax-2, optional Tikhonov ridge,
 //                        Z0 and the J Newton-Schulz iterations (all iterates saved)
@@ -53,7 +57,34 @@ struct GemmWs {
   uint32_t tmem;
   uint32_t phase;
   int* status;
+  // A slice may be worked on by a thread-block cluster of cs CTAs (rank = this CTA's place in it):
+  // every product is split by output columns, every element-wise phase by elements, and the phases
+  // meet at a cluster barrier; operands and results live in global memory (L2) as before.
+  int cs, rank;
+  int gt, gn;           // thread index and thread count over the whole cluster
+  int defer_sync;       // 1: a product ends without the cluster barrier (the caller places it)
 };
+
+__device__ __forceinline__ int cluster_size() {
+  uint32_t n;
+  asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(n));
+  return (int)n;
+}
+__device__ __forceinline__ int cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return (int)r;
+}
+// End of a phase: what the CTAs of the cluster wrote to global memory is visible to all of them
+// afterwards.  All threads of all CTAs of the cluster call (a hardware barrier: no spin-wait).
+__device__ __forceinline__ void mid_sync(int cs) {
+  if (cs > 1) {
+    __threadfence();
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+  } else {
+    __syncthreads();
+  }
+}
 
 // rows x cols FP32 matrix in global memory (leading dimension ld) -> three swizzled bf16 term tiles,
 // zero beyond rows / cols.  All NT threads of the CTA.
@@ -222,10 +253,171 @@ __device__ inline void cta_gemm_tc(float* C, int ldc, const float* A, int lda, c
 #endif
 }
 
+
+// One column block of op(B) for the product of a cluster: rows [n0, n0 + nrows) of the (N x K) operand
+// (stored_nk) or columns [n0, n0 + nrows) of the (K x N) operand, always written as a K-major tile
+// whose row is the output column (so the MMA needs no partial swizzle atom along N).
+template <int NT>
+__device__ inline void tc_gemm_load_nblock(uint8_t* set, const float* B, int ldb, bool stored_nk, int n0, int nrows,
+                                           int NB, int K) {
+  const bool vec = stored_nk && (ldb & 3) == 0 && (K & 7) == 0 && (reinterpret_cast<uintptr_t>(B) & 15u) == 0;
+  for (int item = threadIdx.x; item < NB * 16; item += NT) {
+    // lanes run along the contiguous direction of the stored operand
+    const int r = stored_nk ? item >> 4 : item % NB;
+    const int ch = stored_nk ? item & 15 : item / NB;
+    const int c0 = ch * 8;
+    float v[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = 0.f;
+    if (r < nrows && c0 < K) {
+      if (stored_nk) {
+        const float* g = B + (size_t)(n0 + r) * ldb + c0;
+        if (vec) {
+          const float4 a = *reinterpret_cast<const float4*>(g), b = *reinterpret_cast<const float4*>(g + 4);
+          v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+        } else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) if (c0 + i < K) v[i] = g[i];
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) if (c0 + i < K) v[i] = B[(size_t)(c0 + i) * ldb + n0 + r];
+      }
+    }
+    uint32_t w0[4], w1[4], w2[4];
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+      float a = v[2 * p], b = v[2 * p + 1];
+      w0[p] = tc::pack2<__nv_bfloat16>(a, b);
+      a -= __uint_as_float(w0[p] << 16);
+      b -= __uint_as_float(w0[p] & 0xffff0000u);
+      w1[p] = tc::pack2<__nv_bfloat16>(a, b);
+      a -= __uint_as_float(w1[p] << 16);
+      b -= __uint_as_float(w1[p] & 0xffff0000u);
+      w2[p] = tc::pack2<__nv_bfloat16>(a, b);
+    }
+    const uint32_t off = (uint32_t)(ch >> 3) * (128 * 128) + tc::sw128_offset(r, ch & 7);
+    *reinterpret_cast<uint4*>(set + off) = make_uint4(w0[0], w0[1], w0[2], w0[3]);
+    *reinterpret_cast<uint4*>(set + kTcGemmTerm + off) = make_uint4(w1[0], w1[1], w1[2], w1[3]);
+    *reinterpret_cast<uint4*>(set + 2 * kTcGemmTerm + off) = make_uint4(w2[0], w2[1], w2[2], w2[3]);
+  }
+}
+
+// The product of cta_gemm_tc shared by the ws.cs CTAs of a cluster: CTA `rank` forms the output columns
+// [rank NB, rank NB + NB), NB = 128 / cs, from the whole of op(A) and its column block of op(B) (MMAs of
+// M = 128, N = NB), and writes them to global memory straight from the accumulator rows; the cluster
+// barrier at the end makes the whole result visible to every CTA.  C must not alias an operand.
+template <bool TA, bool TB, int NT>
+__device__ inline void cluster_gemm_tc(float* C, int ldc, const float* A, int lda, const float* B, int ldb, int M, int N,
+                                       int K, float alpha, float beta, float diag, GemmWs& ws, float* C2, float alpha2,
+                                       float diag2) {
+  const int NB = 128 / ws.cs, n0 = ws.rank * NB;
+  const int ncols = min(NB, N - n0);          // <= 0: this CTA has no column of the result
+  uint8_t* setA = ws.tiles;
+  uint8_t* setB = ws.tiles + kTcGemmSet;
+  GEMM_T0();
+  if (ncols > 0) {
+    tc_gemm_load<NT>(setA, A, lda, TA ? K : M, TA ? M : K);
+    tc_gemm_load_nblock<NT>(setB, B, ldb, TB, n0, ncols, NB, K);
+    tc::fence_proxy_async();
+    __syncthreads();
+    GEMM_T(0);
+    if (threadIdx.x == 0) {
+      tc::tc_fence_after();
+      constexpr bool AR = TA;
+      const uint32_t idesc = tc::make_idesc<__nv_bfloat16>(128, NB, TA, false);
+      const uint64_t da = tc_gemm_desc(tc::smem_u32(setA), AR, 0), db = tc_gemm_desc(tc::smem_u32(setB), false, 0);
+      const int ksteps = (K + 15) >> 4;
+      uint32_t acc = 0;
+#pragma unroll
+      for (int t = 0; t < 6; ++t) {
+        constexpr int oi[6] = {1, 0, 2, 0, 1, 0}, oj[6] = {1, 2, 0, 1, 0, 0};
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          if (k < ksteps) {
+            const uint32_t offa = oi[t] * kTcGemmTerm + (AR ? k * 2048 : (k >> 2) * (128 * 128) + (k & 3) * 32);
+            const uint32_t offb = oj[t] * kTcGemmTerm + (k >> 2) * (128 * 128) + (k & 3) * 32;
+            tc::umma(ws.tmem, da + (offa >> 4), db + (offb >> 4), idesc, acc);
+            acc = 1;
+          }
+        }
+      }
+      tc::umma_commit(ws.bar);
+      GEMM_T(1);
+      // the issuing thread alone waits for the MMAs; the other threads sleep at the barrier below
+      // instead of polling beside it
+      tc::Abort ab{reinterpret_cast<volatile int*>(ws.bar + 1), ws.status};
+      tc::mbar_wait(ws.bar, ws.phase, ab, 0x5100);
+    }
+    ws.phase ^= 1u;
+    __syncthreads();
+    tc::tc_fence_after();
+    GEMM_T(2);
+    // epilogue: warp w holds accumulator rows 32 (w & 3) .. + 31 and NB / 4 of the block's columns
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int r = (warp & 3) * 32 + lane, cpw = NB / (NT / 128);
+    const bool vec = (ldc & 3) == 0 && (N & 3) == 0 && (reinterpret_cast<uintptr_t>(C) & 15u) == 0 &&
+                     (!C2 || (reinterpret_cast<uintptr_t>(C2) & 15u) == 0);
+    for (int cb = (warp >> 2) * cpw; cb < (warp >> 2) * cpw + cpw; cb += 8) {
+      float v[8];
+      tc::tmem_ld8(ws.tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)cb, v);
+      tc::tmem_ld_wait();
+      const int c = n0 + cb;
+      if (r < M && c < N) {
+        float* dst = C + (size_t)r * ldc + c;
+        float o[8], o2[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          o[j] = alpha * v[j];
+          o2[j] = alpha2 * v[j];
+        }
+        if (vec) {
+          if (beta != 0.f) {
+#pragma unroll
+            for (int q = 0; q < 8; q += 4)
+              if (c + q < N) {
+                const float4 old = *reinterpret_cast<const float4*>(dst + q);
+                o[q] += beta * old.x; o[q + 1] += beta * old.y; o[q + 2] += beta * old.z; o[q + 3] += beta * old.w;
+              }
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            if (c + j == r) { o[j] += diag; o2[j] += diag2; }
+#pragma unroll
+          for (int q = 0; q < 8; q += 4)
+            if (c + q < N) {
+              *reinterpret_cast<float4*>(dst + q) = make_float4(o[q], o[q + 1], o[q + 2], o[q + 3]);
+              if (C2) *reinterpret_cast<float4*>(C2 + (size_t)r * ldc + c + q) = make_float4(o2[q], o2[q + 1], o2[q + 2], o2[q + 3]);
+            }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            if (c + j < N) {
+              float val = o[j];
+              if (beta != 0.f) val += beta * dst[j];
+              if (c + j == r) val += diag;
+              dst[j] = val;
+              if (C2) C2[(size_t)r * ldc + c + j] = o2[j] + (c + j == r ? diag2 : 0.f);
+            }
+        }
+      }
+    }
+    tc::tc_fence_before();
+  }
+  GEMM_T(3);
+  if (!ws.defer_sync) mid_sync(ws.cs);
+  GEMM_T(5);
+#ifdef FNB_TC_TRACE
+  if (blockIdx.x == 0 && threadIdx.x == 0) atomicAdd(&g_gemm_cycles[4], 1ull);
+#endif
+}
+
 // set-up / teardown of the tensor-core products inside a kernel of this file (all threads call)
 __device__ inline void gemm_ws_open(GemmWs& ws, float* sm, uint8_t* dyn, bool use_tc, uint64_t* bar_and_flag,
                                     uint32_t* tmem_slot, int* status) {
   ws.sm = sm; ws.tiles = nullptr; ws.bar = bar_and_flag; ws.tmem = 0; ws.phase = 0; ws.status = status;
+  ws.cs = cluster_size(); ws.rank = cluster_rank(); ws.defer_sync = 0;
+  ws.gt = ws.rank * (int)blockDim.x + (int)threadIdx.x; ws.gn = ws.cs * (int)blockDim.x;
   if (!use_tc || blockDim.x != kMidTcThreads) return;   // the tensor-core products are written for kMidTcThreads threads
   ws.tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(dyn) + 1023) & ~(uintptr_t)1023);
   if (threadIdx.x == 0) {
@@ -267,7 +459,10 @@ __device__ __noinline__ void cta_gemm(float* C, int ldc, const float* A, int lda
                          float* C2 = nullptr, float alpha2 = 0.f, float diag2 = 0.f) {
   if (ws.tiles) {
     // (tiles are only handed out to CTAs of kMidTcThreads threads)
-    cta_gemm_tc<TA, TB, kMidTcThreads>(C, ldc, A, lda, B, ldb, M, N, K, alpha, beta, diag, ws, C2, alpha2, diag2);
+    if (ws.cs > 1)
+      cluster_gemm_tc<TA, TB, kMidTcThreads>(C, ldc, A, lda, B, ldb, M, N, K, alpha, beta, diag, ws, C2, alpha2, diag2);
+    else
+      cta_gemm_tc<TA, TB, kMidTcThreads>(C, ldc, A, lda, B, ldb, M, N, K, alpha, beta, diag, ws, C2, alpha2, diag2);
     return;
   }
   // (the CUDA-core product below is written for 256 threads: kernels that take this branch are
@@ -431,11 +626,11 @@ __device__ inline void pinv_forward(const float* k2, float* iterates, float* k2i
   }
   Norms na = cta_norms(A, m, red);
   const float c = fmaxf(na.n1 * na.ninf, 1e-12f);
-  for (int idx = threadIdx.x; idx < mm; idx += (int)blockDim.x) {
+  for (int idx = ws.gt; idx < mm; idx += ws.gn) {
     int r = idx / m, cc = idx - r * m;
     iterates[idx] = A[cc * m + r] / c;
   }
-  __syncthreads();
+  mid_sync(ws.cs);
   for (int j = 0; j < J; ++j) {
     const float* Z = iterates + (size_t)j * mm;
     float* Zn = iterates + (size_t)(j + 1) * mm;
@@ -448,8 +643,8 @@ __device__ inline void pinv_forward(const float* k2, float* iterates, float* k2i
   if (kappa > 0.f) {
     cta_gemm<false, true>(k2inv, m, ZJ, m, k2, m, m, m, m, 1.f, 0.f, 0.f, ws);
   } else {
-    for (int idx = threadIdx.x; idx < mm; idx += (int)blockDim.x) k2inv[idx] = ZJ[idx];
-    __syncthreads();
+    for (int idx = ws.gt; idx < mm; idx += ws.gn) k2inv[idx] = ZJ[idx];
+    mid_sync(ws.cs);
   }
 }
 
@@ -484,14 +679,49 @@ __device__ inline void pinv_backward(const float* k2, const float* iterates, con
     cta_gemm<true, false>(dK2a, m, G, m, ZJ, m, m, m, m, 1.f, 0.f, 0.f, ws);   // G^T Z_J
     cta_gemm<false, false>(dZ, m, G, m, k2, m, m, m, m, 1.f, 0.f, 0.f, ws);    // G K2
   } else {
-    for (int idx = threadIdx.x; idx < mm; idx += (int)blockDim.x) dZ[idx] = G[idx];
+    for (int idx = ws.gt; idx < mm; idx += ws.gn) dZ[idx] = G[idx];
   }
-  __syncthreads();
+  mid_sync(ws.cs);
   if (J == 0) {
-    for (int idx = threadIdx.x; idx < mm; idx += (int)blockDim.x) dA[idx] = 0.f;
-    __syncthreads();
+    for (int idx = ws.gt; idx < mm; idx += ws.gn) dA[idx] = 0.f;
+    mid_sync(ws.cs);
   }
 
+  if (ws.tiles && ws.cs == 4) {
+    // A cluster of four CTAs works as two pairs: the eleven products of an iteration form four steps of
+    // independent groups (as in the kernel for up to 64 landmarks), a pair takes one group of a step
+    // and shares each of its products by halves of the output columns; a cluster barrier ends a step.
+    // A pair's accumulating products need no barrier in between: every CTA re-reads only its own columns.
+    GemmWs pr = ws;
+    pr.cs = 2; pr.rank = ws.rank & 1; pr.defer_sync = 1;
+    const bool left = (ws.rank >> 1) == 0;
+    for (int j = J - 1; j >= 0; --j) {
+      const float* Z = iterates + (size_t)j * mm;
+      if (left) cta_gemm<false, false>(Mb, m, A, m, Z, m, m, m, m, 1.f, 0.f, 0.f, pr, Ub, -1.f, 7.f);   // M and U = 7I - M
+      else cta_gemm<true, false>(dT, m, Z, m, dZ, m, m, m, m, 0.25f, 0.f, 0.f, pr);                       // dT = Z^T dZ / 4
+      mid_sync(ws.cs);
+      if (left) cta_gemm<false, false>(Vb, m, Mb, m, Ub, m, m, m, m, -1.f, 0.f, 15.f, pr);                 // V = 15I - M U
+      else cta_gemm<true, false>(dV, m, Mb, m, dT, m, m, m, m, -1.f, 0.f, 0.f, pr);                        // dV = -M^T dT
+      mid_sync(ws.cs);
+      if (left) {
+        cta_gemm<false, true>(dM, m, dT, m, Vb, m, m, m, m, -1.f, 0.f, 0.f, pr);    // -dT V^T
+        cta_gemm<false, true>(dM, m, dV, m, Ub, m, m, m, m, -1.f, 1.f, 0.f, pr);    // -= dV U^T
+        cta_gemm<true, false>(dM, m, Mb, m, dV, m, m, m, m, 1.f, 1.f, 0.f, pr);     // += M^T dV
+      } else {
+        cta_gemm<false, false>(Tb, m, Mb, m, Vb, m, m, m, m, -1.f, 0.f, 13.f, pr);  // T = 13I - M V
+      }
+      mid_sync(ws.cs);
+      if (left) {
+        cta_gemm<false, true>(dZo, m, dZ, m, Tb, m, m, m, m, 0.25f, 0.f, 0.f, pr);  // dZ T^T / 4
+        cta_gemm<true, false>(dZo, m, A, m, dM, m, m, m, m, 1.f, 1.f, 0.f, pr);     // dZ' = dZ T^T / 4 + A^T dM
+      } else {
+        cta_gemm<false, true>(dA, m, dM, m, Z, m, m, m, m, 1.f, j == J - 1 ? 0.f : 1.f, 0.f, pr);   // dA += dM Z^T
+      }
+      mid_sync(ws.cs);
+      { float* tmp = dZ; dZ = dZo; dZo = tmp; }
+    }
+    ws.phase = pr.phase;   // (of this CTA's own mbarrier)
+  } else
   for (int j = J - 1; j >= 0; --j) {
     const float* Z = iterates + (size_t)j * mm;
     cta_gemm<false, false>(Mb, m, A, m, Z, m, m, m, m, 1.f, 0.f, 0.f, ws, Ub, -1.f, 7.f);   // M and U = 7I - M
@@ -511,7 +741,7 @@ __device__ inline void pinv_backward(const float* k2, const float* iterates, con
   Norms na = cta_norms(A, m, red);
   const float craw = na.n1 * na.ninf;
   const float c = fmaxf(craw, 1e-12f);
-  // S = sum_{a,b} dZ0[a,b] A[b,a]
+  // S = sum_{a,b} dZ0[a,b] A[b,a]   (every CTA of a cluster forms the norms and this sum for itself)
   float part = 0.f;
   for (int idx = threadIdx.x; idx < mm; idx += (int)blockDim.x) {
     int a = idx / m, b = idx - a * m;
@@ -526,7 +756,7 @@ __device__ inline void pinv_backward(const float* k2, const float* iterates, con
   const bool clamped = !(craw > 1e-12f);
   const float col_term = clamped ? 0.f : -S * na.ninf / (c * c);
   const float row_term = clamped ? 0.f : -S * na.n1 / (c * c);
-  for (int idx = threadIdx.x; idx < mm; idx += (int)blockDim.x) {
+  for (int idx = ws.gt; idx < mm; idx += ws.gn) {
     int r = idx / m, cc = idx - r * m;
     float a = A[idx];
     float sg = a > 0.f ? 1.f : (a < 0.f ? -1.f : 0.f);
@@ -535,20 +765,20 @@ __device__ inline void pinv_backward(const float* k2, const float* iterates, con
     if (r == na.ir) g += sg * row_term;
     dA[idx] = g;
   }
-  __syncthreads();
+  mid_sync(ws.cs);
   if (kappa > 0.f) {
     // dK2 = dK2a + K2 (dA + dA^T)
-    for (int idx = threadIdx.x; idx < mm; idx += (int)blockDim.x) {
+    for (int idx = ws.gt; idx < mm; idx += ws.gn) {
       int r = idx / m, cc = idx - r * m;
       dM[idx] = dA[idx] + dA[cc * m + r];
     }
-    __syncthreads();
+    mid_sync(ws.cs);
     cta_gemm<false, false>(dK2a, m, k2, m, dM, m, m, m, m, 1.f, 1.f, 0.f, ws);
-    for (int idx = threadIdx.x; idx < mm; idx += (int)blockDim.x) dK2[idx] = dK2a[idx];
+    for (int idx = ws.gt; idx < mm; idx += ws.gn) dK2[idx] = dK2a[idx];
   } else {
-    for (int idx = threadIdx.x; idx < mm; idx += (int)blockDim.x) dK2[idx] = dA[idx];
+    for (int idx = ws.gt; idx < mm; idx += ws.gn) dK2[idx] = dA[idx];
   }
-  __syncthreads();
+  mid_sync(ws.cs);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -574,12 +804,13 @@ __global__ void __launch_bounds__(kMidTcThreads) mid_fwd_kernel(MidFwdParams p) 
   __shared__ uint64_t gemm_bar[2];
   __shared__ uint32_t gemm_tmem;
   extern __shared__ uint8_t gemm_dyn[];
-  const int64_t bh = blockIdx.x;
+  const int cs = cluster_size(), rank = cluster_rank();
+  const int64_t bh = blockIdx.x / cs;
   const int m = p.m, D = p.D, t = threadIdx.x;
   Segments sg(p.N, m);
   float* qt = p.qt + bh * m * D;
   float* kt = p.kt + bh * m * D;
-  for (int idx = t; idx < 2 * m * D; idx += (int)blockDim.x) {
+  for (int idx = rank * (int)blockDim.x + t; idx < 2 * m * D; idx += cs * (int)blockDim.x) {
     int which = idx / (m * D), rem = idx - which * m * D;
     int l = rem / D, d = rem - l * D;
     const float* src = p.land_partial + ((((size_t)which * p.BH + bh) * m + l) * p.C) * D + d;
@@ -588,8 +819,8 @@ __global__ void __launch_bounds__(kMidTcThreads) mid_fwd_kernel(MidFwdParams p) 
     float val = s * (p.scale / (float)sg.len(l));
     (which ? kt : qt)[rem] = val;
   }
-  __syncthreads();
-  if (p.qt16)
+  mid_sync(cs);
+  if (p.qt16 && rank == 0)
     pack_pair(qt, reinterpret_cast<char*>(p.qt16) + (size_t)bh * p.MP * D * 2, nullptr, p.dtype, m, D, p.MP,
               p.qt16_mul);
   if (p.landmarks_only) return;
@@ -598,8 +829,8 @@ __global__ void __launch_bounds__(kMidTcThreads) mid_fwd_kernel(MidFwdParams p) 
   float* k2 = p.k2 + bh * m * m;
   cta_gemm<false, true>(k2, m, qt, D, kt, D, m, m, D, 1.f, 0.f, 0.f, ws);
   // row softmax, one warp per row
-  const int w = t >> 5, lane = t & 31;
-  for (int r = w; r < m; r += ((int)blockDim.x >> 5)) {
+  const int w = ws.gt >> 5, lane = t & 31;
+  for (int r = w; r < m; r += (ws.gn >> 5)) {
     float mx = -INFINITY;
     for (int c = lane; c < m; c += 32) mx = fmaxf(mx, k2[r * m + c]);
     for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
@@ -609,7 +840,7 @@ __global__ void __launch_bounds__(kMidTcThreads) mid_fwd_kernel(MidFwdParams p) 
     for (int c = lane; c < m; c += 32) k2[r * m + c] = expf(k2[r * m + c] - mx) / sum;
     if (lane == 0) p.lse2[bh * m + r] = mx + logf(sum);
   }
-  __syncthreads();
+  mid_sync(cs);
   pinv_forward(k2, p.iterates + bh * (size_t)(p.J + 1) * m * m, p.k2inv + bh * m * m,
                p.scratch + bh * (size_t)kPinvFwdBufs * m * m, m, p.J, p.kappa, ws);
   gemm_ws_close(ws);
@@ -622,7 +853,7 @@ pinv_fwd_debug_kernel(const float* k2, float* iterates, float* k2inv, float* scr
   __shared__ uint64_t gemm_bar[2];
   __shared__ uint32_t gemm_tmem;
   extern __shared__ uint8_t gemm_dyn[];
-  const int64_t bh = blockIdx.x;
+  const int64_t bh = blockIdx.x / cluster_size();
   GemmWs ws;
   gemm_ws_open(ws, sm, gemm_dyn, use_tc != 0, gemm_bar, &gemm_tmem, nullptr);
   pinv_forward(k2 + bh * m * m, iterates + bh * (size_t)(J + 1) * m * m, k2inv + bh * m * m,
@@ -637,7 +868,7 @@ pinv_bwd_debug_kernel(const float* k2, const float* iterates, const float* G, fl
   __shared__ uint64_t gemm_bar[2];
   __shared__ uint32_t gemm_tmem;
   extern __shared__ uint8_t gemm_dyn[];
-  const int64_t bh = blockIdx.x;
+  const int64_t bh = blockIdx.x / cluster_size();
   GemmWs ws;
   gemm_ws_open(ws, sm, gemm_dyn, use_tc != 0, gemm_bar, &gemm_tmem, nullptr);
   pinv_backward(k2 + bh * m * m, iterates + bh * (size_t)(J + 1) * m * m, G + bh * m * m,
@@ -742,17 +973,17 @@ __global__ void __launch_bounds__(kMidTcThreads) mid_bwd_kernel(MidBwdParams p) 
   extern __shared__ uint8_t gemm_dyn[];
   GemmWs ws;
   gemm_ws_open(ws, sm, gemm_dyn, p.use_tc != 0 && !p.first_half_only, gemm_bar, &gemm_tmem, p.status);
-  const int64_t bh = blockIdx.x;
+  const int64_t bh = blockIdx.x / ws.cs;
   const int m = p.m, D = p.D, t = threadIdx.x, mm = m * m, md = m * D;
   float* dstep2 = p.dstep2 + bh * md;
   float* dkt_a = p.dkt_a + bh * md;
   const float* partA = p.partA + bh * (size_t)p.nchunk * 2 * md;
-  for (int idx = t; idx < 2 * md; idx += (int)blockDim.x) {
+  for (int idx = ws.gt; idx < 2 * md; idx += ws.gn) {
     float s = 0.f;
     for (int c = 0; c < p.nchunk; ++c) s += partA[(size_t)c * 2 * md + idx];
     if (idx < md) dstep2[idx] = s; else dkt_a[idx - md] = s;
   }
-  __syncthreads();
+  mid_sync(ws.cs);
   const float* k2inv = p.k2inv + bh * mm;
   const float* bmat = p.bmat + bh * md;
   const float* k2 = p.k2 + bh * mm;
@@ -764,8 +995,8 @@ __global__ void __launch_bounds__(kMidTcThreads) mid_bwd_kernel(MidBwdParams p) 
   cta_gemm<true, false>(dO3, D, k2inv, m, dstep2, D, m, D, m, 1.f, 0.f, 0.f, ws);   // K2inv^T dstep2
   cta_gemm<false, true>(G, m, dstep2, D, bmat, D, m, m, D, 1.f, 0.f, 0.f, ws);      // dstep2 Bmat^T
   {
-    const int w = t >> 5, lane = t & 31;
-    for (int l = w; l < m; l += ((int)blockDim.x >> 5)) {
+    const int w = ws.gt >> 5, lane = t & 31;
+    for (int l = w; l < m; l += (ws.gn >> 5)) {
       float s = 0.f;
       for (int d = lane; d < D; d += 32) s += bmat[l * D + d] * dO3[l * D + d];
       for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
@@ -777,20 +1008,20 @@ __global__ void __launch_bounds__(kMidTcThreads) mid_bwd_kernel(MidBwdParams p) 
                 p.scratch + bh * (size_t)kPinvBwdBufs * mm, m, p.J, p.kappa, ws);
   // softmax-2 Jacobian, in place: dS2 = K2 o (dK2 - rowsum(dK2 o K2))
   {
-    const int w = t >> 5, lane = t & 31;
-    for (int r = w; r < m; r += ((int)blockDim.x >> 5)) {
+    const int w = ws.gt >> 5, lane = t & 31;
+    for (int r = w; r < m; r += (ws.gn >> 5)) {
       float s = 0.f;
       for (int c = lane; c < m; c += 32) s += dK2[r * m + c] * k2[r * m + c];
       for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
       for (int c = lane; c < m; c += 32) dK2[r * m + c] = k2[r * m + c] * (dK2[r * m + c] - s);
     }
   }
-  __syncthreads();
+  mid_sync(ws.cs);
   float* dqt_ns = p.dqt_ns + bh * md;
   float* dkt_tot = p.dkt_tot + bh * md;
   cta_gemm<false, false>(dqt_ns, D, dK2, m, kt, D, m, D, m, 1.f, 0.f, 0.f, ws);      // dS2 Kt
-  for (int idx = t; idx < md; idx += (int)blockDim.x) dkt_tot[idx] = dkt_a[idx];
-  __syncthreads();
+  for (int idx = ws.gt; idx < md; idx += ws.gn) dkt_tot[idx] = dkt_a[idx];
+  mid_sync(ws.cs);
   cta_gemm<true, false>(dkt_tot, D, dK2, m, qt, D, m, D, m, 1.f, 1.f, 0.f, ws);      // += dS2^T Qt
   gemm_ws_close(ws);
 }
