@@ -349,15 +349,35 @@ static cudaError_t launch_cluster(void (*kern)(KArgs...), dim3 grid, dim3 block,
 }
 
 // CTAs per slice of the landmark-sized kernels for more than 64 landmarks when their products run on
-// the tensor cores (a thread-block cluster shares every product by output columns).  FNB_MID_CLUSTER
-// in the environment at load overrides the default (1, 2 or 4; kept for A/B measurements).
-static int mid_cluster_size() {
-  static const int cs = [] {
+// the tensor cores (a thread-block cluster shares every product by output columns): eight if the
+// device can hold a cluster of eight for every slice at once (each CTA takes an SM to itself, and
+// a cluster must fit into one GPC), else four.  FNB_MID_CLUSTER in the environment at load fixes the
+// size (1, 2, 4 or 8; kept for A/B measurements).
+template <class... KArgs>
+static int mid_cluster_size(void (*kern)(KArgs...), int64_t slices, int device) {
+  static const int forced = [] {
     const char* e = getenv("FNB_MID_CLUSTER");
-    const int v = e ? atoi(e) : 4;
-    return (v == 1 || v == 2 || v == 4) ? v : 4;
+    const int v = e ? atoi(e) : 0;
+    return (v == 1 || v == 2 || v == 4 || v == 8) ? v : 0;
   }();
-  return cs;
+  if (forced) return forced;
+  static std::mutex mu;
+  static std::map<std::pair<const void*, int>, int> fit8;   // (kernel, device) -> clusters of eight that fit at once
+  std::lock_guard<std::mutex> lock(mu);
+  auto key = std::make_pair((const void*)kern, device);
+  auto it = fit8.find(key);
+  if (it == fit8.end()) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(8 * 64); cfg.blockDim = dim3(kMidTcThreads); cfg.dynamicSmemBytes = kTcGemmSmem;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = 8; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+    cfg.attrs = at; cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) { n = 0; cudaGetLastError(); }
+    it = fit8.emplace(key, n).first;
+  }
+  return slices <= it->second ? 8 : 4;
 }
 
 // The Newton-Schulz kernels for num_landmarks <= 64 run on the tensor cores (three-term bf16
@@ -516,7 +536,7 @@ static int forward_impl(const fnb_fwd_args& a, const Plan& p, const FwdWs& w, in
     if (mp.use_tc)
       if (int rc = set_smem(mid_fwd_kernel, mid_smem, max_smem, "mid_fwd")) return rc;
     if (mp.use_tc) {
-      const int cs = mid_cluster_size();
+      const int cs = mid_cluster_size(mid_fwd_kernel, p.BH, a.device);
       FNB_CUDA(launch_cluster(mid_fwd_kernel, dim3((unsigned)(p.BH * cs)), dim3(kMidTcThreads), mid_smem, st, cs, mp));
     } else {
       mid_fwd_kernel<<<(unsigned)p.BH, kThreads, mid_smem, st>>>(mp);
@@ -833,7 +853,7 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
       if (mp.use_tc)
         if (int rc = set_smem(mid_bwd_kernel, mid_smem, max_smem, "mid_bwd")) return rc;
       if (mp.use_tc && !mp.first_half_only) {
-        const int cs = mid_cluster_size();
+        const int cs = mid_cluster_size(mid_bwd_kernel, p.BH, a.device);
         FNB_CUDA(launch_cluster(mid_bwd_kernel, dim3((unsigned)(p.BH * cs)), dim3(kMidTcThreads), mid_smem, st, cs, mp));
       } else {
         mid_bwd_kernel<<<(unsigned)p.BH, kThreads, mid_smem, st>>>(mp);
@@ -1171,7 +1191,7 @@ int fnb_debug_pinv_forward(int64_t bh, int32_t m, int32_t J, float kappa, const 
     const int use_tc = ns_on_tensor_cores(0) ? 1 : 0;
     if (use_tc)
       FNB_CUDA(cudaFuncSetAttribute(pinv_fwd_debug_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcGemmSmem));
-    const int cs = use_tc ? mid_cluster_size() : 1;
+    const int cs = use_tc ? mid_cluster_size(pinv_fwd_debug_kernel, bh, device) : 1;
     FNB_CUDA(launch_cluster(pinv_fwd_debug_kernel, dim3((unsigned)(bh * cs)), dim3(use_tc ? kMidTcThreads : kThreads),
                             use_tc ? kTcGemmSmem : 0, (cudaStream_t)stream, cs, k2, ns_iterates, k2_inv, (float*)workspace, m,
                             J, kappa, use_tc));
@@ -1201,7 +1221,7 @@ int fnb_debug_pinv_backward(int64_t bh, int32_t m, int32_t J, float kappa, const
     const int use_tc = ns_on_tensor_cores(0) ? 1 : 0;
     if (use_tc)
       FNB_CUDA(cudaFuncSetAttribute(pinv_bwd_debug_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcGemmSmem));
-    const int cs = use_tc ? mid_cluster_size() : 1;
+    const int cs = use_tc ? mid_cluster_size(pinv_bwd_debug_kernel, bh, device) : 1;
     FNB_CUDA(launch_cluster(pinv_bwd_debug_kernel, dim3((unsigned)(bh * cs)), dim3(use_tc ? kMidTcThreads : kThreads),
                             use_tc ? kTcGemmSmem : 0, (cudaStream_t)stream, cs, k2, ns_iterates, d_k2_inv, d_k2,
                             (float*)workspace, m, J, kappa, use_tc));

@@ -3,8 +3,8 @@
 // and stay in L2), so the same code serves every m <= 128.  On the CUDA cores: one CTA of 256
 // threads per slice, products staged through shared memory k-slab by k-slab.  On the tensor
 // cores: 512 threads per CTA and, for mid_fwd_kernel / mid_bwd_kernel, a thread-block cluster of
-// up to four CTAs per slice that shares the products (by output columns; in the backward
-// iterations also as two pairs that take independent products side by side) and the element-wise
+// up to eight CTAs per slice that shares the products (by output columns; in the backward
+// iterations also as two halves that take independent products side by side) and the element-wise
 // phases, meeting at cluster barriers.
 //
 //   mid_fwd_kernel     : landmark finalisation, softmax-2, optional Tikhonov ridge,
@@ -353,12 +353,14 @@ __device__ inline void cluster_gemm_tc(float* C, int ldc, const float* A, int ld
     __syncthreads();
     tc::tc_fence_after();
     GEMM_T(2);
-    // epilogue: warp w holds accumulator rows 32 (w & 3) .. + 31 and NB / 4 of the block's columns
+    // epilogue: warp w holds accumulator rows 32 (w & 3) .. + 31 and takes groups of 8 of the block's columns
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int r = (warp & 3) * 32 + lane, cpw = NB / (NT / 128);
+    const int r = (warp & 3) * 32 + lane;
     const bool vec = (ldc & 3) == 0 && (N & 3) == 0 && (reinterpret_cast<uintptr_t>(C) & 15u) == 0 &&
                      (!C2 || (reinterpret_cast<uintptr_t>(C2) & 15u) == 0);
-    for (int cb = (warp >> 2) * cpw; cb < (warp >> 2) * cpw + cpw; cb += 8) {
+    // (a CTA moves about 14 bytes per clock to global memory: the fewer columns a CTA owns, the
+    // shorter this phase)
+    for (int cb = (warp >> 2) * 8; cb < NB; cb += (NT / 128) * 8) {
       float v[8];
       tc::tmem_ld8(ws.tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)cb, v);
       tc::tmem_ld_wait();
@@ -687,14 +689,14 @@ __device__ inline void pinv_backward(const float* k2, const float* iterates, con
     mid_sync(ws.cs);
   }
 
-  if (ws.tiles && ws.cs == 4) {
-    // A cluster of four CTAs works as two pairs: the eleven products of an iteration form four steps of
-    // independent groups (as in the kernel for up to 64 landmarks), a pair takes one group of a step
-    // and shares each of its products by halves of the output columns; a cluster barrier ends a step.
-    // A pair's accumulating products need no barrier in between: every CTA re-reads only its own columns.
+  if (ws.tiles && ws.cs >= 4) {
+    // A cluster of four or eight CTAs works as two halves: the eleven products of an iteration form four
+    // steps of independent groups (as in the kernel for up to 64 landmarks), a half takes one group of a
+    // step and shares each of its products by blocks of the output columns; a cluster barrier ends a step.
+    // A half's accumulating products need no barrier in between: every CTA re-reads only its own columns.
     GemmWs pr = ws;
-    pr.cs = 2; pr.rank = ws.rank & 1; pr.defer_sync = 1;
-    const bool left = (ws.rank >> 1) == 0;
+    pr.cs = ws.cs / 2; pr.rank = ws.rank % pr.cs; pr.defer_sync = 1;
+    const bool left = ws.rank < pr.cs;
     for (int j = J - 1; j >= 0; --j) {
       const float* Z = iterates + (size_t)j * mm;
       if (left) cta_gemm<false, false>(Mb, m, A, m, Z, m, m, m, m, 1.f, 0.f, 0.f, pr, Ub, -1.f, 7.f);   // M and U = 7I - M
