@@ -322,7 +322,8 @@ __device__ inline void cluster_gemm_tc(float* C, int ldc, const float* A, int ld
     tc::fence_proxy_async();
     __syncthreads();
     GEMM_T(0);
-    if (threadIdx.x == 0) {
+    // warp 0 issues from warp-uniform code (one elected lane per MMA)
+    if (__shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0) == 0) {
       tc::tc_fence_after();
       constexpr bool AR = TA;
       const uint32_t idesc = tc::make_idesc<__nv_bfloat16>(128, NB, TA, false);
@@ -337,17 +338,19 @@ __device__ inline void cluster_gemm_tc(float* C, int ldc, const float* A, int ld
           if (k < ksteps) {
             const uint32_t offa = oi[t] * kTcGemmTerm + (AR ? k * 2048 : (k >> 2) * (128 * 128) + (k & 3) * 32);
             const uint32_t offb = oj[t] * kTcGemmTerm + (k >> 2) * (128 * 128) + (k & 3) * 32;
-            tc::umma(ws.tmem, da + (offa >> 4), db + (offb >> 4), idesc, acc);
+            tc::umma_elect(ws.tmem, da + (offa >> 4), db + (offb >> 4), idesc, acc);
             acc = 1;
           }
         }
       }
-      tc::umma_commit(ws.bar);
+      tc::umma_commit_elect(ws.bar);
       GEMM_T(1);
-      // the issuing thread alone waits for the MMAs; the other threads sleep at the barrier below
-      // instead of polling beside it
-      tc::Abort ab{reinterpret_cast<volatile int*>(ws.bar + 1), ws.status};
-      tc::mbar_wait(ws.bar, ws.phase, ab, 0x5100);
+      // one thread alone waits for the MMAs; the others sleep at the barrier below instead of
+      // polling beside it
+      if (threadIdx.x == 0) {
+        tc::Abort ab{reinterpret_cast<volatile int*>(ws.bar + 1), ws.status};
+        tc::mbar_wait(ws.bar, ws.phase, ab, 0x5100);
+      }
     }
     ws.phase ^= 1u;
     __syncthreads();
