@@ -281,12 +281,12 @@ def forward_backward_autograd(q, k, v, dO, num_landmarks, newton_iter=6, kappa_s
 # --------------------------------------------------------------------------------------
 def rel_max(a: torch.Tensor, b: torch.Tensor) -> float:
     """max|a-b| / max|b| : the 'max relative error' the tolerances are quoted in."""
-    a, b = a.double(), b.double()
+    a, b = a.detach().double(), b.detach().double()
     return float((a - b).abs().max() / b.abs().max().clamp(min=1e-300))
 
 
 def rel_fro(a: torch.Tensor, b: torch.Tensor) -> float:
-    a, b = a.double(), b.double()
+    a, b = a.detach().double(), b.detach().double()
     return float((a - b).norm() / b.norm().clamp(min=1e-300))
 
 
