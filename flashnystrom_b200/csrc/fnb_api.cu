@@ -867,7 +867,7 @@ static int backward_impl(const fnb_bwd_args& a, const Plan& p, const BwdWs& w, i
       pp.dO3 = w.dO3; pp.q_landmarks = a.q_landmarks; pp.dkt_tot = w.dkt_tot; pp.do3n = do3n; pp.do3_scale = w.do3_scale;
       pp.qt16 = qt16; pp.rows_k = w.rows_k; pp.m = p.m; pp.D = p.D; pp.MP = MP; pp.dtype = a.shape.dtype;
       pp.qt_mul = scale * tc::kLog2e; pp.scale = scale; pp.N = seg_N;
-      mid_pack_kernel<<<(unsigned)p.BH, kThreads, 0, st>>>(pp);
+      mid_pack_kernel<<<dim3((unsigned)p.BH, kMidPackSplit), kThreads, 0, st>>>(pp);
       if (L.end("mid_pack")) return L.status;
     }
   }

@@ -17,6 +17,15 @@ __device__ __forceinline__ void store16(void* p, int dtype, size_t idx, float v)
   else reinterpret_cast<__nv_bfloat16*>(p)[idx] = __float2bfloat16_rn(v);
 }
 
+__device__ __forceinline__ uint32_t pack2x16(int dtype, float a, float b) {
+  if (dtype == 1) {
+    __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+  }
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
 // max over the CTA; red: 8 floats of shared scratch.  Ends with a barrier.
 __device__ __forceinline__ float cta_max(float v, float* red) {
   for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
@@ -38,9 +47,12 @@ __device__ __forceinline__ float pow2_scale(float amax) {
 // 16-bit copies of an FP32 (m x D) global matrix: out_n[MP][D] and / or out_t[D][MP], times mul.
 __device__ __forceinline__ void pack_pair(const float* src, void* out_n, void* out_t, int dtype, int m, int D,
                                           int MP, float mul) {
-  if (out_n)
-    for (int idx = threadIdx.x; idx < MP * D; idx += kThreads)
-      store16(out_n, dtype, idx, (idx / D) < m ? src[idx] * mul : 0.f);
+  if (out_n)   // four consecutive columns per step (D is a multiple of 16, the matrices are 16-byte aligned)
+    for (int g = threadIdx.x; g < MP * D / 4; g += (int)blockDim.x) {
+      float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+      if ((g * 4) / D < m) x = reinterpret_cast<const float4*>(src)[g];
+      reinterpret_cast<uint2*>(out_n)[g] = make_uint2(pack2x16(dtype, x.x * mul, x.y * mul), pack2x16(dtype, x.z * mul, x.w * mul));
+    }
   if (out_t)
     for (int idx = threadIdx.x; idx < D * MP; idx += kThreads) {
       int d = idx / MP, l = idx - d * MP;
@@ -499,27 +511,41 @@ struct MidPackParams {
   float qt_mul, scale;
   int64_t N;
 };
+// gridDim.y CTAs share a slice: each finds the scale for itself (the slice's dO3 comes from L2) and
+// packs its share of the rows, four values per thread and step.
+constexpr int kMidPackSplit = 8;
 __global__ void __launch_bounds__(kThreads) mid_pack_kernel(MidPackParams p) {
   __shared__ float red[8];
   const int64_t bh = blockIdx.x;
   const int md = p.m * p.D, t = threadIdx.x;
   const float* dO3 = p.dO3 + bh * (int64_t)md;
   float amax = 0.f;
-  for (int idx = t; idx < md; idx += kThreads) amax = fmaxf(amax, fabsf(dO3[idx]));
-  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-  if ((t & 31) == 0) red[t >> 5] = amax;
-  __syncthreads();
-  float cmax = red[0];
-  for (int w = 1; w < kThreads / 32; ++w) cmax = fmaxf(cmax, red[w]);
-  const float sc = pow2_scale(cmax);
-  if (t == 0) p.do3_scale[bh] = sc;
+  for (int idx = t; idx < md / 4; idx += kThreads) {
+    const float4 x = reinterpret_cast<const float4*>(dO3)[idx];
+    amax = fmaxf(fmaxf(amax, fmaxf(fabsf(x.x), fabsf(x.y))), fmaxf(fabsf(x.z), fabsf(x.w)));
+  }
+  const float sc = pow2_scale(cta_max(amax, red)), inv_sc = 1.f / sc;
+  if (t == 0 && blockIdx.y == 0) p.do3_scale[bh] = sc;
   const size_t ob = (size_t)bh * p.MP * p.D * 2;
-  pack_pair(dO3, reinterpret_cast<char*>(p.do3n) + ob, nullptr, p.dtype, p.m, p.D, p.MP, 1.f / sc);
-  pack_pair(p.q_landmarks + bh * (int64_t)md, reinterpret_cast<char*>(p.qt16) + ob, nullptr, p.dtype, p.m, p.D, p.MP,
-            p.qt_mul);
+  const float* qt = p.q_landmarks + bh * (int64_t)md;
+  const float* dkt = p.dkt_tot + bh * (int64_t)md;
   Segments sg(p.N, p.m);
-  for (int idx = t; idx < md; idx += kThreads)
-    p.rows_k[bh * (int64_t)md + idx] = p.dkt_tot[bh * (int64_t)md + idx] * (p.scale / (float)sg.len(idx / p.D));
+  const int groups = p.MP * p.D / 4;       // groups of four consecutive columns of the padded operands
+  for (int g = blockIdx.y * kThreads + t; g < groups; g += gridDim.y * kThreads) {
+    const int l = (g * 4) / p.D;
+    float4 a = make_float4(0.f, 0.f, 0.f, 0.f), q = a;
+    if (l < p.m) {
+      a = reinterpret_cast<const float4*>(dO3)[g];
+      q = reinterpret_cast<const float4*>(qt)[g];
+      const float4 k = reinterpret_cast<const float4*>(dkt)[g];
+      const float f = p.scale / (float)sg.len(l);
+      reinterpret_cast<float4*>(p.rows_k + bh * (int64_t)md)[g] = make_float4(k.x * f, k.y * f, k.z * f, k.w * f);
+    }
+    reinterpret_cast<uint2*>(reinterpret_cast<char*>(p.do3n) + ob)[g] =
+        make_uint2(pack2x16(p.dtype, a.x * inv_sc, a.y * inv_sc), pack2x16(p.dtype, a.z * inv_sc, a.w * inv_sc));
+    reinterpret_cast<uint2*>(reinterpret_cast<char*>(p.qt16) + ob)[g] =
+        make_uint2(pack2x16(p.dtype, q.x * p.qt_mul, q.y * p.qt_mul), pack2x16(p.dtype, q.z * p.qt_mul, q.w * p.qt_mul));
+  }
 }
 
 // ------------------------------------------------------------------------------------------
@@ -672,15 +698,6 @@ struct ColpassOperandParams {
   int m, dtype;
 };
 constexpr int kColpassOperandSmem = 3 * 64 * 64 * (int)sizeof(float);
-
-__device__ __forceinline__ uint32_t pack2x16(int dtype, float a, float b) {
-  if (dtype == 1) {
-    __half2 h = __floats2half2_rn(a, b);
-    return *reinterpret_cast<uint32_t*>(&h);
-  }
-  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
-  return *reinterpret_cast<uint32_t*>(&h);
-}
 
 __global__ void __launch_bounds__(kThreads) colpass_operands_kernel(ColpassOperandParams p) {
   constexpr int D = 64;
