@@ -84,20 +84,25 @@ def test_config1_fp32(cuda_device):
     assert e["out"] <= 2e-4 and max(e["dq"], e["dk"], e["dv"]) <= 2e-3, e
 
 
-def test_deterministic(cuda_device):
-    """No atomics anywhere: two calls give bit-identical outputs and gradients."""
-    q, k, v, dO = O.make_inputs(2, 2, 777, 64, seed=3, dtype=torch.float16)
-    a = run_cuda(q, k, v, dO, 48, 6, 0.0)
-    b = run_cuda(q, k, v, dO, 48, 6, 0.0)
-    for key in ("out", "dq", "dk", "dv", "bmat", "step2"):
-        assert torch.equal(a[key], b[key]), key
+# (head_dim, landmarks, kappa): the second case takes the kernels for more than 64 landmarks, whose
+# thread-block clusters share every product (their size depends on the number of slices)
+@pytest.mark.parametrize("D,m,kap", [(64, 48, 0.0), (128, 100, 5.0)])
+def test_deterministic(cuda_device, D, m, kap):
+    """No atomics anywhere: repeated calls give bit-identical outputs and gradients."""
+    q, k, v, dO = O.make_inputs(2, 2, 777, D, seed=3, dtype=torch.float16)
+    a = run_cuda(q, k, v, dO, m, 6, kap)
+    for _ in range(3):
+        b = run_cuda(q, k, v, dO, m, 6, kap)
+        for key in ("out", "dq", "dk", "dv", "bmat", "step2", "k2inv"):
+            assert torch.equal(a[key], b[key]), key
 
 
-def test_slices_independent(cuda_device):
+@pytest.mark.parametrize("D,m,kap", [(64, 20, 0.0), (128, 100, 5.0)])
+def test_slices_independent(cuda_device, D, m, kap):
     """Each (b,h) slice alone gives the same bits as inside the batch."""
-    q, k, v, dO = O.make_inputs(2, 3, 500, 64, seed=5, dtype=torch.float16)
-    full = run_cuda(q, k, v, dO, 20, 6, 0.0)
+    q, k, v, dO = O.make_inputs(2, 3, 500, D, seed=5, dtype=torch.float16)
+    full = run_cuda(q, k, v, dO, m, 6, kap)
     for b in range(2):
-        part = run_cuda(q[b:b + 1], k[b:b + 1], v[b:b + 1], dO[b:b + 1], 20, 6, 0.0)
+        part = run_cuda(q[b:b + 1], k[b:b + 1], v[b:b + 1], dO[b:b + 1], m, 6, kap)
         for key in ("out", "dq", "dk", "dv"):
             assert torch.equal(full[key][b:b + 1], part[key]), key
