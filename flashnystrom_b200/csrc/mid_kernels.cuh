@@ -417,6 +417,17 @@ __device__ inline void cluster_gemm_tc(float* C, int ldc, const float* A, int ld
 #endif
 }
 
+// One half of a cluster of four or eight CTAs as the owner of a product: the halves take independent
+// products side by side (each shared by the CTAs of the half by blocks of the output columns); the
+// caller ends the step with mid_sync(ws.cs) and takes the mbarrier phase back (ws.phase = half.phase).
+__device__ __forceinline__ bool gemm_halves(const GemmWs& ws) { return ws.tiles && ws.cs >= 4; }
+__device__ __forceinline__ GemmWs gemm_half(const GemmWs& ws) {
+  GemmWs pr = ws;
+  pr.cs = ws.cs / 2; pr.rank = ws.rank % pr.cs; pr.defer_sync = 1;
+  return pr;
+}
+__device__ __forceinline__ bool gemm_left_half(const GemmWs& ws) { return ws.rank < ws.cs / 2; }
+
 // set-up / teardown of the tensor-core products inside a kernel of this file (all threads call)
 __device__ inline void gemm_ws_open(GemmWs& ws, float* sm, uint8_t* dyn, bool use_tc, uint64_t* bar_and_flag,
                                     uint32_t* tmem_slot, int* status) {
@@ -679,10 +690,21 @@ __device__ inline void pinv_backward(const float* k2, const float* iterates, con
   if (kappa > 0.f) {
     Norms nk = cta_norms(k2, m, red);
     float lam = nk.n1 * nk.ninf / kappa;
-    cta_gemm<true, false>(Ab, m, k2, m, k2, m, m, m, m, 1.f, 0.f, lam, ws);
     A = Ab;
-    cta_gemm<true, false>(dK2a, m, G, m, ZJ, m, m, m, m, 1.f, 0.f, 0.f, ws);   // G^T Z_J
-    cta_gemm<false, false>(dZ, m, G, m, k2, m, m, m, m, 1.f, 0.f, 0.f, ws);    // G K2
+    if (gemm_halves(ws)) {
+      GemmWs pr = gemm_half(ws);
+      if (gemm_left_half(ws)) {
+        cta_gemm<true, false>(Ab, m, k2, m, k2, m, m, m, m, 1.f, 0.f, lam, pr);
+        cta_gemm<false, false>(dZ, m, G, m, k2, m, m, m, m, 1.f, 0.f, 0.f, pr);    // G K2
+      } else {
+        cta_gemm<true, false>(dK2a, m, G, m, ZJ, m, m, m, m, 1.f, 0.f, 0.f, pr);   // G^T Z_J
+      }
+      ws.phase = pr.phase;
+    } else {
+      cta_gemm<true, false>(Ab, m, k2, m, k2, m, m, m, m, 1.f, 0.f, lam, ws);
+      cta_gemm<true, false>(dK2a, m, G, m, ZJ, m, m, m, m, 1.f, 0.f, 0.f, ws);   // G^T Z_J
+      cta_gemm<false, false>(dZ, m, G, m, k2, m, m, m, m, 1.f, 0.f, 0.f, ws);    // G K2
+    }
   } else {
     for (int idx = ws.gt; idx < mm; idx += ws.gn) dZ[idx] = G[idx];
   }
@@ -692,14 +714,13 @@ __device__ inline void pinv_backward(const float* k2, const float* iterates, con
     mid_sync(ws.cs);
   }
 
-  if (ws.tiles && ws.cs >= 4) {
+  if (gemm_halves(ws)) {
     // A cluster of four or eight CTAs works as two halves: the eleven products of an iteration form four
     // steps of independent groups (as in the kernel for up to 64 landmarks), a half takes one group of a
     // step and shares each of its products by blocks of the output columns; a cluster barrier ends a step.
     // A half's accumulating products need no barrier in between: every CTA re-reads only its own columns.
-    GemmWs pr = ws;
-    pr.cs = ws.cs / 2; pr.rank = ws.rank % pr.cs; pr.defer_sync = 1;
-    const bool left = ws.rank < pr.cs;
+    GemmWs pr = gemm_half(ws);
+    const bool left = gemm_left_half(ws);
     for (int j = J - 1; j >= 0; --j) {
       const float* Z = iterates + (size_t)j * mm;
       if (left) cta_gemm<false, false>(Mb, m, A, m, Z, m, m, m, m, 1.f, 0.f, 0.f, pr, Ub, -1.f, 7.f);   // M and U = 7I - M
@@ -997,8 +1018,16 @@ __global__ void __launch_bounds__(kMidTcThreads) mid_bwd_kernel(MidBwdParams p) 
   float* dO3 = p.dO3 + bh * md;
   float* G = p.G + bh * mm;
   float* dK2 = p.dK2 + bh * mm;
-  cta_gemm<true, false>(dO3, D, k2inv, m, dstep2, D, m, D, m, 1.f, 0.f, 0.f, ws);   // K2inv^T dstep2
-  cta_gemm<false, true>(G, m, dstep2, D, bmat, D, m, m, D, 1.f, 0.f, 0.f, ws);      // dstep2 Bmat^T
+  if (gemm_halves(ws)) {
+    GemmWs pr = gemm_half(ws);
+    if (gemm_left_half(ws)) cta_gemm<true, false>(dO3, D, k2inv, m, dstep2, D, m, D, m, 1.f, 0.f, 0.f, pr);   // K2inv^T dstep2
+    else cta_gemm<false, true>(G, m, dstep2, D, bmat, D, m, m, D, 1.f, 0.f, 0.f, pr);                         // dstep2 Bmat^T
+    ws.phase = pr.phase;
+    mid_sync(ws.cs);
+  } else {
+    cta_gemm<true, false>(dO3, D, k2inv, m, dstep2, D, m, D, m, 1.f, 0.f, 0.f, ws);   // K2inv^T dstep2
+    cta_gemm<false, true>(G, m, dstep2, D, bmat, D, m, m, D, 1.f, 0.f, 0.f, ws);      // dstep2 Bmat^T
+  }
   {
     const int w = ws.gt >> 5, lane = t & 31;
     for (int l = w; l < m; l += (ws.gn >> 5)) {
@@ -1024,10 +1053,18 @@ __global__ void __launch_bounds__(kMidTcThreads) mid_bwd_kernel(MidBwdParams p) 
   mid_sync(ws.cs);
   float* dqt_ns = p.dqt_ns + bh * md;
   float* dkt_tot = p.dkt_tot + bh * md;
-  cta_gemm<false, false>(dqt_ns, D, dK2, m, kt, D, m, D, m, 1.f, 0.f, 0.f, ws);      // dS2 Kt
   for (int idx = ws.gt; idx < md; idx += ws.gn) dkt_tot[idx] = dkt_a[idx];
   mid_sync(ws.cs);
-  cta_gemm<true, false>(dkt_tot, D, dK2, m, qt, D, m, D, m, 1.f, 1.f, 0.f, ws);      // += dS2^T Qt
+  if (gemm_halves(ws)) {
+    GemmWs pr = gemm_half(ws);
+    if (gemm_left_half(ws)) cta_gemm<false, false>(dqt_ns, D, dK2, m, kt, D, m, D, m, 1.f, 0.f, 0.f, pr);   // dS2 Kt
+    else cta_gemm<true, false>(dkt_tot, D, dK2, m, qt, D, m, D, m, 1.f, 1.f, 0.f, pr);                      // += dS2^T Qt
+    ws.phase = pr.phase;
+    mid_sync(ws.cs);
+  } else {
+    cta_gemm<false, false>(dqt_ns, D, dK2, m, kt, D, m, D, m, 1.f, 0.f, 0.f, ws);      // dS2 Kt
+    cta_gemm<true, false>(dkt_tot, D, dK2, m, qt, D, m, D, m, 1.f, 1.f, 0.f, ws);      // += dS2^T Qt
+  }
   gemm_ws_close(ws);
 }
 
