@@ -496,7 +496,7 @@ static int forward_impl(const fnb_fwd_args& a, const Plan& p, const FwdWs& w, in
       lp.land_partial = land; lp.C = lmC; lp.qt = a.q_landmarks; lp.kt = a.k_landmarks;
       lp.BH = p.BH; lp.N = seg_N; lp.m = p.m; lp.D = p.D; lp.scale = scale;
       lp.qt16 = use_tc ? w.qt16 : nullptr; lp.dtype = a.shape.dtype; lp.MP = MP; lp.qt16_mul = scale * tc::kLog2e;
-      landmark_finalize_kernel<<<dim3((unsigned)p.BH, 8), kThreads, 0, st>>>(lp);
+      landmark_finalize_kernel<<<dim3((unsigned)p.BH, 16), kThreads, 0, st>>>(lp);
     }
     if (L.end("landmark_finalize")) return L.status;
     }

@@ -617,7 +617,7 @@ dqt_reduce2_kernel(const float* partB, int nchunk, const float* dqt_ns, float* d
 
 // Landmarks from the pooling pass's raw segment sums: qt / kt [BH][m][D] = scale * sum / len,
 // plus the 16-bit copy of qt_mul * qt (rows m..MP-1 zero) for the tensor-core column pass.
-// grid (BH, slices): slice y owns landmark rows y, y + slices, ...
+// grid (BH, parts): the CTAs of a slice share its groups of four columns.
 struct LandmarkFinalizeParams {
   const float* land_partial;  // [2][BH][m][C][D]
   int C;
@@ -632,20 +632,26 @@ __global__ void __launch_bounds__(kThreads) landmark_finalize_kernel(LandmarkFin
   const int64_t bh = blockIdx.x;
   const int m = p.m, D = p.D, rows = p.qt16 ? p.MP : m;
   Segments sg(p.N, m);
-  for (int l = blockIdx.y; l < rows; l += gridDim.y) {
-    for (int e = threadIdx.x; e < 2 * D; e += kThreads) {
-      const int which = e / D, d = e - which * D;
-      float val = 0.f;
-      if (l < m) {
-        const float* src = p.land_partial + ((((size_t)which * p.BH + bh) * m + l) * p.C) * D + d;
-        float s = 0.f;
-        for (int c = 0; c < p.C; ++c) s += src[(size_t)c * D];
-        val = s * (p.scale / (float)sg.len(l));
-        (which ? p.kt : p.qt)[(bh * m + l) * D + d] = val;
+  // an item = four consecutive columns of one landmark row of Q~ or K~ (D is a multiple of 16)
+  const int per_row = 2 * D / 4;
+  for (int item = blockIdx.y * kThreads + threadIdx.x; item < rows * per_row; item += gridDim.y * kThreads) {
+    const int l = item / per_row, r = item - l * per_row;
+    const int which = r / (D / 4), d = (r - which * (D / 4)) * 4;
+    float4 val = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (l < m) {
+      const float* src = p.land_partial + ((((size_t)which * p.BH + bh) * m + l) * p.C) * D + d;
+      for (int c = 0; c < p.C; ++c) {
+        const float4 x = *reinterpret_cast<const float4*>(src + (size_t)c * D);
+        val.x += x.x; val.y += x.y; val.z += x.z; val.w += x.w;
       }
-      if (which == 0 && p.qt16)
-        store16(reinterpret_cast<char*>(p.qt16) + (size_t)bh * p.MP * D * 2, p.dtype, (size_t)l * D + d, val * p.qt16_mul);
+      const float f = p.scale / (float)sg.len(l);
+      val = make_float4(val.x * f, val.y * f, val.z * f, val.w * f);
+      *reinterpret_cast<float4*>((which ? p.kt : p.qt) + (bh * m + l) * D + d) = val;
     }
+    if (which == 0 && p.qt16)
+      *reinterpret_cast<uint2*>(reinterpret_cast<char*>(p.qt16) + ((size_t)bh * p.MP * D + (size_t)l * D + d) * 2) =
+          make_uint2(pack2x16(p.dtype, val.x * p.qt16_mul, val.y * p.qt16_mul),
+                     pack2x16(p.dtype, val.z * p.qt16_mul, val.w * p.qt16_mul));
   }
 }
 
