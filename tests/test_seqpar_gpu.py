@@ -52,6 +52,8 @@ def _run_virtual_ranks(q, k, v, dO, m, J, kappa, world):
     (torch.float16, (1, 2, 2048, 64, 64, 6, 0.0)),
     (torch.float16, (2, 1, 1024, 64, 32, 6, 5.0)),
     (torch.float32, (1, 2, 512, 32, 16, 6, 0.0)),
+    # more than 64 landmarks: the landmark-sized stages run as thread-block clusters
+    (torch.float16, (1, 2, 2048, 128, 128, 6, 5.0)),
 ])
 def test_virtual_ranks_match_oracle(cuda_device, world, dtype, shape):
     B, H, N, D, m, J, kappa = shape
