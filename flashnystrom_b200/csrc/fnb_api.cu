@@ -154,31 +154,39 @@ struct Fork {
 static std::mutex g_smem_mutex;
 static std::map<std::pair<const void*, int>, size_t> g_smem_set;
 
-template <class K>
-static int set_smem(K kernel, size_t bytes, int max_optin, const char* name) {
-  if ((long long)bytes > (long long)max_optin)
-    return fail(FNB_ERR_SMEM, "insufficient smem for %s: needs %zu bytes, device allows %d", name,
-                bytes, max_optin);
+// Raises a kernel's opt-in dynamic shared memory size to `bytes` (never lowers it: the largest size asked
+// for so far is remembered per kernel and device, and launches that need less skip the call).
+static cudaError_t raise_smem(const void* kernel, size_t bytes) {
   int device = 0;
   if (cudaGetDevice(&device) != cudaSuccess) device = -1;
-  const std::pair<const void*, int> key(reinterpret_cast<const void*>(kernel), device);
+  const std::pair<const void*, int> key(kernel, device);
   if (device >= 0) {
     std::lock_guard<std::mutex> lock(g_smem_mutex);
     auto it = g_smem_set.find(key);
-    if (it != g_smem_set.end() && it->second >= bytes) return 0;
+    if (it != g_smem_set.end() && it->second >= bytes) return cudaSuccess;
   }
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
   // ask for the largest shared-memory carveout so that co-residency is limited by the kernel's
   // own footprint, not by the driver's default split between L1 and shared memory
   if (e == cudaSuccess)
     e = cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+  if (e == cudaSuccess && device >= 0) {
+    std::lock_guard<std::mutex> lock(g_smem_mutex);
+    size_t& cur = g_smem_set[key];
+    if (cur < bytes) cur = bytes;
+  }
+  return e;
+}
+
+template <class K>
+static int set_smem(K kernel, size_t bytes, int max_optin, const char* name) {
+  if ((long long)bytes > (long long)max_optin)
+    return fail(FNB_ERR_SMEM, "insufficient smem for %s: needs %zu bytes, device allows %d", name,
+                bytes, max_optin);
+  cudaError_t e = raise_smem(reinterpret_cast<const void*>(kernel), bytes);
   if (e != cudaSuccess)
     return fail(FNB_ERR_CUDA, "cudaFuncSetAttribute(%s, %zu) failed: %s", name, bytes,
                 cudaGetErrorString(e));
-  if (device >= 0) {
-    std::lock_guard<std::mutex> lock(g_smem_mutex);
-    g_smem_set[key] = bytes;
-  }
   return 0;
 }
 
@@ -1374,10 +1382,7 @@ int fnb_kernel_report(int device, fnb_kernel_info* out, int cap) {
     o.threads = k.threads;
     int nb = 0;
     // the same attributes the launches set (set_smem): opt-in dynamic size, largest shared-memory carveout
-    if (k.dyn_smem > 0) {
-      cudaFuncSetAttribute(k.fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)k.dyn_smem);
-      cudaFuncSetAttribute(k.fn, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
-    }
+    if (k.dyn_smem > 0 && raise_smem(k.fn, k.dyn_smem) != cudaSuccess) cudaGetLastError();
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, k.fn, k.threads, k.dyn_smem) != cudaSuccess) { cudaGetLastError(); nb = -1; }
     o.blocks_per_sm = nb;
     ++n;

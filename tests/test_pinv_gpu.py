@@ -130,3 +130,19 @@ def test_probe_occupancy_lists_the_kernels(cuda_device):
     assert all(r["registers"] > 0 and r["threads"] > 0 and r["blocks_per_sm"] >= 1 for r in rep)
     assert by["tc_fwd_c<half,64,64>"]["dynamic_smem_bytes"] * 2 < 227 * 1024
     assert by["tc_fwd_c<half,64,64>"]["registers"] * 320 * 2 <= 65536
+
+
+def test_probe_occupancy_leaves_the_kernels_usable(cuda_device):
+    """The report asks for the shared memory of the 64-landmark / 3-tap instances; a call that needs more
+    of the same kernels (128 landmarks, a 33-tap convolution) has to work before and after it."""
+    from flashnystrom_b200 import _C
+    q, k, v, dO = O.make_inputs(1, 2, 1024, 128, seed=11, dtype=torch.float16)
+    q, k, v = q.cuda(), k.cuda(), v.cuda()
+    w = torch.randn(2, 33, device="cuda")
+    first = _C.forward(q, k, v, 128, 6)[0]
+    conv_first = _C.conv_residual(v, w)
+    _C.probe_occupancy(0)
+    again = _C.forward(q, k, v, 128, 6)[0]
+    conv_again = _C.conv_residual(v, w)
+    torch.cuda.synchronize()
+    assert torch.equal(first, again) and torch.equal(conv_first, conv_again)
